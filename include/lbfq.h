@@ -1,0 +1,231 @@
+/*
+ * lbfq.h -- C ABI of the B200 (sm_100a) fake-quant attention library.
+ *
+ * Every entry point is `extern "C"`, takes plain device pointers, sizes and a
+ * CUDA stream (as `void*`, i.e. a `cudaStream_t`), returns 0 on success or a
+ * negative LBFQ_ERR_* code, never throws and never allocates device memory:
+ * the caller owns inputs, outputs and any workspace. After a non-zero return
+ * `lbfq_last_error()` holds a message for the calling thread.
+ *
+ * Each declaration names the function of the reference project
+ * (DongyunZou/low-bit-attention-fake-quant, paths relative to its root) whose
+ * device work it replaces.
+ *
+ * Tensor conventions
+ *   NHD  : (B, S, H, D) contiguous -- the reference's public layout.
+ *   BHSD : (B, H, S_pad, D) contiguous, S_pad >= S; rows S..S_pad-1 are
+ *          written as zero codes by the quantizers.
+ *   BHDS : (B, H, D, S_pad) contiguous (token index fastest) -- the layout the
+ *          attention kernel wants for V.
+ *   D is 64 or 128. Codes are e4m3 ("fn": no inf, max 448) bytes.
+ */
+#ifndef LBFQ_H_
+#define LBFQ_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ------------------------------------------------------- */
+#define LBFQ_OK 0
+#define LBFQ_ERR_ARG (-1)         /* bad shape / divisibility / mode (ValueError in the host mirror) */
+#define LBFQ_ERR_DTYPE (-2)       /* unsupported element type (TypeError) */
+#define LBFQ_ERR_UNSUPPORTED (-3) /* valid in the reference, not built here yet */
+#define LBFQ_ERR_CUDA (-4)        /* a CUDA runtime / driver call failed */
+#define LBFQ_ERR_DEVICE (-5)      /* a kernel reported a bounded-wait timeout */
+
+/* ---- element types of floating-point tensors ----------------------------- */
+#define LBFQ_F32 0
+#define LBFQ_F16 1
+#define LBFQ_BF16 2
+
+/* ---- layouts of code tensors written by the quantizers ------------------- */
+#define LBFQ_LAYOUT_NHD 0
+#define LBFQ_LAYOUT_BHSD 1
+#define LBFQ_LAYOUT_BHDS 2
+
+const char* lbfq_last_error(void);
+/* ABI version of this header; bumped when a signature changes. */
+int lbfq_abi_version(void);
+
+/* ======================= quantizers (quant_triton.py) ===================== */
+
+/* fp8_block_quant, src/low_bit_fake_quant/quant_triton.py:26-77.
+ * x: NHD of `dtype`. scale: fp32 (B, S/block_s, H). codes: `layout`, with
+ * `s_pad` rows per (b,h) when layout != NHD. */
+int lbfq_fp8_block_quant(const void* x, int dtype, int B, int S, int H, int D, int block_s,
+                         uint8_t* codes, int layout, int s_pad, float* scale, void* stream);
+
+/* fp8_block_dequant, quant_triton.py:80-131. codes NHD -> out NHD of out_dtype. */
+int lbfq_fp8_block_dequant(const uint8_t* codes, const float* scale, int B, int S, int H, int D,
+                           int block_s, void* out, int out_dtype, void* stream);
+
+/* fp8_per_channel_quant, quant_triton.py:134-176. scale: fp32 (B, H, D). */
+int lbfq_fp8_channel_quant(const void* x, int dtype, int B, int S, int H, int D,
+                           uint8_t* codes, int layout, int s_pad, float* scale, void* stream);
+
+/* fp8_per_channel_dequant, quant_triton.py:179-218. */
+int lbfq_fp8_channel_dequant(const uint8_t* codes, const float* scale, int B, int S, int H, int D,
+                             void* out, int out_dtype, void* stream);
+
+/* mxfp8_qk_quant, quant_triton.py:221-271. scale: fp32 (B, S, H, D/block_d)
+ * holding 2**e. If `scale_e8` is non-null it also receives the biased
+ * exponents e+127 as bytes, (B, H, s_pad, D/block_d), for the block-scaled MMA. */
+int lbfq_mxfp8_qk_quant(const void* x, int dtype, int B, int S, int H, int D, int block_d,
+                        uint8_t* codes, int layout, int s_pad, float* scale, uint8_t* scale_e8,
+                        void* stream);
+
+/* mxfp8_qk_dequant, quant_triton.py:274-319. */
+int lbfq_mxfp8_qk_dequant(const uint8_t* codes, const float* scale, int B, int S, int H, int D,
+                          int block_d, void* out, int out_dtype, void* stream);
+
+/* mxfp8_v_quant, quant_triton.py:322-369 (blocks run along S). scale: fp32
+ * (B, S/block_s, H, D). */
+int lbfq_mxfp8_v_quant(const void* x, int dtype, int B, int S, int H, int D, int block_s,
+                       uint8_t* codes, int layout, int s_pad, float* scale, void* stream);
+
+/* mxfp8_v_dequant, quant_triton.py:372-416. */
+int lbfq_mxfp8_v_dequant(const uint8_t* codes, const float* scale, int B, int S, int H, int D,
+                         int block_s, void* out, int out_dtype, void* stream);
+
+/* ================= smoothing / rotation (preprocess.py, hadamard.py) ====== */
+
+/* smooth_k, src/low_bit_fake_quant/preprocess.py:10-57. k, out: NHD of dtype;
+ * mean: fp32 (B, H, D). `partial` is caller scratch of
+ * lbfq_smooth_k_scratch_floats(B,S,H,D) floats. */
+int64_t lbfq_smooth_k_scratch_floats(int B, int S, int H, int D);
+int lbfq_smooth_k(const void* k, int dtype, int B, int S, int H, int D, void* out, float* mean,
+                  float* partial, void* stream);
+
+/* group_mean_q (preprocess.py:60-91,169-193) and smooth_v_per_block
+ * (preprocess.py:94-166): subtract the column mean of each `block`-row group.
+ * mean: fp32 (B, S/block, H, D). */
+int lbfq_block_mean_sub(const void* x, int dtype, int B, int S, int H, int D, int block,
+                        void* out, float* mean, void* stream);
+
+/* apply_qk_hadamard / hadamard_transform_last_dim,
+ * src/low_bit_fake_quant/hadamard.py:25-117: out = FWHT_D(x * sign[h]) * scale,
+ * rounded once into dtype. signs: int8 (H, D) of +-1 on the device, or NULL. */
+int lbfq_hadamard(const void* x, int dtype, int64_t rows, int H, int D, const int8_t* signs,
+                  float scale, void* out, void* stream);
+
+/* ======================= k-means reorder (kmeans.py) ====================== */
+
+/* Lloyd iterations replacing flash_kmeans.batch_kmeans_Euclid as called from
+ * src/low_bit_fake_quant/kmeans.py:77-81. x: NHD of dtype. labels: int32
+ * (B*H, S). `bh_offset` is the global index of slab 0 (for sharded runs).
+ * scratch: lbfq_kmeans_scratch_bytes(...) bytes. */
+int64_t lbfq_kmeans_scratch_bytes(int B, int S, int H, int D, int k);
+int lbfq_kmeans_labels(const void* x, int dtype, int B, int S, int H, int D, int k, int iters,
+                       int seed, int bh_offset, int32_t* labels, void* scratch, void* stream);
+
+/* kmeans.py:84-88: order = stable argsort(labels), inverse[order[j]] = j.
+ * labels int32 (BH, S), values in [0, k); order / inverse int64 (BH, S). */
+int lbfq_label_order(const int32_t* labels, int BH, int S, int k, int64_t* order,
+                     int64_t* inverse, void* stream);
+
+/* kmeans.py:89-90 and apply_kv_permutation (kmeans.py:126-135):
+ * out[b, j, h, :] = x[b, index[b*H+h, j], h, :], NHD -> NHD of the same dtype. */
+int lbfq_gather_rows(const void* x, int dtype, int B, int S, int H, int D, const int64_t* index,
+                     void* out, void* stream);
+
+/* ================== qm . K_smooth correction (attention.py) =============== */
+
+/* The per-key bias of the Q-smoothing correction (attention_triton.py:156-160)
+ * and its row max (_estimate_rowmax_from_qm_k, attention.py:366-395):
+ *   corr[b,h,g,n]   = (sum_d qm[b,g,h,d] * k_smooth[b,n,h,d]) * sm_scale   (fp32)
+ *   rowmax[b,h,g]   = max_n corr[b,h,g,n]
+ * qm: fp32 (B, G, H, D); k_smooth: NHD of dtype; corr: fp32 (B, H, G, s_pad),
+ * columns >= S zero-filled; rowmax: fp32 (B, H, G), may be NULL. */
+int lbfq_qm_corr(const float* qm, const void* k_smooth, int dtype, int B, int S, int H, int D, int G,
+                 float sm_scale, float* corr, int s_pad, float* rowmax, void* stream);
+
+/* ========================= streaming attention ============================ */
+
+/* P quantisation modes (attention_triton.py:78) */
+#define LBFQ_P_ELEMENTWISE 0
+#define LBFQ_P_MX 1
+#define LBFQ_P_DYNAMIC 2
+/* V quantisation kinds */
+#define LBFQ_V_CHANNEL 0
+#define LBFQ_V_BLOCK 1
+#define LBFQ_V_MX 2
+/* Q/K quantisation kinds */
+#define LBFQ_QK_FP8_BLOCK 0
+#define LBFQ_QK_MX 1
+/* BLASST fill kinds (attention_triton.py:39-45) */
+#define LBFQ_FILL_ZERO 0
+#define LBFQ_FILL_MAX 1
+#define LBFQ_FILL_MEAN 2
+#define LBFQ_FILL_LOGN 3
+#define LBFQ_FILL_SAMPLE8 4
+#define LBFQ_FILL_THR 5
+#define LBFQ_FILL_UTA 6
+
+/* Operands of one launch of the streaming kernel that replaces
+ * `_fake_quant_attn_fwd_kernel` / `fake_quant_attention_triton`
+ * (src/low_bit_fake_quant/attention_triton.py:48-671). Field names follow the
+ * reference kernel's arguments. All pointers are device pointers; optional
+ * ones are NULL when the feature is off. */
+typedef struct lbfq_attn_args {
+  int B, H, M, N, D;          /* M query rows, N keys per (b,h) */
+  int m_pad, n_pad;           /* allocated rows of q_codes / k_codes,v_codes per (b,h); multiples of 128 */
+  /* fp8 operands */
+  const uint8_t* q_codes;     /* BHSD (B,H,m_pad,D) */
+  const uint8_t* k_codes;     /* BHSD (B,H,n_pad,D) */
+  const uint8_t* v_codes;     /* BHDS (B,H,D,n_pad) */
+  /* Q/K scales */
+  int qk_kind;                /* LBFQ_QK_* */
+  const float* q_scale;       /* fp8_block: (B, M/qk_block, H) */
+  const float* k_scale;       /* fp8_block: (B, N/qk_block, H) */
+  int qk_block;               /* fp8_block_size */
+  const uint8_t* q_scale_e8;  /* mx: (B,H,m_pad,D/32) biased exponents */
+  const uint8_t* k_scale_e8;  /* mx: (B,H,n_pad,D/32) */
+  /* V scales */
+  int v_kind;                 /* LBFQ_V_* */
+  const float* v_scale;       /* channel: (B,H,D); block: (B, N/v_block, H); mx: (B, N/v_block, H, D) */
+  int v_block;                /* v_fp8_block_size or v_mxfp8_block_size */
+  /* softmax */
+  float sm_scale;
+  float p_max_offset;
+  int p_kind;                 /* LBFQ_P_* */
+  int block_m, block_n;       /* p_requant_block_m / _n of the reference launch */
+  /* V smoothing correction (attention_triton.py:378-383) */
+  const float* v_alpha;       /* (B, N/v_smooth_block, H, D) or NULL */
+  int v_smooth_block;
+  /* Q smoothing correction: per-key bias precomputed by lbfq_qm_corr */
+  const float* qm_corr;       /* (B,H,G,corr_stride) or NULL */
+  int q_smooth_block;
+  int corr_stride;
+  /* row-max modes */
+  const float* rowmax_est;    /* (B,H,M) or NULL (attention_triton.py:126-129) */
+  const float* rowmax_init;   /* (B,H,M) or NULL (attention_triton.py:130-133) */
+  /* BLASST */
+  int use_blasst;
+  float blasst_lambda;
+  int fill_kind;
+  float fill_alpha;
+  int uta_bins;
+  float* blasst_stats;        /* (ceil(M/block_m), B*H, 2) fp32, zero-initialised by the caller, or NULL */
+  /* output */
+  void* out;                  /* rows written through out_row_index when given */
+  int out_dtype;              /* LBFQ_BF16 / LBFQ_F16 / LBFQ_F32 (kernel rounds to BF16 first unless F32 debug) */
+  int out_layout;             /* LBFQ_LAYOUT_NHD (B,M,H,D) or LBFQ_LAYOUT_BHSD (B,H,M,D) */
+  const int64_t* out_row_index; /* (B*H, M): destination row of kernel row r (inverse Q reorder fused), or NULL */
+  int out_fp32_exact;         /* 1: store the FP32 accumulator result without the BF16 rounding */
+  int32_t* status;            /* device int: set non-zero if a bounded wait expired */
+} lbfq_attn_args;
+
+/* Bytes of caller-provided scratch the launch below needs (0 when V smoothing is off). */
+int64_t lbfq_attention_workspace_bytes(const lbfq_attn_args* args);
+
+/* Replaces the launch in fake_quant_attention_triton (attention_triton.py:626-668).
+ * `workspace` holds lbfq_attention_workspace_bytes(args) bytes (may be NULL when that is 0). */
+int lbfq_attention_fwd(const lbfq_attn_args* args, void* workspace, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LBFQ_H_ */

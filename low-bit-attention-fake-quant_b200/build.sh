@@ -1,0 +1,19 @@
+#!/usr/bin/env bash
+# Builds liblbfq.so (sm_100a) next to this script. nvcc cross-compiles without a GPU.
+set -euo pipefail
+here="$(cd "$(dirname "${BASH_SOURCE[0]}")" && pwd)"
+NVCC="${NVCC:-/usr/local/cuda/bin/nvcc}"
+FLAGS=(-gencode arch=compute_100a,code=sm_100a -lineinfo -O3 -std=c++17 --expt-relaxed-constexpr
+       -Xcompiler -fPIC -I"$here/../include" ${LBFQ_NVCC_EXTRA:-})
+mkdir -p "$here/build"
+objs=()
+for f in api quant preprocess kmeans attention; do
+  src="$here/csrc/$f.cu"; obj="$here/build/$f.o"
+  if [[ ! -f "$obj" || "$src" -nt "$obj" || "$here/csrc/common.cuh" -nt "$obj" || "$here/../include/lbfq.h" -nt "$obj" ]]; then
+    "$NVCC" "${FLAGS[@]}" -c "$src" -o "$obj" &
+  fi
+  objs+=("$obj")
+done
+wait
+"$NVCC" -shared -o "$here/liblbfq.so" "${objs[@]}" -lcudart
+echo "built $here/liblbfq.so"

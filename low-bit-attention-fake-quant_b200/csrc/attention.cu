@@ -1,0 +1,878 @@
+// Streaming fake-quant attention for sm_100a: real FP8 tensor-core MMAs.
+//
+// Replaces `_fake_quant_attn_fwd_kernel` and its launcher
+// (src/low_bit_fake_quant/attention_triton.py:48-671). The reference feeds
+// de-quantised BF16 operands to BF16 `tl.dot`; here the e4m3 codes themselves
+// are the MMA operands and every scale is applied in FP32 around the MMA:
+//
+//   S  = (Qc . Kc^T) * ((sq * sk) * sm_scale) [+ corr]      tcgen05.mma kind::f8f6f4, SS form,
+//                                                           operands TMA-staged (128B swizzle),
+//                                                           accumulator in tensor memory (TMEM)
+//   P  = exp2((S - m) * log2e [+ offset]) -> e4m3           one thread per row, registers only
+//   PV = Pc . Vc                                            tcgen05.mma, A = P read from TMEM (TS form),
+//                                                           B = V^T tile (keys contiguous) + 16 rows of 1.0
+//   A' = A' * alpha + c * (PV [* sv_d] + rowsum(Pc) * alpha_v')   FP32 registers, once per key block
+//
+// The per-(row, key block) arithmetic (running max, rescale factor alpha, the
+// three P quantisers, V block scale, V-alpha correction, estimated-row-max
+// thresholds, BLASST skip / fill and its counters) follows the reference kernel
+// line by line; key blocks are walked in order with the reference's BLOCK_N so
+// that every rounding decision of P sees the same running max.
+//
+// CTA = 256 query rows of one (b, h): two softmax warpgroups (one 128-row tile
+// each, thread == row == TMEM lane), one TMA producer warp, one MMA-issuing warp
+// per tile. K / V^T arrive in 128-key stages shared by both tiles. The extra 16
+// rows of ones appended to every V^T stage make column D of the PV accumulator
+// equal to rowsum(Pc), which the V-smoothing correction needs, for free.
+// Every mbarrier wait is bounded; on expiry the kernel raises `*status`, all
+// roles leave their loops, TMEM is released and the launch returns.
+
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
+#include "common.cuh"
+
+namespace lbfq {
+namespace attn {
+
+constexpr int kTileM = 128;              // rows per softmax warpgroup
+constexpr int kCtaM = 2 * kTileM;        // rows per CTA
+constexpr int kChunk = 128;              // keys per TMA stage
+constexpr int kStages = 3;
+constexpr int kThreads = 384;            // 2 softmax warpgroups + 1 warpgroup of service warps
+constexpr int kOnesRows = 16;
+constexpr unsigned long long kWaitCycles = 1000000000ull;   // ~0.5 s: far above any legitimate wait
+
+// ---------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait. Returns false when the wait was given up (here or elsewhere in
+// the CTA); the caller must then leave its loop.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int32_t* status,
+                                          int code) {
+  if (mbar_try(bar, parity)) return true;
+  const unsigned long long t0 = clock64();
+  uint32_t spins = 0;
+  while (true) {
+    if (mbar_try(bar, parity)) return true;
+    if ((++spins & 63u) == 0) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > kWaitCycles) {
+        *abort_flag = 1;
+        if (status) atomicCAS(status, 0, code);
+        return false;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// D[tmem] (+)= A[smem desc] . B[smem desc]^T
+__device__ __forceinline__ void mma_f8_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc) : "memory");
+}
+// D[tmem] (+)= A[tmem] . B[smem desc]^T
+__device__ __forceinline__ void mma_f8_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(acc) : "memory");
+}
+
+#define LBFQ_TMEM_LD32(r, addr)                                                                            \
+  asm volatile(                                                                                           \
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "                                                           \
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "                           \
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"           \
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),   \
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),         \
+        "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]),       \
+        "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]),       \
+        "=r"(r[29]), "=r"(r[30]), "=r"(r[31])                                                            \
+      : "r"(addr) : "memory")
+
+__device__ __forceinline__ uint32_t tmem_ld1(uint32_t addr) {
+  uint32_t v;
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(v) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void tmem_st8(uint32_t addr, const uint32_t* r) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+               ::"r"(addr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+               : "memory");
+}
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// K-major shared-memory matrix descriptor (Blackwell format, version 1):
+// rows of `row_bytes` (128 -> 128B swizzle, 64 -> 64B swizzle), 8-row atoms
+// packed back to back (stride byte offset = 8 * row_bytes).
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, int row_bytes) {
+  const uint64_t layout = row_bytes == 128 ? 2ull : (row_bytes == 64 ? 4ull : 6ull);
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr >> 4) & 0x3fffu);
+  d |= (uint64_t)1 << 16;                                  // leading byte offset: unused for swizzled K-major
+  d |= (uint64_t)(((8u * row_bytes) >> 4) & 0x3fffu) << 32;
+  d |= (uint64_t)1 << 46;                                  // descriptor version
+  d |= layout << 61;
+  return d;
+}
+// kind::f8f6f4, A = B = e4m3, FP32 accumulator, both operands K-major, M = 128.
+__host__ __device__ constexpr uint32_t make_idesc(int n) {
+  return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+}
+
+// ---------------------------------------------------------------------------
+// kernel parameters (a device-side copy of lbfq_attn_args, pre-digested)
+// ---------------------------------------------------------------------------
+struct Params {
+  int B, H, M, N, D;
+  int qk_block;
+  const float* q_scale;
+  const float* k_scale;
+  int v_kind;
+  const float* v_scale;
+  int v_block;
+  float sm_scale, p_off;
+  int p_kind;
+  int block_m;
+  const float* v_alpha;        // pre-divided by the V scale it rides on (alpha')
+  int v_smooth_block;
+  const float* corr;
+  int q_smooth_block, corr_stride, n_groups;
+  const float* rowmax_est;
+  const float* rowmax_init;
+  int rm_mode;                 // 0 online, 1 frozen estimate, 2 estimate with thresholds
+  float log_lambda, lambda;
+  int fill_kind;
+  float fill_alpha;
+  int uta_bins;
+  float* stats;
+  void* out;
+  int out_dtype, out_layout, out_exact;
+  const int64_t* out_row_index;
+  int32_t* status;
+};
+
+template <int D, int BN>
+struct Smem {
+  static constexpr int kQ = kTileM * D;                       // bytes per Q tile
+  static constexpr int kK = kChunk * D;                       // bytes per K stage
+  static constexpr int kV = (D + kOnesRows) * kChunk;         // bytes per V^T stage (with the rows of ones)
+  static constexpr int offQ = 0;
+  static constexpr int offK = offQ + 2 * kQ;
+  static constexpr int offV = offK + kStages * kK;
+  static constexpr int offBar = offV + kStages * kV;
+  static constexpr int kNumBar = 2 + 4 * kStages + 8;
+  static constexpr int offMisc = offBar + kNumBar * 8;
+  static constexpr int total = offMisc + 64;
+};
+
+// ---------------------------------------------------------------------------
+// the kernel
+// ---------------------------------------------------------------------------
+template <int D, int BN, bool BLASST>
+__global__ void __launch_bounds__(kThreads, 1)
+attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+            const __grid_constant__ CUtensorMap tm_v, const Params p) {
+  using SM = Smem<D, BN>;
+  constexpr int NSUB = kChunk / BN;                // key blocks per stage
+  constexpr int PV_N = D + kOnesRows;              // PV accumulator columns
+  constexpr int TCOLS = 256;                       // TMEM columns per tile
+  constexpr int COL_S = 0, COL_P = 64, COL_O = 96;
+  static_assert(BN == 32 || BN == 64, "block_n of 32 or 64");
+  static_assert(COL_O + PV_N <= TCOLS, "TMEM budget");
+
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const uint32_t sbase = smem_u32(smem);
+  const uint32_t bar0 = sbase + SM::offBar;
+  // barrier map
+  auto BAR_QFULL = [&](int t) { return bar0 + 8u * t; };
+  auto BAR_KFULL = [&](int s) { return bar0 + 8u * (2 + s); };
+  auto BAR_VFULL = [&](int s) { return bar0 + 8u * (2 + kStages + s); };
+  auto BAR_KFREE = [&](int s) { return bar0 + 8u * (2 + 2 * kStages + s); };
+  auto BAR_VFREE = [&](int s) { return bar0 + 8u * (2 + 3 * kStages + s); };
+  auto BAR_SFULL = [&](int t) { return bar0 + 8u * (2 + 4 * kStages + t); };
+  auto BAR_SFREE = [&](int t) { return bar0 + 8u * (2 + 4 * kStages + 2 + t); };
+  auto BAR_PRDY = [&](int t) { return bar0 + 8u * (2 + 4 * kStages + 4 + t); };
+  auto BAR_PVFULL = [&](int t) { return bar0 + 8u * (2 + 4 * kStages + 6 + t); };
+  volatile int* misc = (volatile int*)(smem + SM::offMisc);   // [0] tmem base, [1] abort, [2..3] elide flags
+  volatile int* abort_flag = misc + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int bh = blockIdx.y;
+  const int b = bh / p.H, h = bh % p.H;
+  const int m0 = blockIdx.x * kCtaM;
+  const int nblk = (p.N + BN - 1) / BN;
+  const int nchunk = (p.N + kChunk - 1) / kChunk;
+
+  // ---- setup ----------------------------------------------------------------
+  // A CTA scheduled after some other CTA has given up a wait retires at once.
+  if (threadIdx.x == 0) misc[4] = (p.status != nullptr && *reinterpret_cast<volatile int32_t*>(p.status) != 0) ? 1 : 0;
+  __syncthreads();
+  if (misc[4]) return;
+  if (threadIdx.x == 0) {
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(BAR_QFULL(t), 1);
+      mbar_init(BAR_SFULL(t), 1);
+      mbar_init(BAR_SFREE(t), kTileM);
+      mbar_init(BAR_PRDY(t), kTileM);
+      mbar_init(BAR_PVFULL(t), 1);
+    }
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(BAR_KFULL(s), 1);
+      mbar_init(BAR_VFULL(s), 1);
+      mbar_init(BAR_KFREE(s), 2);
+      mbar_init(BAR_VFREE(s), 2);
+    }
+    misc[1] = 0; misc[2] = 0; misc[3] = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  // rows of 1.0 (e4m3 0x38) under every V^T stage
+  for (int i = threadIdx.x; i < kStages * kOnesRows * kChunk / 16; i += kThreads) {
+    const int s = i / (kOnesRows * kChunk / 16), r = i % (kOnesRows * kChunk / 16);
+    *reinterpret_cast<uint4*>(smem + SM::offV + s * SM::kV + D * kChunk + r * 16) =
+        make_uint4(0x38383838u, 0x38383838u, 0x38383838u, 0x38383838u);
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  if (warp == 8) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(sbase + SM::offMisc) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = (uint32_t)misc[0];
+
+  if (warp < 8) {
+    // =========================== softmax warpgroups ===========================
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+    const int t = warp >> 2;                                   // tile
+    const int row_in_tile = (warp & 3) * 32 + lane;
+    const int row = m0 + t * kTileM + row_in_tile;             // query row within (b, h)
+    const bool row_ok = row < p.M;
+    const int rowc = row_ok ? row : (p.M - 1);
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    const uint32_t tS = tmem_base + lane_base + t * TCOLS + COL_S;
+    const uint32_t tP = tmem_base + lane_base + t * TCOLS + COL_P;
+    const uint32_t tO = tmem_base + lane_base + t * TCOLS + COL_O;
+
+    const float sq = p.q_scale ? p.q_scale[((size_t)b * (p.M / p.qk_block) + rowc / p.qk_block) * p.H + h] : 1.f;
+    const float* corr_row = nullptr;
+    if (p.corr) {
+      const int g = ((rowc / p.block_m) * p.block_m) / p.q_smooth_block;
+      corr_row = p.corr + ((size_t)bh * p.n_groups + g) * p.corr_stride;
+    }
+    float m_i = -INFINITY;
+    float est = 0.f;
+    if (p.rowmax_est) { est = p.rowmax_est[(size_t)bh * p.M + rowc]; m_i = est; }
+    else if (p.rowmax_init) { m_i = p.rowmax_init[(size_t)bh * p.M + rowc]; }
+    float l_i = 0.f, max_seen = -INFINITY;
+    float n_skip = 0.f, n_total = 0.f;
+    float a_prev = 1.f, c_prev = 1.f;
+    bool elided_prev = false;
+    int blk_prev = 0;
+    float acc[D];
+#pragma unroll
+    for (int i = 0; i < D; ++i) acc[i] = 0.f;
+
+    // fold PV of block `jb` (scale c, rescale a) into the accumulator
+    auto accumulate = [&](int jb, float a, float c) {
+      tc_fence_after();
+      float rs = 0.f;
+      const float* av = nullptr;
+      const float* vs = nullptr;
+      if (p.v_alpha) {
+        rs = __uint_as_float(tmem_ld1(tO + D));
+        av = p.v_alpha + (((size_t)b * (p.N / p.v_smooth_block) + (jb * BN) / p.v_smooth_block) * p.H + h) * D;
+      }
+      if (p.v_kind == LBFQ_V_MX)
+        vs = p.v_scale + (((size_t)b * (p.N / p.v_block) + (jb * BN) / p.v_block) * p.H + h) * D;
+      const bool rescale = __any_sync(0xffffffffu, a != 1.f);
+#pragma unroll
+      for (int c0 = 0; c0 < D; c0 += 32) {
+        uint32_t r[32];
+        LBFQ_TMEM_LD32(r, tO + c0);
+        tc_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float v = __uint_as_float(r[i]);
+          if (vs) v *= __ldg(vs + c0 + i);
+          if (av) v = fmaf(rs, __ldg(av + c0 + i), v);
+          const float base = rescale ? acc[c0 + i] * a : acc[c0 + i];
+          acc[c0 + i] = fmaf(c, v, base);
+        }
+      }
+    };
+
+    bool alive = true;
+    for (int it = 0; it < nblk && alive; ++it) {
+      // ---- (a) fold the previous block's PV -------------------------------------
+      if (it > 0) {
+        if (!mbar_wait(BAR_PVFULL(t), (it - 1) & 1, abort_flag, p.status, 11)) { alive = false; break; }
+        if (!elided_prev) accumulate(blk_prev, a_prev, c_prev);
+      }
+      // ---- (b) S -> P -------------------------------------------------------------
+      if (!mbar_wait(BAR_SFULL(t), it & 1, abort_flag, p.status, 12)) { alive = false; break; }
+      tc_fence_after();
+      float s[BN];
+      {
+        uint32_t r[32];
+        LBFQ_TMEM_LD32(r, tS);
+        if constexpr (BN == 64) {
+          uint32_t r2[32];
+          LBFQ_TMEM_LD32(r2, tS + 32);
+          tc_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) { s[i] = __uint_as_float(r[i]); s[32 + i] = __uint_as_float(r2[i]); }
+        } else {
+          tc_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) s[i] = __uint_as_float(r[i]);
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(BAR_SFREE(t));
+
+      const int n0 = it * BN;
+      const int nvalid = min(BN, p.N - n0);
+      float f = p.sm_scale;
+      if (p.k_scale) {
+        const float sk = p.k_scale[((size_t)b * (p.N / p.qk_block) + n0 / p.qk_block) * p.H + h];
+        f = (sq * sk) * p.sm_scale;
+      }
+      float bmax = -INFINITY;
+      if (corr_row) {
+        const float4* c4 = reinterpret_cast<const float4*>(corr_row + n0);
+#pragma unroll
+        for (int i = 0; i < BN / 4; ++i) {
+          const float4 cv = __ldg(c4 + i);
+          s[4 * i + 0] = s[4 * i + 0] * f + cv.x;
+          s[4 * i + 1] = s[4 * i + 1] * f + cv.y;
+          s[4 * i + 2] = s[4 * i + 2] * f + cv.z;
+          s[4 * i + 3] = s[4 * i + 3] * f + cv.w;
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < BN; ++i) s[i] *= f;
+      }
+      if (nvalid < BN) {
+#pragma unroll
+        for (int i = 0; i < BN; ++i) if (i >= nvalid) s[i] = -INFINITY;
+      }
+#pragma unroll
+      for (int i = 0; i < BN; ++i) bmax = fmaxf(bmax, s[i]);
+
+      // ---- running max / rescale factor (attention_triton.py:164-217) ----------
+      float m_new, alpha;
+      bool skip = false;
+      if (BLASST) {
+        m_new = fmaxf(m_i, bmax);
+        skip = (bmax - m_new) < p.log_lambda;
+        alpha = skip ? 1.f : ex2((m_i - m_new) * kLog2e);
+        if (skip) m_new = m_i;
+        n_skip += (skip && row_ok) ? 1.f : 0.f;
+        n_total += row_ok ? 1.f : 0.f;
+      } else if (p.rm_mode == 2) {
+        const float seen = fmaxf(max_seen, bmax);
+        const float up = 16.0f / kLog2e, down = 32.0f / kLog2e;
+        const bool under = (bmax - m_i) > up;
+        const bool over = (m_i - seen) > down;
+        const float down_m = (l_i == 0.f) ? seen : fmaxf(seen + down, m_i - 80.0f);
+        m_new = (under || over) ? (under ? bmax : down_m) : m_i;
+        alpha = (under || over) ? ((l_i == 0.f) ? 0.f : ex2((m_i - m_new) * kLog2e)) : 1.f;
+        max_seen = seen;
+      } else if (p.rm_mode == 1) {
+        m_new = est;
+        alpha = 1.f;
+      } else {
+        m_new = fmaxf(m_i, bmax);
+        alpha = ex2((m_i - m_new) * kLog2e);
+      }
+
+      // whole-tile elision: every row of this 128-row tile skips and nothing is filled in
+      bool elide = false;
+      if (BLASST) {
+        if (p.fill_kind == LBFQ_FILL_ZERO) {
+          uint32_t all;
+          asm volatile(
+              "{\n\t.reg .pred pi, po;\n\tsetp.ne.b32 pi, %1, 0;\n\t"
+              "barrier.cta.red.and.pred po, %2, 128, pi;\n\tselp.u32 %0, 1, 0, po;\n\t}"
+              : "=r"(all) : "r"((uint32_t)(skip || !row_ok)), "r"(1 + t) : "memory");
+          elide = all != 0;
+        }
+      }
+
+      float c_blk = 1.f;
+      if (!elide) {
+        // ---- P = exp2(z), l += sum(P) (attention_triton.py:219-326) -------------
+        const float off = p.p_kind == LBFQ_P_ELEMENTWISE ? p.p_off : 0.f;
+        float stat_mean = 0.f, stat_var = 0.f;
+        if (BLASST && p.fill_kind != LBFQ_FILL_ZERO) {
+          // block statistics of the un-skipped scores, needed by the fills
+          float sum = 0.f;
+#pragma unroll
+          for (int i = 0; i < BN; ++i) sum += (i < nvalid) ? s[i] : 0.f;
+          stat_mean = sum / (float)max(nvalid, 1);
+          if (p.fill_kind == LBFQ_FILL_LOGN) {
+            float v2 = 0.f;
+#pragma unroll
+            for (int i = 0; i < BN; ++i) { const float cdev = (i < nvalid) ? s[i] - stat_mean : 0.f; v2 += cdev * cdev; }
+            stat_var = v2 / (float)max(nvalid, 1);
+          }
+        }
+        float fill_bins[(BLASST ? 16 : 1)];
+        int bin_size = BN;
+        float fill_p = 0.f;
+        bool per_bin = false;
+        if (BLASST && p.fill_kind != LBFQ_FILL_ZERO && skip) {
+          const float safe_n = (float)max(nvalid, 1);
+          const float max_bound = safe_n * ex2((bmax - m_new) * kLog2e + off);
+          if (p.fill_kind == LBFQ_FILL_MAX) {
+            fill_p = max_bound * p.fill_alpha / safe_n;
+          } else if (p.fill_kind == LBFQ_FILL_MEAN) {
+            fill_p = fminf(p.fill_alpha * safe_n * ex2((stat_mean - m_new) * kLog2e + off), max_bound) / safe_n;
+          } else if (p.fill_kind == LBFQ_FILL_LOGN) {
+            fill_p = fminf(safe_n * ex2((stat_mean + 0.5f * stat_var - m_new) * kLog2e + off), max_bound) / safe_n;
+          } else if (p.fill_kind == LBFQ_FILL_SAMPLE8) {
+            const int stride = BN >= 8 ? BN / 8 : 1;
+            float ssum = 0.f, cnt = 0.f;
+#pragma unroll
+            for (int i = 0; i < BN; ++i)
+              if ((i % stride) == 0 && i < nvalid) { ssum += ex2((s[i] - m_new) * kLog2e + off); cnt += 1.f; }
+            fill_p = fminf(p.fill_alpha * safe_n * ssum / fmaxf(cnt, 1.f), max_bound) / safe_n;
+          } else if (p.fill_kind == LBFQ_FILL_THR) {
+            const float off_scale = p.p_kind == LBFQ_P_ELEMENTWISE ? exp2f(p.p_off) : 1.f;
+            fill_p = (p.fill_alpha * safe_n * p.lambda * off_scale) / safe_n;
+          } else {                                             // UTA: one value per bin of BN / bins keys
+            per_bin = true;
+            bin_size = BN / p.uta_bins;
+#pragma unroll
+            for (int bi = 0; bi < 16; ++bi) fill_bins[bi] = 0.f;
+            // bins are contiguous column ranges; accumulate with a running bin index
+            float bsum = 0.f, bmx = -INFINITY, bcnt = 0.f;
+            int cur = 0;
+#pragma unroll
+            for (int i = 0; i < BN; ++i) {
+              if (i < nvalid) { bsum += s[i]; bmx = fmaxf(bmx, s[i]); bcnt += 1.f; }
+              if (((i + 1) % bin_size) == 0) {
+                const float safe_c = fmaxf(bcnt, 1.f);
+                const float bound = safe_c * ex2((bmx - m_new) * kLog2e + off);
+                const float mass = p.fill_alpha * safe_c * ex2((bsum / safe_c - m_new) * kLog2e + off);
+                const float val = fminf(mass, bound) / safe_c;
+#pragma unroll
+                for (int bi = 0; bi < 16; ++bi) if (bi == cur) fill_bins[bi] = val;
+                ++cur; bsum = 0.f; bmx = -INFINITY; bcnt = 0.f;
+              }
+            }
+          }
+        }
+
+        float psum = 0.f, pmax = 0.f;
+#pragma unroll
+        for (int i = 0; i < BN; ++i) {
+          float pv;
+          if (BLASST && skip) {
+            if (per_bin) {
+              float val = 0.f;
+              const int bi = i / bin_size;
+#pragma unroll
+              for (int q = 0; q < 16; ++q) if (q == bi) val = fill_bins[q];
+              pv = val;
+            } else {
+              pv = fill_p;
+            }
+          } else {
+            pv = ex2(p.p_kind == LBFQ_P_ELEMENTWISE ? fmaf(s[i] - m_new, kLog2e, off) : (s[i] - m_new) * kLog2e);
+          }
+          if (i >= nvalid) pv = 0.f;
+          s[i] = pv;
+          psum += pv;
+          pmax = fmaxf(pmax, pv);
+        }
+        l_i = l_i * alpha + psum;
+
+        // ---- P quantisation (attention_triton.py:328-360) -----------------------
+        float inv = 1.f;
+        if (p.p_kind == LBFQ_P_MX) {
+          const int e = pow2_scale_exp(fmaxf(pmax, 1e-4f));
+          c_blk = pow2f(e);
+          inv = pow2f(-e);
+        } else if (p.p_kind == LBFQ_P_DYNAMIC) {
+          c_blk = __fdiv_rn(fmaxf(pmax, 1e-12f), kFp8Max);
+          inv = __fdiv_rn(1.0f, c_blk);
+        }
+        uint32_t pk[BN / 4];
+#pragma unroll
+        for (int i = 0; i < BN / 4; ++i) {
+          float q0 = s[4 * i], q1 = s[4 * i + 1], q2 = s[4 * i + 2], q3 = s[4 * i + 3];
+          if (p.p_kind != LBFQ_P_ELEMENTWISE) {
+            q0 = fminf(q0 * inv, kFp8Max); q1 = fminf(q1 * inv, kFp8Max);
+            q2 = fminf(q2 * inv, kFp8Max); q3 = fminf(q3 * inv, kFp8Max);
+          }
+          pk[i] = (uint32_t)f32x2_to_e4m3x2(q0, q1) | ((uint32_t)f32x2_to_e4m3x2(q2, q3) << 16);
+        }
+        tmem_st8(tP, pk);
+        if constexpr (BN == 64) tmem_st8(tP + 8, pk + 8);
+        tc_wait_st();
+      }
+      if (p.v_kind == LBFQ_V_BLOCK)
+        c_blk *= p.v_scale[((size_t)b * (p.N / p.v_block) + n0 / p.v_block) * p.H + h];
+      if (BLASST && row_in_tile == 0) misc[2 + t] = elide ? 1 : 0;
+      tc_fence_before();
+      mbar_arrive(BAR_PRDY(t));
+      a_prev = alpha; c_prev = c_blk; elided_prev = elide; blk_prev = it;
+      m_i = m_new;
+    }
+    if (alive) {
+      if (mbar_wait(BAR_PVFULL(t), (nblk - 1) & 1, abort_flag, p.status, 13)) {
+        if (!elided_prev) accumulate(blk_prev, a_prev, c_prev);
+      } else {
+        alive = false;
+      }
+    }
+
+    // ---- epilogue (attention_triton.py:387-407) ---------------------------------
+    if (alive && row_ok) {
+      const float inv_l = __fdiv_rn(1.0f, l_i);
+      const float* vsc = p.v_kind == LBFQ_V_CHANNEL ? p.v_scale + (size_t)bh * D : nullptr;
+      const int64_t drow = p.out_row_index ? p.out_row_index[(size_t)bh * p.M + row] : row;
+      const size_t o_off = p.out_layout == LBFQ_LAYOUT_NHD
+                               ? (((size_t)b * p.M + drow) * p.H + h) * D
+                               : ((size_t)bh * p.M + drow) * D;
+#pragma unroll
+      for (int i = 0; i < D; ++i) acc[i] = (vsc ? acc[i] * __ldg(vsc + i) : acc[i]) * inv_l;
+      if (p.out_dtype == LBFQ_F32) {
+        float4* o = reinterpret_cast<float4*>((float*)p.out + o_off);
+#pragma unroll
+        for (int i = 0; i < D / 4; ++i) {
+          float4 v = make_float4(acc[4 * i], acc[4 * i + 1], acc[4 * i + 2], acc[4 * i + 3]);
+          if (!p.out_exact) {
+            v.x = round_through<__nv_bfloat16>(v.x); v.y = round_through<__nv_bfloat16>(v.y);
+            v.z = round_through<__nv_bfloat16>(v.z); v.w = round_through<__nv_bfloat16>(v.w);
+          }
+          o[i] = v;
+        }
+      } else {
+        uint4* o = reinterpret_cast<uint4*>((uint16_t*)p.out + o_off);
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i) {
+          uint32_t w[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float x0 = acc[8 * i + 2 * j], x1 = acc[8 * i + 2 * j + 1];
+            if (p.out_dtype == LBFQ_BF16) {
+              __nv_bfloat162 hh = __floats2bfloat162_rn(x0, x1);
+              w[j] = *reinterpret_cast<uint32_t*>(&hh);
+            } else {                                           // the kernel result is BF16; then .to(float16)
+              __half2 hh = __floats2half2_rn(round_through<__nv_bfloat16>(x0), round_through<__nv_bfloat16>(x1));
+              w[j] = *reinterpret_cast<uint32_t*>(&hh);
+            }
+          }
+          o[i] = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+      }
+    }
+    if (BLASST && alive && row_ok && p.stats) {
+      const int mb = row / p.block_m;
+      atomicAdd(p.stats + ((size_t)mb * (p.B * p.H) + bh) * 2 + 0, n_skip);
+      atomicAdd(p.stats + ((size_t)mb * (p.B * p.H) + bh) * 2 + 1, n_total);
+    }
+  } else {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+  }
+  if (warp == 8) {
+    // =========================== TMA producer =====================================
+    if (lane == 0) {
+      for (int t = 0; t < 2; ++t) {
+        mbar_expect_tx(BAR_QFULL(t), SM::kQ);
+        tma_load_3d(sbase + SM::offQ + t * SM::kQ, &tm_q, 0, m0 + t * kTileM, bh, BAR_QFULL(t));
+      }
+      for (int c = 0; c < nchunk; ++c) {
+        const int st = c % kStages;
+        if (c >= kStages) {
+          const uint32_t par = ((c / kStages) - 1) & 1;
+          if (!mbar_wait(BAR_KFREE(st), par, abort_flag, p.status, 21)) break;
+          if (!mbar_wait(BAR_VFREE(st), par, abort_flag, p.status, 22)) break;
+        }
+        mbar_expect_tx(BAR_KFULL(st), SM::kK);
+        tma_load_3d(sbase + SM::offK + st * SM::kK, &tm_k, 0, c * kChunk, bh, BAR_KFULL(st));
+        mbar_expect_tx(BAR_VFULL(st), D * kChunk);
+        tma_load_3d(sbase + SM::offV + st * SM::kV, &tm_v, c * kChunk, 0, bh, BAR_VFULL(st));
+      }
+    }
+  } else if (warp == 9 || warp == 10) {
+    // =========================== MMA issuer of tile t ==============================
+    const int t = warp - 9;
+    if (lane == 0) {
+      const uint32_t tS = tmem_base + t * TCOLS + COL_S;
+      const uint32_t tP = tmem_base + t * TCOLS + COL_P;
+      const uint32_t tO = tmem_base + t * TCOLS + COL_O;
+      const uint32_t id_qk = make_idesc(BN);
+      const uint32_t id_pv = make_idesc(PV_N);
+      const uint64_t dq = make_desc(sbase + SM::offQ + t * SM::kQ, D);
+      bool ok = mbar_wait(BAR_QFULL(t), 0, abort_flag, p.status, 31);
+      auto issue_qk = [&](int j) -> bool {
+        const int c = j / NSUB, sub = j % NSUB, st = c % kStages;
+        if (sub == 0 && !mbar_wait(BAR_KFULL(st), (c / kStages) & 1, abort_flag, p.status, 32)) return false;
+        tc_fence_after();
+        const uint64_t dk = make_desc(sbase + SM::offK + st * SM::kK + sub * BN * D, D);
+#pragma unroll
+        for (int kk = 0; kk < D / 32; ++kk)
+          mma_f8_ss(tS, dq + (uint64_t)(kk * 2), dk + (uint64_t)(kk * 2), id_qk, kk > 0 ? 1u : 0u);
+        tc_commit(BAR_SFULL(t));
+        if (sub == NSUB - 1 || j == nblk - 1) tc_commit(BAR_KFREE(st));
+        return true;
+      };
+      auto issue_pv = [&](int j) -> bool {
+        const int c = j / NSUB, sub = j % NSUB, st = c % kStages;
+        if (sub == 0 && !mbar_wait(BAR_VFULL(st), (c / kStages) & 1, abort_flag, p.status, 33)) return false;
+        tc_fence_after();
+        const bool elide = BLASST && misc[2 + t] != 0;
+        if (!elide) {
+          const uint64_t dv = make_desc(sbase + SM::offV + st * SM::kV, kChunk);
+#pragma unroll
+          for (int kk = 0; kk < BN / 32; ++kk)
+            mma_f8_ts(tO, tP + kk * 8, dv + (uint64_t)((sub * BN + kk * 32) >> 4), id_pv, kk > 0 ? 1u : 0u);
+        }
+        tc_commit(BAR_PVFULL(t));
+        if (sub == NSUB - 1 || j == nblk - 1) tc_commit(BAR_VFREE(st));
+        return true;
+      };
+      if (ok) ok = issue_qk(0);
+      for (int it = 0; it < nblk && ok; ++it) {
+        if (it + 1 < nblk) {
+          ok = mbar_wait(BAR_SFREE(t), it & 1, abort_flag, p.status, 34) && issue_qk(it + 1);
+          if (!ok) break;
+        }
+        ok = mbar_wait(BAR_PRDY(t), it & 1, abort_flag, p.status, 35) && issue_pv(it);
+      }
+    }
+  }
+
+  // ---- teardown -------------------------------------------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 8) {
+    if (*abort_flag && lane == 0) {
+      // give in-flight bulk copies a bounded time to land before the CTA retires
+      const unsigned long long t0 = clock64();
+      while (clock64() - t0 < 2000000ull) { }
+    }
+    __syncwarp();
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem_base) : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------
+static PFN_cuTensorMapEncodeTiled_v12000 get_encode() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = (PFN_cuTensorMapEncodeTiled_v12000)ptr;
+  }
+  return fn;
+}
+
+// 3-D u8 tensor map: dims (inner, rows, slabs), box (box_inner, box_rows, 1)
+static int make_map(CUtensorMap* map, const void* base, uint64_t inner, uint64_t rows, uint64_t slabs,
+                    uint32_t box_inner, uint32_t box_rows) {
+  auto enc = get_encode();
+  LBFQ_REQUIRE(enc != nullptr, LBFQ_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t dims[3] = {inner, rows, slabs};
+  cuuint64_t strides[2] = {inner, inner * rows};
+  cuuint32_t box[3] = {box_inner, box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUtensorMapSwizzle sw = box_inner == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                          : box_inner == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B;
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  LBFQ_REQUIRE(r == CUDA_SUCCESS, LBFQ_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+  return LBFQ_OK;
+}
+
+template <int D, int BN, bool BLASST>
+static int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const Params& p, cudaStream_t st) {
+  using SM = Smem<D, BN>;
+  const int smem_bytes = SM::total + 1024;
+  auto kern = attn_kernel<D, BN, BLASST>;
+  LBFQ_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+  dim3 grid((p.M + kCtaM - 1) / kCtaM, p.B * p.H, 1);
+  kern<<<grid, kThreads, smem_bytes, st>>>(mq, mk, mv, p);
+  return check_launch("attn_kernel");
+}
+
+}  // namespace attn
+}  // namespace lbfq
+
+using namespace lbfq;
+
+// v_alpha' = v_alpha / (the V scale that multiplies the same PV term)
+__global__ void alpha_prep_kernel(const float* __restrict__ alpha, float* __restrict__ out, const float* __restrict__ vscale,
+                                  int v_kind, int B, int NB, int H, int D, int blocks_per_vblock_num, int blocks_per_vblock_den) {
+  const size_t total = (size_t)B * NB * H * D;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const int d = (int)(i % D);
+    const int h = (int)((i / D) % H);
+    const int nb = (int)((i / D / H) % NB);
+    const int b = (int)(i / D / H / NB);
+    float a = alpha[i];
+    if (v_kind == LBFQ_V_CHANNEL) {
+      a = __fdiv_rn(a, vscale[((size_t)b * H + h) * D + d]);
+    } else if (v_kind == LBFQ_V_BLOCK) {
+      // smoothing block nb covers keys [nb * vsb, ...); its V-scale block index = nb * vsb / v_block
+      const int vb = (int)(((int64_t)nb * blocks_per_vblock_num) / blocks_per_vblock_den);
+      const int nvb = (int)(((int64_t)NB * blocks_per_vblock_num) / blocks_per_vblock_den);
+      a = __fdiv_rn(a, vscale[((size_t)b * nvb + vb) * H + h]);
+    }
+    out[i] = a;
+  }
+}
+
+extern "C" int64_t lbfq_attention_workspace_bytes(const lbfq_attn_args* a) {
+  if (!a || !a->v_alpha) return 0;
+  return (int64_t)a->B * (a->N / (a->v_smooth_block > 0 ? a->v_smooth_block : 1)) * a->H * a->D * 4;
+}
+
+extern "C" int lbfq_attention_fwd(const lbfq_attn_args* a, void* workspace, void* stream) {
+  using namespace lbfq::attn;
+  LBFQ_REQUIRE(a != nullptr, LBFQ_ERR_ARG, "null argument block");
+  LBFQ_REQUIRE(a->B > 0 && a->H > 0 && a->M > 0 && a->N > 0, LBFQ_ERR_ARG, "empty attention problem");
+  LBFQ_REQUIRE(a->D == 64 || a->D == 128, LBFQ_ERR_ARG, "head dim must be 64 or 128; got %d", a->D);
+  LBFQ_REQUIRE(a->block_n == 32 || a->block_n == 64, LBFQ_ERR_UNSUPPORTED,
+               "block_n=%d: this build has key blocks of 32 or 64", a->block_n);
+  LBFQ_REQUIRE(a->block_m > 0, LBFQ_ERR_ARG, "block_m must be positive");
+  LBFQ_REQUIRE(a->m_pad >= a->M && a->m_pad % 128 == 0 && a->n_pad >= a->N && a->n_pad % 128 == 0, LBFQ_ERR_ARG,
+               "m_pad / n_pad must cover M / N and be multiples of 128");
+  LBFQ_REQUIRE(a->q_codes && a->k_codes && a->v_codes && a->out, LBFQ_ERR_ARG, "null operand pointer");
+  LBFQ_REQUIRE(a->qk_kind == LBFQ_QK_FP8_BLOCK, LBFQ_ERR_UNSUPPORTED,
+               "block-scaled (mxfp8) Q/K operands go through lbfq_attention_fwd_mx");
+  LBFQ_REQUIRE(a->q_scale && a->k_scale && a->qk_block > 0, LBFQ_ERR_ARG, "fp8_block Q/K needs scales and a block size");
+  LBFQ_REQUIRE(a->M % a->qk_block == 0 && a->N % a->qk_block == 0, LBFQ_ERR_ARG,
+               "S must be divisible by fp8_block_size=%d", a->qk_block);
+  LBFQ_REQUIRE(a->qk_block % a->block_n == 0, LBFQ_ERR_UNSUPPORTED,
+               "fp8_block_size (%d) must be a multiple of block_n (%d)", a->qk_block, a->block_n);
+  LBFQ_REQUIRE(a->p_kind >= 0 && a->p_kind <= 2, LBFQ_ERR_ARG, "unknown p_quant_mode");
+  LBFQ_REQUIRE(a->v_kind >= 0 && a->v_kind <= 2 && a->v_scale, LBFQ_ERR_ARG, "bad V quant kind / scale");
+  if (a->v_kind != LBFQ_V_CHANNEL) {
+    LBFQ_REQUIRE(a->v_block > 0 && a->N % a->v_block == 0, LBFQ_ERR_ARG, "S (%d) must be divisible by v_block_size (%d)", a->N, a->v_block);
+    LBFQ_REQUIRE(a->v_block >= a->block_n && a->v_block % a->block_n == 0, LBFQ_ERR_ARG,
+                 "v_block_size (%d) must be >= block_n (%d) and an integer multiple of block_n", a->v_block, a->block_n);
+  }
+  if (a->v_alpha) {
+    LBFQ_REQUIRE(a->v_smooth_block > 0, LBFQ_ERR_ARG, "v_smooth_block must be > 0 when v_alpha is given");
+    LBFQ_REQUIRE(a->v_smooth_block >= a->block_n && a->v_smooth_block % a->block_n == 0, LBFQ_ERR_ARG,
+                 "v_smooth_block (%d) must be >= block_n (%d) and an integer multiple of block_n", a->v_smooth_block, a->block_n);
+    LBFQ_REQUIRE(a->N % a->v_smooth_block == 0, LBFQ_ERR_ARG, "S (%d) must be divisible by v_smooth_block (%d)", a->N, a->v_smooth_block);
+    LBFQ_REQUIRE(workspace != nullptr, LBFQ_ERR_ARG, "v_alpha needs the workspace of lbfq_attention_workspace_bytes");
+  }
+  if (a->qm_corr) {
+    LBFQ_REQUIRE(a->q_smooth_block > 0, LBFQ_ERR_ARG, "q_smooth_block must be > 0 with qm_bhgd");
+    LBFQ_REQUIRE(a->q_smooth_block >= a->block_m && a->q_smooth_block % a->block_m == 0, LBFQ_ERR_ARG,
+                 "q_smooth_block (%d) must be >= block_m (%d) and an integer multiple of block_m", a->q_smooth_block, a->block_m);
+    LBFQ_REQUIRE(a->M % a->q_smooth_block == 0, LBFQ_ERR_ARG, "S (%d) must be divisible by q_smooth_block (%d)", a->M, a->q_smooth_block);
+    LBFQ_REQUIRE(a->corr_stride >= a->n_pad && a->corr_stride % 4 == 0, LBFQ_ERR_ARG, "corr_stride must cover n_pad");
+  }
+  LBFQ_REQUIRE(!(a->rowmax_est && a->rowmax_init), LBFQ_ERR_ARG, "rowmax_init_bhs and rowmax_est_bhs are mutually exclusive");
+  if (a->use_blasst) {
+    LBFQ_REQUIRE(a->blasst_lambda > 0.f && a->blasst_lambda < 1.f, LBFQ_ERR_ARG, "blasst_lambda must be in (0, 1); got %g", (double)a->blasst_lambda);
+    LBFQ_REQUIRE(a->fill_kind >= 0 && a->fill_kind <= 6, LBFQ_ERR_ARG, "unknown blasst fill kind %d", a->fill_kind);
+    if (a->fill_kind == LBFQ_FILL_UTA) {
+      LBFQ_REQUIRE(a->uta_bins > 0 && a->block_n % a->uta_bins == 0, LBFQ_ERR_ARG,
+                   "blasst UTA bins (%d) must divide block_n (%d)", a->uta_bins, a->block_n);
+      LBFQ_REQUIRE(a->uta_bins <= 16, LBFQ_ERR_UNSUPPORTED, "at most 16 UTA bins are supported; got %d", a->uta_bins);
+    }
+  }
+  cudaStream_t st = (cudaStream_t)stream;
+
+  Params p{};
+  p.B = a->B; p.H = a->H; p.M = a->M; p.N = a->N; p.D = a->D;
+  p.qk_block = a->qk_block; p.q_scale = a->q_scale; p.k_scale = a->k_scale;
+  p.v_kind = a->v_kind; p.v_scale = a->v_scale; p.v_block = a->v_block > 0 ? a->v_block : a->block_n;
+  p.sm_scale = a->sm_scale; p.p_off = a->p_max_offset; p.p_kind = a->p_kind; p.block_m = a->block_m;
+  p.v_alpha = nullptr; p.v_smooth_block = a->v_smooth_block > 0 ? a->v_smooth_block : a->block_n;
+  p.corr = a->qm_corr; p.q_smooth_block = a->q_smooth_block > 0 ? a->q_smooth_block : a->block_m;
+  p.corr_stride = a->corr_stride; p.n_groups = a->qm_corr ? a->M / a->q_smooth_block : 0;
+  p.rowmax_est = a->rowmax_est; p.rowmax_init = a->rowmax_init;
+  p.rm_mode = (a->rowmax_est && !a->use_blasst) ? (a->p_kind == LBFQ_P_DYNAMIC ? 2 : 1) : 0;
+  p.log_lambda = a->use_blasst ? logf(a->blasst_lambda) : 0.f;
+  p.lambda = a->use_blasst ? a->blasst_lambda : 0.f;
+  p.fill_kind = a->use_blasst ? a->fill_kind : 0; p.fill_alpha = a->fill_alpha; p.uta_bins = a->uta_bins > 0 ? a->uta_bins : 1;
+  p.stats = a->use_blasst ? a->blasst_stats : nullptr;
+  p.out = a->out; p.out_dtype = a->out_dtype; p.out_layout = a->out_layout; p.out_exact = a->out_fp32_exact;
+  p.out_row_index = a->out_row_index; p.status = a->status;
+  LBFQ_REQUIRE(p.out_dtype >= 0 && p.out_dtype <= 2, LBFQ_ERR_DTYPE, "unsupported dtype code %d", p.out_dtype);
+
+  if (a->v_alpha) {
+    const int NB = a->N / a->v_smooth_block;
+    const size_t total = (size_t)a->B * NB * a->H * a->D;
+    int g = (int)((total + 255) / 256); if (g > 148 * 8) g = 148 * 8;
+    alpha_prep_kernel<<<g, 256, 0, st>>>(a->v_alpha, (float*)workspace, a->v_scale, a->v_kind, a->B, NB, a->H, a->D,
+                                        a->v_smooth_block, a->v_kind == LBFQ_V_BLOCK ? a->v_block : 1);
+    if (int rc = check_launch("alpha_prep")) return rc;
+    p.v_alpha = (const float*)workspace;
+  }
+
+  CUtensorMap mq, mk, mv;
+  const uint64_t BH = (uint64_t)a->B * a->H;
+  if (int rc = make_map(&mq, a->q_codes, a->D, a->m_pad, BH, a->D, kTileM)) return rc;
+  if (int rc = make_map(&mk, a->k_codes, a->D, a->n_pad, BH, a->D, kChunk)) return rc;
+  if (int rc = make_map(&mv, a->v_codes, a->n_pad, a->D, BH, kChunk, a->D)) return rc;
+
+  const bool bl = a->use_blasst != 0;
+#define LBFQ_LAUNCH(DD, NN)                                                        \
+  return bl ? launch<DD, NN, true>(mq, mk, mv, p, st) : launch<DD, NN, false>(mq, mk, mv, p, st)
+  if (a->D == 128 && a->block_n == 64) { LBFQ_LAUNCH(128, 64); }
+  if (a->D == 128 && a->block_n == 32) { LBFQ_LAUNCH(128, 32); }
+  if (a->D == 64 && a->block_n == 64) { LBFQ_LAUNCH(64, 64); }
+  LBFQ_LAUNCH(64, 32);
+#undef LBFQ_LAUNCH
+}

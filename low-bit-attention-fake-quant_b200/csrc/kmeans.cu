@@ -1,0 +1,254 @@
+// Lloyd k-means over the tokens of each (b, h) slab.
+//
+// Stands in for flash_kmeans.batch_kmeans_Euclid as called from
+// src/low_bit_fake_quant/kmeans.py:77-81 (x fp32 (B*H, S, D), k clusters,
+// max_iters iterations, tol = 0 so the iteration count is fixed, labels of the
+// last assignment returned). That package is a third-party dependency whose
+// source is not part of the reference tree; what is reproduced here is the
+// published algorithm, with a deterministic seeding documented below.
+//
+//   seeding   : centroid j of slab g = the token at index
+//               lo_j + mix32(mix32(mix32(seed) ^ g) ^ j) % (hi_j - lo_j),
+//               [lo_j, hi_j) the j-th of k equal strata of the S axis
+//   assignment: argmin_c |c|^2 - 2 x.c   (fp32, lowest index on ties)
+//   update    : mean of the assigned tokens, summed in a fixed order so that a
+//               run is bit-reproducible; an empty cluster keeps its centroid
+//
+// The update uses the same stable counting sort that later produces the token
+// order: tokens of one cluster become one contiguous segment, reduced by one CTA.
+
+#include "common.cuh"
+
+namespace lbfq {
+
+constexpr int kThreads = 256;
+constexpr int kTok = 128;      // tokens per assignment CTA
+constexpr int kCen = 64;       // centroids per pass
+constexpr int kDc = 32;        // D chunk staged in shared memory
+
+__host__ __device__ __forceinline__ uint32_t mix32(uint32_t x) {
+  x ^= x >> 16; x *= 0x7FEB352Du; x ^= x >> 15; x *= 0x846CA68Bu; x ^= x >> 16;
+  return x;
+}
+
+template <typename T>
+__global__ void init_centroids_kernel(const T* __restrict__ x, int S, int H, int D, int k, uint32_t seed,
+                                      int bh_offset, float* __restrict__ cent, float* __restrict__ cnorm) {
+  const int j = blockIdx.x % k;
+  const int bh = blockIdx.x / k;
+  const int b = bh / H, h = bh % H;
+  const int lo = (int)(((int64_t)j * S) / k);
+  const int hi = (int)(((int64_t)(j + 1) * S) / k);
+  const int span = max(hi - lo, 1);
+  const uint32_t hsh = mix32(mix32(mix32(seed) ^ (uint32_t)(bh_offset + bh)) ^ (uint32_t)j);
+  const int idx = lo + (int)(hsh % (uint32_t)span);
+  __shared__ float red[4];
+  float v = 0.f;
+  if (threadIdx.x < D) {
+    v = Elem<T>::load(x + (((size_t)b * S + idx) * H + h) * D + threadIdx.x);
+    cent[((size_t)bh * k + j) * D + threadIdx.x] = v;
+  }
+  float s = warp_sum(v * v);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+  __syncthreads();
+  if (threadIdx.x == 0) cnorm[(size_t)bh * k + j] = red[0] + red[1] + red[2] + red[3];
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+assign_kernel(const T* __restrict__ x, int S, int H, int D, int k, const float* __restrict__ cent,
+              const float* __restrict__ cnorm, int32_t* __restrict__ labels) {
+  __shared__ float a_s[kDc][kTok + 4];    // [d][token]
+  __shared__ float b_s[kDc][kCen + 4];    // [d][centroid]
+  const int ntile = (S + kTok - 1) / kTok;
+  const int tile = blockIdx.x % ntile;
+  const int bh = blockIdx.x / ntile;
+  const int b = bh / H, h = bh % H;
+  const int t0 = tile * kTok;
+  const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;   // 8 tokens x 4 centroids per thread
+  float best[8];
+  int best_i[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) { best[i] = INFINITY; best_i[i] = 0; }
+
+  for (int c0 = 0; c0 < k; c0 += kCen) {
+    float acc[8][4];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+    for (int d0 = 0; d0 < D; d0 += kDc) {
+      for (int idx = threadIdx.x; idx < kTok * kDc; idx += kThreads) {
+        const int t = idx / kDc, d = idx % kDc;
+        const int tok = t0 + t;
+        a_s[d][t] = tok < S ? Elem<T>::load(x + (((size_t)b * S + tok) * H + h) * D + d0 + d) : 0.f;
+      }
+      for (int idx = threadIdx.x; idx < kCen * kDc; idx += kThreads) {
+        const int c = idx / kDc, d = idx % kDc;
+        b_s[d][c] = (c0 + c) < k ? cent[((size_t)bh * k + c0 + c) * D + d0 + d] : 0.f;
+      }
+      __syncthreads();
+#pragma unroll 8
+      for (int d = 0; d < kDc; ++d) {
+        float av[8], bv[4];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) av[i] = a_s[d][ty * 8 + i];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) bv[j] = b_s[d][tx * 4 + j];
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+      }
+      __syncthreads();
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int c = c0 + tx * 4 + j;
+      if (c < k) {
+        const float cn = cnorm[(size_t)bh * k + c];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float dist = cn - 2.0f * acc[i][j];
+          if (dist < best[i]) { best[i] = dist; best_i[i] = c; }   // ascending c: lowest index wins ties
+        }
+      }
+    }
+  }
+  // combine the 16 tx lanes of a token row (lanes differ in tx only within a half-warp)
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best[i], o);
+      const int oi = __shfl_xor_sync(0xffffffffu, best_i[i], o);
+      if (ob < best[i] || (ob == best[i] && oi < best_i[i])) { best[i] = ob; best_i[i] = oi; }
+    }
+    const int tok = t0 + ty * 8 + i;
+    if (tx == 0 && tok < S) labels[(size_t)bh * S + tok] = best_i[i];
+  }
+}
+
+// stable counting sort (same algorithm as label_order_kernel) that also emits
+// the k+1 segment offsets of each slab
+__global__ void __launch_bounds__(1024)
+sort_segments_kernel(const int32_t* __restrict__ labels, int S, int k, int32_t* __restrict__ order32,
+                     int32_t* __restrict__ seg) {
+  extern __shared__ int sm_counts[];
+  int* counts = sm_counts;
+  int* offsets = sm_counts + k;
+  const int32_t* lab = labels + (size_t)blockIdx.x * S;
+  int32_t* ord = order32 + (size_t)blockIdx.x * S;
+  for (int i = threadIdx.x; i < k; i += blockDim.x) counts[i] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < S; i += blockDim.x) atomicAdd(&counts[lab[i]], 1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int run = 0;
+    for (int c = 0; c < k; ++c) { offsets[c] = run; seg[(size_t)blockIdx.x * (k + 1) + c] = run; run += counts[c]; }
+    seg[(size_t)blockIdx.x * (k + 1) + k] = run;
+  }
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  for (int c = warp; c < k; c += nwarps) {
+    int pos = offsets[c];
+    for (int base = 0; base < S; base += 32) {
+      const int i = base + lane;
+      const bool hit = (i < S) && (lab[i] == c);
+      const unsigned m = __ballot_sync(0xffffffffu, hit);
+      if (hit) ord[pos + __popc(m & ((1u << lane) - 1u))] = i;
+      pos += __popc(m);
+    }
+  }
+}
+
+// one CTA per (slab, cluster): mean of the cluster's tokens in sorted order
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+segment_mean_kernel(const T* __restrict__ x, int S, int H, int D, int k, const int32_t* __restrict__ order32,
+                    const int32_t* __restrict__ seg, float* __restrict__ cent, float* __restrict__ cnorm) {
+  __shared__ float buf[kThreads / 8][128 + 1];
+  __shared__ float red[4];
+  const int c = blockIdx.x % k;
+  const int bh = blockIdx.x / k;
+  const int b = bh / H, h = bh % H;
+  const int beg = seg[(size_t)bh * (k + 1) + c], end = seg[(size_t)bh * (k + 1) + c + 1];
+  if (end == beg) return;                           // empty cluster keeps centroid and norm
+  const int tpr = D / 8, rpi = kThreads / tpr;
+  const int tr = threadIdx.x / tpr, d0 = (threadIdx.x % tpr) * 8;
+  float acc[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+  for (int r = beg + tr; r < end; r += rpi) {
+    const int tok = order32[(size_t)bh * S + r];
+    const T* p = x + (((size_t)b * S + tok) * H + h) * D + d0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] += Elem<T>::load(p + i);
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) buf[tr][d0 + i] = acc[i];
+  __syncthreads();
+  float v = 0.f;
+  if (threadIdx.x < D) {
+    float s = 0.f;
+    for (int r = 0; r < rpi; ++r) s += buf[r][threadIdx.x];
+    v = __fdiv_rn(s, (float)(end - beg));
+    cent[((size_t)bh * k + c) * D + threadIdx.x] = v;
+  }
+  float s2 = warp_sum(v * v);
+  if ((threadIdx.x & 31) == 0 && threadIdx.x < 128) red[threadIdx.x >> 5] = s2;
+  __syncthreads();
+  if (threadIdx.x == 0) cnorm[(size_t)bh * k + c] = red[0] + red[1] + red[2] + red[3];
+}
+
+struct KmScratch {
+  float* cent; float* cnorm; int32_t* order32; int32_t* seg;
+};
+static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+static size_t scratch_layout(int BH, int S, int D, int k, uint8_t* base, KmScratch* out) {
+  size_t off = 0;
+  auto take = [&](size_t bytes) { size_t o = off; off = align_up(off + bytes, 256); return base ? base + o : nullptr; };
+  uint8_t* p0 = take((size_t)BH * k * D * 4);
+  uint8_t* p1 = take((size_t)BH * k * 4);
+  uint8_t* p2 = take((size_t)BH * S * 4);
+  uint8_t* p3 = take((size_t)BH * (k + 1) * 4);
+  if (out) { out->cent = (float*)p0; out->cnorm = (float*)p1; out->order32 = (int32_t*)p2; out->seg = (int32_t*)p3; }
+  return off;
+}
+
+}  // namespace lbfq
+
+using namespace lbfq;
+
+extern "C" int64_t lbfq_kmeans_scratch_bytes(int B, int S, int H, int D, int k) {
+  return (int64_t)scratch_layout(B * H, S, D, k, nullptr, nullptr);
+}
+
+extern "C" int lbfq_kmeans_labels(const void* x, int dtype, int B, int S, int H, int D, int k, int iters,
+                                  int seed, int bh_offset, int32_t* labels, void* scratch, void* stream) {
+  LBFQ_REQUIRE(B > 0 && S > 0 && H > 0, LBFQ_ERR_ARG, "kmeans: empty input");
+  LBFQ_REQUIRE(D == 64 || D == 128, LBFQ_ERR_ARG, "kmeans: D must be 64 or 128; got %d", D);
+  LBFQ_REQUIRE(k > 0 && k <= S, LBFQ_ERR_ARG, "n_clusters must be in [1, S]; got %d for S=%d", k, S);
+  LBFQ_REQUIRE(k <= 4096, LBFQ_ERR_UNSUPPORTED, "kmeans: k=%d above the supported 4096", k);
+  cudaStream_t st = (cudaStream_t)stream;
+  const int BH = B * H;
+  KmScratch sc;
+  scratch_layout(BH, S, D, k, (uint8_t*)scratch, &sc);
+  if (iters < 1) iters = 1;
+  LBFQ_DISPATCH_DTYPE(dtype, T,
+      init_centroids_kernel<T><<<BH * k, 128, 0, st>>>((const T*)x, S, H, D, k, (uint32_t)seed, bh_offset, sc.cent, sc.cnorm));
+  if (int rc = check_launch("kmeans init")) return rc;
+  const int ntile = (S + kTok - 1) / kTok;
+  for (int it = 0; it < iters; ++it) {
+    LBFQ_DISPATCH_DTYPE(dtype, T,
+        assign_kernel<T><<<BH * ntile, kThreads, 0, st>>>((const T*)x, S, H, D, k, sc.cent, sc.cnorm, labels));
+    if (int rc = check_launch("kmeans assign")) return rc;
+    if (it + 1 == iters) break;                     // labels of the last assignment are the result
+    sort_segments_kernel<<<BH, 1024, 2 * k * sizeof(int), st>>>(labels, S, k, sc.order32, sc.seg);
+    if (int rc = check_launch("kmeans sort")) return rc;
+    LBFQ_DISPATCH_DTYPE(dtype, T,
+        segment_mean_kernel<T><<<BH * k, kThreads, 0, st>>>((const T*)x, S, H, D, k, sc.order32, sc.seg, sc.cent, sc.cnorm));
+    if (int rc = check_launch("kmeans update")) return rc;
+  }
+  return LBFQ_OK;
+}

@@ -1,0 +1,142 @@
+"""ctypes binding of ``liblbfq.so`` (the sm_100a CUDA library) -- plumbing only.
+
+The library is looked up next to the package (``../liblbfq.so``, built by
+``build.sh``). There is no fallback: if it is missing, importing any op of this
+package raises, and every op refuses CPU tensors exactly as the reference does.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import os
+from typing import Optional
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.environ.get("LBFQ_LIB", os.path.join(os.path.dirname(_HERE), "liblbfq.so"))
+
+F32, F16, BF16 = 0, 1, 2
+LAYOUT_NHD, LAYOUT_BHSD, LAYOUT_BHDS = 0, 1, 2
+P_KINDS = {"elementwise": 0, "mx": 1, "dynamic": 2}
+V_CHANNEL, V_BLOCK, V_MX = 0, 1, 2
+QK_FP8_BLOCK, QK_MX = 0, 1
+
+ERR_ARG, ERR_DTYPE, ERR_UNSUPPORTED, ERR_CUDA, ERR_DEVICE = -1, -2, -3, -4, -5
+
+_DTYPES = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}
+
+
+class AttnArgs(C.Structure):
+    """Mirror of ``lbfq_attn_args`` (include/lbfq.h)."""
+
+    _fields_ = [
+        ("B", C.c_int), ("H", C.c_int), ("M", C.c_int), ("N", C.c_int), ("D", C.c_int),
+        ("m_pad", C.c_int), ("n_pad", C.c_int),
+        ("q_codes", C.c_void_p), ("k_codes", C.c_void_p), ("v_codes", C.c_void_p),
+        ("qk_kind", C.c_int),
+        ("q_scale", C.c_void_p), ("k_scale", C.c_void_p),
+        ("qk_block", C.c_int),
+        ("q_scale_e8", C.c_void_p), ("k_scale_e8", C.c_void_p),
+        ("v_kind", C.c_int),
+        ("v_scale", C.c_void_p),
+        ("v_block", C.c_int),
+        ("sm_scale", C.c_float), ("p_max_offset", C.c_float),
+        ("p_kind", C.c_int),
+        ("block_m", C.c_int), ("block_n", C.c_int),
+        ("v_alpha", C.c_void_p),
+        ("v_smooth_block", C.c_int),
+        ("qm_corr", C.c_void_p),
+        ("q_smooth_block", C.c_int),
+        ("corr_stride", C.c_int),
+        ("rowmax_est", C.c_void_p), ("rowmax_init", C.c_void_p),
+        ("use_blasst", C.c_int),
+        ("blasst_lambda", C.c_float),
+        ("fill_kind", C.c_int),
+        ("fill_alpha", C.c_float),
+        ("uta_bins", C.c_int),
+        ("blasst_stats", C.c_void_p),
+        ("out", C.c_void_p),
+        ("out_dtype", C.c_int), ("out_layout", C.c_int),
+        ("out_row_index", C.c_void_p),
+        ("out_fp32_exact", C.c_int),
+        ("status", C.c_void_p),
+    ]
+
+
+_P = C.c_void_p
+_I = C.c_int
+_SIGS = {
+    "lbfq_last_error": (C.c_char_p, []),
+    "lbfq_abi_version": (_I, []),
+    "lbfq_fp8_block_quant": (_I, [_P, _I, _I, _I, _I, _I, _I, _P, _I, _I, _P, _P]),
+    "lbfq_fp8_block_dequant": (_I, [_P, _P, _I, _I, _I, _I, _I, _P, _I, _P]),
+    "lbfq_fp8_channel_quant": (_I, [_P, _I, _I, _I, _I, _I, _P, _I, _I, _P, _P]),
+    "lbfq_fp8_channel_dequant": (_I, [_P, _P, _I, _I, _I, _I, _P, _I, _P]),
+    "lbfq_mxfp8_qk_quant": (_I, [_P, _I, _I, _I, _I, _I, _I, _P, _I, _I, _P, _P, _P]),
+    "lbfq_mxfp8_qk_dequant": (_I, [_P, _P, _I, _I, _I, _I, _I, _P, _I, _P]),
+    "lbfq_mxfp8_v_quant": (_I, [_P, _I, _I, _I, _I, _I, _I, _P, _I, _I, _P, _P]),
+    "lbfq_mxfp8_v_dequant": (_I, [_P, _P, _I, _I, _I, _I, _I, _P, _I, _P]),
+    "lbfq_smooth_k_scratch_floats": (C.c_int64, [_I, _I, _I, _I]),
+    "lbfq_smooth_k": (_I, [_P, _I, _I, _I, _I, _I, _P, _P, _P, _P]),
+    "lbfq_block_mean_sub": (_I, [_P, _I, _I, _I, _I, _I, _I, _P, _P, _P]),
+    "lbfq_hadamard": (_I, [_P, _I, C.c_int64, _I, _I, _P, C.c_float, _P, _P]),
+    "lbfq_kmeans_scratch_bytes": (C.c_int64, [_I, _I, _I, _I, _I]),
+    "lbfq_kmeans_labels": (_I, [_P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P]),
+    "lbfq_label_order": (_I, [_P, _I, _I, _I, _P, _P, _P]),
+    "lbfq_gather_rows": (_I, [_P, _I, _I, _I, _I, _I, _P, _P, _P]),
+    "lbfq_qm_corr": (_I, [_P, _P, _I, _I, _I, _I, _I, _I, C.c_float, _P, _I, _P, _P]),
+    "lbfq_attention_workspace_bytes": (C.c_int64, [C.POINTER(AttnArgs)]),
+    "lbfq_attention_fwd": (_I, [C.POINTER(AttnArgs), _P, _P]),
+}
+
+_lib: Optional[C.CDLL] = None
+
+
+def lib() -> C.CDLL:
+    """The loaded library; raises ``RuntimeError`` when it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} not found: build the CUDA library first "
+                "(low-bit-attention-fake-quant_b200/build.sh); there is no CPU or Triton fallback")
+        handle = C.CDLL(LIB_PATH)
+        for name, (res, args) in _SIGS.items():
+            fn = getattr(handle, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = handle
+    return _lib
+
+
+def exported_symbols():
+    return list(_SIGS.keys())
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    if dt not in _DTYPES:
+        raise TypeError(f"unsupported dtype {dt}")
+    return _DTYPES[dt]
+
+
+def check(rc: int) -> None:
+    """Map a status code to the exception class the reference raises."""
+    if rc == 0:
+        return
+    msg = lib().lbfq_last_error().decode("utf-8", "replace")
+    if rc == ERR_ARG:
+        raise ValueError(msg)
+    if rc == ERR_DTYPE:
+        raise TypeError(msg)
+    if rc == ERR_UNSUPPORTED:
+        raise NotImplementedError(msg)
+    raise RuntimeError(f"liblbfq error {rc}: {msg}")
+
+
+def ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def stream_ptr(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream

@@ -1,0 +1,347 @@
+"""Public entry point of the fake-quant attention path (host orchestration).
+
+Drop-in for src/low_bit_fake_quant/attention.py: ``fake_quant_attention``
+(:706-806), ``prepare_for_attention`` (:673-703), ``PreprocessCache``
+(:647-670), ``FakeQuantArtifacts`` (:77-86), ``reference_attention``
+(:809-825) keep their signatures, argument meaning, return types and errors.
+
+What differs is below the API: every device step is a kernel of
+``liblbfq.so``. In the P-requant path the quantizers write e4m3 codes
+directly in the head-major layouts the attention kernel's TMA descriptors
+read (no de-quantised BF16 copies, no NHD->BHSD permutes), the Q-smoothing
+correction is one fp32 product ``qm . K_smooth`` whose row max doubles as the
+``qm_k`` row-max estimate, and the inverse Q reorder is fused into the
+kernel's output store.
+"""
+
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+import torch.nn.functional as F
+
+from . import _lib as L
+from .attention_triton import fake_quant_attention_fp8, qm_corr
+from .config import QuantConfig
+from .hadamard import apply_qk_hadamard
+from .kmeans import KMeansReorderResult, _gather, apply_kv_permutation, kmeans_reorder_tokens
+from .preprocess import group_mean_q, smooth_k, smooth_v_per_block
+from .quant_triton import (
+    fp8_block_dequant,
+    fp8_block_quant,
+    fp8_per_channel_dequant,
+    fp8_per_channel_quant,
+    mxfp8_qk_dequant,
+    mxfp8_qk_quant,
+    mxfp8_v_dequant,
+    mxfp8_v_quant,
+)
+
+
+@dataclass
+class FakeQuantArtifacts:
+    """Side data emitted by :func:`fake_quant_attention` for debugging."""
+
+    qm: Optional[torch.Tensor] = None
+    k_mean: Optional[torch.Tensor] = None
+    kmeans: Optional[KMeansReorderResult] = None
+    q_eff_dtype: Optional[torch.dtype] = None
+    p_requant: bool = False
+    qk_hadamard: bool = False
+
+
+@dataclass
+class PreprocessCache:
+    """Output of :func:`prepare_for_attention`, reusable across configs that
+    share the smoothing / k-means / V-smoothing settings recorded here."""
+
+    q_work: torch.Tensor
+    k_work: torch.Tensor
+    v_work: torch.Tensor
+    qm: Optional[torch.Tensor]
+    v_alpha: Optional[torch.Tensor]
+    q_kmeans: Optional[KMeansReorderResult]
+    v_kmeans: Optional[KMeansReorderResult]
+    smoothing: str
+    q_kmeans_k: Optional[int]
+    q_smooth_block_size: int
+    v_smooth_mode: str
+    v_smooth_block_size: int
+    v_kmeans_k: Optional[int]
+
+
+def _round_up(x: int, m: int) -> int:
+    return (x + m - 1) // m * m
+
+
+# ---------------------------------------------------------------------------
+# preprocess: Q k-means -> K smooth -> Q smooth -> V k-means (+K) -> V smooth
+# ---------------------------------------------------------------------------
+
+def _preprocess(q, k, v, cfg: QuantConfig, *, bh_offset: int = 0):
+    """The reference's fixed preprocessing order (attention.py:166-239)."""
+    q_work, k_work, v_work = q.contiguous(), k.contiguous(), v.contiguous()
+    q_km = v_km = None
+    qm = v_alpha = None
+
+    if cfg.q_kmeans_k is not None:
+        q_km = kmeans_reorder_tokens(q_work, n_clusters=cfg.q_kmeans_k, max_iters=cfg.q_kmeans_iters,
+                                     seed=cfg.q_kmeans_seed, bh_offset=bh_offset)
+        q_work = q_km.tensor_reordered
+
+    if cfg.smoothing in ("k_only", "full"):
+        k_work, _ = smooth_k(k_work)
+        if cfg.smoothing == "full":
+            q_work, qm = group_mean_q(q_work, block_q=cfg.q_smooth_block_size)
+    elif cfg.smoothing != "off":
+        raise ValueError(f"unsupported smoothing: {cfg.smoothing!r}")
+
+    if cfg.v_kmeans_k is not None:
+        v_km = kmeans_reorder_tokens(v_work, n_clusters=cfg.v_kmeans_k, max_iters=cfg.v_kmeans_iters,
+                                     seed=cfg.v_kmeans_seed, bh_offset=bh_offset)
+        v_work = v_km.tensor_reordered
+        k_work = apply_kv_permutation(k_work, v_km.order)      # keep every (K[n], V[n]) pair together
+
+    if cfg.v_smooth_mode == "per_block":
+        v_work, v_alpha = smooth_v_per_block(v_work, block_s=cfg.v_smooth_block_size)
+    elif cfg.v_smooth_mode != "off":
+        raise ValueError(f"unsupported v_smooth_mode: {cfg.v_smooth_mode!r}")
+
+    return q_work, k_work, v_work, qm, v_alpha, q_km, v_km
+
+
+def _rotated(q_work, k_work, cfg: QuantConfig):
+    if not cfg.qk_hadamard:
+        return q_work, k_work
+    return apply_qk_hadamard(q_work, k_work, random_sign=cfg.qk_hadamard_random_sign, seed=cfg.qk_hadamard_seed)
+
+
+# ---------------------------------------------------------------------------
+# path A (p_requant=False): quantise, de-quantise, SDPA  (attention.py:247-321)
+# ---------------------------------------------------------------------------
+
+def _quant_dequant_qk(t, cfg: QuantConfig, dtype):
+    if cfg.qk_quant == "fp8_block":
+        c, s = fp8_block_quant(t, block_s=cfg.fp8_block_size)
+        return fp8_block_dequant(c, s, block_s=cfg.fp8_block_size, dtype=dtype)
+    if cfg.qk_quant == "mxfp8":
+        c, s = mxfp8_qk_quant(t, block_d=cfg.mxfp8_block_size)
+        return mxfp8_qk_dequant(c, s, block_d=cfg.mxfp8_block_size, dtype=dtype)
+    raise ValueError(f"unsupported qk_quant: {cfg.qk_quant!r}")
+
+
+def _quant_dequant_v(t, cfg: QuantConfig, dtype):
+    if cfg.v_quant == "fp8_channel":
+        c, s = fp8_per_channel_quant(t)
+        return fp8_per_channel_dequant(c, s, dtype=dtype)
+    if cfg.v_quant == "fp8_block":
+        c, s = fp8_block_quant(t, block_s=cfg.v_fp8_block_size)
+        return fp8_block_dequant(c, s, block_s=cfg.v_fp8_block_size, dtype=dtype)
+    if cfg.v_quant == "mxfp8":
+        c, s = mxfp8_v_quant(t, block_s=cfg.v_mxfp8_block_size)
+        return mxfp8_v_dequant(c, s, block_s=cfg.v_mxfp8_block_size, dtype=dtype)
+    raise ValueError(f"unsupported v_quant: {cfg.v_quant!r}")
+
+
+def _fake_quant_attention_sdpa(q_work, k_work, v_work, qm, v_alpha, cfg: QuantConfig, sm_scale, sdpa_dtype):
+    """P stays unquantised (upper-bound path). With Q smoothing the score is
+    ``Q_deq.K_deq^T + qm.K_smooth^T`` with the second term on the un-quantised K."""
+    b, s, h, d = q_work.shape
+    q_in, k_in = _rotated(q_work, k_work, cfg)
+    q_deq = _quant_dequant_qk(q_in, cfg, sdpa_dtype)
+    k_deq = _quant_dequant_qk(k_in, cfg, sdpa_dtype)
+    v_deq = _quant_dequant_v(v_work, cfg, sdpa_dtype)
+    if v_alpha is not None:
+        bv = cfg.v_smooth_block_size
+        if s % bv != 0:
+            raise ValueError(f"S={s} not divisible by v_smooth_block_size={bv}")
+        v_deq = v_deq + v_alpha.repeat_interleave(bv, dim=1).to(sdpa_dtype)
+
+    to_bh = lambda t: t.permute(0, 2, 1, 3).contiguous()
+    if qm is None:
+        o = F.scaled_dot_product_attention(to_bh(q_deq), to_bh(k_deq), to_bh(v_deq), scale=sm_scale)
+        return o.permute(0, 2, 1, 3).contiguous()
+
+    block_q = cfg.q_smooth_block_size
+    chunk = max(block_q, 256)
+    qb, kb, vb = to_bh(q_deq), to_bh(k_deq), to_bh(v_deq)
+    qmb = to_bh(qm)
+    ksb = to_bh(k_work).float()
+    out = torch.empty_like(qb)
+    group = torch.arange(s, device=q_work.device) // block_q
+    for m0 in range(0, s, chunk):
+        m1 = min(m0 + chunk, s)
+        main = torch.matmul(qb[:, :, m0:m1], kb.transpose(-2, -1)).float() * sm_scale
+        corr = torch.matmul(qmb[:, :, group[m0:m1]], ksb.transpose(-2, -1)) * sm_scale
+        p = torch.softmax(main + corr, dim=-1).to(sdpa_dtype)
+        out[:, :, m0:m1] = torch.matmul(p, vb)
+    return out.permute(0, 2, 1, 3).contiguous()
+
+
+# ---------------------------------------------------------------------------
+# path B (p_requant=True): FP8 streaming kernel  (attention.py:505-639)
+# ---------------------------------------------------------------------------
+
+def _fake_quant_attention_p_requant(q_work, k_work, v_work, qm, v_alpha, q_kmeans, cfg: QuantConfig,
+                                    sm_scale, out_dtype, *, return_stats: bool = False,
+                                    out_fp32_exact: bool = False):
+    """Quantise straight into the kernel's layouts and launch it. Returns the
+    output in NHD, rows already back in the original Q order."""
+    b, s, h, d = q_work.shape
+    s_pad = _round_up(s, 128)
+    q_in, k_in = _rotated(q_work, k_work, cfg)
+
+    if cfg.qk_quant == "fp8_block":
+        q_codes, q_scale = fp8_block_quant(q_in, block_s=cfg.fp8_block_size, _layout=L.LAYOUT_BHSD, _s_pad=s_pad)
+        k_codes, k_scale = fp8_block_quant(k_in, block_s=cfg.fp8_block_size, _layout=L.LAYOUT_BHSD, _s_pad=s_pad)
+    elif cfg.qk_quant == "mxfp8":
+        raise NotImplementedError("qk_quant='mxfp8' with p_requant=True: block-scaled Q.K^T is not built yet")
+    else:
+        raise ValueError(f"unsupported qk_quant: {cfg.qk_quant!r}")
+
+    v_block = 0
+    if cfg.v_quant == "fp8_channel":
+        v_codes, v_scale = fp8_per_channel_quant(v_work, _layout=L.LAYOUT_BHDS, _s_pad=s_pad)
+    elif cfg.v_quant == "fp8_block":
+        v_block = cfg.v_fp8_block_size
+        v_codes, v_scale = fp8_block_quant(v_work, block_s=v_block, _layout=L.LAYOUT_BHDS, _s_pad=s_pad)
+    elif cfg.v_quant == "mxfp8":
+        v_block = cfg.v_mxfp8_block_size
+        v_codes, v_scale = mxfp8_v_quant(v_work, block_s=v_block, _layout=L.LAYOUT_BHDS, _s_pad=s_pad)
+    else:
+        raise ValueError(f"unsupported v_quant: {cfg.v_quant!r}")
+
+    corr = None
+    rowmax_est = None
+    if cfg.rowmax_mode not in ("online", "qm_k"):
+        raise ValueError(f"unsupported rowmax_mode: {cfg.rowmax_mode!r}")
+    if cfg.rowmax_mode == "qm_k" and qm is None:
+        raise ValueError("rowmax_mode='qm_k' requires smoothing='full' so qm exists")
+    if qm is not None:
+        want_est = cfg.rowmax_mode == "qm_k"
+        corr, rowmax_g = qm_corr(qm, k_work.to(torch.bfloat16), sm_scale=sm_scale, s_pad=s_pad, want_rowmax=want_est)
+        if want_est:
+            rowmax_est = rowmax_g.repeat_interleave(cfg.q_smooth_block_size, dim=2).contiguous()
+
+    p_mode = cfg.p_quant
+    if p_mode == "auto":
+        p_mode = "mx" if cfg.v_quant == "mxfp8" else "elementwise"
+    p_mx_block_n = cfg.p_mx_block_n if cfg.p_mx_block_n > 0 else cfg.v_mxfp8_block_size
+
+    return fake_quant_attention_fp8(
+        q_codes, k_codes, v_codes,
+        seq_q=s, seq_k=s,
+        q_scale=q_scale, k_scale=k_scale, qk_block=cfg.fp8_block_size,
+        v_kind=cfg.v_quant, v_scale=v_scale, v_block=v_block,
+        sm_scale=float(sm_scale), p_max_offset=int(cfg.p_max_offset),
+        block_m=cfg.p_requant_block_m, block_n=cfg.p_requant_block_n,
+        v_alpha=v_alpha, v_smooth_block=cfg.v_smooth_block_size if v_alpha is not None else 0,
+        qm_corr=corr, q_smooth_block=cfg.q_smooth_block_size if qm is not None else 0,
+        p_quant_mode=p_mode, p_mx_block_n=p_mx_block_n,
+        rowmax_est_bhs=rowmax_est,
+        blasst_lambda=cfg.blasst_lambda, blasst_fill_mode=cfg.blasst_fill,
+        blasst_fill_alpha=cfg.blasst_fill_alpha, blasst_uta_bins=cfg.blasst_uta_bins,
+        return_blasst_stats=return_stats,
+        out_dtype=torch.float32 if out_fp32_exact else out_dtype, out_nhd=True,
+        out_row_index=q_kmeans.order if q_kmeans is not None else None,
+        out_fp32_exact=out_fp32_exact,
+    )
+
+
+# ---------------------------------------------------------------------------
+# public entry points
+# ---------------------------------------------------------------------------
+
+def prepare_for_attention(q, k, v, cfg: QuantConfig) -> PreprocessCache:
+    """Run k-means + Q/K smoothing + V smoothing without any quantization."""
+    if q.shape != k.shape or q.shape != v.shape:
+        raise ValueError("q/k/v shapes must match")
+    if q.ndim != 4 or not q.is_cuda:
+        raise ValueError("q/k/v must be 4-D NHD on CUDA")
+    q_work, k_work, v_work, qm, v_alpha, q_km, v_km = _preprocess(q, k, v, cfg)
+    return PreprocessCache(
+        q_work=q_work, k_work=k_work, v_work=v_work, qm=qm, v_alpha=v_alpha, q_kmeans=q_km, v_kmeans=v_km,
+        smoothing=cfg.smoothing, q_kmeans_k=cfg.q_kmeans_k, q_smooth_block_size=cfg.q_smooth_block_size,
+        v_smooth_mode=cfg.v_smooth_mode, v_smooth_block_size=cfg.v_smooth_block_size, v_kmeans_k=cfg.v_kmeans_k,
+    )
+
+
+def fake_quant_attention(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    cfg: Optional[QuantConfig] = None,
+    *,
+    sm_scale: Optional[float] = None,
+    return_artifacts: bool = False,
+    preprocess_cache: Optional[PreprocessCache] = None,
+    _debug_fp32: bool = False,
+):
+    """Fake-quant attention with FP8/MXFP8 Q/K/V (and optional P requant).
+
+    ``q, k, v``: (B, S, H, D), D in {64, 128}, BF16/FP16/FP32 on CUDA.
+    Returns the (B, S, H, D) output in ``q``'s dtype (and the artifacts).
+    ``_debug_fp32`` (testing aid) returns the kernel's FP32 result without the
+    BF16 rounding of the store.
+    """
+    if cfg is None:
+        cfg = QuantConfig()
+    if q.shape != k.shape or q.shape != v.shape:
+        raise ValueError(f"q/k/v shapes must match; got {tuple(q.shape)}, {tuple(k.shape)}, {tuple(v.shape)}")
+    if q.ndim != 4:
+        raise ValueError(f"q/k/v must be 4-D (B,S,H,D); got {q.shape}")
+    if not (q.is_cuda and k.is_cuda and v.is_cuda):
+        raise ValueError("q/k/v must live on CUDA")
+    out_dtype = q.dtype
+    if out_dtype not in (torch.float16, torch.bfloat16, torch.float32):
+        raise TypeError(f"unsupported dtype {out_dtype}")
+    sdpa_dtype = torch.float16 if out_dtype == torch.float16 else torch.bfloat16
+    d = q.shape[-1]
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(d)
+    if cfg.blasst_lambda is not None and not cfg.p_requant:
+        raise ValueError("BLASST skip/fill requires cfg.p_requant=True")
+
+    if preprocess_cache is not None:
+        pc = preprocess_cache
+        same = (pc.smoothing == cfg.smoothing and pc.q_kmeans_k == cfg.q_kmeans_k
+                and pc.q_smooth_block_size == cfg.q_smooth_block_size and pc.v_smooth_mode == cfg.v_smooth_mode
+                and pc.v_smooth_block_size == cfg.v_smooth_block_size and pc.v_kmeans_k == cfg.v_kmeans_k)
+        if not same:
+            raise ValueError("preprocess_cache does not match cfg's smoothing/kmeans/v_smooth settings")
+        q_work, k_work, v_work, qm, v_alpha, q_km = pc.q_work, pc.k_work, pc.v_work, pc.qm, pc.v_alpha, pc.q_kmeans
+    else:
+        q_work, k_work, v_work, qm, v_alpha, q_km, _ = _preprocess(q, k, v, cfg)
+
+    if cfg.p_requant:
+        # the kernel scatters its rows through q_km.order: no separate inverse gather
+        o = _fake_quant_attention_p_requant(q_work, k_work, v_work, qm, v_alpha, q_km, cfg, sm_scale, out_dtype,
+                                            out_fp32_exact=_debug_fp32)
+    else:
+        o = _fake_quant_attention_sdpa(q_work, k_work, v_work, qm, v_alpha, cfg, sm_scale, sdpa_dtype)
+        o = o.float() if _debug_fp32 else o.to(out_dtype)
+        if q_km is not None:
+            o = _gather(o, q_km.inverse_order)
+
+    if return_artifacts:
+        return o, FakeQuantArtifacts(qm=qm, kmeans=q_km, q_eff_dtype=sdpa_dtype, p_requant=cfg.p_requant,
+                                     qk_hadamard=cfg.qk_hadamard)
+    return o
+
+
+def reference_attention(q, k, v, *, sm_scale: Optional[float] = None) -> torch.Tensor:
+    """BF16 SDPA on the raw inputs: the accuracy baseline."""
+    if q.ndim != 4:
+        raise ValueError(f"q/k/v must be (B,S,H,D); got {q.shape}")
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(q.shape[-1])
+    o = F.scaled_dot_product_attention(q.permute(0, 2, 1, 3).contiguous(), k.permute(0, 2, 1, 3).contiguous(),
+                                       v.permute(0, 2, 1, 3).contiguous(), scale=sm_scale)
+    return o.permute(0, 2, 1, 3).contiguous()
+
+
+__all__ = ["FakeQuantArtifacts", "PreprocessCache", "fake_quant_attention", "prepare_for_attention",
+           "reference_attention"]

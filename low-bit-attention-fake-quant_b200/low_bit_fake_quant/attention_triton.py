@@ -1,0 +1,230 @@
+"""Launcher of the streaming fake-quant attention kernel (CUDA, sm_100a).
+
+Takes the place of ``fake_quant_attention_triton`` and ``_parse_blasst_fill``
+(src/low_bit_fake_quant/attention_triton.py:410-714). The module name is kept
+for import compatibility; the kernel is ``csrc/attention.cu`` (tcgen05 FP8
+MMAs, TMA, TMEM), reached through ``lbfq_attention_fwd``.
+
+The reference launcher takes de-quantised BF16 operands; the kernel here
+multiplies the e4m3 codes themselves, so its native entry point,
+:func:`fake_quant_attention_fp8`, takes codes plus scales. Argument names,
+validation rules, error messages, the P / V / row-max / BLASST modes and the
+stats tensor contract are the reference's.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import re
+from typing import Optional
+
+import torch
+
+from . import _lib as L
+
+_BLASST_FILL_ZERO = 0
+_BLASST_FILL_MAX = 1
+_BLASST_FILL_MEAN = 2
+_BLASST_FILL_LOGN = 3
+_BLASST_FILL_SAMPLE8 = 4
+_BLASST_FILL_THR = 5
+_BLASST_FILL_UTA = 6
+
+_status_dev: dict[int, torch.Tensor] = {}
+_status_host: dict[int, torch.Tensor] = {}
+
+
+def _status_for(device: torch.device) -> torch.Tensor:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx not in _status_dev:
+        _status_dev[idx] = torch.zeros(1, dtype=torch.int32, device=device)
+        _status_host[idx] = torch.zeros(1, dtype=torch.int32).pin_memory()
+    host = _status_host[idx]
+    if int(host[0]) != 0:          # set by an earlier launch whose bounded wait expired
+        code = int(host[0])
+        host.zero_()
+        _status_dev[idx].zero_()
+        raise RuntimeError(f"fake-quant attention kernel gave up a bounded wait (code {code})")
+    return _status_dev[idx]
+
+
+def raise_if_device_error(device: Optional[torch.device] = None) -> None:
+    """Synchronise and raise if any launch on ``device`` reported a timeout."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+    torch.cuda.synchronize(device)
+    _status_for(device)
+
+
+def _parse_blasst_fill(mode: Optional[str], *, alpha: float, uta_bins: int) -> tuple[int, float, int]:
+    """BLASST fill string -> (kind, alpha, bins); accepts ``mean`` + alpha as
+    well as the probe spellings ``mean_a1.5`` / ``uta16_a1.5``."""
+    if mode is None or mode == "zero":
+        return _BLASST_FILL_ZERO, float(alpha), 1
+    plain = {"max": _BLASST_FILL_MAX, "mean": _BLASST_FILL_MEAN, "logn": _BLASST_FILL_LOGN,
+             "sample8": _BLASST_FILL_SAMPLE8, "thr": _BLASST_FILL_THR}
+    if mode in plain:
+        return plain[mode], float(alpha), 1
+    for name in ("max", "mean", "sample8", "thr"):
+        if mode.startswith(name + "_a"):
+            return plain[name], float(mode[len(name) + 2:]), 1
+    if mode == "uta":
+        if uta_bins <= 0:
+            raise ValueError(f"blasst_uta_bins must be > 0; got {uta_bins}")
+        return _BLASST_FILL_UTA, float(alpha), int(uta_bins)
+    m = re.fullmatch(r"uta(\d+)(?:_a([0-9]+(?:\.[0-9]+)?))?", mode)
+    if m:
+        bins = int(m.group(1))
+        if bins <= 0:
+            raise ValueError(f"UTA bin count must be > 0; got {bins}")
+        return _BLASST_FILL_UTA, (float(m.group(2)) if m.group(2) is not None else float(alpha)), bins
+    raise ValueError(f"unknown blasst_fill_mode: {mode!r}")
+
+
+def fake_quant_attention_fp8(
+    q_codes: torch.Tensor,          # (B, H, m_pad, D) e4m3
+    k_codes: torch.Tensor,          # (B, H, n_pad, D) e4m3
+    v_codes_t: torch.Tensor,        # (B, H, D, n_pad) e4m3 (keys contiguous)
+    *,
+    seq_q: int,
+    seq_k: int,
+    q_scale: torch.Tensor,          # (B, M/qk_block, H) fp32
+    k_scale: torch.Tensor,          # (B, N/qk_block, H) fp32
+    qk_block: int,
+    v_kind: str,                    # "fp8_channel" | "fp8_block" | "mxfp8"
+    v_scale: torch.Tensor,
+    v_block: int = 0,
+    sm_scale: float,
+    p_max_offset: int,
+    block_m: int = 64,
+    block_n: int = 64,
+    v_alpha: Optional[torch.Tensor] = None,
+    v_smooth_block: int = 0,
+    qm_corr: Optional[torch.Tensor] = None,       # (B, H, G, corr_stride) fp32 from qm_corr()
+    q_smooth_block: int = 0,
+    p_quant_mode: str = "elementwise",
+    p_mx_block_n: int = 0,
+    rowmax_est_bhs: Optional[torch.Tensor] = None,
+    rowmax_init_bhs: Optional[torch.Tensor] = None,
+    blasst_lambda: Optional[float] = None,
+    blasst_fill_mode: Optional[str] = "zero",
+    blasst_fill_alpha: float = 1.0,
+    blasst_uta_bins: int = 16,
+    return_blasst_stats: bool = False,
+    out_dtype: torch.dtype = torch.bfloat16,
+    out_nhd: bool = False,
+    out_row_index: Optional[torch.Tensor] = None,
+    out_fp32_exact: bool = False,
+):
+    """Streaming attention on e4m3 operands; output (B,H,M,D) or NHD (B,M,H,D).
+
+    ``out_row_index`` (B*H, M) int64 scatters kernel row r to output row
+    ``out_row_index[bh, r]`` (the inverse Q reorder fused into the store).
+    """
+    if not q_codes.is_cuda:
+        raise ValueError("operands must live on CUDA")
+    B, H, m_pad, D = q_codes.shape
+    n_pad = k_codes.shape[2]
+    M, N = int(seq_q), int(seq_k)
+    dev = q_codes.device
+    if p_quant_mode not in L.P_KINDS:
+        raise ValueError(f"unknown p_quant_mode: {p_quant_mode!r}")
+    if p_quant_mode == "mx":
+        if p_mx_block_n <= 0:
+            raise ValueError("p_mx_block_n must be > 0 when p_quant_mode='mx'")
+        if p_mx_block_n != block_n:
+            raise ValueError(
+                f"p_mx_block_n ({p_mx_block_n}) currently must equal block_n ({block_n}); "
+                "sub-block scaling within a K block is not implemented")
+    use_blasst = blasst_lambda is not None
+    if use_blasst:
+        if not (0.0 < float(blasst_lambda) < 1.0):
+            raise ValueError(f"blasst_lambda must be in (0, 1); got {blasst_lambda}")
+        fill_kind, fill_alpha, uta_bins = _parse_blasst_fill(
+            blasst_fill_mode, alpha=blasst_fill_alpha, uta_bins=blasst_uta_bins)
+        if fill_kind == _BLASST_FILL_UTA and block_n % uta_bins != 0:
+            raise ValueError(f"blasst UTA bins ({uta_bins}) must divide block_n ({block_n})")
+    else:
+        if blasst_fill_mode not in ("zero", None):
+            raise ValueError("blasst_fill_mode requires blasst_lambda")
+        fill_kind, fill_alpha, uta_bins = _BLASST_FILL_ZERO, 1.0, 1
+    if rowmax_est_bhs is not None and rowmax_init_bhs is not None:
+        raise ValueError("rowmax_init_bhs and rowmax_est_bhs are mutually exclusive")
+    v_kind_code = {"fp8_channel": L.V_CHANNEL, "fp8_block": L.V_BLOCK, "mxfp8": L.V_MX}[v_kind]
+
+    keep = []   # tensors that must outlive the launch call
+
+    def f32(t):
+        if t is None:
+            return None
+        t = t.to(torch.float32).contiguous()
+        keep.append(t)
+        return t
+
+    q_scale, k_scale, v_scale = f32(q_scale), f32(k_scale), f32(v_scale)
+    v_alpha, qm_corr = f32(v_alpha), f32(qm_corr)
+    rowmax_est_bhs, rowmax_init_bhs = f32(rowmax_est_bhs), f32(rowmax_init_bhs)
+
+    stats = None
+    if return_blasst_stats:
+        stats = torch.zeros(((M + block_m - 1) // block_m, B * H, 2), dtype=torch.float32, device=dev)
+    out_shape = (B, M, H, D) if out_nhd else (B, H, M, D)
+    out = torch.empty(out_shape, dtype=out_dtype, device=dev)
+
+    with torch.cuda.device(dev):
+        status = _status_for(dev)
+        a = L.AttnArgs()
+        a.B, a.H, a.M, a.N, a.D = B, H, M, N, D
+        a.m_pad, a.n_pad = m_pad, n_pad
+        a.q_codes, a.k_codes, a.v_codes = q_codes.data_ptr(), k_codes.data_ptr(), v_codes_t.data_ptr()
+        a.qk_kind = L.QK_FP8_BLOCK
+        a.q_scale, a.k_scale, a.qk_block = L.ptr(q_scale), L.ptr(k_scale), int(qk_block)
+        a.q_scale_e8 = a.k_scale_e8 = None
+        a.v_kind, a.v_scale, a.v_block = v_kind_code, L.ptr(v_scale), int(v_block)
+        a.sm_scale, a.p_max_offset = float(sm_scale), float(p_max_offset)
+        a.p_kind = L.P_KINDS[p_quant_mode]
+        a.block_m, a.block_n = int(block_m), int(block_n)
+        a.v_alpha, a.v_smooth_block = L.ptr(v_alpha), int(v_smooth_block)
+        a.qm_corr, a.q_smooth_block = L.ptr(qm_corr), int(q_smooth_block)
+        a.corr_stride = int(qm_corr.shape[-1]) if qm_corr is not None else 0
+        a.rowmax_est, a.rowmax_init = L.ptr(rowmax_est_bhs), L.ptr(rowmax_init_bhs)
+        a.use_blasst = 1 if use_blasst else 0
+        a.blasst_lambda = float(blasst_lambda) if use_blasst else 0.0
+        a.fill_kind, a.fill_alpha, a.uta_bins = int(fill_kind), float(fill_alpha), int(uta_bins)
+        a.blasst_stats = L.ptr(stats)
+        a.out = out.data_ptr()
+        a.out_dtype = L.dtype_code(out_dtype)
+        a.out_layout = L.LAYOUT_NHD if out_nhd else L.LAYOUT_BHSD
+        a.out_row_index = L.ptr(out_row_index.contiguous()) if out_row_index is not None else None
+        a.out_fp32_exact = 1 if out_fp32_exact else 0
+        a.status = status.data_ptr()
+        ws_bytes = L.lib().lbfq_attention_workspace_bytes(C.byref(a))
+        ws = torch.empty((max(int(ws_bytes), 1),), dtype=torch.uint8, device=dev)
+        L.check(L.lib().lbfq_attention_fwd(C.byref(a), ws.data_ptr(), L.stream_ptr(dev)))
+        idx = dev.index if dev.index is not None else torch.cuda.current_device()
+        _status_host[idx].copy_(status, non_blocking=True)
+    if return_blasst_stats:
+        return out, stats
+    return out
+
+
+def qm_corr(qm: torch.Tensor, k_smooth: torch.Tensor, *, sm_scale: float, s_pad: int,
+            want_rowmax: bool = False):
+    """``corr[b,h,g,n] = (qm[b,g,h,:] . k_smooth[b,n,h,:]) * sm_scale`` (fp32, (B,H,G,s_pad))
+    and optionally its row max (B,H,G) -- the Q-smoothing score correction of
+    attention_triton.py:156-160 and the estimate of attention.py:366-395."""
+    b, g, h, d = qm.shape
+    _, s, hk, dk = k_smooth.shape
+    if h != hk or d != dk:
+        raise ValueError(f"qm/k shape mismatch: qm={tuple(qm.shape)} k={tuple(k_smooth.shape)}")
+    qm = qm.to(torch.float32).contiguous()
+    k_smooth = k_smooth.contiguous()
+    corr = torch.empty((b, h, g, s_pad), dtype=torch.float32, device=qm.device)
+    rowmax = torch.empty((b, h, g), dtype=torch.float32, device=qm.device) if want_rowmax else None
+    with torch.cuda.device(qm.device):
+        L.check(L.lib().lbfq_qm_corr(qm.data_ptr(), k_smooth.data_ptr(), L.dtype_code(k_smooth.dtype), b, s, h, d, g,
+                                     float(sm_scale), corr.data_ptr(), s_pad, L.ptr(rowmax),
+                                     L.stream_ptr(qm.device)))
+    return corr, rowmax
+
+
+__all__ = ["fake_quant_attention_fp8", "qm_corr", "raise_if_device_error"]

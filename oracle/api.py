@@ -1,0 +1,401 @@
+"""CPU restatement of the reference orchestration around the kernels.
+
+TEST INFRASTRUCTURE ONLY (see ``oracle/quant_ops.py``).
+
+Restates, on CPU tensors, the glue of src/low_bit_fake_quant/attention.py
+(``_preprocess`` :166-239, ``_fake_quant_attention_sdpa`` :247-321,
+``_estimate_rowmax_from_qm_k`` :366-395, ``_fake_quant_attention_p_requant``
+:505-639, ``fake_quant_attention`` :706-806, ``reference_attention``
+:809-825) and of src/low_bit_fake_quant/kmeans.py:44-135, on top of
+``oracle.quant_ops`` and ``oracle.k12``.
+
+K-means: the reference delegates Lloyd's algorithm to the third-party package
+``flash-kmeans`` 0.3.0 (git 3f1ea6ba5fb09242913516b5a8ab8366c2b0bfe8, pinned in
+the reference's uv.lock:387-389), whose source is not part of the reference
+tree and whose centroid initialisation draws from the CUDA global RNG. Label
+parity with it is therefore UNPINNED. ``lloyd_labels`` below restates the
+published algorithm (Euclidean assignment, mean update, fixed iteration count
+because the reference passes ``tol=0``) with a documented deterministic
+initialisation; what is pinned is everything the reference's own call site
+and tests rely on: stable argsort of the labels, the inverse permutation, the
+row gather, K/V co-permutation invariance.
+"""
+
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+import torch.nn.functional as F
+
+from . import quant_ops as Q
+from .k12 import k12_attention
+
+
+# --------------------------------------------------------------------------
+# k-means reorder (kmeans.py)
+# --------------------------------------------------------------------------
+
+_M32 = 0xFFFFFFFF
+
+
+def mix32(x: int) -> int:
+    """32-bit integer finaliser (lowbias32) used for the centroid seeding."""
+    x &= _M32
+    x ^= x >> 16
+    x = (x * 0x7FEB352D) & _M32
+    x ^= x >> 15
+    x = (x * 0x846CA68B) & _M32
+    x ^= x >> 16
+    return x
+
+
+def init_indices(seed: int, bh_global: int, k: int, s: int):
+    """Token index seeding centroid j of slab ``bh_global``: one token from
+    each of k equal strata of the S axis, offset by a hash of (seed, slab, j)."""
+    out = []
+    for j in range(k):
+        lo = (j * s) // k
+        hi = ((j + 1) * s) // k
+        span = max(hi - lo, 1)
+        hsh = mix32(mix32(mix32(seed & _M32) ^ (bh_global & _M32)) ^ j)
+        out.append(lo + hsh % span)
+    return out
+
+
+def lloyd_labels(x: torch.Tensor, k: int, iters: int, seed: int, bh_offset: int = 0) -> torch.Tensor:
+    """Lloyd iterations on ``x`` (BH, S, D) fp32 -> int64 labels (BH, S).
+
+    Per iteration: assign every token to the centroid minimising
+    ``|c|^2 - 2 x.c`` (lowest index on ties), then replace each centroid by
+    the mean of its tokens (an empty cluster keeps its centroid). The labels
+    returned are those of the last assignment, as in ``batch_kmeans_Euclid``
+    called with ``tol=0`` (kmeans.py:79-81).
+    """
+    bh, s, d = x.shape
+    x = x.float()
+    labels = torch.zeros((bh, s), dtype=torch.int64)
+    for i in range(bh):
+        xi = x[i]
+        c = xi[torch.tensor(init_indices(seed, bh_offset + i, k, s))].clone()
+        lab = torch.zeros(s, dtype=torch.int64)
+        for _ in range(max(int(iters), 1)):
+            dist = (c * c).sum(-1)[None, :] - 2.0 * (xi @ c.t())
+            lab = dist.argmin(dim=1)
+            sums = torch.zeros((k, d)).index_add_(0, lab, xi)
+            cnt = torch.zeros(k).index_add_(0, lab, torch.ones(s))
+            c = torch.where(cnt[:, None] > 0, sums / cnt.clamp_min(1.0)[:, None], c)
+        labels[i] = lab
+    return labels
+
+
+@dataclass
+class KMeansReorderResult:
+    tensor_reordered: torch.Tensor
+    order: torch.Tensor
+    inverse_order: torch.Tensor
+    labels: torch.Tensor
+
+
+def reorder_from_labels(t: torch.Tensor, labels: torch.Tensor) -> KMeansReorderResult:
+    """kmeans.py:84-95: stable argsort, inverse by scatter, row gather."""
+    b, s, h, d = t.shape
+    x = t.permute(0, 2, 1, 3).reshape(b * h, s, d).contiguous().float()
+    order = torch.argsort(labels, dim=1, stable=True)
+    pos = torch.arange(s).expand_as(order)
+    inverse = torch.empty_like(order)
+    inverse.scatter_(1, order, pos)
+    xr = torch.gather(x, 1, order.unsqueeze(-1).expand(-1, -1, d))
+    tr = xr.reshape(b, h, s, d).permute(0, 2, 1, 3).to(t.dtype).contiguous()
+    return KMeansReorderResult(tr, order, inverse, labels)
+
+
+def kmeans_reorder_tokens(t, *, n_clusters: int, max_iters: int = 10, seed: int = 0,
+                          labels: Optional[torch.Tensor] = None, bh_offset: int = 0):
+    b, s, h, d = t.shape
+    if n_clusters <= 0 or n_clusters > s:
+        raise ValueError(f"n_clusters must be in [1, S]; got {n_clusters} for S={s}")
+    if labels is None:
+        x = t.permute(0, 2, 1, 3).reshape(b * h, s, d).contiguous().float()
+        labels = lloyd_labels(x, n_clusters, max_iters, seed, bh_offset)
+    return reorder_from_labels(t, labels.to(torch.int64))
+
+
+def apply_kv_permutation(t: torch.Tensor, order: torch.Tensor) -> torch.Tensor:
+    """kmeans.py:126-135."""
+    b, s, h, d = t.shape
+    tb = t.permute(0, 2, 1, 3).reshape(b * h, s, d).contiguous()
+    tr = torch.gather(tb, 1, order.unsqueeze(-1).expand(-1, -1, d))
+    return tr.reshape(b, h, s, d).permute(0, 2, 1, 3).contiguous().to(t.dtype)
+
+
+# --------------------------------------------------------------------------
+# preprocess + quant dispatch (attention.py:89-239)
+# --------------------------------------------------------------------------
+
+def preprocess(q, k, v, cfg, *, q_labels=None, v_labels=None):
+    """attention.py:166-239, same order: Q k-means, K smooth, Q smooth,
+    V k-means (+K co-permute), V smooth."""
+    qw, kw, vw = q.contiguous(), k.contiguous(), v.contiguous()
+    q_km = None
+    if cfg.q_kmeans_k is not None:
+        q_km = kmeans_reorder_tokens(qw, n_clusters=cfg.q_kmeans_k, max_iters=cfg.q_kmeans_iters,
+                                     seed=cfg.q_kmeans_seed, labels=q_labels)
+        qw = q_km.tensor_reordered
+    qm = None
+    if cfg.smoothing == "k_only":
+        kw, _ = Q.smooth_k(kw)
+    elif cfg.smoothing == "full":
+        kw, _ = Q.smooth_k(kw)
+        qw, qm = Q.group_mean_q(qw, block_q=cfg.q_smooth_block_size)
+    elif cfg.smoothing != "off":
+        raise ValueError(f"unsupported smoothing: {cfg.smoothing!r}")
+    v_km = None
+    if cfg.v_kmeans_k is not None:
+        v_km = kmeans_reorder_tokens(vw, n_clusters=cfg.v_kmeans_k, max_iters=cfg.v_kmeans_iters,
+                                     seed=cfg.v_kmeans_seed, labels=v_labels)
+        vw = v_km.tensor_reordered
+        kw = apply_kv_permutation(kw, v_km.order)
+    v_alpha = None
+    if cfg.v_smooth_mode == "per_block":
+        vw, v_alpha = Q.smooth_v_per_block(vw, block_s=cfg.v_smooth_block_size)
+    elif cfg.v_smooth_mode != "off":
+        raise ValueError(f"unsupported v_smooth_mode: {cfg.v_smooth_mode!r}")
+    return qw, kw, vw, qm, v_alpha, q_km, v_km
+
+
+def quant_qk(t, cfg):
+    if cfg.qk_quant == "fp8_block":
+        c, s = Q.fp8_block_quant(t, block_s=cfg.fp8_block_size)
+        return c, s, {"kind": "fp8_block", "block_s": cfg.fp8_block_size}
+    if cfg.qk_quant == "mxfp8":
+        c, s = Q.mxfp8_qk_quant(t, block_d=cfg.mxfp8_block_size)
+        return c, s, {"kind": "mxfp8", "block_d": cfg.mxfp8_block_size}
+    raise ValueError(f"unsupported qk_quant: {cfg.qk_quant!r}")
+
+
+def dequant_qk(c, s, meta, dtype):
+    if meta["kind"] == "fp8_block":
+        return Q.fp8_block_dequant(c, s, block_s=meta["block_s"], dtype=dtype)
+    return Q.mxfp8_qk_dequant(c, s, block_d=meta["block_d"], dtype=dtype)
+
+
+def quant_v(t, cfg):
+    if cfg.v_quant == "fp8_channel":
+        c, s = Q.fp8_per_channel_quant(t)
+        return c, s, {"kind": "fp8_channel"}
+    if cfg.v_quant == "fp8_block":
+        c, s = Q.fp8_block_quant(t, block_s=cfg.v_fp8_block_size)
+        return c, s, {"kind": "fp8_block", "block_s": cfg.v_fp8_block_size}
+    if cfg.v_quant == "mxfp8":
+        c, s = Q.mxfp8_v_quant(t, block_s=cfg.v_mxfp8_block_size)
+        return c, s, {"kind": "mxfp8", "block_s": cfg.v_mxfp8_block_size}
+    raise ValueError(f"unsupported v_quant: {cfg.v_quant!r}")
+
+
+def dequant_v(c, s, meta, dtype):
+    if meta["kind"] == "fp8_channel":
+        return Q.fp8_per_channel_dequant(c, s, dtype=dtype)
+    if meta["kind"] == "fp8_block":
+        return Q.fp8_block_dequant(c, s, block_s=meta["block_s"], dtype=dtype)
+    return Q.mxfp8_v_dequant(c, s, block_s=meta["block_s"], dtype=dtype)
+
+
+def qk_inputs_for_quant(qw, kw, cfg):
+    if not cfg.qk_hadamard:
+        return qw, kw
+    return Q.apply_qk_hadamard(qw, kw, random_sign=cfg.qk_hadamard_random_sign, seed=cfg.qk_hadamard_seed)
+
+
+def estimate_rowmax_from_qm_k(qm, k_work, *, block_q: int, sm_scale: float, chunk_n: int = 4096):
+    """attention.py:366-395."""
+    b, g, h, d = qm.shape
+    s = k_work.shape[1]
+    qmb = qm.permute(0, 2, 1, 3).contiguous().float()
+    kb = k_work.permute(0, 2, 1, 3).contiguous().float()
+    rm = torch.full((b, h, g), -float("inf"))
+    for n0 in range(0, s, chunk_n):
+        sc = torch.matmul(qmb, kb[:, :, n0:n0 + chunk_n].transpose(-2, -1))
+        rm = torch.maximum(rm, sc.amax(dim=-1))
+    return (rm * float(sm_scale)).repeat_interleave(block_q, dim=2).contiguous()
+
+
+# --------------------------------------------------------------------------
+# path A: de-quantise and run SDPA (attention.py:247-321)
+# --------------------------------------------------------------------------
+
+def attention_sdpa(qw, kw, vw, qm, v_alpha, cfg, sm_scale, sdpa_dtype):
+    b, s, h, d = qw.shape
+    qi, ki = qk_inputs_for_quant(qw, kw, cfg)
+    qc, qs, qmeta = quant_qk(qi, cfg)
+    kc, ks, kmeta = quant_qk(ki, cfg)
+    vc, vs, vmeta = quant_v(vw, cfg)
+    qd = dequant_qk(qc, qs, qmeta, sdpa_dtype)
+    kd = dequant_qk(kc, ks, kmeta, sdpa_dtype)
+    vd = dequant_v(vc, vs, vmeta, sdpa_dtype)
+    if v_alpha is not None:
+        vd = vd + v_alpha.repeat_interleave(cfg.v_smooth_block_size, dim=1).to(sdpa_dtype)
+    if qm is None:
+        o = F.scaled_dot_product_attention(qd.permute(0, 2, 1, 3), kd.permute(0, 2, 1, 3),
+                                           vd.permute(0, 2, 1, 3), scale=sm_scale)
+        return o.permute(0, 2, 1, 3).contiguous()
+    block_q = cfg.q_smooth_block_size
+    chunk = max(block_q, 256)
+    qb = qd.permute(0, 2, 1, 3).contiguous()
+    qmb = qm.permute(0, 2, 1, 3).contiguous()
+    kdb = kd.permute(0, 2, 1, 3).contiguous()
+    ksb = kw.permute(0, 2, 1, 3).contiguous()
+    vb = vd.permute(0, 2, 1, 3).contiguous()
+    out = torch.empty_like(qb)
+    grp = torch.arange(s) // block_q
+    for m0 in range(0, s, chunk):
+        m1 = min(m0 + chunk, s)
+        s_main = torch.matmul(qb[:, :, m0:m1], kdb.transpose(-2, -1)).float() * sm_scale
+        s_corr = torch.matmul(qmb[:, :, grp[m0:m1]], ksb.float().transpose(-2, -1)) * sm_scale
+        p = torch.softmax(s_main + s_corr, dim=-1).to(sdpa_dtype)
+        out[:, :, m0:m1] = torch.matmul(p, vb)
+    return out.permute(0, 2, 1, 3).contiguous()
+
+
+# --------------------------------------------------------------------------
+# path B: streaming kernel with P re-quantisation (attention.py:505-639)
+# --------------------------------------------------------------------------
+
+def attention_p_requant(qw, kw, vw, qm, v_alpha, cfg, sm_scale, *, faithful: bool,
+                        return_stats: bool = False):
+    """Returns the kernel's FP32 output in NHD (B,S,H,D), before the final cast."""
+    b, s, h, d = qw.shape
+    qi, ki = qk_inputs_for_quant(qw, kw, cfg)
+    qc, qs, qmeta = quant_qk(qi, cfg)
+    kc, ks, kmeta = quant_qk(ki, cfg)
+    vc, vs, vmeta = quant_v(vw, cfg)
+    perm = lambda t: t.permute(0, 2, 1, 3).contiguous()
+
+    row_scale = col_scale = None
+    if faithful or qmeta["kind"] == "mxfp8":
+        # power-of-two scales make the BF16 de-quantisation exact, so the
+        # mxfp8 operands are identical under both conventions
+        q_op = perm(dequant_qk(qc, qs, qmeta, torch.bfloat16)).float()
+        k_op = perm(dequant_qk(kc, ks, kmeta, torch.bfloat16)).float()
+    else:
+        blk = qmeta["block_s"]
+        q_op = perm(qc.float())
+        k_op = perm(kc.float())
+        row_scale = qs.permute(0, 2, 1).repeat_interleave(blk, dim=2).contiguous()   # (B,H,S)
+        col_scale = ks.permute(0, 2, 1).repeat_interleave(blk, dim=2).contiguous()
+
+    v_block_scale = None
+    v_block_size = 0
+    if vmeta["kind"] == "fp8_channel":
+        v_op = perm(vc.float())
+        v_scale_bhd = vs.float()
+    elif vmeta["kind"] == "fp8_block":
+        v_op = perm(vc.float())
+        v_scale_bhd = torch.ones((b, h, d))
+        v_block_scale = vs.float()
+        v_block_size = vmeta["block_s"]
+    else:
+        v_op = perm(dequant_v(vc, vs, vmeta, torch.bfloat16)).float()
+        v_scale_bhd = torch.ones((b, h, d))
+
+    k_smooth = qm_arg = None
+    if qm is not None:
+        k_smooth = perm(kw.to(torch.bfloat16))
+        qm_arg = qm.float()
+    rowmax_est = None
+    if cfg.rowmax_mode == "qm_k":
+        if qm is None:
+            raise ValueError("rowmax_mode='qm_k' requires smoothing='full' so qm exists")
+        rowmax_est = estimate_rowmax_from_qm_k(qm, kw, block_q=cfg.q_smooth_block_size, sm_scale=sm_scale)
+    elif cfg.rowmax_mode != "online":
+        raise ValueError(f"unsupported rowmax_mode: {cfg.rowmax_mode!r}")
+    p_mode = cfg.p_quant
+    if p_mode == "auto":
+        p_mode = "mx" if vmeta["kind"] == "mxfp8" else "elementwise"
+
+    res = k12_attention(
+        q_op, k_op, v_op, v_scale_bhd,
+        sm_scale=float(sm_scale), p_max_offset=int(cfg.p_max_offset),
+        block_m=cfg.p_requant_block_m, block_n=cfg.p_requant_block_n,
+        row_scale=row_scale, col_scale=col_scale,
+        v_alpha=v_alpha.float() if v_alpha is not None else None,
+        v_smooth_block=cfg.v_smooth_block_size if v_alpha is not None else 0,
+        k_smooth=k_smooth, qm=qm_arg,
+        q_smooth_block=cfg.q_smooth_block_size if qm is not None else 0,
+        v_block_scale=v_block_scale, v_block_size=v_block_size,
+        p_quant_mode=p_mode, rowmax_est=rowmax_est,
+        blasst_lambda=cfg.blasst_lambda, blasst_fill_mode=cfg.blasst_fill,
+        blasst_fill_alpha=cfg.blasst_fill_alpha, blasst_uta_bins=cfg.blasst_uta_bins,
+        faithful=faithful, return_stats=return_stats,
+    )
+    if return_stats:
+        return res[0].permute(0, 2, 1, 3).contiguous(), res[1]
+    return res.permute(0, 2, 1, 3).contiguous()
+
+
+# --------------------------------------------------------------------------
+# entry points (attention.py:706-825)
+# --------------------------------------------------------------------------
+
+def fake_quant_attention(q, k, v, cfg, *, sm_scale: Optional[float] = None, faithful: bool = True,
+                         q_labels=None, v_labels=None, out_fp32: bool = False):
+    """attention.py:706-806 on CPU tensors.
+
+    ``faithful=True`` follows the reference's BF16 de-quantised operands;
+    ``faithful=False`` is the true-FP8 convention (see ``oracle/k12.py``).
+    ``out_fp32`` returns the kernel's FP32 result before the cast to
+    ``q.dtype`` so that tolerances below one BF16 ulp can be checked.
+    """
+    if q.shape != k.shape or q.shape != v.shape:
+        raise ValueError(f"q/k/v shapes must match; got {tuple(q.shape)}, {tuple(k.shape)}, {tuple(v.shape)}")
+    if q.ndim != 4:
+        raise ValueError(f"q/k/v must be 4-D (B,S,H,D); got {q.shape}")
+    out_dtype = q.dtype
+    if out_dtype not in (torch.float16, torch.bfloat16, torch.float32):
+        raise TypeError(f"unsupported dtype {out_dtype}")
+    sdpa_dtype = torch.float16 if out_dtype == torch.float16 else torch.bfloat16
+    b, s, h, d = q.shape
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(d)
+    if cfg.blasst_lambda is not None and not cfg.p_requant:
+        raise ValueError("BLASST skip/fill requires cfg.p_requant=True")
+    qw, kw, vw, qm, v_alpha, q_km, _ = preprocess(q, k, v, cfg, q_labels=q_labels, v_labels=v_labels)
+    if cfg.p_requant:
+        o = attention_p_requant(qw, kw, vw, qm, v_alpha, cfg, sm_scale, faithful=faithful)
+        if not out_fp32:
+            o = o.to(torch.bfloat16).to(out_dtype)        # kernel stores BF16, then .to(out_dtype)
+    else:
+        o = attention_sdpa(qw, kw, vw, qm, v_alpha, cfg, sm_scale, sdpa_dtype)
+        o = o.float() if out_fp32 else o.to(out_dtype)
+    if q_km is not None:
+        inv = q_km.inverse_order
+        ob = o.permute(0, 2, 1, 3).reshape(b * h, s, d)
+        ob = torch.gather(ob, 1, inv.unsqueeze(-1).expand(-1, -1, d))
+        o = ob.reshape(b, h, s, d).permute(0, 2, 1, 3).contiguous()
+    return o
+
+
+def reference_attention(q, k, v, *, sm_scale: Optional[float] = None):
+    """attention.py:809-825: SDPA on the raw inputs."""
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(q.shape[-1])
+    o = F.scaled_dot_product_attention(q.permute(0, 2, 1, 3), k.permute(0, 2, 1, 3),
+                                       v.permute(0, 2, 1, 3), scale=sm_scale)
+    return o.permute(0, 2, 1, 3).contiguous()
+
+
+def compute_metrics(out: torch.Tensor, ref: torch.Tensor) -> dict:
+    """mse / rmse / global cosine / rel_l2 / max_abs (bench/eval_wan21.py:109-125)."""
+    a = out.float().flatten()
+    r = ref.float().flatten()
+    diff = a - r
+    mse = float((diff * diff).mean())
+    return {
+        "mse": mse,
+        "rmse": math.sqrt(mse),
+        "cosine": float(F.cosine_similarity(a[None], r[None]).item()),
+        "rel_l2": float(diff.norm() / r.norm().clamp_min(1e-12)),
+        "max_abs": float(diff.abs().max()),
+    }
