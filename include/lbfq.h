@@ -49,6 +49,9 @@ extern "C" {
 const char* lbfq_last_error(void);
 /* ABI version of this header; bumped when a signature changes. */
 int lbfq_abi_version(void);
+/* Number of kernels this library has launched in the calling process (a plain counter,
+ * not thread-safe; used by the benchmark to report its launch count). */
+unsigned long long lbfq_launch_count(void);
 
 /* ======================= quantizers (quant_triton.py) ===================== */
 

@@ -30,6 +30,10 @@ _BLASST_FILL_SAMPLE8 = 4
 _BLASST_FILL_THR = 5
 _BLASST_FILL_UTA = 6
 
+# When set to a list, every launch appends a (start, end) pair of CUDA events recorded
+# on the launching stream around the attention kernel (used by bench.py for the roofline).
+KERNEL_EVENTS: Optional[list] = None
+
 _status_dev: dict[int, torch.Tensor] = {}
 _status_host: dict[int, torch.Tensor] = {}
 
@@ -199,7 +203,13 @@ def fake_quant_attention_fp8(
         a.status = status.data_ptr()
         ws_bytes = L.lib().lbfq_attention_workspace_bytes(C.byref(a))
         ws = torch.empty((max(int(ws_bytes), 1),), dtype=torch.uint8, device=dev)
+        if KERNEL_EVENTS is not None:
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            ev0.record()
         L.check(L.lib().lbfq_attention_fwd(C.byref(a), ws.data_ptr(), L.stream_ptr(dev)))
+        if KERNEL_EVENTS is not None:
+            ev1.record()
+            KERNEL_EVENTS.append((ev0, ev1))
         idx = dev.index if dev.index is not None else torch.cuda.current_device()
         _status_host[idx].copy_(status, non_blocking=True)
     if return_blasst_stats:

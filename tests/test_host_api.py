@@ -1,0 +1,110 @@
+"""Host-side mirror of the reference API and the C-ABI boundary (no GPU needed)."""
+import ctypes
+import dataclasses
+import os
+import re
+
+import pytest
+import torch
+
+import low_bit_fake_quant as fq
+from low_bit_fake_quant import _lib as L
+from low_bit_fake_quant.sharding import all_ranges, slab_range
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_loads_and_exports_every_declared_symbol():
+    lib = L.lib()
+    assert lib.lbfq_abi_version() >= 1
+    header = open(os.path.join(ROOT, "include", "lbfq.h")).read()
+    header = re.sub(r"/\*.*?\*/", "", header, flags=re.S)
+    declared = sorted(set(re.findall(r"\b(lbfq_[a-z0-9_]+)\s*\(", header)))
+    assert len(declared) >= 20
+    for name in declared:
+        assert hasattr(lib, name), f"{name} declared in include/lbfq.h but not exported"
+    assert sorted(L.exported_symbols()) == declared          # the ctypes table covers the whole header
+
+
+def test_attn_args_struct_matches_header_field_order():
+    header = open(os.path.join(ROOT, "include", "lbfq.h")).read()
+    body = re.search(r"typedef struct lbfq_attn_args \{(.*?)\} lbfq_attn_args;", header, flags=re.S).group(1)
+    body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
+    names = []
+    for stmt in body.split(";"):
+        stmt = stmt.strip()
+        if not stmt:
+            continue
+        for part in stmt.split(","):
+            names.append(re.findall(r"([A-Za-z_][A-Za-z0-9_]*)\s*$", part.strip())[0])
+    assert names == [f[0] for f in L.AttnArgs._fields_]
+
+
+def test_public_names_match_reference_package():
+    want = {"FakeQuantArtifacts", "KMeansReorderResult", "PreparedQKV", "PreprocessCache", "QuantConfig",
+            "apply_qk_hadamard", "fake_quant_attention", "fast_hadamard_available", "prepare_for_attention",
+            "fp8_block_dequant", "fp8_block_quant", "fp8_per_channel_dequant", "fp8_per_channel_quant",
+            "group_mean_q", "hadamard_transform_last_dim", "smooth_v_per_block", "mxfp8_qk_dequant",
+            "mxfp8_qk_quant", "mxfp8_v_dequant", "mxfp8_v_quant", "prepare_qkv", "apply_kv_permutation",
+            "kmeans_reorder_tokens", "q_kmeans_reorder", "v_kmeans_reorder", "reference_attention", "smooth_k"}
+    assert set(fq.__all__) == want
+    for n in want:
+        assert hasattr(fq, n)
+
+
+def test_quant_config_defaults_and_frozen():
+    c = fq.QuantConfig()
+    assert (c.qk_quant, c.v_quant, c.smoothing) == ("fp8_block", "fp8_channel", "full")
+    assert (c.q_smooth_block_size, c.q_kmeans_k, c.q_kmeans_iters, c.q_kmeans_seed) == (256, 32, 10, 0)
+    assert (c.fp8_block_size, c.mxfp8_block_size, c.v_fp8_block_size, c.v_mxfp8_block_size) == (128, 32, 64, 64)
+    assert (c.p_quant, c.rowmax_mode, c.p_mx_block_n, c.p_max_offset, c.p_requant) == ("auto", "online", 0, 8, True)
+    assert (c.p_requant_q_chunk, c.p_requant_block_m, c.p_requant_block_n) == (512, 64, 64)
+    assert (c.blasst_lambda, c.blasst_fill, c.blasst_fill_alpha, c.blasst_uta_bins) == (None, "zero", 1.0, 16)
+    assert (c.v_smooth_mode, c.v_smooth_block_size, c.v_kmeans_k, c.v_kmeans_iters, c.v_kmeans_seed) == ("off", 64, None, 10, 0)
+    assert c.correction_dtype == torch.float16 and c.qk_hadamard is False and c.qk_hadamard_random_sign is True
+    assert len(dataclasses.fields(c)) == 32
+    with pytest.raises(dataclasses.FrozenInstanceError):
+        c.qk_quant = "mxfp8"
+
+
+def test_cpu_tensors_are_refused_like_the_reference():
+    x = torch.zeros(1, 64, 1, 64, dtype=torch.bfloat16)
+    with pytest.raises(ValueError, match="must live on CUDA"):
+        fq.fake_quant_attention(x, x, x)
+    with pytest.raises(ValueError, match="must live on CUDA"):
+        fq.fp8_block_quant(x)
+    with pytest.raises(ValueError, match="on CUDA"):
+        fq.smooth_k(x)
+    with pytest.raises(ValueError, match="CUDA"):
+        fq.apply_qk_hadamard(x, x)
+    with pytest.raises(ValueError, match="on CUDA"):
+        fq.kmeans_reorder_tokens(x, n_clusters=2)
+    with pytest.raises(ValueError, match="4-D"):
+        fq.fake_quant_attention(x[0], x[0], x[0])
+    with pytest.raises(ValueError, match="shapes must match"):
+        fq.fake_quant_attention(x, x[:, :32], x)
+
+
+def test_c_abi_argument_errors_without_a_gpu():
+    """Validation happens before any CUDA call, so it is observable on a CPU box."""
+    lib = L.lib()
+    rc = lib.lbfq_fp8_block_quant(None, L.BF16, 1, 100, 1, 128, 64, None, 0, 0, None, None)
+    assert rc == L.ERR_ARG and b"divisible" in lib.lbfq_last_error()
+    rc = lib.lbfq_fp8_block_quant(None, L.BF16, 1, 128, 1, 96, 64, None, 0, 0, None, None)
+    assert rc == L.ERR_ARG and b"64 or 128" in lib.lbfq_last_error()
+    with pytest.raises(ValueError):
+        L.check(rc)
+    a = L.AttnArgs()
+    assert lib.lbfq_attention_fwd(ctypes.byref(a), None, None) == L.ERR_ARG
+
+
+def test_slab_ranges_partition_the_heads():
+    for total in (40, 80, 7):
+        for world in (1, 2, 4, 8):
+            r = all_ranges(total, world)
+            assert r[0][0] == 0 and r[-1][1] == total
+            assert all(r[i][1] == r[i + 1][0] for i in range(world - 1))
+            sizes = [hi - lo for lo, hi in r]
+            assert max(sizes) - min(sizes) <= 1
+    with pytest.raises(ValueError):
+        slab_range(8, 2, 2)
