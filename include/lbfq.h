@@ -118,11 +118,13 @@ int lbfq_hadamard(const void* x, int dtype, int64_t rows, int H, int D, const in
 
 /* Lloyd iterations replacing flash_kmeans.batch_kmeans_Euclid as called from
  * src/low_bit_fake_quant/kmeans.py:77-81. x: NHD of dtype. labels: int32
- * (B*H, S). `bh_offset` is the global index of slab 0 (for sharded runs).
- * scratch: lbfq_kmeans_scratch_bytes(...) bytes. */
+ * (B*H, S). The centroid seeding hashes the slab index of the unsharded problem,
+ * b * total_heads + head_offset + h, so a heads shard reproduces the full run
+ * (total_heads <= 0 means "not sharded"). scratch: lbfq_kmeans_scratch_bytes(...) bytes. */
 int64_t lbfq_kmeans_scratch_bytes(int B, int S, int H, int D, int k);
 int lbfq_kmeans_labels(const void* x, int dtype, int B, int S, int H, int D, int k, int iters,
-                       int seed, int bh_offset, int32_t* labels, void* scratch, void* stream);
+                       int seed, int head_offset, int total_heads, int32_t* labels, void* scratch,
+                       void* stream);
 
 /* kmeans.py:84-88: order = stable argsort(labels), inverse[order[j]] = j.
  * labels int32 (BH, S), values in [0, k); order / inverse int64 (BH, S). */

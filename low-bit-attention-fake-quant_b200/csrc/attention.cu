@@ -317,9 +317,32 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
 #pragma unroll
     for (int i = 0; i < D; ++i) acc[i] = 0.f;
 
-    // fold PV of block `jb` (scale c, rescale a) into the accumulator
+    // fold PV of block `jb` (scale c, rescale a) into the accumulator. The mode
+    // switches are warp-uniform and hoisted out of the unrolled loops so that no
+    // lane issues predicated-off work.
     auto accumulate = [&](int jb, float a, float c) {
       tc_fence_after();
+      const bool rescale = __any_sync(0xffffffffu, a != 1.f);
+      const bool scaled = __any_sync(0xffffffffu, c != 1.f);
+      if (!p.v_alpha && p.v_kind != LBFQ_V_MX) {
+#pragma unroll
+        for (int c0 = 0; c0 < D; c0 += 32) {
+          uint32_t r[32];
+          LBFQ_TMEM_LD32(r, tO + c0);
+          tc_wait_ld();
+          if (rescale) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) acc[c0 + i] = fmaf(c, __uint_as_float(r[i]), acc[c0 + i] * a);
+          } else if (scaled) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) acc[c0 + i] = fmaf(c, __uint_as_float(r[i]), acc[c0 + i]);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) acc[c0 + i] += __uint_as_float(r[i]);
+          }
+        }
+        return;
+      }
       float rs = 0.f;
       const float* av = nullptr;
       const float* vs = nullptr;
@@ -329,19 +352,39 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
       }
       if (p.v_kind == LBFQ_V_MX)
         vs = p.v_scale + (((size_t)b * (p.N / p.v_block) + (jb * BN) / p.v_block) * p.H + h) * D;
-      const bool rescale = __any_sync(0xffffffffu, a != 1.f);
 #pragma unroll
       for (int c0 = 0; c0 < D; c0 += 32) {
         uint32_t r[32];
         LBFQ_TMEM_LD32(r, tO + c0);
         tc_wait_ld();
+        if (vs) {
+          const float4* v4 = reinterpret_cast<const float4*>(vs + c0);
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float v = __uint_as_float(r[i]);
-          if (vs) v *= __ldg(vs + c0 + i);
-          if (av) v = fmaf(rs, __ldg(av + c0 + i), v);
-          const float base = rescale ? acc[c0 + i] * a : acc[c0 + i];
-          acc[c0 + i] = fmaf(c, v, base);
+          for (int i = 0; i < 8; ++i) {
+            const float4 w = __ldg(v4 + i);
+            r[4 * i + 0] = __float_as_uint(__uint_as_float(r[4 * i + 0]) * w.x);
+            r[4 * i + 1] = __float_as_uint(__uint_as_float(r[4 * i + 1]) * w.y);
+            r[4 * i + 2] = __float_as_uint(__uint_as_float(r[4 * i + 2]) * w.z);
+            r[4 * i + 3] = __float_as_uint(__uint_as_float(r[4 * i + 3]) * w.w);
+          }
+        }
+        if (av) {
+          const float4* a4 = reinterpret_cast<const float4*>(av + c0);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float4 w = __ldg(a4 + i);
+            r[4 * i + 0] = __float_as_uint(fmaf(rs, w.x, __uint_as_float(r[4 * i + 0])));
+            r[4 * i + 1] = __float_as_uint(fmaf(rs, w.y, __uint_as_float(r[4 * i + 1])));
+            r[4 * i + 2] = __float_as_uint(fmaf(rs, w.z, __uint_as_float(r[4 * i + 2])));
+            r[4 * i + 3] = __float_as_uint(fmaf(rs, w.w, __uint_as_float(r[4 * i + 3])));
+          }
+        }
+        if (rescale) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) acc[c0 + i] = fmaf(c, __uint_as_float(r[i]), acc[c0 + i] * a);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) acc[c0 + i] = fmaf(c, __uint_as_float(r[i]), acc[c0 + i]);
         }
       }
     };
@@ -382,7 +425,6 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         const float sk = p.k_scale[((size_t)b * (p.N / p.qk_block) + n0 / p.qk_block) * p.H + h];
         f = (sq * sk) * p.sm_scale;
       }
-      float bmax = -INFINITY;
       if (corr_row) {
         const float4* c4 = reinterpret_cast<const float4*>(corr_row + n0);
 #pragma unroll
@@ -397,12 +439,16 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
 #pragma unroll
         for (int i = 0; i < BN; ++i) s[i] *= f;
       }
-      if (nvalid < BN) {
+      if (nvalid < BN) {                    // ragged tail: only the last block of a sequence
 #pragma unroll
         for (int i = 0; i < BN; ++i) if (i >= nvalid) s[i] = -INFINITY;
       }
+      float bm0 = s[0], bm1 = s[1], bm2 = s[2], bm3 = s[3];
 #pragma unroll
-      for (int i = 0; i < BN; ++i) bmax = fmaxf(bmax, s[i]);
+      for (int i = 4; i < BN; i += 4) {
+        bm0 = fmaxf(bm0, s[i]); bm1 = fmaxf(bm1, s[i + 1]); bm2 = fmaxf(bm2, s[i + 2]); bm3 = fmaxf(bm3, s[i + 3]);
+      }
+      const float bmax = fmaxf(fmaxf(bm0, bm1), fmaxf(bm2, bm3));
 
       // ---- running max / rescale factor (attention_triton.py:164-217) ----------
       float m_new, alpha;
@@ -447,111 +493,114 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
       float c_blk = 1.f;
       if (!elide) {
         // ---- P = exp2(z), l += sum(P) (attention_triton.py:219-326) -------------
+        // z = (s - m) * log2e + off in every mode (off = 0 for the scaled P modes, where the
+        // product alone is what the reference computes: fma(x, c, 0) == x * c).
         const float off = p.p_kind == LBFQ_P_ELEMENTWISE ? p.p_off : 0.f;
-        float stat_mean = 0.f, stat_var = 0.f;
-        if (BLASST && p.fill_kind != LBFQ_FILL_ZERO) {
-          // block statistics of the un-skipped scores, needed by the fills
-          float sum = 0.f;
+        float psum, pmax;
+        if (BLASST && skip) {
+          // a skipped row contributes only its softmax-free fill (zero for the "zero" fill)
+          psum = 0.f; pmax = 0.f;
+          if (p.fill_kind == LBFQ_FILL_ZERO) {
 #pragma unroll
-          for (int i = 0; i < BN; ++i) sum += (i < nvalid) ? s[i] : 0.f;
-          stat_mean = sum / (float)max(nvalid, 1);
-          if (p.fill_kind == LBFQ_FILL_LOGN) {
-            float v2 = 0.f;
-#pragma unroll
-            for (int i = 0; i < BN; ++i) { const float cdev = (i < nvalid) ? s[i] - stat_mean : 0.f; v2 += cdev * cdev; }
-            stat_var = v2 / (float)max(nvalid, 1);
-          }
-        }
-        float fill_bins[(BLASST ? 16 : 1)];
-        int bin_size = BN;
-        float fill_p = 0.f;
-        bool per_bin = false;
-        if (BLASST && p.fill_kind != LBFQ_FILL_ZERO && skip) {
-          const float safe_n = (float)max(nvalid, 1);
-          const float max_bound = safe_n * ex2((bmax - m_new) * kLog2e + off);
-          if (p.fill_kind == LBFQ_FILL_MAX) {
-            fill_p = max_bound * p.fill_alpha / safe_n;
-          } else if (p.fill_kind == LBFQ_FILL_MEAN) {
-            fill_p = fminf(p.fill_alpha * safe_n * ex2((stat_mean - m_new) * kLog2e + off), max_bound) / safe_n;
-          } else if (p.fill_kind == LBFQ_FILL_LOGN) {
-            fill_p = fminf(safe_n * ex2((stat_mean + 0.5f * stat_var - m_new) * kLog2e + off), max_bound) / safe_n;
-          } else if (p.fill_kind == LBFQ_FILL_SAMPLE8) {
-            const int stride = BN >= 8 ? BN / 8 : 1;
-            float ssum = 0.f, cnt = 0.f;
-#pragma unroll
-            for (int i = 0; i < BN; ++i)
-              if ((i % stride) == 0 && i < nvalid) { ssum += ex2((s[i] - m_new) * kLog2e + off); cnt += 1.f; }
-            fill_p = fminf(p.fill_alpha * safe_n * ssum / fmaxf(cnt, 1.f), max_bound) / safe_n;
-          } else if (p.fill_kind == LBFQ_FILL_THR) {
-            const float off_scale = p.p_kind == LBFQ_P_ELEMENTWISE ? exp2f(p.p_off) : 1.f;
-            fill_p = (p.fill_alpha * safe_n * p.lambda * off_scale) / safe_n;
-          } else {                                             // UTA: one value per bin of BN / bins keys
-            per_bin = true;
-            bin_size = BN / p.uta_bins;
-#pragma unroll
-            for (int bi = 0; bi < 16; ++bi) fill_bins[bi] = 0.f;
-            // bins are contiguous column ranges; accumulate with a running bin index
-            float bsum = 0.f, bmx = -INFINITY, bcnt = 0.f;
-            int cur = 0;
-#pragma unroll
-            for (int i = 0; i < BN; ++i) {
-              if (i < nvalid) { bsum += s[i]; bmx = fmaxf(bmx, s[i]); bcnt += 1.f; }
-              if (((i + 1) % bin_size) == 0) {
-                const float safe_c = fmaxf(bcnt, 1.f);
-                const float bound = safe_c * ex2((bmx - m_new) * kLog2e + off);
-                const float mass = p.fill_alpha * safe_c * ex2((bsum / safe_c - m_new) * kLog2e + off);
-                const float val = fminf(mass, bound) / safe_c;
-#pragma unroll
-                for (int bi = 0; bi < 16; ++bi) if (bi == cur) fill_bins[bi] = val;
-                ++cur; bsum = 0.f; bmx = -INFINITY; bcnt = 0.f;
-              }
-            }
-          }
-        }
-
-        float psum = 0.f, pmax = 0.f;
-#pragma unroll
-        for (int i = 0; i < BN; ++i) {
-          float pv;
-          if (BLASST && skip) {
-            if (per_bin) {
-              float val = 0.f;
-              const int bi = i / bin_size;
-#pragma unroll
-              for (int q = 0; q < 16; ++q) if (q == bi) val = fill_bins[q];
-              pv = val;
-            } else {
-              pv = fill_p;
-            }
+            for (int i = 0; i < BN; ++i) s[i] = 0.f;
           } else {
-            pv = ex2(p.p_kind == LBFQ_P_ELEMENTWISE ? fmaf(s[i] - m_new, kLog2e, off) : (s[i] - m_new) * kLog2e);
+            const float safe_n = (float)max(nvalid, 1);
+            float sum = 0.f;
+#pragma unroll
+            for (int i = 0; i < BN; ++i) sum += (i < nvalid) ? s[i] : 0.f;
+            const float mean = sum / safe_n;
+            const float max_bound = safe_n * ex2((bmax - m_new) * kLog2e + off);
+            float fill_p = 0.f;
+            if (p.fill_kind == LBFQ_FILL_MAX) {
+              fill_p = max_bound * p.fill_alpha / safe_n;
+            } else if (p.fill_kind == LBFQ_FILL_MEAN) {
+              fill_p = fminf(p.fill_alpha * safe_n * ex2((mean - m_new) * kLog2e + off), max_bound) / safe_n;
+            } else if (p.fill_kind == LBFQ_FILL_LOGN) {
+              float v2 = 0.f;
+#pragma unroll
+              for (int i = 0; i < BN; ++i) { const float cd = (i < nvalid) ? s[i] - mean : 0.f; v2 += cd * cd; }
+              const float var = v2 / safe_n;
+              fill_p = fminf(safe_n * ex2((mean + 0.5f * var - m_new) * kLog2e + off), max_bound) / safe_n;
+            } else if (p.fill_kind == LBFQ_FILL_SAMPLE8) {
+              const int stride = BN >= 8 ? BN / 8 : 1;
+              float ssum = 0.f, cnt = 0.f;
+#pragma unroll
+              for (int i = 0; i < BN; i += stride)
+                if (i < nvalid) { ssum += ex2((s[i] - m_new) * kLog2e + off); cnt += 1.f; }
+              fill_p = fminf(p.fill_alpha * safe_n * ssum / fmaxf(cnt, 1.f), max_bound) / safe_n;
+            } else if (p.fill_kind == LBFQ_FILL_THR) {
+              const float off_scale = p.p_kind == LBFQ_P_ELEMENTWISE ? exp2f(p.p_off) : 1.f;
+              fill_p = (p.fill_alpha * safe_n * p.lambda * off_scale) / safe_n;
+            }
+            if (p.fill_kind != LBFQ_FILL_UTA) {
+#pragma unroll
+              for (int i = 0; i < BN; ++i) s[i] = (i < nvalid) ? fill_p : 0.f;
+              psum = fill_p * 0.f;
+#pragma unroll
+              for (int i = 0; i < BN; ++i) psum += s[i];
+              pmax = fill_p;
+            } else {                                           // UTA: one value per bin of BN / bins keys
+              const int bin_size = BN / p.uta_bins;
+              float bsum = 0.f, bmx = -INFINITY, bcnt = 0.f;
+              int first = 0;
+#pragma unroll
+              for (int i = 0; i < BN; ++i) {
+                if (i < nvalid) { bsum += s[i]; bmx = fmaxf(bmx, s[i]); bcnt += 1.f; }
+                if (((i + 1) % bin_size) == 0) {
+                  const float safe_c = fmaxf(bcnt, 1.f);
+                  const float bound = safe_c * ex2((bmx - m_new) * kLog2e + off);
+                  const float mass = p.fill_alpha * safe_c * ex2((bsum / safe_c - m_new) * kLog2e + off);
+                  const float val = fminf(mass, bound) / safe_c;
+#pragma unroll
+                  for (int q = 0; q < BN; ++q)
+                    if (q >= first && q <= i) s[q] = (q < nvalid) ? val : 0.f;
+                  first = i + 1; bsum = 0.f; bmx = -INFINITY; bcnt = 0.f;
+                }
+              }
+#pragma unroll
+              for (int i = 0; i < BN; ++i) { psum += s[i]; pmax = fmaxf(pmax, s[i]); }
+            }
           }
-          if (i >= nvalid) pv = 0.f;
-          s[i] = pv;
-          psum += pv;
-          pmax = fmaxf(pmax, pv);
+        } else {
+          // masked columns hold -inf, so their exp2 is exactly 0 without a select
+          float ps0 = 0.f, ps1 = 0.f, ps2 = 0.f, ps3 = 0.f;
+#pragma unroll
+          for (int i = 0; i < BN; i += 4) {
+            const float p0 = ex2(fmaf(s[i] - m_new, kLog2e, off));
+            const float p1 = ex2(fmaf(s[i + 1] - m_new, kLog2e, off));
+            const float p2 = ex2(fmaf(s[i + 2] - m_new, kLog2e, off));
+            const float p3 = ex2(fmaf(s[i + 3] - m_new, kLog2e, off));
+            s[i] = p0; s[i + 1] = p1; s[i + 2] = p2; s[i + 3] = p3;
+            ps0 += p0; ps1 += p1; ps2 += p2; ps3 += p3;
+          }
+          psum = (ps0 + ps1) + (ps2 + ps3);
+          // exp2 is monotonic: the largest P of the block is the P of the largest score, and it is
+          // produced by the same instruction sequence, so it is bit-identical to max_i(P_i)
+          pmax = ex2(fmaf(bmax - m_new, kLog2e, off));
         }
         l_i = l_i * alpha + psum;
 
         // ---- P quantisation (attention_triton.py:328-360) -----------------------
-        float inv = 1.f;
-        if (p.p_kind == LBFQ_P_MX) {
-          const int e = pow2_scale_exp(fmaxf(pmax, 1e-4f));
-          c_blk = pow2f(e);
-          inv = pow2f(-e);
-        } else if (p.p_kind == LBFQ_P_DYNAMIC) {
-          c_blk = __fdiv_rn(fmaxf(pmax, 1e-12f), kFp8Max);
-          inv = __fdiv_rn(1.0f, c_blk);
-        }
         uint32_t pk[BN / 4];
+        if (p.p_kind == LBFQ_P_ELEMENTWISE) {
 #pragma unroll
-        for (int i = 0; i < BN / 4; ++i) {
-          float q0 = s[4 * i], q1 = s[4 * i + 1], q2 = s[4 * i + 2], q3 = s[4 * i + 3];
-          if (p.p_kind != LBFQ_P_ELEMENTWISE) {
-            q0 = fminf(q0 * inv, kFp8Max); q1 = fminf(q1 * inv, kFp8Max);
-            q2 = fminf(q2 * inv, kFp8Max); q3 = fminf(q3 * inv, kFp8Max);
+          for (int i = 0; i < BN / 4; ++i)
+            pk[i] = (uint32_t)f32x2_to_e4m3x2(s[4 * i], s[4 * i + 1]) | ((uint32_t)f32x2_to_e4m3x2(s[4 * i + 2], s[4 * i + 3]) << 16);
+        } else {
+          float inv;
+          if (p.p_kind == LBFQ_P_MX) {
+            const int e = pow2_scale_exp(fmaxf(pmax, 1e-4f));
+            c_blk = pow2f(e);
+            inv = pow2f(-e);
+          } else {
+            c_blk = __fdiv_rn(fmaxf(pmax, 1e-12f), kFp8Max);
+            inv = __fdiv_rn(1.0f, c_blk);
           }
-          pk[i] = (uint32_t)f32x2_to_e4m3x2(q0, q1) | ((uint32_t)f32x2_to_e4m3x2(q2, q3) << 16);
+          // the conversion saturates at 448, which is the reference's clamp
+#pragma unroll
+          for (int i = 0; i < BN / 4; ++i)
+            pk[i] = (uint32_t)f32x2_to_e4m3x2(s[4 * i] * inv, s[4 * i + 1] * inv) |
+                    ((uint32_t)f32x2_to_e4m3x2(s[4 * i + 2] * inv, s[4 * i + 3] * inv) << 16);
         }
         tmem_st8(tP, pk);
         if constexpr (BN == 64) tmem_st8(tP + 8, pk + 8);

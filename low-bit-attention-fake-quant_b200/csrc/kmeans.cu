@@ -8,7 +8,7 @@
 // published algorithm, with a deterministic seeding documented below.
 //
 //   seeding   : centroid j of slab g = the token at index
-//               lo_j + mix32(mix32(mix32(seed) ^ g) ^ j) % (hi_j - lo_j),
+//               lo_j + mix32(mix32(mix32(seed) ^ g) ^ j) % (hi_j - lo_j), g = b * total_heads + head,
 //               [lo_j, hi_j) the j-th of k equal strata of the S axis
 //   assignment: argmin_c |c|^2 - 2 x.c   (fp32, lowest index on ties)
 //   update    : mean of the assigned tokens, summed in a fixed order so that a
@@ -33,14 +33,16 @@ __host__ __device__ __forceinline__ uint32_t mix32(uint32_t x) {
 
 template <typename T>
 __global__ void init_centroids_kernel(const T* __restrict__ x, int S, int H, int D, int k, uint32_t seed,
-                                      int bh_offset, float* __restrict__ cent, float* __restrict__ cnorm) {
+                                      int head_offset, int total_heads, float* __restrict__ cent,
+                                      float* __restrict__ cnorm) {
   const int j = blockIdx.x % k;
   const int bh = blockIdx.x / k;
   const int b = bh / H, h = bh % H;
   const int lo = (int)(((int64_t)j * S) / k);
   const int hi = (int)(((int64_t)(j + 1) * S) / k);
   const int span = max(hi - lo, 1);
-  const uint32_t hsh = mix32(mix32(mix32(seed) ^ (uint32_t)(bh_offset + bh)) ^ (uint32_t)j);
+  const uint32_t slab = (uint32_t)(b * total_heads + head_offset + h);     // index in the unsharded problem
+  const uint32_t hsh = mix32(mix32(mix32(seed) ^ slab) ^ (uint32_t)j);
   const int idx = lo + (int)(hsh % (uint32_t)span);
   __shared__ float red[4];
   float v = 0.f;
@@ -225,18 +227,22 @@ extern "C" int64_t lbfq_kmeans_scratch_bytes(int B, int S, int H, int D, int k) 
 }
 
 extern "C" int lbfq_kmeans_labels(const void* x, int dtype, int B, int S, int H, int D, int k, int iters,
-                                  int seed, int bh_offset, int32_t* labels, void* scratch, void* stream) {
+                                  int seed, int head_offset, int total_heads, int32_t* labels, void* scratch,
+                                  void* stream) {
   LBFQ_REQUIRE(B > 0 && S > 0 && H > 0, LBFQ_ERR_ARG, "kmeans: empty input");
   LBFQ_REQUIRE(D == 64 || D == 128, LBFQ_ERR_ARG, "kmeans: D must be 64 or 128; got %d", D);
   LBFQ_REQUIRE(k > 0 && k <= S, LBFQ_ERR_ARG, "n_clusters must be in [1, S]; got %d for S=%d", k, S);
   LBFQ_REQUIRE(k <= 4096, LBFQ_ERR_UNSUPPORTED, "kmeans: k=%d above the supported 4096", k);
+  if (total_heads <= 0) { total_heads = H; head_offset = 0; }
+  LBFQ_REQUIRE(head_offset >= 0 && head_offset + H <= total_heads, LBFQ_ERR_ARG,
+               "kmeans: heads [%d, %d) do not fit in %d total heads", head_offset, head_offset + H, total_heads);
   cudaStream_t st = (cudaStream_t)stream;
   const int BH = B * H;
   KmScratch sc;
   scratch_layout(BH, S, D, k, (uint8_t*)scratch, &sc);
   if (iters < 1) iters = 1;
   LBFQ_DISPATCH_DTYPE(dtype, T,
-      init_centroids_kernel<T><<<BH * k, 128, 0, st>>>((const T*)x, S, H, D, k, (uint32_t)seed, bh_offset, sc.cent, sc.cnorm));
+      init_centroids_kernel<T><<<BH * k, 128, 0, st>>>((const T*)x, S, H, D, k, (uint32_t)seed, head_offset, total_heads, sc.cent, sc.cnorm));
   if (int rc = check_launch("kmeans init")) return rc;
   const int ntile = (S + kTok - 1) / kTok;
   for (int it = 0; it < iters; ++it) {

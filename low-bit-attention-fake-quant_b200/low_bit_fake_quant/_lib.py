@@ -83,7 +83,7 @@ _SIGS = {
     "lbfq_block_mean_sub": (_I, [_P, _I, _I, _I, _I, _I, _I, _P, _P, _P]),
     "lbfq_hadamard": (_I, [_P, _I, C.c_int64, _I, _I, _P, C.c_float, _P, _P]),
     "lbfq_kmeans_scratch_bytes": (C.c_int64, [_I, _I, _I, _I, _I]),
-    "lbfq_kmeans_labels": (_I, [_P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P]),
+    "lbfq_kmeans_labels": (_I, [_P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P]),
     "lbfq_label_order": (_I, [_P, _I, _I, _I, _P, _P, _P]),
     "lbfq_gather_rows": (_I, [_P, _I, _I, _I, _I, _I, _P, _P, _P]),
     "lbfq_qm_corr": (_I, [_P, _P, _I, _I, _I, _I, _I, _I, C.c_float, _P, _I, _P, _P]),

@@ -81,7 +81,7 @@ def _round_up(x: int, m: int) -> int:
 # preprocess: Q k-means -> K smooth -> Q smooth -> V k-means (+K) -> V smooth
 # ---------------------------------------------------------------------------
 
-def _preprocess(q, k, v, cfg: QuantConfig, *, bh_offset: int = 0):
+def _preprocess(q, k, v, cfg: QuantConfig, *, head_offset: int = 0, total_heads: int = 0):
     """The reference's fixed preprocessing order (attention.py:166-239)."""
     q_work, k_work, v_work = q.contiguous(), k.contiguous(), v.contiguous()
     q_km = v_km = None
@@ -89,7 +89,7 @@ def _preprocess(q, k, v, cfg: QuantConfig, *, bh_offset: int = 0):
 
     if cfg.q_kmeans_k is not None:
         q_km = kmeans_reorder_tokens(q_work, n_clusters=cfg.q_kmeans_k, max_iters=cfg.q_kmeans_iters,
-                                     seed=cfg.q_kmeans_seed, bh_offset=bh_offset)
+                                     seed=cfg.q_kmeans_seed, head_offset=head_offset, total_heads=total_heads)
         q_work = q_km.tensor_reordered
 
     if cfg.smoothing in ("k_only", "full"):
@@ -101,7 +101,7 @@ def _preprocess(q, k, v, cfg: QuantConfig, *, bh_offset: int = 0):
 
     if cfg.v_kmeans_k is not None:
         v_km = kmeans_reorder_tokens(v_work, n_clusters=cfg.v_kmeans_k, max_iters=cfg.v_kmeans_iters,
-                                     seed=cfg.v_kmeans_seed, bh_offset=bh_offset)
+                                     seed=cfg.v_kmeans_seed, head_offset=head_offset, total_heads=total_heads)
         v_work = v_km.tensor_reordered
         k_work = apply_kv_permutation(k_work, v_km.order)      # keep every (K[n], V[n]) pair together
 
@@ -113,10 +113,11 @@ def _preprocess(q, k, v, cfg: QuantConfig, *, bh_offset: int = 0):
     return q_work, k_work, v_work, qm, v_alpha, q_km, v_km
 
 
-def _rotated(q_work, k_work, cfg: QuantConfig):
+def _rotated(q_work, k_work, cfg: QuantConfig, head_offset: int = 0, total_heads: int = 0):
     if not cfg.qk_hadamard:
         return q_work, k_work
-    return apply_qk_hadamard(q_work, k_work, random_sign=cfg.qk_hadamard_random_sign, seed=cfg.qk_hadamard_seed)
+    return apply_qk_hadamard(q_work, k_work, random_sign=cfg.qk_hadamard_random_sign, seed=cfg.qk_hadamard_seed,
+                             head_offset=head_offset, total_heads=total_heads if total_heads > 0 else None)
 
 
 # ---------------------------------------------------------------------------
@@ -146,11 +147,12 @@ def _quant_dequant_v(t, cfg: QuantConfig, dtype):
     raise ValueError(f"unsupported v_quant: {cfg.v_quant!r}")
 
 
-def _fake_quant_attention_sdpa(q_work, k_work, v_work, qm, v_alpha, cfg: QuantConfig, sm_scale, sdpa_dtype):
+def _fake_quant_attention_sdpa(q_work, k_work, v_work, qm, v_alpha, cfg: QuantConfig, sm_scale, sdpa_dtype,
+                               head_offset: int = 0, total_heads: int = 0):
     """P stays unquantised (upper-bound path). With Q smoothing the score is
     ``Q_deq.K_deq^T + qm.K_smooth^T`` with the second term on the un-quantised K."""
     b, s, h, d = q_work.shape
-    q_in, k_in = _rotated(q_work, k_work, cfg)
+    q_in, k_in = _rotated(q_work, k_work, cfg, head_offset, total_heads)
     q_deq = _quant_dequant_qk(q_in, cfg, sdpa_dtype)
     k_deq = _quant_dequant_qk(k_in, cfg, sdpa_dtype)
     v_deq = _quant_dequant_v(v_work, cfg, sdpa_dtype)
@@ -187,12 +189,12 @@ def _fake_quant_attention_sdpa(q_work, k_work, v_work, qm, v_alpha, cfg: QuantCo
 
 def _fake_quant_attention_p_requant(q_work, k_work, v_work, qm, v_alpha, q_kmeans, cfg: QuantConfig,
                                     sm_scale, out_dtype, *, return_stats: bool = False,
-                                    out_fp32_exact: bool = False):
+                                    out_fp32_exact: bool = False, head_offset: int = 0, total_heads: int = 0):
     """Quantise straight into the kernel's layouts and launch it. Returns the
     output in NHD, rows already back in the original Q order."""
     b, s, h, d = q_work.shape
     s_pad = _round_up(s, 128)
-    q_in, k_in = _rotated(q_work, k_work, cfg)
+    q_in, k_in = _rotated(q_work, k_work, cfg, head_offset, total_heads)
 
     if cfg.qk_quant == "fp8_block":
         q_codes, q_scale = fp8_block_quant(q_in, block_s=cfg.fp8_block_size, _layout=L.LAYOUT_BHSD, _s_pad=s_pad)
@@ -279,13 +281,17 @@ def fake_quant_attention(
     return_artifacts: bool = False,
     preprocess_cache: Optional[PreprocessCache] = None,
     _debug_fp32: bool = False,
+    _head_offset: int = 0,
+    _total_heads: int = 0,
 ):
     """Fake-quant attention with FP8/MXFP8 Q/K/V (and optional P requant).
 
     ``q, k, v``: (B, S, H, D), D in {64, 128}, BF16/FP16/FP32 on CUDA.
     Returns the (B, S, H, D) output in ``q``'s dtype (and the artifacts).
     ``_debug_fp32`` (testing aid) returns the kernel's FP32 result without the
-    BF16 rounding of the store.
+    BF16 rounding of the store. ``_head_offset`` / ``_total_heads`` tell a heads
+    shard where it sits in the unsharded problem (Hadamard signs and k-means
+    seeding are indexed by global head), so that sharded == unsharded.
     """
     if cfg is None:
         cfg = QuantConfig()
@@ -314,14 +320,17 @@ def fake_quant_attention(
             raise ValueError("preprocess_cache does not match cfg's smoothing/kmeans/v_smooth settings")
         q_work, k_work, v_work, qm, v_alpha, q_km = pc.q_work, pc.k_work, pc.v_work, pc.qm, pc.v_alpha, pc.q_kmeans
     else:
-        q_work, k_work, v_work, qm, v_alpha, q_km, _ = _preprocess(q, k, v, cfg)
+        q_work, k_work, v_work, qm, v_alpha, q_km, _ = _preprocess(q, k, v, cfg, head_offset=_head_offset,
+                                                                   total_heads=_total_heads)
 
     if cfg.p_requant:
         # the kernel scatters its rows through q_km.order: no separate inverse gather
         o = _fake_quant_attention_p_requant(q_work, k_work, v_work, qm, v_alpha, q_km, cfg, sm_scale, out_dtype,
-                                            out_fp32_exact=_debug_fp32)
+                                            out_fp32_exact=_debug_fp32, head_offset=_head_offset,
+                                            total_heads=_total_heads)
     else:
-        o = _fake_quant_attention_sdpa(q_work, k_work, v_work, qm, v_alpha, cfg, sm_scale, sdpa_dtype)
+        o = _fake_quant_attention_sdpa(q_work, k_work, v_work, qm, v_alpha, cfg, sm_scale, sdpa_dtype,
+                                       _head_offset, _total_heads)
         o = o.float() if _debug_fp32 else o.to(out_dtype)
         if q_km is not None:
             o = _gather(o, q_km.inverse_order)

@@ -34,8 +34,9 @@ class KMeansReorderResult:
 
 
 def kmeans_labels(t: torch.Tensor, *, n_clusters: int, max_iters: int = 10, seed: int = 0,
-                  bh_offset: int = 0) -> torch.Tensor:
-    """int32 labels (B*H, S) of the last Lloyd assignment."""
+                  head_offset: int = 0, total_heads: int = 0) -> torch.Tensor:
+    """int32 labels (B*H, S) of the last Lloyd assignment. ``head_offset`` / ``total_heads``
+    place a heads shard inside the unsharded problem (they only enter the seeding hash)."""
     b, s, h, d = t.shape
     t = t.contiguous()
     labels = torch.empty((b * h, s), dtype=torch.int32, device=t.device)
@@ -43,7 +44,7 @@ def kmeans_labels(t: torch.Tensor, *, n_clusters: int, max_iters: int = 10, seed
         nbytes = L.lib().lbfq_kmeans_scratch_bytes(b, s, h, d, n_clusters)
         scratch = torch.empty((nbytes,), dtype=torch.uint8, device=t.device)
         L.check(L.lib().lbfq_kmeans_labels(t.data_ptr(), L.dtype_code(t.dtype), b, s, h, d, n_clusters,
-                                           max_iters, seed, bh_offset, labels.data_ptr(), scratch.data_ptr(),
+                                           max_iters, seed, head_offset, total_heads, labels.data_ptr(), scratch.data_ptr(),
                                            L.stream_ptr(t.device)))
     return labels
 
@@ -79,7 +80,8 @@ def kmeans_reorder_tokens(
     seed: int = 0,
     chunk_tokens: int = 4096,  # kept for signature compatibility; unused
     labels: torch.Tensor | None = None,
-    bh_offset: int = 0,
+    head_offset: int = 0,
+    total_heads: int = 0,
 ) -> KMeansReorderResult:
     """Cluster tokens of ``t`` (B, S, H, D) per (B, H) and reorder them by cluster.
 
@@ -93,7 +95,8 @@ def kmeans_reorder_tokens(
     if n_clusters <= 0 or n_clusters > s:
         raise ValueError(f"n_clusters must be in [1, S]; got {n_clusters} for S={s}")
     if labels is None:
-        labels = kmeans_labels(t, n_clusters=n_clusters, max_iters=max_iters, seed=seed, bh_offset=bh_offset)
+        labels = kmeans_labels(t, n_clusters=n_clusters, max_iters=max_iters, seed=seed, head_offset=head_offset,
+                               total_heads=total_heads)
     order, inverse = order_from_labels(labels, n_clusters)
     return KMeansReorderResult(
         tensor_reordered=_gather(t, order),

