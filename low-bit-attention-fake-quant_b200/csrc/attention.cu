@@ -19,9 +19,12 @@
 // line by line; key blocks are walked in order with the reference's BLOCK_N so
 // that every rounding decision of P sees the same running max.
 //
-// CTA = 256 query rows of one (b, h): two softmax warpgroups (one 128-row tile
-// each, thread == row == TMEM lane), one TMA producer warp, one MMA-issuing warp
-// per tile. K / V^T arrive in 128-key stages shared by both tiles. The extra 16
+// CTA = 256 query rows of one (b, h) in two 128-row tiles. Each row is served by
+// TWO threads (same TMEM lane, warps w and w+4 of the tile): each owns half of the
+// key block's columns for the softmax and half of D for the accumulator, and
+// recomputes the row max over the other half instead of synchronising with its
+// partner -- 16 softmax warps per SM hide the TMEM / MUFU latencies that 8 could
+// not. One TMA producer warp and one MMA-issuing warp per tile complete the CTA. K / V^T arrive in 128-key stages shared by both tiles. The extra 16
 // rows of ones appended to every V^T stage make column D of the PV accumulator
 // equal to rowsum(Pc), which the V-smoothing correction needs, for free.
 // Every mbarrier wait is bounded; on expiry the kernel raises `*status`, all
@@ -39,7 +42,8 @@ constexpr int kTileM = 128;              // rows per softmax warpgroup
 constexpr int kCtaM = 2 * kTileM;        // rows per CTA
 constexpr int kChunk = 128;              // keys per TMA stage
 constexpr int kStages = 3;
-constexpr int kThreads = 384;            // 2 softmax warpgroups + 1 warpgroup of service warps
+constexpr int kSoftmaxWarps = 16;        // 2 tiles x 2 halves x 4 lane quarters
+constexpr int kThreads = 640;            // 16 softmax warps + 1 warpgroup of service warps
 constexpr int kOnesRows = 16;
 constexpr unsigned long long kWaitCycles = 1000000000ull;   // ~0.5 s: far above any legitimate wait
 
@@ -127,6 +131,21 @@ __device__ __forceinline__ void mma_f8_ts(uint32_t d_tmem, uint32_t a_tmem, uint
         "=r"(r[29]), "=r"(r[30]), "=r"(r[31])                                                            \
       : "r"(addr) : "memory")
 
+#define LBFQ_TMEM_LD16(r, addr)                                                                            \
+  asm volatile(                                                                                           \
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "                                                           \
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"                    \
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),   \
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),         \
+        "=r"(r[15])                                                                                       \
+      : "r"(addr) : "memory")
+
+template <int N>
+__device__ __forceinline__ void tmem_ld(uint32_t (&r)[N], uint32_t addr) {
+  static_assert(N == 16 || N == 32, "chunk of 16 or 32 columns");
+  if constexpr (N == 32) { LBFQ_TMEM_LD32(r, addr); } else { LBFQ_TMEM_LD16(r, addr); }
+}
+
 __device__ __forceinline__ uint32_t tmem_ld1(uint32_t addr) {
   uint32_t v;
   asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(v) : "r"(addr) : "memory");
@@ -136,6 +155,11 @@ __device__ __forceinline__ void tmem_st8(uint32_t addr, const uint32_t* r) {
   asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
                ::"r"(addr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
                : "memory");
+}
+
+__device__ __forceinline__ void tmem_st4(uint32_t addr, const uint32_t* r) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};"
+               ::"r"(addr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]) : "memory");
 }
 
 __device__ __forceinline__ float ex2(float x) {
@@ -203,9 +227,10 @@ struct Smem {
   static constexpr int offK = offQ + 2 * kQ;
   static constexpr int offV = offK + kStages * kK;
   static constexpr int offBar = offV + kStages * kV;
-  static constexpr int kNumBar = 2 + 4 * kStages + 8;
+  static constexpr int kNumBar = 2 + 4 * kStages + 10;
   static constexpr int offMisc = offBar + kNumBar * 8;
-  static constexpr int total = offMisc + 64;
+  static constexpr int offL = offMisc + 64;                   // partial row sums [tile][half][row]
+  static constexpr int total = offL + 2 * 2 * kTileM * 4;
 };
 
 // ---------------------------------------------------------------------------
@@ -220,6 +245,8 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
   constexpr int PV_N = D + kOnesRows;              // PV accumulator columns
   constexpr int TCOLS = 256;                       // TMEM columns per tile
   constexpr int COL_S = 0, COL_P = 64, COL_O = 96;
+  constexpr int HB = BN / 2;                       // key columns owned by one thread of a row pair
+  constexpr int HD = D / 2;                        // output columns owned by one thread of a row pair
   static_assert(BN == 32 || BN == 64, "block_n of 32 or 64");
   static_assert(COL_O + PV_N <= TCOLS, "TMEM budget");
 
@@ -237,8 +264,10 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
   auto BAR_SFREE = [&](int t) { return bar0 + 8u * (2 + 4 * kStages + 2 + t); };
   auto BAR_PRDY = [&](int t) { return bar0 + 8u * (2 + 4 * kStages + 4 + t); };
   auto BAR_PVFULL = [&](int t) { return bar0 + 8u * (2 + 4 * kStages + 6 + t); };
+  auto BAR_LRDY = [&](int t) { return bar0 + 8u * (2 + 4 * kStages + 8 + t); };
   volatile int* misc = (volatile int*)(smem + SM::offMisc);   // [0] tmem base, [1] abort, [2..3] elide flags
   volatile int* abort_flag = misc + 1;
+  volatile float* lpart = (volatile float*)(smem + SM::offL);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int bh = blockIdx.y;
@@ -246,6 +275,7 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
   const int m0 = blockIdx.x * kCtaM;
   const int nblk = (p.N + BN - 1) / BN;
   const int nchunk = (p.N + kChunk - 1) / kChunk;
+  constexpr int kTmaWarp = kSoftmaxWarps, kMmaWarp0 = kSoftmaxWarps + 1;
 
   // ---- setup ----------------------------------------------------------------
   // A CTA scheduled after some other CTA has given up a wait retires at once.
@@ -256,9 +286,10 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
     for (int t = 0; t < 2; ++t) {
       mbar_init(BAR_QFULL(t), 1);
       mbar_init(BAR_SFULL(t), 1);
-      mbar_init(BAR_SFREE(t), kTileM);
-      mbar_init(BAR_PRDY(t), kTileM);
+      mbar_init(BAR_SFREE(t), 2 * kTileM);
+      mbar_init(BAR_PRDY(t), 2 * kTileM);
       mbar_init(BAR_PVFULL(t), 1);
+      mbar_init(BAR_LRDY(t), 2 * kTileM);
     }
     for (int s = 0; s < kStages; ++s) {
       mbar_init(BAR_KFULL(s), 1);
@@ -276,7 +307,7 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         make_uint4(0x38383838u, 0x38383838u, 0x38383838u, 0x38383838u);
   }
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-  if (warp == 8) {
+  if (warp == kTmaWarp) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(sbase + SM::offMisc) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -285,10 +316,11 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
   tc_fence_after();
   const uint32_t tmem_base = (uint32_t)misc[0];
 
-  if (warp < 8) {
-    // =========================== softmax warpgroups ===========================
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
-    const int t = warp >> 2;                                   // tile
+  if (warp < kSoftmaxWarps) {
+    // =========================== softmax warps ================================
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 120;");
+    const int t = warp >> 3;                                   // tile
+    const int hf = (warp >> 2) & 1;                            // which half of the columns / of D this thread owns
     const int row_in_tile = (warp & 3) * 32 + lane;
     const int row = m0 + t * kTileM + row_in_tile;             // query row within (b, h)
     const bool row_ok = row < p.M;
@@ -297,6 +329,8 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
     const uint32_t tS = tmem_base + lane_base + t * TCOLS + COL_S;
     const uint32_t tP = tmem_base + lane_base + t * TCOLS + COL_P;
     const uint32_t tO = tmem_base + lane_base + t * TCOLS + COL_O;
+    const int own0 = hf * HB, oth0 = (1 - hf) * HB;            // first column of the own / other half
+    const int d0 = hf * HD;                                    // first output column owned
 
     const float sq = p.q_scale ? p.q_scale[((size_t)b * (p.M / p.qk_block) + rowc / p.qk_block) * p.H + h] : 1.f;
     const float* corr_row = nullptr;
@@ -308,27 +342,31 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
     float est = 0.f;
     if (p.rowmax_est) { est = p.rowmax_est[(size_t)bh * p.M + rowc]; m_i = est; }
     else if (p.rowmax_init) { m_i = p.rowmax_init[(size_t)bh * p.M + rowc]; }
-    float l_i = 0.f, max_seen = -INFINITY;
+    float l_i = 0.f, max_seen = -INFINITY;                     // l_i: partial row sum over the own columns
+    // "the whole row has no probability mass yet" (the reference's l_i == 0 test of the estimated
+    // row-max mode), tracked from quantities both threads of a row share: the block's largest P
+    // is positive exactly when the block added mass, and mass is lost again only when alpha is 0
+    bool l_zero = true;
     float n_skip = 0.f, n_total = 0.f;
     float a_prev = 1.f, c_prev = 1.f;
     bool elided_prev = false;
     int blk_prev = 0;
-    float acc[D];
+    float acc[HD];
 #pragma unroll
-    for (int i = 0; i < D; ++i) acc[i] = 0.f;
+    for (int i = 0; i < HD; ++i) acc[i] = 0.f;
 
-    // fold PV of block `jb` (scale c, rescale a) into the accumulator. The mode
-    // switches are warp-uniform and hoisted out of the unrolled loops so that no
-    // lane issues predicated-off work.
+    // fold PV of block `jb` (scale c, rescale a) into the own half of the accumulator. The mode
+    // switches are warp-uniform and hoisted out of the unrolled loops so that no lane issues
+    // predicated-off work.
     auto accumulate = [&](int jb, float a, float c) {
       tc_fence_after();
       const bool rescale = __any_sync(0xffffffffu, a != 1.f);
       const bool scaled = __any_sync(0xffffffffu, c != 1.f);
       if (!p.v_alpha && p.v_kind != LBFQ_V_MX) {
 #pragma unroll
-        for (int c0 = 0; c0 < D; c0 += 32) {
+        for (int c0 = 0; c0 < HD; c0 += 32) {
           uint32_t r[32];
-          LBFQ_TMEM_LD32(r, tO + c0);
+          LBFQ_TMEM_LD32(r, tO + d0 + c0);
           tc_wait_ld();
           if (rescale) {
 #pragma unroll
@@ -348,14 +386,14 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
       const float* vs = nullptr;
       if (p.v_alpha) {
         rs = __uint_as_float(tmem_ld1(tO + D));
-        av = p.v_alpha + (((size_t)b * (p.N / p.v_smooth_block) + (jb * BN) / p.v_smooth_block) * p.H + h) * D;
+        av = p.v_alpha + (((size_t)b * (p.N / p.v_smooth_block) + (jb * BN) / p.v_smooth_block) * p.H + h) * D + d0;
       }
       if (p.v_kind == LBFQ_V_MX)
-        vs = p.v_scale + (((size_t)b * (p.N / p.v_block) + (jb * BN) / p.v_block) * p.H + h) * D;
+        vs = p.v_scale + (((size_t)b * (p.N / p.v_block) + (jb * BN) / p.v_block) * p.H + h) * D + d0;
 #pragma unroll
-      for (int c0 = 0; c0 < D; c0 += 32) {
+      for (int c0 = 0; c0 < HD; c0 += 32) {
         uint32_t r[32];
-        LBFQ_TMEM_LD32(r, tO + c0);
+        LBFQ_TMEM_LD32(r, tO + d0 + c0);
         tc_wait_ld();
         if (vs) {
           const float4* v4 = reinterpret_cast<const float4*>(vs + c0);
@@ -389,6 +427,37 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
       }
     };
 
+    // scaled scores of HB columns starting at column `col0` of the block, and their max
+    auto load_scores = [&](float (&dst)[HB], uint32_t taddr, int col0, int n0, int nvalid, float f) -> float {
+      uint32_t r[HB];
+      tmem_ld<HB>(r, taddr);
+      tc_wait_ld();
+      if (corr_row) {
+        const float4* c4 = reinterpret_cast<const float4*>(corr_row + n0 + col0);
+#pragma unroll
+        for (int i = 0; i < HB / 4; ++i) {
+          const float4 cv = __ldg(c4 + i);
+          dst[4 * i + 0] = __uint_as_float(r[4 * i + 0]) * f + cv.x;
+          dst[4 * i + 1] = __uint_as_float(r[4 * i + 1]) * f + cv.y;
+          dst[4 * i + 2] = __uint_as_float(r[4 * i + 2]) * f + cv.z;
+          dst[4 * i + 3] = __uint_as_float(r[4 * i + 3]) * f + cv.w;
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < HB; ++i) dst[i] = __uint_as_float(r[i]) * f;
+      }
+      if (nvalid < BN) {                    // ragged tail: only the last block of a sequence
+#pragma unroll
+        for (int i = 0; i < HB; ++i) if (col0 + i >= nvalid) dst[i] = -INFINITY;
+      }
+      float b0 = dst[0], b1 = dst[1], b2 = dst[2], b3 = dst[3];
+#pragma unroll
+      for (int i = 4; i < HB; i += 4) {
+        b0 = fmaxf(b0, dst[i]); b1 = fmaxf(b1, dst[i + 1]); b2 = fmaxf(b2, dst[i + 2]); b3 = fmaxf(b3, dst[i + 3]);
+      }
+      return fmaxf(fmaxf(b0, b1), fmaxf(b2, b3));
+    };
+
     bool alive = true;
     for (int it = 0; it < nblk && alive; ++it) {
       // ---- (a) fold the previous block's PV -------------------------------------
@@ -399,25 +468,6 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
       // ---- (b) S -> P -------------------------------------------------------------
       if (!mbar_wait(BAR_SFULL(t), it & 1, abort_flag, p.status, 12)) { alive = false; break; }
       tc_fence_after();
-      float s[BN];
-      {
-        uint32_t r[32];
-        LBFQ_TMEM_LD32(r, tS);
-        if constexpr (BN == 64) {
-          uint32_t r2[32];
-          LBFQ_TMEM_LD32(r2, tS + 32);
-          tc_wait_ld();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) { s[i] = __uint_as_float(r[i]); s[32 + i] = __uint_as_float(r2[i]); }
-        } else {
-          tc_wait_ld();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) s[i] = __uint_as_float(r[i]);
-        }
-      }
-      tc_fence_before();
-      mbar_arrive(BAR_SFREE(t));
-
       const int n0 = it * BN;
       const int nvalid = min(BN, p.N - n0);
       float f = p.sm_scale;
@@ -425,30 +475,22 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         const float sk = p.k_scale[((size_t)b * (p.N / p.qk_block) + n0 / p.qk_block) * p.H + h];
         f = (sq * sk) * p.sm_scale;
       }
-      if (corr_row) {
-        const float4* c4 = reinterpret_cast<const float4*>(corr_row + n0);
-#pragma unroll
-        for (int i = 0; i < BN / 4; ++i) {
-          const float4 cv = __ldg(c4 + i);
-          s[4 * i + 0] = s[4 * i + 0] * f + cv.x;
-          s[4 * i + 1] = s[4 * i + 1] * f + cv.y;
-          s[4 * i + 2] = s[4 * i + 2] * f + cv.z;
-          s[4 * i + 3] = s[4 * i + 3] * f + cv.w;
-        }
+      float s[HB];                          // own columns
+      float o[BLASST ? HB : 1];             // the partner's columns (kept only for the BLASST fills)
+      float bmax;
+      if constexpr (BLASST) {
+        const float bo = load_scores(o, tS + oth0, oth0, n0, nvalid, f);
+        bmax = fmaxf(bo, load_scores(s, tS + own0, own0, n0, nvalid, f));
       } else {
-#pragma unroll
-        for (int i = 0; i < BN; ++i) s[i] *= f;
+        float bo;
+        {
+          float tmp[HB];
+          bo = load_scores(tmp, tS + oth0, oth0, n0, nvalid, f);
+        }
+        bmax = fmaxf(bo, load_scores(s, tS + own0, own0, n0, nvalid, f));
       }
-      if (nvalid < BN) {                    // ragged tail: only the last block of a sequence
-#pragma unroll
-        for (int i = 0; i < BN; ++i) if (i >= nvalid) s[i] = -INFINITY;
-      }
-      float bm0 = s[0], bm1 = s[1], bm2 = s[2], bm3 = s[3];
-#pragma unroll
-      for (int i = 4; i < BN; i += 4) {
-        bm0 = fmaxf(bm0, s[i]); bm1 = fmaxf(bm1, s[i + 1]); bm2 = fmaxf(bm2, s[i + 2]); bm3 = fmaxf(bm3, s[i + 3]);
-      }
-      const float bmax = fmaxf(fmaxf(bm0, bm1), fmaxf(bm2, bm3));
+      tc_fence_before();
+      mbar_arrive(BAR_SFREE(t));
 
       // ---- running max / rescale factor (attention_triton.py:164-217) ----------
       float m_new, alpha;
@@ -465,9 +507,9 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         const float up = 16.0f / kLog2e, down = 32.0f / kLog2e;
         const bool under = (bmax - m_i) > up;
         const bool over = (m_i - seen) > down;
-        const float down_m = (l_i == 0.f) ? seen : fmaxf(seen + down, m_i - 80.0f);
+        const float down_m = l_zero ? seen : fmaxf(seen + down, m_i - 80.0f);
         m_new = (under || over) ? (under ? bmax : down_m) : m_i;
-        alpha = (under || over) ? ((l_i == 0.f) ? 0.f : ex2((m_i - m_new) * kLog2e)) : 1.f;
+        alpha = (under || over) ? (l_zero ? 0.f : ex2((m_i - m_new) * kLog2e)) : 1.f;
         max_seen = seen;
       } else if (p.rm_mode == 1) {
         m_new = est;
@@ -484,7 +526,7 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
           uint32_t all;
           asm volatile(
               "{\n\t.reg .pred pi, po;\n\tsetp.ne.b32 pi, %1, 0;\n\t"
-              "barrier.cta.red.and.pred po, %2, 128, pi;\n\tselp.u32 %0, 1, 0, po;\n\t}"
+              "barrier.cta.red.and.pred po, %2, 256, pi;\n\tselp.u32 %0, 1, 0, po;\n\t}"
               : "=r"(all) : "r"((uint32_t)(skip || !row_ok)), "r"(1 + t) : "memory");
           elide = all != 0;
         }
@@ -498,17 +540,22 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         const float off = p.p_kind == LBFQ_P_ELEMENTWISE ? p.p_off : 0.f;
         float psum, pmax;
         if (BLASST && skip) {
-          // a skipped row contributes only its softmax-free fill (zero for the "zero" fill)
+          // a skipped row contributes only its softmax-free fill (zero for the "zero" fill);
+          // block statistics run over both halves, always in column order, so that the two
+          // threads of a row compute identical values
           psum = 0.f; pmax = 0.f;
           if (p.fill_kind == LBFQ_FILL_ZERO) {
 #pragma unroll
-            for (int i = 0; i < BN; ++i) s[i] = 0.f;
+            for (int i = 0; i < HB; ++i) s[i] = 0.f;
           } else {
             const float safe_n = (float)max(nvalid, 1);
-            float sum = 0.f;
+            float sum_own = 0.f, sum_oth = 0.f;
 #pragma unroll
-            for (int i = 0; i < BN; ++i) sum += (i < nvalid) ? s[i] : 0.f;
-            const float mean = sum / safe_n;
+            for (int i = 0; i < HB; ++i) {
+              sum_own += (own0 + i < nvalid) ? s[i] : 0.f;
+              sum_oth += (oth0 + i < nvalid) ? o[i] : 0.f;
+            }
+            const float mean = (hf ? (sum_oth + sum_own) : (sum_own + sum_oth)) / safe_n;
             const float max_bound = safe_n * ex2((bmax - m_new) * kLog2e + off);
             float fill_p = 0.f;
             if (p.fill_kind == LBFQ_FILL_MAX) {
@@ -516,17 +563,24 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
             } else if (p.fill_kind == LBFQ_FILL_MEAN) {
               fill_p = fminf(p.fill_alpha * safe_n * ex2((mean - m_new) * kLog2e + off), max_bound) / safe_n;
             } else if (p.fill_kind == LBFQ_FILL_LOGN) {
-              float v2 = 0.f;
+              float v_own = 0.f, v_oth = 0.f;
 #pragma unroll
-              for (int i = 0; i < BN; ++i) { const float cd = (i < nvalid) ? s[i] - mean : 0.f; v2 += cd * cd; }
-              const float var = v2 / safe_n;
+              for (int i = 0; i < HB; ++i) {
+                const float ca = (own0 + i < nvalid) ? s[i] - mean : 0.f;
+                const float cb = (oth0 + i < nvalid) ? o[i] - mean : 0.f;
+                v_own += ca * ca; v_oth += cb * cb;
+              }
+              const float var = (hf ? (v_oth + v_own) : (v_own + v_oth)) / safe_n;
               fill_p = fminf(safe_n * ex2((mean + 0.5f * var - m_new) * kLog2e + off), max_bound) / safe_n;
             } else if (p.fill_kind == LBFQ_FILL_SAMPLE8) {
               const int stride = BN >= 8 ? BN / 8 : 1;
-              float ssum = 0.f, cnt = 0.f;
+              float s_own = 0.f, s_oth = 0.f, cnt = 0.f;
 #pragma unroll
-              for (int i = 0; i < BN; i += stride)
-                if (i < nvalid) { ssum += ex2((s[i] - m_new) * kLog2e + off); cnt += 1.f; }
+              for (int i = 0; i < HB; i += stride) {       // HB is a multiple of the stride
+                if (own0 + i < nvalid) { s_own += ex2((s[i] - m_new) * kLog2e + off); cnt += 1.f; }
+                if (oth0 + i < nvalid) { s_oth += ex2((o[i] - m_new) * kLog2e + off); cnt += 1.f; }
+              }
+              const float ssum = hf ? (s_oth + s_own) : (s_own + s_oth);
               fill_p = fminf(p.fill_alpha * safe_n * ssum / fmaxf(cnt, 1.f), max_bound) / safe_n;
             } else if (p.fill_kind == LBFQ_FILL_THR) {
               const float off_scale = p.p_kind == LBFQ_P_ELEMENTWISE ? exp2f(p.p_off) : 1.f;
@@ -534,38 +588,58 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
             }
             if (p.fill_kind != LBFQ_FILL_UTA) {
 #pragma unroll
-              for (int i = 0; i < BN; ++i) s[i] = (i < nvalid) ? fill_p : 0.f;
-              psum = fill_p * 0.f;
-#pragma unroll
-              for (int i = 0; i < BN; ++i) psum += s[i];
+              for (int i = 0; i < HB; ++i) { s[i] = (own0 + i < nvalid) ? fill_p : 0.f; psum += s[i]; }
               pmax = fill_p;
-            } else {                                           // UTA: one value per bin of BN / bins keys
+            } else if (p.uta_bins == 1) {                      // one bin = the whole block
+              const float cnt = safe_n;
+              const float bound = cnt * ex2((bmax - m_new) * kLog2e + off);
+              const float mass = p.fill_alpha * cnt * ex2((mean - m_new) * kLog2e + off);
+              const float val = fminf(mass, bound) / cnt;
+#pragma unroll
+              for (int i = 0; i < HB; ++i) { s[i] = (own0 + i < nvalid) ? val : 0.f; psum += s[i]; }
+              pmax = val;
+            } else {                                           // UTA: bins of BN / bins keys, each inside one half
               const int bin_size = BN / p.uta_bins;
+              // partner's bins only matter for the block-wide maximum of P
+              {
+                float bsum = 0.f, bmx = -INFINITY, bcnt = 0.f;
+#pragma unroll
+                for (int i = 0; i < HB; ++i) {
+                  if (oth0 + i < nvalid) { bsum += o[i]; bmx = fmaxf(bmx, o[i]); bcnt += 1.f; }
+                  if (((i + 1) % bin_size) == 0) {
+                    const float safe_c = fmaxf(bcnt, 1.f);
+                    const float bound = safe_c * ex2((bmx - m_new) * kLog2e + off);
+                    const float mass = p.fill_alpha * safe_c * ex2((bsum / safe_c - m_new) * kLog2e + off);
+                    if (bcnt > 0.f) pmax = fmaxf(pmax, fminf(mass, bound) / safe_c);
+                    bsum = 0.f; bmx = -INFINITY; bcnt = 0.f;
+                  }
+                }
+              }
               float bsum = 0.f, bmx = -INFINITY, bcnt = 0.f;
               int first = 0;
 #pragma unroll
-              for (int i = 0; i < BN; ++i) {
-                if (i < nvalid) { bsum += s[i]; bmx = fmaxf(bmx, s[i]); bcnt += 1.f; }
+              for (int i = 0; i < HB; ++i) {
+                if (own0 + i < nvalid) { bsum += s[i]; bmx = fmaxf(bmx, s[i]); bcnt += 1.f; }
                 if (((i + 1) % bin_size) == 0) {
                   const float safe_c = fmaxf(bcnt, 1.f);
                   const float bound = safe_c * ex2((bmx - m_new) * kLog2e + off);
                   const float mass = p.fill_alpha * safe_c * ex2((bsum / safe_c - m_new) * kLog2e + off);
                   const float val = fminf(mass, bound) / safe_c;
 #pragma unroll
-                  for (int q = 0; q < BN; ++q)
-                    if (q >= first && q <= i) s[q] = (q < nvalid) ? val : 0.f;
+                  for (int q = 0; q < HB; ++q)
+                    if (q >= first && q <= i) s[q] = (own0 + q < nvalid) ? val : 0.f;
                   first = i + 1; bsum = 0.f; bmx = -INFINITY; bcnt = 0.f;
                 }
               }
 #pragma unroll
-              for (int i = 0; i < BN; ++i) { psum += s[i]; pmax = fmaxf(pmax, s[i]); }
+              for (int i = 0; i < HB; ++i) { psum += s[i]; pmax = fmaxf(pmax, s[i]); }
             }
           }
         } else {
           // masked columns hold -inf, so their exp2 is exactly 0 without a select
           float ps0 = 0.f, ps1 = 0.f, ps2 = 0.f, ps3 = 0.f;
 #pragma unroll
-          for (int i = 0; i < BN; i += 4) {
+          for (int i = 0; i < HB; i += 4) {
             const float p0 = ex2(fmaf(s[i] - m_new, kLog2e, off));
             const float p1 = ex2(fmaf(s[i + 1] - m_new, kLog2e, off));
             const float p2 = ex2(fmaf(s[i + 2] - m_new, kLog2e, off));
@@ -579,12 +653,13 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
           pmax = ex2(fmaf(bmax - m_new, kLog2e, off));
         }
         l_i = l_i * alpha + psum;
+        l_zero = (l_zero || alpha == 0.f) && (pmax == 0.f);
 
         // ---- P quantisation (attention_triton.py:328-360) -----------------------
-        uint32_t pk[BN / 4];
+        uint32_t pk[HB / 4];
         if (p.p_kind == LBFQ_P_ELEMENTWISE) {
 #pragma unroll
-          for (int i = 0; i < BN / 4; ++i)
+          for (int i = 0; i < HB / 4; ++i)
             pk[i] = (uint32_t)f32x2_to_e4m3x2(s[4 * i], s[4 * i + 1]) | ((uint32_t)f32x2_to_e4m3x2(s[4 * i + 2], s[4 * i + 3]) << 16);
         } else {
           float inv;
@@ -598,17 +673,18 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
           }
           // the conversion saturates at 448, which is the reference's clamp
 #pragma unroll
-          for (int i = 0; i < BN / 4; ++i)
+          for (int i = 0; i < HB / 4; ++i)
             pk[i] = (uint32_t)f32x2_to_e4m3x2(s[4 * i] * inv, s[4 * i + 1] * inv) |
                     ((uint32_t)f32x2_to_e4m3x2(s[4 * i + 2] * inv, s[4 * i + 3] * inv) << 16);
         }
-        tmem_st8(tP, pk);
-        if constexpr (BN == 64) tmem_st8(tP + 8, pk + 8);
+        if constexpr (HB == 32) tmem_st8(tP + own0 / 4, pk); else tmem_st4(tP + own0 / 4, pk);
         tc_wait_st();
+      } else {
+        l_i = l_i * alpha;
       }
       if (p.v_kind == LBFQ_V_BLOCK)
         c_blk *= p.v_scale[((size_t)b * (p.N / p.v_block) + n0 / p.v_block) * p.H + h];
-      if (BLASST && row_in_tile == 0) misc[2 + t] = elide ? 1 : 0;
+      if (BLASST && row_in_tile == 0 && hf == 0) misc[2 + t] = elide ? 1 : 0;
       tc_fence_before();
       mbar_arrive(BAR_PRDY(t));
       a_prev = alpha; c_prev = c_blk; elided_prev = elide; blk_prev = it;
@@ -621,32 +697,39 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         alive = false;
       }
     }
+    // the row sum is the sum of the two partial sums (same alpha sequence on both sides)
+    if (alive) {
+      lpart[(t * 2 + hf) * kTileM + row_in_tile] = l_i;
+      mbar_arrive(BAR_LRDY(t));
+      alive = mbar_wait(BAR_LRDY(t), 0, abort_flag, p.status, 14);
+    }
 
     // ---- epilogue (attention_triton.py:387-407) ---------------------------------
     if (alive && row_ok) {
-      const float inv_l = __fdiv_rn(1.0f, l_i);
-      const float* vsc = p.v_kind == LBFQ_V_CHANNEL ? p.v_scale + (size_t)bh * D : nullptr;
+      const float l_row = lpart[(t * 2 + 0) * kTileM + row_in_tile] + lpart[(t * 2 + 1) * kTileM + row_in_tile];
+      const float inv_l = __fdiv_rn(1.0f, l_row);
+      const float* vsc = p.v_kind == LBFQ_V_CHANNEL ? p.v_scale + (size_t)bh * D + d0 : nullptr;
       const int64_t drow = p.out_row_index ? p.out_row_index[(size_t)bh * p.M + row] : row;
-      const size_t o_off = p.out_layout == LBFQ_LAYOUT_NHD
-                               ? (((size_t)b * p.M + drow) * p.H + h) * D
-                               : ((size_t)bh * p.M + drow) * D;
+      const size_t o_off = (p.out_layout == LBFQ_LAYOUT_NHD
+                                ? (((size_t)b * p.M + drow) * p.H + h) * D
+                                : ((size_t)bh * p.M + drow) * D) + d0;
 #pragma unroll
-      for (int i = 0; i < D; ++i) acc[i] = (vsc ? acc[i] * __ldg(vsc + i) : acc[i]) * inv_l;
+      for (int i = 0; i < HD; ++i) acc[i] = (vsc ? acc[i] * __ldg(vsc + i) : acc[i]) * inv_l;
       if (p.out_dtype == LBFQ_F32) {
-        float4* o = reinterpret_cast<float4*>((float*)p.out + o_off);
+        float4* o4 = reinterpret_cast<float4*>((float*)p.out + o_off);
 #pragma unroll
-        for (int i = 0; i < D / 4; ++i) {
+        for (int i = 0; i < HD / 4; ++i) {
           float4 v = make_float4(acc[4 * i], acc[4 * i + 1], acc[4 * i + 2], acc[4 * i + 3]);
           if (!p.out_exact) {
             v.x = round_through<__nv_bfloat16>(v.x); v.y = round_through<__nv_bfloat16>(v.y);
             v.z = round_through<__nv_bfloat16>(v.z); v.w = round_through<__nv_bfloat16>(v.w);
           }
-          o[i] = v;
+          o4[i] = v;
         }
       } else {
-        uint4* o = reinterpret_cast<uint4*>((uint16_t*)p.out + o_off);
+        uint4* o4 = reinterpret_cast<uint4*>((uint16_t*)p.out + o_off);
 #pragma unroll
-        for (int i = 0; i < D / 8; ++i) {
+        for (int i = 0; i < HD / 8; ++i) {
           uint32_t w[4];
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
@@ -659,19 +742,19 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
               w[j] = *reinterpret_cast<uint32_t*>(&hh);
             }
           }
-          o[i] = make_uint4(w[0], w[1], w[2], w[3]);
+          o4[i] = make_uint4(w[0], w[1], w[2], w[3]);
         }
       }
     }
-    if (BLASST && alive && row_ok && p.stats) {
+    if (BLASST && alive && row_ok && hf == 0 && p.stats) {
       const int mb = row / p.block_m;
       atomicAdd(p.stats + ((size_t)mb * (p.B * p.H) + bh) * 2 + 0, n_skip);
       atomicAdd(p.stats + ((size_t)mb * (p.B * p.H) + bh) * 2 + 1, n_total);
     }
   } else {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 32;");
   }
-  if (warp == 8) {
+  if (warp == kTmaWarp) {
     // =========================== TMA producer =====================================
     if (lane == 0) {
       for (int t = 0; t < 2; ++t) {
@@ -691,9 +774,9 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         tma_load_3d(sbase + SM::offV + st * SM::kV, &tm_v, c * kChunk, 0, bh, BAR_VFULL(st));
       }
     }
-  } else if (warp == 9 || warp == 10) {
+  } else if (warp == kMmaWarp0 || warp == kMmaWarp0 + 1) {
     // =========================== MMA issuer of tile t ==============================
-    const int t = warp - 9;
+    const int t = warp - kMmaWarp0;
     if (lane == 0) {
       const uint32_t tS = tmem_base + t * TCOLS + COL_S;
       const uint32_t tP = tmem_base + t * TCOLS + COL_P;
@@ -743,7 +826,7 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
   // ---- teardown -------------------------------------------------------------------
   tc_fence_before();
   __syncthreads();
-  if (warp == 8) {
+  if (warp == kTmaWarp) {
     if (*abort_flag && lane == 0) {
       // give in-flight bulk copies a bounded time to land before the CTA retires
       const unsigned long long t0 = clock64();

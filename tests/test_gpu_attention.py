@@ -126,7 +126,7 @@ def test_blasst_stats_and_whole_tile_elision():
     u = u / u.norm()
     q = (u.view(1, 1, 1, D) + 0.01 * torch.randn(B, S, H, D)).bfloat16()
     k = 0.05 * torch.randn(B, S, H, D)
-    k[:, :64] = 4.0 * u.view(1, 1, 1, D)
+    k[:, :64] = 40.0 * u.view(1, 1, 1, D)
     k = k.bfloat16()
     v = torch.randn(B, S, H, D).bfloat16()
     cfg = QuantConfig(**COMMON, smoothing="off", q_kmeans_k=None, blasst_lambda=0.5)
