@@ -74,8 +74,10 @@ int lbfq_fp8_channel_dequant(const uint8_t* codes, const float* scale, int B, in
                              void* out, int out_dtype, void* stream);
 
 /* mxfp8_qk_quant, quant_triton.py:221-271. scale: fp32 (B, S, H, D/block_d)
- * holding 2**e. If `scale_e8` is non-null it also receives the biased
- * exponents e+127 as bytes, (B, H, s_pad, D/block_d), for the block-scaled MMA. */
+ * holding 2**e. If `scale_e8` is non-null (needs s_pad % 128 == 0, D/block_d <= 4)
+ * it also receives the biased exponents e+127 as bytes for the block-scaled MMA:
+ * (B, H, s_pad/128, 512), each 512-byte tile holding 128 tokens x 4 groups at
+ * byte (t % 32) * 16 + (t / 32) * 4 + g; unused bytes are 127 (scale 1). */
 int lbfq_mxfp8_qk_quant(const void* x, int dtype, int B, int S, int H, int D, int block_d,
                         uint8_t* codes, int layout, int s_pad, float* scale, uint8_t* scale_e8,
                         void* stream);
@@ -101,6 +103,23 @@ int lbfq_mxfp8_v_dequant(const uint8_t* codes, const float* scale, int B, int S,
 int64_t lbfq_smooth_k_scratch_floats(int B, int S, int H, int D);
 int lbfq_smooth_k(const void* k, int dtype, int B, int S, int H, int D, void* out, float* mean,
                   float* partial, void* stream);
+
+/* smooth_k without caller scratch. No counterpart in the reference: it exists for
+ * hosts that can pass inputs and outputs but cannot allocate device memory for the
+ * library (a plugin inside another framework's memory pool, an allocation-free
+ * region such as work being recorded for later replay). Same result as
+ * lbfq_smooth_k; the partial sums live in a 4 MiB array built into the library
+ * (resident on every GPU that loads it, until the process exits). Limits and rules:
+ *  - B*H*ceil(S/256)*D must be <= lbfq_smooth_k_static_max_floats() (1,048,576);
+ *    larger shapes are refused with LBFQ_ERR_ARG;
+ *  - the first call on each device looks up the array's device address (with that
+ *    device current); make that first call before any stream capture;
+ *  - all calls on a device share the one array: calls that may overlap on the GPU
+ *    (different streams) race; serialise them. Nothing needs clearing between calls;
+ *  - it calls no cudaMalloc / cudaFree / allocating library routine. */
+int64_t lbfq_smooth_k_static_max_floats(void);
+int lbfq_smooth_k_static(const void* k, int dtype, int B, int S, int H, int D, void* out, float* mean,
+                         void* stream);
 
 /* group_mean_q (preprocess.py:60-91,169-193) and smooth_v_per_block
  * (preprocess.py:94-166): subtract the column mean of each `block`-row group.
@@ -186,8 +205,8 @@ typedef struct lbfq_attn_args {
   const float* q_scale;       /* fp8_block: (B, M/qk_block, H) */
   const float* k_scale;       /* fp8_block: (B, N/qk_block, H) */
   int qk_block;               /* fp8_block_size */
-  const uint8_t* q_scale_e8;  /* mx: (B,H,m_pad,D/32) biased exponents */
-  const uint8_t* k_scale_e8;  /* mx: (B,H,n_pad,D/32) */
+  const uint8_t* q_scale_e8;  /* mx: (B,H,m_pad/128,512) biased exponents, tile order of lbfq_mxfp8_qk_quant */
+  const uint8_t* k_scale_e8;  /* mx: (B,H,n_pad/128,512) */
   /* V scales */
   int v_kind;                 /* LBFQ_V_* */
   const float* v_scale;       /* channel: (B,H,D); block: (B, N/v_block, H); mx: (B, N/v_block, H, D) */

@@ -45,6 +45,15 @@ constexpr int kStages = 3;
 constexpr int kSoftmaxWarps = 16;        // 2 tiles x 2 halves x 4 lane quarters
 constexpr int kThreads = 640;            // 16 softmax warps + 1 warpgroup of service warps
 constexpr int kOnesRows = 16;
+// Register budget. `setmaxnreg.inc` blocks until the CTA's register pool -- the registers the CTA
+// got at launch, kThreads x kRegsLaunch -- can satisfy it, so the two requests below must fit in
+// that pool or the softmax warps would wait for ever.
+constexpr int kRegsLaunch = (65536 / kThreads) / 8 * 8;      // what __launch_bounds__(kThreads, 1) yields
+constexpr int kRegsSoftmax = 112;
+constexpr int kRegsService = 24;
+static_assert(kSoftmaxWarps * 32 * kRegsSoftmax + (kThreads - kSoftmaxWarps * 32) * kRegsService <= kThreads * kRegsLaunch,
+              "setmaxnreg requests exceed the CTA's register pool");
+static_assert(kRegsSoftmax % 8 == 0 && kRegsService % 8 == 0 && kRegsService >= 24, "setmaxnreg granularity");
 constexpr unsigned long long kWaitCycles = 1000000000ull;   // ~0.5 s: far above any legitimate wait
 
 // ---------------------------------------------------------------------------
@@ -96,6 +105,15 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
       ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(bar) : "memory");
 }
 
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+// 32 rows x 16 bytes of shared memory -> 4 TMEM columns of lanes 0..31, replicated into every lane quarter
+__device__ __forceinline__ void tc_cp_32x128b(uint32_t taddr, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
@@ -110,6 +128,14 @@ __device__ __forceinline__ void mma_f8_ss(uint32_t d_tmem, uint64_t a_desc, uint
       "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc) : "memory");
+}
+// block-scaled: D[tmem] (+)= (A * 2^sfa)[smem desc] . (B * 2^sfb)[smem desc]^T, one UE8M0 scale per row and 32 K
+__device__ __forceinline__ void mma_mxf8_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                            uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc), "r"(sfa_tmem), "r"(sfb_tmem) : "memory");
 }
 // D[tmem] (+)= A[tmem] . B[smem desc]^T
 __device__ __forceinline__ void mma_f8_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
@@ -186,6 +212,16 @@ __host__ __device__ constexpr uint32_t make_idesc(int n) {
   return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
 }
 
+// kind::mxf8f6f4.block_scale, e4m3 x e4m3, UE8M0 scales, K-major operands, M = 128; `sf` = which byte of
+// the 32-bit scale columns (= which 32-wide K block) this instruction uses, for A and for B.
+__host__ __device__ constexpr uint32_t make_idesc_mx(int n, int sf) {
+  return ((uint32_t)sf << 4) | ((uint32_t)(n >> 3) << 17) | (1u << 23) | ((uint32_t)(128 >> 4) << 24) | ((uint32_t)sf << 29);
+}
+// 32 x 16-byte rows, contiguous (no swizzle): the source of a scale-factor copy
+__device__ __forceinline__ uint64_t make_desc_sf(uint32_t saddr) {
+  return (uint64_t)((saddr >> 4) & 0x3fffu) | ((uint64_t)1 << 16) | ((uint64_t)(128 >> 4) << 32) | ((uint64_t)1 << 46);
+}
+
 // ---------------------------------------------------------------------------
 // kernel parameters (a device-side copy of lbfq_attn_args, pre-digested)
 // ---------------------------------------------------------------------------
@@ -194,6 +230,9 @@ struct Params {
   int qk_block;
   const float* q_scale;
   const float* k_scale;
+  const uint8_t* q_sf;         // block-scaled Q/K: UE8M0 scale tiles
+  const uint8_t* k_sf;
+  int m_pad, n_pad;
   int v_kind;
   const float* v_scale;
   int v_block;
@@ -226,7 +265,9 @@ struct Smem {
   static constexpr int offQ = 0;
   static constexpr int offK = offQ + 2 * kQ;
   static constexpr int offV = offK + kStages * kK;
-  static constexpr int offBar = offV + kStages * kV;
+  static constexpr int offQS = offV + kStages * kV;            // Q scale-factor tiles (block-scaled Q/K only)
+  static constexpr int offKS = offQS + 2 * 512;                // K scale-factor tile per stage
+  static constexpr int offBar = offKS + kStages * 512;
   static constexpr int kNumBar = 2 + 4 * kStages + 10;
   static constexpr int offMisc = offBar + kNumBar * 8;
   static constexpr int offL = offMisc + 64;                   // partial row sums [tile][half][row]
@@ -236,7 +277,7 @@ struct Smem {
 // ---------------------------------------------------------------------------
 // the kernel
 // ---------------------------------------------------------------------------
-template <int D, int BN, bool BLASST>
+template <int D, int BN, bool BLASST, bool QKMX>
 __global__ void __launch_bounds__(kThreads, 1)
 attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
             const __grid_constant__ CUtensorMap tm_v, const Params p) {
@@ -244,7 +285,7 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
   constexpr int NSUB = kChunk / BN;                // key blocks per stage
   constexpr int PV_N = D + kOnesRows;              // PV accumulator columns
   constexpr int TCOLS = 256;                       // TMEM columns per tile
-  constexpr int COL_S = 0, COL_P = 64, COL_O = 96;
+  constexpr int COL_S = 0, COL_P = 64, COL_O = 96, COL_SFA = 240, COL_SFB = 244;
   constexpr int HB = BN / 2;                       // key columns owned by one thread of a row pair
   constexpr int HD = D / 2;                        // output columns owned by one thread of a row pair
   static_assert(BN == 32 || BN == 64, "block_n of 32 or 64");
@@ -318,7 +359,7 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
 
   if (warp < kSoftmaxWarps) {
     // =========================== softmax warps ================================
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 120;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsSoftmax));
     const int t = warp >> 3;                                   // tile
     const int hf = (warp >> 2) & 1;                            // which half of the columns / of D this thread owns
     const int row_in_tile = (warp & 3) * 32 + lane;
@@ -752,14 +793,19 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
       atomicAdd(p.stats + ((size_t)mb * (p.B * p.H) + bh) * 2 + 1, n_total);
     }
   } else {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 32;");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsService));
   }
   if (warp == kTmaWarp) {
     // =========================== TMA producer =====================================
     if (lane == 0) {
       for (int t = 0; t < 2; ++t) {
-        mbar_expect_tx(BAR_QFULL(t), SM::kQ);
+        mbar_expect_tx(BAR_QFULL(t), SM::kQ + (QKMX ? 512 : 0));
         tma_load_3d(sbase + SM::offQ + t * SM::kQ, &tm_q, 0, m0 + t * kTileM, bh, BAR_QFULL(t));
+        if (QKMX) {
+          // a tile beyond the padded rows has no scale tile: re-read the last one (its codes are zero-filled)
+          const int tile128 = min((m0 + t * kTileM) >> 7, (p.m_pad >> 7) - 1);
+          bulk_load(sbase + SM::offQS + t * 512, p.q_sf + ((size_t)bh * (p.m_pad >> 7) + tile128) * 512, 512, BAR_QFULL(t));
+        }
       }
       for (int c = 0; c < nchunk; ++c) {
         const int st = c % kStages;
@@ -768,8 +814,9 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
           if (!mbar_wait(BAR_KFREE(st), par, abort_flag, p.status, 21)) break;
           if (!mbar_wait(BAR_VFREE(st), par, abort_flag, p.status, 22)) break;
         }
-        mbar_expect_tx(BAR_KFULL(st), SM::kK);
+        mbar_expect_tx(BAR_KFULL(st), SM::kK + (QKMX ? 512 : 0));
         tma_load_3d(sbase + SM::offK + st * SM::kK, &tm_k, 0, c * kChunk, bh, BAR_KFULL(st));
+        if (QKMX) bulk_load(sbase + SM::offKS + st * 512, p.k_sf + ((size_t)bh * (p.n_pad >> 7) + c) * 512, 512, BAR_KFULL(st));
         mbar_expect_tx(BAR_VFULL(st), D * kChunk);
         tma_load_3d(sbase + SM::offV + st * SM::kV, &tm_v, c * kChunk, 0, bh, BAR_VFULL(st));
       }
@@ -784,15 +831,28 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
       const uint32_t id_qk = make_idesc(BN);
       const uint32_t id_pv = make_idesc(PV_N);
       const uint64_t dq = make_desc(sbase + SM::offQ + t * SM::kQ, D);
+      const uint32_t tSFA = tmem_base + t * TCOLS + COL_SFA;
+      const uint32_t tSFB = tmem_base + t * TCOLS + COL_SFB;
       bool ok = mbar_wait(BAR_QFULL(t), 0, abort_flag, p.status, 31);
+      if (QKMX && ok) tc_cp_32x128b(tSFA, make_desc_sf(sbase + SM::offQS + t * 512));
       auto issue_qk = [&](int j) -> bool {
         const int c = j / NSUB, sub = j % NSUB, st = c % kStages;
         if (sub == 0 && !mbar_wait(BAR_KFULL(st), (c / kStages) & 1, abort_flag, p.status, 32)) return false;
         tc_fence_after();
         const uint64_t dk = make_desc(sbase + SM::offK + st * SM::kK + sub * BN * D, D);
+        if constexpr (QKMX) {
+          // scale factors of this stage's 128 keys: 4 columns, one per group of 32 keys; tcgen05 operations
+          // issued by one thread execute in order, so the copy cannot overtake earlier MMAs that read them
+          if (sub == 0) tc_cp_32x128b(tSFB, make_desc_sf(sbase + SM::offKS + st * 512));
 #pragma unroll
-        for (int kk = 0; kk < D / 32; ++kk)
-          mma_f8_ss(tS, dq + (uint64_t)(kk * 2), dk + (uint64_t)(kk * 2), id_qk, kk > 0 ? 1u : 0u);
+          for (int kk = 0; kk < D / 32; ++kk)
+            mma_mxf8_ss(tS, dq + (uint64_t)(kk * 2), dk + (uint64_t)(kk * 2), make_idesc_mx(BN, kk), tSFA,
+                        tSFB + sub * (BN / 32), kk > 0 ? 1u : 0u);
+        } else {
+#pragma unroll
+          for (int kk = 0; kk < D / 32; ++kk)
+            mma_f8_ss(tS, dq + (uint64_t)(kk * 2), dk + (uint64_t)(kk * 2), id_qk, kk > 0 ? 1u : 0u);
+        }
         tc_commit(BAR_SFULL(t));
         if (sub == NSUB - 1 || j == nblk - 1) tc_commit(BAR_KFREE(st));
         return true;
@@ -871,11 +931,11 @@ static int make_map(CUtensorMap* map, const void* base, uint64_t inner, uint64_t
   return LBFQ_OK;
 }
 
-template <int D, int BN, bool BLASST>
+template <int D, int BN, bool BLASST, bool QKMX>
 static int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const Params& p, cudaStream_t st) {
   using SM = Smem<D, BN>;
   const int smem_bytes = SM::total + 1024;
-  auto kern = attn_kernel<D, BN, BLASST>;
+  auto kern = attn_kernel<D, BN, BLASST, QKMX>;
   LBFQ_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
   dim3 grid((p.M + kCtaM - 1) / kCtaM, p.B * p.H, 1);
   kern<<<grid, kThreads, smem_bytes, st>>>(mq, mk, mv, p);
@@ -925,13 +985,19 @@ extern "C" int lbfq_attention_fwd(const lbfq_attn_args* a, void* workspace, void
   LBFQ_REQUIRE(a->m_pad >= a->M && a->m_pad % 128 == 0 && a->n_pad >= a->N && a->n_pad % 128 == 0, LBFQ_ERR_ARG,
                "m_pad / n_pad must cover M / N and be multiples of 128");
   LBFQ_REQUIRE(a->q_codes && a->k_codes && a->v_codes && a->out, LBFQ_ERR_ARG, "null operand pointer");
-  LBFQ_REQUIRE(a->qk_kind == LBFQ_QK_FP8_BLOCK, LBFQ_ERR_UNSUPPORTED,
-               "block-scaled (mxfp8) Q/K operands go through lbfq_attention_fwd_mx");
-  LBFQ_REQUIRE(a->q_scale && a->k_scale && a->qk_block > 0, LBFQ_ERR_ARG, "fp8_block Q/K needs scales and a block size");
-  LBFQ_REQUIRE(a->M % a->qk_block == 0 && a->N % a->qk_block == 0, LBFQ_ERR_ARG,
-               "S must be divisible by fp8_block_size=%d", a->qk_block);
-  LBFQ_REQUIRE(a->qk_block % a->block_n == 0, LBFQ_ERR_UNSUPPORTED,
-               "fp8_block_size (%d) must be a multiple of block_n (%d)", a->qk_block, a->block_n);
+  LBFQ_REQUIRE(a->qk_kind == LBFQ_QK_FP8_BLOCK || a->qk_kind == LBFQ_QK_MX, LBFQ_ERR_ARG, "unknown qk_kind %d", a->qk_kind);
+  const bool mx = a->qk_kind == LBFQ_QK_MX;
+  if (mx) {
+    LBFQ_REQUIRE(a->q_scale_e8 && a->k_scale_e8, LBFQ_ERR_ARG, "mxfp8 Q/K needs the UE8M0 scale tiles");
+    LBFQ_REQUIRE(a->qk_block == 32, LBFQ_ERR_UNSUPPORTED,
+                 "mxfp8_block_size=%d: the block-scaled MMA scales 32 elements of D at a time", a->qk_block);
+  } else {
+    LBFQ_REQUIRE(a->q_scale && a->k_scale && a->qk_block > 0, LBFQ_ERR_ARG, "fp8_block Q/K needs scales and a block size");
+    LBFQ_REQUIRE(a->M % a->qk_block == 0 && a->N % a->qk_block == 0, LBFQ_ERR_ARG,
+                 "S must be divisible by fp8_block_size=%d", a->qk_block);
+    LBFQ_REQUIRE(a->qk_block % a->block_n == 0, LBFQ_ERR_UNSUPPORTED,
+                 "fp8_block_size (%d) must be a multiple of block_n (%d)", a->qk_block, a->block_n);
+  }
   LBFQ_REQUIRE(a->p_kind >= 0 && a->p_kind <= 2, LBFQ_ERR_ARG, "unknown p_quant_mode");
   LBFQ_REQUIRE(a->v_kind >= 0 && a->v_kind <= 2 && a->v_scale, LBFQ_ERR_ARG, "bad V quant kind / scale");
   if (a->v_kind != LBFQ_V_CHANNEL) {
@@ -967,7 +1033,8 @@ extern "C" int lbfq_attention_fwd(const lbfq_attn_args* a, void* workspace, void
 
   Params p{};
   p.B = a->B; p.H = a->H; p.M = a->M; p.N = a->N; p.D = a->D;
-  p.qk_block = a->qk_block; p.q_scale = a->q_scale; p.k_scale = a->k_scale;
+  p.qk_block = mx ? 1 : a->qk_block; p.q_scale = mx ? nullptr : a->q_scale; p.k_scale = mx ? nullptr : a->k_scale;
+  p.q_sf = a->q_scale_e8; p.k_sf = a->k_scale_e8; p.m_pad = a->m_pad; p.n_pad = a->n_pad;
   p.v_kind = a->v_kind; p.v_scale = a->v_scale; p.v_block = a->v_block > 0 ? a->v_block : a->block_n;
   p.sm_scale = a->sm_scale; p.p_off = a->p_max_offset; p.p_kind = a->p_kind; p.block_m = a->block_m;
   p.v_alpha = nullptr; p.v_smooth_block = a->v_smooth_block > 0 ? a->v_smooth_block : a->block_n;
@@ -1000,8 +1067,9 @@ extern "C" int lbfq_attention_fwd(const lbfq_attn_args* a, void* workspace, void
   if (int rc = make_map(&mv, a->v_codes, a->n_pad, a->D, BH, kChunk, a->D)) return rc;
 
   const bool bl = a->use_blasst != 0;
-#define LBFQ_LAUNCH(DD, NN)                                                        \
-  return bl ? launch<DD, NN, true>(mq, mk, mv, p, st) : launch<DD, NN, false>(mq, mk, mv, p, st)
+#define LBFQ_LAUNCH(DD, NN)                                                                            \
+  return mx ? (bl ? launch<DD, NN, true, true>(mq, mk, mv, p, st) : launch<DD, NN, false, true>(mq, mk, mv, p, st)) \
+            : (bl ? launch<DD, NN, true, false>(mq, mk, mv, p, st) : launch<DD, NN, false, false>(mq, mk, mv, p, st))
   if (a->D == 128 && a->block_n == 64) { LBFQ_LAUNCH(128, 64); }
   if (a->D == 128 && a->block_n == 32) { LBFQ_LAUNCH(128, 32); }
   if (a->D == 64 && a->block_n == 64) { LBFQ_LAUNCH(64, 64); }

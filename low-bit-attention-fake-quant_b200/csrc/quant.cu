@@ -250,7 +250,13 @@ mxfp8_qk_quant_kernel(const T* __restrict__ x, CodeDst dst, float* __restrict__ 
       if ((d0 % block_d) == 0) {
         int g = d0 / block_d;
         scale[((((size_t)b * dst.S + s0 + r) * dst.H + h)) * ngrp + g] = sc;
-        if (scale_e8) scale_e8[(((size_t)b * dst.H + h) * dst.s_pad + s0 + r) * ngrp + g] = (uint8_t)(e + 127);
+        if (scale_e8) {
+          // 128-token x 4-group tiles of 512 bytes in the order the block-scaled MMA reads scale
+          // factors from tensor memory: byte (t % 32) * 16 + (t / 32) * 4 + g for token t of the tile
+          const int tok = s0 + r, tile128 = tok >> 7, tt = tok & 127;
+          scale_e8[(((size_t)b * dst.H + h) * (dst.s_pad >> 7) + tile128) * 512 + (tt & 31) * 16 + (tt >> 5) * 4 + g] =
+              (uint8_t)(e + 127);
+        }
       }
     }
   }
@@ -432,13 +438,15 @@ extern "C" int lbfq_mxfp8_qk_quant(const void* x, int dtype, int B, int S, int H
                "block_d must be a power of two >= 8; got %d", block_d);
   if (layout == LBFQ_LAYOUT_BHDS)
     LBFQ_REQUIRE(S % 16 == 0, LBFQ_ERR_UNSUPPORTED, "transposed code layout needs S %% 16 == 0; got %d", S);
-  if (scale_e8) LBFQ_REQUIRE(layout != LBFQ_LAYOUT_NHD, LBFQ_ERR_ARG, "scale_e8 needs a BH-major layout (s_pad)");
+  if (scale_e8) {
+    LBFQ_REQUIRE(layout != LBFQ_LAYOUT_NHD && s_pad % 128 == 0, LBFQ_ERR_ARG, "scale_e8 needs a BH-major layout with s_pad %% 128 == 0");
+    LBFQ_REQUIRE(D / block_d <= 4, LBFQ_ERR_UNSUPPORTED, "scale_e8 holds at most 4 groups per token; got %d", D / block_d);
+  }
   cudaStream_t st = (cudaStream_t)stream;
   CodeDst dst{codes, layout, S, H, D, s_pad};
   const int grid = B * ((S + kMxRows - 1) / kMxRows) * H;
-  if (scale_e8 && s_pad > S)   // biased exponent 127 (scale 1.0) on padded rows
-    LBFQ_CUDA_OK(cudaMemset2DAsync(scale_e8 + (size_t)S * (D / block_d), (size_t)s_pad * (D / block_d), 127,
-                                   (size_t)(s_pad - S) * (D / block_d), (size_t)B * H, st));
+  if (scale_e8)                // biased exponent 127 (scale 1.0) wherever no token writes
+    LBFQ_CUDA_OK(cudaMemsetAsync(scale_e8, 127, (size_t)B * H * s_pad * 4, st));
   LBFQ_DISPATCH_DTYPE(dtype, T,
       mxfp8_qk_quant_kernel<T><<<grid, kThreads, 0, st>>>((const T*)x, dst, scale, scale_e8, block_d));
   if (int rc = check_launch("mxfp8_qk_quant")) return rc;

@@ -196,11 +196,17 @@ def _fake_quant_attention_p_requant(q_work, k_work, v_work, qm, v_alpha, q_kmean
     s_pad = _round_up(s, 128)
     q_in, k_in = _rotated(q_work, k_work, cfg, head_offset, total_heads)
 
+    q_sf = k_sf = None
     if cfg.qk_quant == "fp8_block":
         q_codes, q_scale = fp8_block_quant(q_in, block_s=cfg.fp8_block_size, _layout=L.LAYOUT_BHSD, _s_pad=s_pad)
         k_codes, k_scale = fp8_block_quant(k_in, block_s=cfg.fp8_block_size, _layout=L.LAYOUT_BHSD, _s_pad=s_pad)
     elif cfg.qk_quant == "mxfp8":
-        raise NotImplementedError("qk_quant='mxfp8' with p_requant=True: block-scaled Q.K^T is not built yet")
+        # codes + UE8M0 scale tiles for the block-scaled MMA (the FP32 scale tensors are by-products here)
+        nsf = b * h * s_pad * 4
+        q_sf = torch.empty((nsf,), dtype=torch.uint8, device=q_in.device)
+        k_sf = torch.empty((nsf,), dtype=torch.uint8, device=q_in.device)
+        q_codes, q_scale = mxfp8_qk_quant(q_in, block_d=cfg.mxfp8_block_size, _layout=L.LAYOUT_BHSD, _s_pad=s_pad, _scale_e8=q_sf)
+        k_codes, k_scale = mxfp8_qk_quant(k_in, block_d=cfg.mxfp8_block_size, _layout=L.LAYOUT_BHSD, _s_pad=s_pad, _scale_e8=k_sf)
     else:
         raise ValueError(f"unsupported qk_quant: {cfg.qk_quant!r}")
 
@@ -236,7 +242,9 @@ def _fake_quant_attention_p_requant(q_work, k_work, v_work, qm, v_alpha, q_kmean
     return fake_quant_attention_fp8(
         q_codes, k_codes, v_codes,
         seq_q=s, seq_k=s,
-        q_scale=q_scale, k_scale=k_scale, qk_block=cfg.fp8_block_size,
+        q_scale=q_scale, k_scale=k_scale,
+        qk_block=cfg.fp8_block_size if cfg.qk_quant == "fp8_block" else cfg.mxfp8_block_size,
+        q_scale_e8=q_sf, k_scale_e8=k_sf,
         v_kind=cfg.v_quant, v_scale=v_scale, v_block=v_block,
         sm_scale=float(sm_scale), p_max_offset=int(cfg.p_max_offset),
         block_m=cfg.p_requant_block_m, block_n=cfg.p_requant_block_n,

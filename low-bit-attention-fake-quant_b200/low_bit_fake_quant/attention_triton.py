@@ -94,6 +94,8 @@ def fake_quant_attention_fp8(
     q_scale: torch.Tensor,          # (B, M/qk_block, H) fp32
     k_scale: torch.Tensor,          # (B, N/qk_block, H) fp32
     qk_block: int,
+    q_scale_e8: Optional[torch.Tensor] = None,   # block-scaled (mxfp8) Q/K: UE8M0 scale tiles from mxfp8_qk_quant
+    k_scale_e8: Optional[torch.Tensor] = None,
     v_kind: str,                    # "fp8_channel" | "fp8_block" | "mxfp8"
     v_scale: torch.Tensor,
     v_block: int = 0,
@@ -180,9 +182,9 @@ def fake_quant_attention_fp8(
         a.B, a.H, a.M, a.N, a.D = B, H, M, N, D
         a.m_pad, a.n_pad = m_pad, n_pad
         a.q_codes, a.k_codes, a.v_codes = q_codes.data_ptr(), k_codes.data_ptr(), v_codes_t.data_ptr()
-        a.qk_kind = L.QK_FP8_BLOCK
+        a.qk_kind = L.QK_MX if q_scale_e8 is not None else L.QK_FP8_BLOCK
         a.q_scale, a.k_scale, a.qk_block = L.ptr(q_scale), L.ptr(k_scale), int(qk_block)
-        a.q_scale_e8 = a.k_scale_e8 = None
+        a.q_scale_e8, a.k_scale_e8 = L.ptr(q_scale_e8), L.ptr(k_scale_e8)
         a.v_kind, a.v_scale, a.v_block = v_kind_code, L.ptr(v_scale), int(v_block)
         a.sm_scale, a.p_max_offset = float(sm_scale), float(p_max_offset)
         a.p_kind = L.P_KINDS[p_quant_mode]

@@ -80,6 +80,11 @@ CASES = {
     "block128_scales": dict(fp8_block_size=128, smoothing="k_only", q_kmeans_k=None),
     "bn32": dict(smoothing="k_only", q_kmeans_k=None, p_requant_block_m=32, p_requant_block_n=32, v_smooth_mode="per_block", v_smooth_block_size=32, p_quant="dynamic"),
     "offset0": dict(smoothing="k_only", q_kmeans_k=None, p_max_offset=0),
+    # block-scaled Q.K^T (kind::mxf8f6f4): in this convention the oracle and the reference agree exactly
+    "mxfp8_qk": dict(qk_quant="mxfp8", smoothing="off", q_kmeans_k=None),
+    "mxfp8_qk_full_dynamic": dict(qk_quant="mxfp8", smoothing="full", q_kmeans_k=8, v_smooth_mode="per_block", p_quant="dynamic", rowmax_mode="qm_k"),
+    "mxfp8_all_hadamard": dict(qk_quant="mxfp8", v_quant="mxfp8", smoothing="off", q_kmeans_k=None, qk_hadamard=True, p_quant="auto"),
+    "mxfp8_qk_bn32": dict(qk_quant="mxfp8", smoothing="k_only", q_kmeans_k=None, p_requant_block_m=32, p_requant_block_n=32),
 }
 
 
@@ -172,7 +177,9 @@ def test_qm_k_vs_online_close():
 @pytest.mark.parametrize("qk_quant,v_quant,p_requant,smoothing", [
     (qk, vq, pr, sm) for qk in ("fp8_block",) for vq in ("fp8_channel", "fp8_block", "mxfp8")
     for pr in (True, False) for sm in ("off", "k_only", "full")] + [("mxfp8", "fp8_channel", False, "full"),
-                                                                      ("mxfp8", "mxfp8", False, "off")])
+                                                                      ("mxfp8", "mxfp8", False, "off"),
+                                                                      ("mxfp8", "fp8_channel", True, "full"),
+                                                                      ("mxfp8", "mxfp8", True, "k_only")])
 def test_tracks_sdpa_like_the_reference_sweep(qk_quant, v_quant, p_requant, smoothing):
     """Floor of the reference's integration sweep: runs, finite, cos vs SDPA > 0.93
     (tests/test_fake_quant_attention.py:38-61, tests/test_v_quant_variants.py:36-62)."""
@@ -198,6 +205,18 @@ def test_path_a_matches_oracle():
     assert OA.compute_metrics(g, o)["cosine"] > 0.9999            # SDPA kernels differ between CPU and GPU
     mg, mo = OA.compute_metrics(g, ref), OA.compute_metrics(o, ref)
     assert abs(mg["mse"] - mo["mse"]) <= 0.05 * mo["mse"] and mg["cosine"] > 0.99
+
+
+def test_mxfp8_matches_the_reference_convention_too():
+    """Power-of-two scales make the reference's BF16 de-quantisation exact, so for the
+    all-mxfp8 stack the kernel is held to the same tolerance against the oracle run in the
+    REFERENCE's operand convention (faithful=True), not only in its own."""
+    q, k, v = _qkv(1, 512, 2, 128, seed=31)
+    cfg = QuantConfig(qk_quant="mxfp8", v_quant="mxfp8", smoothing="off", q_kmeans_k=None, qk_hadamard=True)
+    g = fq.fake_quant_attention(q.to(DEV), k.to(DEV), v.to(DEV), cfg, _debug_fp32=True).float().cpu()
+    raise_if_device_error(torch.device(DEV))
+    o = OA.fake_quant_attention(q, k, v, cfg, faithful=True, out_fp32=True)
+    _check(g, o, (q, k, v))
 
 
 def test_gap_to_reference_convention():
