@@ -405,19 +405,19 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
       const bool scaled = __any_sync(0xffffffffu, c != 1.f);
       if (!p.v_alpha && p.v_kind != LBFQ_V_MX) {
 #pragma unroll
-        for (int c0 = 0; c0 < HD; c0 += 32) {
-          uint32_t r[32];
-          LBFQ_TMEM_LD32(r, tO + d0 + c0);
+        for (int c0 = 0; c0 < HD; c0 += 16) {
+          uint32_t r[16];
+          LBFQ_TMEM_LD16(r, tO + d0 + c0);
           tc_wait_ld();
           if (rescale) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) acc[c0 + i] = fmaf(c, __uint_as_float(r[i]), acc[c0 + i] * a);
+            for (int i = 0; i < 16; ++i) acc[c0 + i] = fmaf(c, __uint_as_float(r[i]), acc[c0 + i] * a);
           } else if (scaled) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) acc[c0 + i] = fmaf(c, __uint_as_float(r[i]), acc[c0 + i]);
+            for (int i = 0; i < 16; ++i) acc[c0 + i] = fmaf(c, __uint_as_float(r[i]), acc[c0 + i]);
           } else {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) acc[c0 + i] += __uint_as_float(r[i]);
+            for (int i = 0; i < 16; ++i) acc[c0 + i] += __uint_as_float(r[i]);
           }
         }
         return;
@@ -432,14 +432,14 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
       if (p.v_kind == LBFQ_V_MX)
         vs = p.v_scale + (((size_t)b * (p.N / p.v_block) + (jb * BN) / p.v_block) * p.H + h) * D + d0;
 #pragma unroll
-      for (int c0 = 0; c0 < HD; c0 += 32) {
-        uint32_t r[32];
-        LBFQ_TMEM_LD32(r, tO + d0 + c0);
+      for (int c0 = 0; c0 < HD; c0 += 16) {
+        uint32_t r[16];
+        LBFQ_TMEM_LD16(r, tO + d0 + c0);
         tc_wait_ld();
         if (vs) {
           const float4* v4 = reinterpret_cast<const float4*>(vs + c0);
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
+          for (int i = 0; i < 4; ++i) {
             const float4 w = __ldg(v4 + i);
             r[4 * i + 0] = __float_as_uint(__uint_as_float(r[4 * i + 0]) * w.x);
             r[4 * i + 1] = __float_as_uint(__uint_as_float(r[4 * i + 1]) * w.y);
@@ -450,7 +450,7 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         if (av) {
           const float4* a4 = reinterpret_cast<const float4*>(av + c0);
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
+          for (int i = 0; i < 4; ++i) {
             const float4 w = __ldg(a4 + i);
             r[4 * i + 0] = __float_as_uint(fmaf(rs, w.x, __uint_as_float(r[4 * i + 0])));
             r[4 * i + 1] = __float_as_uint(fmaf(rs, w.y, __uint_as_float(r[4 * i + 1])));
@@ -460,10 +460,10 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         }
         if (rescale) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) acc[c0 + i] = fmaf(c, __uint_as_float(r[i]), acc[c0 + i] * a);
+          for (int i = 0; i < 16; ++i) acc[c0 + i] = fmaf(c, __uint_as_float(r[i]), acc[c0 + i] * a);
         } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) acc[c0 + i] = fmaf(c, __uint_as_float(r[i]), acc[c0 + i]);
+          for (int i = 0; i < 16; ++i) acc[c0 + i] = fmaf(c, __uint_as_float(r[i]), acc[c0 + i]);
         }
       }
     };
@@ -516,22 +516,51 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         const float sk = p.k_scale[((size_t)b * (p.N / p.qk_block) + n0 / p.qk_block) * p.H + h];
         f = (sq * sk) * p.sm_scale;
       }
-      float s[HB];                          // own columns
-      float o[BLASST ? HB : 1];             // the partner's columns (kept only for the BLASST fills)
+      // BLASST keeps the scores of both halves in registers (its fills need block statistics); the
+      // plain path never holds more than one chunk: pass 1 reduces all BN columns to the row-block
+      // max, pass 2 re-reads the own half 16 columns at a time and turns it into P codes.
+      float s[BLASST ? HB : 1];             // own columns
+      float o[BLASST ? HB : 1];             // the partner's columns
       float bmax;
       if constexpr (BLASST) {
         const float bo = load_scores(o, tS + oth0, oth0, n0, nvalid, f);
         bmax = fmaxf(bo, load_scores(s, tS + own0, own0, n0, nvalid, f));
+        tc_fence_before();
+        mbar_arrive(BAR_SFREE(t));
       } else {
-        float bo;
-        {
-          float tmp[HB];
-          bo = load_scores(tmp, tS + oth0, oth0, n0, nvalid, f);
+        bmax = -INFINITY;
+#pragma unroll
+        for (int c0 = 0; c0 < BN; c0 += 16) {
+          uint32_t r[16];
+          LBFQ_TMEM_LD16(r, tS + c0);
+          tc_wait_ld();
+          float v[16];
+          if (corr_row) {
+            const float4* c4 = reinterpret_cast<const float4*>(corr_row + n0 + c0);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const float4 cv = __ldg(c4 + i);
+              v[4 * i + 0] = __uint_as_float(r[4 * i + 0]) * f + cv.x;
+              v[4 * i + 1] = __uint_as_float(r[4 * i + 1]) * f + cv.y;
+              v[4 * i + 2] = __uint_as_float(r[4 * i + 2]) * f + cv.z;
+              v[4 * i + 3] = __uint_as_float(r[4 * i + 3]) * f + cv.w;
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);     // raw: f > 0 commutes with max
+          }
+          if (nvalid < BN) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) if (c0 + i >= nvalid) v[i] = -INFINITY;
+          }
+          float b0 = fmaxf(v[0], v[4]), b1 = fmaxf(v[1], v[5]), b2 = fmaxf(v[2], v[6]), b3 = fmaxf(v[3], v[7]);
+          b0 = fmaxf(b0, fmaxf(v[8], v[12])); b1 = fmaxf(b1, fmaxf(v[9], v[13]));
+          b2 = fmaxf(b2, fmaxf(v[10], v[14])); b3 = fmaxf(b3, fmaxf(v[11], v[15]));
+          bmax = fmaxf(bmax, fmaxf(fmaxf(b0, b1), fmaxf(b2, b3)));
         }
-        bmax = fmaxf(bo, load_scores(s, tS + own0, own0, n0, nvalid, f));
+        // rounding is monotonic, so max_i(raw_i * f) == max_i(raw_i) * f bit for bit (f > 0)
+        if (!corr_row) bmax *= f;
       }
-      tc_fence_before();
-      mbar_arrive(BAR_SFREE(t));
 
       // ---- running max / rescale factor (attention_triton.py:164-217) ----------
       float m_new, alpha;
@@ -579,6 +608,7 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         // z = (s - m) * log2e + off in every mode (off = 0 for the scaled P modes, where the
         // product alone is what the reference computes: fma(x, c, 0) == x * c).
         const float off = p.p_kind == LBFQ_P_ELEMENTWISE ? p.p_off : 0.f;
+        if constexpr (BLASST) {
         float psum, pmax;
         if (BLASST && skip) {
           // a skipped row contributes only its softmax-free fill (zero for the "zero" fill);
@@ -720,6 +750,72 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         }
         if constexpr (HB == 32) tmem_st8(tP + own0 / 4, pk); else tmem_st4(tP + own0 / 4, pk);
         tc_wait_st();
+        } else {
+          // ---- pass 2: own half -> P codes, 16 columns at a time -----------------
+          const float pmax = ex2(fmaf(bmax - m_new, kLog2e, off));   // largest P of the block (see above)
+          float inv = 1.f;
+          if (p.p_kind == LBFQ_P_MX) {
+            const int e = pow2_scale_exp(fmaxf(pmax, 1e-4f));
+            c_blk = pow2f(e);
+            inv = pow2f(-e);
+          } else if (p.p_kind == LBFQ_P_DYNAMIC) {
+            c_blk = __fdiv_rn(fmaxf(pmax, 1e-12f), kFp8Max);
+            inv = __fdiv_rn(1.0f, c_blk);
+          }
+          float ps0 = 0.f, ps1 = 0.f, ps2 = 0.f, ps3 = 0.f;
+#pragma unroll
+          for (int c0 = 0; c0 < HB; c0 += 16) {
+            uint32_t r[16];
+            LBFQ_TMEM_LD16(r, tS + own0 + c0);
+            tc_wait_ld();
+            if (c0 + 16 >= HB) {            // S is no longer needed: let the next Q.K^T overwrite it
+              tc_fence_before();
+              mbar_arrive(BAR_SFREE(t));
+            }
+            float v[16];
+            if (corr_row) {
+              const float4* c4 = reinterpret_cast<const float4*>(corr_row + n0 + own0 + c0);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const float4 cv = __ldg(c4 + i);
+                v[4 * i + 0] = __uint_as_float(r[4 * i + 0]) * f + cv.x;
+                v[4 * i + 1] = __uint_as_float(r[4 * i + 1]) * f + cv.y;
+                v[4 * i + 2] = __uint_as_float(r[4 * i + 2]) * f + cv.z;
+                v[4 * i + 3] = __uint_as_float(r[4 * i + 3]) * f + cv.w;
+              }
+            } else {
+#pragma unroll
+              for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]) * f;
+            }
+            if (nvalid < BN) {
+#pragma unroll
+              for (int i = 0; i < 16; ++i) if (own0 + c0 + i >= nvalid) v[i] = -INFINITY;
+            }
+#pragma unroll
+            for (int i = 0; i < 16; i += 4) {
+              v[i] = ex2(fmaf(v[i] - m_new, kLog2e, off));
+              v[i + 1] = ex2(fmaf(v[i + 1] - m_new, kLog2e, off));
+              v[i + 2] = ex2(fmaf(v[i + 2] - m_new, kLog2e, off));
+              v[i + 3] = ex2(fmaf(v[i + 3] - m_new, kLog2e, off));
+              ps0 += v[i]; ps1 += v[i + 1]; ps2 += v[i + 2]; ps3 += v[i + 3];
+            }
+            uint32_t pk[4];
+            if (p.p_kind == LBFQ_P_ELEMENTWISE) {
+#pragma unroll
+              for (int i = 0; i < 4; ++i)
+                pk[i] = (uint32_t)f32x2_to_e4m3x2(v[4 * i], v[4 * i + 1]) | ((uint32_t)f32x2_to_e4m3x2(v[4 * i + 2], v[4 * i + 3]) << 16);
+            } else {
+#pragma unroll
+              for (int i = 0; i < 4; ++i)
+                pk[i] = (uint32_t)f32x2_to_e4m3x2(v[4 * i] * inv, v[4 * i + 1] * inv) |
+                        ((uint32_t)f32x2_to_e4m3x2(v[4 * i + 2] * inv, v[4 * i + 3] * inv) << 16);
+            }
+            tmem_st4(tP + (own0 + c0) / 4, pk);
+          }
+          l_i = l_i * alpha + ((ps0 + ps1) + (ps2 + ps3));
+          l_zero = (l_zero || alpha == 0.f) && (pmax == 0.f);
+          tc_wait_st();
+        }
       } else {
         l_i = l_i * alpha;
       }
@@ -874,11 +970,11 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
       };
       if (ok) ok = issue_qk(0);
       for (int it = 0; it < nblk && ok; ++it) {
-        if (it + 1 < nblk) {
-          ok = mbar_wait(BAR_SFREE(t), it & 1, abort_flag, p.status, 34) && issue_qk(it + 1);
-          if (!ok) break;
-        }
+        // the softmax threads consume P.V of block `it` first (they fold it before touching S of
+        // block it + 1), so it is issued first; both signals arrive close together
         ok = mbar_wait(BAR_PRDY(t), it & 1, abort_flag, p.status, 35) && issue_pv(it);
+        if (ok && it + 1 < nblk)
+          ok = mbar_wait(BAR_SFREE(t), it & 1, abort_flag, p.status, 34) && issue_qk(it + 1);
       }
     }
   }
@@ -991,6 +1087,8 @@ extern "C" int lbfq_attention_fwd(const lbfq_attn_args* a, void* workspace, void
     LBFQ_REQUIRE(a->q_scale_e8 && a->k_scale_e8, LBFQ_ERR_ARG, "mxfp8 Q/K needs the UE8M0 scale tiles");
     LBFQ_REQUIRE(a->qk_block == 32, LBFQ_ERR_UNSUPPORTED,
                  "mxfp8_block_size=%d: the block-scaled MMA scales 32 elements of D at a time", a->qk_block);
+    // scale-factor columns of a 32-key block would start at odd TMEM columns, which the MMA rejects
+    LBFQ_REQUIRE(a->block_n == 64, LBFQ_ERR_UNSUPPORTED, "mxfp8 Q/K needs block_n = 64; got %d", a->block_n);
   } else {
     LBFQ_REQUIRE(a->q_scale && a->k_scale && a->qk_block > 0, LBFQ_ERR_ARG, "fp8_block Q/K needs scales and a block size");
     LBFQ_REQUIRE(a->M % a->qk_block == 0 && a->N % a->qk_block == 0, LBFQ_ERR_ARG,
@@ -1067,12 +1165,15 @@ extern "C" int lbfq_attention_fwd(const lbfq_attn_args* a, void* workspace, void
   if (int rc = make_map(&mv, a->v_codes, a->n_pad, a->D, BH, kChunk, a->D)) return rc;
 
   const bool bl = a->use_blasst != 0;
-#define LBFQ_LAUNCH(DD, NN)                                                                            \
-  return mx ? (bl ? launch<DD, NN, true, true>(mq, mk, mv, p, st) : launch<DD, NN, false, true>(mq, mk, mv, p, st)) \
-            : (bl ? launch<DD, NN, true, false>(mq, mk, mv, p, st) : launch<DD, NN, false, false>(mq, mk, mv, p, st))
-  if (a->D == 128 && a->block_n == 64) { LBFQ_LAUNCH(128, 64); }
-  if (a->D == 128 && a->block_n == 32) { LBFQ_LAUNCH(128, 32); }
-  if (a->D == 64 && a->block_n == 64) { LBFQ_LAUNCH(64, 64); }
-  LBFQ_LAUNCH(64, 32);
+#define LBFQ_LAUNCH(DD, NN, MX)                                                                    \
+  return bl ? launch<DD, NN, true, MX>(mq, mk, mv, p, st) : launch<DD, NN, false, MX>(mq, mk, mv, p, st)
+  if (mx) {
+    if (a->D == 128) { LBFQ_LAUNCH(128, 64, true); }
+    LBFQ_LAUNCH(64, 64, true);
+  }
+  if (a->D == 128 && a->block_n == 64) { LBFQ_LAUNCH(128, 64, false); }
+  if (a->D == 128 && a->block_n == 32) { LBFQ_LAUNCH(128, 32, false); }
+  if (a->D == 64 && a->block_n == 64) { LBFQ_LAUNCH(64, 64, false); }
+  LBFQ_LAUNCH(64, 32, false);
 #undef LBFQ_LAUNCH
 }
