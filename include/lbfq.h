@@ -104,6 +104,23 @@ int64_t lbfq_smooth_k_scratch_floats(int B, int S, int H, int D);
 int lbfq_smooth_k(const void* k, int dtype, int B, int S, int H, int D, void* out, float* mean,
                   float* partial, void* stream);
 
+/* smooth_k without caller scratch. No counterpart in the reference: it exists for
+ * hosts that can pass inputs and outputs but cannot allocate device memory for the
+ * library (a plugin inside another framework's memory pool, an allocation-free
+ * region such as work being recorded for later replay). Same result as
+ * lbfq_smooth_k; the partial sums live in a 4 MiB array built into the library
+ * (resident on every GPU that loads it, until the process exits). Limits and rules:
+ *  - B*H*ceil(S/256)*D must be <= lbfq_smooth_k_static_max_floats() (1,048,576);
+ *    larger shapes are refused with LBFQ_ERR_ARG;
+ *  - the first call on each device looks up the array's device address (with that
+ *    device current); make that first call before any stream capture;
+ *  - all calls on a device share the one array: calls that may overlap on the GPU
+ *    (different streams) race; serialise them. Nothing needs clearing between calls;
+ *  - it calls no cudaMalloc / cudaFree / allocating library routine. */
+int64_t lbfq_smooth_k_static_max_floats(void);
+int lbfq_smooth_k_static(const void* k, int dtype, int B, int S, int H, int D, void* out, float* mean,
+                         void* stream);
+
 /* group_mean_q (preprocess.py:60-91,169-193) and smooth_v_per_block
  * (preprocess.py:94-166): subtract the column mean of each `block`-row group.
  * mean: fp32 (B, S/block, H, D). */

@@ -364,6 +364,57 @@ extern "C" int lbfq_smooth_k(const void* k, int dtype, int B, int S, int H, int 
   return check_launch("sub_channel_mean");
 }
 
+// ---------------------------------------------------------------------------
+// smooth_k for callers that cannot allocate device memory.
+//
+// Some hosts of this library hand it input and output buffers but have no way
+// to give it scratch: a plugin running inside another framework's memory
+// pool, a region where allocation is forbidden (for example while the caller
+// is recording work for later replay), or an embedder whose allocator is not
+// reachable from the call site. For them the per-tile partial column sums of
+// smooth_k live in a fixed array inside the library image instead of in a
+// caller buffer. Every GPU that loads the library carries this array
+// (kStaticScratchFloats * 4 bytes = 4 MiB) until the process exits.
+// ---------------------------------------------------------------------------
+constexpr int64_t kStaticScratchFloats = 1 << 20;
+static __device__ __align__(256) float g_smooth_k_scratch[kStaticScratchFloats];
+
+constexpr int kMaxDevices = 64;
+static float* g_scratch_ptr[kMaxDevices] = {};      // device address of the array, per device ordinal
+
+// Host code must not pass `g_smooth_k_scratch` itself to a kernel: in host code that
+// name is only a handle. The device address is asked for once per device, with that
+// device current, and cached.
+static int static_scratch_for_current_device(float** out) {
+  int dev = -1;
+  LBFQ_CUDA_OK(cudaGetDevice(&dev));
+  LBFQ_REQUIRE(dev >= 0 && dev < kMaxDevices, LBFQ_ERR_UNSUPPORTED, "device ordinal %d outside the supported 0..%d", dev, kMaxDevices - 1);
+  if (g_scratch_ptr[dev] == nullptr) {
+    void* ptr = nullptr;
+    LBFQ_CUDA_OK(cudaGetSymbolAddress(&ptr, g_smooth_k_scratch));
+    LBFQ_REQUIRE(ptr != nullptr, LBFQ_ERR_CUDA, "cudaGetSymbolAddress returned a null address");
+    g_scratch_ptr[dev] = static_cast<float*>(ptr);
+  }
+  *out = g_scratch_ptr[dev];
+  return LBFQ_OK;
+}
+
+extern "C" int64_t lbfq_smooth_k_static_max_floats(void) { return kStaticScratchFloats; }
+
+extern "C" int lbfq_smooth_k_static(const void* k, int dtype, int B, int S, int H, int D, void* out, float* mean,
+                                    void* stream) {
+  const int64_t need = lbfq_smooth_k_scratch_floats(B, S, H, D);
+  LBFQ_REQUIRE(B > 0 && S > 0 && H > 0 && D > 0, LBFQ_ERR_ARG, "smooth_k: unsupported shape (%d,%d,%d,%d)", B, S, H, D);
+  LBFQ_REQUIRE(need <= kStaticScratchFloats, LBFQ_ERR_ARG,
+               "smooth_k_static: this shape needs %lld scratch floats (B*H*ceil(S/256)*D) but the built-in array holds "
+               "%lld; use lbfq_smooth_k with caller scratch", (long long)need, (long long)kStaticScratchFloats);
+  float* scratch = nullptr;
+  if (int rc = static_scratch_for_current_device(&scratch)) return rc;
+  // every partial sum the second kernel reads is written by the first one in this call,
+  // so nothing left over from an earlier call needs clearing
+  return lbfq_smooth_k(k, dtype, B, S, H, D, out, mean, scratch, stream);
+}
+
 extern "C" int lbfq_block_mean_sub(const void* x, int dtype, int B, int S, int H, int D, int block,
                                    void* out, float* mean, void* stream) {
   LBFQ_REQUIRE(D == 64 || D == 128, LBFQ_ERR_ARG, "D must be 64 or 128; got %d", D);

@@ -80,6 +80,8 @@ _SIGS = {
     "lbfq_mxfp8_v_dequant": (_I, [_P, _P, _I, _I, _I, _I, _I, _P, _I, _P]),
     "lbfq_smooth_k_scratch_floats": (C.c_int64, [_I, _I, _I, _I]),
     "lbfq_smooth_k": (_I, [_P, _I, _I, _I, _I, _I, _P, _P, _P, _P]),
+    "lbfq_smooth_k_static_max_floats": (C.c_int64, []),
+    "lbfq_smooth_k_static": (_I, [_P, _I, _I, _I, _I, _I, _P, _P, _P]),
     "lbfq_block_mean_sub": (_I, [_P, _I, _I, _I, _I, _I, _I, _P, _P, _P]),
     "lbfq_hadamard": (_I, [_P, _I, C.c_int64, _I, _I, _P, C.c_float, _P, _P]),
     "lbfq_kmeans_scratch_bytes": (C.c_int64, [_I, _I, _I, _I, _I]),
