@@ -19,12 +19,13 @@
 // line by line; key blocks are walked in order with the reference's BLOCK_N so
 // that every rounding decision of P sees the same running max.
 //
-// CTA = 256 query rows of one (b, h) in two 128-row tiles. Each row is served by
-// TWO threads (same TMEM lane, warps w and w+4 of the tile): each owns half of the
-// key block's columns for the softmax and half of D for the accumulator, and
-// recomputes the row max over the other half instead of synchronising with its
-// partner -- 16 softmax warps per SM hide the TMEM / MUFU latencies that 8 could
-// not. One TMA producer warp and one MMA-issuing warp per tile complete the CTA. K / V^T arrive in 128-key stages shared by both tiles. The extra 16
+// CTA = 256 query rows of one (b, h): two softmax warpgroups (one 128-row tile
+// each, thread == row == TMEM lane), one TMA producer warp, one MMA-issuing warp
+// per tile. Per tile the work is software-pipelined so that no thread waits on a
+// tensor-core result it has just asked for: while block j's softmax runs, the
+// tensor core computes P.V of block j-1 (P is double-buffered in TMEM) and
+// Q.K^T of block j+1; block j-1's P.V is folded into the registers after block
+// j's P has been handed over. K / V^T arrive in 128-key stages shared by both tiles. The extra 16
 // rows of ones appended to every V^T stage make column D of the PV accumulator
 // equal to rowsum(Pc), which the V-smoothing correction needs, for free.
 // Every mbarrier wait is bounded; on expiry the kernel raises `*status`, all
@@ -42,15 +43,15 @@ constexpr int kTileM = 128;              // rows per softmax warpgroup
 constexpr int kCtaM = 2 * kTileM;        // rows per CTA
 constexpr int kChunk = 128;              // keys per TMA stage
 constexpr int kStages = 3;
-constexpr int kSoftmaxWarps = 16;        // 2 tiles x 2 halves x 4 lane quarters
-constexpr int kThreads = 640;            // 16 softmax warps + 1 warpgroup of service warps
+constexpr int kSoftmaxWarps = 8;         // 2 tiles x 4 lane quarters: one thread per query row
+constexpr int kThreads = 384;            // 8 softmax warps + 1 warpgroup of service warps
 constexpr int kOnesRows = 16;
 // Register budget. `setmaxnreg.inc` blocks until the CTA's register pool -- the registers the CTA
 // got at launch, kThreads x kRegsLaunch -- can satisfy it, so the two requests below must fit in
 // that pool or the softmax warps would wait for ever.
 constexpr int kRegsLaunch = (65536 / kThreads) / 8 * 8;      // what __launch_bounds__(kThreads, 1) yields
-constexpr int kRegsSoftmax = 112;
-constexpr int kRegsService = 24;
+constexpr int kRegsSoftmax = 232;
+constexpr int kRegsService = 40;
 static_assert(kSoftmaxWarps * 32 * kRegsSoftmax + (kThreads - kSoftmaxWarps * 32) * kRegsService <= kThreads * kRegsLaunch,
               "setmaxnreg requests exceed the CTA's register pool");
 static_assert(kRegsSoftmax % 8 == 0 && kRegsService % 8 == 0 && kRegsService >= 24, "setmaxnreg granularity");
@@ -285,9 +286,7 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
   constexpr int NSUB = kChunk / BN;                // key blocks per stage
   constexpr int PV_N = D + kOnesRows;              // PV accumulator columns
   constexpr int TCOLS = 256;                       // TMEM columns per tile
-  constexpr int COL_S = 0, COL_P = 64, COL_O = 96, COL_SFA = 240, COL_SFB = 244;
-  constexpr int HB = BN / 2;                       // key columns owned by one thread of a row pair
-  constexpr int HD = D / 2;                        // output columns owned by one thread of a row pair
+  constexpr int COL_S = 0, COL_P = 64, COL_O = 96, COL_SFA = 240, COL_SFB = 244;   // P: two buffers of 16 columns
   static_assert(BN == 32 || BN == 64, "block_n of 32 or 64");
   static_assert(COL_O + PV_N <= TCOLS, "TMEM budget");
 
@@ -305,10 +304,9 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
   auto BAR_SFREE = [&](int t) { return bar0 + 8u * (2 + 4 * kStages + 2 + t); };
   auto BAR_PRDY = [&](int t) { return bar0 + 8u * (2 + 4 * kStages + 4 + t); };
   auto BAR_PVFULL = [&](int t) { return bar0 + 8u * (2 + 4 * kStages + 6 + t); };
-  auto BAR_LRDY = [&](int t) { return bar0 + 8u * (2 + 4 * kStages + 8 + t); };
-  volatile int* misc = (volatile int*)(smem + SM::offMisc);   // [0] tmem base, [1] abort, [2..3] elide flags
+  auto BAR_OFREE = [&](int t) { return bar0 + 8u * (2 + 4 * kStages + 8 + t); };
+  volatile int* misc = (volatile int*)(smem + SM::offMisc);   // [0] tmem base, [1] abort, [2..5] elide flags, [6] early exit
   volatile int* abort_flag = misc + 1;
-  volatile float* lpart = (volatile float*)(smem + SM::offL);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int bh = blockIdx.y;
@@ -320,17 +318,17 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
 
   // ---- setup ----------------------------------------------------------------
   // A CTA scheduled after some other CTA has given up a wait retires at once.
-  if (threadIdx.x == 0) misc[4] = (p.status != nullptr && *reinterpret_cast<volatile int32_t*>(p.status) != 0) ? 1 : 0;
+  if (threadIdx.x == 0) misc[6] = (p.status != nullptr && *reinterpret_cast<volatile int32_t*>(p.status) != 0) ? 1 : 0;
   __syncthreads();
-  if (misc[4]) return;
+  if (misc[6]) return;
   if (threadIdx.x == 0) {
     for (int t = 0; t < 2; ++t) {
       mbar_init(BAR_QFULL(t), 1);
       mbar_init(BAR_SFULL(t), 1);
-      mbar_init(BAR_SFREE(t), 2 * kTileM);
-      mbar_init(BAR_PRDY(t), 2 * kTileM);
+      mbar_init(BAR_SFREE(t), kTileM);
+      mbar_init(BAR_PRDY(t), kTileM);
       mbar_init(BAR_PVFULL(t), 1);
-      mbar_init(BAR_LRDY(t), 2 * kTileM);
+      mbar_init(BAR_OFREE(t), kTileM);
     }
     for (int s = 0; s < kStages; ++s) {
       mbar_init(BAR_KFULL(s), 1);
@@ -338,7 +336,7 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
       mbar_init(BAR_KFREE(s), 2);
       mbar_init(BAR_VFREE(s), 2);
     }
-    misc[1] = 0; misc[2] = 0; misc[3] = 0;
+    misc[1] = 0; misc[2] = 0; misc[3] = 0; misc[4] = 0; misc[5] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   // rows of 1.0 (e4m3 0x38) under every V^T stage
@@ -358,10 +356,9 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
   const uint32_t tmem_base = (uint32_t)misc[0];
 
   if (warp < kSoftmaxWarps) {
-    // =========================== softmax warps ================================
+    // =========================== softmax warpgroups ===========================
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsSoftmax));
-    const int t = warp >> 3;                                   // tile
-    const int hf = (warp >> 2) & 1;                            // which half of the columns / of D this thread owns
+    const int t = warp >> 2;                                   // tile
     const int row_in_tile = (warp & 3) * 32 + lane;
     const int row = m0 + t * kTileM + row_in_tile;             // query row within (b, h)
     const bool row_ok = row < p.M;
@@ -370,8 +367,6 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
     const uint32_t tS = tmem_base + lane_base + t * TCOLS + COL_S;
     const uint32_t tP = tmem_base + lane_base + t * TCOLS + COL_P;
     const uint32_t tO = tmem_base + lane_base + t * TCOLS + COL_O;
-    const int own0 = hf * HB, oth0 = (1 - hf) * HB;            // first column of the own / other half
-    const int d0 = hf * HD;                                    // first output column owned
 
     const float sq = p.q_scale ? p.q_scale[((size_t)b * (p.M / p.qk_block) + rowc / p.qk_block) * p.H + h] : 1.f;
     const float* corr_row = nullptr;
@@ -383,41 +378,37 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
     float est = 0.f;
     if (p.rowmax_est) { est = p.rowmax_est[(size_t)bh * p.M + rowc]; m_i = est; }
     else if (p.rowmax_init) { m_i = p.rowmax_init[(size_t)bh * p.M + rowc]; }
-    float l_i = 0.f, max_seen = -INFINITY;                     // l_i: partial row sum over the own columns
-    // "the whole row has no probability mass yet" (the reference's l_i == 0 test of the estimated
-    // row-max mode), tracked from quantities both threads of a row share: the block's largest P
-    // is positive exactly when the block added mass, and mass is lost again only when alpha is 0
-    bool l_zero = true;
+    float l_i = 0.f, max_seen = -INFINITY;
     float n_skip = 0.f, n_total = 0.f;
     float a_prev = 1.f, c_prev = 1.f;
     bool elided_prev = false;
     int blk_prev = 0;
-    float acc[HD];
+    float acc[D];
 #pragma unroll
-    for (int i = 0; i < HD; ++i) acc[i] = 0.f;
+    for (int i = 0; i < D; ++i) acc[i] = 0.f;
 
-    // fold PV of block `jb` (scale c, rescale a) into the own half of the accumulator. The mode
-    // switches are warp-uniform and hoisted out of the unrolled loops so that no lane issues
-    // predicated-off work.
+    // fold PV of block `jb` (scale c, rescale a) into the accumulator. The mode
+    // switches are warp-uniform and hoisted out of the unrolled loops so that no
+    // lane issues predicated-off work.
     auto accumulate = [&](int jb, float a, float c) {
       tc_fence_after();
       const bool rescale = __any_sync(0xffffffffu, a != 1.f);
       const bool scaled = __any_sync(0xffffffffu, c != 1.f);
       if (!p.v_alpha && p.v_kind != LBFQ_V_MX) {
 #pragma unroll
-        for (int c0 = 0; c0 < HD; c0 += 16) {
-          uint32_t r[16];
-          LBFQ_TMEM_LD16(r, tO + d0 + c0);
+        for (int c0 = 0; c0 < D; c0 += 32) {
+          uint32_t r[32];
+          LBFQ_TMEM_LD32(r, tO + c0);
           tc_wait_ld();
           if (rescale) {
 #pragma unroll
-            for (int i = 0; i < 16; ++i) acc[c0 + i] = fmaf(c, __uint_as_float(r[i]), acc[c0 + i] * a);
+            for (int i = 0; i < 32; ++i) acc[c0 + i] = fmaf(c, __uint_as_float(r[i]), acc[c0 + i] * a);
           } else if (scaled) {
 #pragma unroll
-            for (int i = 0; i < 16; ++i) acc[c0 + i] = fmaf(c, __uint_as_float(r[i]), acc[c0 + i]);
+            for (int i = 0; i < 32; ++i) acc[c0 + i] = fmaf(c, __uint_as_float(r[i]), acc[c0 + i]);
           } else {
 #pragma unroll
-            for (int i = 0; i < 16; ++i) acc[c0 + i] += __uint_as_float(r[i]);
+            for (int i = 0; i < 32; ++i) acc[c0 + i] += __uint_as_float(r[i]);
           }
         }
         return;
@@ -427,19 +418,19 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
       const float* vs = nullptr;
       if (p.v_alpha) {
         rs = __uint_as_float(tmem_ld1(tO + D));
-        av = p.v_alpha + (((size_t)b * (p.N / p.v_smooth_block) + (jb * BN) / p.v_smooth_block) * p.H + h) * D + d0;
+        av = p.v_alpha + (((size_t)b * (p.N / p.v_smooth_block) + (jb * BN) / p.v_smooth_block) * p.H + h) * D;
       }
       if (p.v_kind == LBFQ_V_MX)
-        vs = p.v_scale + (((size_t)b * (p.N / p.v_block) + (jb * BN) / p.v_block) * p.H + h) * D + d0;
+        vs = p.v_scale + (((size_t)b * (p.N / p.v_block) + (jb * BN) / p.v_block) * p.H + h) * D;
 #pragma unroll
-      for (int c0 = 0; c0 < HD; c0 += 16) {
-        uint32_t r[16];
-        LBFQ_TMEM_LD16(r, tO + d0 + c0);
+      for (int c0 = 0; c0 < D; c0 += 32) {
+        uint32_t r[32];
+        LBFQ_TMEM_LD32(r, tO + c0);
         tc_wait_ld();
         if (vs) {
           const float4* v4 = reinterpret_cast<const float4*>(vs + c0);
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
+          for (int i = 0; i < 8; ++i) {
             const float4 w = __ldg(v4 + i);
             r[4 * i + 0] = __float_as_uint(__uint_as_float(r[4 * i + 0]) * w.x);
             r[4 * i + 1] = __float_as_uint(__uint_as_float(r[4 * i + 1]) * w.y);
@@ -450,7 +441,7 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         if (av) {
           const float4* a4 = reinterpret_cast<const float4*>(av + c0);
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
+          for (int i = 0; i < 8; ++i) {
             const float4 w = __ldg(a4 + i);
             r[4 * i + 0] = __float_as_uint(fmaf(rs, w.x, __uint_as_float(r[4 * i + 0])));
             r[4 * i + 1] = __float_as_uint(fmaf(rs, w.y, __uint_as_float(r[4 * i + 1])));
@@ -460,55 +451,38 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         }
         if (rescale) {
 #pragma unroll
-          for (int i = 0; i < 16; ++i) acc[c0 + i] = fmaf(c, __uint_as_float(r[i]), acc[c0 + i] * a);
+          for (int i = 0; i < 32; ++i) acc[c0 + i] = fmaf(c, __uint_as_float(r[i]), acc[c0 + i] * a);
         } else {
 #pragma unroll
-          for (int i = 0; i < 16; ++i) acc[c0 + i] = fmaf(c, __uint_as_float(r[i]), acc[c0 + i]);
+          for (int i = 0; i < 32; ++i) acc[c0 + i] = fmaf(c, __uint_as_float(r[i]), acc[c0 + i]);
         }
       }
-    };
-
-    // scaled scores of HB columns starting at column `col0` of the block, and their max
-    auto load_scores = [&](float (&dst)[HB], uint32_t taddr, int col0, int n0, int nvalid, float f) -> float {
-      uint32_t r[HB];
-      tmem_ld<HB>(r, taddr);
-      tc_wait_ld();
-      if (corr_row) {
-        const float4* c4 = reinterpret_cast<const float4*>(corr_row + n0 + col0);
-#pragma unroll
-        for (int i = 0; i < HB / 4; ++i) {
-          const float4 cv = __ldg(c4 + i);
-          dst[4 * i + 0] = __uint_as_float(r[4 * i + 0]) * f + cv.x;
-          dst[4 * i + 1] = __uint_as_float(r[4 * i + 1]) * f + cv.y;
-          dst[4 * i + 2] = __uint_as_float(r[4 * i + 2]) * f + cv.z;
-          dst[4 * i + 3] = __uint_as_float(r[4 * i + 3]) * f + cv.w;
-        }
-      } else {
-#pragma unroll
-        for (int i = 0; i < HB; ++i) dst[i] = __uint_as_float(r[i]) * f;
-      }
-      if (nvalid < BN) {                    // ragged tail: only the last block of a sequence
-#pragma unroll
-        for (int i = 0; i < HB; ++i) if (col0 + i >= nvalid) dst[i] = -INFINITY;
-      }
-      float b0 = dst[0], b1 = dst[1], b2 = dst[2], b3 = dst[3];
-#pragma unroll
-      for (int i = 4; i < HB; i += 4) {
-        b0 = fmaxf(b0, dst[i]); b1 = fmaxf(b1, dst[i + 1]); b2 = fmaxf(b2, dst[i + 2]); b3 = fmaxf(b3, dst[i + 3]);
-      }
-      return fmaxf(fmaxf(b0, b1), fmaxf(b2, b3));
     };
 
     bool alive = true;
     for (int it = 0; it < nblk && alive; ++it) {
-      // ---- (a) fold the previous block's PV -------------------------------------
-      if (it > 0) {
-        if (!mbar_wait(BAR_PVFULL(t), (it - 1) & 1, abort_flag, p.status, 11)) { alive = false; break; }
-        if (!elided_prev) accumulate(blk_prev, a_prev, c_prev);
-      }
       // ---- (b) S -> P -------------------------------------------------------------
       if (!mbar_wait(BAR_SFULL(t), it & 1, abort_flag, p.status, 12)) { alive = false; break; }
       tc_fence_after();
+      float s[BN];
+      {
+        uint32_t r[32];
+        LBFQ_TMEM_LD32(r, tS);
+        if constexpr (BN == 64) {
+          uint32_t r2[32];
+          LBFQ_TMEM_LD32(r2, tS + 32);
+          tc_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) { s[i] = __uint_as_float(r[i]); s[32 + i] = __uint_as_float(r2[i]); }
+        } else {
+          tc_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) s[i] = __uint_as_float(r[i]);
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(BAR_SFREE(t));
+
       const int n0 = it * BN;
       const int nvalid = min(BN, p.N - n0);
       float f = p.sm_scale;
@@ -516,51 +490,30 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         const float sk = p.k_scale[((size_t)b * (p.N / p.qk_block) + n0 / p.qk_block) * p.H + h];
         f = (sq * sk) * p.sm_scale;
       }
-      // BLASST keeps the scores of both halves in registers (its fills need block statistics); the
-      // plain path never holds more than one chunk: pass 1 reduces all BN columns to the row-block
-      // max, pass 2 re-reads the own half 16 columns at a time and turns it into P codes.
-      float s[BLASST ? HB : 1];             // own columns
-      float o[BLASST ? HB : 1];             // the partner's columns
-      float bmax;
-      if constexpr (BLASST) {
-        const float bo = load_scores(o, tS + oth0, oth0, n0, nvalid, f);
-        bmax = fmaxf(bo, load_scores(s, tS + own0, own0, n0, nvalid, f));
-        tc_fence_before();
-        mbar_arrive(BAR_SFREE(t));
-      } else {
-        bmax = -INFINITY;
+      if (corr_row) {
+        const float4* c4 = reinterpret_cast<const float4*>(corr_row + n0);
 #pragma unroll
-        for (int c0 = 0; c0 < BN; c0 += 16) {
-          uint32_t r[16];
-          LBFQ_TMEM_LD16(r, tS + c0);
-          tc_wait_ld();
-          float v[16];
-          if (corr_row) {
-            const float4* c4 = reinterpret_cast<const float4*>(corr_row + n0 + c0);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const float4 cv = __ldg(c4 + i);
-              v[4 * i + 0] = __uint_as_float(r[4 * i + 0]) * f + cv.x;
-              v[4 * i + 1] = __uint_as_float(r[4 * i + 1]) * f + cv.y;
-              v[4 * i + 2] = __uint_as_float(r[4 * i + 2]) * f + cv.z;
-              v[4 * i + 3] = __uint_as_float(r[4 * i + 3]) * f + cv.w;
-            }
-          } else {
-#pragma unroll
-            for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);     // raw: f > 0 commutes with max
-          }
-          if (nvalid < BN) {
-#pragma unroll
-            for (int i = 0; i < 16; ++i) if (c0 + i >= nvalid) v[i] = -INFINITY;
-          }
-          float b0 = fmaxf(v[0], v[4]), b1 = fmaxf(v[1], v[5]), b2 = fmaxf(v[2], v[6]), b3 = fmaxf(v[3], v[7]);
-          b0 = fmaxf(b0, fmaxf(v[8], v[12])); b1 = fmaxf(b1, fmaxf(v[9], v[13]));
-          b2 = fmaxf(b2, fmaxf(v[10], v[14])); b3 = fmaxf(b3, fmaxf(v[11], v[15]));
-          bmax = fmaxf(bmax, fmaxf(fmaxf(b0, b1), fmaxf(b2, b3)));
+        for (int i = 0; i < BN / 4; ++i) {
+          const float4 cv = __ldg(c4 + i);
+          s[4 * i + 0] = s[4 * i + 0] * f + cv.x;
+          s[4 * i + 1] = s[4 * i + 1] * f + cv.y;
+          s[4 * i + 2] = s[4 * i + 2] * f + cv.z;
+          s[4 * i + 3] = s[4 * i + 3] * f + cv.w;
         }
-        // rounding is monotonic, so max_i(raw_i * f) == max_i(raw_i) * f bit for bit (f > 0)
-        if (!corr_row) bmax *= f;
+      } else {
+#pragma unroll
+        for (int i = 0; i < BN; ++i) s[i] *= f;
       }
+      if (nvalid < BN) {                    // ragged tail: only the last block of a sequence
+#pragma unroll
+        for (int i = 0; i < BN; ++i) if (i >= nvalid) s[i] = -INFINITY;
+      }
+      float bm0 = s[0], bm1 = s[1], bm2 = s[2], bm3 = s[3];
+#pragma unroll
+      for (int i = 4; i < BN; i += 4) {
+        bm0 = fmaxf(bm0, s[i]); bm1 = fmaxf(bm1, s[i + 1]); bm2 = fmaxf(bm2, s[i + 2]); bm3 = fmaxf(bm3, s[i + 3]);
+      }
+      const float bmax = fmaxf(fmaxf(bm0, bm1), fmaxf(bm2, bm3));
 
       // ---- running max / rescale factor (attention_triton.py:164-217) ----------
       float m_new, alpha;
@@ -577,9 +530,9 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         const float up = 16.0f / kLog2e, down = 32.0f / kLog2e;
         const bool under = (bmax - m_i) > up;
         const bool over = (m_i - seen) > down;
-        const float down_m = l_zero ? seen : fmaxf(seen + down, m_i - 80.0f);
+        const float down_m = (l_i == 0.f) ? seen : fmaxf(seen + down, m_i - 80.0f);
         m_new = (under || over) ? (under ? bmax : down_m) : m_i;
-        alpha = (under || over) ? (l_zero ? 0.f : ex2((m_i - m_new) * kLog2e)) : 1.f;
+        alpha = (under || over) ? ((l_i == 0.f) ? 0.f : ex2((m_i - m_new) * kLog2e)) : 1.f;
         max_seen = seen;
       } else if (p.rm_mode == 1) {
         m_new = est;
@@ -596,7 +549,7 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
           uint32_t all;
           asm volatile(
               "{\n\t.reg .pred pi, po;\n\tsetp.ne.b32 pi, %1, 0;\n\t"
-              "barrier.cta.red.and.pred po, %2, 256, pi;\n\tselp.u32 %0, 1, 0, po;\n\t}"
+              "barrier.cta.red.and.pred po, %2, 128, pi;\n\tselp.u32 %0, 1, 0, po;\n\t}"
               : "=r"(all) : "r"((uint32_t)(skip || !row_ok)), "r"(1 + t) : "memory");
           elide = all != 0;
         }
@@ -608,25 +561,19 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         // z = (s - m) * log2e + off in every mode (off = 0 for the scaled P modes, where the
         // product alone is what the reference computes: fma(x, c, 0) == x * c).
         const float off = p.p_kind == LBFQ_P_ELEMENTWISE ? p.p_off : 0.f;
-        if constexpr (BLASST) {
         float psum, pmax;
         if (BLASST && skip) {
-          // a skipped row contributes only its softmax-free fill (zero for the "zero" fill);
-          // block statistics run over both halves, always in column order, so that the two
-          // threads of a row compute identical values
+          // a skipped row contributes only its softmax-free fill (zero for the "zero" fill)
           psum = 0.f; pmax = 0.f;
           if (p.fill_kind == LBFQ_FILL_ZERO) {
 #pragma unroll
-            for (int i = 0; i < HB; ++i) s[i] = 0.f;
+            for (int i = 0; i < BN; ++i) s[i] = 0.f;
           } else {
             const float safe_n = (float)max(nvalid, 1);
-            float sum_own = 0.f, sum_oth = 0.f;
+            float sum = 0.f;
 #pragma unroll
-            for (int i = 0; i < HB; ++i) {
-              sum_own += (own0 + i < nvalid) ? s[i] : 0.f;
-              sum_oth += (oth0 + i < nvalid) ? o[i] : 0.f;
-            }
-            const float mean = (hf ? (sum_oth + sum_own) : (sum_own + sum_oth)) / safe_n;
+            for (int i = 0; i < BN; ++i) sum += (i < nvalid) ? s[i] : 0.f;
+            const float mean = sum / safe_n;
             const float max_bound = safe_n * ex2((bmax - m_new) * kLog2e + off);
             float fill_p = 0.f;
             if (p.fill_kind == LBFQ_FILL_MAX) {
@@ -634,24 +581,17 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
             } else if (p.fill_kind == LBFQ_FILL_MEAN) {
               fill_p = fminf(p.fill_alpha * safe_n * ex2((mean - m_new) * kLog2e + off), max_bound) / safe_n;
             } else if (p.fill_kind == LBFQ_FILL_LOGN) {
-              float v_own = 0.f, v_oth = 0.f;
+              float v2 = 0.f;
 #pragma unroll
-              for (int i = 0; i < HB; ++i) {
-                const float ca = (own0 + i < nvalid) ? s[i] - mean : 0.f;
-                const float cb = (oth0 + i < nvalid) ? o[i] - mean : 0.f;
-                v_own += ca * ca; v_oth += cb * cb;
-              }
-              const float var = (hf ? (v_oth + v_own) : (v_own + v_oth)) / safe_n;
+              for (int i = 0; i < BN; ++i) { const float cd = (i < nvalid) ? s[i] - mean : 0.f; v2 += cd * cd; }
+              const float var = v2 / safe_n;
               fill_p = fminf(safe_n * ex2((mean + 0.5f * var - m_new) * kLog2e + off), max_bound) / safe_n;
             } else if (p.fill_kind == LBFQ_FILL_SAMPLE8) {
               const int stride = BN >= 8 ? BN / 8 : 1;
-              float s_own = 0.f, s_oth = 0.f, cnt = 0.f;
+              float ssum = 0.f, cnt = 0.f;
 #pragma unroll
-              for (int i = 0; i < HB; i += stride) {       // HB is a multiple of the stride
-                if (own0 + i < nvalid) { s_own += ex2((s[i] - m_new) * kLog2e + off); cnt += 1.f; }
-                if (oth0 + i < nvalid) { s_oth += ex2((o[i] - m_new) * kLog2e + off); cnt += 1.f; }
-              }
-              const float ssum = hf ? (s_oth + s_own) : (s_own + s_oth);
+              for (int i = 0; i < BN; i += stride)
+                if (i < nvalid) { ssum += ex2((s[i] - m_new) * kLog2e + off); cnt += 1.f; }
               fill_p = fminf(p.fill_alpha * safe_n * ssum / fmaxf(cnt, 1.f), max_bound) / safe_n;
             } else if (p.fill_kind == LBFQ_FILL_THR) {
               const float off_scale = p.p_kind == LBFQ_P_ELEMENTWISE ? exp2f(p.p_off) : 1.f;
@@ -659,58 +599,38 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
             }
             if (p.fill_kind != LBFQ_FILL_UTA) {
 #pragma unroll
-              for (int i = 0; i < HB; ++i) { s[i] = (own0 + i < nvalid) ? fill_p : 0.f; psum += s[i]; }
+              for (int i = 0; i < BN; ++i) s[i] = (i < nvalid) ? fill_p : 0.f;
+              psum = fill_p * 0.f;
+#pragma unroll
+              for (int i = 0; i < BN; ++i) psum += s[i];
               pmax = fill_p;
-            } else if (p.uta_bins == 1) {                      // one bin = the whole block
-              const float cnt = safe_n;
-              const float bound = cnt * ex2((bmax - m_new) * kLog2e + off);
-              const float mass = p.fill_alpha * cnt * ex2((mean - m_new) * kLog2e + off);
-              const float val = fminf(mass, bound) / cnt;
-#pragma unroll
-              for (int i = 0; i < HB; ++i) { s[i] = (own0 + i < nvalid) ? val : 0.f; psum += s[i]; }
-              pmax = val;
-            } else {                                           // UTA: bins of BN / bins keys, each inside one half
+            } else {                                           // UTA: one value per bin of BN / bins keys
               const int bin_size = BN / p.uta_bins;
-              // partner's bins only matter for the block-wide maximum of P
-              {
-                float bsum = 0.f, bmx = -INFINITY, bcnt = 0.f;
-#pragma unroll
-                for (int i = 0; i < HB; ++i) {
-                  if (oth0 + i < nvalid) { bsum += o[i]; bmx = fmaxf(bmx, o[i]); bcnt += 1.f; }
-                  if (((i + 1) % bin_size) == 0) {
-                    const float safe_c = fmaxf(bcnt, 1.f);
-                    const float bound = safe_c * ex2((bmx - m_new) * kLog2e + off);
-                    const float mass = p.fill_alpha * safe_c * ex2((bsum / safe_c - m_new) * kLog2e + off);
-                    if (bcnt > 0.f) pmax = fmaxf(pmax, fminf(mass, bound) / safe_c);
-                    bsum = 0.f; bmx = -INFINITY; bcnt = 0.f;
-                  }
-                }
-              }
               float bsum = 0.f, bmx = -INFINITY, bcnt = 0.f;
               int first = 0;
 #pragma unroll
-              for (int i = 0; i < HB; ++i) {
-                if (own0 + i < nvalid) { bsum += s[i]; bmx = fmaxf(bmx, s[i]); bcnt += 1.f; }
+              for (int i = 0; i < BN; ++i) {
+                if (i < nvalid) { bsum += s[i]; bmx = fmaxf(bmx, s[i]); bcnt += 1.f; }
                 if (((i + 1) % bin_size) == 0) {
                   const float safe_c = fmaxf(bcnt, 1.f);
                   const float bound = safe_c * ex2((bmx - m_new) * kLog2e + off);
                   const float mass = p.fill_alpha * safe_c * ex2((bsum / safe_c - m_new) * kLog2e + off);
                   const float val = fminf(mass, bound) / safe_c;
 #pragma unroll
-                  for (int q = 0; q < HB; ++q)
-                    if (q >= first && q <= i) s[q] = (own0 + q < nvalid) ? val : 0.f;
+                  for (int q = 0; q < BN; ++q)
+                    if (q >= first && q <= i) s[q] = (q < nvalid) ? val : 0.f;
                   first = i + 1; bsum = 0.f; bmx = -INFINITY; bcnt = 0.f;
                 }
               }
 #pragma unroll
-              for (int i = 0; i < HB; ++i) { psum += s[i]; pmax = fmaxf(pmax, s[i]); }
+              for (int i = 0; i < BN; ++i) { psum += s[i]; pmax = fmaxf(pmax, s[i]); }
             }
           }
         } else {
           // masked columns hold -inf, so their exp2 is exactly 0 without a select
           float ps0 = 0.f, ps1 = 0.f, ps2 = 0.f, ps3 = 0.f;
 #pragma unroll
-          for (int i = 0; i < HB; i += 4) {
+          for (int i = 0; i < BN; i += 4) {
             const float p0 = ex2(fmaf(s[i] - m_new, kLog2e, off));
             const float p1 = ex2(fmaf(s[i + 1] - m_new, kLog2e, off));
             const float p2 = ex2(fmaf(s[i + 2] - m_new, kLog2e, off));
@@ -724,13 +644,12 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
           pmax = ex2(fmaf(bmax - m_new, kLog2e, off));
         }
         l_i = l_i * alpha + psum;
-        l_zero = (l_zero || alpha == 0.f) && (pmax == 0.f);
 
         // ---- P quantisation (attention_triton.py:328-360) -----------------------
-        uint32_t pk[HB / 4];
+        uint32_t pk[BN / 4];
         if (p.p_kind == LBFQ_P_ELEMENTWISE) {
 #pragma unroll
-          for (int i = 0; i < HB / 4; ++i)
+          for (int i = 0; i < BN / 4; ++i)
             pk[i] = (uint32_t)f32x2_to_e4m3x2(s[4 * i], s[4 * i + 1]) | ((uint32_t)f32x2_to_e4m3x2(s[4 * i + 2], s[4 * i + 3]) << 16);
         } else {
           float inv;
@@ -744,86 +663,28 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
           }
           // the conversion saturates at 448, which is the reference's clamp
 #pragma unroll
-          for (int i = 0; i < HB / 4; ++i)
+          for (int i = 0; i < BN / 4; ++i)
             pk[i] = (uint32_t)f32x2_to_e4m3x2(s[4 * i] * inv, s[4 * i + 1] * inv) |
                     ((uint32_t)f32x2_to_e4m3x2(s[4 * i + 2] * inv, s[4 * i + 3] * inv) << 16);
         }
-        if constexpr (HB == 32) tmem_st8(tP + own0 / 4, pk); else tmem_st4(tP + own0 / 4, pk);
+        const uint32_t tPb = tP + (it & 1) * 16;
+        tmem_st8(tPb, pk);
+        if constexpr (BN == 64) tmem_st8(tPb + 8, pk + 8);
         tc_wait_st();
-        } else {
-          // ---- pass 2: own half -> P codes, 16 columns at a time -----------------
-          const float pmax = ex2(fmaf(bmax - m_new, kLog2e, off));   // largest P of the block (see above)
-          float inv = 1.f;
-          if (p.p_kind == LBFQ_P_MX) {
-            const int e = pow2_scale_exp(fmaxf(pmax, 1e-4f));
-            c_blk = pow2f(e);
-            inv = pow2f(-e);
-          } else if (p.p_kind == LBFQ_P_DYNAMIC) {
-            c_blk = __fdiv_rn(fmaxf(pmax, 1e-12f), kFp8Max);
-            inv = __fdiv_rn(1.0f, c_blk);
-          }
-          float ps0 = 0.f, ps1 = 0.f, ps2 = 0.f, ps3 = 0.f;
-#pragma unroll
-          for (int c0 = 0; c0 < HB; c0 += 16) {
-            uint32_t r[16];
-            LBFQ_TMEM_LD16(r, tS + own0 + c0);
-            tc_wait_ld();
-            if (c0 + 16 >= HB) {            // S is no longer needed: let the next Q.K^T overwrite it
-              tc_fence_before();
-              mbar_arrive(BAR_SFREE(t));
-            }
-            float v[16];
-            if (corr_row) {
-              const float4* c4 = reinterpret_cast<const float4*>(corr_row + n0 + own0 + c0);
-#pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                const float4 cv = __ldg(c4 + i);
-                v[4 * i + 0] = __uint_as_float(r[4 * i + 0]) * f + cv.x;
-                v[4 * i + 1] = __uint_as_float(r[4 * i + 1]) * f + cv.y;
-                v[4 * i + 2] = __uint_as_float(r[4 * i + 2]) * f + cv.z;
-                v[4 * i + 3] = __uint_as_float(r[4 * i + 3]) * f + cv.w;
-              }
-            } else {
-#pragma unroll
-              for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]) * f;
-            }
-            if (nvalid < BN) {
-#pragma unroll
-              for (int i = 0; i < 16; ++i) if (own0 + c0 + i >= nvalid) v[i] = -INFINITY;
-            }
-#pragma unroll
-            for (int i = 0; i < 16; i += 4) {
-              v[i] = ex2(fmaf(v[i] - m_new, kLog2e, off));
-              v[i + 1] = ex2(fmaf(v[i + 1] - m_new, kLog2e, off));
-              v[i + 2] = ex2(fmaf(v[i + 2] - m_new, kLog2e, off));
-              v[i + 3] = ex2(fmaf(v[i + 3] - m_new, kLog2e, off));
-              ps0 += v[i]; ps1 += v[i + 1]; ps2 += v[i + 2]; ps3 += v[i + 3];
-            }
-            uint32_t pk[4];
-            if (p.p_kind == LBFQ_P_ELEMENTWISE) {
-#pragma unroll
-              for (int i = 0; i < 4; ++i)
-                pk[i] = (uint32_t)f32x2_to_e4m3x2(v[4 * i], v[4 * i + 1]) | ((uint32_t)f32x2_to_e4m3x2(v[4 * i + 2], v[4 * i + 3]) << 16);
-            } else {
-#pragma unroll
-              for (int i = 0; i < 4; ++i)
-                pk[i] = (uint32_t)f32x2_to_e4m3x2(v[4 * i] * inv, v[4 * i + 1] * inv) |
-                        ((uint32_t)f32x2_to_e4m3x2(v[4 * i + 2] * inv, v[4 * i + 3] * inv) << 16);
-            }
-            tmem_st4(tP + (own0 + c0) / 4, pk);
-          }
-          l_i = l_i * alpha + ((ps0 + ps1) + (ps2 + ps3));
-          l_zero = (l_zero || alpha == 0.f) && (pmax == 0.f);
-          tc_wait_st();
-        }
-      } else {
-        l_i = l_i * alpha;
       }
       if (p.v_kind == LBFQ_V_BLOCK)
         c_blk *= p.v_scale[((size_t)b * (p.N / p.v_block) + n0 / p.v_block) * p.H + h];
-      if (BLASST && row_in_tile == 0 && hf == 0) misc[2 + t] = elide ? 1 : 0;
+      if (BLASST && row_in_tile == 0) misc[2 + 2 * t + (it & 1)] = elide ? 1 : 0;   // per P buffer
       tc_fence_before();
       mbar_arrive(BAR_PRDY(t));
+      // ---- fold the previous block's P.V (issued while this block's softmax ran), then hand the
+      // scratch accumulator back so that this block's P.V may be issued
+      if (it > 0) {
+        if (!mbar_wait(BAR_PVFULL(t), (it - 1) & 1, abort_flag, p.status, 11)) { alive = false; break; }
+        if (!elided_prev) accumulate(blk_prev, a_prev, c_prev);
+        tc_fence_before();
+        mbar_arrive(BAR_OFREE(t));
+      }
       a_prev = alpha; c_prev = c_blk; elided_prev = elide; blk_prev = it;
       m_i = m_new;
     }
@@ -834,39 +695,32 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         alive = false;
       }
     }
-    // the row sum is the sum of the two partial sums (same alpha sequence on both sides)
-    if (alive) {
-      lpart[(t * 2 + hf) * kTileM + row_in_tile] = l_i;
-      mbar_arrive(BAR_LRDY(t));
-      alive = mbar_wait(BAR_LRDY(t), 0, abort_flag, p.status, 14);
-    }
 
     // ---- epilogue (attention_triton.py:387-407) ---------------------------------
     if (alive && row_ok) {
-      const float l_row = lpart[(t * 2 + 0) * kTileM + row_in_tile] + lpart[(t * 2 + 1) * kTileM + row_in_tile];
-      const float inv_l = __fdiv_rn(1.0f, l_row);
-      const float* vsc = p.v_kind == LBFQ_V_CHANNEL ? p.v_scale + (size_t)bh * D + d0 : nullptr;
+      const float inv_l = __fdiv_rn(1.0f, l_i);
+      const float* vsc = p.v_kind == LBFQ_V_CHANNEL ? p.v_scale + (size_t)bh * D : nullptr;
       const int64_t drow = p.out_row_index ? p.out_row_index[(size_t)bh * p.M + row] : row;
-      const size_t o_off = (p.out_layout == LBFQ_LAYOUT_NHD
-                                ? (((size_t)b * p.M + drow) * p.H + h) * D
-                                : ((size_t)bh * p.M + drow) * D) + d0;
+      const size_t o_off = p.out_layout == LBFQ_LAYOUT_NHD
+                               ? (((size_t)b * p.M + drow) * p.H + h) * D
+                               : ((size_t)bh * p.M + drow) * D;
 #pragma unroll
-      for (int i = 0; i < HD; ++i) acc[i] = (vsc ? acc[i] * __ldg(vsc + i) : acc[i]) * inv_l;
+      for (int i = 0; i < D; ++i) acc[i] = (vsc ? acc[i] * __ldg(vsc + i) : acc[i]) * inv_l;
       if (p.out_dtype == LBFQ_F32) {
-        float4* o4 = reinterpret_cast<float4*>((float*)p.out + o_off);
+        float4* o = reinterpret_cast<float4*>((float*)p.out + o_off);
 #pragma unroll
-        for (int i = 0; i < HD / 4; ++i) {
+        for (int i = 0; i < D / 4; ++i) {
           float4 v = make_float4(acc[4 * i], acc[4 * i + 1], acc[4 * i + 2], acc[4 * i + 3]);
           if (!p.out_exact) {
             v.x = round_through<__nv_bfloat16>(v.x); v.y = round_through<__nv_bfloat16>(v.y);
             v.z = round_through<__nv_bfloat16>(v.z); v.w = round_through<__nv_bfloat16>(v.w);
           }
-          o4[i] = v;
+          o[i] = v;
         }
       } else {
-        uint4* o4 = reinterpret_cast<uint4*>((uint16_t*)p.out + o_off);
+        uint4* o = reinterpret_cast<uint4*>((uint16_t*)p.out + o_off);
 #pragma unroll
-        for (int i = 0; i < HD / 8; ++i) {
+        for (int i = 0; i < D / 8; ++i) {
           uint32_t w[4];
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
@@ -879,11 +733,11 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
               w[j] = *reinterpret_cast<uint32_t*>(&hh);
             }
           }
-          o4[i] = make_uint4(w[0], w[1], w[2], w[3]);
+          o[i] = make_uint4(w[0], w[1], w[2], w[3]);
         }
       }
     }
-    if (BLASST && alive && row_ok && hf == 0 && p.stats) {
+    if (BLASST && alive && row_ok && p.stats) {
       const int mb = row / p.block_m;
       atomicAdd(p.stats + ((size_t)mb * (p.B * p.H) + bh) * 2 + 0, n_skip);
       atomicAdd(p.stats + ((size_t)mb * (p.B * p.H) + bh) * 2 + 1, n_total);
@@ -957,12 +811,12 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         const int c = j / NSUB, sub = j % NSUB, st = c % kStages;
         if (sub == 0 && !mbar_wait(BAR_VFULL(st), (c / kStages) & 1, abort_flag, p.status, 33)) return false;
         tc_fence_after();
-        const bool elide = BLASST && misc[2 + t] != 0;
+        const bool elide = BLASST && misc[2 + 2 * t + (j & 1)] != 0;
         if (!elide) {
           const uint64_t dv = make_desc(sbase + SM::offV + st * SM::kV, kChunk);
 #pragma unroll
           for (int kk = 0; kk < BN / 32; ++kk)
-            mma_f8_ts(tO, tP + kk * 8, dv + (uint64_t)((sub * BN + kk * 32) >> 4), id_pv, kk > 0 ? 1u : 0u);
+            mma_f8_ts(tO, tP + (j & 1) * 16 + kk * 8, dv + (uint64_t)((sub * BN + kk * 32) >> 4), id_pv, kk > 0 ? 1u : 0u);
         }
         tc_commit(BAR_PVFULL(t));
         if (sub == NSUB - 1 || j == nblk - 1) tc_commit(BAR_VFREE(st));
@@ -970,11 +824,15 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
       };
       if (ok) ok = issue_qk(0);
       for (int it = 0; it < nblk && ok; ++it) {
-        // the softmax threads consume P.V of block `it` first (they fold it before touching S of
-        // block it + 1), so it is issued first; both signals arrive close together
-        ok = mbar_wait(BAR_PRDY(t), it & 1, abort_flag, p.status, 35) && issue_pv(it);
-        if (ok && it + 1 < nblk)
+        // Q.K^T of the next block as soon as the softmax threads have copied S out
+        if (it + 1 < nblk) {
           ok = mbar_wait(BAR_SFREE(t), it & 1, abort_flag, p.status, 34) && issue_qk(it + 1);
+          if (!ok) break;
+        }
+        // P.V of this block once its P is in TMEM and the previous P.V has been folded
+        ok = mbar_wait(BAR_PRDY(t), it & 1, abort_flag, p.status, 35);
+        if (ok && it > 0) ok = mbar_wait(BAR_OFREE(t), (it - 1) & 1, abort_flag, p.status, 36);
+        if (ok) ok = issue_pv(it);
       }
     }
   }

@@ -84,7 +84,6 @@ CASES = {
     "mxfp8_qk": dict(qk_quant="mxfp8", smoothing="off", q_kmeans_k=None),
     "mxfp8_qk_full_dynamic": dict(qk_quant="mxfp8", smoothing="full", q_kmeans_k=8, v_smooth_mode="per_block", p_quant="dynamic", rowmax_mode="qm_k"),
     "mxfp8_all_hadamard": dict(qk_quant="mxfp8", v_quant="mxfp8", smoothing="off", q_kmeans_k=None, qk_hadamard=True, p_quant="auto"),
-    "mxfp8_qk_bn32": dict(qk_quant="mxfp8", smoothing="k_only", q_kmeans_k=None, p_requant_block_m=32, p_requant_block_n=32),
 }
 
 
@@ -232,6 +231,13 @@ def test_gap_to_reference_convention():
     assert abs(mg["mse"] - mf["mse"]) <= 0.05 * mf["mse"]
     assert abs(mg["cosine"] - mf["cosine"]) <= 2e-4
     assert OA.compute_metrics(g, faithful)["cosine"] > 0.9995
+
+
+def test_mxfp8_qk_needs_block_n_64():
+    x = torch.zeros(1, 128, 1, 128, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(NotImplementedError, match="block_n = 64"):
+        fq.fake_quant_attention(x, x, x, QuantConfig(qk_quant="mxfp8", smoothing="off", q_kmeans_k=None,
+                                                     p_requant_block_m=32, p_requant_block_n=32))
 
 
 def test_errors():
