@@ -256,7 +256,21 @@ struct Params {
   int out_dtype, out_layout, out_exact;
   const int64_t* out_row_index;
   int32_t* status;
+  // element counts of the side tensors, used by the LBFQ_BOUNDS debug build to validate every index
+  long long n_v_scale, n_v_alpha, n_corr, n_qk_scale_q, n_qk_scale_k, n_out;
 };
+
+#ifdef LBFQ_BOUNDS
+#define LBFQ_CHECK_IDX(idx, count, limit, code)                                                   \
+  do {                                                                                            \
+    if ((long long)(idx) < 0 || (long long)(idx) + (long long)(count) > (long long)(limit)) {    \
+      if (p.status) atomicCAS(p.status, 0, (code));                                               \
+      return;                                                                                     \
+    }                                                                                             \
+  } while (0)
+#else
+#define LBFQ_CHECK_IDX(idx, count, limit, code) do { } while (0)
+#endif
 
 template <int D, int BN>
 struct Smem {
@@ -413,48 +427,44 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         }
         return;
       }
+      // Generic fold: per-column V scales (mxfp8 V) and / or the V-smoothing term. Both side vectors are
+      // addressed through always-valid pointers (the unused one aliases the used tensor's base) and
+      // selected by warp-uniform flags, never by pointer nullness.
+      const bool has_av = p.v_alpha != nullptr;
+      const bool has_vs = p.v_kind == LBFQ_V_MX;
       float rs = 0.f;
-      const float* av = nullptr;
-      const float* vs = nullptr;
-      if (p.v_alpha) {
+      const float* av = p.v_scale;
+      const float* vs = p.v_scale;
+      if (has_av) {
         rs = __uint_as_float(tmem_ld1(tO + D));
-        av = p.v_alpha + (((size_t)b * (p.N / p.v_smooth_block) + (jb * BN) / p.v_smooth_block) * p.H + h) * D;
+        const size_t ia = (((size_t)b * (p.N / p.v_smooth_block) + (jb * BN) / p.v_smooth_block) * p.H + h) * D;
+        LBFQ_CHECK_IDX(ia, D, p.n_v_alpha, 101);
+        av = p.v_alpha + ia;
       }
-      if (p.v_kind == LBFQ_V_MX)
-        vs = p.v_scale + (((size_t)b * (p.N / p.v_block) + (jb * BN) / p.v_block) * p.H + h) * D;
+      if (has_vs) {
+        const size_t iv = (((size_t)b * (p.N / p.v_block) + (jb * BN) / p.v_block) * p.H + h) * D;
+        LBFQ_CHECK_IDX(iv, D, p.n_v_scale, 102);
+        vs = p.v_scale + iv;
+      }
 #pragma unroll
-      for (int c0 = 0; c0 < D; c0 += 32) {
-        uint32_t r[32];
-        LBFQ_TMEM_LD32(r, tO + c0);
+      for (int c0 = 0; c0 < D; c0 += 16) {
+        uint32_t r[16];
+        LBFQ_TMEM_LD16(r, tO + c0);
         tc_wait_ld();
-        if (vs) {
-          const float4* v4 = reinterpret_cast<const float4*>(vs + c0);
+        if (has_vs) {
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const float4 w = __ldg(v4 + i);
-            r[4 * i + 0] = __float_as_uint(__uint_as_float(r[4 * i + 0]) * w.x);
-            r[4 * i + 1] = __float_as_uint(__uint_as_float(r[4 * i + 1]) * w.y);
-            r[4 * i + 2] = __float_as_uint(__uint_as_float(r[4 * i + 2]) * w.z);
-            r[4 * i + 3] = __float_as_uint(__uint_as_float(r[4 * i + 3]) * w.w);
-          }
+          for (int i = 0; i < 16; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * vs[c0 + i]);
         }
-        if (av) {
-          const float4* a4 = reinterpret_cast<const float4*>(av + c0);
+        if (has_av) {
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const float4 w = __ldg(a4 + i);
-            r[4 * i + 0] = __float_as_uint(fmaf(rs, w.x, __uint_as_float(r[4 * i + 0])));
-            r[4 * i + 1] = __float_as_uint(fmaf(rs, w.y, __uint_as_float(r[4 * i + 1])));
-            r[4 * i + 2] = __float_as_uint(fmaf(rs, w.z, __uint_as_float(r[4 * i + 2])));
-            r[4 * i + 3] = __float_as_uint(fmaf(rs, w.w, __uint_as_float(r[4 * i + 3])));
-          }
+          for (int i = 0; i < 16; ++i) r[i] = __float_as_uint(fmaf(rs, av[c0 + i], __uint_as_float(r[i])));
         }
         if (rescale) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) acc[c0 + i] = fmaf(c, __uint_as_float(r[i]), acc[c0 + i] * a);
+          for (int i = 0; i < 16; ++i) acc[c0 + i] = fmaf(c, __uint_as_float(r[i]), acc[c0 + i] * a);
         } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) acc[c0 + i] = fmaf(c, __uint_as_float(r[i]), acc[c0 + i]);
+          for (int i = 0; i < 16; ++i) acc[c0 + i] = fmaf(c, __uint_as_float(r[i]), acc[c0 + i]);
         }
       }
     };
@@ -1004,6 +1014,12 @@ extern "C" int lbfq_attention_fwd(const lbfq_attn_args* a, void* workspace, void
   p.stats = a->use_blasst ? a->blasst_stats : nullptr;
   p.out = a->out; p.out_dtype = a->out_dtype; p.out_layout = a->out_layout; p.out_exact = a->out_fp32_exact;
   p.out_row_index = a->out_row_index; p.status = a->status;
+  p.n_v_scale = a->v_kind == LBFQ_V_CHANNEL ? (long long)a->B * a->H * a->D
+                : a->v_kind == LBFQ_V_BLOCK ? (long long)a->B * (a->N / p.v_block) * a->H
+                                            : (long long)a->B * (a->N / p.v_block) * a->H * a->D;
+  p.n_v_alpha = a->v_alpha ? (long long)a->B * (a->N / a->v_smooth_block) * a->H * a->D : 0;
+  p.n_corr = a->qm_corr ? (long long)a->B * a->H * p.n_groups * a->corr_stride : 0;
+  p.n_out = (long long)a->B * a->H * a->M * a->D;
   LBFQ_REQUIRE(p.out_dtype >= 0 && p.out_dtype <= 2, LBFQ_ERR_DTYPE, "unsupported dtype code %d", p.out_dtype);
 
   if (a->v_alpha) {
