@@ -475,6 +475,25 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
       // ---- (b) S -> P -------------------------------------------------------------
       if (!mbar_wait(BAR_SFULL(t), it & 1, abort_flag, p.status, 12)) { alive = false; break; }
       tc_fence_after();
+      float s[BN];
+      {
+        uint32_t r[32];
+        LBFQ_TMEM_LD32(r, tS);
+        if constexpr (BN == 64) {
+          uint32_t r2[32];
+          LBFQ_TMEM_LD32(r2, tS + 32);
+          tc_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) { s[i] = __uint_as_float(r[i]); s[32 + i] = __uint_as_float(r2[i]); }
+        } else {
+          tc_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) s[i] = __uint_as_float(r[i]);
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(BAR_SFREE(t));
+
       const int n0 = it * BN;
       const int nvalid = min(BN, p.N - n0);
       float f = p.sm_scale;
@@ -482,91 +501,30 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         const float sk = p.k_scale[((size_t)b * (p.N / p.qk_block) + n0 / p.qk_block) * p.H + h];
         f = (sq * sk) * p.sm_scale;
       }
-      // BLASST keeps the whole row block in registers (its fills need block statistics). The plain
-      // path never holds more than 32 scores: pass 1 reduces the block to its row max, pass 2 re-reads
-      // S from TMEM chunk by chunk and turns it into P codes. With the accumulator taking 128
-      // registers, this is what leaves the scheduler enough free registers to interleave
-      // independent exp chains.
-      float s[BLASST ? BN : 1];
-      float bmax;
-      if constexpr (BLASST) {
-        {
-          uint32_t r[32];
-          LBFQ_TMEM_LD32(r, tS);
-          if constexpr (BN == 64) {
-            uint32_t r2[32];
-            LBFQ_TMEM_LD32(r2, tS + 32);
-            tc_wait_ld();
+      if (corr_row) {
+        const float4* c4 = reinterpret_cast<const float4*>(corr_row + n0);
 #pragma unroll
-            for (int i = 0; i < 32; ++i) { s[i] = __uint_as_float(r[i]); s[(32 + i) % BN] = __uint_as_float(r2[i]); }
-          } else {
-            tc_wait_ld();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) s[i % BN] = __uint_as_float(r[i]);
-          }
+        for (int i = 0; i < BN / 4; ++i) {
+          const float4 cv = __ldg(c4 + i);
+          s[4 * i + 0] = s[4 * i + 0] * f + cv.x;
+          s[4 * i + 1] = s[4 * i + 1] * f + cv.y;
+          s[4 * i + 2] = s[4 * i + 2] * f + cv.z;
+          s[4 * i + 3] = s[4 * i + 3] * f + cv.w;
         }
-        tc_fence_before();
-        mbar_arrive(BAR_SFREE(t));
-        if (corr_row) {
-          const float4* c4 = reinterpret_cast<const float4*>(corr_row + n0);
-#pragma unroll
-          for (int i = 0; i < BN / 4; ++i) {
-            const float4 cv = __ldg(c4 + i);
-            s[4 * i + 0] = s[4 * i + 0] * f + cv.x;
-            s[4 * i + 1] = s[4 * i + 1] * f + cv.y;
-            s[4 * i + 2] = s[4 * i + 2] * f + cv.z;
-            s[4 * i + 3] = s[4 * i + 3] * f + cv.w;
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < BN; ++i) s[i] *= f;
-        }
-        if (nvalid < BN) {                    // ragged tail: only the last block of a sequence
-#pragma unroll
-          for (int i = 0; i < BN; ++i) if (i >= nvalid) s[i] = -INFINITY;
-        }
-        float bm0 = s[0], bm1 = s[1], bm2 = s[2], bm3 = s[3];
-#pragma unroll
-        for (int i = 4; i < BN; i += 4) {
-          bm0 = fmaxf(bm0, s[i]); bm1 = fmaxf(bm1, s[i + 1]); bm2 = fmaxf(bm2, s[i + 2]); bm3 = fmaxf(bm3, s[i + 3]);
-        }
-        bmax = fmaxf(fmaxf(bm0, bm1), fmaxf(bm2, bm3));
       } else {
-        bmax = -INFINITY;
 #pragma unroll
-        for (int c0 = 0; c0 < BN; c0 += 32) {
-          uint32_t r[32];
-          LBFQ_TMEM_LD32(r, tS + c0);
-          tc_wait_ld();
-          float v[32];
-          if (corr_row) {
-            const float4* c4 = reinterpret_cast<const float4*>(corr_row + n0 + c0);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              const float4 cv = __ldg(c4 + i);
-              v[4 * i + 0] = __uint_as_float(r[4 * i + 0]) * f + cv.x;
-              v[4 * i + 1] = __uint_as_float(r[4 * i + 1]) * f + cv.y;
-              v[4 * i + 2] = __uint_as_float(r[4 * i + 2]) * f + cv.z;
-              v[4 * i + 3] = __uint_as_float(r[4 * i + 3]) * f + cv.w;
-            }
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);     // raw: f > 0 commutes with max
-          }
-          if (nvalid < BN) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) if (c0 + i >= nvalid) v[i] = -INFINITY;
-          }
-          float b0 = fmaxf(v[0], v[4]), b1 = fmaxf(v[1], v[5]), b2 = fmaxf(v[2], v[6]), b3 = fmaxf(v[3], v[7]);
-#pragma unroll
-          for (int i = 8; i < 32; i += 4) {
-            b0 = fmaxf(b0, v[i]); b1 = fmaxf(b1, v[i + 1]); b2 = fmaxf(b2, v[i + 2]); b3 = fmaxf(b3, v[i + 3]);
-          }
-          bmax = fmaxf(bmax, fmaxf(fmaxf(b0, b1), fmaxf(b2, b3)));
-        }
-        // rounding is monotonic, so max_i(raw_i * f) == max_i(raw_i) * f bit for bit (f > 0)
-        if (!corr_row) bmax *= f;
+        for (int i = 0; i < BN; ++i) s[i] *= f;
       }
+      if (nvalid < BN) {                    // ragged tail: only the last block of a sequence
+#pragma unroll
+        for (int i = 0; i < BN; ++i) if (i >= nvalid) s[i] = -INFINITY;
+      }
+      float bm0 = s[0], bm1 = s[1], bm2 = s[2], bm3 = s[3];
+#pragma unroll
+      for (int i = 4; i < BN; i += 4) {
+        bm0 = fmaxf(bm0, s[i]); bm1 = fmaxf(bm1, s[i + 1]); bm2 = fmaxf(bm2, s[i + 2]); bm3 = fmaxf(bm3, s[i + 3]);
+      }
+      const float bmax = fmaxf(fmaxf(bm0, bm1), fmaxf(bm2, bm3));
 
       // ---- running max / rescale factor (attention_triton.py:164-217) ----------
       float m_new, alpha;
@@ -614,7 +572,6 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         // z = (s - m) * log2e + off in every mode (off = 0 for the scaled P modes, where the
         // product alone is what the reference computes: fma(x, c, 0) == x * c).
         const float off = p.p_kind == LBFQ_P_ELEMENTWISE ? p.p_off : 0.f;
-        if constexpr (BLASST) {
         float psum, pmax;
         if (BLASST && skip) {
           // a skipped row contributes only its softmax-free fill (zero for the "zero" fill)
@@ -725,74 +682,6 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         tmem_st8(tPb, pk);
         if constexpr (BN == 64) tmem_st8(tPb + 8, pk + 8);
         tc_wait_st();
-              } else {
-          // ---- pass 2: S -> P codes, 32 columns at a time -------------------------
-          const float pmax = ex2(fmaf(bmax - m_new, kLog2e, off));   // largest P of the block: exp2 is monotonic and
-                                                                     // this is the same instruction sequence as below
-          float inv = 1.f;
-          if (p.p_kind == LBFQ_P_MX) {
-            const int e = pow2_scale_exp(fmaxf(pmax, 1e-4f));
-            c_blk = pow2f(e);
-            inv = pow2f(-e);
-          } else if (p.p_kind == LBFQ_P_DYNAMIC) {
-            c_blk = __fdiv_rn(fmaxf(pmax, 1e-12f), kFp8Max);
-            inv = __fdiv_rn(1.0f, c_blk);
-          }
-          const uint32_t tPb = tP + (it & 1) * 16;
-          float ps0 = 0.f, ps1 = 0.f, ps2 = 0.f, ps3 = 0.f, ps4 = 0.f, ps5 = 0.f, ps6 = 0.f, ps7 = 0.f;
-#pragma unroll
-          for (int c0 = 0; c0 < BN; c0 += 32) {
-            uint32_t r[32];
-            LBFQ_TMEM_LD32(r, tS + c0);
-            tc_wait_ld();
-            if (c0 + 32 >= BN) {            // S is no longer needed: let the next Q.K^T overwrite it
-              tc_fence_before();
-              mbar_arrive(BAR_SFREE(t));
-            }
-            float v[32];
-            if (corr_row) {
-              const float4* c4 = reinterpret_cast<const float4*>(corr_row + n0 + c0);
-#pragma unroll
-              for (int i = 0; i < 8; ++i) {
-                const float4 cv = __ldg(c4 + i);
-                v[4 * i + 0] = __uint_as_float(r[4 * i + 0]) * f + cv.x;
-                v[4 * i + 1] = __uint_as_float(r[4 * i + 1]) * f + cv.y;
-                v[4 * i + 2] = __uint_as_float(r[4 * i + 2]) * f + cv.z;
-                v[4 * i + 3] = __uint_as_float(r[4 * i + 3]) * f + cv.w;
-              }
-            } else {
-#pragma unroll
-              for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * f;
-            }
-            if (nvalid < BN) {
-#pragma unroll
-              for (int i = 0; i < 32; ++i) if (c0 + i >= nvalid) v[i] = -INFINITY;
-            }
-            // masked columns hold -inf, so their exp2 is exactly 0 without a select
-#pragma unroll
-            for (int i = 0; i < 32; i += 8) {
-#pragma unroll
-              for (int j = 0; j < 8; ++j) v[i + j] = ex2(fmaf(v[i + j] - m_new, kLog2e, off));
-              ps0 += v[i]; ps1 += v[i + 1]; ps2 += v[i + 2]; ps3 += v[i + 3];
-              ps4 += v[i + 4]; ps5 += v[i + 5]; ps6 += v[i + 6]; ps7 += v[i + 7];
-            }
-            uint32_t pk[8];
-            if (p.p_kind == LBFQ_P_ELEMENTWISE) {
-#pragma unroll
-              for (int i = 0; i < 8; ++i)
-                pk[i] = (uint32_t)f32x2_to_e4m3x2(v[4 * i], v[4 * i + 1]) | ((uint32_t)f32x2_to_e4m3x2(v[4 * i + 2], v[4 * i + 3]) << 16);
-            } else {
-              // the conversion saturates at 448, which is the reference's clamp
-#pragma unroll
-              for (int i = 0; i < 8; ++i)
-                pk[i] = (uint32_t)f32x2_to_e4m3x2(v[4 * i] * inv, v[4 * i + 1] * inv) |
-                        ((uint32_t)f32x2_to_e4m3x2(v[4 * i + 2] * inv, v[4 * i + 3] * inv) << 16);
-            }
-            tmem_st8(tPb + c0 / 4, pk);
-          }
-          l_i = l_i * alpha + (((ps0 + ps1) + (ps2 + ps3)) + ((ps4 + ps5) + (ps6 + ps7)));
-          tc_wait_st();
-        }
       }
       if (p.v_kind == LBFQ_V_BLOCK)
         c_blk *= p.v_scale[((size_t)b * (p.N / p.v_block) + n0 / p.v_block) * p.H + h];
