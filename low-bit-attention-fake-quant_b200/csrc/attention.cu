@@ -453,12 +453,26 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         LBFQ_TMEM_LD16(r, tO + c0);
         tc_wait_ld();
         if (has_vs) {
+          const float4* v4 = reinterpret_cast<const float4*>(vs + c0);
 #pragma unroll
-          for (int i = 0; i < 16; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * vs[c0 + i]);
+          for (int i = 0; i < 4; ++i) {
+            const float4 w = v4[i];
+            r[4 * i + 0] = __float_as_uint(__uint_as_float(r[4 * i + 0]) * w.x);
+            r[4 * i + 1] = __float_as_uint(__uint_as_float(r[4 * i + 1]) * w.y);
+            r[4 * i + 2] = __float_as_uint(__uint_as_float(r[4 * i + 2]) * w.z);
+            r[4 * i + 3] = __float_as_uint(__uint_as_float(r[4 * i + 3]) * w.w);
+          }
         }
         if (has_av) {
+          const float4* a4 = reinterpret_cast<const float4*>(av + c0);
 #pragma unroll
-          for (int i = 0; i < 16; ++i) r[i] = __float_as_uint(fmaf(rs, av[c0 + i], __uint_as_float(r[i])));
+          for (int i = 0; i < 4; ++i) {
+            const float4 w = a4[i];
+            r[4 * i + 0] = __float_as_uint(fmaf(rs, w.x, __uint_as_float(r[4 * i + 0])));
+            r[4 * i + 1] = __float_as_uint(fmaf(rs, w.y, __uint_as_float(r[4 * i + 1])));
+            r[4 * i + 2] = __float_as_uint(fmaf(rs, w.z, __uint_as_float(r[4 * i + 2])));
+            r[4 * i + 3] = __float_as_uint(fmaf(rs, w.w, __uint_as_float(r[4 * i + 3])));
+          }
         }
         if (rescale) {
 #pragma unroll
