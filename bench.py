@@ -302,8 +302,11 @@ def main():
         fp8_peak = 2.0 * bf16_peak          # dense FP8 tensor rate = 2 x the measured dense BF16 rate
         k_ms = sum(kernel_ms) / max(len(kernel_ms), 1)
         achieved = flops_per_step / (k_ms * 1e-3) / 1e12 if k_ms > 0 else 0.0
+        # DRAM bytes of one attention launch: 55.4 MB measured by ncu on a 4-head launch of the same S
+        # (profiles/attn_kernel_wan14b_k_smooth_static.md), scaled by heads (each head's traffic is independent)
+        traffic = 55.44e6 * heads / 4.0 if seq == S_REAL else None
         roofline = {"bound": "tensor", "achieved": achieved, "peak": fp8_peak, "unit": "TFLOP/s",
-                    "frac": achieved / fp8_peak, "traffic": None, "kernel": "attn_kernel<128,64>",
+                    "frac": achieved / fp8_peak, "traffic": traffic, "kernel": "attn_kernel<128,64>",
                     "kernel_ms": k_ms, "peak_source": f"2 x bf16_tflops ({peak_src})"}
         cpu = None
         if not args.no_cpu_baseline and world == 1:

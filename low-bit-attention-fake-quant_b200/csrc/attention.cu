@@ -244,6 +244,8 @@ struct Params {
   int v_smooth_block;
   const float* corr;
   int q_smooth_block, corr_stride, n_groups;
+  int corr_staged;             // 1: every 128-row tile lies in one Q group, corr rows go through shared memory
+  int side_bytes;              // bytes of side vectors the producer stages per 128-key stage (0: none)
   const float* rowmax_est;
   const float* rowmax_init;
   int rm_mode;                 // 0 online, 1 frozen estimate, 2 estimate with thresholds
@@ -282,8 +284,15 @@ struct Smem {
   static constexpr int offV = offK + kStages * kK;
   static constexpr int offQS = offV + kStages * kV;            // Q scale-factor tiles (block-scaled Q/K only)
   static constexpr int offKS = offQS + 2 * 512;                // K scale-factor tile per stage
-  static constexpr int offBar = offKS + kStages * 512;
-  static constexpr int kNumBar = 2 + 4 * kStages + 10;
+  // side vectors staged per 128-key stage for the softmax threads (read with broadcast shared loads
+  // instead of per-thread global loads): the score bias `corr` of each tile's Q group (128 floats per
+  // tile), and per key block the V-smoothing vector alpha' and the mxfp8 V scales (D floats each)
+  static constexpr int kSub = kChunk / BN;
+  static constexpr int offCorr = offKS + kStages * 512;
+  static constexpr int offAlpha = offCorr + kStages * 2 * kChunk * 4;
+  static constexpr int offVs = offAlpha + kStages * kSub * D * 4;
+  static constexpr int offBar = offVs + kStages * kSub * D * 4;
+  static constexpr int kNumBar = 2 + 4 * kStages + 10 + 2 * kStages;
   static constexpr int offMisc = offBar + kNumBar * 8;
   static constexpr int offL = offMisc + 64;                   // partial row sums [tile][half][row]
   static constexpr int total = offL + 2 * 2 * kTileM * 4;
@@ -319,6 +328,8 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
   auto BAR_PRDY = [&](int t) { return bar0 + 8u * (2 + 4 * kStages + 4 + t); };
   auto BAR_PVFULL = [&](int t) { return bar0 + 8u * (2 + 4 * kStages + 6 + t); };
   auto BAR_OFREE = [&](int t) { return bar0 + 8u * (2 + 4 * kStages + 8 + t); };
+  auto BAR_SIDEFULL = [&](int s) { return bar0 + 8u * (2 + 4 * kStages + 10 + s); };
+  auto BAR_SIDEFREE = [&](int s) { return bar0 + 8u * (2 + 4 * kStages + 10 + kStages + s); };
   volatile int* misc = (volatile int*)(smem + SM::offMisc);   // [0] tmem base, [1] abort, [2..5] elide flags, [6] early exit
   volatile int* abort_flag = misc + 1;
 
@@ -349,6 +360,8 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
       mbar_init(BAR_VFULL(s), 1);
       mbar_init(BAR_KFREE(s), 2);
       mbar_init(BAR_VFREE(s), 2);
+      mbar_init(BAR_SIDEFULL(s), 1);
+      mbar_init(BAR_SIDEFREE(s), 2 * kTileM);
     }
     misc[1] = 0; misc[2] = 0; misc[3] = 0; misc[4] = 0; misc[5] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -384,8 +397,10 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
 
     float sq = 1.f;
     if (p.q_scale != nullptr) sq = p.q_scale[((size_t)b * (p.M / p.qk_block) + rowc / p.qk_block) * p.H + h];
+    const bool side = p.side_bytes > 0;
+    const bool corr_smem = p.corr != nullptr && p.corr_staged != 0;
     const float* corr_row = nullptr;
-    if (p.corr) {
+    if (p.corr != nullptr && !corr_smem) {
       const int g = ((rowc / p.block_m) * p.block_m) / p.q_smooth_block;
       corr_row = p.corr + ((size_t)bh * p.n_groups + g) * p.corr_stride;
     }
@@ -434,19 +449,11 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
       const bool has_av = p.v_alpha != nullptr;
       const bool has_vs = p.v_kind == LBFQ_V_MX;
       float rs = 0.f;
-      const float* av = p.v_scale;
-      const float* vs = p.v_scale;
-      if (has_av) {
-        rs = __uint_as_float(tmem_ld1(tO + D));
-        const size_t ia = (((size_t)b * (p.N / p.v_smooth_block) + (jb * BN) / p.v_smooth_block) * p.H + h) * D;
-        LBFQ_CHECK_IDX(ia, D, p.n_v_alpha, 101);
-        av = p.v_alpha + ia;
-      }
-      if (has_vs) {
-        const size_t iv = (((size_t)b * (p.N / p.v_block) + (jb * BN) / p.v_block) * p.H + h) * D;
-        LBFQ_CHECK_IDX(iv, D, p.n_v_scale, 102);
-        vs = p.v_scale + iv;
-      }
+      if (has_av) rs = __uint_as_float(tmem_ld1(tO + D));
+      // both vectors were staged by the producer with the stage that holds key block jb
+      const int slot = ((jb / NSUB) % kStages) * NSUB + (jb % NSUB);
+      const float* av = reinterpret_cast<const float*>(smem + SM::offAlpha) + slot * D;
+      const float* vs = reinterpret_cast<const float*>(smem + SM::offVs) + slot * D;
 #pragma unroll
       for (int c0 = 0; c0 < D; c0 += 16) {
         uint32_t r[16];
@@ -515,7 +522,22 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         const float sk = p.k_scale[((size_t)b * (p.N / p.qk_block) + n0 / p.qk_block) * p.H + h];
         f = (sq * sk) * p.sm_scale;
       }
-      if (corr_row) {
+      if (side && (it % NSUB) == 0) {        // first key block of a stage: its side vectors must have landed
+        const int c = it / NSUB;
+        if (!mbar_wait(BAR_SIDEFULL(c % kStages), (c / kStages) & 1, abort_flag, p.status, 15)) { alive = false; break; }
+      }
+      if (corr_smem) {
+        const float4* c4 = reinterpret_cast<const float4*>(
+            smem + SM::offCorr + (((it / NSUB) % kStages) * 2 + t) * (kChunk * 4) + (it % NSUB) * (BN * 4));
+#pragma unroll
+        for (int i = 0; i < BN / 4; ++i) {
+          const float4 cv = c4[i];               // same address in every lane: one broadcast wavefront
+          s[4 * i + 0] = s[4 * i + 0] * f + cv.x;
+          s[4 * i + 1] = s[4 * i + 1] * f + cv.y;
+          s[4 * i + 2] = s[4 * i + 2] * f + cv.z;
+          s[4 * i + 3] = s[4 * i + 3] * f + cv.w;
+        }
+      } else if (corr_row) {
         const float4* c4 = reinterpret_cast<const float4*>(corr_row + n0);
 #pragma unroll
         for (int i = 0; i < BN / 4; ++i) {
@@ -709,6 +731,8 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         if (!elided_prev) accumulate(blk_prev, a_prev, c_prev);
         tc_fence_before();
         mbar_arrive(BAR_OFREE(t));
+        // the side vectors of a stage are dead once its last key block has been folded
+        if (side && (blk_prev % NSUB) == NSUB - 1) mbar_arrive(BAR_SIDEFREE((blk_prev / NSUB) % kStages));
       }
       a_prev = alpha; c_prev = c_blk; elided_prev = elide; blk_prev = it;
       m_i = m_new;
@@ -801,6 +825,28 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         if (QKMX) bulk_load(sbase + SM::offKS + st * 512, p.k_sf + ((size_t)bh * (p.n_pad >> 7) + c) * 512, 512, BAR_KFULL(st));
         mbar_expect_tx(BAR_VFULL(st), D * kChunk);
         tma_load_3d(sbase + SM::offV + st * SM::kV, &tm_v, c * kChunk, 0, bh, BAR_VFULL(st));
+        if (p.side_bytes > 0) {
+          if (c >= kStages && !mbar_wait(BAR_SIDEFREE(st), ((c / kStages) - 1) & 1, abort_flag, p.status, 23)) break;
+          mbar_expect_tx(BAR_SIDEFULL(st), p.side_bytes);
+          if (p.corr != nullptr && p.corr_staged) {
+            for (int t = 0; t < 2; ++t) {
+              const int g = min((m0 + t * kTileM) / p.q_smooth_block, p.n_groups - 1);
+              bulk_load(sbase + SM::offCorr + (st * 2 + t) * (kChunk * 4),
+                        p.corr + ((size_t)bh * p.n_groups + g) * p.corr_stride + (size_t)c * kChunk, kChunk * 4, BAR_SIDEFULL(st));
+            }
+          }
+          for (int sub = 0; sub < NSUB; ++sub) {
+            const int key = min(c * kChunk + sub * BN, p.N - 1);     // a block past the end re-reads the last one
+            if (p.v_alpha != nullptr)
+              bulk_load(sbase + SM::offAlpha + (st * NSUB + sub) * (D * 4),
+                        p.v_alpha + (((size_t)b * (p.N / p.v_smooth_block) + key / p.v_smooth_block) * p.H + h) * D, D * 4,
+                        BAR_SIDEFULL(st));
+            if (p.v_kind == LBFQ_V_MX)
+              bulk_load(sbase + SM::offVs + (st * NSUB + sub) * (D * 4),
+                        p.v_scale + (((size_t)b * (p.N / p.v_block) + key / p.v_block) * p.H + h) * D, D * 4,
+                        BAR_SIDEFULL(st));
+          }
+        }
       }
     }
   } else if (warp == kMmaWarp0 || warp == kMmaWarp0 + 1) {
@@ -1028,6 +1074,9 @@ extern "C" int lbfq_attention_fwd(const lbfq_attn_args* a, void* workspace, void
   p.v_alpha = nullptr; p.v_smooth_block = a->v_smooth_block > 0 ? a->v_smooth_block : a->block_n;
   p.corr = a->qm_corr; p.q_smooth_block = a->q_smooth_block > 0 ? a->q_smooth_block : a->block_m;
   p.corr_stride = a->corr_stride; p.n_groups = a->qm_corr ? a->M / a->q_smooth_block : 0;
+  p.corr_staged = (a->qm_corr && a->q_smooth_block % 128 == 0) ? 1 : 0;
+  p.side_bytes = (p.corr_staged ? 2 * kChunk * 4 : 0) +
+                 ((a->v_alpha ? 1 : 0) + (a->v_kind == LBFQ_V_MX ? 1 : 0)) * (kChunk / a->block_n) * a->D * 4;
   p.rowmax_est = a->rowmax_est; p.rowmax_init = a->rowmax_init;
   p.rm_mode = (a->rowmax_est && !a->use_blasst) ? (a->p_kind == LBFQ_P_DYNAMIC ? 2 : 1) : 0;
   p.log_lambda = a->use_blasst ? logf(a->blasst_lambda) : 0.f;
