@@ -306,7 +306,7 @@ def main():
         # (profiles/attn_kernel_wan14b_k_smooth_static.md), scaled by heads (each head's traffic is independent)
         traffic = 55.44e6 * heads / 4.0 if seq == S_REAL else None
         roofline = {"bound": "tensor", "achieved": achieved, "peak": fp8_peak, "unit": "TFLOP/s",
-                    "frac": achieved / fp8_peak, "traffic": traffic, "kernel": "attn_kernel<128,64>",
+                    "frac": achieved / fp8_peak, "traffic": traffic, "kernel": "attn_fast_kernel<128,64>" if lib.lbfq_attention_last_variant() == 1 else "attn_kernel<128,64>",
                     "kernel_ms": k_ms, "peak_source": f"2 x bf16_tflops ({peak_src})"}
         cpu = None
         if not args.no_cpu_baseline and world == 1:

@@ -249,6 +249,12 @@ int64_t lbfq_attention_workspace_bytes(const lbfq_attn_args* args);
  * `workspace` holds lbfq_attention_workspace_bytes(args) bytes (may be NULL when that is 0). */
 int lbfq_attention_fwd(const lbfq_attn_args* args, void* workspace, void* stream);
 
+/* Which kernel the calling thread's last lbfq_attention_fwd launched: 0 = the general kernel (P.V folded in
+ * registers per key block), 1 = the variant whose output accumulator stays in tensor memory (element-wise P,
+ * per-channel V, FP8-block Q/K, no V smoothing, no score bias, no BLASST). Setting the environment variable
+ * LBFQ_ATTN_GENERIC=1 keeps every configuration on the general kernel. No counterpart in the reference. */
+int lbfq_attention_last_variant(void);
+
 #ifdef __cplusplus
 }
 #endif

@@ -31,248 +31,13 @@
 // Every mbarrier wait is bounded; on expiry the kernel raises `*status`, all
 // roles leave their loops, TMEM is released and the launch returns.
 
-#include <cuda.h>
-#include <cudaTypedefs.h>
+#include <cstdlib>
 
-#include "common.cuh"
+#include "attn_prims.cuh"
 
 namespace lbfq {
 namespace attn {
 
-constexpr int kTileM = 128;              // rows per softmax warpgroup
-constexpr int kCtaM = 2 * kTileM;        // rows per CTA
-constexpr int kChunk = 128;              // keys per TMA stage
-constexpr int kStages = 3;
-constexpr int kSoftmaxWarps = 8;         // 2 tiles x 4 lane quarters: one thread per query row
-constexpr int kThreads = 384;            // 8 softmax warps + 1 warpgroup of service warps
-constexpr int kOnesRows = 16;
-// Register budget. `setmaxnreg.inc` blocks until the CTA's register pool -- the registers the CTA
-// got at launch, kThreads x kRegsLaunch -- can satisfy it, so the two requests below must fit in
-// that pool or the softmax warps would wait for ever.
-constexpr int kRegsLaunch = (65536 / kThreads) / 8 * 8;      // what __launch_bounds__(kThreads, 1) yields
-constexpr int kRegsSoftmax = 232;
-constexpr int kRegsService = 40;
-static_assert(kSoftmaxWarps * 32 * kRegsSoftmax + (kThreads - kSoftmaxWarps * 32) * kRegsService <= kThreads * kRegsLaunch,
-              "setmaxnreg requests exceed the CTA's register pool");
-static_assert(kRegsSoftmax % 8 == 0 && kRegsService % 8 == 0 && kRegsService >= 24, "setmaxnreg granularity");
-constexpr unsigned long long kWaitCycles = 1000000000ull;   // ~0.5 s: far above any legitimate wait
-
-// ---------------------------------------------------------------------------
-// PTX wrappers
-// ---------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-  return ok != 0;
-}
-// Bounded wait. Returns false when the wait was given up (here or elsewhere in
-// the CTA); the caller must then leave its loop.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int32_t* status,
-                                          int code) {
-  if (mbar_try(bar, parity)) return true;
-  const unsigned long long t0 = clock64();
-  uint32_t spins = 0;
-  while (true) {
-    if (mbar_try(bar, parity)) return true;
-    if ((++spins & 63u) == 0) {
-      if (*abort_flag) return false;
-      if (clock64() - t0 > kWaitCycles) {
-        *abort_flag = 1;
-        if (status) atomicCAS(status, 0, code);
-        return false;
-      }
-    }
-  }
-}
-
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
-      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(bar) : "memory");
-}
-
-__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
-}
-// 32 rows x 16 bytes of shared memory -> 4 TMEM columns of lanes 0..31, replicated into every lane quarter
-__device__ __forceinline__ void tc_cp_32x128b(uint32_t taddr, uint64_t sdesc) {
-  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
-}
-
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-
-// D[tmem] (+)= A[smem desc] . B[smem desc]^T
-__device__ __forceinline__ void mma_f8_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc) : "memory");
-}
-// block-scaled: D[tmem] (+)= (A * 2^sfa)[smem desc] . (B * 2^sfb)[smem desc]^T, one UE8M0 scale per row and 32 K
-__device__ __forceinline__ void mma_mxf8_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                            uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t acc) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc), "r"(sfa_tmem), "r"(sfb_tmem) : "memory");
-}
-// D[tmem] (+)= A[tmem] . B[smem desc]^T
-__device__ __forceinline__ void mma_f8_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [%1], %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(acc) : "memory");
-}
-
-#define LBFQ_TMEM_LD32(r, addr)                                                                            \
-  asm volatile(                                                                                           \
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "                                                           \
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "                           \
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"           \
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),   \
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),         \
-        "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]),       \
-        "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]),       \
-        "=r"(r[29]), "=r"(r[30]), "=r"(r[31])                                                            \
-      : "r"(addr) : "memory")
-
-#define LBFQ_TMEM_LD16(r, addr)                                                                            \
-  asm volatile(                                                                                           \
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "                                                           \
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"                    \
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),   \
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),         \
-        "=r"(r[15])                                                                                       \
-      : "r"(addr) : "memory")
-
-template <int N>
-__device__ __forceinline__ void tmem_ld(uint32_t (&r)[N], uint32_t addr) {
-  static_assert(N == 16 || N == 32, "chunk of 16 or 32 columns");
-  if constexpr (N == 32) { LBFQ_TMEM_LD32(r, addr); } else { LBFQ_TMEM_LD16(r, addr); }
-}
-
-__device__ __forceinline__ uint32_t tmem_ld1(uint32_t addr) {
-  uint32_t v;
-  asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(v) : "r"(addr) : "memory");
-  return v;
-}
-__device__ __forceinline__ void tmem_st8(uint32_t addr, const uint32_t* r) {
-  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
-               ::"r"(addr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
-               : "memory");
-}
-
-__device__ __forceinline__ void tmem_st4(uint32_t addr, const uint32_t* r) {
-  asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};"
-               ::"r"(addr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]) : "memory");
-}
-
-__device__ __forceinline__ float ex2(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-
-// K-major shared-memory matrix descriptor (Blackwell format, version 1):
-// rows of `row_bytes` (128 -> 128B swizzle, 64 -> 64B swizzle), 8-row atoms
-// packed back to back (stride byte offset = 8 * row_bytes).
-__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, int row_bytes) {
-  const uint64_t layout = row_bytes == 128 ? 2ull : (row_bytes == 64 ? 4ull : 6ull);
-  uint64_t d = 0;
-  d |= (uint64_t)((saddr >> 4) & 0x3fffu);
-  d |= (uint64_t)1 << 16;                                  // leading byte offset: unused for swizzled K-major
-  d |= (uint64_t)(((8u * row_bytes) >> 4) & 0x3fffu) << 32;
-  d |= (uint64_t)1 << 46;                                  // descriptor version
-  d |= layout << 61;
-  return d;
-}
-// kind::f8f6f4, A = B = e4m3, FP32 accumulator, both operands K-major, M = 128.
-__host__ __device__ constexpr uint32_t make_idesc(int n) {
-  return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-}
-
-// kind::mxf8f6f4.block_scale, e4m3 x e4m3, UE8M0 scales, K-major operands, M = 128; `sf` = which byte of
-// the 32-bit scale columns (= which 32-wide K block) this instruction uses, for A and for B.
-__host__ __device__ constexpr uint32_t make_idesc_mx(int n, int sf) {
-  return ((uint32_t)sf << 4) | ((uint32_t)(n >> 3) << 17) | (1u << 23) | ((uint32_t)(128 >> 4) << 24) | ((uint32_t)sf << 29);
-}
-// 32 x 16-byte rows, contiguous (no swizzle): the source of a scale-factor copy
-__device__ __forceinline__ uint64_t make_desc_sf(uint32_t saddr) {
-  return (uint64_t)((saddr >> 4) & 0x3fffu) | ((uint64_t)1 << 16) | ((uint64_t)(128 >> 4) << 32) | ((uint64_t)1 << 46);
-}
-
-// ---------------------------------------------------------------------------
-// kernel parameters (a device-side copy of lbfq_attn_args, pre-digested)
-// ---------------------------------------------------------------------------
-struct Params {
-  int B, H, M, N, D;
-  int qk_block;
-  const float* q_scale;
-  const float* k_scale;
-  const uint8_t* q_sf;         // block-scaled Q/K: UE8M0 scale tiles
-  const uint8_t* k_sf;
-  int m_pad, n_pad;
-  int v_kind;
-  const float* v_scale;
-  int v_block;
-  float sm_scale, p_off;
-  int p_kind;
-  int block_m;
-  const float* v_alpha;        // pre-divided by the V scale it rides on (alpha')
-  int v_smooth_block;
-  const float* corr;
-  int q_smooth_block, corr_stride, n_groups;
-  int corr_staged;             // 1: every 128-row tile lies in one Q group, corr rows go through shared memory
-  int side_bytes;              // bytes of side vectors the producer stages per 128-key stage (0: none)
-  const float* rowmax_est;
-  const float* rowmax_init;
-  int rm_mode;                 // 0 online, 1 frozen estimate, 2 estimate with thresholds
-  float log_lambda, lambda;
-  int fill_kind;
-  float fill_alpha;
-  int uta_bins;
-  float* stats;
-  void* out;
-  int out_dtype, out_layout, out_exact;
-  const int64_t* out_row_index;
-  int32_t* status;
-  // element counts of the side tensors, used by the LBFQ_BOUNDS debug build to validate every index
-  long long n_v_scale, n_v_alpha, n_corr, n_qk_scale_q, n_qk_scale_k, n_out;
-};
-
-#ifdef LBFQ_BOUNDS
-#define LBFQ_CHECK_IDX(idx, count, limit, code)                                                   \
-  do {                                                                                            \
-    if ((long long)(idx) < 0 || (long long)(idx) + (long long)(count) > (long long)(limit)) {    \
-      if (p.status) atomicCAS(p.status, 0, (code));                                               \
-      return;                                                                                     \
-    }                                                                                             \
-  } while (0)
-#else
-#define LBFQ_CHECK_IDX(idx, count, limit, code) do { } while (0)
-#endif
 
 template <int D, int BN>
 struct Smem {
@@ -1001,6 +766,9 @@ __global__ void alpha_prep_kernel(const float* __restrict__ alpha, float* __rest
   }
 }
 
+static thread_local int g_last_variant = 0;
+extern "C" int lbfq_attention_last_variant(void) { return g_last_variant; }
+
 extern "C" int64_t lbfq_attention_workspace_bytes(const lbfq_attn_args* a) {
   if (!a || !a->v_alpha) return 0;
   return (int64_t)a->B * (a->N / (a->v_smooth_block > 0 ? a->v_smooth_block : 1)) * a->H * a->D * 4;
@@ -1110,6 +878,13 @@ extern "C" int lbfq_attention_fwd(const lbfq_attn_args* a, void* workspace, void
   if (int rc = make_map(&mv, a->v_codes, a->n_pad, a->D, BH, kChunk, a->D)) return rc;
 
   const bool bl = a->use_blasst != 0;
+  // LBFQ_ATTN_GENERIC=1 keeps every configuration on the general kernel (used to cross-check the two)
+  const char* force_generic = getenv("LBFQ_ATTN_GENERIC");
+  g_last_variant = 0;
+  if (!(force_generic && force_generic[0] == '1') && fast_eligible(p, a->block_n, bl, mx)) {
+    g_last_variant = 1;
+    return launch_fast(mq, mk, mv, p, a->block_n, st);
+  }
 #define LBFQ_LAUNCH(DD, NN, MX)                                                                    \
   return bl ? launch<DD, NN, true, MX>(mq, mk, mv, p, st) : launch<DD, NN, false, MX>(mq, mk, mv, p, st)
   if (mx) {

@@ -1,0 +1,391 @@
+// Streaming fake-quant attention for sm_100a, output accumulator resident in tensor memory.
+//
+// Same operator as attention.cu (`_fake_quant_attn_fwd_kernel`, src/low_bit_fake_quant/attention_triton.py:48-671),
+// specialised for the configurations in which every key block's P.V enters the output with weight one:
+// element-wise (static offset) P quantisation, V quantised per channel, no V-smoothing term, no score bias,
+// no BLASST, FP8 block scales on Q / K, row max tracked online or frozen to an estimate. There
+//
+//   O <- O * alpha + Pc . Vc                                      (attention_triton.py:362-385)
+//
+// and alpha = exp2(m_old - m_new) is exactly 1 for every row whose running max did not move, so the tensor
+// core accumulates P.V straight into one TMEM accumulator and the softmax threads touch O only in the blocks
+// where some row of their warp raised its max (TMEM -> registers -> * alpha -> TMEM), plus once at the end.
+//
+// Per 128-row tile the tensor memory holds two S buffers (64 columns each) and O (D columns). P of block j is
+// written over the first columns of S buffer j & 1 once S has been copied to registers, and Q.K^T of block
+// j + 2 is issued behind P.V of block j by the same thread: tcgen05 operations of one thread execute in
+// order, so neither the S buffer nor P needs a "free" barrier. Per key block a softmax thread waits on one
+// barrier (S ready) and arrives on one (P ready).
+//
+// The score arithmetic is contracted the way a compiler contracts the reference's expression
+// exp2((dot * f - m) * log2e + off) with f = (sq * sk) * sm_scale: the block max is taken over the raw dot
+// products (f > 0), the running max is kept in the log2 domain, and every element costs one FFMA, one exp2,
+// one add (row sum) and half a conversion.
+//
+// CTA = 256 query rows of one (b, h): 8 softmax warps (thread == row == TMEM lane), one TMA producer warp,
+// one MMA-issuing warp per tile. Every mbarrier wait is bounded; on expiry the kernel raises `*status`, all
+// roles leave their loops, TMEM is released and the launch returns.
+
+#include "attn_prims.cuh"
+
+namespace lbfq {
+namespace attn {
+
+namespace {
+
+constexpr int kFastStages = 4;
+
+template <int D>
+struct FastSmem {
+  static constexpr int kQ = kTileM * D;                       // bytes per Q tile
+  static constexpr int kK = kChunk * D;                       // bytes per K stage
+  static constexpr int kV = D * kChunk;                       // bytes per V^T stage
+  static constexpr int offQ = 0;
+  static constexpr int offK = offQ + 2 * kQ;
+  static constexpr int offV = offK + kFastStages * kK;
+  static constexpr int offBar = offV + kFastStages * kV;
+  static constexpr int kNumBar = 2 + 4 * kFastStages + 4 + 2 + 2;
+  static constexpr int offMisc = offBar + kNumBar * 8;
+  static constexpr int total = offMisc + 64;
+};
+
+template <int D, int BN>
+__global__ void __launch_bounds__(kThreads, 1)
+attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                 const __grid_constant__ CUtensorMap tm_v, const Params p) {
+  using SM = FastSmem<D>;
+  constexpr int NSUB = kChunk / BN;                // key blocks per stage
+  constexpr int TCOLS = 256;                       // TMEM columns per tile
+  constexpr int COL_S = 0, S_STRIDE = 64, COL_O = 128;
+  static_assert(BN == 32 || BN == 64, "block_n of 32 or 64");
+  static_assert(COL_O + D <= TCOLS, "TMEM budget");
+
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const uint32_t sbase = smem_u32(smem);
+  const uint32_t bar0 = sbase + SM::offBar;
+  auto BAR_QFULL = [&](int t) { return bar0 + 8u * t; };
+  auto BAR_KFULL = [&](int s) { return bar0 + 8u * (2 + s); };
+  auto BAR_VFULL = [&](int s) { return bar0 + 8u * (2 + kFastStages + s); };
+  auto BAR_KFREE = [&](int s) { return bar0 + 8u * (2 + 2 * kFastStages + s); };
+  auto BAR_VFREE = [&](int s) { return bar0 + 8u * (2 + 3 * kFastStages + s); };
+  auto BAR_SFULL = [&](int t, int buf) { return bar0 + 8u * (2 + 4 * kFastStages + 2 * t + buf); };
+  auto BAR_PRDY = [&](int t) { return bar0 + 8u * (2 + 4 * kFastStages + 4 + t); };
+  auto BAR_PVDONE = [&](int t) { return bar0 + 8u * (2 + 4 * kFastStages + 6 + t); };
+  volatile int* misc = (volatile int*)(smem + SM::offMisc);   // [0] tmem base, [1] abort, [6] early exit
+  volatile int* abort_flag = misc + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int bh = blockIdx.y;
+  const int b = bh / p.H, h = bh % p.H;
+  const int m0 = blockIdx.x * kCtaM;
+  const int nblk = (p.N + BN - 1) / BN;
+  const int nchunk = (p.N + kChunk - 1) / kChunk;
+  constexpr int kTmaWarp = kSoftmaxWarps, kMmaWarp0 = kSoftmaxWarps + 1;
+
+  // ---- setup ----------------------------------------------------------------
+  // A CTA scheduled after some other CTA has given up a wait retires at once.
+  if (threadIdx.x == 0) misc[6] = (p.status != nullptr && *reinterpret_cast<volatile int32_t*>(p.status) != 0) ? 1 : 0;
+  __syncthreads();
+  if (misc[6]) return;
+  if (threadIdx.x == 0) {
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(BAR_QFULL(t), 1);
+      mbar_init(BAR_SFULL(t, 0), 1);
+      mbar_init(BAR_SFULL(t, 1), 1);
+      mbar_init(BAR_PRDY(t), kTileM);
+      mbar_init(BAR_PVDONE(t), 1);
+    }
+    for (int s = 0; s < kFastStages; ++s) {
+      mbar_init(BAR_KFULL(s), 1);
+      mbar_init(BAR_VFULL(s), 1);
+      mbar_init(BAR_KFREE(s), 2);
+      mbar_init(BAR_VFREE(s), 2);
+    }
+    misc[1] = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == kTmaWarp) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(sbase + SM::offMisc) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = (uint32_t)misc[0];
+
+  if (warp < kSoftmaxWarps) {
+    // =========================== softmax warps ===========================
+    const int t = warp >> 2;                                   // tile
+    const int row_in_tile = (warp & 3) * 32 + lane;
+    const int row = m0 + t * kTileM + row_in_tile;             // query row within (b, h)
+    const bool row_ok = row < p.M;
+    const int rowc = row_ok ? row : (p.M - 1);
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    const uint32_t tS = tmem_base + lane_base + t * TCOLS + COL_S;
+    const uint32_t tO = tmem_base + lane_base + t * TCOLS + COL_O;
+
+    const float sq = p.q_scale[((size_t)b * (p.M / p.qk_block) + rowc / p.qk_block) * p.H + h];
+    const float qf = sq;                                       // (sq * sk) * sm_scale * log2e, in the reference's order
+    const float* ksc = p.k_scale + (size_t)b * (p.N / p.qk_block) * p.H + h;
+    const bool frozen = p.rm_mode == 1;
+    // running max in the log2 domain (the reference's m_i times log2e)
+    float m2 = -INFINITY;
+    if (p.rowmax_est) m2 = p.rowmax_est[(size_t)bh * p.M + rowc] * kLog2e;
+    else if (p.rowmax_init) m2 = p.rowmax_init[(size_t)bh * p.M + rowc] * kLog2e;
+    float l_i = 0.f;
+    float sk = ksc[0];
+
+    bool alive = true;
+    for (int it = 0; it < nblk; ++it) {
+      const int buf = it & 1;
+      // the vote keeps the warp together if a bounded wait gives up in only some of its lanes
+      if (!__all_sync(0xffffffffu, mbar_wait(BAR_SFULL(t, buf), (it >> 1) & 1, abort_flag, p.status, 12))) { alive = false; break; }
+      tc_fence_after();
+      float s[BN];
+      {
+        uint32_t r[32];
+        LBFQ_TMEM_LD32(r, tS + buf * S_STRIDE);
+        if constexpr (BN == 64) {
+          uint32_t r2[32];
+          LBFQ_TMEM_LD32(r2, tS + buf * S_STRIDE + 32);
+          tc_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) { s[i] = __uint_as_float(r[i]); s[32 + i] = __uint_as_float(r2[i]); }
+        } else {
+          tc_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) s[i] = __uint_as_float(r[i]);
+        }
+      }
+      const int n0 = it * BN;
+      const float c = ((qf * sk) * p.sm_scale) * kLog2e;
+      if (it + 1 < nblk) sk = ksc[(size_t)((n0 + BN) / p.qk_block) * p.H];   // next block's scale, off the critical path
+      const int nvalid = p.N - n0;
+      if (nvalid < BN) {                    // ragged tail: only the last block of a sequence
+#pragma unroll
+        for (int i = 0; i < BN; ++i) if (i >= nvalid) s[i] = -INFINITY;
+      }
+      float bm0 = s[0], bm1 = s[1], bm2 = s[2], bm3 = s[3];
+#pragma unroll
+      for (int i = 4; i < BN; i += 4) {
+        bm0 = fmaxf(bm0, s[i]); bm1 = fmaxf(bm1, s[i + 1]); bm2 = fmaxf(bm2, s[i + 2]); bm3 = fmaxf(bm3, s[i + 3]);
+      }
+      const float bmax = fmaxf(fmaxf(bm0, bm1), fmaxf(bm2, bm3)) * c;
+
+      // ---- running max / rescale factor (attention_triton.py:164-217) ----------
+      const float m_new = frozen ? m2 : fmaxf(m2, bmax);
+      const float alpha = frozen ? 1.f : ex2(m2 - m_new);
+      // P.V of the previous block is observed in every block (it completed long ago: it was issued before this
+      // block's S was read), so that this barrier's phases are never skipped and its parity stays unambiguous
+      if (it > 0 && !__all_sync(0xffffffffu, mbar_wait(BAR_PVDONE(t), (it - 1) & 1, abort_flag, p.status, 11))) { alive = false; break; }
+      if (it > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+        // some row of this warp raised its max: rescale the warp's 32 accumulator rows in place
+        tc_fence_after();
+#pragma unroll
+        for (int c0 = 0; c0 < D; c0 += 32) {
+          uint32_t r[32];
+          LBFQ_TMEM_LD32(r, tO + c0);
+          tc_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+          LBFQ_TMEM_ST32(tO + c0, r);
+        }
+      }
+
+      // ---- P = exp2(dot * c - m + off), l += sum(P) (attention_triton.py:219-326) ----
+      // masked columns hold -inf, so their exp2 is exactly 0 without a select
+      const float bias = p.p_off - m_new;
+      float ps0 = 0.f, ps1 = 0.f, ps2 = 0.f, ps3 = 0.f;
+      uint32_t pk[BN / 4];
+#pragma unroll
+      for (int i = 0; i < BN; i += 4) {
+        const float p0 = ex2(fmaf(s[i], c, bias));
+        const float p1 = ex2(fmaf(s[i + 1], c, bias));
+        const float p2 = ex2(fmaf(s[i + 2], c, bias));
+        const float p3 = ex2(fmaf(s[i + 3], c, bias));
+        ps0 += p0; ps1 += p1; ps2 += p2; ps3 += p3;
+        // the conversion saturates at 448, which is the reference's clamp (attention_triton.py:328-336)
+        pk[i / 4] = (uint32_t)f32x2_to_e4m3x2(p0, p1) | ((uint32_t)f32x2_to_e4m3x2(p2, p3) << 16);
+      }
+      l_i = l_i * alpha + ((ps0 + ps1) + (ps2 + ps3));
+      tmem_st8(tS + buf * S_STRIDE, pk);
+      if constexpr (BN == 64) tmem_st8(tS + buf * S_STRIDE + 8, pk + 8);
+      tc_wait_st();
+      tc_fence_before();
+      mbar_arrive(BAR_PRDY(t));
+      m2 = m_new;
+    }
+
+    // ---- epilogue (attention_triton.py:387-407) ---------------------------------
+    if (alive) alive = __all_sync(0xffffffffu, mbar_wait(BAR_PVDONE(t), (nblk - 1) & 1, abort_flag, p.status, 13));
+    if (alive) {
+      tc_fence_after();
+      const float inv_l = __fdiv_rn(1.0f, l_i);
+      const bool has_vsc = p.v_kind == LBFQ_V_CHANNEL;
+      const float* vsc = has_vsc ? p.v_scale + (size_t)bh * D : p.v_scale;
+      int64_t drow = rowc;
+      if (p.out_row_index != nullptr) drow = p.out_row_index[(size_t)bh * p.M + rowc];
+      const size_t o_off = p.out_layout == LBFQ_LAYOUT_NHD
+                               ? (((size_t)b * p.M + drow) * p.H + h) * D
+                               : ((size_t)bh * p.M + drow) * D;
+#pragma unroll
+      for (int c0 = 0; c0 < D; c0 += 32) {
+        uint32_t r[32];
+        float a[32];
+        LBFQ_TMEM_LD32(r, tO + c0);             // warp-collective: rows past M take part and store nothing
+        tc_wait_ld();
+        if (has_vsc) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) a[i] = (__uint_as_float(r[i]) * vsc[c0 + i]) * inv_l;
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) a[i] = __uint_as_float(r[i]) * inv_l;
+        }
+        if (!row_ok) {
+          // rows past M only took part in the collective load
+        } else if (p.out_dtype == LBFQ_F32) {
+          float4* o = reinterpret_cast<float4*>((float*)p.out + o_off + c0);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            float4 v = make_float4(a[4 * i], a[4 * i + 1], a[4 * i + 2], a[4 * i + 3]);
+            if (!p.out_exact) {
+              v.x = round_through<__nv_bfloat16>(v.x); v.y = round_through<__nv_bfloat16>(v.y);
+              v.z = round_through<__nv_bfloat16>(v.z); v.w = round_through<__nv_bfloat16>(v.w);
+            }
+            o[i] = v;
+          }
+        } else {
+          uint4* o = reinterpret_cast<uint4*>((uint16_t*)p.out + o_off + c0);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint32_t w[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float x0 = a[8 * i + 2 * j], x1 = a[8 * i + 2 * j + 1];
+              if (p.out_dtype == LBFQ_BF16) {
+                __nv_bfloat162 hh = __floats2bfloat162_rn(x0, x1);
+                w[j] = *reinterpret_cast<uint32_t*>(&hh);
+              } else {                                           // the kernel result is BF16; then .to(float16)
+                __half2 hh = __floats2half2_rn(round_through<__nv_bfloat16>(x0), round_through<__nv_bfloat16>(x1));
+                w[j] = *reinterpret_cast<uint32_t*>(&hh);
+              }
+            }
+            o[i] = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        }
+      }
+    }
+  } else if (warp == kTmaWarp) {
+    // =========================== TMA producer =====================================
+    if (lane == 0) {
+      for (int t = 0; t < 2; ++t) {
+        mbar_expect_tx(BAR_QFULL(t), SM::kQ);
+        tma_load_3d(sbase + SM::offQ + t * SM::kQ, &tm_q, 0, m0 + t * kTileM, bh, BAR_QFULL(t));
+      }
+      for (int c = 0; c < nchunk; ++c) {
+        const int st = c % kFastStages;
+        if (c >= kFastStages) {
+          const uint32_t par = ((c / kFastStages) - 1) & 1;
+          if (!mbar_wait(BAR_KFREE(st), par, abort_flag, p.status, 21)) break;
+        }
+        mbar_expect_tx(BAR_KFULL(st), SM::kK);
+        tma_load_3d(sbase + SM::offK + st * SM::kK, &tm_k, 0, c * kChunk, bh, BAR_KFULL(st));
+        if (c >= kFastStages) {
+          const uint32_t par = ((c / kFastStages) - 1) & 1;
+          if (!mbar_wait(BAR_VFREE(st), par, abort_flag, p.status, 22)) break;
+        }
+        mbar_expect_tx(BAR_VFULL(st), SM::kV);
+        tma_load_3d(sbase + SM::offV + st * SM::kV, &tm_v, c * kChunk, 0, bh, BAR_VFULL(st));
+      }
+    }
+  } else if (warp == kMmaWarp0 || warp == kMmaWarp0 + 1) {
+    // =========================== MMA issuer of tile t ==============================
+    const int t = warp - kMmaWarp0;
+    if (lane == 0) {
+      const uint32_t tS = tmem_base + t * TCOLS + COL_S;
+      const uint32_t tO = tmem_base + t * TCOLS + COL_O;
+      const uint32_t id_qk = make_idesc(BN);
+      const uint32_t id_pv = make_idesc(D);
+      const uint64_t dq = make_desc(sbase + SM::offQ + t * SM::kQ, D);
+      bool ok = mbar_wait(BAR_QFULL(t), 0, abort_flag, p.status, 31);
+      auto issue_qk = [&](int j) -> bool {
+        const int c = j / NSUB, sub = j % NSUB, st = c % kFastStages;
+        if (sub == 0 && !mbar_wait(BAR_KFULL(st), (c / kFastStages) & 1, abort_flag, p.status, 32)) return false;
+        tc_fence_after();
+        const uint64_t dk = make_desc(sbase + SM::offK + st * SM::kK + sub * BN * D, D);
+#pragma unroll
+        for (int kk = 0; kk < D / 32; ++kk)
+          mma_f8_ss(tS + (j & 1) * S_STRIDE, dq + (uint64_t)(kk * 2), dk + (uint64_t)(kk * 2), id_qk, kk > 0 ? 1u : 0u);
+        tc_commit(BAR_SFULL(t, j & 1));
+        if (sub == NSUB - 1 || j == nblk - 1) tc_commit(BAR_KFREE(st));
+        return true;
+      };
+      auto issue_pv = [&](int j) -> bool {
+        const int c = j / NSUB, sub = j % NSUB, st = c % kFastStages;
+        if (sub == 0 && !mbar_wait(BAR_VFULL(st), (c / kFastStages) & 1, abort_flag, p.status, 33)) return false;
+        tc_fence_after();
+        const uint64_t dv = make_desc(sbase + SM::offV + st * SM::kV, kChunk);
+#pragma unroll
+        for (int kk = 0; kk < BN / 32; ++kk)
+          mma_f8_ts(tO, tS + (j & 1) * S_STRIDE + kk * 8, dv + (uint64_t)((sub * BN + kk * 32) >> 4), id_pv,
+                    (j > 0 || kk > 0) ? 1u : 0u);
+        tc_commit(BAR_PVDONE(t));
+        if (sub == NSUB - 1 || j == nblk - 1) tc_commit(BAR_VFREE(st));
+        return true;
+      };
+      if (ok) ok = issue_qk(0);
+      if (ok && nblk > 1) ok = issue_qk(1);
+      for (int it = 0; it < nblk && ok; ++it) {
+        // P.V of this block once its P is in TMEM (and the rows that raised their max are rescaled), then
+        // Q.K^T of block it + 2 into the S buffer that P has just been read from
+        ok = mbar_wait(BAR_PRDY(t), it & 1, abort_flag, p.status, 35);
+        if (ok) ok = issue_pv(it);
+        if (ok && it + 2 < nblk) ok = issue_qk(it + 2);
+      }
+    }
+  }
+
+  // ---- teardown -------------------------------------------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (warp == kTmaWarp) {
+    if (*abort_flag && lane == 0) {
+      // give in-flight bulk copies a bounded time to land before the CTA retires
+      const unsigned long long t0 = clock64();
+      while (clock64() - t0 < 2000000ull) { }
+    }
+    __syncwarp();
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem_base) : "memory");
+  }
+}
+
+template <int D, int BN>
+int launch_fast_t(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const Params& p, cudaStream_t st) {
+  using SM = FastSmem<D>;
+  const int smem_bytes = SM::total + 1024;
+  auto kern = attn_fast_kernel<D, BN>;
+  LBFQ_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+  dim3 grid((p.M + kCtaM - 1) / kCtaM, p.B * p.H, 1);
+  kern<<<grid, kThreads, smem_bytes, st>>>(mq, mk, mv, p);
+  return check_launch("attn_fast_kernel");
+}
+
+}  // namespace
+
+bool fast_eligible(const Params& p, int block_n, bool blasst, bool qk_mx) {
+  (void)block_n;
+  return !blasst && !qk_mx && p.q_scale != nullptr && p.k_scale != nullptr && p.p_kind == LBFQ_P_ELEMENTWISE &&
+         p.v_kind == LBFQ_V_CHANNEL && p.v_alpha == nullptr && p.corr == nullptr && (p.rm_mode == 0 || p.rm_mode == 1) &&
+         p.sm_scale > 0.f;
+}
+
+int launch_fast(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const Params& p, int block_n,
+                cudaStream_t st) {
+  if (p.D == 128) return block_n == 64 ? launch_fast_t<128, 64>(mq, mk, mv, p, st) : launch_fast_t<128, 32>(mq, mk, mv, p, st);
+  return block_n == 64 ? launch_fast_t<64, 64>(mq, mk, mv, p, st) : launch_fast_t<64, 32>(mq, mk, mv, p, st);
+}
+
+}  // namespace attn
+}  // namespace lbfq

@@ -70,6 +70,7 @@ _SIGS = {
     "lbfq_last_error": (C.c_char_p, []),
     "lbfq_abi_version": (_I, []),
     "lbfq_launch_count": (C.c_ulonglong, []),
+    "lbfq_attention_last_variant": (_I, []),
     "lbfq_fp8_block_quant": (_I, [_P, _I, _I, _I, _I, _I, _I, _P, _I, _I, _P, _P]),
     "lbfq_fp8_block_dequant": (_I, [_P, _P, _I, _I, _I, _I, _I, _P, _I, _P]),
     "lbfq_fp8_channel_quant": (_I, [_P, _I, _I, _I, _I, _I, _P, _I, _I, _P, _P]),

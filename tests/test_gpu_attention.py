@@ -233,6 +233,80 @@ def test_gap_to_reference_convention():
     assert OA.compute_metrics(g, faithful)["cosine"] > 0.9995
 
 
+# --- the kernel variant whose output accumulator stays in tensor memory ---------------------------------
+
+def _variant():
+    from low_bit_fake_quant import _lib as L
+    return L.lib().lbfq_attention_last_variant()
+
+
+def _fast_and_general(q, k, v, cfg, monkeypatch):
+    monkeypatch.delenv("LBFQ_ATTN_GENERIC", raising=False)
+    fast = fq.fake_quant_attention(q.to(DEV), k.to(DEV), v.to(DEV), cfg, _debug_fp32=True).float().cpu()
+    assert _variant() == 1
+    monkeypatch.setenv("LBFQ_ATTN_GENERIC", "1")
+    gen = fq.fake_quant_attention(q.to(DEV), k.to(DEV), v.to(DEV), cfg, _debug_fp32=True).float().cpu()
+    assert _variant() == 0
+    raise_if_device_error(torch.device(DEV))
+    return fast, gen
+
+
+@pytest.mark.parametrize("S,D,bn,extra", [
+    (1984, 128, 64, {}),                                   # 31 key blocks: ragged last 128-key stage, 8 row tiles
+    (2048, 64, 64, dict(smoothing="off")),
+    (960, 128, 32, {}),
+    (1024, 64, 32, dict(p_max_offset=0)),
+    (4096, 128, 64, dict(fp8_block_size=128)),             # more key blocks than pipeline stages several times over
+])
+def test_tmem_resident_variant_matches_oracle_and_general_kernel(S, D, bn, extra, monkeypatch):
+    kw = {**COMMON, **dict(smoothing="k_only", q_kmeans_k=None, p_requant_block_m=bn, p_requant_block_n=bn), **extra}
+    cfg = QuantConfig(**kw)
+    q, k, v = _qkv(2, S, 3, D, seed=S + D + bn)
+    fast, gen = _fast_and_general(q, k, v, cfg, monkeypatch)
+    o = OA.fake_quant_attention(q, k, v, cfg, faithful=False, out_fp32=True)
+    _check(fast, o, (q, k, v))
+    _check(gen, o, (q, k, v))
+    assert OA.parity_ok(OA.parity_report(fast, gen, q, k, v))
+
+
+def test_tmem_resident_variant_with_peaked_rows(monkeypatch):
+    """Rows whose max keeps rising through the sweep (keys sorted by growing alignment with the queries): the
+    accumulator is rescaled in tensor memory in most key blocks."""
+    torch.manual_seed(4)
+    B, S, H, D = 1, 1024, 2, 128
+    u = torch.randn(D)
+    u = u / u.norm()
+    q = (3.0 * u.view(1, 1, 1, D) + 0.3 * torch.randn(B, S, H, D)).bfloat16()
+    ramp = torch.linspace(0.0, 6.0, S).view(1, S, 1, 1)
+    k = (ramp * u.view(1, 1, 1, D) + 0.3 * torch.randn(B, S, H, D)).bfloat16()
+    v = torch.randn(B, S, H, D).bfloat16()
+    cfg = QuantConfig(**COMMON, smoothing="off", q_kmeans_k=None)
+    fast, gen = _fast_and_general(q, k, v, cfg, monkeypatch)
+    o = OA.fake_quant_attention(q, k, v, cfg, faithful=False, out_fp32=True)
+    _check(fast, o, (q, k, v))
+    assert OA.parity_ok(OA.parity_report(fast, gen, q, k, v))
+
+
+@pytest.mark.parametrize("mode", ["rowmax_init_bhs", "rowmax_est_bhs"])
+def test_tmem_resident_variant_row_max_seeds(mode, monkeypatch):
+    """A seeded running max (`rowmax_init_bhs`) and a frozen one (`rowmax_est_bhs` with element-wise P) give the
+    same result in both kernels; the general kernel is the one checked against the oracle for these modes."""
+    import low_bit_fake_quant.attention as A
+    q, k, v = _qkv(1, 768, 2, 128, seed=17)
+    cfg = QuantConfig(**COMMON, smoothing="k_only", q_kmeans_k=None)
+    seed_rows = torch.full((1, 2, 768), 12.0, device=DEV)         # above every score of these inputs
+    inner = A.fake_quant_attention_fp8
+
+    def seeded(*a, **kw):
+        kw[mode] = seed_rows
+        return inner(*a, **kw)
+
+    monkeypatch.setattr(A, "fake_quant_attention_fp8", seeded)
+    fast, gen = _fast_and_general(q, k, v, cfg, monkeypatch)
+    assert torch.isfinite(fast).all() and fast.abs().max() > 0
+    assert OA.parity_ok(OA.parity_report(fast, gen, q, k, v))
+
+
 def test_mxfp8_qk_needs_block_n_64():
     x = torch.zeros(1, 128, 1, 128, dtype=torch.bfloat16, device=DEV)
     with pytest.raises(NotImplementedError, match="block_n = 64"):
