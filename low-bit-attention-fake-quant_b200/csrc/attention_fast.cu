@@ -22,8 +22,8 @@
 // products (f > 0), the running max is kept in the log2 domain, and every element costs one FFMA, one exp2,
 // one add (row sum) and half a conversion.
 //
-// CTA = 256 query rows of one (b, h): 8 softmax warps (thread == row == TMEM lane), one TMA producer warp,
-// one MMA-issuing warp per tile. Every mbarrier wait is bounded; on expiry the kernel raises `*status`, all
+// CTA = 256 query rows of one (b, h): 16 softmax warps (two threads per row, TMEM lane == row), one TMA
+// producer warp, one MMA-issuing warp per tile. Every mbarrier wait is bounded; on expiry the kernel raises `*status`, all
 // roles leave their loops, TMEM is released and the launch returns.
 
 #include "attn_prims.cuh"
@@ -34,6 +34,18 @@ namespace attn {
 namespace {
 
 constexpr int kFastStages = 4;
+// Two threads per query row: the pair reads the same S block, both take its maximum (so they never have to
+// talk to each other), and each computes the exponentials, the P codes and the accumulator rescale of one
+// half of the columns. 16 softmax warps give every scheduler four of them to hide each other's waits.
+constexpr int kFastSoftmaxWarps = 16;
+constexpr int kFastThreads = (kFastSoftmaxWarps + 4) * 32;
+constexpr int kFastRegsLaunch = (65536 / kFastThreads) / 8 * 8;   // what __launch_bounds__(kFastThreads, 1) yields
+constexpr int kFastRegsSoftmax = 104;
+constexpr int kFastRegsService = 40;
+// `setmaxnreg.inc` blocks until the CTA's register pool can satisfy it: the requests must fit in the pool
+static_assert(kFastSoftmaxWarps * 32 * kFastRegsSoftmax + 4 * 32 * kFastRegsService <= kFastThreads * kFastRegsLaunch,
+              "setmaxnreg requests exceed the CTA's register pool");
+static_assert(kFastRegsSoftmax % 8 == 0 && kFastRegsService % 8 == 0, "setmaxnreg granularity");
 
 template <int D>
 struct FastSmem {
@@ -46,11 +58,12 @@ struct FastSmem {
   static constexpr int offBar = offV + kFastStages * kV;
   static constexpr int kNumBar = 2 + 4 * kFastStages + 4 + 2 + 2;
   static constexpr int offMisc = offBar + kNumBar * 8;
-  static constexpr int total = offMisc + 64;
+  static constexpr int offL = offMisc + 64;                    // row sums of the two column halves [tile][half][row]
+  static constexpr int total = offL + 2 * 2 * kTileM * 4;
 };
 
 template <int D, int BN>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kFastThreads, 1)
 attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                  const __grid_constant__ CUtensorMap tm_v, const Params p) {
   using SM = FastSmem<D>;
@@ -81,7 +94,9 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   const int m0 = blockIdx.x * kCtaM;
   const int nblk = (p.N + BN - 1) / BN;
   const int nchunk = (p.N + kChunk - 1) / kChunk;
-  constexpr int kTmaWarp = kSoftmaxWarps, kMmaWarp0 = kSoftmaxWarps + 1;
+  constexpr int kTmaWarp = kFastSoftmaxWarps, kMmaWarp0 = kFastSoftmaxWarps + 1;
+  constexpr int HB = BN / 2;                       // S columns whose P one thread produces
+  constexpr int HD = D / 2;                        // accumulator columns one thread rescales and stores
 
   // ---- setup ----------------------------------------------------------------
   // A CTA scheduled after some other CTA has given up a wait retires at once.
@@ -93,7 +108,7 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       mbar_init(BAR_QFULL(t), 1);
       mbar_init(BAR_SFULL(t, 0), 1);
       mbar_init(BAR_SFULL(t, 1), 1);
-      mbar_init(BAR_PRDY(t), kTileM);
+      mbar_init(BAR_PRDY(t), 2 * kTileM);
       mbar_init(BAR_PVDONE(t), 1);
     }
     for (int s = 0; s < kFastStages; ++s) {
@@ -114,123 +129,136 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   tc_fence_after();
   const uint32_t tmem_base = (uint32_t)misc[0];
 
-  if (warp < kSoftmaxWarps) {
+  if (warp < kFastSoftmaxWarps) {
     // =========================== softmax warps ===========================
-    const int t = warp >> 2;                                   // tile
-    const int row_in_tile = (warp & 3) * 32 + lane;
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kFastRegsSoftmax));
+    const int t = warp >> 3;                                   // tile
+    const int half = (warp >> 2) & 1;                          // which half of the columns this thread produces
+    const int row_in_tile = (warp & 3) * 32 + lane;            // a warp reaches the TMEM lanes of its id mod 4
     const int row = m0 + t * kTileM + row_in_tile;             // query row within (b, h)
     const bool row_ok = row < p.M;
     const int rowc = row_ok ? row : (p.M - 1);
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     const uint32_t tS = tmem_base + lane_base + t * TCOLS + COL_S;
-    const uint32_t tO = tmem_base + lane_base + t * TCOLS + COL_O;
+    const uint32_t tO = tmem_base + lane_base + t * TCOLS + COL_O + half * HD;
 
     const float sq = p.q_scale[((size_t)b * (p.M / p.qk_block) + rowc / p.qk_block) * p.H + h];
-    const float qf = sq;                                       // (sq * sk) * sm_scale * log2e, in the reference's order
     const float* ksc = p.k_scale + (size_t)b * (p.N / p.qk_block) * p.H + h;
     const bool frozen = p.rm_mode == 1;
     // running max in the log2 domain (the reference's m_i times log2e)
     float m2 = -INFINITY;
     if (p.rowmax_est) m2 = p.rowmax_est[(size_t)bh * p.M + rowc] * kLog2e;
     else if (p.rowmax_init) m2 = p.rowmax_init[(size_t)bh * p.M + rowc] * kLog2e;
-    float l_i = 0.f;
+    float l_i = 0.f;                                           // row sum over this thread's columns
     float sk = ksc[0];
+    const int blocks_per_scale = p.qk_block / BN;               // fp8_block_size is a multiple of block_n
+    int scale_sub = 0;
+    const uint32_t bar_sfull = BAR_SFULL(t, 0), bar_pvdone = BAR_PVDONE(t), bar_prdy = BAR_PRDY(t);
 
     bool alive = true;
     for (int it = 0; it < nblk; ++it) {
       const int buf = it & 1;
-      // the vote keeps the warp together if a bounded wait gives up in only some of its lanes
-      if (!__all_sync(0xffffffffu, mbar_wait(BAR_SFULL(t, buf), (it >> 1) & 1, abort_flag, p.status, 12))) { alive = false; break; }
+      // the votes keep the warp together if a bounded wait gives up in only some of its lanes
+      if (!__all_sync(0xffffffffu, mbar_wait(bar_sfull + 8u * buf, (it >> 1) & 1, abort_flag, p.status, 12))) { alive = false; break; }
       tc_fence_after();
-      float s[BN];
-      {
-        uint32_t r[32];
-        LBFQ_TMEM_LD32(r, tS + buf * S_STRIDE);
-        if constexpr (BN == 64) {
-          uint32_t r2[32];
-          LBFQ_TMEM_LD32(r2, tS + buf * S_STRIDE + 32);
-          tc_wait_ld();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) { s[i] = __uint_as_float(r[i]); s[32 + i] = __uint_as_float(r2[i]); }
-        } else {
-          tc_wait_ld();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) s[i] = __uint_as_float(r[i]);
-        }
-      }
+      uint32_t mine[HB], oth[HB];
+      tmem_ld(mine, tS + buf * S_STRIDE + half * HB);
+      tmem_ld(oth, tS + buf * S_STRIDE + (1 - half) * HB);
+      tc_wait_ld();
       const int n0 = it * BN;
-      const float c = ((qf * sk) * p.sm_scale) * kLog2e;
-      if (it + 1 < nblk) sk = ksc[(size_t)((n0 + BN) / p.qk_block) * p.H];   // next block's scale, off the critical path
+      // (sq * sk) * sm_scale in the reference's order, then into the log2 domain
+      const float c = ((sq * sk) * p.sm_scale) * kLog2e;
+      if (++scale_sub == blocks_per_scale) {   // next block's scale, off the critical path (K is padded: in bounds)
+        scale_sub = 0;
+        ksc += p.H;
+        if (it + 1 < nblk) sk = *ksc;
+      }
       const int nvalid = p.N - n0;
       if (nvalid < BN) {                    // ragged tail: only the last block of a sequence
 #pragma unroll
-        for (int i = 0; i < BN; ++i) if (i >= nvalid) s[i] = -INFINITY;
+        for (int i = 0; i < HB; ++i) {
+          if (half * HB + i >= nvalid) mine[i] = 0xff800000u;
+          if ((1 - half) * HB + i >= nvalid) oth[i] = 0xff800000u;
+        }
       }
-      float bm0 = s[0], bm1 = s[1], bm2 = s[2], bm3 = s[3];
+      float bm0 = fmaxf(__uint_as_float(mine[0]), __uint_as_float(oth[0]));
+      float bm1 = fmaxf(__uint_as_float(mine[1]), __uint_as_float(oth[1]));
 #pragma unroll
-      for (int i = 4; i < BN; i += 4) {
-        bm0 = fmaxf(bm0, s[i]); bm1 = fmaxf(bm1, s[i + 1]); bm2 = fmaxf(bm2, s[i + 2]); bm3 = fmaxf(bm3, s[i + 3]);
+      for (int i = 2; i < HB; i += 2) {
+        bm0 = fmaxf(bm0, fmaxf(__uint_as_float(mine[i]), __uint_as_float(oth[i])));
+        bm1 = fmaxf(bm1, fmaxf(__uint_as_float(mine[i + 1]), __uint_as_float(oth[i + 1])));
       }
-      const float bmax = fmaxf(fmaxf(bm0, bm1), fmaxf(bm2, bm3)) * c;
+      const float bmax = fmaxf(bm0, bm1) * c;
 
       // ---- running max / rescale factor (attention_triton.py:164-217) ----------
       const float m_new = frozen ? m2 : fmaxf(m2, bmax);
       const float alpha = frozen ? 1.f : ex2(m2 - m_new);
-      // P.V of the previous block is observed in every block (it completed long ago: it was issued before this
-      // block's S was read), so that this barrier's phases are never skipped and its parity stays unambiguous
-      if (it > 0 && !__all_sync(0xffffffffu, mbar_wait(BAR_PVDONE(t), (it - 1) & 1, abort_flag, p.status, 11))) { alive = false; break; }
-      if (it > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
-        // some row of this warp raised its max: rescale the warp's 32 accumulator rows in place
-        tc_fence_after();
-#pragma unroll
-        for (int c0 = 0; c0 < D; c0 += 32) {
-          uint32_t r[32];
-          LBFQ_TMEM_LD32(r, tO + c0);
-          tc_wait_ld();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-          LBFQ_TMEM_ST32(tO + c0, r);
-        }
-      }
-
       // ---- P = exp2(dot * c - m + off), l += sum(P) (attention_triton.py:219-326) ----
       // masked columns hold -inf, so their exp2 is exactly 0 without a select
       const float bias = p.p_off - m_new;
-      float ps0 = 0.f, ps1 = 0.f, ps2 = 0.f, ps3 = 0.f;
-      uint32_t pk[BN / 4];
+      // two columns per instruction: fma.rn.f32x2 / add.rn.f32x2 round each half exactly like the scalar forms
+      const float2 c2 = make_float2(c, c), bias2 = make_float2(bias, bias);
+      float2 psa = make_float2(0.f, 0.f), psb = make_float2(0.f, 0.f);
+      uint32_t pk[HB / 4];
 #pragma unroll
-      for (int i = 0; i < BN; i += 4) {
-        const float p0 = ex2(fmaf(s[i], c, bias));
-        const float p1 = ex2(fmaf(s[i + 1], c, bias));
-        const float p2 = ex2(fmaf(s[i + 2], c, bias));
-        const float p3 = ex2(fmaf(s[i + 3], c, bias));
-        ps0 += p0; ps1 += p1; ps2 += p2; ps3 += p3;
+      for (int i = 0; i < HB; i += 4) {
+        const float2 za = __ffma2_rn(make_float2(__uint_as_float(mine[i]), __uint_as_float(mine[i + 1])), c2, bias2);
+        const float2 zb = __ffma2_rn(make_float2(__uint_as_float(mine[i + 2]), __uint_as_float(mine[i + 3])), c2, bias2);
+        const float2 pa = make_float2(ex2(za.x), ex2(za.y));
+        const float2 pb = make_float2(ex2(zb.x), ex2(zb.y));
+        psa = __fadd2_rn(psa, pa);
+        psb = __fadd2_rn(psb, pb);
         // the conversion saturates at 448, which is the reference's clamp (attention_triton.py:328-336)
-        pk[i / 4] = (uint32_t)f32x2_to_e4m3x2(p0, p1) | ((uint32_t)f32x2_to_e4m3x2(p2, p3) << 16);
+        pk[i / 4] = (uint32_t)f32x2_to_e4m3x2(pa.x, pa.y) | ((uint32_t)f32x2_to_e4m3x2(pb.x, pb.y) << 16);
       }
-      l_i = l_i * alpha + ((ps0 + ps1) + (ps2 + ps3));
-      tmem_st8(tS + buf * S_STRIDE, pk);
-      if constexpr (BN == 64) tmem_st8(tS + buf * S_STRIDE + 8, pk + 8);
+      l_i = l_i * alpha + ((psa.x + psa.y) + (psb.x + psb.y));
+      // P.V of the previous block is observed in every block (it was issued a whole block's exponentials ago),
+      // so that this barrier's phases are never skipped and its parity stays unambiguous
+      if (it > 0 && !__all_sync(0xffffffffu, mbar_wait(bar_pvdone, (it - 1) & 1, abort_flag, p.status, 11))) { alive = false; break; }
+      if (it > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+        // some row of this warp raised its max: rescale this warp's half of the 32 accumulator rows in place
+        tc_fence_after();
+#pragma unroll
+        for (int c0 = 0; c0 < HD; c0 += 32) {
+          uint32_t r[32];
+          LBFQ_TMEM_LD32(r, tO + c0);
+          tc_wait_ld();
+          const float2 a2 = make_float2(alpha, alpha);
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const float2 v = __fmul2_rn(make_float2(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), a2);
+            r[i] = __float_as_uint(v.x); r[i + 1] = __float_as_uint(v.y);
+          }
+          LBFQ_TMEM_ST32(tO + c0, r);
+        }
+      }
+      if constexpr (BN == 64) tmem_st8(tS + buf * S_STRIDE + half * (HB / 4), pk);
+      else tmem_st4(tS + buf * S_STRIDE + half * (HB / 4), pk);
       tc_wait_st();
       tc_fence_before();
-      mbar_arrive(BAR_PRDY(t));
+      mbar_arrive(bar_prdy);
       m2 = m_new;
     }
 
     // ---- epilogue (attention_triton.py:387-407) ---------------------------------
-    if (alive) alive = __all_sync(0xffffffffu, mbar_wait(BAR_PVDONE(t), (nblk - 1) & 1, abort_flag, p.status, 13));
-    if (alive) {
+    if (alive) alive = __all_sync(0xffffffffu, mbar_wait(bar_pvdone, (nblk - 1) & 1, abort_flag, p.status, 13));
+    // the row sum is the sum of the two column halves; every softmax thread takes part in the barrier, also
+    // after a wait was given up
+    float* lsum = reinterpret_cast<float*>(smem + SM::offL);
+    lsum[(t * 2 + half) * kTileM + row_in_tile] = l_i;
+    asm volatile("bar.sync 1, %0;" ::"n"(kFastSoftmaxWarps * 32) : "memory");
+    if (alive && *abort_flag == 0) {
       tc_fence_after();
-      const float inv_l = __fdiv_rn(1.0f, l_i);
+      const float inv_l = __fdiv_rn(1.0f, lsum[(t * 2) * kTileM + row_in_tile] + lsum[(t * 2 + 1) * kTileM + row_in_tile]);
       const bool has_vsc = p.v_kind == LBFQ_V_CHANNEL;
-      const float* vsc = has_vsc ? p.v_scale + (size_t)bh * D : p.v_scale;
+      const float* vsc = (has_vsc ? p.v_scale + (size_t)bh * D : p.v_scale) + half * HD;
       int64_t drow = rowc;
       if (p.out_row_index != nullptr) drow = p.out_row_index[(size_t)bh * p.M + rowc];
-      const size_t o_off = p.out_layout == LBFQ_LAYOUT_NHD
+      const size_t o_off = (p.out_layout == LBFQ_LAYOUT_NHD
                                ? (((size_t)b * p.M + drow) * p.H + h) * D
-                               : ((size_t)bh * p.M + drow) * D;
+                               : ((size_t)bh * p.M + drow) * D) + half * HD;
 #pragma unroll
-      for (int c0 = 0; c0 < D; c0 += 32) {
+      for (int c0 = 0; c0 < HD; c0 += 32) {
         uint32_t r[32];
         float a[32];
         LBFQ_TMEM_LD32(r, tO + c0);             // warp-collective: rows past M take part and store nothing
@@ -276,7 +304,10 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         }
       }
     }
-  } else if (warp == kTmaWarp) {
+  } else {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kFastRegsService));
+  }
+  if (warp == kTmaWarp) {
     // =========================== TMA producer =====================================
     if (lane == 0) {
       for (int t = 0; t < 2; ++t) {
@@ -368,7 +399,7 @@ int launch_fast_t(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMa
   auto kern = attn_fast_kernel<D, BN>;
   LBFQ_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
   dim3 grid((p.M + kCtaM - 1) / kCtaM, p.B * p.H, 1);
-  kern<<<grid, kThreads, smem_bytes, st>>>(mq, mk, mv, p);
+  kern<<<grid, kFastThreads, smem_bytes, st>>>(mq, mk, mv, p);
   return check_launch("attn_fast_kernel");
 }
 
