@@ -56,7 +56,7 @@ struct FastSmem {
   static constexpr int offK = offQ + 2 * kQ;
   static constexpr int offV = offK + kFastStages * kK;
   static constexpr int offBar = offV + kFastStages * kV;
-  static constexpr int kNumBar = 2 + 4 * kFastStages + 4 + 2 + 2;
+  static constexpr int kNumBar = 2 + 4 * kFastStages + 4 + 2 + 2 + 2;
   static constexpr int offMisc = offBar + kNumBar * 8;
   static constexpr int offL = offMisc + 64;                    // row sums of the two column halves [tile][half][row]
   static constexpr int total = offL + 2 * 2 * kTileM * 4;
@@ -84,7 +84,8 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   auto BAR_VFREE = [&](int s) { return bar0 + 8u * (2 + 3 * kFastStages + s); };
   auto BAR_SFULL = [&](int t, int buf) { return bar0 + 8u * (2 + 4 * kFastStages + 2 * t + buf); };
   auto BAR_PRDY = [&](int t) { return bar0 + 8u * (2 + 4 * kFastStages + 4 + t); };
-  auto BAR_PVDONE = [&](int t) { return bar0 + 8u * (2 + 4 * kFastStages + 6 + t); };
+  auto BAR_PENULT = [&](int t) { return bar0 + 8u * (2 + 4 * kFastStages + 6 + t); };   // P.V of block nblk - 2 done
+  auto BAR_ODONE = [&](int t) { return bar0 + 8u * (2 + 4 * kFastStages + 8 + t); };    // P.V of the last block done
   volatile int* misc = (volatile int*)(smem + SM::offMisc);   // [0] tmem base, [1] abort, [6] early exit
   volatile int* abort_flag = misc + 1;
 
@@ -109,7 +110,8 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       mbar_init(BAR_SFULL(t, 0), 1);
       mbar_init(BAR_SFULL(t, 1), 1);
       mbar_init(BAR_PRDY(t), 2 * kTileM);
-      mbar_init(BAR_PVDONE(t), 1);
+      mbar_init(BAR_PENULT(t), 1);
+      mbar_init(BAR_ODONE(t), 1);
     }
     for (int s = 0; s < kFastStages; ++s) {
       mbar_init(BAR_KFULL(s), 1);
@@ -153,27 +155,31 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     float sk = ksc[0];
     const int blocks_per_scale = p.qk_block / BN;               // fp8_block_size is a multiple of block_n
     int scale_sub = 0;
-    const uint32_t bar_sfull = BAR_SFULL(t, 0), bar_pvdone = BAR_PVDONE(t), bar_prdy = BAR_PRDY(t);
+    const uint32_t bar_sfull = BAR_SFULL(t, 0), bar_prdy = BAR_PRDY(t);
+    const float p_off = p.p_off, sm_scale = p.sm_scale;
+    const int n_keys = p.N, k_stride = p.H;
 
-    bool alive = true;
+    // Waits here never bail out (mbar_wait_cont): the warp stays convergent around the collective TMEM
+    // accesses whatever happens, and a launch whose wait expired ends with `*status` raised.
+    bool s_seen = false;                     // this block's S-ready barrier was already observed (warp-uniform)
     for (int it = 0; it < nblk; ++it) {
       const int buf = it & 1;
-      // the votes keep the warp together if a bounded wait gives up in only some of its lanes
-      if (!__all_sync(0xffffffffu, mbar_wait(bar_sfull + 8u * buf, (it >> 1) & 1, abort_flag, p.status, 12))) { alive = false; break; }
+      if (!s_seen) mbar_wait_cont(bar_sfull + 8u * buf, (it >> 1) & 1, abort_flag, p.status, 12);
+      s_seen = false;
       tc_fence_after();
       uint32_t mine[HB], oth[HB];
       tmem_ld(mine, tS + buf * S_STRIDE + half * HB);
       tmem_ld(oth, tS + buf * S_STRIDE + (1 - half) * HB);
       tc_wait_ld();
-      const int n0 = it * BN;
       // (sq * sk) * sm_scale in the reference's order, then into the log2 domain
-      const float c = ((sq * sk) * p.sm_scale) * kLog2e;
-      if (++scale_sub == blocks_per_scale) {   // next block's scale, off the critical path (K is padded: in bounds)
+      const float c = ((sq * sk) * sm_scale) * kLog2e;
+      const bool more = it + 1 < nblk;
+      if (++scale_sub == blocks_per_scale) {   // next block's scale, off the critical path
         scale_sub = 0;
-        ksc += p.H;
-        if (it + 1 < nblk) sk = *ksc;
+        ksc += k_stride;
+        if (more) sk = *ksc;
       }
-      const int nvalid = p.N - n0;
+      const int nvalid = n_keys - it * BN;
       if (nvalid < BN) {                    // ragged tail: only the last block of a sequence
 #pragma unroll
         for (int i = 0; i < HB; ++i) {
@@ -195,7 +201,7 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       const float alpha = frozen ? 1.f : ex2(m2 - m_new);
       // ---- P = exp2(dot * c - m + off), l += sum(P) (attention_triton.py:219-326) ----
       // masked columns hold -inf, so their exp2 is exactly 0 without a select
-      const float bias = p.p_off - m_new;
+      const float bias = p_off - m_new;
       // two columns per instruction: fma.rn.f32x2 / add.rn.f32x2 round each half exactly like the scalar forms
       const float2 c2 = make_float2(c, c), bias2 = make_float2(bias, bias);
       float2 psa = make_float2(0.f, 0.f), psb = make_float2(0.f, 0.f);
@@ -212,12 +218,20 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         pk[i / 4] = (uint32_t)f32x2_to_e4m3x2(pa.x, pa.y) | ((uint32_t)f32x2_to_e4m3x2(pb.x, pb.y) << 16);
       }
       l_i = l_i * alpha + ((psa.x + psa.y) + (psb.x + psb.y));
-      // P.V of the previous block is observed in every block (it was issued a whole block's exponentials ago),
-      // so that this barrier's phases are never skipped and its parity stays unambiguous
-      if (it > 0 && !__all_sync(0xffffffffu, mbar_wait(bar_pvdone, (it - 1) & 1, abort_flag, p.status, 11))) { alive = false; break; }
       if (it > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
-        // some row of this warp raised its max: rescale this warp's half of the 32 accumulator rows in place
-        tc_fence_after();
+        // Some row of this warp raised its max: the accumulator must be rescaled before this block's P.V,
+        // and P.V of the previous block must have completed. S of the next block was issued behind that
+        // P.V by the same thread, and a commit covers everything issued before it: once the next S is ready
+        // (a wait that is due at the top of the next block anyway), the accumulator is quiescent. The last
+        // block has no successor and waits for its predecessor's P.V directly. A warp whose rows keep their
+        // max -- nearly every warp after the first few hundred keys -- waits for nothing here.
+        if (more) {
+          mbar_wait_cont(bar_sfull + 8u * (buf ^ 1), ((it + 1) >> 1) & 1, abort_flag, p.status, 12);
+          s_seen = true;
+        } else {
+          mbar_wait_cont(BAR_PENULT(t), 0, abort_flag, p.status, 11);
+        }
+        tc_fence_after();                     // rescale this warp's half of its 32 accumulator rows in place
 #pragma unroll
         for (int c0 = 0; c0 < HD; c0 += 32) {
           uint32_t r[32];
@@ -241,13 +255,13 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     }
 
     // ---- epilogue (attention_triton.py:387-407) ---------------------------------
-    if (alive) alive = __all_sync(0xffffffffu, mbar_wait(bar_pvdone, (nblk - 1) & 1, abort_flag, p.status, 13));
-    // the row sum is the sum of the two column halves; every softmax thread takes part in the barrier, also
-    // after a wait was given up
+    mbar_wait_cont(BAR_ODONE(t), 0, abort_flag, p.status, 13);
+    // the row sum is the sum of the two column halves
     float* lsum = reinterpret_cast<float*>(smem + SM::offL);
     lsum[(t * 2 + half) * kTileM + row_in_tile] = l_i;
     asm volatile("bar.sync 1, %0;" ::"n"(kFastSoftmaxWarps * 32) : "memory");
-    if (alive && *abort_flag == 0) {
+    const bool store_ok = row_ok && *abort_flag == 0;          // the loads below are collective, the stores are not
+    {
       tc_fence_after();
       const float inv_l = __fdiv_rn(1.0f, lsum[(t * 2) * kTileM + row_in_tile] + lsum[(t * 2 + 1) * kTileM + row_in_tile]);
       const bool has_vsc = p.v_kind == LBFQ_V_CHANNEL;
@@ -270,8 +284,8 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 #pragma unroll
           for (int i = 0; i < 32; ++i) a[i] = __uint_as_float(r[i]) * inv_l;
         }
-        if (!row_ok) {
-          // rows past M only took part in the collective load
+        if (!store_ok) {
+          // rows past M, and every row of a launch that gave up a wait, only take part in the collective load
         } else if (p.out_dtype == LBFQ_F32) {
           float4* o = reinterpret_cast<float4*>((float*)p.out + o_off + c0);
 #pragma unroll
@@ -361,7 +375,8 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         for (int kk = 0; kk < BN / 32; ++kk)
           mma_f8_ts(tO, tS + (j & 1) * S_STRIDE + kk * 8, dv + (uint64_t)((sub * BN + kk * 32) >> 4), id_pv,
                     (j > 0 || kk > 0) ? 1u : 0u);
-        tc_commit(BAR_PVDONE(t));
+        if (j == nblk - 2) tc_commit(BAR_PENULT(t));
+        if (j == nblk - 1) tc_commit(BAR_ODONE(t));
         if (sub == NSUB - 1 || j == nblk - 1) tc_commit(BAR_VFREE(st));
         return true;
       };

@@ -80,6 +80,23 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
 }
 
+// Bounded wait for code that must stay convergent (warp-collective tcgen05.ld / st follow it): it always
+// returns. When the wait is given up -- here, or earlier anywhere in the CTA -- the abort flag is set and every
+// later wait falls through at once, so that all roles run to the end of their loops in step and the launch
+// ends with `*status` raised and a result that the host discards.
+__device__ __forceinline__ void mbar_wait_cont(uint32_t bar, uint32_t parity, volatile int* abort_flag, int32_t* status,
+                                               int code) {
+  if (mbar_try(bar, parity)) return;
+  const unsigned long long t0 = clock64();
+  while (!*abort_flag && !mbar_try_parked(bar, parity, 20000u)) {
+    if (clock64() - t0 > kWaitCycles) {
+      *abort_flag = 1;
+      if (status) atomicCAS(status, 0, code);
+      return;
+    }
+  }
+}
+
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, uint32_t bar) {
   asm volatile(
       "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
