@@ -26,6 +26,8 @@
 // producer warp, one MMA-issuing warp per tile. Every mbarrier wait is bounded; on expiry the kernel raises `*status`, all
 // roles leave their loops, TMEM is released and the launch returns.
 
+#include <type_traits>
+
 #include "attn_prims.cuh"
 
 namespace lbfq {
@@ -161,30 +163,40 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 
     // Waits here never bail out (mbar_wait_cont): the warp stays convergent around the collective TMEM
     // accesses whatever happens, and a launch whose wait expired ends with `*status` raised.
+    // Key blocks alternate between the two S buffers; the loop body is instantiated once per buffer so that
+    // every TMEM and barrier address in it is a loop-invariant register.
+    const uint32_t tS_mine[2] = {tS + half * HB, tS + S_STRIDE + half * HB};
+    const uint32_t tS_oth[2] = {tS + (1 - half) * HB, tS + S_STRIDE + (1 - half) * HB};
+    const uint32_t tP[2] = {tS + half * (HB / 4), tS + S_STRIDE + half * (HB / 4)};
+    const uint32_t bar_s[2] = {bar_sfull, bar_sfull + 8u};
+    const uint32_t bar_penult = BAR_PENULT(t);
+    const int last = nblk - 1;
+    const int tail_valid = n_keys - last * BN;      // keys in the last block (BN unless the sequence is ragged)
     bool s_seen = false;                     // this block's S-ready barrier was already observed (warp-uniform)
-    for (int it = 0; it < nblk; ++it) {
-      const int buf = it & 1;
-      if (!s_seen) mbar_wait_cont(bar_sfull + 8u * buf, (it >> 1) & 1, abort_flag, p.status, 12);
+    uint32_t par = 0;                        // parity of the S-ready phases of the current pair of blocks
+
+    auto body = [&](auto buf_c, const int it) {
+      constexpr int BUF = decltype(buf_c)::value;
+      if (!s_seen) mbar_wait_cont(bar_s[BUF], par, abort_flag, p.status, 12);
       s_seen = false;
       tc_fence_after();
       uint32_t mine[HB], oth[HB];
-      tmem_ld(mine, tS + buf * S_STRIDE + half * HB);
-      tmem_ld(oth, tS + buf * S_STRIDE + (1 - half) * HB);
+      tmem_ld(mine, tS_mine[BUF]);
+      tmem_ld(oth, tS_oth[BUF]);
       tc_wait_ld();
       // (sq * sk) * sm_scale in the reference's order, then into the log2 domain
       const float c = ((sq * sk) * sm_scale) * kLog2e;
-      const bool more = it + 1 < nblk;
+      const bool more = it != last;
       if (++scale_sub == blocks_per_scale) {   // next block's scale, off the critical path
         scale_sub = 0;
         ksc += k_stride;
         if (more) sk = *ksc;
       }
-      const int nvalid = n_keys - it * BN;
-      if (nvalid < BN) {                    // ragged tail: only the last block of a sequence
+      if (!more && tail_valid < BN) {          // ragged tail: only the last block of a sequence
 #pragma unroll
         for (int i = 0; i < HB; ++i) {
-          if (half * HB + i >= nvalid) mine[i] = 0xff800000u;
-          if ((1 - half) * HB + i >= nvalid) oth[i] = 0xff800000u;
+          if (half * HB + i >= tail_valid) mine[i] = 0xff800000u;
+          if ((1 - half) * HB + i >= tail_valid) oth[i] = 0xff800000u;
         }
       }
       float bm0 = fmaxf(__uint_as_float(mine[0]), __uint_as_float(oth[0]));
@@ -215,7 +227,7 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         psa = __fadd2_rn(psa, pa);
         psb = __fadd2_rn(psb, pb);
         // the conversion saturates at 448, which is the reference's clamp (attention_triton.py:328-336)
-        pk[i / 4] = (uint32_t)f32x2_to_e4m3x2(pa.x, pa.y) | ((uint32_t)f32x2_to_e4m3x2(pb.x, pb.y) << 16);
+        pk[i / 4] = f32x4_to_e4m3x4(pa.x, pa.y, pb.x, pb.y);
       }
       l_i = l_i * alpha + ((psa.x + psa.y) + (psb.x + psb.y));
       if (it > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
@@ -226,10 +238,10 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         // block has no successor and waits for its predecessor's P.V directly. A warp whose rows keep their
         // max -- nearly every warp after the first few hundred keys -- waits for nothing here.
         if (more) {
-          mbar_wait_cont(bar_sfull + 8u * (buf ^ 1), ((it + 1) >> 1) & 1, abort_flag, p.status, 12);
+          mbar_wait_cont(bar_s[BUF ^ 1], BUF == 0 ? par : (par ^ 1u), abort_flag, p.status, 12);
           s_seen = true;
         } else {
-          mbar_wait_cont(BAR_PENULT(t), 0, abort_flag, p.status, 11);
+          mbar_wait_cont(bar_penult, 0, abort_flag, p.status, 11);
         }
         tc_fence_after();                     // rescale this warp's half of its 32 accumulator rows in place
 #pragma unroll
@@ -246,12 +258,22 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           LBFQ_TMEM_ST32(tO + c0, r);
         }
       }
-      if constexpr (BN == 64) tmem_st8(tS + buf * S_STRIDE + half * (HB / 4), pk);
-      else tmem_st4(tS + buf * S_STRIDE + half * (HB / 4), pk);
+      if constexpr (BN == 64) tmem_st8(tP[BUF], pk);
+      else tmem_st4(tP[BUF], pk);
       tc_wait_st();
       tc_fence_before();
       mbar_arrive(bar_prdy);
       m2 = m_new;
+    };
+    {
+      int it = 0;
+#pragma unroll 1
+      for (; it + 1 < nblk; it += 2) {
+        body(std::integral_constant<int, 0>{}, it);
+        body(std::integral_constant<int, 1>{}, it + 1);
+        par ^= 1u;
+      }
+      if (it < nblk) body(std::integral_constant<int, 0>{}, it);
     }
 
     // ---- epilogue (attention_triton.py:387-407) ---------------------------------
@@ -385,7 +407,11 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       for (int it = 0; it < nblk && ok; ++it) {
         // P.V of this block once its P is in TMEM (and the rows that raised their max are rescaled), then
         // Q.K^T of block it + 2 into the S buffer that P has just been read from
+#ifdef LBFQ_MMA_SPIN
+        { unsigned long long t0 = clock64(); ok = true; uint32_t n = 0; while (!mbar_try(BAR_PRDY(t), it & 1)) { if ((++n & 1023u) == 0 && (*abort_flag || clock64() - t0 > kWaitCycles)) { *abort_flag = 1; if (p.status) atomicCAS(p.status, 0, 35); ok = false; break; } } }
+#else
         ok = mbar_wait(BAR_PRDY(t), it & 1, abort_flag, p.status, 35);
+#endif
         if (ok) ok = issue_pv(it);
         if (ok && it + 2 < nblk) ok = issue_qk(it + 2);
       }

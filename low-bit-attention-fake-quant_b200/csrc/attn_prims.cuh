@@ -27,6 +27,9 @@ constexpr int kRegsService = 40;
 static_assert(kSoftmaxWarps * 32 * kRegsSoftmax + (kThreads - kSoftmaxWarps * 32) * kRegsService <= kThreads * kRegsLaunch,
               "setmaxnreg requests exceed the CTA's register pool");
 static_assert(kRegsSoftmax % 8 == 0 && kRegsService % 8 == 0 && kRegsService >= 24, "setmaxnreg granularity");
+#ifndef LBFQ_PARK_NS
+#define LBFQ_PARK_NS 20000u
+#endif
 constexpr unsigned long long kWaitCycles = 1000000000ull;   // ~0.5 s: far above any legitimate wait
 
 // ---------------------------------------------------------------------------
@@ -70,7 +73,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   if (mbar_try(bar, parity)) return true;
   const unsigned long long t0 = clock64();
   while (true) {
-    if (mbar_try_parked(bar, parity, 20000u)) return true;
+    if (mbar_try_parked(bar, parity, LBFQ_PARK_NS)) return true;
     if (*abort_flag) return false;
     if (clock64() - t0 > kWaitCycles) {
       *abort_flag = 1;
@@ -88,7 +91,7 @@ __device__ __forceinline__ void mbar_wait_cont(uint32_t bar, uint32_t parity, vo
                                                int code) {
   if (mbar_try(bar, parity)) return;
   const unsigned long long t0 = clock64();
-  while (!*abort_flag && !mbar_try_parked(bar, parity, 20000u)) {
+  while (!*abort_flag && !mbar_try_parked(bar, parity, LBFQ_PARK_NS)) {
     if (clock64() - t0 > kWaitCycles) {
       *abort_flag = 1;
       if (status) atomicCAS(status, 0, code);
@@ -195,6 +198,18 @@ __device__ __forceinline__ void tmem_st8(uint32_t addr, const uint32_t* r) {
 __device__ __forceinline__ void tmem_st4(uint32_t addr, const uint32_t* r) {
   asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};"
                ::"r"(addr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]) : "memory");
+}
+
+// four FP32 -> four e4m3 codes in one 32-bit word (a = byte 0 ... d = byte 3), round-to-nearest-even,
+// saturating at +-448: two cvt.rn.satfinite.e4m3x2.f32 whose halves the assembler can merge in place
+__device__ __forceinline__ uint32_t f32x4_to_e4m3x4(float a, float b, float c, float d) {
+  uint32_t r;
+  asm("{\n\t.reg .b16 lo, hi;\n\t"
+      "cvt.rn.satfinite.e4m3x2.f32 lo, %2, %1;\n\t"
+      "cvt.rn.satfinite.e4m3x2.f32 hi, %4, %3;\n\t"
+      "mov.b32 %0, {lo, hi};\n\t}"
+      : "=r"(r) : "f"(a), "f"(b), "f"(c), "f"(d));
+  return r;
 }
 
 __device__ __forceinline__ float ex2(float x) {
