@@ -22,6 +22,7 @@
 #ifndef LBFQ_H_
 #define LBFQ_H_
 
+#include <stddef.h>
 #include <stdint.h>
 
 #ifdef __cplusplus
@@ -254,6 +255,15 @@ int lbfq_attention_fwd(const lbfq_attn_args* args, void* workspace, void* stream
  * per-channel V, FP8-block Q/K, no V smoothing, no score bias, no BLASST). Setting the environment variable
  * LBFQ_ATTN_GENERIC=1 keeps every configuration on the general kernel. No counterpart in the reference. */
 int lbfq_attention_last_variant(void);
+
+/* ======================= host-buffer plumbing ============================== */
+
+/* `rows` rows of `width` bytes between a pitched host buffer and a pitched device buffer, enqueued on `stream`
+ * (to_device != 0: host -> device). Used by the host-buffer entry of the Python mirror to move a heads slice
+ * (B, S, h0:h1, D) of an (B, S, H, D) host tensor without a staging copy. No counterpart in the reference,
+ * whose callers hold their tensors on the device. */
+int lbfq_copy_rows_async(void* dst, size_t dst_pitch, const void* src, size_t src_pitch, size_t width, size_t rows,
+                         int to_device, void* stream);
 
 #ifdef __cplusplus
 }

@@ -20,3 +20,15 @@ extern "C" int lbfq_abi_version(void) { return 1; }
 // Kernels launched by this library since load (all entry points count through check_launch()).
 namespace lbfq { unsigned long long g_launches = 0; }
 extern "C" unsigned long long lbfq_launch_count(void) { return lbfq::g_launches; }
+
+// Rows of `width` bytes between pitched host and device buffers, enqueued on `stream` (one cudaMemcpy2DAsync).
+// `to_device` != 0: host -> device, else device -> host.
+extern "C" int lbfq_copy_rows_async(void* dst, size_t dst_pitch, const void* src, size_t src_pitch, size_t width,
+                                    size_t rows, int to_device, void* stream) {
+  LBFQ_REQUIRE(dst != nullptr && src != nullptr, LBFQ_ERR_ARG, "null pointer");
+  LBFQ_REQUIRE(width <= dst_pitch && width <= src_pitch, LBFQ_ERR_ARG, "row width exceeds a pitch");
+  if (width == 0 || rows == 0) return LBFQ_OK;
+  LBFQ_CUDA_OK(cudaMemcpy2DAsync(dst, dst_pitch, src, src_pitch, width, rows,
+                                 to_device ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+  return LBFQ_OK;
+}

@@ -14,6 +14,7 @@ from .attention import (
     reference_attention,
 )
 from .config import QuantConfig
+from .host import fake_quant_attention_host  # extension: not in the reference, hence not in __all__
 from .hadamard import apply_qk_hadamard, fast_hadamard_available, hadamard_transform_last_dim
 from .kmeans import (
     KMeansReorderResult,

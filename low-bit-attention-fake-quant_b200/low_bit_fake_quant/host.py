@@ -1,0 +1,109 @@
+"""Host-buffer entry: ``fake_quant_attention`` for callers whose Q, K, V live in host memory.
+
+The reference has no such entry (its callers hold CUDA tensors,
+src/low_bit_fake_quant/attention.py:741-742). Every (batch, head) slab of the
+operator is independent end to end (the k-means rows, the K mean, every scale
+tensor and the attention grid are all indexed by head), so the heads are cut
+into chunks and pipelined over three streams: while chunk ``i`` is computed,
+chunk ``i + 1`` travels host -> device and the result of chunk ``i - 1`` travels
+device -> host. The result is bit-identical to one call on the whole tensors:
+Hadamard signs and k-means seeding are indexed by the global head.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import _lib as L
+from .attention import fake_quant_attention
+from .config import QuantConfig
+
+
+def _copy_rows(dst: torch.Tensor, src: torch.Tensor, h0: int, h1: int, rows_s: int, to_device: bool, stream) -> None:
+    """(B, :rows_s, h0:h1, D) of the host tensor <-> a contiguous (B, S_dev, h1-h0, D) device tensor."""
+    host, dev = (src, dst) if to_device else (dst, src)
+    b, s_host, h, d = host.shape
+    es = host.element_size()
+    width = (h1 - h0) * d * es
+    for bi in range(b):
+        hp = host.data_ptr() + (bi * s_host * h + h0) * d * es
+        dp = dev.data_ptr() + bi * dev.shape[1] * width
+        if to_device:
+            L.check(L.lib().lbfq_copy_rows_async(dp, width, hp, h * d * es, width, rows_s, 1, stream.cuda_stream))
+        else:
+            L.check(L.lib().lbfq_copy_rows_async(hp, h * d * es, dp, width, width, rows_s, 0, stream.cuda_stream))
+
+
+def fake_quant_attention_host(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    cfg: Optional[QuantConfig] = None,
+    *,
+    sm_scale: Optional[float] = None,
+    out: Optional[torch.Tensor] = None,
+    device: Optional[torch.device] = None,
+    heads_per_chunk: int = 8,
+) -> torch.Tensor:
+    """``fake_quant_attention`` on host tensors.
+
+    ``q, k, v``: contiguous (B, S, H, D) CPU tensors (pinned memory makes the copies asynchronous).
+    ``out``: optional contiguous (B, S_out <= S, H, D) CPU tensor of ``q``'s dtype; only its first ``S_out``
+    rows are brought back (the caller's way to drop padding rows). Returns ``out``; it is complete when
+    this function returns.
+    """
+    if cfg is None:
+        cfg = QuantConfig()
+    if q.shape != k.shape or q.shape != v.shape:
+        raise ValueError(f"q/k/v shapes must match; got {tuple(q.shape)}, {tuple(k.shape)}, {tuple(v.shape)}")
+    if q.ndim != 4:
+        raise ValueError(f"q/k/v must be 4-D (B,S,H,D); got {q.shape}")
+    if q.is_cuda or k.is_cuda or v.is_cuda:
+        raise ValueError("q/k/v must live in host memory; use fake_quant_attention for CUDA tensors")
+    if not (q.dtype == k.dtype == v.dtype):
+        raise TypeError("q/k/v must share a dtype")
+    if q.dtype not in (torch.float16, torch.bfloat16, torch.float32):
+        raise TypeError(f"unsupported dtype {q.dtype}")
+    if not (q.is_contiguous() and k.is_contiguous() and v.is_contiguous()):
+        raise ValueError("q/k/v must be contiguous")
+    b, s, h, d = q.shape
+    if out is None:
+        out = torch.empty_like(q, pin_memory=q.is_pinned())
+    if out.ndim != 4 or out.shape[0] != b or out.shape[2] != h or out.shape[3] != d or out.shape[1] > s:
+        raise ValueError(f"out must be (B, S_out <= S, H, D); got {tuple(out.shape)}")
+    if out.dtype != q.dtype or out.is_cuda or not out.is_contiguous():
+        raise ValueError("out must be a contiguous host tensor of q's dtype")
+    if heads_per_chunk <= 0:
+        raise ValueError("heads_per_chunk must be positive")
+    dev = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+    hc = min(heads_per_chunk, h)
+    bounds = [(h0, min(h0 + hc, h)) for h0 in range(0, h, hc)]
+    s_out = out.shape[1]
+
+    with torch.cuda.device(dev):
+        comp = torch.cuda.current_stream(dev)
+        s_in, s_back = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+        s_in.wait_stream(comp)
+        slots = [[torch.empty((b, s, hc, d), dtype=q.dtype, device=dev) for _ in range(3)] for _ in range(2)]
+        loaded = [torch.cuda.Event() for _ in bounds]
+        computed = [torch.cuda.Event() for _ in bounds]
+        results = []
+        for i, (h0, h1) in enumerate(bounds):
+            n = h1 - h0
+            bufs = [t[:, :, :n] if n == hc else t.view(-1)[: b * s * n * d].view(b, s, n, d) for t in slots[i % 2]]
+            if i >= 2:
+                s_in.wait_event(computed[i - 2])            # the slot's previous occupant has been consumed
+            for dst, src in zip(bufs, (q, k, v)):
+                _copy_rows(dst, src, h0, h1, s, True, s_in)
+            loaded[i].record(s_in)
+            comp.wait_event(loaded[i])
+            o = fake_quant_attention(bufs[0], bufs[1], bufs[2], cfg, sm_scale=sm_scale, _head_offset=h0, _total_heads=h)
+            computed[i].record(comp)
+            s_back.wait_event(computed[i])
+            o.record_stream(s_back)
+            _copy_rows(out, o, h0, h1, s_out, False, s_back)
+            results.append(o)
+        s_back.synchronize()
+        comp.synchronize()
+    return out

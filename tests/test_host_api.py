@@ -50,6 +50,7 @@ def test_public_names_match_reference_package():
     assert set(fq.__all__) == want
     for n in want:
         assert hasattr(fq, n)
+    assert callable(fq.fake_quant_attention_host)             # extension, kept out of __all__
 
 
 def test_quant_config_defaults_and_frozen():
