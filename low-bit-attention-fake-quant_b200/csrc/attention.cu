@@ -195,15 +195,29 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
           uint32_t r[32];
           LBFQ_TMEM_LD32(r, tO + c0);
           tc_wait_ld();
+          // two columns per instruction (fma / mul / add .f32x2 round each half like the scalar forms)
+          const float2 a2 = make_float2(a, a), cc2 = make_float2(c, c);
           if (rescale) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) acc[c0 + i] = fmaf(c, __uint_as_float(r[i]), acc[c0 + i] * a);
+            for (int i = 0; i < 32; i += 2) {
+              const float2 v = __ffma2_rn(cc2, make_float2(__uint_as_float(r[i]), __uint_as_float(r[i + 1])),
+                                          __fmul2_rn(make_float2(acc[c0 + i], acc[c0 + i + 1]), a2));
+              acc[c0 + i] = v.x; acc[c0 + i + 1] = v.y;
+            }
           } else if (scaled) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) acc[c0 + i] = fmaf(c, __uint_as_float(r[i]), acc[c0 + i]);
+            for (int i = 0; i < 32; i += 2) {
+              const float2 v = __ffma2_rn(cc2, make_float2(__uint_as_float(r[i]), __uint_as_float(r[i + 1])),
+                                          make_float2(acc[c0 + i], acc[c0 + i + 1]));
+              acc[c0 + i] = v.x; acc[c0 + i + 1] = v.y;
+            }
           } else {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) acc[c0 + i] += __uint_as_float(r[i]);
+            for (int i = 0; i < 32; i += 2) {
+              const float2 v = __fadd2_rn(make_float2(acc[c0 + i], acc[c0 + i + 1]),
+                                          make_float2(__uint_as_float(r[i]), __uint_as_float(r[i + 1])));
+              acc[c0 + i] = v.x; acc[c0 + i + 1] = v.y;
+            }
           }
         }
         return;
@@ -229,29 +243,40 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             const float4 w = v4[i];
-            r[4 * i + 0] = __float_as_uint(__uint_as_float(r[4 * i + 0]) * w.x);
-            r[4 * i + 1] = __float_as_uint(__uint_as_float(r[4 * i + 1]) * w.y);
-            r[4 * i + 2] = __float_as_uint(__uint_as_float(r[4 * i + 2]) * w.z);
-            r[4 * i + 3] = __float_as_uint(__uint_as_float(r[4 * i + 3]) * w.w);
+            const float2 lo = __fmul2_rn(make_float2(__uint_as_float(r[4 * i + 0]), __uint_as_float(r[4 * i + 1])), make_float2(w.x, w.y));
+            const float2 hi = __fmul2_rn(make_float2(__uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3])), make_float2(w.z, w.w));
+            r[4 * i + 0] = __float_as_uint(lo.x); r[4 * i + 1] = __float_as_uint(lo.y);
+            r[4 * i + 2] = __float_as_uint(hi.x); r[4 * i + 3] = __float_as_uint(hi.y);
           }
         }
         if (has_av) {
           const float4* a4 = reinterpret_cast<const float4*>(av + c0);
 #pragma unroll
+          const float2 rs2 = make_float2(rs, rs);
+#pragma unroll
           for (int i = 0; i < 4; ++i) {
             const float4 w = a4[i];
-            r[4 * i + 0] = __float_as_uint(fmaf(rs, w.x, __uint_as_float(r[4 * i + 0])));
-            r[4 * i + 1] = __float_as_uint(fmaf(rs, w.y, __uint_as_float(r[4 * i + 1])));
-            r[4 * i + 2] = __float_as_uint(fmaf(rs, w.z, __uint_as_float(r[4 * i + 2])));
-            r[4 * i + 3] = __float_as_uint(fmaf(rs, w.w, __uint_as_float(r[4 * i + 3])));
+            const float2 lo = __ffma2_rn(rs2, make_float2(w.x, w.y), make_float2(__uint_as_float(r[4 * i + 0]), __uint_as_float(r[4 * i + 1])));
+            const float2 hi = __ffma2_rn(rs2, make_float2(w.z, w.w), make_float2(__uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3])));
+            r[4 * i + 0] = __float_as_uint(lo.x); r[4 * i + 1] = __float_as_uint(lo.y);
+            r[4 * i + 2] = __float_as_uint(hi.x); r[4 * i + 3] = __float_as_uint(hi.y);
           }
         }
+        const float2 a2 = make_float2(a, a), cc2 = make_float2(c, c);
         if (rescale) {
 #pragma unroll
-          for (int i = 0; i < 16; ++i) acc[c0 + i] = fmaf(c, __uint_as_float(r[i]), acc[c0 + i] * a);
+          for (int i = 0; i < 16; i += 2) {
+            const float2 v = __ffma2_rn(cc2, make_float2(__uint_as_float(r[i]), __uint_as_float(r[i + 1])),
+                                        __fmul2_rn(make_float2(acc[c0 + i], acc[c0 + i + 1]), a2));
+            acc[c0 + i] = v.x; acc[c0 + i + 1] = v.y;
+          }
         } else {
 #pragma unroll
-          for (int i = 0; i < 16; ++i) acc[c0 + i] = fmaf(c, __uint_as_float(r[i]), acc[c0 + i]);
+          for (int i = 0; i < 16; i += 2) {
+            const float2 v = __ffma2_rn(cc2, make_float2(__uint_as_float(r[i]), __uint_as_float(r[i + 1])),
+                                        make_float2(acc[c0 + i], acc[c0 + i + 1]));
+            acc[c0 + i] = v.x; acc[c0 + i + 1] = v.y;
+          }
         }
       }
     };
@@ -291,30 +316,32 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         const int c = it / NSUB;
         if (!mbar_wait(BAR_SIDEFULL(c % kStages), (c / kStages) & 1, abort_flag, p.status, 15)) { alive = false; break; }
       }
+      const float2 f2 = make_float2(f, f);
       if (corr_smem) {
         const float4* c4 = reinterpret_cast<const float4*>(
             smem + SM::offCorr + (((it / NSUB) % kStages) * 2 + t) * (kChunk * 4) + (it % NSUB) * (BN * 4));
 #pragma unroll
         for (int i = 0; i < BN / 4; ++i) {
           const float4 cv = c4[i];               // same address in every lane: one broadcast wavefront
-          s[4 * i + 0] = s[4 * i + 0] * f + cv.x;
-          s[4 * i + 1] = s[4 * i + 1] * f + cv.y;
-          s[4 * i + 2] = s[4 * i + 2] * f + cv.z;
-          s[4 * i + 3] = s[4 * i + 3] * f + cv.w;
+          const float2 lo = __ffma2_rn(make_float2(s[4 * i + 0], s[4 * i + 1]), f2, make_float2(cv.x, cv.y));
+          const float2 hi = __ffma2_rn(make_float2(s[4 * i + 2], s[4 * i + 3]), f2, make_float2(cv.z, cv.w));
+          s[4 * i + 0] = lo.x; s[4 * i + 1] = lo.y; s[4 * i + 2] = hi.x; s[4 * i + 3] = hi.y;
         }
       } else if (corr_row) {
         const float4* c4 = reinterpret_cast<const float4*>(corr_row + n0);
 #pragma unroll
         for (int i = 0; i < BN / 4; ++i) {
           const float4 cv = __ldg(c4 + i);
-          s[4 * i + 0] = s[4 * i + 0] * f + cv.x;
-          s[4 * i + 1] = s[4 * i + 1] * f + cv.y;
-          s[4 * i + 2] = s[4 * i + 2] * f + cv.z;
-          s[4 * i + 3] = s[4 * i + 3] * f + cv.w;
+          const float2 lo = __ffma2_rn(make_float2(s[4 * i + 0], s[4 * i + 1]), f2, make_float2(cv.x, cv.y));
+          const float2 hi = __ffma2_rn(make_float2(s[4 * i + 2], s[4 * i + 3]), f2, make_float2(cv.z, cv.w));
+          s[4 * i + 0] = lo.x; s[4 * i + 1] = lo.y; s[4 * i + 2] = hi.x; s[4 * i + 3] = hi.y;
         }
       } else {
 #pragma unroll
-        for (int i = 0; i < BN; ++i) s[i] *= f;
+        for (int i = 0; i < BN; i += 2) {
+          const float2 v = __fmul2_rn(make_float2(s[i], s[i + 1]), f2);
+          s[i] = v.x; s[i + 1] = v.y;
+        }
       }
       if (nvalid < BN) {                    // ragged tail: only the last block of a sequence
 #pragma unroll
@@ -440,17 +467,19 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
           }
         } else {
           // masked columns hold -inf, so their exp2 is exactly 0 without a select
-          float ps0 = 0.f, ps1 = 0.f, ps2 = 0.f, ps3 = 0.f;
+          float2 psa = make_float2(0.f, 0.f), psb = make_float2(0.f, 0.f);
+          const float2 nm2 = make_float2(-m_new, -m_new), l2 = make_float2(kLog2e, kLog2e), off2 = make_float2(off, off);
 #pragma unroll
           for (int i = 0; i < BN; i += 4) {
-            const float p0 = ex2(fmaf(s[i] - m_new, kLog2e, off));
-            const float p1 = ex2(fmaf(s[i + 1] - m_new, kLog2e, off));
-            const float p2 = ex2(fmaf(s[i + 2] - m_new, kLog2e, off));
-            const float p3 = ex2(fmaf(s[i + 3] - m_new, kLog2e, off));
-            s[i] = p0; s[i + 1] = p1; s[i + 2] = p2; s[i + 3] = p3;
-            ps0 += p0; ps1 += p1; ps2 += p2; ps3 += p3;
+            const float2 za = __ffma2_rn(__fadd2_rn(make_float2(s[i], s[i + 1]), nm2), l2, off2);
+            const float2 zb = __ffma2_rn(__fadd2_rn(make_float2(s[i + 2], s[i + 3]), nm2), l2, off2);
+            const float2 pa = make_float2(ex2(za.x), ex2(za.y));
+            const float2 pb = make_float2(ex2(zb.x), ex2(zb.y));
+            s[i] = pa.x; s[i + 1] = pa.y; s[i + 2] = pb.x; s[i + 3] = pb.y;
+            psa = __fadd2_rn(psa, pa);
+            psb = __fadd2_rn(psb, pb);
           }
-          psum = (ps0 + ps1) + (ps2 + ps3);
+          psum = (psa.x + psa.y) + (psb.x + psb.y);
           // exp2 is monotonic: the largest P of the block is the P of the largest score, and it is
           // produced by the same instruction sequence, so it is bit-identical to max_i(P_i)
           pmax = ex2(fmaf(bmax - m_new, kLog2e, off));
@@ -462,7 +491,7 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         if (p.p_kind == LBFQ_P_ELEMENTWISE) {
 #pragma unroll
           for (int i = 0; i < BN / 4; ++i)
-            pk[i] = (uint32_t)f32x2_to_e4m3x2(s[4 * i], s[4 * i + 1]) | ((uint32_t)f32x2_to_e4m3x2(s[4 * i + 2], s[4 * i + 3]) << 16);
+            pk[i] = f32x4_to_e4m3x4(s[4 * i], s[4 * i + 1], s[4 * i + 2], s[4 * i + 3]);
         } else {
           float inv;
           if (p.p_kind == LBFQ_P_MX) {
@@ -475,9 +504,13 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
           }
           // the conversion saturates at 448, which is the reference's clamp
 #pragma unroll
-          for (int i = 0; i < BN / 4; ++i)
-            pk[i] = (uint32_t)f32x2_to_e4m3x2(s[4 * i] * inv, s[4 * i + 1] * inv) |
-                    ((uint32_t)f32x2_to_e4m3x2(s[4 * i + 2] * inv, s[4 * i + 3] * inv) << 16);
+          const float2 inv2 = make_float2(inv, inv);
+#pragma unroll
+          for (int i = 0; i < BN / 4; ++i) {
+            const float2 lo = __fmul2_rn(make_float2(s[4 * i], s[4 * i + 1]), inv2);
+            const float2 hi = __fmul2_rn(make_float2(s[4 * i + 2], s[4 * i + 3]), inv2);
+            pk[i] = f32x4_to_e4m3x4(lo.x, lo.y, hi.x, hi.y);
+          }
         }
         const uint32_t tPb = tP + (it & 1) * 16;
         tmem_st8(tPb, pk);
