@@ -79,7 +79,8 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
   static_assert(COL_O + PV_N <= TCOLS, "TMEM budget");
 
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  // rounded up to 1 KB by pointer arithmetic, so that the compiler still knows it points into shared memory
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   const uint32_t sbase = smem_u32(smem);
   const uint32_t bar0 = sbase + SM::offBar;
   // barrier map
