@@ -17,7 +17,10 @@
 // The update uses the same stable counting sort that later produces the token
 // order: tokens of one cluster become one contiguous segment, reduced by one CTA.
 
+#include <cstdlib>
+
 #include "common.cuh"
+#include "kmeans_tc.h"
 
 namespace lbfq {
 
@@ -204,7 +207,7 @@ segment_mean_kernel(const T* __restrict__ x, int S, int H, int D, int k, const i
 }
 
 struct KmScratch {
-  float* cent; float* cnorm; int32_t* order32; int32_t* seg;
+  float* cent; float* cnorm; int32_t* order32; int32_t* seg; void* split;
 };
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 static size_t scratch_layout(int BH, int S, int D, int k, uint8_t* base, KmScratch* out) {
@@ -214,6 +217,8 @@ static size_t scratch_layout(int BH, int S, int D, int k, uint8_t* base, KmScrat
   uint8_t* p1 = take((size_t)BH * k * 4);
   uint8_t* p2 = take((size_t)BH * S * 4);
   uint8_t* p3 = take((size_t)BH * (k + 1) * 4);
+  uint8_t* p4 = take(kmeans_tc_split_bytes(BH, D));       // BF16 pieces of the centroids (tensor-core assignment)
+  if (out) out->split = p4;
   if (out) { out->cent = (float*)p0; out->cnorm = (float*)p1; out->order32 = (int32_t*)p2; out->seg = (int32_t*)p3; }
   return off;
 }
@@ -245,9 +250,16 @@ extern "C" int lbfq_kmeans_labels(const void* x, int dtype, int B, int S, int H,
       init_centroids_kernel<T><<<BH * k, 128, 0, st>>>((const T*)x, S, H, D, k, (uint32_t)seed, head_offset, total_heads, sc.cent, sc.cnorm));
   if (int rc = check_launch("kmeans init")) return rc;
   const int ntile = (S + kTok - 1) / kTok;
+  // LBFQ_KMEANS_FFMA=1 keeps the FP32 FFMA assignment (used to cross-check the two)
+  const char* force_ffma = getenv("LBFQ_KMEANS_FFMA");
+  const bool tc = kmeans_tc_eligible(dtype, D, k) && !(force_ffma && force_ffma[0] == '1');
   for (int it = 0; it < iters; ++it) {
-    LBFQ_DISPATCH_DTYPE(dtype, T,
-        assign_kernel<T><<<BH * ntile, kThreads, 0, st>>>((const T*)x, S, H, D, k, sc.cent, sc.cnorm, labels));
+    if (tc) {
+      if (int rc = kmeans_tc_assign(x, B, S, H, D, k, sc.cent, sc.cnorm, sc.split, labels, st)) return rc;
+    } else {
+      LBFQ_DISPATCH_DTYPE(dtype, T,
+          assign_kernel<T><<<BH * ntile, kThreads, 0, st>>>((const T*)x, S, H, D, k, sc.cent, sc.cnorm, labels));
+    }
     if (int rc = check_launch("kmeans assign")) return rc;
     if (it + 1 == iters) break;                     // labels of the last assignment are the result
     sort_segments_kernel<<<BH, 1024, 2 * k * sizeof(int), st>>>(labels, S, k, sc.order32, sc.seg);

@@ -1,0 +1,228 @@
+// k-means assignment on the tensor cores (BF16 tokens).
+//
+// argmin_c |c|^2 - 2 x.c needs the (tokens x centroids) Gram block x.c^T: a GEMM with M = tokens, N = k <= 64,
+// K = D. The tokens are BF16 already; the FP32 centroids are split into three BF16 pieces
+// (c = hi + mid + lo to 24 bits), so that x.c = x.hi + x.mid + x.lo is accumulated from exact BF16 x BF16
+// products in FP32 -- the same value as the FP32 FFMA kernel up to summation order. One CTA = 128 tokens of one
+// (b, h): TMA brings the token tile (two 64-channel panels, 128B swizzle) and the 3 x 64 centroid rows,
+// one thread issues 3 x D/16 tcgen05.mma.kind::f16 into 64 TMEM columns, then thread == token reads its row of
+// dot products back and takes the argmin (lowest index on ties, as the FFMA kernel does). The kernel is bound by
+// reading the tokens once per Lloyd iteration (HBM / L2), not by arithmetic.
+#include "attn_prims.cuh"
+#include "kmeans_tc.h"
+
+namespace lbfq {
+
+using namespace attn;
+
+namespace {
+
+constexpr int kTcTok = 128;      // tokens per CTA (MMA M)
+constexpr int kTcCen = 64;       // centroid rows per piece (MMA N), zero-padded above k
+
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void mma_bf16_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc) : "memory");
+}
+// kind::f16, A = B = BF16, FP32 accumulator, both operands K-major, M = 128
+__host__ __device__ constexpr uint32_t make_idesc_bf16(int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+}
+
+// (BH, k, D) fp32 -> (BH, 3, 64, D) bf16 pieces, rows >= k zero
+__global__ void split_centroids_kernel(const float* __restrict__ cent, int BH, int k, int D, __nv_bfloat16* __restrict__ out) {
+  const size_t total = (size_t)BH * kTcCen * D;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const int d = (int)(i % D);
+    const int c = (int)((i / D) % kTcCen);
+    const size_t bh = i / D / kTcCen;
+    float v = c < k ? cent[(bh * k + c) * D + d] : 0.f;
+    const __nv_bfloat16 hi = __float2bfloat16_rn(v);
+    v -= __bfloat162float(hi);
+    const __nv_bfloat16 mid = __float2bfloat16_rn(v);
+    v -= __bfloat162float(mid);
+    const __nv_bfloat16 lo = __float2bfloat16_rn(v);
+    __nv_bfloat16* o = out + (bh * 3 * kTcCen + c) * D + d;
+    o[0] = hi;
+    o[(size_t)kTcCen * D] = mid;
+    o[(size_t)2 * kTcCen * D] = lo;
+  }
+}
+
+template <int D>
+__global__ void __launch_bounds__(128)
+assign_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_c, int S, int H, int k,
+                 const float* __restrict__ cnorm, int32_t* __restrict__ labels) {
+  constexpr int NP = D / 64;                         // 64-channel panels (one 128-byte swizzle row each)
+  constexpr int kA = kTcTok * 128;                   // bytes per token panel
+  constexpr int kB = 3 * kTcCen * 128;               // bytes per centroid panel (three pieces)
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  const uint32_t sbase = smem_u32(smem);
+  const uint32_t offA = 0, offB = NP * kA, offBar = offB + NP * kB;
+  const uint32_t bar_full = sbase + offBar, bar_done = sbase + offBar + 8;
+  volatile int* misc = (volatile int*)(smem + offBar + 16);       // [0] tmem base, [1] abort
+  volatile int* abort_flag = misc + 1;
+
+  const int ntile = (S + kTcTok - 1) / kTcTok;
+  const int tile = blockIdx.x % ntile;
+  const int bh = blockIdx.x / ntile;
+  const int b = bh / H, h = bh % H;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    mbar_init(bar_full, 1);
+    mbar_init(bar_done, 1);
+    misc[1] = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 64;" ::"r"(sbase + offBar + 16) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = (uint32_t)misc[0];
+
+  if (threadIdx.x == 0) {
+    mbar_expect_tx(bar_full, NP * (kA + kB));
+#pragma unroll
+    for (int pn = 0; pn < NP; ++pn) {
+      tma_load_4d(sbase + offA + pn * kA, &tm_x, pn * 64, h, tile * kTcTok, b, bar_full);
+      tma_load_3d(sbase + offB + pn * kB, &tm_c, pn * 64, 0, bh, bar_full);
+    }
+    if (mbar_wait(bar_full, 0, abort_flag, nullptr, 1)) {
+      tc_fence_after();
+      const uint32_t idesc = make_idesc_bf16(kTcCen);
+      bool first = true;
+#pragma unroll
+      for (int pc = 0; pc < 3; ++pc)
+#pragma unroll
+        for (int pn = 0; pn < NP; ++pn) {
+          const uint64_t da = make_desc(sbase + offA + pn * kA, 128);
+          const uint64_t db = make_desc(sbase + offB + pn * kB + pc * (kTcCen * 128), 128);
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks) {
+            mma_bf16_ss(tmem, da + (uint64_t)(ks * 2), db + (uint64_t)(ks * 2), idesc, first ? 0u : 1u);
+            first = false;
+          }
+        }
+      tc_commit(bar_done);
+    }
+  }
+  __syncwarp();
+  // thread == token == TMEM lane
+  const bool ok = mbar_wait(bar_done, 0, abort_flag, nullptr, 2);
+  const bool all_ok = __all_sync(0xffffffffu, ok);
+  if (all_ok) {
+    tc_fence_after();
+    const uint32_t trow = tmem + ((uint32_t)(warp * 32) << 16);
+    uint32_t r0[32], r1[32];
+    LBFQ_TMEM_LD32(r0, trow);
+    LBFQ_TMEM_LD32(r1, trow + 32);
+    tc_wait_ld();
+    const float* cn = cnorm + (size_t)bh * k;
+    float best = INFINITY;
+    int best_i = 0;
+#pragma unroll
+    for (int c = 0; c < 32; ++c) {
+      if (c < k) {
+        const float dist = cn[c] - 2.0f * __uint_as_float(r0[c]);
+        if (dist < best) { best = dist; best_i = c; }          // ascending c: lowest index wins ties
+      }
+    }
+#pragma unroll
+    for (int c = 0; c < 32; ++c) {
+      if (32 + c < k) {
+        const float dist = cn[32 + c] - 2.0f * __uint_as_float(r1[c]);
+        if (dist < best) { best = dist; best_i = 32 + c; }
+      }
+    }
+    const int tok = tile * kTcTok + warp * 32 + lane;
+    if (tok < S) labels[(size_t)bh * S + tok] = best_i;
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 64;" ::"r"(tmem) : "memory");
+  }
+}
+
+PFN_cuTensorMapEncodeTiled_v12000 encoder() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = (PFN_cuTensorMapEncodeTiled_v12000)ptr;
+  }
+  return fn;
+}
+
+template <int D>
+int launch_assign(const CUtensorMap& mx, const CUtensorMap& mc, int BH, int S, int H, int k, const float* cnorm,
+                  int32_t* labels, cudaStream_t st) {
+  constexpr int NP = D / 64;
+  const int smem_bytes = NP * (kTcTok * 128 + 3 * kTcCen * 128) + 64 + 1024;
+  auto kern = assign_tc_kernel<D>;
+  LBFQ_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+  const int ntile = (S + kTcTok - 1) / kTcTok;
+  kern<<<BH * ntile, 128, smem_bytes, st>>>(mx, mc, S, H, k, cnorm, labels);
+  return check_launch("kmeans assign (tensor cores)");
+}
+
+}  // namespace
+
+bool kmeans_tc_eligible(int dtype, int D, int k) { return dtype == LBFQ_BF16 && (D == 64 || D == 128) && k <= kTcCen; }
+
+size_t kmeans_tc_split_bytes(int BH, int D) { return (size_t)BH * 3 * kTcCen * D * sizeof(__nv_bfloat16); }
+
+int kmeans_tc_assign(const void* x, int B, int S, int H, int D, int k, const float* cent, const float* cnorm,
+                     void* split, int32_t* labels, cudaStream_t st) {
+  const int BH = B * H;
+  const size_t total = (size_t)BH * kTcCen * D;
+  int g = (int)((total + 255) / 256);
+  if (g > 148 * 8) g = 148 * 8;
+  split_centroids_kernel<<<g, 256, 0, st>>>(cent, BH, k, D, (__nv_bfloat16*)split);
+  if (int rc = check_launch("kmeans centroid split")) return rc;
+
+  auto enc = encoder();
+  LBFQ_REQUIRE(enc != nullptr, LBFQ_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  CUtensorMap mx, mc;
+  {
+    // tokens: x is (B, S, H, D) bf16
+    cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)H, (cuuint64_t)S, (cuuint64_t)B};
+    cuuint64_t strides[3] = {(cuuint64_t)D * 2, (cuuint64_t)H * D * 2, (cuuint64_t)S * H * D * 2};
+    cuuint32_t box[4] = {64, 1, (cuuint32_t)kTcTok, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = enc(&mx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(x), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    LBFQ_REQUIRE(r == CUDA_SUCCESS, LBFQ_ERR_CUDA, "cuTensorMapEncodeTiled (tokens) failed with code %d", (int)r);
+  }
+  {
+    // centroid pieces: (BH, 3 * 64, D) bf16
+    cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)(3 * kTcCen), (cuuint64_t)BH};
+    cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)3 * kTcCen * D * 2};
+    cuuint32_t box[3] = {64, (cuuint32_t)(3 * kTcCen), 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = enc(&mc, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, split, dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    LBFQ_REQUIRE(r == CUDA_SUCCESS, LBFQ_ERR_CUDA, "cuTensorMapEncodeTiled (centroids) failed with code %d", (int)r);
+  }
+  if (D == 128) return launch_assign<128>(mx, mc, BH, S, H, k, cnorm, labels, st);
+  return launch_assign<64>(mx, mc, BH, S, H, k, cnorm, labels, st);
+}
+
+}  // namespace lbfq

@@ -173,6 +173,21 @@ def test_kmeans_labels_invariants_and_oracle_agreement():
     assert torch.equal(g3, g1[1::2])
 
 
+@pytest.mark.parametrize("k,D", [(32, 128), (64, 128), (5, 64)])
+def test_kmeans_tensor_core_assignment_agrees_with_fp32_assignment(k, D, monkeypatch):
+    """BF16 tokens take the tensor-core assignment (centroids split into three BF16 pieces); the FP32 FFMA
+    assignment is the cross-check. They differ only in summation order, i.e. on near-ties."""
+    torch.manual_seed(k + D)
+    x = (torch.randn(2, 1000, 3, D) + 2.0 * torch.randn(1, 1, 3, D)).bfloat16().to(DEV)      # ragged last tile
+    monkeypatch.delenv("LBFQ_KMEANS_FFMA", raising=False)
+    tc = kmeans_labels(x, n_clusters=k, max_iters=5, seed=1)
+    assert torch.equal(tc, kmeans_labels(x, n_clusters=k, max_iters=5, seed=1))               # reproducible
+    monkeypatch.setenv("LBFQ_KMEANS_FFMA", "1")
+    ff = kmeans_labels(x, n_clusters=k, max_iters=5, seed=1)
+    assert int(tc.min()) >= 0 and int(tc.max()) < k
+    assert (tc == ff).float().mean().item() > 0.995
+
+
 def test_qm_corr_and_rowmax():
     torch.manual_seed(10)
     qm = torch.randn(2, 3, 2, 128)
