@@ -58,13 +58,15 @@ struct FastSmem {
   static constexpr int offK = offQ + 2 * kQ;
   static constexpr int offV = offK + kFastStages * kK;
   static constexpr int offBar = offV + kFastStages * kV;
-  static constexpr int kNumBar = 2 + 4 * kFastStages + 4 + 2 + 2 + 2;
+  static constexpr int kNumBar = 2 + 4 * kFastStages + 4 + 2 + 2 + 2 + 2 * kFastStages;
   static constexpr int offMisc = offBar + kNumBar * 8;
   static constexpr int offL = offMisc + 64;                    // row sums of the two column halves [tile][half][row]
-  static constexpr int total = offL + 2 * 2 * kTileM * 4;
+  // score-bias rows (`corr`) of each tile's Q group, staged per 128-key stage by the producer
+  static constexpr int offCorr = offL + 2 * 2 * kTileM * 4;
+  static constexpr int total = offCorr + kFastStages * 2 * kChunk * 4;
 };
 
-template <int D, int BN>
+template <int D, int BN, bool CORR>
 __global__ void __launch_bounds__(kFastThreads, 1)
 attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                  const __grid_constant__ CUtensorMap tm_v, const Params p) {
@@ -89,6 +91,8 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   auto BAR_PRDY = [&](int t) { return bar0 + 8u * (2 + 4 * kFastStages + 4 + t); };
   auto BAR_PENULT = [&](int t) { return bar0 + 8u * (2 + 4 * kFastStages + 6 + t); };   // P.V of block nblk - 2 done
   auto BAR_ODONE = [&](int t) { return bar0 + 8u * (2 + 4 * kFastStages + 8 + t); };    // P.V of the last block done
+  auto BAR_SIDEFULL = [&](int s) { return bar0 + 8u * (2 + 4 * kFastStages + 10 + s); };
+  auto BAR_SIDEFREE = [&](int s) { return bar0 + 8u * (2 + 4 * kFastStages + 10 + kFastStages + s); };
   volatile int* misc = (volatile int*)(smem + SM::offMisc);   // [0] tmem base, [1] abort, [6] early exit
   volatile int* abort_flag = misc + 1;
 
@@ -121,6 +125,8 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       mbar_init(BAR_VFULL(s), 1);
       mbar_init(BAR_KFREE(s), 2);
       mbar_init(BAR_VFREE(s), 2);
+      mbar_init(BAR_SIDEFULL(s), 1);
+      mbar_init(BAR_SIDEFREE(s), kFastSoftmaxWarps * 32);
     }
     misc[1] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -150,10 +156,15 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const float sq = p.q_scale[((size_t)b * (p.M / p.qk_block) + rowc / p.qk_block) * p.H + h];
     const float* ksc = p.k_scale + (size_t)b * (p.N / p.qk_block) * p.H + h;
     const bool frozen = p.rm_mode == 1;
-    // running max in the log2 domain (the reference's m_i times log2e)
+    // running max: in the log2 domain (the reference's m_i times log2e) without a score bias; with one the
+    // scores are formed as the reference forms them, dot * f + corr, and the max stays in their own units
+    constexpr float kDom = CORR ? 1.0f : kLog2e;
     float m2 = -INFINITY;
-    if (p.rowmax_est) m2 = p.rowmax_est[(size_t)bh * p.M + rowc] * kLog2e;
-    else if (p.rowmax_init) m2 = p.rowmax_init[(size_t)bh * p.M + rowc] * kLog2e;
+    if (p.rowmax_est) m2 = p.rowmax_est[(size_t)bh * p.M + rowc] * kDom;
+    else if (p.rowmax_init) m2 = p.rowmax_init[(size_t)bh * p.M + rowc] * kDom;
+    const float* corr_sm = reinterpret_cast<const float*>(smem + SM::offCorr) + t * kChunk;
+    int side_sub = 0, side_stage = 0;
+    uint32_t side_par = 0;
     float l_i = 0.f;                                           // row sum over this thread's columns
     float sk = ksc[0];
     const int blocks_per_scale = p.qk_block / BN;               // fp8_block_size is a multiple of block_n
@@ -185,13 +196,34 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       tmem_ld(mine, tS_mine[BUF]);
       tmem_ld(oth, tS_oth[BUF]);
       tc_wait_ld();
-      // (sq * sk) * sm_scale in the reference's order, then into the log2 domain
-      const float c = ((sq * sk) * sm_scale) * kLog2e;
+      // (sq * sk) * sm_scale in the reference's order; without a score bias straight into the log2 domain
+      const float f = (sq * sk) * sm_scale;
+      const float c = CORR ? 1.0f : f * kLog2e;
       const bool more = it != last;
       if (++scale_sub == blocks_per_scale) {   // next block's scale, off the critical path
         scale_sub = 0;
         ksc += k_stride;
         if (more) sk = *ksc;
+      }
+      if constexpr (CORR) {
+        // scores = dot * f + corr (attention_triton.py:154-160), all 64 columns: the max needs them
+        if (side_sub == 0) mbar_wait_cont(BAR_SIDEFULL(side_stage), side_par, abort_flag, p.status, 15);
+        const float* crow = corr_sm + side_stage * (2 * kChunk) + side_sub * BN;
+        const float4* cm = reinterpret_cast<const float4*>(crow + half * HB);
+        const float4* co = reinterpret_cast<const float4*>(crow + (1 - half) * HB);
+        const float2 f2 = make_float2(f, f);
+#pragma unroll
+        for (int i = 0; i < HB / 4; ++i) {
+          const float4 a = cm[i], o = co[i];               // same address in every lane: broadcast loads
+          const float2 m01 = __ffma2_rn(make_float2(__uint_as_float(mine[4 * i]), __uint_as_float(mine[4 * i + 1])), f2, make_float2(a.x, a.y));
+          const float2 m23 = __ffma2_rn(make_float2(__uint_as_float(mine[4 * i + 2]), __uint_as_float(mine[4 * i + 3])), f2, make_float2(a.z, a.w));
+          const float2 o01 = __ffma2_rn(make_float2(__uint_as_float(oth[4 * i]), __uint_as_float(oth[4 * i + 1])), f2, make_float2(o.x, o.y));
+          const float2 o23 = __ffma2_rn(make_float2(__uint_as_float(oth[4 * i + 2]), __uint_as_float(oth[4 * i + 3])), f2, make_float2(o.z, o.w));
+          mine[4 * i] = __float_as_uint(m01.x); mine[4 * i + 1] = __float_as_uint(m01.y);
+          mine[4 * i + 2] = __float_as_uint(m23.x); mine[4 * i + 3] = __float_as_uint(m23.y);
+          oth[4 * i] = __float_as_uint(o01.x); oth[4 * i + 1] = __float_as_uint(o01.y);
+          oth[4 * i + 2] = __float_as_uint(o23.x); oth[4 * i + 3] = __float_as_uint(o23.y);
+        }
       }
       if (!more && tail_valid < BN) {          // ragged tail: only the last block of a sequence
 #pragma unroll
@@ -211,18 +243,26 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 
       // ---- running max / rescale factor (attention_triton.py:164-217) ----------
       const float m_new = frozen ? m2 : fmaxf(m2, bmax);
-      const float alpha = frozen ? 1.f : ex2(m2 - m_new);
+      const float alpha = frozen ? 1.f : ex2(CORR ? (m2 - m_new) * kLog2e : m2 - m_new);
       // ---- P = exp2(dot * c - m + off), l += sum(P) (attention_triton.py:219-326) ----
       // masked columns hold -inf, so their exp2 is exactly 0 without a select
-      const float bias = p_off - m_new;
-      // two columns per instruction: fma.rn.f32x2 / add.rn.f32x2 round each half exactly like the scalar forms
-      const float2 c2 = make_float2(c, c), bias2 = make_float2(bias, bias);
+      // two columns per instruction: fma.rn.f32x2 / add.rn.f32x2 round each half exactly like the scalar forms.
+      // Without a score bias: exp2(dot * c + (off - m)). With one: exp2((score - m) * log2e + off), the
+      // reference's own sequence.
+      const float bias = CORR ? -m_new : p_off - m_new;
+      const float2 c2 = make_float2(CORR ? kLog2e : c, CORR ? kLog2e : c);
+      const float2 bias2 = make_float2(bias, bias), off2 = make_float2(p_off, p_off);
+      auto arg = [&](uint32_t x0, uint32_t x1) -> float2 {
+        const float2 v = make_float2(__uint_as_float(x0), __uint_as_float(x1));
+        if constexpr (CORR) return __ffma2_rn(__fadd2_rn(v, bias2), c2, off2);
+        else return __ffma2_rn(v, c2, bias2);
+      };
       float2 psa = make_float2(0.f, 0.f), psb = make_float2(0.f, 0.f);
       uint32_t pk[HB / 4];
 #pragma unroll
       for (int i = 0; i < HB; i += 4) {
-        const float2 za = __ffma2_rn(make_float2(__uint_as_float(mine[i]), __uint_as_float(mine[i + 1])), c2, bias2);
-        const float2 zb = __ffma2_rn(make_float2(__uint_as_float(mine[i + 2]), __uint_as_float(mine[i + 3])), c2, bias2);
+        const float2 za = arg(mine[i], mine[i + 1]);
+        const float2 zb = arg(mine[i + 2], mine[i + 3]);
         const float2 pa = make_float2(ex2(za.x), ex2(za.y));
         const float2 pb = make_float2(ex2(zb.x), ex2(zb.y));
         psa = __fadd2_rn(psa, pa);
@@ -265,6 +305,14 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       tc_fence_before();
       mbar_arrive(bar_prdy);
       m2 = m_new;
+      if constexpr (CORR) {
+        // the stage's bias rows are dead once its last key block has read them
+        if (side_sub == NSUB - 1 || !more) mbar_arrive(BAR_SIDEFREE(side_stage));
+        if (++side_sub == NSUB) {
+          side_sub = 0;
+          if (++side_stage == kFastStages) { side_stage = 0; side_par ^= 1u; }
+        }
+      }
     };
     {
       int it = 0;
@@ -365,6 +413,15 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         }
         mbar_expect_tx(BAR_VFULL(st), SM::kV);
         tma_load_3d(sbase + SM::offV + st * SM::kV, &tm_v, c * kChunk, 0, bh, BAR_VFULL(st));
+        if constexpr (CORR) {
+          if (c >= kFastStages && !mbar_wait(BAR_SIDEFREE(st), ((c / kFastStages) - 1) & 1, abort_flag, p.status, 23)) break;
+          mbar_expect_tx(BAR_SIDEFULL(st), 2 * kChunk * 4);
+          for (int t = 0; t < 2; ++t) {
+            const int g = min((m0 + t * kTileM) / p.q_smooth_block, p.n_groups - 1);
+            bulk_load(sbase + SM::offCorr + (st * 2 + t) * (kChunk * 4),
+                      p.corr + ((size_t)bh * p.n_groups + g) * p.corr_stride + (size_t)c * kChunk, kChunk * 4, BAR_SIDEFULL(st));
+          }
+        }
       }
     }
   } else if (warp == kMmaWarp0 || warp == kMmaWarp0 + 1) {
@@ -434,11 +491,11 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   }
 }
 
-template <int D, int BN>
+template <int D, int BN, bool CORR>
 int launch_fast_t(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const Params& p, cudaStream_t st) {
   using SM = FastSmem<D>;
   const int smem_bytes = SM::total + 1024;
-  auto kern = attn_fast_kernel<D, BN>;
+  auto kern = attn_fast_kernel<D, BN, CORR>;
   LBFQ_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
   dim3 grid((p.M + kCtaM - 1) / kCtaM, p.B * p.H, 1);
   kern<<<grid, kFastThreads, smem_bytes, st>>>(mq, mk, mv, p);
@@ -450,14 +507,19 @@ int launch_fast_t(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMa
 bool fast_eligible(const Params& p, int block_n, bool blasst, bool qk_mx) {
   (void)block_n;
   return !blasst && !qk_mx && p.q_scale != nullptr && p.k_scale != nullptr && p.p_kind == LBFQ_P_ELEMENTWISE &&
-         p.v_kind == LBFQ_V_CHANNEL && p.v_alpha == nullptr && p.corr == nullptr && (p.rm_mode == 0 || p.rm_mode == 1) &&
-         p.sm_scale > 0.f;
+         p.v_kind == LBFQ_V_CHANNEL && p.v_alpha == nullptr && (p.corr == nullptr || p.corr_staged != 0) &&
+         (p.rm_mode == 0 || p.rm_mode == 1) && p.sm_scale > 0.f;
 }
 
 int launch_fast(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const Params& p, int block_n,
                 cudaStream_t st) {
-  if (p.D == 128) return block_n == 64 ? launch_fast_t<128, 64>(mq, mk, mv, p, st) : launch_fast_t<128, 32>(mq, mk, mv, p, st);
-  return block_n == 64 ? launch_fast_t<64, 64>(mq, mk, mv, p, st) : launch_fast_t<64, 32>(mq, mk, mv, p, st);
+#define LBFQ_FAST(DD, NN) \
+  return p.corr != nullptr ? launch_fast_t<DD, NN, true>(mq, mk, mv, p, st) : launch_fast_t<DD, NN, false>(mq, mk, mv, p, st)
+  if (p.D == 128 && block_n == 64) { LBFQ_FAST(128, 64); }
+  if (p.D == 128) { LBFQ_FAST(128, 32); }
+  if (block_n == 64) { LBFQ_FAST(64, 64); }
+  LBFQ_FAST(64, 32);
+#undef LBFQ_FAST
 }
 
 }  // namespace attn

@@ -257,13 +257,19 @@ def _fast_and_general(q, k, v, cfg, monkeypatch):
     (960, 128, 32, {}),
     (1024, 64, 32, dict(p_max_offset=0)),
     (4096, 128, 64, dict(fp8_block_size=128)),             # more key blocks than pipeline stages several times over
+    (2048, 128, 64, dict(smoothing="full")),               # score bias qm.K_smooth staged through shared memory
+    (1792, 64, 32, dict(smoothing="full", rowmax_mode="qm_k")),          # ... with the row max frozen to its estimate
+    (1024, 128, 64, dict(smoothing="full", q_kmeans_k=8, fp8_block_size=128)),   # ... and rows scattered back through `order`
 ])
 def test_tmem_resident_variant_matches_oracle_and_general_kernel(S, D, bn, extra, monkeypatch):
     kw = {**COMMON, **dict(smoothing="k_only", q_kmeans_k=None, p_requant_block_m=bn, p_requant_block_n=bn), **extra}
     cfg = QuantConfig(**kw)
     q, k, v = _qkv(2, S, 3, D, seed=S + D + bn)
     fast, gen = _fast_and_general(q, k, v, cfg, monkeypatch)
-    o = OA.fake_quant_attention(q, k, v, cfg, faithful=False, out_fp32=True)
+    ql = None
+    if cfg.q_kmeans_k is not None:                         # k-means labels are not pinned: hand the GPU's to the oracle
+        ql = fq.prepare_for_attention(q.to(DEV), k.to(DEV), v.to(DEV), cfg).q_kmeans.labels.cpu()
+    o = OA.fake_quant_attention(q, k, v, cfg, faithful=False, out_fp32=True, q_labels=ql)
     _check(fast, o, (q, k, v))
     _check(gen, o, (q, k, v))
     assert OA.parity_ok(OA.parity_report(fast, gen, q, k, v))
