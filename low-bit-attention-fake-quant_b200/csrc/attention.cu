@@ -762,6 +762,22 @@ static int make_map(CUtensorMap* map, const void* base, uint64_t inner, uint64_t
   return LBFQ_OK;
 }
 
+// 3-D bf16 tensor map: dims (inner, rows, slabs) in elements, box (box_inner <= 64 elements, box_rows, 1), 128B swizzle
+static int make_map_bf16(CUtensorMap* map, const void* base, uint64_t inner, uint64_t rows, uint64_t slabs,
+                         uint32_t box_inner, uint32_t box_rows) {
+  auto enc = get_encode();
+  LBFQ_REQUIRE(enc != nullptr, LBFQ_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t dims[3] = {inner, rows, slabs};
+  cuuint64_t strides[2] = {inner * 2, inner * rows * 2};
+  cuuint32_t box[3] = {box_inner, box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  LBFQ_REQUIRE(r == CUDA_SUCCESS, LBFQ_ERR_CUDA, "cuTensorMapEncodeTiled (bf16) failed with code %d", (int)r);
+  return LBFQ_OK;
+}
+
 template <int D, int BN, bool BLASST, bool QKMX>
 static int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const Params& p, cudaStream_t st) {
   using SM = Smem<D, BN>;
@@ -800,12 +816,51 @@ __global__ void alpha_prep_kernel(const float* __restrict__ alpha, float* __rest
   }
 }
 
+// V^T codes (B*H, D, n_pad) e4m3 -> BF16 of the same layout for the BF16 P.V of the TMEM-resident kernel: the codes
+// themselves (per-channel V: the channel scale is applied in the epilogue) or codes * 2^e (mxfp8 V: exact in BF16,
+// the operand the reference builds at attention.py:571-586)
+__global__ void v_codes_to_bf16_kernel(const uint8_t* __restrict__ codes, __nv_bfloat16* __restrict__ out, int v_kind,
+                                       const float* __restrict__ vscale, int B, int H, int D, int N, int n_pad, int v_block) {
+  const size_t total8 = (size_t)B * H * D * n_pad / 8;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total8; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t e0 = i * 8;
+    const int key0 = (int)(e0 % n_pad);
+    const int d = (int)((e0 / n_pad) % D);
+    const int bh = (int)(e0 / n_pad / D);
+    const uint2 raw = *reinterpret_cast<const uint2*>(codes + e0);
+    const uint8_t* c8 = reinterpret_cast<const uint8_t*>(&raw);
+    float sc = 1.f;
+    if (v_kind == LBFQ_V_MX) {
+      const int b = bh / H, h = bh % H;
+      const int blk = min(key0, N - 1) / v_block;              // 8 consecutive keys never straddle a block
+      sc = vscale[(((size_t)b * (N / v_block) + blk) * H + h) * D + d];
+    }
+    __align__(16) __nv_bfloat16 o[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = __float2bfloat16_rn(e4m3_to_f32(c8[j]) * sc);
+    *reinterpret_cast<uint4*>(out + e0) = *reinterpret_cast<const uint4*>(o);
+  }
+}
+
+static size_t align256(size_t v) { return (v + 255) / 256 * 256; }
+static size_t alpha_ws_bytes(const lbfq_attn_args* a) {
+  if (!a->v_alpha) return 0;
+  return align256((size_t)a->B * (a->N / (a->v_smooth_block > 0 ? a->v_smooth_block : 1)) * a->H * a->D * 4);
+}
+// mx / dynamic P on FP8-block Q/K may take the BF16-P kernel, which wants a BF16 copy of V^T in the workspace
+static bool may_want_v_bf16(const lbfq_attn_args* a) {
+  return a->p_kind != LBFQ_P_ELEMENTWISE && a->v_kind != LBFQ_V_BLOCK && !a->use_blasst && a->qk_kind == LBFQ_QK_FP8_BLOCK &&
+         !a->v_alpha;
+}
+
 static thread_local int g_last_variant = 0;
 extern "C" int lbfq_attention_last_variant(void) { return g_last_variant; }
 
 extern "C" int64_t lbfq_attention_workspace_bytes(const lbfq_attn_args* a) {
-  if (!a || !a->v_alpha) return 0;
-  return (int64_t)a->B * (a->N / (a->v_smooth_block > 0 ? a->v_smooth_block : 1)) * a->H * a->D * 4;
+  if (!a) return 0;
+  size_t bytes = alpha_ws_bytes(a);
+  if (may_want_v_bf16(a)) bytes += align256((size_t)a->B * a->H * a->D * a->n_pad * 2);
+  return (int64_t)bytes;
 }
 
 extern "C" int lbfq_attention_fwd(const lbfq_attn_args* a, void* workspace, void* stream) {
@@ -915,9 +970,23 @@ extern "C" int lbfq_attention_fwd(const lbfq_attn_args* a, void* workspace, void
   // LBFQ_ATTN_GENERIC=1 keeps every configuration on the general kernel (used to cross-check the two)
   const char* force_generic = getenv("LBFQ_ATTN_GENERIC");
   g_last_variant = 0;
-  if (!(force_generic && force_generic[0] == '1') && fast_eligible(p, a->block_n, bl, mx)) {
+  const int fv = (force_generic && force_generic[0] == '1') ? 0 : fast_variant(p, bl, mx);
+  if (fv == 1) {
     g_last_variant = 1;
-    return launch_fast(mq, mk, mv, p, a->block_n, st);
+    return launch_fast(mq, mk, mv, p, a->block_n, 1, st);
+  }
+  if (fv == 2 && may_want_v_bf16(a)) {
+    LBFQ_REQUIRE(workspace != nullptr, LBFQ_ERR_ARG, "this configuration needs the workspace of lbfq_attention_workspace_bytes");
+    __nv_bfloat16* vb = reinterpret_cast<__nv_bfloat16*>((uint8_t*)workspace + alpha_ws_bytes(a));
+    const size_t total8 = (size_t)a->B * a->H * a->D * a->n_pad / 8;
+    int g = (int)((total8 + 255) / 256); if (g > 148 * 16) g = 148 * 16;
+    v_codes_to_bf16_kernel<<<g, 256, 0, st>>>((const uint8_t*)a->v_codes, vb, a->v_kind, a->v_scale, a->B, a->H, a->D, a->N,
+                                              a->n_pad, p.v_block);
+    if (int rc = check_launch("v_codes_to_bf16")) return rc;
+    CUtensorMap mvb;
+    if (int rc = make_map_bf16(&mvb, vb, a->n_pad, a->D, BH, 64, a->D)) return rc;
+    g_last_variant = 1;
+    return launch_fast(mq, mk, mvb, p, a->block_n, 2, st);
   }
 #define LBFQ_LAUNCH(DD, NN, MX)                                                                    \
   return bl ? launch<DD, NN, true, MX>(mq, mk, mv, p, st) : launch<DD, NN, false, MX>(mq, mk, mv, p, st)

@@ -35,7 +35,6 @@ namespace attn {
 
 namespace {
 
-constexpr int kFastStages = 4;
 // Two threads per query row: the pair reads the same S block, both take its maximum (so they never have to
 // talk to each other), and each computes the exponentials, the P codes and the accumulator rescale of one
 // half of the columns. 16 softmax warps give every scheduler four of them to hide each other's waits.
@@ -49,28 +48,33 @@ static_assert(kFastSoftmaxWarps * 32 * kFastRegsSoftmax + 4 * 32 * kFastRegsServ
               "setmaxnreg requests exceed the CTA's register pool");
 static_assert(kFastRegsSoftmax % 8 == 0 && kFastRegsService % 8 == 0, "setmaxnreg granularity");
 
-template <int D>
+// PK = 0: P as e4m3 codes, P.V an FP8 MMA over the V^T codes (4 key stages).
+// PK = 1: P re-scaled and rounded to BF16 as the reference does for its mx / dynamic P modes, P.V a BF16 MMA
+//         over a BF16 copy of V^T (3 key stages: a V stage is twice as large).
+template <int D, int PK>
 struct FastSmem {
+  static constexpr int kStages = PK ? 3 : 4;
   static constexpr int kQ = kTileM * D;                       // bytes per Q tile
   static constexpr int kK = kChunk * D;                       // bytes per K stage
-  static constexpr int kV = D * kChunk;                       // bytes per V^T stage
+  static constexpr int kV = D * kChunk * (PK ? 2 : 1);        // bytes per V^T stage
   static constexpr int offQ = 0;
   static constexpr int offK = offQ + 2 * kQ;
-  static constexpr int offV = offK + kFastStages * kK;
-  static constexpr int offBar = offV + kFastStages * kV;
-  static constexpr int kNumBar = 2 + 4 * kFastStages + 4 + 2 + 2 + 2 + 2 * kFastStages;
+  static constexpr int offV = offK + kStages * kK;
+  static constexpr int offBar = offV + kStages * kV;
+  static constexpr int kNumBar = 2 + 4 * kStages + 4 + 2 + 2 + 2 + 2 * kStages;
   static constexpr int offMisc = offBar + kNumBar * 8;
   static constexpr int offL = offMisc + 64;                    // row sums of the two column halves [tile][half][row]
   // score-bias rows (`corr`) of each tile's Q group, staged per 128-key stage by the producer
   static constexpr int offCorr = offL + 2 * 2 * kTileM * 4;
-  static constexpr int total = offCorr + kFastStages * 2 * kChunk * 4;
+  static constexpr int total = offCorr + kStages * 2 * kChunk * 4;
 };
 
-template <int D, int BN, bool CORR>
+template <int D, int BN, bool CORR, int PK>
 __global__ void __launch_bounds__(kFastThreads, 1)
 attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                  const __grid_constant__ CUtensorMap tm_v, const Params p) {
-  using SM = FastSmem<D>;
+  using SM = FastSmem<D, PK>;
+  constexpr int kFastStages = SM::kStages;
   constexpr int NSUB = kChunk / BN;                // key blocks per stage
   constexpr int TCOLS = 256;                       // TMEM columns per tile
   constexpr int COL_S = 0, S_STRIDE = 64, COL_O = 128;
@@ -156,6 +160,9 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const float sq = p.q_scale[((size_t)b * (p.M / p.qk_block) + rowc / p.qk_block) * p.H + h];
     const float* ksc = p.k_scale + (size_t)b * (p.N / p.qk_block) * p.H + h;
     const bool frozen = p.rm_mode == 1;
+    const bool thresholds = PK != 0 && p.rm_mode == 2;   // estimated row max corrected by the up-16 / down-32 rule (dynamic P only)
+    float max_seen = -INFINITY;
+    bool l_pos = false;                          // the row sum is positive (kept as a flag: each thread holds half of it)
     // running max: in the log2 domain (the reference's m_i times log2e) without a score bias; with one the
     // scores are formed as the reference forms them, dot * f + corr, and the max stays in their own units
     constexpr float kDom = CORR ? 1.0f : kLog2e;
@@ -170,7 +177,8 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const int blocks_per_scale = p.qk_block / BN;               // fp8_block_size is a multiple of block_n
     int scale_sub = 0;
     const uint32_t bar_sfull = BAR_SFULL(t, 0), bar_prdy = BAR_PRDY(t);
-    const float p_off = p.p_off, sm_scale = p.sm_scale;
+    const float p_off = PK ? 0.f : p.p_off, sm_scale = p.sm_scale;    // the offset belongs to element-wise P only
+    const bool p_mx = p.p_kind == LBFQ_P_MX;
     const int n_keys = p.N, k_stride = p.H;
 
     // Waits here never bail out (mbar_wait_cont): the warp stays convergent around the collective TMEM
@@ -179,7 +187,8 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     // every TMEM and barrier address in it is a loop-invariant register.
     const uint32_t tS_mine[2] = {tS + half * HB, tS + S_STRIDE + half * HB};
     const uint32_t tS_oth[2] = {tS + (1 - half) * HB, tS + S_STRIDE + (1 - half) * HB};
-    const uint32_t tP[2] = {tS + half * (HB / 4), tS + S_STRIDE + half * (HB / 4)};
+    constexpr int PW = PK ? HB / 2 : HB / 4;         // 32-bit words of P per thread: two BF16 or four e4m3 per word
+    const uint32_t tP[2] = {tS + half * PW, tS + S_STRIDE + half * PW};
     const uint32_t bar_s[2] = {bar_sfull, bar_sfull + 8u};
     const uint32_t bar_penult = BAR_PENULT(t);
     const int last = nblk - 1;
@@ -239,11 +248,28 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         bm0 = fmaxf(bm0, fmaxf(__uint_as_float(mine[i]), __uint_as_float(oth[i])));
         bm1 = fmaxf(bm1, fmaxf(__uint_as_float(mine[i + 1]), __uint_as_float(oth[i + 1])));
       }
-      const float bmax = fmaxf(bm0, bm1) * c;
+      const float bmax_raw = fmaxf(bm0, bm1);
+      const float bmax = bmax_raw * c;
 
       // ---- running max / rescale factor (attention_triton.py:164-217) ----------
-      const float m_new = frozen ? m2 : fmaxf(m2, bmax);
-      const float alpha = frozen ? 1.f : ex2(CORR ? (m2 - m_new) * kLog2e : m2 - m_new);
+      constexpr float kUp = CORR ? 16.0f / kLog2e : 16.0f, kDown = CORR ? 32.0f / kLog2e : 32.0f;
+      constexpr float kFloor = CORR ? 80.0f : 80.0f * kLog2e;
+      float m_new;
+      bool fresh = false;                      // thresholds mode, nothing accumulated yet: alpha = 0
+      bool moved = !frozen;
+      if (thresholds) {
+        const float seen = fmaxf(max_seen, bmax);
+        const bool under = (bmax - m2) > kUp;
+        const bool over = (m2 - seen) > kDown;
+        const float down_m = l_pos ? fmaxf(seen + kDown, m2 - kFloor) : seen;
+        moved = under || over;
+        m_new = moved ? (under ? bmax : down_m) : m2;
+        fresh = moved && !l_pos;
+        max_seen = seen;
+      } else {
+        m_new = frozen ? m2 : fmaxf(m2, bmax);
+      }
+      const float alpha = !moved ? 1.f : (fresh ? 0.f : ex2(CORR ? (m2 - m_new) * kLog2e : m2 - m_new));
       // ---- P = exp2(dot * c - m + off), l += sum(P) (attention_triton.py:219-326) ----
       // masked columns hold -inf, so their exp2 is exactly 0 without a select
       // two columns per instruction: fma.rn.f32x2 / add.rn.f32x2 round each half exactly like the scalar forms.
@@ -258,7 +284,26 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         else return __ffma2_rn(v, c2, bias2);
       };
       float2 psa = make_float2(0.f, 0.f), psb = make_float2(0.f, 0.f);
-      uint32_t pk[HB / 4];
+      uint32_t pk[PW];
+      // exp2 is monotonic: the largest P of the block is the P of the largest score, produced by the same
+      // instruction sequence as the elements, so it is bit-identical to max_i(P_i) -- and both threads of the
+      // row know it without talking to each other
+      float pmax = 1.f;
+      float s_p = 1.f, inv_p = 1.f;
+      if constexpr (PK != 0) {
+        if constexpr (CORR) pmax = ex2(fmaf(bmax - m_new, kLog2e, p_off));
+        else pmax = ex2(fmaf(bmax_raw, c, bias));
+        // P scale of the block (attention_triton.py:338-360): a power of two (mx) or amax / 448 (dynamic)
+        if (p_mx) {
+          const int e = pow2_scale_exp(fmaxf(pmax, 1e-4f));
+          s_p = pow2f(e);
+          inv_p = pow2f(-e);
+        } else {
+          s_p = __fdiv_rn(fmaxf(pmax, 1e-12f), kFp8Max);
+          inv_p = __fdiv_rn(1.0f, s_p);
+        }
+      }
+      const float2 inv2 = make_float2(inv_p, inv_p);
 #pragma unroll
       for (int i = 0; i < HB; i += 4) {
         const float2 za = arg(mine[i], mine[i + 1]);
@@ -267,10 +312,18 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         const float2 pb = make_float2(ex2(zb.x), ex2(zb.y));
         psa = __fadd2_rn(psa, pa);
         psb = __fadd2_rn(psb, pb);
-        // the conversion saturates at 448, which is the reference's clamp (attention_triton.py:328-336)
-        pk[i / 4] = f32x4_to_e4m3x4(pa.x, pa.y, pb.x, pb.y);
+        if constexpr (PK == 0) {
+          // the conversion saturates at 448, which is the reference's clamp (attention_triton.py:328-336)
+          pk[i / 4] = f32x4_to_e4m3x4(pa.x, pa.y, pb.x, pb.y);
+        } else {
+          // e4m3(p / s) * s, rounded to BF16: the operand the reference gives its P.V product
+          const float2 qa = __fmul2_rn(pa, inv2), qb = __fmul2_rn(pb, inv2);
+          pk[i / 2] = e4m3_round_scale_bf16x2(qa.x, qa.y, s_p);
+          pk[i / 2 + 1] = e4m3_round_scale_bf16x2(qb.x, qb.y, s_p);
+        }
       }
       l_i = l_i * alpha + ((psa.x + psa.y) + (psb.x + psb.y));
+      if constexpr (PK != 0) l_pos = pmax > 0.f || (l_pos && alpha != 0.f);
       if (it > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
         // Some row of this warp raised its max: the accumulator must be rescaled before this block's P.V,
         // and P.V of the previous block must have completed. S of the next block was issued behind that
@@ -299,7 +352,8 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           LBFQ_TMEM_ST32(tO + c0, r);
         }
       }
-      if constexpr (BN == 64) tmem_st8(tP[BUF], pk);
+      if constexpr (PW == 16) { LBFQ_TMEM_ST16(tP[BUF], pk); }
+      else if constexpr (PW == 8) tmem_st8(tP[BUF], pk);
       else tmem_st4(tP[BUF], pk);
       tc_wait_st();
       tc_fence_before();
@@ -412,7 +466,12 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           if (!mbar_wait(BAR_VFREE(st), par, abort_flag, p.status, 22)) break;
         }
         mbar_expect_tx(BAR_VFULL(st), SM::kV);
-        tma_load_3d(sbase + SM::offV + st * SM::kV, &tm_v, c * kChunk, 0, bh, BAR_VFULL(st));
+        if constexpr (PK == 0) {
+          tma_load_3d(sbase + SM::offV + st * SM::kV, &tm_v, c * kChunk, 0, bh, BAR_VFULL(st));
+        } else {                                      // BF16 V^T: two 64-key panels of D rows x 128 bytes
+          tma_load_3d(sbase + SM::offV + st * SM::kV, &tm_v, c * kChunk, 0, bh, BAR_VFULL(st));
+          tma_load_3d(sbase + SM::offV + st * SM::kV + D * 128, &tm_v, c * kChunk + 64, 0, bh, BAR_VFULL(st));
+        }
         if constexpr (CORR) {
           if (c >= kFastStages && !mbar_wait(BAR_SIDEFREE(st), ((c / kFastStages) - 1) & 1, abort_flag, p.status, 23)) break;
           mbar_expect_tx(BAR_SIDEFULL(st), 2 * kChunk * 4);
@@ -432,6 +491,7 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       const uint32_t tO = tmem_base + t * TCOLS + COL_O;
       const uint32_t id_qk = make_idesc(BN);
       const uint32_t id_pv = make_idesc(D);
+      const uint32_t id_pv_bf16 = make_idesc_bf16(D);
       const uint64_t dq = make_desc(sbase + SM::offQ + t * SM::kQ, D);
       bool ok = mbar_wait(BAR_QFULL(t), 0, abort_flag, p.status, 31);
       auto issue_qk = [&](int j) -> bool {
@@ -450,11 +510,22 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         const int c = j / NSUB, sub = j % NSUB, st = c % kFastStages;
         if (sub == 0 && !mbar_wait(BAR_VFULL(st), (c / kFastStages) & 1, abort_flag, p.status, 33)) return false;
         tc_fence_after();
-        const uint64_t dv = make_desc(sbase + SM::offV + st * SM::kV, kChunk);
+        if constexpr (PK == 0) {
+          const uint64_t dv = make_desc(sbase + SM::offV + st * SM::kV, kChunk);
 #pragma unroll
-        for (int kk = 0; kk < BN / 32; ++kk)
-          mma_f8_ts(tO, tS + (j & 1) * S_STRIDE + kk * 8, dv + (uint64_t)((sub * BN + kk * 32) >> 4), id_pv,
-                    (j > 0 || kk > 0) ? 1u : 0u);
+          for (int kk = 0; kk < BN / 32; ++kk)
+            mma_f8_ts(tO, tS + (j & 1) * S_STRIDE + kk * 8, dv + (uint64_t)((sub * BN + kk * 32) >> 4), id_pv,
+                      (j > 0 || kk > 0) ? 1u : 0u);
+        } else {
+          // keys sub * BN ... of the stage: panel (sub * BN) / 64, (sub * BN) % 64 keys = 2 bytes each into its rows
+          const int key0 = sub * BN;
+          const uint64_t dv = make_desc(sbase + SM::offV + st * SM::kV + (key0 >> 6) * (D * 128), 128) +
+                              (uint64_t)(((key0 & 63) * 2) >> 4);
+#pragma unroll
+          for (int kk = 0; kk < BN / 16; ++kk)
+            mma_bf16_ts(tO, tS + (j & 1) * S_STRIDE + kk * 8, dv + (uint64_t)(kk * 2), id_pv_bf16,
+                        (j > 0 || kk > 0) ? 1u : 0u);
+        }
         if (j == nblk - 2) tc_commit(BAR_PENULT(t));
         if (j == nblk - 1) tc_commit(BAR_ODONE(t));
         if (sub == NSUB - 1 || j == nblk - 1) tc_commit(BAR_VFREE(st));
@@ -491,11 +562,11 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   }
 }
 
-template <int D, int BN, bool CORR>
+template <int D, int BN, bool CORR, int PK>
 int launch_fast_t(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const Params& p, cudaStream_t st) {
-  using SM = FastSmem<D>;
+  using SM = FastSmem<D, PK>;
   const int smem_bytes = SM::total + 1024;
-  auto kern = attn_fast_kernel<D, BN, CORR>;
+  auto kern = attn_fast_kernel<D, BN, CORR, PK>;
   LBFQ_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
   dim3 grid((p.M + kCtaM - 1) / kCtaM, p.B * p.H, 1);
   kern<<<grid, kFastThreads, smem_bytes, st>>>(mq, mk, mv, p);
@@ -504,17 +575,22 @@ int launch_fast_t(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMa
 
 }  // namespace
 
-bool fast_eligible(const Params& p, int block_n, bool blasst, bool qk_mx) {
-  (void)block_n;
-  return !blasst && !qk_mx && p.q_scale != nullptr && p.k_scale != nullptr && p.p_kind == LBFQ_P_ELEMENTWISE &&
-         p.v_kind == LBFQ_V_CHANNEL && p.v_alpha == nullptr && (p.corr == nullptr || p.corr_staged != 0) &&
-         (p.rm_mode == 0 || p.rm_mode == 1) && p.sm_scale > 0.f;
+// 0: the general kernel; 1: TMEM-resident with e4m3 P (element-wise P); 2: TMEM-resident with BF16 P (mx / dynamic P,
+// needs a BF16 copy of V^T)
+int fast_variant(const Params& p, bool blasst, bool qk_mx) {
+  const bool common = !blasst && !qk_mx && p.q_scale != nullptr && p.k_scale != nullptr && p.v_alpha == nullptr &&
+                      (p.corr == nullptr || p.corr_staged != 0) && p.sm_scale > 0.f;
+  if (!common) return 0;
+  if (p.p_kind == LBFQ_P_ELEMENTWISE) return (p.v_kind == LBFQ_V_CHANNEL && (p.rm_mode == 0 || p.rm_mode == 1)) ? 1 : 0;
+  return (p.v_kind == LBFQ_V_CHANNEL || p.v_kind == LBFQ_V_MX) ? 2 : 0;
 }
 
 int launch_fast(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const Params& p, int block_n,
-                cudaStream_t st) {
-#define LBFQ_FAST(DD, NN) \
-  return p.corr != nullptr ? launch_fast_t<DD, NN, true>(mq, mk, mv, p, st) : launch_fast_t<DD, NN, false>(mq, mk, mv, p, st)
+                int variant, cudaStream_t st) {
+#define LBFQ_FAST(DD, NN)                                                                                         \
+  if (variant == 2)                                                                                               \
+    return p.corr != nullptr ? launch_fast_t<DD, NN, true, 1>(mq, mk, mv, p, st) : launch_fast_t<DD, NN, false, 1>(mq, mk, mv, p, st); \
+  return p.corr != nullptr ? launch_fast_t<DD, NN, true, 0>(mq, mk, mv, p, st) : launch_fast_t<DD, NN, false, 0>(mq, mk, mv, p, st)
   if (p.D == 128 && block_n == 64) { LBFQ_FAST(128, 64); }
   if (p.D == 128) { LBFQ_FAST(128, 32); }
   if (block_n == 64) { LBFQ_FAST(64, 64); }

@@ -146,6 +146,21 @@ __device__ __forceinline__ void mma_f8_ts(uint32_t d_tmem, uint32_t a_tmem, uint
       ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(acc) : "memory");
 }
 
+// kind::f16 with BF16 operands: D[tmem] (+)= A[smem desc] . B[smem desc]^T
+__device__ __forceinline__ void mma_bf16_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc) : "memory");
+}
+// ... with A read from tensor memory
+__device__ __forceinline__ void mma_bf16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(acc) : "memory");
+}
+
 #define LBFQ_TMEM_LD32(r, addr)                                                                            \
   asm volatile(                                                                                           \
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "                                                           \
@@ -176,6 +191,14 @@ __device__ __forceinline__ void mma_f8_ts(uint32_t d_tmem, uint32_t a_tmem, uint
         "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),     \
         "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),   \
         "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])    \
+      : "memory")
+
+#define LBFQ_TMEM_ST16(addr, r)                                                                            \
+  asm volatile(                                                                                           \
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "                                                     \
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"                          \
+      ::"r"(addr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), \
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])      \
       : "memory")
 
 template <int N>
@@ -212,6 +235,23 @@ __device__ __forceinline__ uint32_t f32x4_to_e4m3x4(float a, float b, float c, f
   return r;
 }
 
+// two FP32 -> e4m3 (round-to-nearest-even, saturating) -> times `scale` in FP32 -> two BF16 in one word (a low):
+// what the reference hands to its P.V product for the scaled P modes (attention_triton.py:338-360)
+__device__ __forceinline__ uint32_t e4m3_round_scale_bf16x2(float a, float b, float scale) {
+  uint32_t r;
+  asm("{\n\t.reg .b16 c, lo, hi;\n\t.reg .b32 h2;\n\t.reg .f32 fa, fb;\n\t"
+      "cvt.rn.satfinite.e4m3x2.f32 c, %2, %1;\n\t"
+      "cvt.rn.f16x2.e4m3x2 h2, c;\n\t"
+      "mov.b32 {lo, hi}, h2;\n\t"
+      "cvt.f32.f16 fa, lo;\n\t"
+      "cvt.f32.f16 fb, hi;\n\t"
+      "mul.rn.f32 fa, fa, %3;\n\t"
+      "mul.rn.f32 fb, fb, %3;\n\t"
+      "cvt.rn.bf16x2.f32 %0, fb, fa;\n\t}"
+      : "=r"(r) : "f"(a), "f"(b), "f"(scale));
+  return r;
+}
+
 __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -236,6 +276,10 @@ __host__ __device__ constexpr uint32_t make_idesc(int n) {
   return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
 }
 
+// kind::f16, A = B = BF16, FP32 accumulator, both operands K-major, M = 128
+__host__ __device__ constexpr uint32_t make_idesc_bf16(int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+}
 // kind::mxf8f6f4.block_scale, e4m3 x e4m3, UE8M0 scales, K-major operands, M = 128; `sf` = which byte of
 // the 32-bit scale columns (= which 32-wide K block) this instruction uses, for A and for B.
 __host__ __device__ constexpr uint32_t make_idesc_mx(int n, int sf) {
@@ -298,9 +342,9 @@ struct Params {
 #endif
 
 // attention_fast.cu: online-softmax variant whose output accumulator lives in tensor memory
-bool fast_eligible(const Params& p, int block_n, bool blasst, bool qk_mx);
+int fast_variant(const Params& p, bool blasst, bool qk_mx);
 int launch_fast(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const Params& p, int block_n,
-                cudaStream_t st);
+                int variant, cudaStream_t st);
 
 }  // namespace attn
 }  // namespace lbfq

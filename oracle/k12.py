@@ -93,6 +93,7 @@ def k12_attention(
     blasst_fill_alpha: float = 1.0,
     blasst_uta_bins: int = 16,
     faithful: Optional[bool] = None,
+    p_bf16: Optional[bool] = None,
     return_stats: bool = False,
 ):
     """Returns FP32 output (B,H,M,D) before the final cast (and stats)."""
@@ -100,6 +101,8 @@ def k12_attention(
     N = k_op.shape[2]
     if faithful is None:
         faithful = row_scale is None
+    if p_bf16 is None:            # the reference rounds the re-scaled P to BF16 before P.V (attention_triton.py:331-360)
+        p_bf16 = faithful
     pk = {"elementwise": 0, "mx": 1, "dynamic": 2}[p_quant_mode]
     use_blasst = blasst_lambda is not None
     if use_blasst:
@@ -258,7 +261,7 @@ def k12_attention(
             amax = p.abs().amax(dim=-1).clamp_min(1e-12)
             s_p = amax / _f32(FP8_MAX)
             p_rec = to_e4m3(p / s_p[..., None]).float() * s_p[..., None]
-        if faithful:
+        if p_bf16:
             p_rec = p_rec.to(torch.bfloat16).float()
 
         pv = torch.matmul(p_rec, v_op[:, :, n0:n1])                        # :363

@@ -48,7 +48,11 @@ def _run_both(q, k, v, cfg):
         pc = fq.prepare_for_attention(q.to(DEV), k.to(DEV), v.to(DEV), cfg)
         ql = pc.q_kmeans.labels.cpu() if pc.q_kmeans is not None else None
         vl = pc.v_kmeans.labels.cpu() if pc.v_kmeans is not None else None
-    o = OA.fake_quant_attention(q, k, v, cfg, faithful=False, out_fp32=True, q_labels=ql, v_labels=vl)
+    # the TMEM-resident kernel hands dynamic / mx P to the tensor core as the reference does: re-scaled and
+    # rounded to BF16 (exact for mx); the general kernel keeps the codes and applies the scale in FP32
+    from low_bit_fake_quant import _lib as L
+    p_bf16 = L.lib().lbfq_attention_last_variant() == 1 and cfg.p_requant
+    o = OA.fake_quant_attention(q, k, v, cfg, faithful=False, out_fp32=True, q_labels=ql, v_labels=vl, p_bf16=p_bf16)
     return g.float().cpu(), o
 
 
@@ -260,6 +264,10 @@ def _fast_and_general(q, k, v, cfg, monkeypatch):
     (2048, 128, 64, dict(smoothing="full")),               # score bias qm.K_smooth staged through shared memory
     (1792, 64, 32, dict(smoothing="full", rowmax_mode="qm_k")),          # ... with the row max frozen to its estimate
     (1024, 128, 64, dict(smoothing="full", q_kmeans_k=8, fp8_block_size=128)),   # ... and rows scattered back through `order`
+    (2048, 128, 64, dict(p_quant="dynamic")),              # P re-scaled and rounded to BF16, P.V a BF16 MMA
+    (1024, 64, 32, dict(p_quant="mx", p_mx_block_n=32)),
+    (1536, 128, 64, dict(smoothing="full", p_quant="dynamic", rowmax_mode="qm_k")),   # estimate + up / down thresholds
+    (1024, 128, 64, dict(v_quant="mxfp8", p_quant="auto")),                           # mxfp8 V folded into the BF16 copy
 ])
 def test_tmem_resident_variant_matches_oracle_and_general_kernel(S, D, bn, extra, monkeypatch):
     kw = {**COMMON, **dict(smoothing="k_only", q_kmeans_k=None, p_requant_block_m=bn, p_requant_block_n=bn), **extra}
@@ -270,9 +278,15 @@ def test_tmem_resident_variant_matches_oracle_and_general_kernel(S, D, bn, extra
     if cfg.q_kmeans_k is not None:                         # k-means labels are not pinned: hand the GPU's to the oracle
         ql = fq.prepare_for_attention(q.to(DEV), k.to(DEV), v.to(DEV), cfg).q_kmeans.labels.cpu()
     o = OA.fake_quant_attention(q, k, v, cfg, faithful=False, out_fp32=True, q_labels=ql)
-    _check(fast, o, (q, k, v))
     _check(gen, o, (q, k, v))
-    assert OA.parity_ok(OA.parity_report(fast, gen, q, k, v))
+    if kw.get("p_quant", "elementwise") == "dynamic":
+        # the variant rounds the re-scaled P to BF16 as the reference does; the general kernel keeps codes x FP32 scale
+        o_b = OA.fake_quant_attention(q, k, v, cfg, faithful=False, out_fp32=True, q_labels=ql, p_bf16=True)
+        _check(fast, o_b, (q, k, v))
+        assert OA.compute_metrics(fast, gen)["cosine"] > 0.99999
+    else:
+        _check(fast, o, (q, k, v))
+        assert OA.parity_ok(OA.parity_report(fast, gen, q, k, v))
 
 
 def test_tmem_resident_variant_with_peaked_rows(monkeypatch):
