@@ -842,15 +842,40 @@ __global__ void v_codes_to_bf16_kernel(const uint8_t* __restrict__ codes, __nv_b
   }
 }
 
+// alpha' (B, NB, H, D) fp32 -> (B, NB, H, D, 16) BF16: the three BF16 pieces h, m, l of each value laid out as
+// [h m l h m h 0 0] twice, the B operand rows of the K-extension step of P.V (see attention_fast.cu)
+__global__ void alpha_ext_kernel(const float* __restrict__ alpha, __nv_bfloat16* __restrict__ out, size_t total) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    float v = alpha[i];
+    const __nv_bfloat16 h = __float2bfloat16_rn(v);
+    v -= __bfloat162float(h);
+    const __nv_bfloat16 m = __float2bfloat16_rn(v);
+    v -= __bfloat162float(m);
+    const __nv_bfloat16 l = __float2bfloat16_rn(v);
+    const __nv_bfloat16 z = __float2bfloat16_rn(0.f);
+    __align__(16) __nv_bfloat16 o[16] = {h, m, l, h, m, h, z, z, h, m, l, h, m, h, z, z};
+    uint4* dst = reinterpret_cast<uint4*>(out + i * 16);
+    dst[0] = reinterpret_cast<const uint4*>(o)[0];
+    dst[1] = reinterpret_cast<const uint4*>(o)[1];
+  }
+}
+
 static size_t align256(size_t v) { return (v + 255) / 256 * 256; }
 static size_t alpha_ws_bytes(const lbfq_attn_args* a) {
   if (!a->v_alpha) return 0;
   return align256((size_t)a->B * (a->N / (a->v_smooth_block > 0 ? a->v_smooth_block : 1)) * a->H * a->D * 4);
 }
-// mx / dynamic P on FP8-block Q/K may take the BF16-P kernel, which wants a BF16 copy of V^T in the workspace
+// mx / dynamic P, or any P with the V-smoothing term, on FP8-block Q/K may take the BF16-P kernel, which wants a BF16
+// copy of V^T (and the alpha' pieces) in the workspace
 static bool may_want_v_bf16(const lbfq_attn_args* a) {
-  return a->p_kind != LBFQ_P_ELEMENTWISE && a->v_kind != LBFQ_V_BLOCK && !a->use_blasst && a->qk_kind == LBFQ_QK_FP8_BLOCK &&
-         !a->v_alpha;
+  return (a->p_kind != LBFQ_P_ELEMENTWISE || a->v_alpha) && a->v_kind != LBFQ_V_BLOCK && !a->use_blasst &&
+         a->qk_kind == LBFQ_QK_FP8_BLOCK;
+}
+static size_t v_bf16_ws_bytes(const lbfq_attn_args* a) {
+  return may_want_v_bf16(a) ? align256((size_t)a->B * a->H * a->D * a->n_pad * 2) : 0;
+}
+static size_t alpha_ext_ws_bytes(const lbfq_attn_args* a) {
+  return (may_want_v_bf16(a) && a->v_alpha) ? 8 * alpha_ws_bytes(a) : 0;      // 16 BF16 per FP32 value
 }
 
 static thread_local int g_last_variant = 0;
@@ -858,9 +883,7 @@ extern "C" int lbfq_attention_last_variant(void) { return g_last_variant; }
 
 extern "C" int64_t lbfq_attention_workspace_bytes(const lbfq_attn_args* a) {
   if (!a) return 0;
-  size_t bytes = alpha_ws_bytes(a);
-  if (may_want_v_bf16(a)) bytes += align256((size_t)a->B * a->H * a->D * a->n_pad * 2);
-  return (int64_t)bytes;
+  return (int64_t)(alpha_ws_bytes(a) + v_bf16_ws_bytes(a) + alpha_ext_ws_bytes(a));
 }
 
 extern "C" int lbfq_attention_fwd(const lbfq_attn_args* a, void* workspace, void* stream) {
@@ -973,7 +996,7 @@ extern "C" int lbfq_attention_fwd(const lbfq_attn_args* a, void* workspace, void
   const int fv = (force_generic && force_generic[0] == '1') ? 0 : fast_variant(p, bl, mx);
   if (fv == 1) {
     g_last_variant = 1;
-    return launch_fast(mq, mk, mv, p, a->block_n, 1, st);
+    return launch_fast(mq, mk, mv, mv, p, a->block_n, 1, st);
   }
   if (fv == 2 && may_want_v_bf16(a)) {
     LBFQ_REQUIRE(workspace != nullptr, LBFQ_ERR_ARG, "this configuration needs the workspace of lbfq_attention_workspace_bytes");
@@ -983,10 +1006,28 @@ extern "C" int lbfq_attention_fwd(const lbfq_attn_args* a, void* workspace, void
     v_codes_to_bf16_kernel<<<g, 256, 0, st>>>((const uint8_t*)a->v_codes, vb, a->v_kind, a->v_scale, a->B, a->H, a->D, a->N,
                                               a->n_pad, p.v_block);
     if (int rc = check_launch("v_codes_to_bf16")) return rc;
-    CUtensorMap mvb;
+    CUtensorMap mvb, ma;
     if (int rc = make_map_bf16(&mvb, vb, a->n_pad, a->D, BH, 64, a->D)) return rc;
+    ma = mvb;
+    if (a->v_alpha) {
+      __nv_bfloat16* ext = reinterpret_cast<__nv_bfloat16*>((uint8_t*)workspace + alpha_ws_bytes(a) + v_bf16_ws_bytes(a));
+      const size_t total = (size_t)a->B * (a->N / a->v_smooth_block) * a->H * a->D;
+      int ge = (int)((total + 255) / 256); if (ge > 148 * 16) ge = 148 * 16;
+      alpha_ext_kernel<<<ge, 256, 0, st>>>(p.v_alpha, ext, total);
+      if (int rc = check_launch("alpha_ext")) return rc;
+      // (16, D, B * NB * H) BF16, one (D x 16) tile per (b, smoothing block, h), 32-byte rows, 32B swizzle
+      auto enc = get_encode();
+      LBFQ_REQUIRE(enc != nullptr, LBFQ_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+      cuuint64_t dims[3] = {16, (cuuint64_t)a->D, (cuuint64_t)a->B * (a->N / a->v_smooth_block) * a->H};
+      cuuint64_t strides[2] = {32, (cuuint64_t)a->D * 32};
+      cuuint32_t box[3] = {16, (cuuint32_t)a->D, 1};
+      cuuint32_t estr[3] = {1, 1, 1};
+      CUresult r = enc(&ma, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, ext, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                       CU_TENSOR_MAP_SWIZZLE_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+      LBFQ_REQUIRE(r == CUDA_SUCCESS, LBFQ_ERR_CUDA, "cuTensorMapEncodeTiled (alpha pieces) failed with code %d", (int)r);
+    }
     g_last_variant = 1;
-    return launch_fast(mq, mk, mvb, p, a->block_n, 2, st);
+    return launch_fast(mq, mk, mvb, ma, p, a->block_n, 2, st);
   }
 #define LBFQ_LAUNCH(DD, NN, MX)                                                                    \
   return bl ? launch<DD, NN, true, MX>(mq, mk, mv, p, st) : launch<DD, NN, false, MX>(mq, mk, mv, p, st)

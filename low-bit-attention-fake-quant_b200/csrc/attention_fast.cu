@@ -66,13 +66,17 @@ struct FastSmem {
   static constexpr int offL = offMisc + 64;                    // row sums of the two column halves [tile][half][row]
   // score-bias rows (`corr`) of each tile's Q group, staged per 128-key stage by the producer
   static constexpr int offCorr = offL + 2 * 2 * kTileM * 4;
-  static constexpr int total = offCorr + kStages * 2 * kChunk * 4;
+  // V-smoothing tiles for the K-extension of P.V: per stage up to two (D x 16) BF16 tiles (32-byte rows)
+  static constexpr int kAext = D * 32;
+  static constexpr int offAext = (offCorr + kStages * 2 * kChunk * 4 + 1023) / 1024 * 1024;   // TMA destination, swizzled
+  static constexpr int total = offAext + (PK ? kStages * 2 * kAext : 0);
 };
 
-template <int D, int BN, bool CORR, int PK>
+template <int D, int BN, bool CORR, int PK, bool VALPHA>
 __global__ void __launch_bounds__(kFastThreads, 1)
 attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                 const __grid_constant__ CUtensorMap tm_v, const Params p) {
+                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_a, const Params p) {
+  static_assert(!VALPHA || PK == 1, "the V-smoothing term rides on the BF16 P.V");
   using SM = FastSmem<D, PK>;
   constexpr int kFastStages = SM::kStages;
   constexpr int NSUB = kChunk / BN;                // key blocks per stage
@@ -130,7 +134,7 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       mbar_init(BAR_KFREE(s), 2);
       mbar_init(BAR_VFREE(s), 2);
       mbar_init(BAR_SIDEFULL(s), 1);
-      mbar_init(BAR_SIDEFREE(s), kFastSoftmaxWarps * 32);
+      mbar_init(BAR_SIDEFREE(s), (CORR ? kFastSoftmaxWarps * 32 : 0) + (VALPHA ? 2 : 0) + ((CORR || VALPHA) ? 0 : 1));
     }
     misc[1] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -177,8 +181,8 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const int blocks_per_scale = p.qk_block / BN;               // fp8_block_size is a multiple of block_n
     int scale_sub = 0;
     const uint32_t bar_sfull = BAR_SFULL(t, 0), bar_prdy = BAR_PRDY(t);
-    const float p_off = PK ? 0.f : p.p_off, sm_scale = p.sm_scale;    // the offset belongs to element-wise P only
-    const bool p_mx = p.p_kind == LBFQ_P_MX;
+    const bool p_el = p.p_kind == LBFQ_P_ELEMENTWISE, p_mx = p.p_kind == LBFQ_P_MX;
+    const float p_off = p_el ? p.p_off : 0.f, sm_scale = p.sm_scale;  // the offset belongs to element-wise P only
     const int n_keys = p.N, k_stride = p.H;
 
     // Waits here never bail out (mbar_wait_cont): the warp stays convergent around the collective TMEM
@@ -189,6 +193,8 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const uint32_t tS_oth[2] = {tS + (1 - half) * HB, tS + S_STRIDE + (1 - half) * HB};
     constexpr int PW = PK ? HB / 2 : HB / 4;         // 32-bit words of P per thread: two BF16 or four e4m3 per word
     const uint32_t tP[2] = {tS + half * PW, tS + S_STRIDE + half * PW};
+    // K-extension columns of P (V-smoothing term): 16 BF16 = 8 columns behind the 32 columns of P, 4 per thread
+    const uint32_t tA[2] = {tS + 32 + half * 4, tS + S_STRIDE + 32 + half * 4};
     const uint32_t bar_s[2] = {bar_sfull, bar_sfull + 8u};
     const uint32_t bar_penult = BAR_PENULT(t);
     const int last = nblk - 1;
@@ -294,7 +300,9 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         if constexpr (CORR) pmax = ex2(fmaf(bmax - m_new, kLog2e, p_off));
         else pmax = ex2(fmaf(bmax_raw, c, bias));
         // P scale of the block (attention_triton.py:338-360): a power of two (mx) or amax / 448 (dynamic)
-        if (p_mx) {
+        if (p_el) {
+          // element-wise P keeps scale 1 (it takes this path when the V-smoothing term needs the BF16 P.V)
+        } else if (p_mx) {
           const int e = pow2_scale_exp(fmaxf(pmax, 1e-4f));
           s_p = pow2f(e);
           inv_p = pow2f(-e);
@@ -351,6 +359,24 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           }
           LBFQ_TMEM_ST32(tO + c0, r);
         }
+      }
+      if constexpr (VALPHA) {
+        // c_acc += rowsum(P) * alpha_v (attention_triton.py:378-383) as one more K step of P.V: this thread's part of
+        // the row sum of the BF16 P, split into three BF16 pieces, against the pieces of alpha' staged by the
+        // producer: (h + m + l) * (h' + m' + l') without the three smallest cross terms
+        float2 rs2 = make_float2(0.f, 0.f);
+#pragma unroll
+        for (int w = 0; w < PW; ++w)
+          rs2 = __fadd2_rn(rs2, make_float2(__uint_as_float(pk[w] << 16), __uint_as_float(pk[w] & 0xffff0000u)));
+        float rs = rs2.x + rs2.y;
+        const __nv_bfloat16 rh = __float2bfloat16_rn(rs);
+        rs -= __bfloat162float(rh);
+        const __nv_bfloat16 rm = __float2bfloat16_rn(rs);
+        rs -= __bfloat162float(rm);
+        const __nv_bfloat16 rl = __float2bfloat16_rn(rs);
+        const uint32_t uh = __bfloat16_as_ushort(rh), um = __bfloat16_as_ushort(rm), ul = __bfloat16_as_ushort(rl);
+        const uint32_t ext[4] = {uh | (uh << 16), uh | (um << 16), um | (ul << 16), 0u};      // h h h m m l 0 0
+        tmem_st4(tA[BUF], ext);
       }
       if constexpr (PW == 16) { LBFQ_TMEM_ST16(tP[BUF], pk); }
       else if constexpr (PW == 8) tmem_st8(tP[BUF], pk);
@@ -472,13 +498,24 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           tma_load_3d(sbase + SM::offV + st * SM::kV, &tm_v, c * kChunk, 0, bh, BAR_VFULL(st));
           tma_load_3d(sbase + SM::offV + st * SM::kV + D * 128, &tm_v, c * kChunk + 64, 0, bh, BAR_VFULL(st));
         }
-        if constexpr (CORR) {
+        if constexpr (CORR || VALPHA) {
           if (c >= kFastStages && !mbar_wait(BAR_SIDEFREE(st), ((c / kFastStages) - 1) & 1, abort_flag, p.status, 23)) break;
-          mbar_expect_tx(BAR_SIDEFULL(st), 2 * kChunk * 4);
-          for (int t = 0; t < 2; ++t) {
-            const int g = min((m0 + t * kTileM) / p.q_smooth_block, p.n_groups - 1);
-            bulk_load(sbase + SM::offCorr + (st * 2 + t) * (kChunk * 4),
-                      p.corr + ((size_t)bh * p.n_groups + g) * p.corr_stride + (size_t)c * kChunk, kChunk * 4, BAR_SIDEFULL(st));
+          const int vsb_c = min(p.v_smooth_block, kChunk);          // keys per V-smoothing tile within a stage
+          const int ntile = VALPHA ? kChunk / vsb_c : 0;
+          mbar_expect_tx(BAR_SIDEFULL(st), (CORR ? 2 * kChunk * 4 : 0) + ntile * SM::kAext);
+          if constexpr (CORR) {
+            for (int t = 0; t < 2; ++t) {
+              const int g = min((m0 + t * kTileM) / p.q_smooth_block, p.n_groups - 1);
+              bulk_load(sbase + SM::offCorr + (st * 2 + t) * (kChunk * 4),
+                        p.corr + ((size_t)bh * p.n_groups + g) * p.corr_stride + (size_t)c * kChunk, kChunk * 4, BAR_SIDEFULL(st));
+            }
+          }
+          if constexpr (VALPHA) {
+            for (int sl = 0; sl < ntile; ++sl) {
+              const int key = min(c * kChunk + sl * vsb_c, p.N - 1);   // a tile past the end re-reads the last one
+              const int slab = (b * (p.N / p.v_smooth_block) + key / p.v_smooth_block) * p.H + h;
+              tma_load_3d(sbase + SM::offAext + (st * 2 + sl) * SM::kAext, &tm_a, 0, 0, slab, BAR_SIDEFULL(st));
+            }
           }
         }
       }
@@ -509,6 +546,9 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       auto issue_pv = [&](int j) -> bool {
         const int c = j / NSUB, sub = j % NSUB, st = c % kFastStages;
         if (sub == 0 && !mbar_wait(BAR_VFULL(st), (c / kFastStages) & 1, abort_flag, p.status, 33)) return false;
+        if constexpr (VALPHA) {
+          if (sub == 0 && !mbar_wait(BAR_SIDEFULL(st), (c / kFastStages) & 1, abort_flag, p.status, 37)) return false;
+        }
         tc_fence_after();
         if constexpr (PK == 0) {
           const uint64_t dv = make_desc(sbase + SM::offV + st * SM::kV, kChunk);
@@ -525,10 +565,19 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           for (int kk = 0; kk < BN / 16; ++kk)
             mma_bf16_ts(tO, tS + (j & 1) * S_STRIDE + kk * 8, dv + (uint64_t)(kk * 2), id_pv_bf16,
                         (j > 0 || kk > 0) ? 1u : 0u);
+          if constexpr (VALPHA) {
+            // one more K step: the row-sum pieces (TMEM columns 32..39 of the block's buffer) against alpha' pieces
+            const int sl = key0 / min(p.v_smooth_block, kChunk);
+            mma_bf16_ts(tO, tS + (j & 1) * S_STRIDE + 32, make_desc(sbase + SM::offAext + (st * 2 + sl) * SM::kAext, 32),
+                        id_pv_bf16, 1u);
+          }
         }
         if (j == nblk - 2) tc_commit(BAR_PENULT(t));
         if (j == nblk - 1) tc_commit(BAR_ODONE(t));
-        if (sub == NSUB - 1 || j == nblk - 1) tc_commit(BAR_VFREE(st));
+        if (sub == NSUB - 1 || j == nblk - 1) {
+          tc_commit(BAR_VFREE(st));
+          if constexpr (VALPHA) tc_commit(BAR_SIDEFREE(st));
+        }
         return true;
       };
       if (ok) ok = issue_qk(0);
@@ -562,40 +611,48 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   }
 }
 
-template <int D, int BN, bool CORR, int PK>
-int launch_fast_t(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const Params& p, cudaStream_t st) {
+template <int D, int BN, bool CORR, int PK, bool VALPHA>
+int launch_fast_t(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& ma, const Params& p,
+                  cudaStream_t st) {
   using SM = FastSmem<D, PK>;
   const int smem_bytes = SM::total + 1024;
-  auto kern = attn_fast_kernel<D, BN, CORR, PK>;
+  auto kern = attn_fast_kernel<D, BN, CORR, PK, VALPHA>;
   LBFQ_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
   dim3 grid((p.M + kCtaM - 1) / kCtaM, p.B * p.H, 1);
-  kern<<<grid, kFastThreads, smem_bytes, st>>>(mq, mk, mv, p);
+  kern<<<grid, kFastThreads, smem_bytes, st>>>(mq, mk, mv, ma, p);
   return check_launch("attn_fast_kernel");
 }
 
 }  // namespace
 
-// 0: the general kernel; 1: TMEM-resident with e4m3 P (element-wise P); 2: TMEM-resident with BF16 P (mx / dynamic P,
-// needs a BF16 copy of V^T)
+// 0: the general kernel; 1: TMEM-resident with e4m3 P (element-wise P, no V-smoothing term); 2: TMEM-resident with
+// BF16 P (mx / dynamic P, or any P with the V-smoothing term; needs a BF16 copy of V^T, and the alpha' pieces)
 int fast_variant(const Params& p, bool blasst, bool qk_mx) {
-  const bool common = !blasst && !qk_mx && p.q_scale != nullptr && p.k_scale != nullptr && p.v_alpha == nullptr &&
+  const bool common = !blasst && !qk_mx && p.q_scale != nullptr && p.k_scale != nullptr &&
                       (p.corr == nullptr || p.corr_staged != 0) && p.sm_scale > 0.f;
   if (!common) return 0;
+  const bool v_ok = p.v_kind == LBFQ_V_CHANNEL || p.v_kind == LBFQ_V_MX;
+  if (p.v_alpha != nullptr) return (v_ok && p.v_smooth_block >= 64 && (p.p_kind != LBFQ_P_ELEMENTWISE || p.rm_mode != 2)) ? 2 : 0;
   if (p.p_kind == LBFQ_P_ELEMENTWISE) return (p.v_kind == LBFQ_V_CHANNEL && (p.rm_mode == 0 || p.rm_mode == 1)) ? 1 : 0;
-  return (p.v_kind == LBFQ_V_CHANNEL || p.v_kind == LBFQ_V_MX) ? 2 : 0;
+  return v_ok ? 2 : 0;
 }
 
-int launch_fast(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const Params& p, int block_n,
-                int variant, cudaStream_t st) {
-#define LBFQ_FAST(DD, NN)                                                                                         \
+int launch_fast(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& ma, const Params& p,
+                int block_n, int variant, cudaStream_t st) {
+  const bool va = p.v_alpha != nullptr;
+#define LBFQ_FAST2(DD, NN, CC)                                                                                    \
   if (variant == 2)                                                                                               \
-    return p.corr != nullptr ? launch_fast_t<DD, NN, true, 1>(mq, mk, mv, p, st) : launch_fast_t<DD, NN, false, 1>(mq, mk, mv, p, st); \
-  return p.corr != nullptr ? launch_fast_t<DD, NN, true, 0>(mq, mk, mv, p, st) : launch_fast_t<DD, NN, false, 0>(mq, mk, mv, p, st)
+    return va ? launch_fast_t<DD, NN, CC, 1, true>(mq, mk, mv, ma, p, st) : launch_fast_t<DD, NN, CC, 1, false>(mq, mk, mv, ma, p, st); \
+  return launch_fast_t<DD, NN, CC, 0, false>(mq, mk, mv, ma, p, st)
+#define LBFQ_FAST(DD, NN)                                                                                         \
+  if (p.corr != nullptr) { LBFQ_FAST2(DD, NN, true); }                                                            \
+  LBFQ_FAST2(DD, NN, false)
   if (p.D == 128 && block_n == 64) { LBFQ_FAST(128, 64); }
   if (p.D == 128) { LBFQ_FAST(128, 32); }
   if (block_n == 64) { LBFQ_FAST(64, 64); }
   LBFQ_FAST(64, 32);
 #undef LBFQ_FAST
+#undef LBFQ_FAST2
 }
 
 }  // namespace attn

@@ -343,8 +343,8 @@ struct Params {
 
 // attention_fast.cu: online-softmax variant whose output accumulator lives in tensor memory
 int fast_variant(const Params& p, bool blasst, bool qk_mx);
-int launch_fast(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const Params& p, int block_n,
-                int variant, cudaStream_t st);
+int launch_fast(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& ma, const Params& p,
+                int block_n, int variant, cudaStream_t st);
 
 }  // namespace attn
 }  // namespace lbfq

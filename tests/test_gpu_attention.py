@@ -268,20 +268,26 @@ def _fast_and_general(q, k, v, cfg, monkeypatch):
     (1024, 64, 32, dict(p_quant="mx", p_mx_block_n=32)),
     (1536, 128, 64, dict(smoothing="full", p_quant="dynamic", rowmax_mode="qm_k")),   # estimate + up / down thresholds
     (1024, 128, 64, dict(v_quant="mxfp8", p_quant="auto")),                           # mxfp8 V folded into the BF16 copy
+    (2048, 128, 64, dict(v_smooth_mode="per_block")),      # V-smoothing term as one more K step of the BF16 P.V
+    (1024, 64, 64, dict(v_smooth_mode="per_block", v_smooth_block_size=128, p_quant="dynamic")),
+    (1536, 128, 64, dict(smoothing="full", q_kmeans_k=8, v_kmeans_k=8, v_smooth_mode="per_block", p_quant="dynamic",
+                         rowmax_mode="qm_k")),             # the full stack of the benchmark's second workload
 ])
 def test_tmem_resident_variant_matches_oracle_and_general_kernel(S, D, bn, extra, monkeypatch):
     kw = {**COMMON, **dict(smoothing="k_only", q_kmeans_k=None, p_requant_block_m=bn, p_requant_block_n=bn), **extra}
     cfg = QuantConfig(**kw)
     q, k, v = _qkv(2, S, 3, D, seed=S + D + bn)
     fast, gen = _fast_and_general(q, k, v, cfg, monkeypatch)
-    ql = None
-    if cfg.q_kmeans_k is not None:                         # k-means labels are not pinned: hand the GPU's to the oracle
-        ql = fq.prepare_for_attention(q.to(DEV), k.to(DEV), v.to(DEV), cfg).q_kmeans.labels.cpu()
-    o = OA.fake_quant_attention(q, k, v, cfg, faithful=False, out_fp32=True, q_labels=ql)
+    ql = vl = None
+    if cfg.q_kmeans_k is not None or cfg.v_kmeans_k is not None:     # k-means labels are not pinned: hand the GPU's to the oracle
+        pc = fq.prepare_for_attention(q.to(DEV), k.to(DEV), v.to(DEV), cfg)
+        ql = pc.q_kmeans.labels.cpu() if pc.q_kmeans is not None else None
+        vl = pc.v_kmeans.labels.cpu() if pc.v_kmeans is not None else None
+    o = OA.fake_quant_attention(q, k, v, cfg, faithful=False, out_fp32=True, q_labels=ql, v_labels=vl)
     _check(gen, o, (q, k, v))
     if kw.get("p_quant", "elementwise") == "dynamic":
         # the variant rounds the re-scaled P to BF16 as the reference does; the general kernel keeps codes x FP32 scale
-        o_b = OA.fake_quant_attention(q, k, v, cfg, faithful=False, out_fp32=True, q_labels=ql, p_bf16=True)
+        o_b = OA.fake_quant_attention(q, k, v, cfg, faithful=False, out_fp32=True, q_labels=ql, v_labels=vl, p_bf16=True)
         _check(fast, o_b, (q, k, v))
         assert OA.compute_metrics(fast, gen)["cosine"] > 0.99999
     else:
