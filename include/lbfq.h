@@ -180,6 +180,10 @@ int lbfq_qm_corr(const float* qm, const void* k_smooth, int dtype, int B, int S,
 /* Q/K quantisation kinds */
 #define LBFQ_QK_FP8_BLOCK 0
 #define LBFQ_QK_MX 1
+/* Q, K and V^T are BF16 tensors holding the de-quantised (Q, K) / code-valued or de-quantised (V) operands the
+ * reference's own launcher receives (attention_triton.py:410-436): q_codes, k_codes, v_codes then point to BF16 data
+ * of the same shapes, Q.K^T and P.V run as BF16 MMAs, and q_scale / k_scale are not read. */
+#define LBFQ_QK_BF16 2
 /* BLASST fill kinds (attention_triton.py:39-45) */
 #define LBFQ_FILL_ZERO 0
 #define LBFQ_FILL_MAX 1

@@ -875,7 +875,8 @@ static size_t v_bf16_ws_bytes(const lbfq_attn_args* a) {
   return may_want_v_bf16(a) ? align256((size_t)a->B * a->H * a->D * a->n_pad * 2) : 0;
 }
 static size_t alpha_ext_ws_bytes(const lbfq_attn_args* a) {
-  return (may_want_v_bf16(a) && a->v_alpha) ? 8 * alpha_ws_bytes(a) : 0;      // 16 BF16 per FP32 value
+  const bool bf = a->qk_kind == LBFQ_QK_BF16;
+  return ((bf || may_want_v_bf16(a)) && a->v_alpha) ? 8 * alpha_ws_bytes(a) : 0;      // 16 BF16 per FP32 value
 }
 
 static thread_local int g_last_variant = 0;
@@ -884,6 +885,27 @@ extern "C" int lbfq_attention_last_variant(void) { return g_last_variant; }
 extern "C" int64_t lbfq_attention_workspace_bytes(const lbfq_attn_args* a) {
   if (!a) return 0;
   return (int64_t)(alpha_ws_bytes(a) + v_bf16_ws_bytes(a) + alpha_ext_ws_bytes(a));
+}
+
+// BF16 pieces of alpha' into `dst` and the tensor map over them: (16, D, B * NB * H) BF16, one (D x 16) tile per
+// (b, smoothing block, h), 32-byte rows, 32B swizzle
+static int make_alpha_ext(const lbfq_attn_args* a, const lbfq::attn::Params& p, void* dst, CUtensorMap* ma, cudaStream_t st) {
+  using namespace lbfq::attn;
+  __nv_bfloat16* ext = reinterpret_cast<__nv_bfloat16*>(dst);
+  const size_t total = (size_t)a->B * (a->N / a->v_smooth_block) * a->H * a->D;
+  int ge = (int)((total + 255) / 256); if (ge > 148 * 16) ge = 148 * 16;
+  alpha_ext_kernel<<<ge, 256, 0, st>>>(p.v_alpha, ext, total);
+  if (int rc = check_launch("alpha_ext")) return rc;
+  auto enc = get_encode();
+  LBFQ_REQUIRE(enc != nullptr, LBFQ_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t dims[3] = {16, (cuuint64_t)a->D, (cuuint64_t)a->B * (a->N / a->v_smooth_block) * a->H};
+  cuuint64_t strides[2] = {32, (cuuint64_t)a->D * 32};
+  cuuint32_t box[3] = {16, (cuuint32_t)a->D, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(ma, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, ext, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  LBFQ_REQUIRE(r == CUDA_SUCCESS, LBFQ_ERR_CUDA, "cuTensorMapEncodeTiled (alpha pieces) failed with code %d", (int)r);
+  return LBFQ_OK;
 }
 
 extern "C" int lbfq_attention_fwd(const lbfq_attn_args* a, void* workspace, void* stream) {
@@ -897,9 +919,13 @@ extern "C" int lbfq_attention_fwd(const lbfq_attn_args* a, void* workspace, void
   LBFQ_REQUIRE(a->m_pad >= a->M && a->m_pad % 128 == 0 && a->n_pad >= a->N && a->n_pad % 128 == 0, LBFQ_ERR_ARG,
                "m_pad / n_pad must cover M / N and be multiples of 128");
   LBFQ_REQUIRE(a->q_codes && a->k_codes && a->v_codes && a->out, LBFQ_ERR_ARG, "null operand pointer");
-  LBFQ_REQUIRE(a->qk_kind == LBFQ_QK_FP8_BLOCK || a->qk_kind == LBFQ_QK_MX, LBFQ_ERR_ARG, "unknown qk_kind %d", a->qk_kind);
+  LBFQ_REQUIRE(a->qk_kind == LBFQ_QK_FP8_BLOCK || a->qk_kind == LBFQ_QK_MX || a->qk_kind == LBFQ_QK_BF16, LBFQ_ERR_ARG,
+               "unknown qk_kind %d", a->qk_kind);
   const bool mx = a->qk_kind == LBFQ_QK_MX;
-  if (mx) {
+  const bool bf = a->qk_kind == LBFQ_QK_BF16;
+  if (bf) {
+    // nothing to check: the operands carry their scales already
+  } else if (mx) {
     LBFQ_REQUIRE(a->q_scale_e8 && a->k_scale_e8, LBFQ_ERR_ARG, "mxfp8 Q/K needs the UE8M0 scale tiles");
     LBFQ_REQUIRE(a->qk_block == 32, LBFQ_ERR_UNSUPPORTED,
                  "mxfp8_block_size=%d: the block-scaled MMA scales 32 elements of D at a time", a->qk_block);
@@ -947,7 +973,9 @@ extern "C" int lbfq_attention_fwd(const lbfq_attn_args* a, void* workspace, void
 
   Params p{};
   p.B = a->B; p.H = a->H; p.M = a->M; p.N = a->N; p.D = a->D;
-  p.qk_block = mx ? 1 : a->qk_block; p.q_scale = mx ? nullptr : a->q_scale; p.k_scale = mx ? nullptr : a->k_scale;
+  p.qk_block = mx ? 1 : (bf ? a->block_n : a->qk_block);
+  p.q_scale = (mx || bf) ? nullptr : a->q_scale; p.k_scale = (mx || bf) ? nullptr : a->k_scale;
+  p.qk_bf16 = bf ? 1 : 0;
   p.q_sf = a->q_scale_e8; p.k_sf = a->k_scale_e8; p.m_pad = a->m_pad; p.n_pad = a->n_pad;
   p.v_kind = a->v_kind; p.v_scale = a->v_scale; p.v_block = a->v_block > 0 ? a->v_block : a->block_n;
   p.sm_scale = a->sm_scale; p.p_off = a->p_max_offset; p.p_kind = a->p_kind; p.block_m = a->block_m;
@@ -985,6 +1013,21 @@ extern "C" int lbfq_attention_fwd(const lbfq_attn_args* a, void* workspace, void
 
   CUtensorMap mq, mk, mv;
   const uint64_t BH = (uint64_t)a->B * a->H;
+  if (bf) {
+    // BF16 operands: only the TMEM-resident kernel multiplies them
+    const int fvb = fast_variant(p, a->use_blasst != 0, false);
+    LBFQ_REQUIRE(fvb == 2, LBFQ_ERR_UNSUPPORTED,
+                 "BF16 operands are served for V per channel / pre-dequantised, without BLASST, with q_smooth_block a "
+                 "multiple of 128 and v_smooth_block >= 64; the FP8-code entry covers the rest");
+    if (int rc = make_map_bf16(&mq, a->q_codes, a->D, a->m_pad, BH, 64, kTileM)) return rc;
+    if (int rc = make_map_bf16(&mk, a->k_codes, a->D, a->n_pad, BH, 64, kChunk)) return rc;
+    if (int rc = make_map_bf16(&mv, a->v_codes, a->n_pad, a->D, BH, 64, a->D)) return rc;
+    CUtensorMap ma = mv;
+    if (a->v_alpha)
+      if (int rc = make_alpha_ext(a, p, (uint8_t*)workspace + alpha_ws_bytes(a), &ma, st)) return rc;
+    g_last_variant = 1;
+    return launch_fast(mq, mk, mv, ma, p, a->block_n, 2, st);
+  }
   if (int rc = make_map(&mq, a->q_codes, a->D, a->m_pad, BH, a->D, kTileM)) return rc;
   if (int rc = make_map(&mk, a->k_codes, a->D, a->n_pad, BH, a->D, kChunk)) return rc;
   if (int rc = make_map(&mv, a->v_codes, a->n_pad, a->D, BH, kChunk, a->D)) return rc;
@@ -1009,23 +1052,8 @@ extern "C" int lbfq_attention_fwd(const lbfq_attn_args* a, void* workspace, void
     CUtensorMap mvb, ma;
     if (int rc = make_map_bf16(&mvb, vb, a->n_pad, a->D, BH, 64, a->D)) return rc;
     ma = mvb;
-    if (a->v_alpha) {
-      __nv_bfloat16* ext = reinterpret_cast<__nv_bfloat16*>((uint8_t*)workspace + alpha_ws_bytes(a) + v_bf16_ws_bytes(a));
-      const size_t total = (size_t)a->B * (a->N / a->v_smooth_block) * a->H * a->D;
-      int ge = (int)((total + 255) / 256); if (ge > 148 * 16) ge = 148 * 16;
-      alpha_ext_kernel<<<ge, 256, 0, st>>>(p.v_alpha, ext, total);
-      if (int rc = check_launch("alpha_ext")) return rc;
-      // (16, D, B * NB * H) BF16, one (D x 16) tile per (b, smoothing block, h), 32-byte rows, 32B swizzle
-      auto enc = get_encode();
-      LBFQ_REQUIRE(enc != nullptr, LBFQ_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
-      cuuint64_t dims[3] = {16, (cuuint64_t)a->D, (cuuint64_t)a->B * (a->N / a->v_smooth_block) * a->H};
-      cuuint64_t strides[2] = {32, (cuuint64_t)a->D * 32};
-      cuuint32_t box[3] = {16, (cuuint32_t)a->D, 1};
-      cuuint32_t estr[3] = {1, 1, 1};
-      CUresult r = enc(&ma, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, ext, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                       CU_TENSOR_MAP_SWIZZLE_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-      LBFQ_REQUIRE(r == CUDA_SUCCESS, LBFQ_ERR_CUDA, "cuTensorMapEncodeTiled (alpha pieces) failed with code %d", (int)r);
-    }
+    if (a->v_alpha)
+      if (int rc = make_alpha_ext(a, p, (uint8_t*)workspace + alpha_ws_bytes(a) + v_bf16_ws_bytes(a), &ma, st)) return rc;
     g_last_variant = 1;
     return launch_fast(mq, mk, mvb, ma, p, a->block_n, 2, st);
   }

@@ -51,11 +51,12 @@ static_assert(kFastRegsSoftmax % 8 == 0 && kFastRegsService % 8 == 0, "setmaxnre
 // PK = 0: P as e4m3 codes, P.V an FP8 MMA over the V^T codes (4 key stages).
 // PK = 1: P re-scaled and rounded to BF16 as the reference does for its mx / dynamic P modes, P.V a BF16 MMA
 //         over a BF16 copy of V^T (3 key stages: a V stage is twice as large).
-template <int D, int PK>
+// QB = 1: Q and K are BF16 tensors (the reference's de-quantised operands) and Q.K^T a BF16 MMA; two key stages.
+template <int D, int PK, int QB>
 struct FastSmem {
-  static constexpr int kStages = PK ? 3 : 4;
-  static constexpr int kQ = kTileM * D;                       // bytes per Q tile
-  static constexpr int kK = kChunk * D;                       // bytes per K stage
+  static constexpr int kStages = QB ? 2 : (PK ? 3 : 4);
+  static constexpr int kQ = kTileM * D * (QB ? 2 : 1);         // bytes per Q tile
+  static constexpr int kK = kChunk * D * (QB ? 2 : 1);         // bytes per K stage
   static constexpr int kV = D * kChunk * (PK ? 2 : 1);        // bytes per V^T stage
   static constexpr int offQ = 0;
   static constexpr int offK = offQ + 2 * kQ;
@@ -72,12 +73,13 @@ struct FastSmem {
   static constexpr int total = offAext + (PK ? kStages * 2 * kAext : 0);
 };
 
-template <int D, int BN, bool CORR, int PK, bool VALPHA>
+template <int D, int BN, bool CORR, int PK, bool VALPHA, int QB>
 __global__ void __launch_bounds__(kFastThreads, 1)
 attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                  const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_a, const Params p) {
   static_assert(!VALPHA || PK == 1, "the V-smoothing term rides on the BF16 P.V");
-  using SM = FastSmem<D, PK>;
+  static_assert(!QB || PK == 1, "BF16 Q / K come with the BF16 P.V");
+  using SM = FastSmem<D, PK, QB>;
   constexpr int kFastStages = SM::kStages;
   constexpr int NSUB = kChunk / BN;                // key blocks per stage
   constexpr int TCOLS = 256;                       // TMEM columns per tile
@@ -161,8 +163,9 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const uint32_t tS = tmem_base + lane_base + t * TCOLS + COL_S;
     const uint32_t tO = tmem_base + lane_base + t * TCOLS + COL_O + half * HD;
 
-    const float sq = p.q_scale[((size_t)b * (p.M / p.qk_block) + rowc / p.qk_block) * p.H + h];
-    const float* ksc = p.k_scale + (size_t)b * (p.N / p.qk_block) * p.H + h;
+    // BF16 operands are already de-quantised: no Q / K scales
+    const float sq = QB ? 1.0f : p.q_scale[((size_t)b * (p.M / p.qk_block) + rowc / p.qk_block) * p.H + h];
+    const float* ksc = QB ? nullptr : p.k_scale + (size_t)b * (p.N / p.qk_block) * p.H + h;
     const bool frozen = p.rm_mode == 1;
     const bool thresholds = PK != 0 && p.rm_mode == 2;   // estimated row max corrected by the up-16 / down-32 rule (dynamic P only)
     float max_seen = -INFINITY;
@@ -177,7 +180,7 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     int side_sub = 0, side_stage = 0;
     uint32_t side_par = 0;
     float l_i = 0.f;                                           // row sum over this thread's columns
-    float sk = ksc[0];
+    float sk = QB ? 1.0f : ksc[0];
     const int blocks_per_scale = p.qk_block / BN;               // fp8_block_size is a multiple of block_n
     int scale_sub = 0;
     const uint32_t bar_sfull = BAR_SFULL(t, 0), bar_prdy = BAR_PRDY(t);
@@ -217,8 +220,10 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       const bool more = it != last;
       if (++scale_sub == blocks_per_scale) {   // next block's scale, off the critical path
         scale_sub = 0;
-        ksc += k_stride;
-        if (more) sk = *ksc;
+        if constexpr (!QB) {
+          ksc += k_stride;
+          if (more) sk = *ksc;
+        }
       }
       if constexpr (CORR) {
         // scores = dot * f + corr (attention_triton.py:154-160), all 64 columns: the max needs them
@@ -477,7 +482,12 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     if (lane == 0) {
       for (int t = 0; t < 2; ++t) {
         mbar_expect_tx(BAR_QFULL(t), SM::kQ);
-        tma_load_3d(sbase + SM::offQ + t * SM::kQ, &tm_q, 0, m0 + t * kTileM, bh, BAR_QFULL(t));
+        if constexpr (QB == 0) {
+          tma_load_3d(sbase + SM::offQ + t * SM::kQ, &tm_q, 0, m0 + t * kTileM, bh, BAR_QFULL(t));
+        } else {                                          // BF16: D / 64 panels of 128 rows x 128 bytes
+          for (int pn = 0; pn < D / 64; ++pn)
+            tma_load_3d(sbase + SM::offQ + t * SM::kQ + pn * (kTileM * 128), &tm_q, pn * 64, m0 + t * kTileM, bh, BAR_QFULL(t));
+        }
       }
       for (int c = 0; c < nchunk; ++c) {
         const int st = c % kFastStages;
@@ -486,7 +496,12 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           if (!mbar_wait(BAR_KFREE(st), par, abort_flag, p.status, 21)) break;
         }
         mbar_expect_tx(BAR_KFULL(st), SM::kK);
-        tma_load_3d(sbase + SM::offK + st * SM::kK, &tm_k, 0, c * kChunk, bh, BAR_KFULL(st));
+        if constexpr (QB == 0) {
+          tma_load_3d(sbase + SM::offK + st * SM::kK, &tm_k, 0, c * kChunk, bh, BAR_KFULL(st));
+        } else {
+          for (int pn = 0; pn < D / 64; ++pn)
+            tma_load_3d(sbase + SM::offK + st * SM::kK + pn * (kChunk * 128), &tm_k, pn * 64, c * kChunk, bh, BAR_KFULL(st));
+        }
         if (c >= kFastStages) {
           const uint32_t par = ((c / kFastStages) - 1) & 1;
           if (!mbar_wait(BAR_VFREE(st), par, abort_flag, p.status, 22)) break;
@@ -535,10 +550,22 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         const int c = j / NSUB, sub = j % NSUB, st = c % kFastStages;
         if (sub == 0 && !mbar_wait(BAR_KFULL(st), (c / kFastStages) & 1, abort_flag, p.status, 32)) return false;
         tc_fence_after();
-        const uint64_t dk = make_desc(sbase + SM::offK + st * SM::kK + sub * BN * D, D);
+        if constexpr (QB == 0) {
+          const uint64_t dk = make_desc(sbase + SM::offK + st * SM::kK + sub * BN * D, D);
 #pragma unroll
-        for (int kk = 0; kk < D / 32; ++kk)
-          mma_f8_ss(tS + (j & 1) * S_STRIDE, dq + (uint64_t)(kk * 2), dk + (uint64_t)(kk * 2), id_qk, kk > 0 ? 1u : 0u);
+          for (int kk = 0; kk < D / 32; ++kk)
+            mma_f8_ss(tS + (j & 1) * S_STRIDE, dq + (uint64_t)(kk * 2), dk + (uint64_t)(kk * 2), id_qk, kk > 0 ? 1u : 0u);
+        } else {
+          // BF16: K steps of 16 channels, four per 64-channel panel
+          const uint32_t id_qk_bf16 = make_idesc_bf16(BN);
+#pragma unroll
+          for (int kk = 0; kk < D / 16; ++kk) {
+            const uint64_t da = make_desc(sbase + SM::offQ + t * SM::kQ + (kk >> 2) * (kTileM * 128), 128) + (uint64_t)((kk & 3) * 2);
+            const uint64_t db = make_desc(sbase + SM::offK + st * SM::kK + (kk >> 2) * (kChunk * 128) + sub * BN * 128, 128) +
+                                (uint64_t)((kk & 3) * 2);
+            mma_bf16_ss(tS + (j & 1) * S_STRIDE, da, db, id_qk_bf16, kk > 0 ? 1u : 0u);
+          }
+        }
         tc_commit(BAR_SFULL(t, j & 1));
         if (sub == NSUB - 1 || j == nblk - 1) tc_commit(BAR_KFREE(st));
         return true;
@@ -611,12 +638,12 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   }
 }
 
-template <int D, int BN, bool CORR, int PK, bool VALPHA>
+template <int D, int BN, bool CORR, int PK, bool VALPHA, int QB>
 int launch_fast_t(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& ma, const Params& p,
                   cudaStream_t st) {
-  using SM = FastSmem<D, PK>;
+  using SM = FastSmem<D, PK, QB>;
   const int smem_bytes = SM::total + 1024;
-  auto kern = attn_fast_kernel<D, BN, CORR, PK, VALPHA>;
+  auto kern = attn_fast_kernel<D, BN, CORR, PK, VALPHA, QB>;
   LBFQ_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
   dim3 grid((p.M + kCtaM - 1) / kCtaM, p.B * p.H, 1);
   kern<<<grid, kFastThreads, smem_bytes, st>>>(mq, mk, mv, ma, p);
@@ -628,11 +655,13 @@ int launch_fast_t(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMa
 // 0: the general kernel; 1: TMEM-resident with e4m3 P (element-wise P, no V-smoothing term); 2: TMEM-resident with
 // BF16 P (mx / dynamic P, or any P with the V-smoothing term; needs a BF16 copy of V^T, and the alpha' pieces)
 int fast_variant(const Params& p, bool blasst, bool qk_mx) {
-  const bool common = !blasst && !qk_mx && p.q_scale != nullptr && p.k_scale != nullptr &&
+  const bool common = !blasst && !qk_mx && (p.qk_bf16 != 0 || (p.q_scale != nullptr && p.k_scale != nullptr)) &&
                       (p.corr == nullptr || p.corr_staged != 0) && p.sm_scale > 0.f;
   if (!common) return 0;
   const bool v_ok = p.v_kind == LBFQ_V_CHANNEL || p.v_kind == LBFQ_V_MX;
-  if (p.v_alpha != nullptr) return (v_ok && p.v_smooth_block >= 64 && (p.p_kind != LBFQ_P_ELEMENTWISE || p.rm_mode != 2)) ? 2 : 0;
+  const bool alpha_ok = p.v_alpha == nullptr || p.v_smooth_block >= 64;
+  if (p.qk_bf16) return (v_ok && alpha_ok && (p.p_kind == LBFQ_P_DYNAMIC || p.rm_mode != 2)) ? 2 : 0;
+  if (p.v_alpha != nullptr) return (v_ok && alpha_ok && (p.p_kind != LBFQ_P_ELEMENTWISE || p.rm_mode != 2)) ? 2 : 0;
   if (p.p_kind == LBFQ_P_ELEMENTWISE) return (p.v_kind == LBFQ_V_CHANNEL && (p.rm_mode == 0 || p.rm_mode == 1)) ? 1 : 0;
   return v_ok ? 2 : 0;
 }
@@ -640,10 +669,15 @@ int fast_variant(const Params& p, bool blasst, bool qk_mx) {
 int launch_fast(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& ma, const Params& p,
                 int block_n, int variant, cudaStream_t st) {
   const bool va = p.v_alpha != nullptr;
+#define LBFQ_FAST3(DD, NN, CC, VV)                                                                                \
+  if (p.qk_bf16) return launch_fast_t<DD, NN, CC, 1, VV, 1>(mq, mk, mv, ma, p, st);                               \
+  return launch_fast_t<DD, NN, CC, 1, VV, 0>(mq, mk, mv, ma, p, st)
 #define LBFQ_FAST2(DD, NN, CC)                                                                                    \
-  if (variant == 2)                                                                                               \
-    return va ? launch_fast_t<DD, NN, CC, 1, true>(mq, mk, mv, ma, p, st) : launch_fast_t<DD, NN, CC, 1, false>(mq, mk, mv, ma, p, st); \
-  return launch_fast_t<DD, NN, CC, 0, false>(mq, mk, mv, ma, p, st)
+  if (variant == 2) {                                                                                             \
+    if (va) { LBFQ_FAST3(DD, NN, CC, true); }                                                                     \
+    LBFQ_FAST3(DD, NN, CC, false);                                                                                \
+  }                                                                                                               \
+  return launch_fast_t<DD, NN, CC, 0, false, 0>(mq, mk, mv, ma, p, st)
 #define LBFQ_FAST(DD, NN)                                                                                         \
   if (p.corr != nullptr) { LBFQ_FAST2(DD, NN, true); }                                                            \
   LBFQ_FAST2(DD, NN, false)
@@ -653,6 +687,7 @@ int launch_fast(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap&
   LBFQ_FAST(64, 32);
 #undef LBFQ_FAST
 #undef LBFQ_FAST2
+#undef LBFQ_FAST3
 }
 
 }  // namespace attn

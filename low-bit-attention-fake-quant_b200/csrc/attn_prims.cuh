@@ -296,6 +296,7 @@ __device__ __forceinline__ uint64_t make_desc_sf(uint32_t saddr) {
 struct Params {
   int B, H, M, N, D;
   int qk_block;
+  int qk_bf16;                 // 1: Q / K are BF16 (already de-quantised), Q.K^T is a BF16 MMA, no Q / K scales
   const float* q_scale;
   const float* k_scale;
   const uint8_t* q_sf;         // block-scaled Q/K: UE8M0 scale tiles

@@ -24,7 +24,7 @@ import torch
 import torch.nn.functional as F
 
 from . import _lib as L
-from .attention_triton import fake_quant_attention_fp8, qm_corr
+from .attention_triton import fake_quant_attention_fp8, fake_quant_attention_triton, qm_corr
 from .config import QuantConfig
 from .hadamard import apply_qk_hadamard
 from .kmeans import KMeansReorderResult, _gather, apply_kv_permutation, kmeans_reorder_tokens
@@ -279,6 +279,55 @@ def prepare_for_attention(q, k, v, cfg: QuantConfig) -> PreprocessCache:
     )
 
 
+def _fake_quant_attention_p_requant_reference_operands(q_work, k_work, v_work, qm, v_alpha, q_kmeans, cfg: QuantConfig,
+                                                       sm_scale, out_dtype, *, out_fp32_exact: bool = False,
+                                                       head_offset: int = 0, total_heads: int = 0):
+    """Path B with the operands the reference itself builds (attention.py:505-639): Q / K de-quantised to BF16,
+    V as BF16 code values with its per-channel scale (or de-quantised for mxfp8), handed to the direct-launch
+    entry. Q.K^T and P.V then run as BF16 MMAs, i.e. in the reference's numerics."""
+    q_in, k_in = _rotated(q_work, k_work, cfg, head_offset, total_heads)
+    q_deq = _quant_dequant_qk(q_in, cfg, torch.bfloat16)
+    k_deq = _quant_dequant_qk(k_in, cfg, torch.bfloat16)
+    b, s, h, d = q_work.shape
+    if cfg.v_quant == "fp8_channel":
+        codes, v_scale = fp8_per_channel_quant(v_work)
+        v_bf = codes.to(torch.bfloat16)                       # code values, exact in BF16
+    elif cfg.v_quant == "mxfp8":
+        v_bf = _quant_dequant_v(v_work, cfg, torch.bfloat16)  # codes x 2^e, exact in BF16
+        v_scale = torch.ones((b, h, d), dtype=torch.float32, device=v_work.device)
+    else:
+        raise NotImplementedError("fp8_block V with the reference's BF16 operands is not built; use the FP8-code path")
+    if cfg.blasst_lambda is not None:
+        raise NotImplementedError("BLASST with the reference's BF16 operands is not built; use the FP8-code path")
+    if cfg.rowmax_mode not in ("online", "qm_k"):
+        raise ValueError(f"unsupported rowmax_mode: {cfg.rowmax_mode!r}")
+    if cfg.rowmax_mode == "qm_k" and qm is None:
+        raise ValueError("rowmax_mode='qm_k' requires smoothing='full' so qm exists")
+    to_bh = lambda t: t.permute(0, 2, 1, 3).contiguous()
+    rowmax_est = None
+    if qm is not None and cfg.rowmax_mode == "qm_k":
+        _, rowmax_g = qm_corr(qm, k_work.to(torch.bfloat16), sm_scale=sm_scale, s_pad=_round_up(s, 128), want_rowmax=True)
+        rowmax_est = rowmax_g.repeat_interleave(cfg.q_smooth_block_size, dim=2).contiguous()
+    p_mode = cfg.p_quant
+    if p_mode == "auto":
+        p_mode = "mx" if cfg.v_quant == "mxfp8" else "elementwise"
+    p_mx_block_n = cfg.p_mx_block_n if cfg.p_mx_block_n > 0 else cfg.v_mxfp8_block_size
+    o = fake_quant_attention_triton(
+        to_bh(q_deq), to_bh(k_deq), to_bh(v_bf), v_scale,
+        sm_scale=float(sm_scale), p_max_offset=int(cfg.p_max_offset),
+        block_m=cfg.p_requant_block_m, block_n=cfg.p_requant_block_n,
+        v_alpha=v_alpha, v_smooth_block=cfg.v_smooth_block_size if v_alpha is not None else 0,
+        k_smooth_bhsd=to_bh(k_work.to(torch.bfloat16)) if qm is not None else None,
+        qm_bhgd=to_bh(qm) if qm is not None else None,
+        q_smooth_block=cfg.q_smooth_block_size if qm is not None else 0,
+        p_quant_mode=p_mode, p_mx_block_n=p_mx_block_n, rowmax_est_bhs=rowmax_est, _out_fp32=out_fp32_exact)
+    o = o.permute(0, 2, 1, 3).contiguous()                    # (B, S, H, D)
+    o = o if out_fp32_exact else o.to(out_dtype)
+    if q_kmeans is not None:
+        o = _gather(o, q_kmeans.inverse_order)
+    return o
+
+
 def fake_quant_attention(
     q: torch.Tensor,
     k: torch.Tensor,
@@ -291,6 +340,7 @@ def fake_quant_attention(
     _debug_fp32: bool = False,
     _head_offset: int = 0,
     _total_heads: int = 0,
+    _reference_operands: bool = False,
 ):
     """Fake-quant attention with FP8/MXFP8 Q/K/V (and optional P requant).
 
@@ -300,6 +350,8 @@ def fake_quant_attention(
     BF16 rounding of the store. ``_head_offset`` / ``_total_heads`` tell a heads
     shard where it sits in the unsharded problem (Hadamard signs and k-means
     seeding are indexed by global head), so that sharded == unsharded.
+    ``_reference_operands`` runs path B on the reference's own BF16 operands
+    (BF16 MMAs) instead of the FP8 codes: the reference's numerics, at BF16 speed.
     """
     if cfg is None:
         cfg = QuantConfig()
@@ -331,7 +383,11 @@ def fake_quant_attention(
         q_work, k_work, v_work, qm, v_alpha, q_km, _ = _preprocess(q, k, v, cfg, head_offset=_head_offset,
                                                                    total_heads=_total_heads)
 
-    if cfg.p_requant:
+    if cfg.p_requant and _reference_operands:
+        o = _fake_quant_attention_p_requant_reference_operands(
+            q_work, k_work, v_work, qm, v_alpha, q_km, cfg, sm_scale, out_dtype, out_fp32_exact=_debug_fp32,
+            head_offset=_head_offset, total_heads=_total_heads)
+    elif cfg.p_requant:
         # the kernel scatters its rows through q_km.order: no separate inverse gather
         o = _fake_quant_attention_p_requant(q_work, k_work, v_work, qm, v_alpha, q_km, cfg, sm_scale, out_dtype,
                                             out_fp32_exact=_debug_fp32, head_offset=_head_offset,

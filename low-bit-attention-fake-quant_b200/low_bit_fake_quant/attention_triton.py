@@ -91,9 +91,10 @@ def fake_quant_attention_fp8(
     *,
     seq_q: int,
     seq_k: int,
-    q_scale: torch.Tensor,          # (B, M/qk_block, H) fp32
-    k_scale: torch.Tensor,          # (B, N/qk_block, H) fp32
+    q_scale: Optional[torch.Tensor],   # (B, M/qk_block, H) fp32
+    k_scale: Optional[torch.Tensor],   # (B, N/qk_block, H) fp32
     qk_block: int,
+    operands_bf16: bool = False,    # q/k/v are BF16 (de-quantised Q/K, BF16 V^T): the reference's own operand convention
     q_scale_e8: Optional[torch.Tensor] = None,   # block-scaled (mxfp8) Q/K: UE8M0 scale tiles from mxfp8_qk_quant
     k_scale_e8: Optional[torch.Tensor] = None,
     v_kind: str,                    # "fp8_channel" | "fp8_block" | "mxfp8"
@@ -182,7 +183,7 @@ def fake_quant_attention_fp8(
         a.B, a.H, a.M, a.N, a.D = B, H, M, N, D
         a.m_pad, a.n_pad = m_pad, n_pad
         a.q_codes, a.k_codes, a.v_codes = q_codes.data_ptr(), k_codes.data_ptr(), v_codes_t.data_ptr()
-        a.qk_kind = L.QK_MX if q_scale_e8 is not None else L.QK_FP8_BLOCK
+        a.qk_kind = L.QK_BF16 if operands_bf16 else (L.QK_MX if q_scale_e8 is not None else L.QK_FP8_BLOCK)
         a.q_scale, a.k_scale, a.qk_block = L.ptr(q_scale), L.ptr(k_scale), int(qk_block)
         a.q_scale_e8, a.k_scale_e8 = L.ptr(q_scale_e8), L.ptr(k_scale_e8)
         a.v_kind, a.v_scale, a.v_block = v_kind_code, L.ptr(v_scale), int(v_block)
@@ -239,4 +240,98 @@ def qm_corr(qm: torch.Tensor, k_smooth: torch.Tensor, *, sm_scale: float, s_pad:
     return corr, rowmax
 
 
-__all__ = ["fake_quant_attention_fp8", "qm_corr", "raise_if_device_error"]
+__all__ = ["fake_quant_attention_fp8", "fake_quant_attention_triton", "qm_corr", "raise_if_device_error"]
+
+
+def fake_quant_attention_triton(
+    q_bhsd: torch.Tensor,
+    k_bhsd: torch.Tensor,
+    v_bhsd_bf16: torch.Tensor,
+    v_scale_bhd: torch.Tensor,
+    *,
+    sm_scale: float,
+    p_max_offset: int,
+    block_m: int = 64,
+    block_n: int = 64,
+    v_alpha: Optional[torch.Tensor] = None,
+    v_smooth_block: int = 0,
+    k_smooth_bhsd: Optional[torch.Tensor] = None,
+    qm_bhgd: Optional[torch.Tensor] = None,
+    q_smooth_block: int = 0,
+    v_block_scale_bsh: Optional[torch.Tensor] = None,
+    v_block_size: int = 0,
+    p_quant_mode: str = "elementwise",
+    p_mx_block_n: int = 0,
+    rowmax_est_bhs: Optional[torch.Tensor] = None,
+    rowmax_init_bhs: Optional[torch.Tensor] = None,
+    blasst_lambda: Optional[float] = None,
+    blasst_fill_mode: str = "zero",
+    blasst_fill_alpha: float = 1.0,
+    blasst_uta_bins: int = 16,
+    return_blasst_stats: bool = False,
+    _out_fp32: bool = False,
+):
+    """The reference's direct-launch entry (src/low_bit_fake_quant/attention_triton.py:410-671), same signature.
+
+    ``q_bhsd`` / ``k_bhsd``: the de-quantised BF16 operands (B, H, S, D); ``v_bhsd_bf16``: V as BF16 (code values or
+    pre-de-quantised) with its per-channel post-scale ``v_scale_bhd`` (FP32 ones when unused). Q.K^T and P.V run as
+    BF16 MMAs on exactly these operands, i.e. in the reference's own numerics. Returns (B, H, S, D) BF16.
+    Not served through this entry (``NotImplementedError``): ``v_block_scale_bsh`` (fp8_block V) and BLASST, which
+    only the FP8-code kernel behind ``fake_quant_attention`` implements.
+    """
+    if q_bhsd.ndim != 4 or k_bhsd.shape[:2] != q_bhsd.shape[:2] or v_bhsd_bf16.shape != k_bhsd.shape:
+        raise ValueError("q/k/v must be (B, H, S, D) with matching batch, heads and key length")
+    for t in (q_bhsd, k_bhsd, v_bhsd_bf16):
+        if t.dtype != torch.bfloat16:
+            raise TypeError("q_bhsd, k_bhsd and v_bhsd_bf16 must be BF16")
+    if v_scale_bhd.dtype != torch.float32:
+        raise TypeError("v_scale_bhd must be FP32")
+    if v_block_scale_bsh is not None:
+        raise NotImplementedError("v_block_scale_bsh (fp8_block V) is served by fake_quant_attention only")
+    if blasst_lambda is not None or return_blasst_stats:
+        raise NotImplementedError("BLASST is served by fake_quant_attention only")
+    B, H, M, D = q_bhsd.shape
+    N = k_bhsd.shape[2]
+    if v_scale_bhd.shape != (B, H, D):
+        raise ValueError("v_scale_bhd must be (B, H, D)")
+    if v_alpha is not None:
+        if v_smooth_block <= 0:
+            raise ValueError("v_smooth_block must be > 0 when v_alpha is given")
+        if v_smooth_block < block_n or v_smooth_block % block_n != 0:
+            raise ValueError(f"v_smooth_block ({v_smooth_block}) must be >= block_n ({block_n}) "
+                             "and an integer multiple of block_n")
+        if N % v_smooth_block != 0:
+            raise ValueError(f"S ({N}) must be divisible by v_smooth_block ({v_smooth_block})")
+    corr = None
+    m_pad, n_pad = (M + 127) // 128 * 128, (N + 127) // 128 * 128
+    if qm_bhgd is not None:
+        if k_smooth_bhsd is None:
+            raise ValueError("k_smooth_bhsd required with qm_bhgd")
+        if q_smooth_block <= 0:
+            raise ValueError("q_smooth_block must be > 0 with qm_bhgd")
+        if q_smooth_block < block_m or q_smooth_block % block_m != 0:
+            raise ValueError(f"q_smooth_block ({q_smooth_block}) must be >= block_m ({block_m}) "
+                             "and an integer multiple of block_m")
+        if M % q_smooth_block != 0:
+            raise ValueError(f"S ({M}) must be divisible by q_smooth_block ({q_smooth_block})")
+        corr, _ = qm_corr(qm_bhgd.permute(0, 2, 1, 3).contiguous().float(), k_smooth_bhsd.permute(0, 2, 1, 3).contiguous(),
+                          sm_scale=sm_scale, s_pad=n_pad, want_rowmax=False)
+
+    def pad_rows(t, rows):       # (B, H, S, D) -> (B, H, rows, D), zero rows appended
+        if t.shape[2] == rows:
+            return t.contiguous()
+        out = t.new_zeros(t.shape[0], t.shape[1], rows, t.shape[3])
+        out[:, :, : t.shape[2]] = t
+        return out
+
+    q_p, k_p = pad_rows(q_bhsd, m_pad), pad_rows(k_bhsd, n_pad)
+    v_t = pad_rows(v_bhsd_bf16, n_pad).transpose(2, 3).contiguous()              # (B, H, D, n_pad), keys contiguous
+    return fake_quant_attention_fp8(
+        q_p, k_p, v_t, seq_q=M, seq_k=N, q_scale=None, k_scale=None, qk_block=block_n, operands_bf16=True,
+        v_kind="fp8_channel", v_scale=v_scale_bhd, v_block=0,
+        sm_scale=float(sm_scale), p_max_offset=int(p_max_offset), block_m=block_m, block_n=block_n,
+        v_alpha=v_alpha, v_smooth_block=v_smooth_block, qm_corr=corr, q_smooth_block=q_smooth_block,
+        p_quant_mode=p_quant_mode, p_mx_block_n=p_mx_block_n,
+        rowmax_est_bhs=rowmax_est_bhs, rowmax_init_bhs=rowmax_init_bhs,
+        out_dtype=torch.float32 if _out_fp32 else torch.bfloat16, out_nhd=False, out_fp32_exact=_out_fp32,
+    )
