@@ -192,6 +192,8 @@ def main():
     ap.add_argument("--seq", type=int, default=S_REAL)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--reference-operands", action="store_true",
+                    help="run path B on the reference's own BF16 operands (BF16 MMAs) instead of the FP8 codes; not the headline")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     cfg_kwargs, batch = WORKLOADS[args.workload]
@@ -227,7 +229,7 @@ def main():
     lib = L.lib()
 
     def step(qq, kk, vv):
-        o = fq.fake_quant_attention(qq, kk, vv, cfg)
+        o = fq.fake_quant_attention(qq, kk, vv, cfg, _reference_operands=args.reference_operands)
         return o[:, :seq]
 
     def barrier():
@@ -325,8 +327,9 @@ def main():
         line = {
             "metric": "fused FP8 fake-quant attn TFLOP/s at 40x32760x128", "value": value, "unit": "TFLOP/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3", "data": "synthetic",
-            "config": {"workload": args.workload, "B_per_gpu": batch, "global_batch": batch * world, "H": heads,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16 (reference-operand mode)" if args.reference_operands else "fp8_e4m3", "data": "synthetic",
+            "config": {"workload": args.workload + ("+reference_operands" if args.reference_operands else ""), "B_per_gpu": batch, "global_batch": batch * world, "H": heads,
                        "S": seq, "S_padded": seq + pad, "D": D_HEAD, "input_dtype": "bf16",
                        "l2": "inputs (3 x %.0f MB) exceed the 126 MB L2" % (qp.numel() * 2 / 1e6),
                        "parallelism": f"batch x heads sharded over {world} GPU(s), no collective"},
