@@ -321,9 +321,11 @@ def main():
         cpu = None
         if not args.no_cpu_baseline and world == 1:
             torch.set_num_threads(os.cpu_count() or 1)
-            tf, dt = cpu_oracle_sample(cfg_kwargs, seq=32768, heads=1, steps=1)
+            reps = 8                                   # about 10-20 s of host work
+            tf, dt = cpu_oracle_sample(cfg_kwargs, seq=32768, heads=1, steps=reps)
             cpu = {"value": tf, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
-                   "sample": f"1 head x S=32768 of the workload (1/40 of a step), {dt:.2f} s, oracle port on the host cores"}
+                   "sample": f"1 head x S=32768 of the workload (1/40 of a step) x {reps} repeats, {dt:.2f} s each, "
+                             "oracle port on the host cores"}
         line = {
             "metric": "fused FP8 fake-quant attn TFLOP/s at 40x32760x128", "value": value, "unit": "TFLOP/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
