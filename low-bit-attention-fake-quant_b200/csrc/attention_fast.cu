@@ -35,9 +35,10 @@ namespace attn {
 
 namespace {
 
-// Two threads per query row: the pair reads the same S block, both take its maximum (so they never have to
-// talk to each other), and each computes the exponentials, the P codes and the accumulator rescale of one
-// half of the columns. 16 softmax warps give every scheduler four of them to hide each other's waits.
+// Two threads per query row: each reads one half of the S block's columns, takes their maximum, and the two halves'
+// maxima meet through shared memory and a 64-thread named barrier; each thread then computes the exponentials,
+// the P codes and the accumulator rescale of its half. 16 softmax warps give every scheduler four of them to hide
+// each other's waits.
 constexpr int kFastSoftmaxWarps = 16;
 constexpr int kFastThreads = (kFastSoftmaxWarps + 4) * 32;
 constexpr int kFastRegsLaunch = (65536 / kFastThreads) / 8 * 8;   // what __launch_bounds__(kFastThreads, 1) yields
@@ -66,7 +67,9 @@ struct FastSmem {
   static constexpr int offMisc = offBar + kNumBar * 8;
   static constexpr int offL = offMisc + 64;                    // row sums of the two column halves [tile][half][row]
   // score-bias rows (`corr`) of each tile's Q group, staged per 128-key stage by the producer
-  static constexpr int offCorr = offL + 2 * 2 * kTileM * 4;
+  // block maxima exchanged between the two threads of a row: [block parity][tile][half][row]
+  static constexpr int offX = offL + 2 * 2 * kTileM * 4;
+  static constexpr int offCorr = offX + 2 * 2 * 2 * kTileM * 4;
   // V-smoothing tiles for the K-extension of P.V: per stage up to two (D x 16) BF16 tiles (32-byte rows)
   static constexpr int kAext = D * 32;
   static constexpr int offAext = (offCorr + kStages * 2 * kChunk * 4 + 1023) / 1024 * 1024;   // TMA destination, swizzled
@@ -193,7 +196,13 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     // Key blocks alternate between the two S buffers; the loop body is instantiated once per buffer so that
     // every TMEM and barrier address in it is a loop-invariant register.
     const uint32_t tS_mine[2] = {tS + half * HB, tS + S_STRIDE + half * HB};
-    const uint32_t tS_oth[2] = {tS + (1 - half) * HB, tS + S_STRIDE + (1 - half) * HB};
+    // each thread takes the maximum of its own half of a block's columns; the halves meet through shared memory
+    // and a 64-thread named barrier per (tile, lane quarter) pair of warps (ids 2..9)
+    float* xch = reinterpret_cast<float*>(smem + SM::offX);
+    float* const x_mine[2] = {xch + ((0 * 2 + t) * 2 + half) * kTileM + row_in_tile, xch + ((1 * 2 + t) * 2 + half) * kTileM + row_in_tile};
+    const float* const x_oth[2] = {xch + ((0 * 2 + t) * 2 + (1 - half)) * kTileM + row_in_tile,
+                                   xch + ((1 * 2 + t) * 2 + (1 - half)) * kTileM + row_in_tile};
+    const uint32_t pair_bar = 2u + (uint32_t)(t * 4 + (warp & 3));
     constexpr int PW = PK ? HB / 2 : HB / 4;         // 32-bit words of P per thread: two BF16 or four e4m3 per word
     const uint32_t tP[2] = {tS + half * PW, tS + S_STRIDE + half * PW};
     // K-extension columns of P (V-smoothing term): 16 BF16 = 8 columns behind the 32 columns of P, 4 per thread
@@ -210,9 +219,8 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       if (!s_seen) mbar_wait_cont(bar_s[BUF], par, abort_flag, p.status, 12);
       s_seen = false;
       tc_fence_after();
-      uint32_t mine[HB], oth[HB];
+      uint32_t mine[HB];
       tmem_ld(mine, tS_mine[BUF]);
-      tmem_ld(oth, tS_oth[BUF]);
       tc_wait_ld();
       // (sq * sk) * sm_scale in the reference's order; without a score bias straight into the log2 domain
       const float f = (sq * sk) * sm_scale;
@@ -226,39 +234,38 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         }
       }
       if constexpr (CORR) {
-        // scores = dot * f + corr (attention_triton.py:154-160), all 64 columns: the max needs them
+        // scores = dot * f + corr (attention_triton.py:154-160)
         if (side_sub == 0) mbar_wait_cont(BAR_SIDEFULL(side_stage), side_par, abort_flag, p.status, 15);
         const float* crow = corr_sm + side_stage * (2 * kChunk) + side_sub * BN;
         const float4* cm = reinterpret_cast<const float4*>(crow + half * HB);
-        const float4* co = reinterpret_cast<const float4*>(crow + (1 - half) * HB);
         const float2 f2 = make_float2(f, f);
 #pragma unroll
         for (int i = 0; i < HB / 4; ++i) {
-          const float4 a = cm[i], o = co[i];               // same address in every lane: broadcast loads
+          const float4 a = cm[i];                          // same address in every lane: broadcast loads
           const float2 m01 = __ffma2_rn(make_float2(__uint_as_float(mine[4 * i]), __uint_as_float(mine[4 * i + 1])), f2, make_float2(a.x, a.y));
           const float2 m23 = __ffma2_rn(make_float2(__uint_as_float(mine[4 * i + 2]), __uint_as_float(mine[4 * i + 3])), f2, make_float2(a.z, a.w));
-          const float2 o01 = __ffma2_rn(make_float2(__uint_as_float(oth[4 * i]), __uint_as_float(oth[4 * i + 1])), f2, make_float2(o.x, o.y));
-          const float2 o23 = __ffma2_rn(make_float2(__uint_as_float(oth[4 * i + 2]), __uint_as_float(oth[4 * i + 3])), f2, make_float2(o.z, o.w));
           mine[4 * i] = __float_as_uint(m01.x); mine[4 * i + 1] = __float_as_uint(m01.y);
           mine[4 * i + 2] = __float_as_uint(m23.x); mine[4 * i + 3] = __float_as_uint(m23.y);
-          oth[4 * i] = __float_as_uint(o01.x); oth[4 * i + 1] = __float_as_uint(o01.y);
-          oth[4 * i + 2] = __float_as_uint(o23.x); oth[4 * i + 3] = __float_as_uint(o23.y);
         }
       }
       if (!more && tail_valid < BN) {          // ragged tail: only the last block of a sequence
 #pragma unroll
-        for (int i = 0; i < HB; ++i) {
+        for (int i = 0; i < HB; ++i)
           if (half * HB + i >= tail_valid) mine[i] = 0xff800000u;
-          if ((1 - half) * HB + i >= tail_valid) oth[i] = 0xff800000u;
-        }
       }
-      float bm0 = fmaxf(__uint_as_float(mine[0]), __uint_as_float(oth[0]));
-      float bm1 = fmaxf(__uint_as_float(mine[1]), __uint_as_float(oth[1]));
+      float bm0 = __uint_as_float(mine[0]), bm1 = __uint_as_float(mine[1]);
 #pragma unroll
       for (int i = 2; i < HB; i += 2) {
-        bm0 = fmaxf(bm0, fmaxf(__uint_as_float(mine[i]), __uint_as_float(oth[i])));
-        bm1 = fmaxf(bm1, fmaxf(__uint_as_float(mine[i + 1]), __uint_as_float(oth[i + 1])));
+        bm0 = fmaxf(bm0, __uint_as_float(mine[i]));
+        bm1 = fmaxf(bm1, __uint_as_float(mine[i + 1]));
       }
+      // the other half's maximum (a block's two slots alternate, so a slot is rewritten only after the barrier
+      // of the next block, when its reader is done with it)
+      const float own_max = fmaxf(bm0, bm1);
+      *x_mine[BUF] = own_max;
+      asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
+      bm0 = own_max;
+      bm1 = *x_oth[BUF];
       const float bmax_raw = fmaxf(bm0, bm1);
       const float bmax = bmax_raw * c;
 
