@@ -720,8 +720,8 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
   if (warp == kTmaWarp) {
     if (*abort_flag && lane == 0) {
       // give in-flight bulk copies a bounded time to land before the CTA retires
-      const unsigned long long t0 = clock64();
-      while (clock64() - t0 < 2000000ull) { }
+      const long long t0 = wall_ns();
+      while (wall_ns() - t0 < 1000000ll) { }
     }
     __syncwarp();
     tc_fence_after();

@@ -263,6 +263,7 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       // of the next block, when its reader is done with it)
       const float own_max = fmaxf(bm0, bm1);
       *x_mine[BUF] = own_max;
+      __syncwarp();                            // a named barrier counts warps: arrive once, converged
       asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
       bm0 = own_max;
       bm1 = *x_oth[BUF];
@@ -619,11 +620,7 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       for (int it = 0; it < nblk && ok; ++it) {
         // P.V of this block once its P is in TMEM (and the rows that raised their max are rescaled), then
         // Q.K^T of block it + 2 into the S buffer that P has just been read from
-#ifdef LBFQ_MMA_SPIN
-        { unsigned long long t0 = clock64(); ok = true; uint32_t n = 0; while (!mbar_try(BAR_PRDY(t), it & 1)) { if ((++n & 1023u) == 0 && (*abort_flag || clock64() - t0 > kWaitCycles)) { *abort_flag = 1; if (p.status) atomicCAS(p.status, 0, 35); ok = false; break; } } }
-#else
         ok = mbar_wait(BAR_PRDY(t), it & 1, abort_flag, p.status, 35);
-#endif
         if (ok) ok = issue_pv(it);
         if (ok && it + 2 < nblk) ok = issue_qk(it + 2);
       }
@@ -636,8 +633,8 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   if (warp == kTmaWarp) {
     if (*abort_flag && lane == 0) {
       // give in-flight bulk copies a bounded time to land before the CTA retires
-      const unsigned long long t0 = clock64();
-      while (clock64() - t0 < 2000000ull) { }
+      const long long t0 = wall_ns();
+      while (wall_ns() - t0 < 1000000ll) { }
     }
     __syncwarp();
     tc_fence_after();

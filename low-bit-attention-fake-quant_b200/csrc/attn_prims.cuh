@@ -30,7 +30,15 @@ static_assert(kRegsSoftmax % 8 == 0 && kRegsService % 8 == 0 && kRegsService >= 
 #ifndef LBFQ_PARK_NS
 #define LBFQ_PARK_NS 20000u
 #endif
-constexpr unsigned long long kWaitCycles = 1000000000ull;   // ~0.5 s: far above any legitimate wait
+// Bound of every wait, in nanoseconds of the device-wide %globaltimer: far above any legitimate wait, and long enough
+// to ride out a pause of the whole context (another process's start-up on the same driver has been seen to stall a
+// running launch). The per-SM cycle counter is not used: it is not guaranteed to be continuous across such pauses.
+constexpr long long kWaitNs = 4000000000ll;   // 4 s
+__device__ __forceinline__ long long wall_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return (long long)t;
+}
 
 // ---------------------------------------------------------------------------
 // PTX wrappers
@@ -71,11 +79,11 @@ __device__ __forceinline__ bool mbar_try_parked(uint32_t bar, uint32_t parity, u
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int32_t* status,
                                           int code) {
   if (mbar_try(bar, parity)) return true;
-  const unsigned long long t0 = clock64();
+  const long long t0 = wall_ns();
   while (true) {
     if (mbar_try_parked(bar, parity, LBFQ_PARK_NS)) return true;
     if (*abort_flag) return false;
-    if (clock64() - t0 > kWaitCycles) {
+    if (wall_ns() - t0 > kWaitNs) {
       *abort_flag = 1;
       if (status) atomicCAS(status, 0, code);
       return false;
@@ -90,9 +98,9 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 __device__ __forceinline__ void mbar_wait_cont(uint32_t bar, uint32_t parity, volatile int* abort_flag, int32_t* status,
                                                int code) {
   if (mbar_try(bar, parity)) return;
-  const unsigned long long t0 = clock64();
+  const long long t0 = wall_ns();
   while (!*abort_flag && !mbar_try_parked(bar, parity, LBFQ_PARK_NS)) {
-    if (clock64() - t0 > kWaitCycles) {
+    if (wall_ns() - t0 > kWaitNs) {
       *abort_flag = 1;
       if (status) atomicCAS(status, 0, code);
       return;
