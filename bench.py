@@ -218,6 +218,10 @@ def main():
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group(backend="nccl", device_id=dev)
+        # bring the communicator up now, before any of the library's kernels is in flight: its set-up (peer
+        # mappings, NVLS binding) otherwise runs under the first barrier, concurrently with the warm-up launches
+        dist.all_reduce(torch.zeros(1, device=dev))
+        torch.cuda.synchronize(dev)
 
     cfg = QuantConfig(**cfg_kwargs)
     heads, seq = args.heads, args.seq
@@ -233,9 +237,10 @@ def main():
         return o[:, :seq]
 
     def barrier():
+        torch.cuda.synchronize(dev)
         if dist is not None:
             dist.barrier()
-        torch.cuda.synchronize(dev)
+            torch.cuda.synchronize(dev)
 
     # the clock sampler (an nvidia-smi child) is started before the warm-up: its start-up takes the driver's
     # locks for a few hundred ms, which would otherwise stall kernel launches inside a short timed region
