@@ -311,15 +311,15 @@ def main():
         k_ms = sum(kernel_ms) / max(len(kernel_ms), 1)
         achieved = flops_per_step / (k_ms * 1e-3) / 1e12 if k_ms > 0 else 0.0
         # DRAM bytes of one attention launch, measured by ncu on a 4-head launch of the same S and scaled by heads
-        # (each head's traffic is independent): 53.9 MB for the TMEM-resident variant
-        # (profiles/attn_fast_kernel_wan14b_k_smooth_static.md), 136.6 MB for the general kernel on the
+        # (each head's traffic is independent): 55.5 MB for the TMEM-resident kernel on the k_smooth_static stack, 171.1 MB
+        # on the full_dynamic stack (profiles/attn_fast_kernel_wan14b_*.md), 136.6 MB for the general kernel on the
         # full_dynamic stack (profiles/attn_kernel_wan14b_full_dynamic.md)
         fast = lib.lbfq_attention_last_variant() == 1
         traffic = None
         if seq == S_REAL and fast and args.workload == "wan14b_self_attn_k_smooth_static":
-            traffic = 53.87e6 * heads / 4.0
-        elif seq == S_REAL and not fast and args.workload == "wan14b_self_attn_full_dynamic":
-            traffic = 136.6e6 * heads / 4.0
+            traffic = 55.47e6 * heads / 4.0
+        elif seq == S_REAL and args.workload == "wan14b_self_attn_full_dynamic":
+            traffic = (171.1e6 if fast else 136.6e6) * heads / 4.0
         roofline = {"bound": "tensor", "achieved": achieved, "peak": fp8_peak, "unit": "TFLOP/s",
                     "frac": achieved / fp8_peak, "traffic": traffic, "kernel": "attn_fast_kernel<128,64>" if lib.lbfq_attention_last_variant() == 1 else "attn_kernel<128,64>",
                     "kernel_ms": k_ms, "peak_source": f"2 x bf16_tflops ({peak_src})"}
