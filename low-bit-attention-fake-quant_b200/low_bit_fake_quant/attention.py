@@ -17,6 +17,7 @@ kernel's output store.
 from __future__ import annotations
 
 import math
+import os
 from dataclasses import dataclass
 from typing import Optional
 
@@ -383,7 +384,15 @@ def fake_quant_attention(
         q_work, k_work, v_work, qm, v_alpha, q_km, _ = _preprocess(q, k, v, cfg, head_offset=_head_offset,
                                                                    total_heads=_total_heads)
 
-    if cfg.p_requant and _reference_operands:
+    # mxfp8 Q / K de-quantise to BF16 exactly (power-of-two scales), so for them the BF16-operand kernel computes
+    # the same products as a block-scaled FP8 MMA and, unlike the general kernel, keeps the accumulator in tensor
+    # memory; it takes them whenever it serves the rest of the configuration
+    # (LBFQ_ATTN_GENERIC=1 keeps them on the general kernel's block-scaled Q.K^T, the cross-check)
+    mx_as_bf16 = (cfg.qk_quant == "mxfp8" and cfg.v_quant != "fp8_block" and cfg.blasst_lambda is None
+                  and os.environ.get("LBFQ_ATTN_GENERIC") != "1"
+                  and (qm is None or cfg.q_smooth_block_size % 128 == 0)
+                  and (v_alpha is None or cfg.v_smooth_block_size >= 64))
+    if cfg.p_requant and (_reference_operands or mx_as_bf16):
         o = _fake_quant_attention_p_requant_reference_operands(
             q_work, k_work, v_work, qm, v_alpha, q_km, cfg, sm_scale, out_dtype, out_fp32_exact=_debug_fp32,
             head_offset=_head_offset, total_heads=_total_heads)

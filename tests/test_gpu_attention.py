@@ -333,11 +333,30 @@ def test_tmem_resident_variant_row_max_seeds(mode, monkeypatch):
     assert OA.parity_ok(OA.parity_report(fast, gen, q, k, v))
 
 
-def test_mxfp8_qk_needs_block_n_64():
+@pytest.mark.parametrize("name", ["mxfp8_qk", "mxfp8_qk_full_dynamic", "mxfp8_all_hadamard"])
+def test_block_scaled_general_kernel_matches_oracle(name, monkeypatch):
+    """mxfp8 Q / K normally run as exact BF16 operands on the TMEM-resident kernel; the general kernel's block-scaled
+    Q.K^T (kind::mxf8f6f4 with UE8M0 scales in tensor memory) stays covered through the override."""
+    monkeypatch.setenv("LBFQ_ATTN_GENERIC", "1")
+    cfg = QuantConfig(**{**COMMON, **CASES[name]})
+    q, k, v = _qkv(1, 512, 2, 128, seed=zlib.crc32(name.encode()) % 1000)
+    g, o = _run_both(q, k, v, cfg)
+    assert _variant() == 0
+    _check(g, o)
+
+
+def test_mxfp8_qk_block_n_32_runs_on_bf16_operands():
+    """Block-scaled Q.K^T needs block_n = 64 (scale-factor columns); with block_n = 32 mxfp8 Q / K are served as
+    BF16 operands (exact for power-of-two scales) by the TMEM-resident kernel. BLASST keeps them on the general
+    kernel, which then refuses block_n = 32."""
+    q, k, v = _qkv(1, 512, 2, 128, seed=41)
+    cfg = QuantConfig(qk_quant="mxfp8", smoothing="off", q_kmeans_k=None, p_requant_block_m=32, p_requant_block_n=32)
+    g, o = _run_both(q, k, v, cfg)
+    _check(g, o)
     x = torch.zeros(1, 128, 1, 128, dtype=torch.bfloat16, device=DEV)
     with pytest.raises(NotImplementedError, match="block_n = 64"):
         fq.fake_quant_attention(x, x, x, QuantConfig(qk_quant="mxfp8", smoothing="off", q_kmeans_k=None,
-                                                     p_requant_block_m=32, p_requant_block_n=32))
+                                                     p_requant_block_m=32, p_requant_block_n=32, blasst_lambda=0.1))
 
 
 def test_errors():
