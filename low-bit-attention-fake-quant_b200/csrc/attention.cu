@@ -1,7 +1,11 @@
-// Streaming fake-quant attention for sm_100a: real FP8 tensor-core MMAs.
+// Streaming fake-quant attention for sm_100a: the general kernel, and the host side of lbfq_attention_fwd.
 //
 // Replaces `_fake_quant_attn_fwd_kernel` and its launcher
-// (src/low_bit_fake_quant/attention_triton.py:48-671). The reference feeds
+// (src/low_bit_fake_quant/attention_triton.py:48-671). Configurations in which every key block's P.V enters the
+// output with weight one are dispatched to the kernel of attention_fast.cu, whose output accumulator lives in
+// tensor memory; this kernel serves the rest (a per-block FP32 scale on P.V: fp8_block V; BLASST skip / fill;
+// block-scaled mxfp8 Q / K; small score-bias groups or V-smoothing blocks), implements every mode, and is the
+// cross-check of the other one (LBFQ_ATTN_GENERIC=1). The reference feeds
 // de-quantised BF16 operands to BF16 `tl.dot`; here the e4m3 codes themselves
 // are the MMA operands and every scale is applied in FP32 around the MMA:
 //
