@@ -134,11 +134,55 @@ assign_kernel(const T* __restrict__ x, int S, int H, int D, int k, const float* 
   }
 }
 
-// stable counting sort (same algorithm as label_order_kernel) that also emits
-// the k+1 segment offsets of each slab
+// Stable counting sort of one slab's labels, one CTA per slab; also emits the k + 1 segment offsets.
+// Histogram, exclusive scan, then the tokens in chunks of 1024 in token order: a lane finds the lanes of its warp
+// with the same label (__match_any_sync), the warp leaders of each label publish their counts, an exclusive scan
+// over the 32 warps per label turns them into positions, and every lane stores its token. O(S) work per slab;
+// the order inside a cluster is the token order, so the sums taken over it are bit-reproducible.
+constexpr int kSortMaxK = 64;
 __global__ void __launch_bounds__(1024)
 sort_segments_kernel(const int32_t* __restrict__ labels, int S, int k, int32_t* __restrict__ order32,
                      int32_t* __restrict__ seg) {
+  __shared__ int counts[kSortMaxK];
+  __shared__ int offsets[kSortMaxK];
+  __shared__ int wc[32][kSortMaxK];               // per warp and label: count, then start position
+  const int32_t* lab = labels + (size_t)blockIdx.x * S;
+  int32_t* ord = order32 + (size_t)blockIdx.x * S;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int i = threadIdx.x; i < k; i += blockDim.x) counts[i] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < S; i += blockDim.x) atomicAdd(&counts[lab[i]], 1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int run = 0;
+    for (int c = 0; c < k; ++c) { offsets[c] = run; seg[(size_t)blockIdx.x * (k + 1) + c] = run; run += counts[c]; }
+    seg[(size_t)blockIdx.x * (k + 1) + k] = run;
+  }
+  for (int base = 0; base < S; base += 1024) {
+    for (int i = threadIdx.x; i < 32 * kSortMaxK; i += blockDim.x) (&wc[0][0])[i] = 0;
+    __syncthreads();                                          // also orders `offsets` (first pass: thread 0's scan)
+    const int i = base + (int)threadIdx.x;
+    const bool valid = i < S;
+    const int lbl = valid ? lab[i] : -1;
+    const unsigned peers = __match_any_sync(0xffffffffu, lbl);
+    const int rank = __popc(peers & ((1u << lane) - 1u));
+    if (valid && rank == 0) wc[warp][lbl] = __popc(peers);
+    __syncthreads();
+    if ((int)threadIdx.x < k) {                               // exclusive scan over the warps, in token order
+      int run = offsets[threadIdx.x];
+      for (int w = 0; w < 32; ++w) { const int c = wc[w][threadIdx.x]; wc[w][threadIdx.x] = run; run += c; }
+      offsets[threadIdx.x] = run;
+    }
+    __syncthreads();
+    if (valid) ord[wc[warp][lbl] + rank] = i;
+    __syncthreads();
+  }
+}
+
+// the same sort for more labels than the shared-memory tables above hold: one warp per label scans the slab
+__global__ void __launch_bounds__(1024)
+sort_segments_scan_kernel(const int32_t* __restrict__ labels, int S, int k, int32_t* __restrict__ order32,
+                          int32_t* __restrict__ seg) {
   extern __shared__ int sm_counts[];
   int* counts = sm_counts;
   int* offsets = sm_counts + k;
@@ -262,7 +306,8 @@ extern "C" int lbfq_kmeans_labels(const void* x, int dtype, int B, int S, int H,
     }
     if (int rc = check_launch("kmeans assign")) return rc;
     if (it + 1 == iters) break;                     // labels of the last assignment are the result
-    sort_segments_kernel<<<BH, 1024, 2 * k * sizeof(int), st>>>(labels, S, k, sc.order32, sc.seg);
+    if (k <= kSortMaxK) sort_segments_kernel<<<BH, 1024, 0, st>>>(labels, S, k, sc.order32, sc.seg);
+    else sort_segments_scan_kernel<<<BH, 1024, 2 * k * sizeof(int), st>>>(labels, S, k, sc.order32, sc.seg);
     if (int rc = check_launch("kmeans sort")) return rc;
     LBFQ_DISPATCH_DTYPE(dtype, T,
         segment_mean_kernel<T><<<BH * k, kThreads, 0, st>>>((const T*)x, S, H, D, k, sc.order32, sc.seg, sc.cent, sc.cnorm));
