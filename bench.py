@@ -224,6 +224,8 @@ def main():
     ap.add_argument("--seq", type=int, default=S_REAL)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--e2e-heads-per-chunk", type=int, default=None,
+                    help="heads per pipelined chunk of the host-buffer entry (default: the entry's own choice)")
     ap.add_argument("--reference-operands", action="store_true",
                     help="run path B on the reference's own BF16 operands (BF16 MMAs) instead of the FP8 codes; not the headline")
     args = ap.parse_args()
@@ -317,7 +319,7 @@ def main():
         hout = torch.empty((batch, seq, heads, D_HEAD), dtype=qp.dtype).pin_memory()
 
         def e2e_step():
-            fq.fake_quant_attention_host(hq, hk, hv, cfg, out=hout, device=dev)
+            fq.fake_quant_attention_host(hq, hk, hv, cfg, out=hout, device=dev, heads_per_chunk=args.e2e_heads_per_chunk)
 
         for _ in range(2):
             e2e_step()

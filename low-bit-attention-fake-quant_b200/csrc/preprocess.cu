@@ -199,10 +199,57 @@ hadamard_kernel(const T* __restrict__ x, T* __restrict__ out, const int8_t* __re
 }
 
 // ---- permutation -------------------------------------------------------------
-// stable counting sort of labels: one CTA per (b,h) slab, one warp per label.
+// Stable counting sort of labels, one CTA per (b,h) slab (kmeans.py:84-88: order = stable argsort(labels),
+// inverse[order[j]] = j). Up to 64 labels: histogram, scan, then the tokens in chunks of 1024 in token order -- a lane
+// finds the lanes of its warp with the same label, the warp leaders publish their counts, an exclusive scan over
+// the 32 warps per label turns them into positions. More labels: one warp per label scans the slab.
+constexpr int kOrderMaxK = 64;
 __global__ void __launch_bounds__(1024)
 label_order_kernel(const int32_t* __restrict__ labels, int S, int k, int64_t* __restrict__ order,
                    int64_t* __restrict__ inverse) {
+  __shared__ int counts[kOrderMaxK];
+  __shared__ int offsets[kOrderMaxK];
+  __shared__ int wc[32][kOrderMaxK];              // per warp and label: count, then start position
+  const int32_t* lab = labels + (size_t)blockIdx.x * S;
+  int64_t* ord = order + (size_t)blockIdx.x * S;
+  int64_t* inv = inverse + (size_t)blockIdx.x * S;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int i = threadIdx.x; i < k; i += blockDim.x) counts[i] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < S; i += blockDim.x) atomicAdd(&counts[lab[i]], 1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int run = 0;
+    for (int c = 0; c < k; ++c) { offsets[c] = run; run += counts[c]; }
+  }
+  for (int base = 0; base < S; base += 1024) {
+    for (int i = threadIdx.x; i < 32 * kOrderMaxK; i += blockDim.x) (&wc[0][0])[i] = 0;
+    __syncthreads();
+    const int i = base + (int)threadIdx.x;
+    const bool valid = i < S;
+    const int lbl = valid ? lab[i] : -1;
+    const unsigned peers = __match_any_sync(0xffffffffu, lbl);
+    const int rank = __popc(peers & ((1u << lane) - 1u));
+    if (valid && rank == 0) wc[warp][lbl] = __popc(peers);
+    __syncthreads();
+    if ((int)threadIdx.x < k) {                               // exclusive scan over the warps, in token order
+      int run = offsets[threadIdx.x];
+      for (int w = 0; w < 32; ++w) { const int c = wc[w][threadIdx.x]; wc[w][threadIdx.x] = run; run += c; }
+      offsets[threadIdx.x] = run;
+    }
+    __syncthreads();
+    if (valid) {
+      const int p = wc[warp][lbl] + rank;
+      ord[p] = i;
+      inv[i] = p;
+    }
+    __syncthreads();
+  }
+}
+
+__global__ void __launch_bounds__(1024)
+label_order_scan_kernel(const int32_t* __restrict__ labels, int S, int k, int64_t* __restrict__ order,
+                        int64_t* __restrict__ inverse) {
   extern __shared__ int sm_counts[];              // k counts, then k offsets
   int* counts = sm_counts;
   int* offsets = sm_counts + k;
@@ -444,7 +491,8 @@ extern "C" int lbfq_hadamard(const void* x, int dtype, int64_t rows, int H, int 
 extern "C" int lbfq_label_order(const int32_t* labels, int BH, int S, int k, int64_t* order, int64_t* inverse,
                                 void* stream) {
   LBFQ_REQUIRE(BH > 0 && S > 0 && k > 0 && k <= 4096, LBFQ_ERR_ARG, "label_order: bad sizes BH=%d S=%d k=%d", BH, S, k);
-  label_order_kernel<<<BH, 1024, 2 * k * sizeof(int), (cudaStream_t)stream>>>(labels, S, k, order, inverse);
+  if (k <= kOrderMaxK) label_order_kernel<<<BH, 1024, 0, (cudaStream_t)stream>>>(labels, S, k, order, inverse);
+  else label_order_scan_kernel<<<BH, 1024, 2 * k * sizeof(int), (cudaStream_t)stream>>>(labels, S, k, order, inverse);
   return check_launch("label_order");
 }
 

@@ -44,14 +44,14 @@ def fake_quant_attention_host(
     sm_scale: Optional[float] = None,
     out: Optional[torch.Tensor] = None,
     device: Optional[torch.device] = None,
-    heads_per_chunk: int = 8,
+    heads_per_chunk: Optional[int] = None,
 ) -> torch.Tensor:
     """``fake_quant_attention`` on host tensors.
 
     ``q, k, v``: contiguous (B, S, H, D) CPU tensors (pinned memory makes the copies asynchronous).
     ``out``: optional contiguous (B, S_out <= S, H, D) CPU tensor of ``q``'s dtype; only its first ``S_out``
     rows are brought back (the caller's way to drop padding rows). Returns ``out``; it is complete when
-    this function returns.
+    this function returns. ``heads_per_chunk``: heads per pipelined chunk (default 4, or 8 with k-means reorder).
     """
     if cfg is None:
         cfg = QuantConfig()
@@ -74,6 +74,9 @@ def fake_quant_attention_host(
         raise ValueError(f"out must be (B, S_out <= S, H, D); got {tuple(out.shape)}")
     if out.dtype != q.dtype or out.is_cuda or not out.is_contiguous():
         raise ValueError("out must be a contiguous host tensor of q's dtype")
+    if heads_per_chunk is None:
+        # small chunks hide more of the copies; the k-means passes want enough heads per launch to fill the GPU
+        heads_per_chunk = 8 if (cfg.q_kmeans_k is not None or cfg.v_kmeans_k is not None) else 4
     if heads_per_chunk <= 0:
         raise ValueError("heads_per_chunk must be positive")
     dev = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
