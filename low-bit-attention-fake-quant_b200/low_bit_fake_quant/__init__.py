@@ -1,67 +1,33 @@
 """B200-native drop-in for the ``low_bit_fake_quant`` package.
 
-Exports the same names as the reference package
-(src/low_bit_fake_quant/__init__.py:3-60). Every device step runs in
-``liblbfq.so`` (hand-written sm_100a CUDA behind a C ABI, see include/lbfq.h);
-there is no Triton, no CPU fallback and no other backend.
+The public names are those of the reference package (src/low_bit_fake_quant/__init__.py:3-60); every device step
+behind them runs in ``liblbfq.so`` (hand-written sm_100a CUDA behind a C ABI, see include/lbfq.h). There is no
+Triton, no CPU fallback and no other backend. ``fake_quant_attention_host`` is an extension (host-resident tensors,
+copies pipelined with compute) and is therefore kept out of ``__all__``.
 """
-
-from .attention import (
-    FakeQuantArtifacts,
-    PreprocessCache,
-    fake_quant_attention,
-    prepare_for_attention,
-    reference_attention,
-)
+from . import attention as _attention
+from . import hadamard as _hadamard
+from . import kmeans as _kmeans
+from . import pipeline as _pipeline
+from . import preprocess as _preprocess
+from . import quant_triton as _quant
 from .config import QuantConfig
-from .host import fake_quant_attention_host  # extension: not in the reference, hence not in __all__
-from .hadamard import apply_qk_hadamard, fast_hadamard_available, hadamard_transform_last_dim
-from .kmeans import (
-    KMeansReorderResult,
-    apply_kv_permutation,
-    kmeans_reorder_tokens,
-    q_kmeans_reorder,
-    v_kmeans_reorder,
-)
-from .pipeline import PreparedQKV, prepare_qkv
-from .preprocess import group_mean_q, smooth_k, smooth_v_per_block
-from .quant_triton import (
-    fp8_block_dequant,
-    fp8_block_quant,
-    fp8_per_channel_dequant,
-    fp8_per_channel_quant,
-    mxfp8_qk_dequant,
-    mxfp8_qk_quant,
-    mxfp8_v_dequant,
-    mxfp8_v_quant,
-)
+from .host import fake_quant_attention_host
 
-__all__ = [
-    "FakeQuantArtifacts",
-    "KMeansReorderResult",
-    "PreparedQKV",
-    "PreprocessCache",
-    "QuantConfig",
-    "apply_qk_hadamard",
-    "fake_quant_attention",
-    "fast_hadamard_available",
-    "prepare_for_attention",
-    "fp8_block_dequant",
-    "fp8_block_quant",
-    "fp8_per_channel_dequant",
-    "fp8_per_channel_quant",
-    "group_mean_q",
-    "hadamard_transform_last_dim",
-    "smooth_v_per_block",
-    "mxfp8_qk_dequant",
-    "mxfp8_qk_quant",
-    "mxfp8_v_dequant",
-    "mxfp8_v_quant",
-    "prepare_qkv",
-    "apply_kv_permutation",
-    "kmeans_reorder_tokens",
-    "q_kmeans_reorder",
-    "v_kmeans_reorder",
-    "reference_attention",
-    "smooth_k",
-]
+# name -> module that defines it; the export list below is generated from this table
+_EXPORTS = {
+    _attention: "FakeQuantArtifacts PreprocessCache fake_quant_attention prepare_for_attention reference_attention",
+    _hadamard: "apply_qk_hadamard fast_hadamard_available hadamard_transform_last_dim",
+    _kmeans: "KMeansReorderResult apply_kv_permutation kmeans_reorder_tokens q_kmeans_reorder v_kmeans_reorder",
+    _pipeline: "PreparedQKV prepare_qkv",
+    _preprocess: "group_mean_q smooth_k smooth_v_per_block",
+    _quant: ("fp8_block_quant fp8_block_dequant fp8_per_channel_quant fp8_per_channel_dequant "
+             "mxfp8_qk_quant mxfp8_qk_dequant mxfp8_v_quant mxfp8_v_dequant"),
+}
+__all__ = ["QuantConfig"]
+for _module, _names in _EXPORTS.items():
+    for _name in _names.split():
+        globals()[_name] = getattr(_module, _name)
+        __all__.append(_name)
+__all__.sort()
+del _module, _names, _name

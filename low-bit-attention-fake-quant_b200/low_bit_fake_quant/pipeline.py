@@ -32,52 +32,55 @@ class PreparedQKV:
     kmeans: KMeansReorderResult | None = None
 
 
-def prepare_qkv(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cfg: QuantConfig) -> PreparedQKV:
-    """Run the configured QKV preprocessing and quantization pipeline."""
-    if q.shape != k.shape or q.shape != v.shape:
+# quantizer dispatch by configuration string: (tensor, cfg) -> (codes, scale)
+_QK_QUANTIZERS = {
+    "fp8_block": lambda t, cfg: fp8_block_quant(t, block_s=cfg.fp8_block_size),
+    "mxfp8": lambda t, cfg: mxfp8_qk_quant(t, block_d=cfg.mxfp8_block_size),
+}
+_V_QUANTIZERS = {
+    "fp8_channel": lambda t, cfg: fp8_per_channel_quant(t),
+    "fp8_block": lambda t, cfg: fp8_block_quant(t, block_s=cfg.v_fp8_block_size),
+    "mxfp8": lambda t, cfg: mxfp8_v_quant(t, block_s=cfg.v_mxfp8_block_size),
+}
+
+
+def _checked_inputs(q, k, v):
+    if not (q.shape == k.shape == v.shape):
         raise ValueError(f"q/k/v shapes must match; got {q.shape}, {k.shape}, {v.shape}")
     if q.ndim != 4:
         raise ValueError(f"q/k/v must be 4-D NHD; got {q.shape}")
-    if not (q.is_cuda and k.is_cuda and v.is_cuda):
+    if not all(t.is_cuda for t in (q, k, v)):
         raise ValueError("q/k/v must live on CUDA")
-    res = PreparedQKV(q=None, k=None, v=None, q_scale=None, k_scale=None, v_scale=None)  # type: ignore[arg-type]
-    q_work, k_work, v_work = q.contiguous(), k.contiguous(), v.contiguous()
+    return q.contiguous(), k.contiguous(), v.contiguous()
+
+
+def prepare_qkv(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cfg: QuantConfig) -> PreparedQKV:
+    """Preprocess (Q k-means reorder, K / Q smoothing, Hadamard) and quantise; codes and scales come back in the
+    reference's shapes (pipeline.py:42-110)."""
+    if cfg.smoothing not in ("off", "k_only", "full"):
+        raise ValueError(f"unsupported smoothing mode: {cfg.smoothing!r}")
+    if cfg.qk_quant not in _QK_QUANTIZERS:
+        raise ValueError(f"unsupported qk_quant: {cfg.qk_quant!r}")
+    if cfg.v_quant not in _V_QUANTIZERS:
+        raise ValueError(f"unsupported v_quant: {cfg.v_quant!r}")
+    qw, kw, vw = _checked_inputs(q, k, v)
+    kmeans = qm = k_mean = correction = None
 
     if cfg.q_kmeans_k is not None:
-        res.kmeans = q_kmeans_reorder(q_work, n_clusters=cfg.q_kmeans_k, max_iters=cfg.q_kmeans_iters,
-                                      seed=cfg.q_kmeans_seed)
-        q_work = res.kmeans.q_reordered
-
-    if cfg.smoothing in ("k_only", "full"):
-        k_work, res.k_mean = smooth_k(k_work)
-        if cfg.smoothing == "full":
-            q_work, res.qm = group_mean_q(q_work, block_q=cfg.q_smooth_block_size)
-            # einsum("bqhd,bshd->bqhs") of the reference, as one fp32 product on the device
-            s = k_work.shape[1]
-            corr, _ = qm_corr(res.qm, k_work, sm_scale=1.0, s_pad=(s + 63) // 64 * 64)
-            res.correction = corr[..., :s].permute(0, 2, 1, 3).contiguous().to(cfg.correction_dtype)
-    elif cfg.smoothing != "off":
-        raise ValueError(f"unsupported smoothing mode: {cfg.smoothing!r}")
-
+        kmeans = q_kmeans_reorder(qw, n_clusters=cfg.q_kmeans_k, max_iters=cfg.q_kmeans_iters, seed=cfg.q_kmeans_seed)
+        qw = kmeans.q_reordered
+    if cfg.smoothing != "off":
+        kw, k_mean = smooth_k(kw)
+    if cfg.smoothing == "full":
+        qw, qm = group_mean_q(qw, block_q=cfg.q_smooth_block_size)
+        # the reference's einsum("bqhd,bshd->bqhs") as one FP32 product on the device
+        n_keys = kw.shape[1]
+        corr, _ = qm_corr(qm, kw, sm_scale=1.0, s_pad=(n_keys + 63) // 64 * 64)
+        correction = corr[..., :n_keys].permute(0, 2, 1, 3).contiguous().to(cfg.correction_dtype)
     if cfg.qk_hadamard:
-        q_work, k_work = apply_qk_hadamard(q_work, k_work, random_sign=cfg.qk_hadamard_random_sign,
-                                           seed=cfg.qk_hadamard_seed)
+        qw, kw = apply_qk_hadamard(qw, kw, random_sign=cfg.qk_hadamard_random_sign, seed=cfg.qk_hadamard_seed)
 
-    if cfg.qk_quant == "fp8_block":
-        res.q, res.q_scale = fp8_block_quant(q_work, block_s=cfg.fp8_block_size)
-        res.k, res.k_scale = fp8_block_quant(k_work, block_s=cfg.fp8_block_size)
-    elif cfg.qk_quant == "mxfp8":
-        res.q, res.q_scale = mxfp8_qk_quant(q_work, block_d=cfg.mxfp8_block_size)
-        res.k, res.k_scale = mxfp8_qk_quant(k_work, block_d=cfg.mxfp8_block_size)
-    else:
-        raise ValueError(f"unsupported qk_quant: {cfg.qk_quant!r}")
-
-    if cfg.v_quant == "fp8_channel":
-        res.v, res.v_scale = fp8_per_channel_quant(v_work)
-    elif cfg.v_quant == "fp8_block":
-        res.v, res.v_scale = fp8_block_quant(v_work, block_s=cfg.v_fp8_block_size)
-    elif cfg.v_quant == "mxfp8":
-        res.v, res.v_scale = mxfp8_v_quant(v_work, block_s=cfg.v_mxfp8_block_size)
-    else:
-        raise ValueError(f"unsupported v_quant: {cfg.v_quant!r}")
-    return res
+    (q_codes, q_scale), (k_codes, k_scale) = (_QK_QUANTIZERS[cfg.qk_quant](t, cfg) for t in (qw, kw))
+    v_codes, v_scale = _V_QUANTIZERS[cfg.v_quant](vw, cfg)
+    return PreparedQKV(q=q_codes, k=k_codes, v=v_codes, q_scale=q_scale, k_scale=k_scale, v_scale=v_scale,
+                       qm=qm, k_mean=k_mean, correction=correction, kmeans=kmeans)
