@@ -96,21 +96,8 @@ def make_inputs(batch, heads, seq, dim, seed, device, dtype=torch.bfloat16):
 def pad_like_hook(q, k, v, cfg):
     """Pad S up to the lcm of the block sizes: Q rows zero, K/V replicate the last row
     (the policy of the reference's Wan hook, bench/wan_attention_hook.py:253-294)."""
-    blocks = [cfg.fp8_block_size, cfg.v_fp8_block_size, cfg.p_requant_block_m, cfg.p_requant_block_n]
-    if cfg.smoothing == "full":
-        blocks.append(cfg.q_smooth_block_size)
-    if cfg.v_smooth_mode == "per_block":
-        blocks.append(cfg.v_smooth_block_size)
-    lcm = 1
-    for b in blocks:
-        lcm = lcm * b // math.gcd(lcm, b)
-    s = q.shape[1]
-    pad = (lcm - s % lcm) % lcm
-    if pad == 0:
-        return q, k, v, 0
-    qp = torch.cat([q, q.new_zeros(q.shape[0], pad, q.shape[2], q.shape[3])], dim=1)
-    kp = torch.cat([k, k[:, -1:].expand(-1, pad, -1, -1)], dim=1)
-    vp = torch.cat([v, v[:, -1:].expand(-1, pad, -1, -1)], dim=1)
+    from low_bit_fake_quant.hook import pad_qkv
+    qp, kp, vp, pad = pad_qkv(q, k, v, cfg)
     return qp.contiguous(), kp.contiguous(), vp.contiguous(), pad
 
 

@@ -2,8 +2,9 @@
 
 The public names are those of the reference package (src/low_bit_fake_quant/__init__.py:3-60); every device step
 behind them runs in ``liblbfq.so`` (hand-written sm_100a CUDA behind a C ABI, see include/lbfq.h). There is no
-Triton, no CPU fallback and no other backend. ``fake_quant_attention_host`` is an extension (host-resident tensors,
-copies pipelined with compute) and is therefore kept out of ``__all__``.
+Triton, no CPU fallback and no other backend. ``fake_quant_attention_host`` (host-resident tensors,
+copies pipelined with compute) and ``fake_quant_attention_padded`` (the reference hook's pad-to-block-multiple policy)
+are extensions and are therefore kept out of ``__all__``.
 """
 from . import attention as _attention
 from . import hadamard as _hadamard
@@ -12,6 +13,7 @@ from . import pipeline as _pipeline
 from . import preprocess as _preprocess
 from . import quant_triton as _quant
 from .config import QuantConfig
+from .hook import fake_quant_attention_padded
 from .host import fake_quant_attention_host
 
 # name -> module that defines it; the export list below is generated from this table

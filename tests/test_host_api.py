@@ -109,3 +109,21 @@ def test_slab_ranges_partition_the_heads():
             assert max(sizes) - min(sizes) <= 1
     with pytest.raises(ValueError):
         slab_range(8, 2, 2)
+
+
+def test_hook_padding_policy():
+    """bench/wan_attention_hook.py:253-294 of the reference: pad to the lcm of the block sizes in play."""
+    from low_bit_fake_quant.config import QuantConfig
+    from low_bit_fake_quant.hook import pad_qkv, required_multiple
+    cfg = QuantConfig(fp8_block_size=64, smoothing="full", q_smooth_block_size=256, v_smooth_mode="per_block",
+                      v_smooth_block_size=96, q_kmeans_k=None)
+    assert required_multiple(cfg) == 768                        # lcm(64, 64, 64, 64, 256, 96)
+    assert required_multiple(QuantConfig(fp8_block_size=64, smoothing="k_only", q_kmeans_k=None)) == 64
+    q = torch.arange(2 * 100 * 1 * 4, dtype=torch.float32).view(2, 100, 1, 4)
+    qp, kp, vp, pad = pad_qkv(q, q + 1, q + 2, QuantConfig(fp8_block_size=64, smoothing="k_only", q_kmeans_k=None))
+    assert pad == 28 and qp.shape == (2, 128, 1, 4)
+    assert torch.equal(qp[:, :100], q) and qp[:, 100:].abs().sum() == 0
+    assert torch.equal(kp[:, 100:], (q + 1)[:, -1:].expand(-1, 28, -1, -1))
+    assert torch.equal(vp[:, 100:], (q + 2)[:, -1:].expand(-1, 28, -1, -1))
+    same = pad_qkv(q[:, :64], q[:, :64], q[:, :64], QuantConfig(fp8_block_size=64, smoothing="k_only", q_kmeans_k=None))
+    assert same[3] == 0 and same[0] is not None and same[0].shape[1] == 64
