@@ -61,7 +61,7 @@ struct Smem {
   static constexpr int offAlpha = offCorr + kStages * 2 * kChunk * 4;
   static constexpr int offVs = offAlpha + kStages * kSub * D * 4;
   static constexpr int offBar = offVs + kStages * kSub * D * 4;
-  static constexpr int kNumBar = 2 + 4 * kStages + 10 + 2 * kStages;
+  static constexpr int kNumBar = 2 + 4 * kStages + 12 + 2 * kStages;
   static constexpr int offMisc = offBar + kNumBar * 8;
   static constexpr int offL = offMisc + 64;                   // partial row sums [tile][half][row]
   static constexpr int total = offL + 2 * 2 * kTileM * 4;
@@ -95,11 +95,15 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
   auto BAR_VFREE = [&](int s) { return bar0 + 8u * (2 + 3 * kStages + s); };
   auto BAR_SFULL = [&](int t) { return bar0 + 8u * (2 + 4 * kStages + t); };
   auto BAR_SFREE = [&](int t) { return bar0 + 8u * (2 + 4 * kStages + 2 + t); };
-  auto BAR_PRDY = [&](int t) { return bar0 + 8u * (2 + 4 * kStages + 4 + t); };
-  auto BAR_PVFULL = [&](int t) { return bar0 + 8u * (2 + 4 * kStages + 6 + t); };
-  auto BAR_OFREE = [&](int t) { return bar0 + 8u * (2 + 4 * kStages + 8 + t); };
-  auto BAR_SIDEFULL = [&](int s) { return bar0 + 8u * (2 + 4 * kStages + 10 + s); };
-  auto BAR_SIDEFREE = [&](int s) { return bar0 + 8u * (2 + 4 * kStages + 10 + kStages + s); };
+  // P ready, one barrier per block parity: a warp can finish block j + 1 (whose S only waits for every thread to have
+  // copied S of block j out) before a slower warp has delivered P of block j; with a single barrier that second
+  // arrival would be counted into block j's phase. Two blocks ahead is impossible (S of block j + 2 waits for every
+  // thread's copy of block j + 1).
+  auto BAR_PRDY = [&](int t, int par) { return bar0 + 8u * (2 + 4 * kStages + 4 + 2 * t + par); };
+  auto BAR_PVFULL = [&](int t) { return bar0 + 8u * (2 + 4 * kStages + 8 + t); };
+  auto BAR_OFREE = [&](int t) { return bar0 + 8u * (2 + 4 * kStages + 10 + t); };
+  auto BAR_SIDEFULL = [&](int s) { return bar0 + 8u * (2 + 4 * kStages + 12 + s); };
+  auto BAR_SIDEFREE = [&](int s) { return bar0 + 8u * (2 + 4 * kStages + 12 + kStages + s); };
   volatile int* misc = (volatile int*)(smem + SM::offMisc);   // [0] tmem base, [1] abort, [2..5] elide flags, [6] early exit
   volatile int* abort_flag = misc + 1;
 
@@ -121,7 +125,8 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
       mbar_init(BAR_QFULL(t), 1);
       mbar_init(BAR_SFULL(t), 1);
       mbar_init(BAR_SFREE(t), kTileM);
-      mbar_init(BAR_PRDY(t), kTileM);
+      mbar_init(BAR_PRDY(t, 0), kTileM);
+      mbar_init(BAR_PRDY(t, 1), kTileM);
       mbar_init(BAR_PVFULL(t), 1);
       mbar_init(BAR_OFREE(t), kTileM);
     }
@@ -526,7 +531,7 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         c_blk *= p.v_scale[((size_t)b * (p.N / p.v_block) + n0 / p.v_block) * p.H + h];
       if (BLASST && row_in_tile == 0) misc[2 + 2 * t + (it & 1)] = elide ? 1 : 0;   // per P buffer
       tc_fence_before();
-      mbar_arrive(BAR_PRDY(t));
+      mbar_arrive(BAR_PRDY(t, it & 1));
       // ---- fold the previous block's P.V (issued while this block's softmax ran), then hand the
       // scratch accumulator back so that this block's P.V may be issued
       if (it > 0) {
@@ -711,7 +716,7 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
           if (!ok) break;
         }
         // P.V of this block once its P is in TMEM and the previous P.V has been folded
-        ok = mbar_wait(BAR_PRDY(t), it & 1, abort_flag, p.status, 35);
+        ok = mbar_wait(BAR_PRDY(t, it & 1), (it >> 1) & 1, abort_flag, p.status, 35);
         if (ok && it > 0) ok = mbar_wait(BAR_OFREE(t), (it - 1) & 1, abort_flag, p.status, 36);
         if (ok) ok = issue_pv(it);
       }
@@ -872,8 +877,9 @@ static size_t alpha_ws_bytes(const lbfq_attn_args* a) {
 // mx / dynamic P, or any P with the V-smoothing term, on FP8-block Q/K may take the BF16-P kernel, which wants a BF16
 // copy of V^T (and the alpha' pieces) in the workspace
 static bool may_want_v_bf16(const lbfq_attn_args* a) {
-  return (a->p_kind != LBFQ_P_ELEMENTWISE || a->v_alpha) && a->v_kind != LBFQ_V_BLOCK && !a->use_blasst &&
-         a->qk_kind == LBFQ_QK_FP8_BLOCK;
+  if (a->use_blasst && (a->v_alpha || a->qm_corr || !lbfq::attn::fast_blasst_fill(a->fill_kind, a->uta_bins, a->block_n)))
+    return false;
+  return (a->p_kind != LBFQ_P_ELEMENTWISE || a->v_alpha) && a->v_kind != LBFQ_V_BLOCK && a->qk_kind == LBFQ_QK_FP8_BLOCK;
 }
 static size_t v_bf16_ws_bytes(const lbfq_attn_args* a) {
   return may_want_v_bf16(a) ? align256((size_t)a->B * a->H * a->D * a->n_pad * 2) : 0;
@@ -991,6 +997,7 @@ extern "C" int lbfq_attention_fwd(const lbfq_attn_args* a, void* workspace, void
                  ((a->v_alpha ? 1 : 0) + (a->v_kind == LBFQ_V_MX ? 1 : 0)) * (kChunk / a->block_n) * a->D * 4;
   p.rowmax_est = a->rowmax_est; p.rowmax_init = a->rowmax_init;
   p.rm_mode = (a->rowmax_est && !a->use_blasst) ? (a->p_kind == LBFQ_P_DYNAMIC ? 2 : 1) : 0;
+  p.blasst = a->use_blasst ? 1 : 0; p.block_n = a->block_n;
   p.log_lambda = a->use_blasst ? logf(a->blasst_lambda) : 0.f;
   p.lambda = a->use_blasst ? a->blasst_lambda : 0.f;
   p.fill_kind = a->use_blasst ? a->fill_kind : 0; p.fill_alpha = a->fill_alpha; p.uta_bins = a->uta_bins > 0 ? a->uta_bins : 1;

@@ -3,7 +3,8 @@
 // Same operator as attention.cu (`_fake_quant_attn_fwd_kernel`, src/low_bit_fake_quant/attention_triton.py:48-671),
 // specialised for the configurations in which every key block's P.V enters the output with weight one:
 // element-wise (static offset) P quantisation, V quantised per channel, no V-smoothing term, no score bias,
-// no BLASST, FP8 block scales on Q / K, row max tracked online or frozen to an estimate. There
+// FP8 block scales on Q / K, row max tracked online or frozen to an estimate (template flags add the BF16-P
+// modes, the score bias, the V-smoothing term and BLASST row skipping with its constant and per-bin fills). There
 //
 //   O <- O * alpha + Pc . Vc                                      (attention_triton.py:362-385)
 //
@@ -53,7 +54,8 @@ static_assert(kFastRegsSoftmax % 8 == 0 && kFastRegsService % 8 == 0, "setmaxnre
 // PK = 1: P re-scaled and rounded to BF16 as the reference does for its mx / dynamic P modes, P.V a BF16 MMA
 //         over a BF16 copy of V^T (3 key stages: a V stage is twice as large).
 // QB = 1: Q and K are BF16 tensors (the reference's de-quantised operands) and Q.K^T a BF16 MMA; two key stages.
-template <int D, int PK, int QB>
+// BL = 1: BLASST; the row-pair exchange carries three values per block (maximum, sum of scores, largest fill).
+template <int D, int PK, int QB, int BL = 0>
 struct FastSmem {
   static constexpr int kStages = QB ? 2 : (PK ? 3 : 4);
   static constexpr int kQ = kTileM * D * (QB ? 2 : 1);         // bytes per Q tile
@@ -63,26 +65,30 @@ struct FastSmem {
   static constexpr int offK = offQ + 2 * kQ;
   static constexpr int offV = offK + kStages * kK;
   static constexpr int offBar = offV + kStages * kV;
-  static constexpr int kNumBar = 2 + 4 * kStages + 4 + 2 + 2 + 2 + 2 * kStages;
+  static constexpr int kNumBar = 2 + 4 * kStages + 4 + 4 + 2 + 2 + 2 * kStages;
   static constexpr int offMisc = offBar + kNumBar * 8;
   static constexpr int offL = offMisc + 64;                    // row sums of the two column halves [tile][half][row]
   // score-bias rows (`corr`) of each tile's Q group, staged per 128-key stage by the producer
   // block maxima exchanged between the two threads of a row: [block parity][tile][half][row]
   static constexpr int offX = offL + 2 * 2 * kTileM * 4;
-  static constexpr int offCorr = offX + 2 * 2 * 2 * kTileM * 4;
+  static constexpr int kXch = 2 * 2 * 2 * kTileM;             // floats per exchanged quantity
+  static constexpr int offCorr = offX + (BL ? 3 : 1) * kXch * 4;
   // V-smoothing tiles for the K-extension of P.V: per stage up to two (D x 16) BF16 tiles (32-byte rows)
   static constexpr int kAext = D * 32;
   static constexpr int offAext = (offCorr + kStages * 2 * kChunk * 4 + 1023) / 1024 * 1024;   // TMA destination, swizzled
   static constexpr int total = offAext + (PK ? kStages * 2 * kAext : 0);
 };
 
-template <int D, int BN, bool CORR, int PK, bool VALPHA, int QB>
+template <int D, int BN, bool CORR, int PK, bool VALPHA, int QB, bool BL = false>
 __global__ void __launch_bounds__(kFastThreads, 1)
 attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                  const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_a, const Params p) {
   static_assert(!VALPHA || PK == 1, "the V-smoothing term rides on the BF16 P.V");
   static_assert(!QB || PK == 1, "BF16 Q / K come with the BF16 P.V");
-  using SM = FastSmem<D, PK, QB>;
+  static_assert(!BL || (!CORR && !VALPHA && QB == 0), "BLASST is built without score bias, V-smoothing term, BF16 Q / K");
+  // scores kept in the reference's own units (natural-log domain) instead of the log2 domain
+  constexpr bool NAT = CORR || BL;
+  using SM = FastSmem<D, PK, QB, BL ? 1 : 0>;
   constexpr int kFastStages = SM::kStages;
   constexpr int NSUB = kChunk / BN;                // key blocks per stage
   constexpr int TCOLS = 256;                       // TMEM columns per tile
@@ -101,11 +107,14 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   auto BAR_KFREE = [&](int s) { return bar0 + 8u * (2 + 2 * kFastStages + s); };
   auto BAR_VFREE = [&](int s) { return bar0 + 8u * (2 + 3 * kFastStages + s); };
   auto BAR_SFULL = [&](int t, int buf) { return bar0 + 8u * (2 + 4 * kFastStages + 2 * t + buf); };
-  auto BAR_PRDY = [&](int t) { return bar0 + 8u * (2 + 4 * kFastStages + 4 + t); };
-  auto BAR_PENULT = [&](int t) { return bar0 + 8u * (2 + 4 * kFastStages + 6 + t); };   // P.V of block nblk - 2 done
-  auto BAR_ODONE = [&](int t) { return bar0 + 8u * (2 + 4 * kFastStages + 8 + t); };    // P.V of the last block done
-  auto BAR_SIDEFULL = [&](int s) { return bar0 + 8u * (2 + 4 * kFastStages + 10 + s); };
-  auto BAR_SIDEFREE = [&](int s) { return bar0 + 8u * (2 + 4 * kFastStages + 10 + kFastStages + s); };
+  // P ready, one barrier per S buffer: a warp may finish block j + 1 (its S is ready early) before a slower warp has
+  // finished block j, and with a single barrier its second arrival would be counted into block j's phase. It cannot
+  // be two blocks ahead: S of block j + 2 is issued behind P.V of block j, which waits for every arrival of block j.
+  auto BAR_PRDY = [&](int t, int buf) { return bar0 + 8u * (2 + 4 * kFastStages + 4 + 2 * t + buf); };
+  auto BAR_PENULT = [&](int t) { return bar0 + 8u * (2 + 4 * kFastStages + 8 + t); };   // P.V of block nblk - 2 done
+  auto BAR_ODONE = [&](int t) { return bar0 + 8u * (2 + 4 * kFastStages + 10 + t); };   // P.V of the last block done
+  auto BAR_SIDEFULL = [&](int s) { return bar0 + 8u * (2 + 4 * kFastStages + 12 + s); };
+  auto BAR_SIDEFREE = [&](int s) { return bar0 + 8u * (2 + 4 * kFastStages + 12 + kFastStages + s); };
   volatile int* misc = (volatile int*)(smem + SM::offMisc);   // [0] tmem base, [1] abort, [6] early exit
   volatile int* abort_flag = misc + 1;
 
@@ -129,7 +138,8 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       mbar_init(BAR_QFULL(t), 1);
       mbar_init(BAR_SFULL(t, 0), 1);
       mbar_init(BAR_SFULL(t, 1), 1);
-      mbar_init(BAR_PRDY(t), 2 * kTileM);
+      mbar_init(BAR_PRDY(t, 0), 2 * kTileM);
+      mbar_init(BAR_PRDY(t, 1), 2 * kTileM);
       mbar_init(BAR_PENULT(t), 1);
       mbar_init(BAR_ODONE(t), 1);
     }
@@ -175,7 +185,7 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     bool l_pos = false;                          // the row sum is positive (kept as a flag: each thread holds half of it)
     // running max: in the log2 domain (the reference's m_i times log2e) without a score bias; with one the
     // scores are formed as the reference forms them, dot * f + corr, and the max stays in their own units
-    constexpr float kDom = CORR ? 1.0f : kLog2e;
+    constexpr float kDom = NAT ? 1.0f : kLog2e;
     float m2 = -INFINITY;
     if (p.rowmax_est) m2 = p.rowmax_est[(size_t)bh * p.M + rowc] * kDom;
     else if (p.rowmax_init) m2 = p.rowmax_init[(size_t)bh * p.M + rowc] * kDom;
@@ -186,7 +196,7 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     float sk = QB ? 1.0f : ksc[0];
     const int blocks_per_scale = p.qk_block / BN;               // fp8_block_size is a multiple of block_n
     int scale_sub = 0;
-    const uint32_t bar_sfull = BAR_SFULL(t, 0), bar_prdy = BAR_PRDY(t);
+    const uint32_t bar_sfull = BAR_SFULL(t, 0), bar_prdy = BAR_PRDY(t, 0);
     const bool p_el = p.p_kind == LBFQ_P_ELEMENTWISE, p_mx = p.p_kind == LBFQ_P_MX;
     const float p_off = p_el ? p.p_off : 0.f, sm_scale = p.sm_scale;  // the offset belongs to element-wise P only
     const int n_keys = p.N, k_stride = p.H;
@@ -211,6 +221,8 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const uint32_t bar_penult = BAR_PENULT(t);
     const int last = nblk - 1;
     const int tail_valid = n_keys - last * BN;      // keys in the last block (BN unless the sequence is ragged)
+    const bool fill_sum = BL && p.fill_kind == LBFQ_FILL_MEAN;   // the fill needs the block's mean score
+    int n_skip = 0;                          // BLASST: blocks this row skipped
     bool s_seen = false;                     // this block's S-ready barrier was already observed (warp-uniform)
     uint32_t par = 0;                        // parity of the S-ready phases of the current pair of blocks
 
@@ -224,7 +236,7 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       tc_wait_ld();
       // (sq * sk) * sm_scale in the reference's order; without a score bias straight into the log2 domain
       const float f = (sq * sk) * sm_scale;
-      const float c = CORR ? 1.0f : f * kLog2e;
+      const float c = NAT ? 1.0f : f * kLog2e;
       const bool more = it != last;
       if (++scale_sub == blocks_per_scale) {   // next block's scale, off the critical path
         scale_sub = 0;
@@ -248,7 +260,17 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           mine[4 * i + 2] = __float_as_uint(m23.x); mine[4 * i + 3] = __float_as_uint(m23.y);
         }
       }
-      if (!more && tail_valid < BN) {          // ragged tail: only the last block of a sequence
+      if constexpr (BL) {
+        // scores = dot * f: the skip test and the fills are stated on them (attention_triton.py:154, 165-175)
+        const float2 f2 = make_float2(f, f);
+#pragma unroll
+        for (int i = 0; i < HB; i += 2) {
+          const float2 v = __fmul2_rn(make_float2(__uint_as_float(mine[i]), __uint_as_float(mine[i + 1])), f2);
+          mine[i] = __float_as_uint(v.x); mine[i + 1] = __float_as_uint(v.y);
+        }
+      }
+      const bool ragged = !more && tail_valid < BN;
+      if (ragged) {                            // ragged tail: only the last block of a sequence
 #pragma unroll
         for (int i = 0; i < HB; ++i)
           if (half * HB + i >= tail_valid) mine[i] = 0xff800000u;
@@ -263,10 +285,34 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       // of the next block, when its reader is done with it)
       const float own_max = fmaxf(bm0, bm1);
       *x_mine[BUF] = own_max;
+      [[maybe_unused]] float row_sum = 0.f;                     // BLASST mean fill: sum of the block's valid scores
+      if constexpr (BL) {
+        if (fill_sum) {
+          float2 sa = make_float2(0.f, 0.f), sb = make_float2(0.f, 0.f);
+#pragma unroll
+          for (int i = 0; i < HB; i += 4) {
+            float2 a = make_float2(__uint_as_float(mine[i]), __uint_as_float(mine[i + 1]));
+            float2 b2 = make_float2(__uint_as_float(mine[i + 2]), __uint_as_float(mine[i + 3]));
+            if (ragged) {
+              if (half * HB + i >= tail_valid) a.x = 0.f;
+              if (half * HB + i + 1 >= tail_valid) a.y = 0.f;
+              if (half * HB + i + 2 >= tail_valid) b2.x = 0.f;
+              if (half * HB + i + 3 >= tail_valid) b2.y = 0.f;
+            }
+            sa = __fadd2_rn(sa, a);
+            sb = __fadd2_rn(sb, b2);
+          }
+          row_sum = (sa.x + sa.y) + (sb.x + sb.y);
+          x_mine[BUF][SM::kXch] = row_sum;
+        }
+      }
       __syncwarp();                            // a named barrier counts warps: arrive once, converged
       asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
       bm0 = own_max;
       bm1 = *x_oth[BUF];
+      if constexpr (BL) {
+        if (fill_sum) row_sum += x_oth[BUF][SM::kXch];           // commutative: both threads of the row get the same bits
+      }
       const float bmax_raw = fmaxf(bm0, bm1);
       const float bmax = bmax_raw * c;
 
@@ -288,18 +334,25 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       } else {
         m_new = frozen ? m2 : fmaxf(m2, bmax);
       }
-      const float alpha = !moved ? 1.f : (fresh ? 0.f : ex2(CORR ? (m2 - m_new) * kLog2e : m2 - m_new));
+      bool skip = false;                       // BLASST: this row's block is below the threshold (attention_triton.py:165-175)
+      if constexpr (BL) {
+        skip = (bmax - m_new) < p.log_lambda;
+        if (skip) m_new = m2;
+        moved = !skip;
+        n_skip += skip ? 1 : 0;
+      }
+      const float alpha = !moved ? 1.f : (fresh ? 0.f : ex2(NAT ? (m2 - m_new) * kLog2e : m2 - m_new));
       // ---- P = exp2(dot * c - m + off), l += sum(P) (attention_triton.py:219-326) ----
       // masked columns hold -inf, so their exp2 is exactly 0 without a select
       // two columns per instruction: fma.rn.f32x2 / add.rn.f32x2 round each half exactly like the scalar forms.
       // Without a score bias: exp2(dot * c + (off - m)). With one: exp2((score - m) * log2e + off), the
       // reference's own sequence.
-      const float bias = CORR ? -m_new : p_off - m_new;
-      const float2 c2 = make_float2(CORR ? kLog2e : c, CORR ? kLog2e : c);
+      const float bias = NAT ? -m_new : p_off - m_new;
+      const float2 c2 = make_float2(NAT ? kLog2e : c, NAT ? kLog2e : c);
       const float2 bias2 = make_float2(bias, bias), off2 = make_float2(p_off, p_off);
       auto arg = [&](uint32_t x0, uint32_t x1) -> float2 {
         const float2 v = make_float2(__uint_as_float(x0), __uint_as_float(x1));
-        if constexpr (CORR) return __ffma2_rn(__fadd2_rn(v, bias2), c2, off2);
+        if constexpr (NAT) return __ffma2_rn(__fadd2_rn(v, bias2), c2, off2);
         else return __ffma2_rn(v, c2, bias2);
       };
       float2 psa = make_float2(0.f, 0.f), psb = make_float2(0.f, 0.f);
@@ -307,11 +360,82 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       // exp2 is monotonic: the largest P of the block is the P of the largest score, produced by the same
       // instruction sequence as the elements, so it is bit-identical to max_i(P_i) -- and both threads of the
       // row know it without talking to each other
-      float pmax = 1.f;
-      float s_p = 1.f, inv_p = 1.f;
-      if constexpr (PK != 0) {
+      [[maybe_unused]] float pmax = 1.f;
+      [[maybe_unused]] float s_p = 1.f, inv_p = 1.f;
+      if constexpr (BL) {
+        // A skipped row contributes a softmax-free fill instead of its exponentials (attention_triton.py:231-324):
+        // the fill values replace the scores in `mine`, their maximum stands in for the largest P.
+        float fill_max = 0.f;
+        if (skip) {
+          const int nvalid = more ? BN : tail_valid;
+          const float safe_n = (float)nvalid;                       // a block holds at least one key
+          if (p.fill_kind == LBFQ_FILL_UTA) {
+            // one value per bin of BN / bins keys; a bin never straddles the two halves of the block
+            auto bins = [&](auto bs_c) {
+              constexpr int BS = decltype(bs_c)::value;
+              if constexpr (BS <= HB) {
+#pragma unroll
+                for (int b0 = 0; b0 < HB; b0 += BS) {
+                  float bsum = 0.f, bmx = -INFINITY, bcnt = 0.f;
+#pragma unroll
+                  for (int i = b0; i < b0 + BS; ++i) {
+                    const bool ok = half * HB + i < nvalid;
+                    const float x = __uint_as_float(mine[i]);
+                    bsum += ok ? x : 0.f;
+                    bmx = fmaxf(bmx, x);                            // masked scores are -inf already
+                    bcnt += ok ? 1.f : 0.f;
+                  }
+                  const float safe_c = fmaxf(bcnt, 1.f);
+                  const float bound = safe_c * ex2(fmaf(bmx - m_new, kLog2e, p_off));
+                  const float mass = p.fill_alpha * safe_c * ex2(fmaf(bsum / safe_c - m_new, kLog2e, p_off));
+                  const float val = fminf(mass, bound) / safe_c;
+                  fill_max = fmaxf(fill_max, val);
+#pragma unroll
+                  for (int i = b0; i < b0 + BS; ++i) mine[i] = (half * HB + i < nvalid) ? __float_as_uint(val) : 0u;
+                }
+              }
+            };
+            switch (BN / p.uta_bins) {
+              case 2: bins(std::integral_constant<int, 2>{}); break;
+              case 4: bins(std::integral_constant<int, 4>{}); break;
+              case 8: bins(std::integral_constant<int, 8>{}); break;
+              case 16: bins(std::integral_constant<int, 16>{}); break;
+              default: bins(std::integral_constant<int, 32>{}); break;
+            }
+          } else {
+            float fill_p = 0.f;
+            if (p.fill_kind != LBFQ_FILL_ZERO) {
+              const float max_bound = safe_n * ex2(fmaf(bmax - m_new, kLog2e, p_off));
+              if (p.fill_kind == LBFQ_FILL_MAX) {
+                fill_p = max_bound * p.fill_alpha / safe_n;
+              } else if (p.fill_kind == LBFQ_FILL_MEAN) {
+                fill_p = fminf(p.fill_alpha * safe_n * ex2(fmaf(row_sum / safe_n - m_new, kLog2e, p_off)), max_bound) / safe_n;
+              } else {                                              // LBFQ_FILL_THR
+                const float off_scale = p_el ? exp2f(p_off) : 1.f;
+                fill_p = (p.fill_alpha * safe_n * p.lambda * off_scale) / safe_n;
+              }
+            }
+            fill_max = fill_p;
+#pragma unroll
+            for (int i = 0; i < HB; ++i) mine[i] = (half * HB + i < nvalid) ? __float_as_uint(fill_p) : 0u;
+          }
+        }
+        if constexpr (PK != 0) {
+          // the per-bin fills differ between the two halves of a row: their maxima meet like the block maxima did
+          // (in every block, whatever the rows decide: the number of barriers a warp passes never depends on data)
+          if (p.fill_kind == LBFQ_FILL_UTA) {
+            x_mine[BUF][2 * SM::kXch] = fill_max;
+            __syncwarp();
+            asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
+            fill_max = fmaxf(fill_max, x_oth[BUF][2 * SM::kXch]);
+          }
+          pmax = skip ? fill_max : ex2(fmaf(bmax - m_new, kLog2e, p_off));
+        }
+      } else if constexpr (PK != 0) {
         if constexpr (CORR) pmax = ex2(fmaf(bmax - m_new, kLog2e, p_off));
         else pmax = ex2(fmaf(bmax_raw, c, bias));
+      }
+      if constexpr (PK != 0) {
         // P scale of the block (attention_triton.py:338-360): a power of two (mx) or amax / 448 (dynamic)
         if (p_el) {
           // element-wise P keeps scale 1 (it takes this path when the V-smoothing term needs the BF16 P.V)
@@ -325,12 +449,8 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         }
       }
       const float2 inv2 = make_float2(inv_p, inv_p);
-#pragma unroll
-      for (int i = 0; i < HB; i += 4) {
-        const float2 za = arg(mine[i], mine[i + 1]);
-        const float2 zb = arg(mine[i + 2], mine[i + 3]);
-        const float2 pa = make_float2(ex2(za.x), ex2(za.y));
-        const float2 pb = make_float2(ex2(zb.x), ex2(zb.y));
+      // row sum over the unquantised P, then the P operand of the block's P.V
+      auto emit = [&](const int i, const float2 pa, const float2 pb) {
         psa = __fadd2_rn(psa, pa);
         psb = __fadd2_rn(psb, pb);
         if constexpr (PK == 0) {
@@ -341,6 +461,19 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           const float2 qa = __fmul2_rn(pa, inv2), qb = __fmul2_rn(pb, inv2);
           pk[i / 2] = e4m3_round_scale_bf16x2(qa.x, qa.y, s_p);
           pk[i / 2 + 1] = e4m3_round_scale_bf16x2(qb.x, qb.y, s_p);
+        }
+      };
+      if (BL && skip) {
+#pragma unroll
+        for (int i = 0; i < HB; i += 4)
+          emit(i, make_float2(__uint_as_float(mine[i]), __uint_as_float(mine[i + 1])),
+               make_float2(__uint_as_float(mine[i + 2]), __uint_as_float(mine[i + 3])));
+      } else {
+#pragma unroll
+        for (int i = 0; i < HB; i += 4) {
+          const float2 za = arg(mine[i], mine[i + 1]);
+          const float2 zb = arg(mine[i + 2], mine[i + 3]);
+          emit(i, make_float2(ex2(za.x), ex2(za.y)), make_float2(ex2(zb.x), ex2(zb.y)));
         }
       }
       l_i = l_i * alpha + ((psa.x + psa.y) + (psb.x + psb.y));
@@ -396,7 +529,7 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       else tmem_st4(tP[BUF], pk);
       tc_wait_st();
       tc_fence_before();
-      mbar_arrive(bar_prdy);
+      mbar_arrive(bar_prdy + 8u * BUF);
       m2 = m_new;
       if constexpr (CORR) {
         // the stage's bias rows are dead once its last key block has read them
@@ -480,6 +613,14 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             o[i] = make_uint4(w[0], w[1], w[2], w[3]);
           }
         }
+      }
+    }
+    if constexpr (BL) {
+      // skipped and total row-decisions per block_m rows (attention_triton.py:404-407)
+      if (half == 0 && row_ok && p.stats != nullptr && *abort_flag == 0) {
+        float* st2 = p.stats + ((size_t)(row / p.block_m) * (p.B * p.H) + bh) * 2;
+        atomicAdd(st2 + 0, (float)n_skip);
+        atomicAdd(st2 + 1, (float)nblk);
       }
     }
   } else {
@@ -620,7 +761,7 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       for (int it = 0; it < nblk && ok; ++it) {
         // P.V of this block once its P is in TMEM (and the rows that raised their max are rescaled), then
         // Q.K^T of block it + 2 into the S buffer that P has just been read from
-        ok = mbar_wait(BAR_PRDY(t), it & 1, abort_flag, p.status, 35);
+        ok = mbar_wait(BAR_PRDY(t, it & 1), (it >> 1) & 1, abort_flag, p.status, 35);
         if (ok) ok = issue_pv(it);
         if (ok && it + 2 < nblk) ok = issue_qk(it + 2);
       }
@@ -642,12 +783,12 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   }
 }
 
-template <int D, int BN, bool CORR, int PK, bool VALPHA, int QB>
+template <int D, int BN, bool CORR, int PK, bool VALPHA, int QB, bool BL = false>
 int launch_fast_t(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& ma, const Params& p,
                   cudaStream_t st) {
-  using SM = FastSmem<D, PK, QB>;
+  using SM = FastSmem<D, PK, QB, BL ? 1 : 0>;
   const int smem_bytes = SM::total + 1024;
-  auto kern = attn_fast_kernel<D, BN, CORR, PK, VALPHA, QB>;
+  auto kern = attn_fast_kernel<D, BN, CORR, PK, VALPHA, QB, BL>;
   LBFQ_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
   dim3 grid((p.M + kCtaM - 1) / kCtaM, p.B * p.H, 1);
   kern<<<grid, kFastThreads, smem_bytes, st>>>(mq, mk, mv, ma, p);
@@ -656,13 +797,30 @@ int launch_fast_t(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMa
 
 }  // namespace
 
+// BLASST fills the TMEM-resident kernel produces: the constant ones that need at most the block's mean score, and
+// the per-bin fill when a bin lies within one half of the block's columns
+bool fast_blasst_fill(int fill_kind, int uta_bins, int block_n) {
+  if (fill_kind == LBFQ_FILL_ZERO || fill_kind == LBFQ_FILL_MAX || fill_kind == LBFQ_FILL_MEAN || fill_kind == LBFQ_FILL_THR)
+    return true;
+  if (fill_kind != LBFQ_FILL_UTA || uta_bins < 2 || block_n % uta_bins != 0) return false;
+  const int bs = block_n / uta_bins;
+  return bs >= 2 && bs <= block_n / 2;
+}
+
 // 0: the general kernel; 1: TMEM-resident with e4m3 P (element-wise P, no V-smoothing term); 2: TMEM-resident with
 // BF16 P (mx / dynamic P, or any P with the V-smoothing term; needs a BF16 copy of V^T, and the alpha' pieces)
 int fast_variant(const Params& p, bool blasst, bool qk_mx) {
-  const bool common = !blasst && !qk_mx && (p.qk_bf16 != 0 || (p.q_scale != nullptr && p.k_scale != nullptr)) &&
+  const bool common = !qk_mx && (p.qk_bf16 != 0 || (p.q_scale != nullptr && p.k_scale != nullptr)) &&
                       (p.corr == nullptr || p.corr_staged != 0) && p.sm_scale > 0.f;
   if (!common) return 0;
   const bool v_ok = p.v_kind == LBFQ_V_CHANNEL || p.v_kind == LBFQ_V_MX;
+  if (blasst) {
+    // row skipping is built for the plain stacks: FP8 block scales, no score bias, no V-smoothing term
+    if (p.qk_bf16 || p.corr != nullptr || p.v_alpha != nullptr || p.rm_mode != 0) return 0;
+    if (!fast_blasst_fill(p.fill_kind, p.uta_bins, p.block_n)) return 0;
+    if (p.p_kind == LBFQ_P_ELEMENTWISE) return p.v_kind == LBFQ_V_CHANNEL ? 1 : 0;
+    return v_ok ? 2 : 0;
+  }
   const bool alpha_ok = p.v_alpha == nullptr || p.v_smooth_block >= 64;
   if (p.qk_bf16) return (v_ok && alpha_ok && (p.p_kind == LBFQ_P_DYNAMIC || p.rm_mode != 2)) ? 2 : 0;
   if (p.v_alpha != nullptr) return (v_ok && alpha_ok && (p.p_kind != LBFQ_P_ELEMENTWISE || p.rm_mode != 2)) ? 2 : 0;
@@ -673,6 +831,16 @@ int fast_variant(const Params& p, bool blasst, bool qk_mx) {
 int launch_fast(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& ma, const Params& p,
                 int block_n, int variant, cudaStream_t st) {
   const bool va = p.v_alpha != nullptr;
+  if (p.blasst) {
+#define LBFQ_FAST_BL(DD, NN)                                                                                      \
+  if (variant == 2) return launch_fast_t<DD, NN, false, 1, false, 0, true>(mq, mk, mv, ma, p, st);                \
+  return launch_fast_t<DD, NN, false, 0, false, 0, true>(mq, mk, mv, ma, p, st)
+    if (p.D == 128 && block_n == 64) { LBFQ_FAST_BL(128, 64); }
+    if (p.D == 128) { LBFQ_FAST_BL(128, 32); }
+    if (block_n == 64) { LBFQ_FAST_BL(64, 64); }
+    LBFQ_FAST_BL(64, 32);
+#undef LBFQ_FAST_BL
+  }
 #define LBFQ_FAST3(DD, NN, CC, VV)                                                                                \
   if (p.qk_bf16) return launch_fast_t<DD, NN, CC, 1, VV, 1>(mq, mk, mv, ma, p, st);                               \
   return launch_fast_t<DD, NN, CC, 1, VV, 0>(mq, mk, mv, ma, p, st)

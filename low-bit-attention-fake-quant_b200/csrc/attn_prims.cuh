@@ -325,6 +325,8 @@ struct Params {
   const float* rowmax_est;
   const float* rowmax_init;
   int rm_mode;                 // 0 online, 1 frozen estimate, 2 estimate with thresholds
+  int blasst;                  // 1: BLASST row skipping (online row max)
+  int block_n;                 // keys per softmax block
   float log_lambda, lambda;
   int fill_kind;
   float fill_alpha;
@@ -352,6 +354,7 @@ struct Params {
 
 // attention_fast.cu: online-softmax variant whose output accumulator lives in tensor memory
 int fast_variant(const Params& p, bool blasst, bool qk_mx);
+bool fast_blasst_fill(int fill_kind, int uta_bins, int block_n);
 int launch_fast(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& ma, const Params& p,
                 int block_n, int variant, cudaStream_t st);
 

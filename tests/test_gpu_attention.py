@@ -295,6 +295,60 @@ def test_tmem_resident_variant_matches_oracle_and_general_kernel(S, D, bn, extra
         assert OA.parity_ok(OA.parity_report(fast, gen, q, k, v))
 
 
+BLASST_FAST = [
+    (2048, 128, 64, 1e-2, dict()),                                                   # zero fill, e4m3 P
+    (1984, 128, 64, 1e-1, dict(blasst_fill="mean_a1.5", p_quant="dynamic")),
+    (1024, 64, 32, 1e-2, dict(blasst_fill="uta16_a1.5", p_quant="dynamic")),         # bins of 2 keys
+    (1536, 128, 64, 1e-2, dict(blasst_fill="uta", blasst_uta_bins=8, v_quant="mxfp8", p_quant="auto")),   # mx P
+    (1024, 64, 64, 1e-2, dict(blasst_fill="max_a0.25")),
+    (960, 128, 32, 1e-2, dict(blasst_fill="thr_a0.25", p_quant="dynamic")),
+    (1024, 128, 64, 1e-2, dict(blasst_fill="uta", blasst_uta_bins=2)),                # one bin per half of the block
+]
+
+
+@pytest.mark.parametrize("S,D,bn,lam,extra", BLASST_FAST)
+def test_tmem_resident_variant_blasst(S, D, bn, lam, extra, monkeypatch):
+    """BLASST row skipping on the TMEM-resident kernel: same skip decisions (the stats tensor) as the general
+    kernel and the oracle, output within the parity bound of both."""
+    from low_bit_fake_quant.attention import _fake_quant_attention_p_requant
+    from oracle.api import attention_p_requant
+    kw = {**COMMON, **dict(smoothing="off", q_kmeans_k=None, p_requant_block_m=bn, p_requant_block_n=bn,
+                           blasst_lambda=lam, blasst_fill_alpha=0.5), **extra}
+    cfg = QuantConfig(**kw)
+    q, k, v = _qkv(1, S, 2, D, seed=S + D + bn, outliers=True)
+    sm = 1 / math.sqrt(D)
+
+    def run():
+        out, st = _fake_quant_attention_p_requant(q.to(DEV), k.to(DEV), v.to(DEV), None, None, None, cfg, sm,
+                                                  torch.bfloat16, return_stats=True, out_fp32_exact=True)
+        raise_if_device_error(torch.device(DEV))
+        return out.float().cpu(), st.cpu()
+
+    monkeypatch.delenv("LBFQ_ATTN_GENERIC", raising=False)
+    fast, st_fast = run()
+    assert _variant() == 1
+    monkeypatch.setenv("LBFQ_ATTN_GENERIC", "1")
+    gen, st_gen = run()
+    assert _variant() == 0
+    assert torch.equal(st_fast, st_gen)
+    frac = st_fast[..., 0].sum().item() / st_fast[..., 1].sum().item()
+    assert 0.02 < frac < 0.999, frac                                   # the case does skip, and does not skip everything
+    # mx / dynamic P reach the tensor core rounded to BF16 on this kernel, as in the reference
+    o, ostats = attention_p_requant(q, k, v, None, None, cfg, sm, faithful=False, return_stats=True, p_bf16=True)
+    assert torch.equal(st_fast, ostats)
+    _check(fast, o, (q, k, v))
+    assert OA.compute_metrics(fast, gen)["cosine"] > 0.99999
+
+
+def test_blasst_fills_outside_the_tmem_resident_kernel_take_the_general_one():
+    q, k, v = _qkv(1, 256, 1, 128, seed=5, outliers=True)
+    for fill, bins in (("logn", 16), ("sample8_a1.25", 16), ("uta", 1)):
+        cfg = QuantConfig(**COMMON, smoothing="off", q_kmeans_k=None, blasst_lambda=1e-2, blasst_fill=fill,
+                          blasst_uta_bins=bins)
+        fq.fake_quant_attention(q.to(DEV), k.to(DEV), v.to(DEV), cfg)
+        assert _variant() == 0
+
+
 def test_tmem_resident_variant_with_peaked_rows(monkeypatch):
     """Rows whose max keeps rising through the sweep (keys sorted by growing alignment with the queries): the
     accumulator is rescaled in tensor memory in most key blocks."""
