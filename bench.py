@@ -44,8 +44,8 @@ WORKLOADS = {
         qk_quant="fp8_block", v_quant="fp8_channel", q_smooth_block_size=256, fp8_block_size=64, p_requant=True,
         p_requant_block_m=64, p_requant_block_n=64, smoothing="full", q_kmeans_k=32, v_smooth_mode="per_block",
         v_smooth_block_size=64, v_kmeans_k=64, p_quant="dynamic", rowmax_mode="qm_k"), 1),
-    # the other two stacks of the benchmark list; they run on the general attention kernel (block-scaled Q.K^T;
-    # BLASST skip / fill), are parity-test cases first and are timed here for the record
+    # the other two stacks of the benchmark list (mxfp8 + Hadamard; BLASST skip / fill on video-like tokens): parity-test
+    # cases first, timed here for the record
     "wan14b_self_attn_mxfp8_hadamard": (dict(
         qk_quant="mxfp8", v_quant="mxfp8", mxfp8_block_size=32, v_mxfp8_block_size=64, qk_hadamard=True, p_requant=True,
         p_requant_block_m=64, p_requant_block_n=64, smoothing="off", q_kmeans_k=None, v_smooth_mode="off",
@@ -99,6 +99,22 @@ def pad_like_hook(q, k, v, cfg):
     from low_bit_fake_quant.hook import pad_qkv
     qp, kp, vp, pad = pad_qkv(q, k, v, cfg)
     return qp.contiguous(), kp.contiguous(), vp.contiguous(), pad
+
+
+def blasst_skip_ratios(qp, kp, vp, cfg):
+    """Row-skip and whole-program skip ratios from the kernel's stats tensor, computed the way the reference's BLASST
+    evaluation does (bench/eval_blasst_quant.py:216-227). One extra call, outside the timed region."""
+    import low_bit_fake_quant as fq
+    from low_bit_fake_quant.attention import _fake_quant_attention_p_requant
+    k_work = fq.smooth_k(kp)[0] if cfg.smoothing != "off" else kp
+    _, stats = _fake_quant_attention_p_requant(qp, k_work, vp, None, None, None, cfg, 1.0 / math.sqrt(qp.shape[-1]),
+                                               qp.dtype, return_stats=True)
+    skipped, total = float(stats[..., 0].sum().item()), float(stats[..., 1].sum().item())
+    tiles = stats[..., 1].gt(0)
+    tile_skipped = float((stats[..., 0] == stats[..., 1]).logical_and(tiles).sum().item())
+    return {"row_skip_ratio": skipped / total if total > 0 else 0.0,
+            "tile_skip_ratio": tile_skipped / float(tiles.sum().item()) if tiles.any() else 0.0,
+            "skipped_row_blocks": skipped, "total_row_blocks": total}
 
 
 class ClockSampler:
@@ -215,9 +231,17 @@ def main():
                     help="heads per pipelined chunk of the host-buffer entry (default: the entry's own choice)")
     ap.add_argument("--reference-operands", action="store_true",
                     help="run path B on the reference's own BF16 operands (BF16 MMAs) instead of the FP8 codes; not the headline")
+    ap.add_argument("--blasst-lambda", type=float, default=None, help="override the BLASST threshold of a BLASST workload")
+    ap.add_argument("--blasst-fill", default=None, help="override the BLASST fill of a BLASST workload (zero, mean_a1.5, uta16_a1.5 ...)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     cfg_kwargs, batch = WORKLOADS[args.workload]
+    if cfg_kwargs.get("blasst_lambda") is not None:
+        cfg_kwargs = dict(cfg_kwargs)
+        if args.blasst_lambda is not None:
+            cfg_kwargs["blasst_lambda"] = args.blasst_lambda
+        if args.blasst_fill is not None:
+            cfg_kwargs["blasst_fill"] = args.blasst_fill
 
     if args.impl == "reference":
         run_reference_arm(args, args.workload, cfg_kwargs)
@@ -353,6 +377,9 @@ def main():
             cpu = {"value": tf, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
                    "sample": f"1 head x S=32768 of the workload (1/40 of a step) x {reps} repeats, {dt:.2f} s each, "
                              "oracle port on the host cores"}
+        blasst = None
+        if cfg.blasst_lambda is not None and cfg.smoothing != "full" and cfg.q_kmeans_k is None and cfg.v_kmeans_k is None:
+            blasst = dict(blasst_skip_ratios(qp, kp, vp, cfg), blasst_lambda=cfg.blasst_lambda, blasst_fill=cfg.blasst_fill)
         line = {
             "metric": "fused FP8 fake-quant attn TFLOP/s at 40x32760x128", "value": value, "unit": "TFLOP/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
@@ -364,6 +391,8 @@ def main():
                        "parallelism": f"batch x heads sharded over {world} GPU(s), no collective"},
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
         }
+        if blasst is not None:
+            line["config"]["blasst"] = blasst       # flops are not reduced for skipped row-blocks
         print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()
