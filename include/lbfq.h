@@ -245,6 +245,12 @@ typedef struct lbfq_attn_args {
   const int64_t* out_row_index; /* (B*H, M): destination row of kernel row r (inverse Q reorder fused), or NULL */
   int out_fp32_exact;         /* 1: store the FP32 accumulator result without the BF16 rounding */
   int32_t* status;            /* device int: set non-zero if a bounded wait expired */
+  /* Optional diagnostic (bench/count_rowmax_updates_triton.py:27-171 counts the same events in a kernel of its
+   * own): six device counters, zero-initialised by the caller, or NULL. [0] row-max updates, [1] accumulator
+   * rescales (updates of a row that already holds mass), [2] upward updates, [3] downward updates (estimated row
+   * max only), [4] rows with at least one update, [5] largest number of updates of one row. Requests the general
+   * kernel. */
+  long long* rowmax_counters;
 } lbfq_attn_args;
 
 /* Bytes of caller-provided scratch the launch below needs (0 when V smoothing is off). */

@@ -15,7 +15,7 @@ void set_error(const char* fmt, ...) {
 }  // namespace lbfq
 
 extern "C" const char* lbfq_last_error(void) { return lbfq::g_err; }
-extern "C" int lbfq_abi_version(void) { return 1; }
+extern "C" int lbfq_abi_version(void) { return 2; }
 
 // Kernels launched by this library since load (all entry points count through check_launch()).
 namespace lbfq { unsigned long long g_launches = 0; }

@@ -185,6 +185,7 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
     else if (p.rowmax_init) { m_i = p.rowmax_init[(size_t)bh * p.M + rowc]; }
     float l_i = 0.f, max_seen = -INFINITY;
     float n_skip = 0.f, n_total = 0.f;
+    int n_upd = 0, n_resc = 0, n_down = 0;       // optional diagnostic: row-max updates of this row
     float a_prev = 1.f, c_prev = 1.f;
     bool elided_prev = false;
     int blk_prev = 0;
@@ -261,7 +262,6 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         }
         if (has_av) {
           const float4* a4 = reinterpret_cast<const float4*>(av + c0);
-#pragma unroll
           const float2 rs2 = make_float2(rs, rs);
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
@@ -391,6 +391,20 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         alpha = ex2((m_i - m_new) * kLog2e);
       }
 
+      if (p.counters != nullptr) {
+        // an update moves the row's reference max; it costs a rescale when the row already holds mass
+        bool adjust, downward = false;
+        if (!BLASST && p.rm_mode == 2) {
+          adjust = m_new != m_i;
+          downward = adjust && !((bmax - m_i) > 16.0f / kLog2e);
+        } else {
+          adjust = m_new > m_i;
+        }
+        n_upd += adjust ? 1 : 0;
+        n_resc += (adjust && l_i != 0.f) ? 1 : 0;
+        n_down += downward ? 1 : 0;
+      }
+
       // whole-tile elision: every row of this 128-row tile skips and nothing is filled in
       bool elide = false;
       if (BLASST) {
@@ -513,7 +527,6 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
             inv = __fdiv_rn(1.0f, c_blk);
           }
           // the conversion saturates at 448, which is the reference's clamp
-#pragma unroll
           const float2 inv2 = make_float2(inv, inv);
 #pragma unroll
           for (int i = 0; i < BN / 4; ++i) {
@@ -599,6 +612,28 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
           }
           o[i] = make_uint4(w[0], w[1], w[2], w[3]);
         }
+      }
+    }
+    if (p.counters != nullptr) {                  // every lane takes part in the warp sums
+      const bool live = row_ok && alive;
+      const unsigned long long upd = live ? n_upd : 0, resc = live ? n_resc : 0, down = live ? n_down : 0;
+      auto warp_sum = [](unsigned long long v) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        return v;
+      };
+      const unsigned long long s_upd = warp_sum(upd), s_resc = warp_sum(resc), s_down = warp_sum(down);
+      const unsigned long long s_rows = warp_sum(upd > 0 ? 1ull : 0ull);
+      unsigned int mx = (unsigned int)upd;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      if (lane == 0) {
+        atomicAdd(p.counters + 0, s_upd);
+        atomicAdd(p.counters + 1, s_resc);
+        atomicAdd(p.counters + 2, s_upd - s_down);
+        atomicAdd(p.counters + 3, s_down);
+        atomicAdd(p.counters + 4, s_rows);
+        atomicMax(p.counters + 5, (unsigned long long)mx);
       }
     }
     if (BLASST && alive && row_ok && p.stats) {
@@ -1002,6 +1037,7 @@ extern "C" int lbfq_attention_fwd(const lbfq_attn_args* a, void* workspace, void
   p.lambda = a->use_blasst ? a->blasst_lambda : 0.f;
   p.fill_kind = a->use_blasst ? a->fill_kind : 0; p.fill_alpha = a->fill_alpha; p.uta_bins = a->uta_bins > 0 ? a->uta_bins : 1;
   p.stats = a->use_blasst ? a->blasst_stats : nullptr;
+  p.counters = reinterpret_cast<unsigned long long*>(a->rowmax_counters);
   p.out = a->out; p.out_dtype = a->out_dtype; p.out_layout = a->out_layout; p.out_exact = a->out_fp32_exact;
   p.out_row_index = a->out_row_index; p.status = a->status;
   p.n_v_scale = a->v_kind == LBFQ_V_CHANNEL ? (long long)a->B * a->H * a->D
@@ -1026,6 +1062,7 @@ extern "C" int lbfq_attention_fwd(const lbfq_attn_args* a, void* workspace, void
   const uint64_t BH = (uint64_t)a->B * a->H;
   if (bf) {
     // BF16 operands: only the TMEM-resident kernel multiplies them
+    LBFQ_REQUIRE(a->rowmax_counters == nullptr, LBFQ_ERR_UNSUPPORTED, "rowmax_counters are served on FP8-code operands only");
     const int fvb = fast_variant(p, a->use_blasst != 0, false);
     LBFQ_REQUIRE(fvb == 2, LBFQ_ERR_UNSUPPORTED,
                  "BF16 operands are served for V per channel / pre-dequantised, without BLASST, with q_smooth_block a "
@@ -1047,7 +1084,7 @@ extern "C" int lbfq_attention_fwd(const lbfq_attn_args* a, void* workspace, void
   // LBFQ_ATTN_GENERIC=1 keeps every configuration on the general kernel (used to cross-check the two)
   const char* force_generic = getenv("LBFQ_ATTN_GENERIC");
   g_last_variant = 0;
-  const int fv = (force_generic && force_generic[0] == '1') ? 0 : fast_variant(p, bl, mx);
+  const int fv = ((force_generic && force_generic[0] == '1') || p.counters != nullptr) ? 0 : fast_variant(p, bl, mx);
   if (fv == 1) {
     g_last_variant = 1;
     return launch_fast(mq, mk, mv, mv, p, a->block_n, 1, st);

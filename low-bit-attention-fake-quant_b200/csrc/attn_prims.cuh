@@ -332,6 +332,7 @@ struct Params {
   float fill_alpha;
   int uta_bins;
   float* stats;
+  unsigned long long* counters; // optional row-max update counters (6), general kernel only
   void* out;
   int out_dtype, out_layout, out_exact;
   const int64_t* out_row_index;

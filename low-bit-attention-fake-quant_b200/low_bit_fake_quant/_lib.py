@@ -61,6 +61,7 @@ class AttnArgs(C.Structure):
         ("out_row_index", C.c_void_p),
         ("out_fp32_exact", C.c_int),
         ("status", C.c_void_p),
+        ("rowmax_counters", C.c_void_p),
     ]
 
 

@@ -190,7 +190,8 @@ def _fake_quant_attention_sdpa(q_work, k_work, v_work, qm, v_alpha, cfg: QuantCo
 
 def _fake_quant_attention_p_requant(q_work, k_work, v_work, qm, v_alpha, q_kmeans, cfg: QuantConfig,
                                     sm_scale, out_dtype, *, return_stats: bool = False,
-                                    out_fp32_exact: bool = False, head_offset: int = 0, total_heads: int = 0):
+                                    out_fp32_exact: bool = False, head_offset: int = 0, total_heads: int = 0,
+                                    rowmax_counters=None):
     """Quantise straight into the kernel's layouts and launch it. Returns the
     output in NHD, rows already back in the original Q order."""
     b, s, h, d = q_work.shape
@@ -259,6 +260,7 @@ def _fake_quant_attention_p_requant(q_work, k_work, v_work, qm, v_alpha, q_kmean
         out_dtype=torch.float32 if out_fp32_exact else out_dtype, out_nhd=True,
         out_row_index=q_kmeans.order if q_kmeans is not None else None,
         out_fp32_exact=out_fp32_exact,
+        rowmax_counters=rowmax_counters,
     )
 
 

@@ -121,8 +121,12 @@ def fake_quant_attention_fp8(
     out_nhd: bool = False,
     out_row_index: Optional[torch.Tensor] = None,
     out_fp32_exact: bool = False,
+    rowmax_counters: Optional[torch.Tensor] = None,
 ):
     """Streaming attention on e4m3 operands; output (B,H,M,D) or NHD (B,M,H,D).
+
+    ``rowmax_counters``: optional int64 tensor of 6 zeros on the device; the kernel adds its row-max update
+    counts to it (see ``low_bit_fake_quant.diagnostics``).
 
     ``out_row_index`` (B*H, M) int64 scatters kernel row r to output row
     ``out_row_index[bh, r]`` (the inverse Q reorder fused into the store).
@@ -204,6 +208,10 @@ def fake_quant_attention_fp8(
         a.out_row_index = L.ptr(out_row_index.contiguous()) if out_row_index is not None else None
         a.out_fp32_exact = 1 if out_fp32_exact else 0
         a.status = status.data_ptr()
+        if rowmax_counters is not None:
+            if rowmax_counters.dtype != torch.int64 or rowmax_counters.numel() != 6 or rowmax_counters.device != dev:
+                raise ValueError("rowmax_counters must be 6 int64 values on the operands' device")
+            a.rowmax_counters = rowmax_counters.data_ptr()
         ws_bytes = L.lib().lbfq_attention_workspace_bytes(C.byref(a))
         ws = torch.empty((max(int(ws_bytes), 1),), dtype=torch.uint8, device=dev)
         if KERNEL_EVENTS is not None:

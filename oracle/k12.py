@@ -95,8 +95,13 @@ def k12_attention(
     faithful: Optional[bool] = None,
     p_bf16: Optional[bool] = None,
     return_stats: bool = False,
+    rowmax_counters: Optional[dict] = None,
 ):
-    """Returns FP32 output (B,H,M,D) before the final cast (and stats)."""
+    """Returns FP32 output (B,H,M,D) before the final cast (and stats).
+
+    ``rowmax_counters``: a dict that receives the row-max update counts of this run, the events the reference's
+    diagnostic kernel counts (bench/count_rowmax_updates_triton.py:118-171): an update moves a row's reference max,
+    a rescale is an update of a row that already holds mass."""
     B, H, M, D = q_op.shape
     N = k_op.shape[2]
     if faithful is None:
@@ -144,6 +149,8 @@ def k12_attention(
     max_seen = torch.full((B, H, M), -float("inf"))
     skipped_cnt = torch.zeros((B, H, M))
     total_cnt = torch.zeros((B, H, M))
+    upd_cnt = torch.zeros((B, H, M), dtype=torch.int64)
+    n_resc = n_down = 0
 
     for n0 in range(0, N, block_n):
         n1 = min(n0 + block_n, N)
@@ -192,6 +199,15 @@ def k12_attention(
         else:                                                              # :215-217
             m_ij = torch.maximum(m_i, block_max)
             alpha = torch.exp2((m_i - m_ij) * log2e)
+
+        if rowmax_counters is not None:
+            moved = m_ij != m_i
+            if est is not None and pk == 2 and not use_blasst:
+                n_down += int((moved & ~((block_max - m_i) > _f32(16.0) / log2e)).sum())
+            else:
+                moved = m_ij > m_i
+            upd_cnt += moved.long()
+            n_resc += int((moved & (l_i != 0.0)).sum())
 
         if pk == 0:
             z = (s - m_ij[..., None]) * log2e + off
@@ -274,6 +290,10 @@ def k12_attention(
             c_acc = c_acc * alpha[..., None] + p_rec.sum(dim=-1)[..., None] * a_v[:, :, None, :]
         m_i = m_ij
 
+    if rowmax_counters is not None:
+        n_upd = int(upd_cnt.sum())
+        rowmax_counters.update(updates=n_upd, rescales=n_resc, upward_updates=n_upd - n_down, downward_updates=n_down,
+                               rows_with_update=int((upd_cnt > 0).sum()), max_updates_per_row=int(upd_cnt.max()))
     inv_l = 1.0 / l_i[..., None]                                           # :387-399
     out_main = acc * v_scale_bhd.float()[:, :, None, :] if v_block_scale is None else acc
     out = (out_main + c_acc) * inv_l if v_alpha is not None else out_main * inv_l

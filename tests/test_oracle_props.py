@@ -161,3 +161,23 @@ def test_errors_match_reference_messages():
                                                      rowmax_mode="qm_k"))
     with pytest.raises(ValueError, match="shapes must match"):
         OA.fake_quant_attention(q, q[:, :32], q, QuantConfig())
+
+
+def test_rowmax_counters_of_the_oracle():
+    """The events bench/count_rowmax_updates_triton.py of the reference counts: every row updates in its first block
+    (no rescale: no mass yet), the frozen estimate never updates, the thresholded estimate updates far less often."""
+    torch.manual_seed(6)
+    q, k, v = (torch.randn(1, 512, 2, 64).bfloat16() for _ in range(3))
+    kw = dict(fp8_block_size=64, q_smooth_block_size=64, q_kmeans_k=None, smoothing="full")
+    counts = {}
+    for name, extra in (("online", dict(p_quant="dynamic")), ("thresholds", dict(p_quant="dynamic", rowmax_mode="qm_k")),
+                        ("frozen", dict(rowmax_mode="qm_k"))):
+        c = {}
+        OA.fake_quant_attention(q, k, v, QuantConfig(**kw, **extra), faithful=False, rowmax_counters=c)
+        counts[name] = c
+    on, th, fr = counts["online"], counts["thresholds"], counts["frozen"]
+    rows = 1 * 512 * 2
+    assert on["rows_with_update"] == rows and on["updates"] - on["rescales"] == rows and on["downward_updates"] == 0
+    assert 1 <= on["max_updates_per_row"] <= 512 // 64
+    assert fr == dict(updates=0, rescales=0, upward_updates=0, downward_updates=0, rows_with_update=0, max_updates_per_row=0)
+    assert th["updates"] == th["upward_updates"] + th["downward_updates"] and th["rescales"] * 4 < on["rescales"]
