@@ -50,6 +50,12 @@ WORKLOADS = {
         qk_quant="mxfp8", v_quant="mxfp8", mxfp8_block_size=32, v_mxfp8_block_size=64, qk_hadamard=True, p_requant=True,
         p_requant_block_m=64, p_requant_block_n=64, smoothing="off", q_kmeans_k=None, v_smooth_mode="off",
         v_kmeans_k=None, p_quant="auto", rowmax_mode="online"), 1),
+    # the cross-attention shape of the same stack (32760 video queries over 512 text keys): an extension with no
+    # counterpart in the reference, whose hook sends cross-attention to plain SDPA; device-resident timing only
+    "wan14b_cross_attn_mxfp8_hadamard": (dict(
+        qk_quant="mxfp8", v_quant="mxfp8", mxfp8_block_size=32, v_mxfp8_block_size=64, qk_hadamard=True, p_requant=True,
+        p_requant_block_m=64, p_requant_block_n=64, smoothing="off", q_kmeans_k=None, v_smooth_mode="off",
+        v_kmeans_k=None, p_quant="auto", rowmax_mode="online"), 1, 512),
     "wan14b_video_blasst_mean_1e-2": (dict(
         qk_quant="fp8_block", v_quant="fp8_channel", fp8_block_size=64, p_requant=True, p_requant_block_m=64,
         p_requant_block_n=64, smoothing="k_only", q_kmeans_k=None, v_smooth_mode="off", v_kmeans_k=None,
@@ -235,7 +241,8 @@ def main():
     ap.add_argument("--blasst-fill", default=None, help="override the BLASST fill of a BLASST workload (zero, mean_a1.5, uta16_a1.5 ...)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
-    cfg_kwargs, batch = WORKLOADS[args.workload]
+    cfg_kwargs, batch = WORKLOADS[args.workload][:2]
+    seq_k = WORKLOADS[args.workload][2] if len(WORKLOADS[args.workload]) > 2 else None     # cross-attention: keys
     if cfg_kwargs.get("blasst_lambda") is not None:
         cfg_kwargs = dict(cfg_kwargs)
         if args.blasst_lambda is not None:
@@ -276,9 +283,18 @@ def main():
     qp, kp, vp, pad = pad_like_hook(q, k, v, cfg)
     del q, k, v
     flops_per_step = 4.0 * batch * heads * seq * seq * D_HEAD          # unpadded, per GPU
+    if seq_k is not None:
+        # queries padded as above; the text keys / values have their own (block-aligned) length
+        _, kp, vp = make_inputs(batch, heads, seq_k, D_HEAD, 4321 + rank, dev)
+        flops_per_step = 4.0 * batch * heads * seq * seq_k * D_HEAD
+        args.no_e2e = True                                              # the host-buffer entry takes equal shapes
+        args.no_cpu_baseline = True
     lib = L.lib()
 
     def step(qq, kk, vv):
+        if seq_k is not None:
+            from low_bit_fake_quant.hook import fake_quant_cross_attention
+            return fake_quant_cross_attention(qq, kk, vv, cfg)[:, :seq]
         o = fq.fake_quant_attention(qq, kk, vv, cfg, _reference_operands=args.reference_operands)
         return o[:, :seq]
 
@@ -386,7 +402,7 @@ def main():
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16 (reference-operand mode)" if args.reference_operands else "fp8_e4m3", "data": "synthetic",
             "config": {"workload": args.workload + ("+reference_operands" if args.reference_operands else ""), "B_per_gpu": batch, "global_batch": batch * world, "H": heads,
-                       "S": seq, "S_padded": seq + pad, "D": D_HEAD, "input_dtype": "bf16",
+                       "S": seq, "S_padded": seq + pad, "S_keys": seq_k if seq_k is not None else seq, "D": D_HEAD, "input_dtype": "bf16",
                        "l2": "inputs (3 x %.0f MB) exceed the 126 MB L2" % (qp.numel() * 2 / 1e6),
                        "parallelism": f"batch x heads sharded over {world} GPU(s), no collective"},
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clocks,

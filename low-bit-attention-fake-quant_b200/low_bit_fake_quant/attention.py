@@ -118,7 +118,8 @@ def _rotated(q_work, k_work, cfg: QuantConfig, head_offset: int = 0, total_heads
     if not cfg.qk_hadamard:
         return q_work, k_work
     return apply_qk_hadamard(q_work, k_work, random_sign=cfg.qk_hadamard_random_sign, seed=cfg.qk_hadamard_seed,
-                             head_offset=head_offset, total_heads=total_heads if total_heads > 0 else None)
+                             head_offset=head_offset, total_heads=total_heads if total_heads > 0 else None,
+                             _cross=q_work.shape[1] != k_work.shape[1])
 
 
 # ---------------------------------------------------------------------------
@@ -194,20 +195,21 @@ def _fake_quant_attention_p_requant(q_work, k_work, v_work, qm, v_alpha, q_kmean
                                     rowmax_counters=None):
     """Quantise straight into the kernel's layouts and launch it. Returns the
     output in NHD, rows already back in the original Q order."""
+    # K / V may have their own length (cross-attention, an extension: the reference's entry takes equal shapes only)
     b, s, h, d = q_work.shape
-    s_pad = _round_up(s, 128)
+    s_k = k_work.shape[1]
+    sq_pad, s_pad = _round_up(s, 128), _round_up(s_k, 128)
     q_in, k_in = _rotated(q_work, k_work, cfg, head_offset, total_heads)
 
     q_sf = k_sf = None
     if cfg.qk_quant == "fp8_block":
-        q_codes, q_scale = fp8_block_quant(q_in, block_s=cfg.fp8_block_size, _layout=L.LAYOUT_BHSD, _s_pad=s_pad)
+        q_codes, q_scale = fp8_block_quant(q_in, block_s=cfg.fp8_block_size, _layout=L.LAYOUT_BHSD, _s_pad=sq_pad)
         k_codes, k_scale = fp8_block_quant(k_in, block_s=cfg.fp8_block_size, _layout=L.LAYOUT_BHSD, _s_pad=s_pad)
     elif cfg.qk_quant == "mxfp8":
         # codes + UE8M0 scale tiles for the block-scaled MMA (the FP32 scale tensors are by-products here)
-        nsf = b * h * s_pad * 4
-        q_sf = torch.empty((nsf,), dtype=torch.uint8, device=q_in.device)
-        k_sf = torch.empty((nsf,), dtype=torch.uint8, device=q_in.device)
-        q_codes, q_scale = mxfp8_qk_quant(q_in, block_d=cfg.mxfp8_block_size, _layout=L.LAYOUT_BHSD, _s_pad=s_pad, _scale_e8=q_sf)
+        q_sf = torch.empty((b * h * sq_pad * 4,), dtype=torch.uint8, device=q_in.device)
+        k_sf = torch.empty((b * h * s_pad * 4,), dtype=torch.uint8, device=q_in.device)
+        q_codes, q_scale = mxfp8_qk_quant(q_in, block_d=cfg.mxfp8_block_size, _layout=L.LAYOUT_BHSD, _s_pad=sq_pad, _scale_e8=q_sf)
         k_codes, k_scale = mxfp8_qk_quant(k_in, block_d=cfg.mxfp8_block_size, _layout=L.LAYOUT_BHSD, _s_pad=s_pad, _scale_e8=k_sf)
     else:
         raise ValueError(f"unsupported qk_quant: {cfg.qk_quant!r}")
@@ -243,7 +245,7 @@ def _fake_quant_attention_p_requant(q_work, k_work, v_work, qm, v_alpha, q_kmean
 
     return fake_quant_attention_fp8(
         q_codes, k_codes, v_codes,
-        seq_q=s, seq_k=s,
+        seq_q=s, seq_k=s_k,
         q_scale=q_scale, k_scale=k_scale,
         qk_block=cfg.fp8_block_size if cfg.qk_quant == "fp8_block" else cfg.mxfp8_block_size,
         q_scale_e8=q_sf, k_scale_e8=k_sf,
@@ -309,7 +311,8 @@ def _fake_quant_attention_p_requant_reference_operands(q_work, k_work, v_work, q
     to_bh = lambda t: t.permute(0, 2, 1, 3).contiguous()
     rowmax_est = None
     if qm is not None and cfg.rowmax_mode == "qm_k":
-        _, rowmax_g = qm_corr(qm, k_work.to(torch.bfloat16), sm_scale=sm_scale, s_pad=_round_up(s, 128), want_rowmax=True)
+        _, rowmax_g = qm_corr(qm, k_work.to(torch.bfloat16), sm_scale=sm_scale, s_pad=_round_up(k_work.shape[1], 128),
+                              want_rowmax=True)
         rowmax_est = rowmax_g.repeat_interleave(cfg.q_smooth_block_size, dim=2).contiguous()
     p_mode = cfg.p_quant
     if p_mode == "auto":
@@ -341,6 +344,7 @@ def fake_quant_attention(
     return_artifacts: bool = False,
     preprocess_cache: Optional[PreprocessCache] = None,
     _debug_fp32: bool = False,
+    _cross: bool = False,
     _head_offset: int = 0,
     _total_heads: int = 0,
     _reference_operands: bool = False,
@@ -358,7 +362,15 @@ def fake_quant_attention(
     """
     if cfg is None:
         cfg = QuantConfig()
-    if q.shape != k.shape or q.shape != v.shape:
+    if _cross:
+        # extension (hook.fake_quant_cross_attention): K / V of their own length, streaming path only
+        ok = (q.ndim == k.ndim == 4 and k.shape == v.shape and q.shape[0] == k.shape[0] and q.shape[2:] == k.shape[2:])
+        if not ok:
+            raise ValueError(f"cross-attention wants q (B,Sq,H,D) and k, v (B,Sk,H,D); got {tuple(q.shape)}, "
+                             f"{tuple(k.shape)}, {tuple(v.shape)}")
+        if not cfg.p_requant:
+            raise ValueError("cross-attention is served by the streaming kernel: requires cfg.p_requant=True")
+    elif q.shape != k.shape or q.shape != v.shape:
         raise ValueError(f"q/k/v shapes must match; got {tuple(q.shape)}, {tuple(k.shape)}, {tuple(v.shape)}")
     if q.ndim != 4:
         raise ValueError(f"q/k/v must be 4-D (B,S,H,D); got {q.shape}")

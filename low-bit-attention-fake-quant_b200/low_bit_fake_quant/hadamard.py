@@ -58,13 +58,15 @@ def apply_qk_hadamard(
     transform: Callable[[torch.Tensor], torch.Tensor] | None = None,
     head_offset: int = 0,
     total_heads: int | None = None,
+    _cross: bool = False,
 ) -> tuple[torch.Tensor, torch.Tensor]:
     """``x' = FWHT(x * sign[h]) / sqrt(D)`` for Q and K with the same signs.
 
     ``head_offset`` / ``total_heads`` (extensions) index the sign table by
     global head so that a heads shard reproduces the unsharded rotation.
     """
-    if q.shape != k.shape:
+    same = q.shape == k.shape or (_cross and q.ndim == k.ndim == 4 and q.shape[0] == k.shape[0] and q.shape[2:] == k.shape[2:])
+    if not same:                                         # `_cross` (extension): K may have its own length
         raise ValueError(f"q/k shapes must match; got {tuple(q.shape)} and {tuple(k.shape)}")
     if q.ndim != 4:
         raise ValueError(f"q/k must be NHD tensors; got {tuple(q.shape)}")

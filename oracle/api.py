@@ -349,8 +349,12 @@ def attention_p_requant(qw, kw, vw, qm, v_alpha, cfg, sm_scale, *, faithful: boo
 
 def fake_quant_attention(q, k, v, cfg, *, sm_scale: Optional[float] = None, faithful: bool = True,
                          q_labels=None, v_labels=None, out_fp32: bool = False, head_offset: int = 0,
-                         total_heads: int = 0, p_bf16: Optional[bool] = None, rowmax_counters: Optional[dict] = None):
+                         total_heads: int = 0, p_bf16: Optional[bool] = None, rowmax_counters: Optional[dict] = None,
+                         cross: bool = False):
     """attention.py:706-806 on CPU tensors.
+
+    ``cross`` (an extension the reference's entry does not have) lets K / V have their own length; every step below
+    already treats the Q side and the K / V side separately.
 
     ``faithful=True`` follows the reference's BF16 de-quantised operands;
     ``faithful=False`` is the true-FP8 convention (see ``oracle/k12.py``);
@@ -358,7 +362,10 @@ def fake_quant_attention(q, k, v, cfg, *, sm_scale: Optional[float] = None, fait
     ``out_fp32`` returns the kernel's FP32 result before the cast to
     ``q.dtype`` so that tolerances below one BF16 ulp can be checked.
     """
-    if q.shape != k.shape or q.shape != v.shape:
+    if cross:
+        if not (q.ndim == 4 and k.shape == v.shape and q.shape[0] == k.shape[0] and q.shape[2:] == k.shape[2:] and cfg.p_requant):
+            raise ValueError("cross-attention wants q (B,Sq,H,D), k and v (B,Sk,H,D) and cfg.p_requant=True")
+    elif q.shape != k.shape or q.shape != v.shape:
         raise ValueError(f"q/k/v shapes must match; got {tuple(q.shape)}, {tuple(k.shape)}, {tuple(v.shape)}")
     if q.ndim != 4:
         raise ValueError(f"q/k/v must be 4-D (B,S,H,D); got {q.shape}")
