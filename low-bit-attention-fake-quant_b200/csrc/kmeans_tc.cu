@@ -3,11 +3,12 @@
 // argmin_c |c|^2 - 2 x.c needs the (tokens x centroids) Gram block x.c^T: a GEMM with M = tokens, N = k <= 64,
 // K = D. The tokens are BF16 already; the FP32 centroids are split into three BF16 pieces
 // (c = hi + mid + lo to 24 bits), so that x.c = x.hi + x.mid + x.lo is accumulated from exact BF16 x BF16
-// products in FP32 -- the same value as the FP32 FFMA kernel up to summation order. One CTA = 128 tokens of one
-// (b, h): TMA brings the token tile (two 64-channel panels, 128B swizzle) and the 3 x 64 centroid rows,
-// one thread issues 3 x D/16 tcgen05.mma.kind::f16 into 64 TMEM columns, then thread == token reads its row of
-// dot products back and takes the argmin (lowest index on ties, as the FFMA kernel does). The kernel is bound by
-// reading the tokens once per Lloyd iteration (HBM / L2), not by arithmetic.
+// products in FP32 -- the same value as the FP32 FFMA kernel up to summation order. One CTA walks a few
+// consecutive 128-token tiles of one (b, h): TMA brings the 3 x 64 centroid rows once and the token tiles (two
+// 64-channel panels, 128B swizzle) through a double buffer, one thread issues 3 x D/16 tcgen05.mma.kind::f16 per tile
+// into one of two 64-column TMEM buffers, then thread == token reads its row of dot products back and takes the
+// argmin (lowest index on ties, as the FFMA kernel does). The kernel is bound by reading the tokens once per Lloyd
+// iteration (HBM / L2), not by arithmetic.
 #include "attn_prims.cuh"
 #include "kmeans_tc.h"
 
@@ -45,6 +46,11 @@ __global__ void split_centroids_kernel(const float* __restrict__ cent, int BH, i
   }
 }
 
+// One CTA walks kTcTiles consecutive 128-token tiles of one (b, h): the centroid pieces are loaded once, the token
+// tiles go through two shared-memory buffers and two 64-column TMEM buffers, so that the TMA load of tile i + 2 and
+// the MMAs of tile i + 1 run while the threads take the argmin of tile i.
+constexpr int kTcTiles = 8;
+
 template <int D>
 __global__ void __launch_bounds__(128)
 assign_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_c, int S, int H, int k,
@@ -52,28 +58,47 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
   constexpr int NP = D / 64;                         // 64-channel panels (one 128-byte swizzle row each)
   constexpr int kA = kTcTok * 128;                   // bytes per token panel
   constexpr int kB = 3 * kTcCen * 128;               // bytes per centroid panel (three pieces)
+  // The swizzled tiles want a 1 KB-aligned base, which the declared alignment of the dynamic shared-memory array
+  // provides; no slack is allocated for rounding up (two CTAs of 112 KB share an SM), so a base that is not
+  // aligned is refused below instead of being rounded.
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint8_t* smem = smem_raw;
   const uint32_t sbase = smem_u32(smem);
-  const uint32_t offA = 0, offB = NP * kA, offBar = offB + NP * kB;
-  const uint32_t bar_full = sbase + offBar, bar_done = sbase + offBar + 8;
-  volatile int* misc = (volatile int*)(smem + offBar + 16);       // [0] tmem base, [1] abort
+  const uint32_t offA = 0, offB = 2 * NP * kA, offBar = offB + NP * kB;
+  auto bar_full = [&](int buf) { return sbase + offBar + 8u * buf; };          // token tile (and, first, centroids) landed
+  auto bar_done = [&](int buf) { return sbase + offBar + 16u + 8u * buf; };    // MMAs of the tile in this buffer done
+  volatile int* misc = (volatile int*)(smem + offBar + 32);       // [0] tmem base, [1] abort
   volatile int* abort_flag = misc + 1;
 
   const int ntile = (S + kTcTok - 1) / kTcTok;
-  const int tile = blockIdx.x % ntile;
-  const int bh = blockIdx.x / ntile;
-  const int b = bh / H, h = bh % H;
+  const int per_bh = (ntile + kTcTiles - 1) / kTcTiles;
+  // heads vary fastest over the grid: the CTAs in flight together read the same token rows of the (B, S, H, D) input,
+  // head by head, so each DRAM page is used whole while it is open
+  const int h = blockIdx.x % H;
+  const int tile0 = ((blockIdx.x / H) % per_bh) * kTcTiles;
+  const int b = blockIdx.x / (H * per_bh);
+  const int bh = b * H + h;
+  const int n = min(kTcTiles, ntile - tile0);        // tiles of this CTA (>= 1)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if ((sbase & 1023u) != 0) {
+    // never expected; the labels are marked invalid so that the caller's checks see it
+    for (int i = 0; i < n; ++i) {
+      const int tok = (tile0 + i) * kTcTok + (int)threadIdx.x;
+      if (tok < S) labels[(size_t)bh * S + tok] = -1;
+    }
+    return;
+  }
 
   if (threadIdx.x == 0) {
-    mbar_init(bar_full, 1);
-    mbar_init(bar_done, 1);
+    mbar_init(bar_full(0), 1);
+    mbar_init(bar_full(1), 1);
+    mbar_init(bar_done(0), 1);
+    mbar_init(bar_done(1), 1);
     misc[1] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 0) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 64;" ::"r"(sbase + offBar + 16) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 128;" ::"r"(sbase + offBar + 32) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   tc_fence_before();
@@ -81,68 +106,101 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
   tc_fence_after();
   const uint32_t tmem = (uint32_t)misc[0];
 
-  if (threadIdx.x == 0) {
-    mbar_expect_tx(bar_full, NP * (kA + kB));
+  auto load_tile = [&](int i) {                       // thread 0: token tile i of this CTA into buffer i & 1
+    const int buf = i & 1;
 #pragma unroll
-    for (int pn = 0; pn < NP; ++pn) {
-      tma_load_4d(sbase + offA + pn * kA, &tm_x, pn * 64, h, tile * kTcTok, b, bar_full);
-      tma_load_3d(sbase + offB + pn * kB, &tm_c, pn * 64, 0, bh, bar_full);
-    }
-    if (mbar_wait(bar_full, 0, abort_flag, nullptr, 1)) {
-      tc_fence_after();
-      const uint32_t idesc = make_idesc_bf16(kTcCen);
-      bool first = true;
-#pragma unroll
-      for (int pc = 0; pc < 3; ++pc)
-#pragma unroll
-        for (int pn = 0; pn < NP; ++pn) {
-          const uint64_t da = make_desc(sbase + offA + pn * kA, 128);
-          const uint64_t db = make_desc(sbase + offB + pn * kB + pc * (kTcCen * 128), 128);
-#pragma unroll
-          for (int ks = 0; ks < 4; ++ks) {
-            mma_bf16_ss(tmem, da + (uint64_t)(ks * 2), db + (uint64_t)(ks * 2), idesc, first ? 0u : 1u);
-            first = false;
-          }
-        }
-      tc_commit(bar_done);
-    }
-  }
-  __syncwarp();
-  // thread == token == TMEM lane
-  const bool ok = mbar_wait(bar_done, 0, abort_flag, nullptr, 2);
-  const bool all_ok = __all_sync(0xffffffffu, ok);
-  if (all_ok) {
+    for (int pn = 0; pn < NP; ++pn)
+      tma_load_4d(sbase + offA + (buf * NP + pn) * kA, &tm_x, pn * 64, h, (tile0 + i) * kTcTok, b, bar_full(buf));
+  };
+  auto issue_mma = [&](int i) -> bool {               // thread 0: Gram block of tile i into TMEM buffer i & 1
+    const int buf = i & 1;
+    if (!mbar_wait(bar_full(buf), (uint32_t)((i >> 1) & 1), abort_flag, nullptr, 1)) return false;
     tc_fence_after();
-    const uint32_t trow = tmem + ((uint32_t)(warp * 32) << 16);
-    uint32_t r0[32], r1[32];
-    LBFQ_TMEM_LD32(r0, trow);
-    LBFQ_TMEM_LD32(r1, trow + 32);
-    tc_wait_ld();
-    const float* cn = cnorm + (size_t)bh * k;
-    float best = INFINITY;
-    int best_i = 0;
+    const uint32_t idesc = make_idesc_bf16(kTcCen);
+    bool first = true;
 #pragma unroll
-    for (int c = 0; c < 32; ++c) {
-      if (c < k) {
-        const float dist = cn[c] - 2.0f * __uint_as_float(r0[c]);
-        if (dist < best) { best = dist; best_i = c; }          // ascending c: lowest index wins ties
-      }
-    }
+    for (int pc = 0; pc < 3; ++pc)
 #pragma unroll
-    for (int c = 0; c < 32; ++c) {
-      if (32 + c < k) {
-        const float dist = cn[32 + c] - 2.0f * __uint_as_float(r1[c]);
-        if (dist < best) { best = dist; best_i = 32 + c; }
+      for (int pn = 0; pn < NP; ++pn) {
+        const uint64_t da = make_desc(sbase + offA + (buf * NP + pn) * kA, 128);
+        const uint64_t db = make_desc(sbase + offB + pn * kB + pc * (kTcCen * 128), 128);
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+          mma_bf16_ss(tmem + buf * kTcCen, da + (uint64_t)(ks * 2), db + (uint64_t)(ks * 2), idesc, first ? 0u : 1u);
+          first = false;
+        }
       }
+    tc_commit(bar_done(buf));
+    return true;
+  };
+
+  if (threadIdx.x == 0) {
+    mbar_expect_tx(bar_full(0), NP * (kA + kB));
+#pragma unroll
+    for (int pn = 0; pn < NP; ++pn) tma_load_3d(sbase + offB + pn * kB, &tm_c, pn * 64, 0, bh, bar_full(0));
+    load_tile(0);
+    if (n > 1) {
+      mbar_expect_tx(bar_full(1), NP * kA);
+      load_tile(1);
     }
-    const int tok = tile * kTcTok + warp * 32 + lane;
-    if (tok < S) labels[(size_t)bh * S + tok] = best_i;
+    issue_mma(0);
+  }
+  const float* cn = cnorm + (size_t)bh * k;
+  for (int i = 0; i < n; ++i) {
+    const int buf = i & 1;
+    // the next tile's MMAs first (its TMEM buffer was read out two tiles ago, before the last barrier)
+    if (threadIdx.x == 0 && i + 1 < n) issue_mma(i + 1);
+    __syncwarp();
+    // thread == token == TMEM lane
+    const bool ok = mbar_wait(bar_done(buf), (uint32_t)((i >> 1) & 1), abort_flag, nullptr, 2);
+    const bool all_ok = __all_sync(0xffffffffu, ok);
+    if (threadIdx.x == 0 && ok && i + 2 < n) {         // the tile's shared-memory buffer is free again
+      mbar_expect_tx(bar_full(buf), NP * kA);
+      load_tile(i + 2);
+    }
+    __syncwarp();
+    if (all_ok) {
+      tc_fence_after();
+      const uint32_t trow = tmem + buf * kTcCen + ((uint32_t)(warp * 32) << 16);
+      uint32_t r0[32], r1[32];
+      LBFQ_TMEM_LD32(r0, trow);
+      LBFQ_TMEM_LD32(r1, trow + 32);
+      tc_wait_ld();
+      float best = INFINITY;
+      int best_i = 0;
+#pragma unroll
+      for (int c = 0; c < 32; ++c) {
+        if (c < k) {
+          const float dist = cn[c] - 2.0f * __uint_as_float(r0[c]);
+          if (dist < best) { best = dist; best_i = c; }          // ascending c: lowest index wins ties
+        }
+      }
+#pragma unroll
+      for (int c = 0; c < 32; ++c) {
+        if (32 + c < k) {
+          const float dist = cn[32 + c] - 2.0f * __uint_as_float(r1[c]);
+          if (dist < best) { best = dist; best_i = 32 + c; }
+        }
+      }
+      const int tok = (tile0 + i) * kTcTok + warp * 32 + lane;
+      if (tok < S) labels[(size_t)bh * S + tok] = best_i;
+    }
+    tc_fence_before();
+    // every thread has read this tile's TMEM buffer before tile i + 2 is multiplied into it; a given-up wait ends
+    // the loop for all threads together
+    if (__syncthreads_or(all_ok ? 0 : 1)) break;
   }
   tc_fence_before();
   __syncthreads();
   if (warp == 0) {
+    if (*abort_flag && lane == 0) {
+      // give in-flight bulk copies a bounded time to land before the CTA retires
+      const long long t0 = wall_ns();
+      while (wall_ns() - t0 < 1000000ll) { }
+    }
+    __syncwarp();
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 64;" ::"r"(tmem) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 128;" ::"r"(tmem) : "memory");
   }
 }
 
@@ -162,11 +220,12 @@ template <int D>
 int launch_assign(const CUtensorMap& mx, const CUtensorMap& mc, int BH, int S, int H, int k, const float* cnorm,
                   int32_t* labels, cudaStream_t st) {
   constexpr int NP = D / 64;
-  const int smem_bytes = NP * (kTcTok * 128 + 3 * kTcCen * 128) + 64 + 1024;
+  const int smem_bytes = NP * (2 * kTcTok * 128 + 3 * kTcCen * 128) + 64;
   auto kern = assign_tc_kernel<D>;
   LBFQ_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
   const int ntile = (S + kTcTok - 1) / kTcTok;
-  kern<<<BH * ntile, 128, smem_bytes, st>>>(mx, mc, S, H, k, cnorm, labels);
+  const int per_bh = (ntile + kTcTiles - 1) / kTcTiles;
+  kern<<<BH * per_bh, 128, smem_bytes, st>>>(mx, mc, S, H, k, cnorm, labels);
   return check_launch("kmeans assign (tensor cores)");
 }
 
