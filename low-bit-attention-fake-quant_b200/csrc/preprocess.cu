@@ -9,7 +9,10 @@
 // D, one read of the source per pass, means kept in fp32 and the centred
 // values rounded once into the input dtype exactly as the reference stores them.
 
+#include <cstdlib>
+
 #include "common.cuh"
+#include "qm_corr_tc.h"
 
 namespace lbfq {
 
@@ -523,6 +526,10 @@ extern "C" int lbfq_qm_corr(const float* qm, const void* k_smooth, int dtype, in
     fill_kernel<<<grid_for((size_t)B * H * G, 256), 256, 0, st>>>(rowmax, (size_t)B * H * G, -INFINITY);
     if (int rc = check_launch("fill")) return rc;
   }
+  // BF16 keys take the tensor-core kernel; LBFQ_QM_CORR_FFMA=1 keeps the FP32 FFMA kernel (the cross-check)
+  const char* force_ffma = getenv("LBFQ_QM_CORR_FFMA");
+  if (qm_corr_tc_eligible(dtype, D, S, k_smooth) && !(force_ffma && force_ffma[0] == '1'))
+    return qm_corr_tc(qm, k_smooth, B, S, H, D, G, sm_scale, corr, s_pad, rowmax, st);
   const int grid = B * H * ((G + kCT - 1) / kCT) * (s_pad / kCT);
   LBFQ_DISPATCH_DTYPE(dtype, T,
       qm_corr_kernel<T><<<grid, kThreads, 0, st>>>(qm, (const T*)k_smooth, B, S, H, D, G, sm_scale, corr, s_pad, rowmax));

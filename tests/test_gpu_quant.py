@@ -199,3 +199,28 @@ def test_qm_corr_and_rowmax():
     torch.testing.assert_close(rm.cpu(), ref.amax(-1), rtol=1e-5, atol=1e-4)
     est = OA.estimate_rowmax_from_qm_k(qm, ks, block_q=64, sm_scale=0.0884)      # (B,H,G*64) needs S == G*64
     assert est.shape[-1] == 192
+
+
+@pytest.mark.parametrize("S,G,D", [(200, 3, 128), (2304, 9, 128), (4096, 130, 64), (1000, 5, 64)])
+def test_qm_corr_tensor_core_kernel_agrees_with_fp32_kernel(S, G, D, monkeypatch):
+    """BF16 keys take the tensor-core kernel (group means split into three BF16 pieces: exact products, FP32 sums);
+    the FP32 FFMA kernel is the cross-check. More than 128 groups span two CTAs along the group axis; a ragged last
+    key tile and the zero-filled columns up to ``s_pad`` are covered."""
+    torch.manual_seed(S + G)
+    qm = torch.randn(2, G, 3, D, device=DEV)
+    ks = (torch.randn(2, S, 3, D, device=DEV) * 2).bfloat16()
+    s_pad = (S + 63) // 64 * 64
+    monkeypatch.delenv("LBFQ_QM_CORR_FFMA", raising=False)
+    c_tc, r_tc = qm_corr(qm, ks, sm_scale=0.0884, s_pad=s_pad, want_rowmax=True)
+    c_tc2, _ = qm_corr(qm, ks, sm_scale=0.0884, s_pad=s_pad)
+    assert torch.equal(c_tc, c_tc2)                                            # reproducible
+    monkeypatch.setenv("LBFQ_QM_CORR_FFMA", "1")
+    c_ff, r_ff = qm_corr(qm, ks, sm_scale=0.0884, s_pad=s_pad, want_rowmax=True)
+    ref = torch.einsum("bghd,bshd->bhgs", qm.double(), ks.double()) * 0.0884
+    assert float(c_tc[..., S:].abs().sum()) == 0.0
+    err_tc = (c_tc[..., :S].double() - ref).abs().max().item()
+    err_ff = (c_ff[..., :S].double() - ref).abs().max().item()
+    assert err_tc <= max(2.0 * err_ff, 1e-5), (err_tc, err_ff)                  # as accurate as the FP32 kernel
+    torch.testing.assert_close(c_tc, c_ff, rtol=1e-5, atol=2e-5)
+    torch.testing.assert_close(r_tc, c_tc[..., :S].amax(-1), rtol=0, atol=0)   # the row max is the max of what was stored
+    torch.testing.assert_close(r_tc, r_ff, rtol=1e-5, atol=2e-5)
