@@ -345,15 +345,13 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       // ---- P = exp2(dot * c - m + off), l += sum(P) (attention_triton.py:219-326) ----
       // masked columns hold -inf, so their exp2 is exactly 0 without a select
       // two columns per instruction: fma.rn.f32x2 / add.rn.f32x2 round each half exactly like the scalar forms.
-      // Without a score bias: exp2(dot * c + (off - m)). With one: exp2((score - m) * log2e + off), the
-      // reference's own sequence.
-      const float bias = NAT ? -m_new : p_off - m_new;
+      // Without a score bias: exp2(dot * c + (off - m)), max in the log2 domain. With scores in their own units:
+      // exp2(score * log2e + (off - m * log2e)), the reference's (score - m) * log2e + off contracted into one FMA.
+      const float bias = NAT ? fmaf(-m_new, kLog2e, p_off) : p_off - m_new;
       const float2 c2 = make_float2(NAT ? kLog2e : c, NAT ? kLog2e : c);
-      const float2 bias2 = make_float2(bias, bias), off2 = make_float2(p_off, p_off);
+      const float2 bias2 = make_float2(bias, bias);
       auto arg = [&](uint32_t x0, uint32_t x1) -> float2 {
-        const float2 v = make_float2(__uint_as_float(x0), __uint_as_float(x1));
-        if constexpr (NAT) return __ffma2_rn(__fadd2_rn(v, bias2), c2, off2);
-        else return __ffma2_rn(v, c2, bias2);
+        return __ffma2_rn(make_float2(__uint_as_float(x0), __uint_as_float(x1)), c2, bias2);
       };
       float2 psa = make_float2(0.f, 0.f), psb = make_float2(0.f, 0.f);
       uint32_t pk[PW];
@@ -436,10 +434,10 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
             fill_max = fmaxf(fill_max, x_oth[BUF][2 * SM::kXch]);
           }
-          pmax = skip ? fill_max : ex2(fmaf(bmax - m_new, kLog2e, p_off));
+          pmax = skip ? fill_max : ex2(fmaf(bmax, kLog2e, bias));
         }
       } else if constexpr (PK != 0) {
-        if constexpr (CORR) pmax = ex2(fmaf(bmax - m_new, kLog2e, p_off));
+        if constexpr (CORR) pmax = ex2(fmaf(bmax, kLog2e, bias));
         else pmax = ex2(fmaf(bmax_raw, c, bias));
       }
       if constexpr (PK != 0) {
