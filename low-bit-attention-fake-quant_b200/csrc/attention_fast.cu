@@ -275,12 +275,15 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         for (int i = 0; i < HB; ++i)
           if (half * HB + i >= tail_valid) mine[i] = 0xff800000u;
       }
+      // three-input max (sm_100): two chains, two columns per instruction
       float bm0 = __uint_as_float(mine[0]), bm1 = __uint_as_float(mine[1]);
+      static_assert((HB - 2) % 4 == 2, "the tail below takes the last two columns");
 #pragma unroll
-      for (int i = 2; i < HB; i += 2) {
-        bm0 = fmaxf(bm0, __uint_as_float(mine[i]));
-        bm1 = fmaxf(bm1, __uint_as_float(mine[i + 1]));
+      for (int i = 2; i + 3 < HB; i += 4) {
+        bm0 = fmax3(bm0, __uint_as_float(mine[i]), __uint_as_float(mine[i + 1]));
+        bm1 = fmax3(bm1, __uint_as_float(mine[i + 2]), __uint_as_float(mine[i + 3]));
       }
+      bm0 = fmax3(bm0, __uint_as_float(mine[HB - 2]), __uint_as_float(mine[HB - 1]));
       // the other half's maximum (a block's two slots alternate, so a slot is rewritten only after the barrier
       // of the next block, when its reader is done with it)
       const float own_max = fmaxf(bm0, bm1);

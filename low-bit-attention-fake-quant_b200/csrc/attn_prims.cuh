@@ -260,6 +260,13 @@ __device__ __forceinline__ uint32_t e4m3_round_scale_bf16x2(float a, float b, fl
   return r;
 }
 
+// max of three (max.f32 with three inputs, sm_100): NaN operands are dropped like fmaxf does
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+
 __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
