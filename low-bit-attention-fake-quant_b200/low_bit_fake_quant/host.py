@@ -82,6 +82,16 @@ def fake_quant_attention_host(
     dev = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
     hc = min(heads_per_chunk, h)
     bounds = [(h0, min(h0 + hc, h)) for h0 in range(0, h, hc)]
+    if len(bounds) > 2 and not (cfg.q_kmeans_k is not None or cfg.v_kmeans_k is not None):
+        # nothing overlaps the last chunk's compute and copy back: taper it (.., hc/2, hc/4, .., 1) so that the tail
+        # of the pipeline is one head long; the k-means passes keep their full chunks
+        h0, h1 = bounds.pop()
+        n = h1 - h0
+        while n > 1:
+            step = (n + 1) // 2
+            bounds.append((h0, h0 + step))
+            h0, n = h0 + step, n - step
+        bounds.append((h0, h1))
     s_out = out.shape[1]
 
     with torch.cuda.device(dev):
