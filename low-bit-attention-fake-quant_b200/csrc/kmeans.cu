@@ -179,6 +179,59 @@ sort_segments_kernel(const int32_t* __restrict__ labels, int S, int k, int32_t* 
   }
 }
 
+// The same sort cut into chunks, for label counts that the assignment kernel has already taken per chunk of
+// `chunk` (= 1024) tokens: one CTA per (slab, chunk) finds where each label's tokens of its chunk start (all smaller
+// labels of the slab, then the same label in the earlier chunks) and ranks its 1024 tokens as above. The order it
+// writes is the same stable order; the slab's work is spread over S / 1024 CTAs instead of one.
+__global__ void __launch_bounds__(1024)
+sort_chunks_kernel(const int32_t* __restrict__ labels, const int32_t* __restrict__ hist, int S, int k, int nchunk,
+                   int32_t* __restrict__ order32, int32_t* __restrict__ seg) {
+  __shared__ int total[kSortMaxK];
+  __shared__ int before[kSortMaxK];
+  __shared__ int offsets[kSortMaxK];
+  __shared__ int wc[32][kSortMaxK];               // per warp and label: count, then start position
+  const int chunk = blockIdx.x % nchunk;
+  const size_t bh = blockIdx.x / nchunk;
+  const int32_t* lab = labels + bh * S;
+  int32_t* ord = order32 + bh * S;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int i = threadIdx.x; i < 32 * kSortMaxK; i += blockDim.x) (&wc[0][0])[i] = 0;
+  if ((int)threadIdx.x < k) {
+    const int32_t* hp = hist + bh * nchunk * kSortMaxK + threadIdx.x;
+    int t = 0, bsum = 0;
+    for (int j = 0; j < nchunk; ++j) {
+      const int c = hp[(size_t)j * kSortMaxK];
+      if (j < chunk) bsum += c;
+      t += c;
+    }
+    total[threadIdx.x] = t;
+    before[threadIdx.x] = bsum;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int run = 0;
+    for (int c = 0; c < k; ++c) {
+      offsets[c] = run + before[c];
+      if (chunk == 0) seg[bh * (k + 1) + c] = run;
+      run += total[c];
+    }
+    if (chunk == 0) seg[bh * (k + 1) + k] = run;
+  }
+  const int i = chunk * 1024 + (int)threadIdx.x;
+  const bool valid = i < S;
+  const int lbl = valid ? lab[i] : -1;
+  const unsigned peers = __match_any_sync(0xffffffffu, lbl);
+  const int rank = __popc(peers & ((1u << lane) - 1u));
+  if (valid && rank == 0) wc[warp][lbl] = __popc(peers);
+  __syncthreads();
+  if ((int)threadIdx.x < k) {                               // exclusive scan over the warps, in token order
+    int run = offsets[threadIdx.x];
+    for (int w = 0; w < 32; ++w) { const int c = wc[w][threadIdx.x]; wc[w][threadIdx.x] = run; run += c; }
+  }
+  __syncthreads();
+  if (valid) ord[wc[warp][lbl] + rank] = i;
+}
+
 // the same sort for more labels than the shared-memory tables above hold: one warp per label scans the slab
 __global__ void __launch_bounds__(1024)
 sort_segments_scan_kernel(const int32_t* __restrict__ labels, int S, int k, int32_t* __restrict__ order32,
@@ -278,7 +331,7 @@ segment_mean_kernel(const T* __restrict__ x, int S, int H, int D, int k, const i
 }
 
 struct KmScratch {
-  float* cent; float* cnorm; int32_t* order32; int32_t* seg; void* split;
+  float* cent; float* cnorm; int32_t* order32; int32_t* seg; void* split; int32_t* hist;
 };
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 static size_t scratch_layout(int BH, int S, int D, int k, uint8_t* base, KmScratch* out) {
@@ -289,7 +342,9 @@ static size_t scratch_layout(int BH, int S, int D, int k, uint8_t* base, KmScrat
   uint8_t* p2 = take((size_t)BH * S * 4);
   uint8_t* p3 = take((size_t)BH * (k + 1) * 4);
   uint8_t* p4 = take(kmeans_tc_split_bytes(BH, D));       // BF16 pieces of the centroids (tensor-core assignment)
-  if (out) out->split = p4;
+  const size_t nchunk = ((size_t)S + kmeans_tc_chunk_tokens() - 1) / kmeans_tc_chunk_tokens();
+  uint8_t* p5 = take((size_t)BH * nchunk * kSortMaxK * 4);   // per-chunk label counts from the tensor-core assignment
+  if (out) { out->split = p4; out->hist = (int32_t*)p5; }
   if (out) { out->cent = (float*)p0; out->cnorm = (float*)p1; out->order32 = (int32_t*)p2; out->seg = (int32_t*)p3; }
   return off;
 }
@@ -326,14 +381,18 @@ extern "C" int lbfq_kmeans_labels(const void* x, int dtype, int B, int S, int H,
   const bool tc = kmeans_tc_eligible(dtype, D, k) && !(force_ffma && force_ffma[0] == '1');
   for (int it = 0; it < iters; ++it) {
     if (tc) {
-      if (int rc = kmeans_tc_assign(x, B, S, H, D, k, sc.cent, sc.cnorm, sc.split, labels, st)) return rc;
+      // the counts are only wanted when a sort follows (not after the last assignment)
+      if (int rc = kmeans_tc_assign(x, B, S, H, D, k, sc.cent, sc.cnorm, sc.split, labels, it + 1 < iters ? sc.hist : nullptr, st)) return rc;
     } else {
       LBFQ_DISPATCH_DTYPE(dtype, T,
           assign_kernel<T><<<BH * ntile, kThreads, 0, st>>>((const T*)x, S, H, D, k, sc.cent, sc.cnorm, labels));
     }
     if (int rc = check_launch("kmeans assign")) return rc;
     if (it + 1 == iters) break;                     // labels of the last assignment are the result
-    if (k <= kSortMaxK) sort_segments_kernel<<<BH, 1024, 0, st>>>(labels, S, k, sc.order32, sc.seg);
+    if (tc && kmeans_tc_chunk_tokens() == 1024) {
+      const int nchunk = (S + 1023) / 1024;
+      sort_chunks_kernel<<<BH * nchunk, 1024, 0, st>>>(labels, sc.hist, S, k, nchunk, sc.order32, sc.seg);
+    } else if (k <= kSortMaxK) sort_segments_kernel<<<BH, 1024, 0, st>>>(labels, S, k, sc.order32, sc.seg);
     else sort_segments_scan_kernel<<<BH, 1024, 2 * k * sizeof(int), st>>>(labels, S, k, sc.order32, sc.seg);
     if (int rc = check_launch("kmeans sort")) return rc;
     LBFQ_DISPATCH_DTYPE(dtype, T,

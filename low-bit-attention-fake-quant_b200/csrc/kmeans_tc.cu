@@ -54,7 +54,7 @@ constexpr int kTcTiles = 8;
 template <int D>
 __global__ void __launch_bounds__(128)
 assign_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_c, int S, int H, int k,
-                 const float* __restrict__ cnorm, int32_t* __restrict__ labels) {
+                 const float* __restrict__ cnorm, int32_t* __restrict__ labels, int32_t* __restrict__ hist) {
   constexpr int NP = D / 64;                         // 64-channel panels (one 128-byte swizzle row each)
   constexpr int kA = kTcTok * 128;                   // bytes per token panel
   constexpr int kB = 3 * kTcCen * 128;               // bytes per centroid panel (three pieces)
@@ -69,6 +69,9 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
   auto bar_done = [&](int buf) { return sbase + offBar + 16u + 8u * buf; };    // MMAs of the tile in this buffer done
   volatile int* misc = (volatile int*)(smem + offBar + 32);       // [0] tmem base, [1] abort
   volatile int* abort_flag = misc + 1;
+  // labels of this CTA's tokens, counted for the sort that follows (kept in the dynamic area: a static array would
+  // push the 1 KB-aligned dynamic base up and cost the second CTA per SM)
+  int* cnt = reinterpret_cast<int*>(smem + offBar + 64);
 
   const int ntile = (S + kTcTok - 1) / kTcTok;
   const int per_bh = (ntile + kTcTiles - 1) / kTcTiles;
@@ -89,6 +92,7 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
     return;
   }
 
+  if (threadIdx.x < kTcCen) cnt[threadIdx.x] = 0;
   if (threadIdx.x == 0) {
     mbar_init(bar_full(0), 1);
     mbar_init(bar_full(1), 1);
@@ -183,7 +187,10 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
         }
       }
       const int tok = (tile0 + i) * kTcTok + warp * 32 + lane;
-      if (tok < S) labels[(size_t)bh * S + tok] = best_i;
+      if (tok < S) {
+        labels[(size_t)bh * S + tok] = best_i;
+        atomicAdd(&cnt[best_i], 1);
+      }
     }
     tc_fence_before();
     // every thread has read this tile's TMEM buffer before tile i + 2 is multiplied into it; a given-up wait ends
@@ -192,6 +199,9 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
   }
   tc_fence_before();
   __syncthreads();
+  // per-label counts of this CTA's chunk of kTcTiles * 128 tokens: (bh, chunk, 64)
+  if (hist != nullptr && threadIdx.x < kTcCen)
+    hist[((size_t)bh * per_bh + tile0 / kTcTiles) * kTcCen + threadIdx.x] = cnt[threadIdx.x];
   if (warp == 0) {
     if (*abort_flag && lane == 0) {
       // give in-flight bulk copies a bounded time to land before the CTA retires
@@ -218,14 +228,14 @@ PFN_cuTensorMapEncodeTiled_v12000 encoder() {
 
 template <int D>
 int launch_assign(const CUtensorMap& mx, const CUtensorMap& mc, int BH, int S, int H, int k, const float* cnorm,
-                  int32_t* labels, cudaStream_t st) {
+                  int32_t* labels, int32_t* hist, cudaStream_t st) {
   constexpr int NP = D / 64;
-  const int smem_bytes = NP * (2 * kTcTok * 128 + 3 * kTcCen * 128) + 64;
+  const int smem_bytes = NP * (2 * kTcTok * 128 + 3 * kTcCen * 128) + 64 + kTcCen * 4;
   auto kern = assign_tc_kernel<D>;
   LBFQ_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
   const int ntile = (S + kTcTok - 1) / kTcTok;
   const int per_bh = (ntile + kTcTiles - 1) / kTcTiles;
-  kern<<<BH * per_bh, 128, smem_bytes, st>>>(mx, mc, S, H, k, cnorm, labels);
+  kern<<<BH * per_bh, 128, smem_bytes, st>>>(mx, mc, S, H, k, cnorm, labels, hist);
   return check_launch("kmeans assign (tensor cores)");
 }
 
@@ -233,10 +243,12 @@ int launch_assign(const CUtensorMap& mx, const CUtensorMap& mc, int BH, int S, i
 
 bool kmeans_tc_eligible(int dtype, int D, int k) { return dtype == LBFQ_BF16 && (D == 64 || D == 128) && k <= kTcCen; }
 
+int kmeans_tc_chunk_tokens() { return kTcTiles * kTcTok; }
+
 size_t kmeans_tc_split_bytes(int BH, int D) { return (size_t)BH * 3 * kTcCen * D * sizeof(__nv_bfloat16); }
 
 int kmeans_tc_assign(const void* x, int B, int S, int H, int D, int k, const float* cent, const float* cnorm,
-                     void* split, int32_t* labels, cudaStream_t st) {
+                     void* split, int32_t* labels, int32_t* hist, cudaStream_t st) {
   const int BH = B * H;
   const size_t total = (size_t)BH * kTcCen * D;
   int g = (int)((total + 255) / 256);
@@ -269,8 +281,8 @@ int kmeans_tc_assign(const void* x, int B, int S, int H, int D, int k, const flo
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     LBFQ_REQUIRE(r == CUDA_SUCCESS, LBFQ_ERR_CUDA, "cuTensorMapEncodeTiled (centroids) failed with code %d", (int)r);
   }
-  if (D == 128) return launch_assign<128>(mx, mc, BH, S, H, k, cnorm, labels, st);
-  return launch_assign<64>(mx, mc, BH, S, H, k, cnorm, labels, st);
+  if (D == 128) return launch_assign<128>(mx, mc, BH, S, H, k, cnorm, labels, hist, st);
+  return launch_assign<64>(mx, mc, BH, S, H, k, cnorm, labels, hist, st);
 }
 
 }  // namespace lbfq
