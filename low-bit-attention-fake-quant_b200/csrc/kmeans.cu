@@ -264,18 +264,26 @@ sort_segments_scan_kernel(const int32_t* __restrict__ labels, int S, int k, int3
   }
 }
 
-// one CTA per (slab, cluster): mean of the cluster's tokens in sorted order
+// Cluster means in two steps, so that one large cluster does not keep a single CTA busy while the rest of the GPU
+// idles: up to kMeanParts CTAs per (slab, cluster) each add a contiguous part of the cluster's sorted rows (fixed order
+// inside a part), then one CTA adds the parts in order, divides and takes the squared norm. Bit-reproducible.
+constexpr int kMeanParts = 8;
+// many small clusters need no splitting (and their partial sums would be large)
+static inline int mean_parts(int k) { return k <= 256 ? kMeanParts : 1; }
+
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
-segment_mean_kernel(const T* __restrict__ x, int S, int H, int D, int k, const int32_t* __restrict__ order32,
-                    const int32_t* __restrict__ seg, float* __restrict__ cent, float* __restrict__ cnorm) {
+segment_part_sums_kernel(const T* __restrict__ x, int S, int H, int D, int k, const int32_t* __restrict__ order32,
+                         const int32_t* __restrict__ seg, float* __restrict__ psum, int parts) {
   __shared__ float buf[kThreads / 8][128 + 1];
-  __shared__ float red[4];
-  const int c = blockIdx.x % k;
-  const int bh = blockIdx.x / k;
+  const int part = blockIdx.x % parts;
+  const int c = (blockIdx.x / parts) % k;
+  const int bh = blockIdx.x / (parts * k);
   const int b = bh / H, h = bh % H;
-  const int beg = seg[(size_t)bh * (k + 1) + c], end = seg[(size_t)bh * (k + 1) + c + 1];
-  if (end == beg) return;                           // empty cluster keeps centroid and norm
+  const int cbeg = seg[(size_t)bh * (k + 1) + c], cend = seg[(size_t)bh * (k + 1) + c + 1];
+  const int len = cend - cbeg;
+  const int beg = cbeg + (int)(((int64_t)len * part) / parts);
+  const int end = cbeg + (int)(((int64_t)len * (part + 1)) / parts);
   const int tpr = D / 8, rpi = kThreads / tpr;
   const int tr = threadIdx.x / tpr, d0 = (threadIdx.x % tpr) * 8;
   float acc[8];
@@ -317,21 +325,36 @@ segment_mean_kernel(const T* __restrict__ x, int S, int H, int D, int k, const i
 #pragma unroll
   for (int i = 0; i < 8; ++i) buf[tr][d0 + i] = acc[i];
   __syncthreads();
-  float v = 0.f;
   if (threadIdx.x < D) {
     float s = 0.f;
     for (int r = 0; r < rpi; ++r) s += buf[r][threadIdx.x];
-    v = __fdiv_rn(s, (float)(end - beg));
-    cent[((size_t)bh * k + c) * D + threadIdx.x] = v;
+    psum[(((size_t)bh * k + c) * parts + part) * D + threadIdx.x] = s;     // zero for an empty part
   }
-  float s2 = warp_sum(v * v);
-  if ((threadIdx.x & 31) == 0 && threadIdx.x < 128) red[threadIdx.x >> 5] = s2;
+}
+
+__global__ void __launch_bounds__(128)
+segment_mean_from_parts_kernel(const float* __restrict__ psum, const int32_t* __restrict__ seg, int D, int k, int parts,
+                               float* __restrict__ cent, float* __restrict__ cnorm) {
+  __shared__ float red[4];
+  const int c = blockIdx.x % k;
+  const size_t bh = blockIdx.x / k;
+  const int n = seg[bh * (k + 1) + c + 1] - seg[bh * (k + 1) + c];
+  if (n == 0) return;                               // empty cluster keeps centroid and norm
+  float v = 0.f;
+  if (threadIdx.x < D) {
+    float s = 0.f;
+    for (int p = 0; p < parts; ++p) s += psum[((bh * k + c) * parts + p) * D + threadIdx.x];
+    v = __fdiv_rn(s, (float)n);
+    cent[(bh * k + c) * D + threadIdx.x] = v;
+  }
+  const float s2 = warp_sum(v * v);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s2;
   __syncthreads();
-  if (threadIdx.x == 0) cnorm[(size_t)bh * k + c] = red[0] + red[1] + red[2] + red[3];
+  if (threadIdx.x == 0) cnorm[bh * k + c] = red[0] + red[1] + red[2] + red[3];
 }
 
 struct KmScratch {
-  float* cent; float* cnorm; int32_t* order32; int32_t* seg; void* split; int32_t* hist;
+  float* cent; float* cnorm; int32_t* order32; int32_t* seg; void* split; int32_t* hist; float* psum;
 };
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 static size_t scratch_layout(int BH, int S, int D, int k, uint8_t* base, KmScratch* out) {
@@ -344,7 +367,8 @@ static size_t scratch_layout(int BH, int S, int D, int k, uint8_t* base, KmScrat
   uint8_t* p4 = take(kmeans_tc_split_bytes(BH, D));       // BF16 pieces of the centroids (tensor-core assignment)
   const size_t nchunk = ((size_t)S + kmeans_tc_chunk_tokens() - 1) / kmeans_tc_chunk_tokens();
   uint8_t* p5 = take((size_t)BH * nchunk * kSortMaxK * 4);   // per-chunk label counts from the tensor-core assignment
-  if (out) { out->split = p4; out->hist = (int32_t*)p5; }
+  uint8_t* p6 = take((size_t)BH * k * mean_parts(k) * D * 4);   // partial sums of the cluster means
+  if (out) { out->split = p4; out->hist = (int32_t*)p5; out->psum = (float*)p6; }
   if (out) { out->cent = (float*)p0; out->cnorm = (float*)p1; out->order32 = (int32_t*)p2; out->seg = (int32_t*)p3; }
   return off;
 }
@@ -396,7 +420,9 @@ extern "C" int lbfq_kmeans_labels(const void* x, int dtype, int B, int S, int H,
     else sort_segments_scan_kernel<<<BH, 1024, 2 * k * sizeof(int), st>>>(labels, S, k, sc.order32, sc.seg);
     if (int rc = check_launch("kmeans sort")) return rc;
     LBFQ_DISPATCH_DTYPE(dtype, T,
-        segment_mean_kernel<T><<<BH * k, kThreads, 0, st>>>((const T*)x, S, H, D, k, sc.order32, sc.seg, sc.cent, sc.cnorm));
+        segment_part_sums_kernel<T><<<BH * k * mean_parts(k), kThreads, 0, st>>>((const T*)x, S, H, D, k, sc.order32, sc.seg, sc.psum, mean_parts(k)));
+    if (int rc = check_launch("kmeans part sums")) return rc;
+    segment_mean_from_parts_kernel<<<BH * k, 128, 0, st>>>(sc.psum, sc.seg, D, k, mean_parts(k), sc.cent, sc.cnorm);
     if (int rc = check_launch("kmeans update")) return rc;
   }
   return LBFQ_OK;
