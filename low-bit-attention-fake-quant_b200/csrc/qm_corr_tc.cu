@@ -156,7 +156,10 @@ qm_corr_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const float* __restr
   const int key_row = (warp & 3) * 32 + lane;         // TMEM lane == key within the tile
   const int half = warp >> 2;                         // which 64 of the CTA's groups this warp stores
   const int gbase = g0 + half * 64;
-  int run[2] = {float_key(-INFINITY), float_key(-INFINITY)};     // lane l keeps the max of groups gbase + l, + 32 + l
+  // running max of this thread's key row over the CTA's tiles, one register per group; the 128 rows meet at the end
+  float run[64];
+#pragma unroll
+  for (int j = 0; j < 64; ++j) run[j] = -INFINITY;
   for (int i = 0; i < n_tiles; ++i) {
     const int buf = i & 1;
     // the next tile's MMAs first (its TMEM buffer was read out two tiles ago, before the last barrier)
@@ -176,15 +179,14 @@ qm_corr_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const float* __restr
       const int n = (tile0 + i) * kKeys + key_row;
       const bool n_real = n < S, n_store = n < s_pad;
       float* out = corr + ((size_t)bh * G + gbase) * s_pad + n;
+      const int ng = min(64, G - gbase);               // warp-uniform
 #pragma unroll
       for (int j = 0; j < 64; ++j) {
-        if (gbase + j < G) {                           // warp-uniform
+        if (j < ng) {
           const float v = __uint_as_float(j < 32 ? r0[j & 31] : r1[j & 31]) * sm_scale;
-          if (n_store) out[(size_t)j * s_pad] = n_real ? v : 0.f;
-          if (rowmax != nullptr) {
-            const int m = __reduce_max_sync(0xffffffffu, float_key(n_real ? v : -INFINITY));
-            if (lane == (j & 31)) run[j >> 5] = max(run[j >> 5], m);
-          }
+          if (n_store) *out = n_real ? v : 0.f;
+          if (n_real) run[j] = fmaxf(run[j], v);
+          out += s_pad;
         }
       }
     }
@@ -194,11 +196,13 @@ qm_corr_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const float* __restr
     if (__syncthreads_or(all_ok ? 0 : 1)) break;
   }
   if (rowmax != nullptr && *abort_flag == 0) {
+    // the warp's 32 rows meet through redux.sync.max on an order-preserving integer image of the floats
 #pragma unroll
-    for (int jj = 0; jj < 2; ++jj) {
-      const int g = gbase + jj * 32 + lane;
-      const float m = key_float(run[jj]);
-      if (g < G && m > -INFINITY) atomic_max_f32(rowmax + (size_t)bh * G + g, m);
+    for (int j = 0; j < 64; ++j) {
+      if (gbase + j < G) {                             // warp-uniform
+        const float m = key_float(__reduce_max_sync(0xffffffffu, float_key(run[j])));
+        if (lane == 0 && m > -INFINITY) atomic_max_f32(rowmax + (size_t)bh * G + gbase + j, m);
+      }
     }
   }
   tc_fence_before();
