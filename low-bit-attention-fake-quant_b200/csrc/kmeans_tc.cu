@@ -149,7 +149,10 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
     }
     issue_mma(0);
   }
-  const float* cn = cnorm + (size_t)bh * k;
+  // |c|^2 of the slab's centroids, once per CTA; +inf above k, so that the argmin needs no bound check
+  float cn[kTcCen];
+#pragma unroll
+  for (int c = 0; c < kTcCen; ++c) cn[c] = c < k ? cnorm[(size_t)bh * k + c] : INFINITY;
   for (int i = 0; i < n; ++i) {
     const int buf = i & 1;
     // the next tile's MMAs first (its TMEM buffer was read out two tiles ago, before the last barrier)
@@ -174,17 +177,13 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
       int best_i = 0;
 #pragma unroll
       for (int c = 0; c < 32; ++c) {
-        if (c < k) {
-          const float dist = cn[c] - 2.0f * __uint_as_float(r0[c]);
-          if (dist < best) { best = dist; best_i = c; }          // ascending c: lowest index wins ties
-        }
+        const float dist = cn[c] - 2.0f * __uint_as_float(r0[c]);
+        if (dist < best) { best = dist; best_i = c; }            // ascending c: lowest index wins ties
       }
 #pragma unroll
       for (int c = 0; c < 32; ++c) {
-        if (32 + c < k) {
-          const float dist = cn[32 + c] - 2.0f * __uint_as_float(r1[c]);
-          if (dist < best) { best = dist; best_i = 32 + c; }
-        }
+        const float dist = cn[32 + c] - 2.0f * __uint_as_float(r1[c]);
+        if (dist < best) { best = dist; best_i = 32 + c; }
       }
       const int tok = (tile0 + i) * kTcTok + warp * 32 + lane;
       if (tok < S) {
