@@ -309,11 +309,14 @@ def _fake_quant_attention_p_requant_reference_operands(q_work, k_work, v_work, q
     if cfg.rowmax_mode == "qm_k" and qm is None:
         raise ValueError("rowmax_mode='qm_k' requires smoothing='full' so qm exists")
     to_bh = lambda t: t.permute(0, 2, 1, 3).contiguous()
-    rowmax_est = None
-    if qm is not None and cfg.rowmax_mode == "qm_k":
-        _, rowmax_g = qm_corr(qm, k_work.to(torch.bfloat16), sm_scale=sm_scale, s_pad=_round_up(k_work.shape[1], 128),
-                              want_rowmax=True)
-        rowmax_est = rowmax_g.repeat_interleave(cfg.q_smooth_block_size, dim=2).contiguous()
+    rowmax_est = corr = None
+    if qm is not None:
+        # one product serves the score bias and the row-max estimate; the launcher takes it instead of forming it again
+        want_est = cfg.rowmax_mode == "qm_k"
+        corr, rowmax_g = qm_corr(qm, k_work.to(torch.bfloat16), sm_scale=sm_scale, s_pad=_round_up(k_work.shape[1], 128),
+                                 want_rowmax=want_est)
+        if want_est:
+            rowmax_est = rowmax_g.repeat_interleave(cfg.q_smooth_block_size, dim=2).contiguous()
     p_mode = cfg.p_quant
     if p_mode == "auto":
         p_mode = "mx" if cfg.v_quant == "mxfp8" else "elementwise"
@@ -326,7 +329,7 @@ def _fake_quant_attention_p_requant_reference_operands(q_work, k_work, v_work, q
         k_smooth_bhsd=to_bh(k_work.to(torch.bfloat16)) if qm is not None else None,
         qm_bhgd=to_bh(qm) if qm is not None else None,
         q_smooth_block=cfg.q_smooth_block_size if qm is not None else 0,
-        p_quant_mode=p_mode, p_mx_block_n=p_mx_block_n, rowmax_est_bhs=rowmax_est, _out_fp32=out_fp32_exact)
+        p_quant_mode=p_mode, p_mx_block_n=p_mx_block_n, rowmax_est_bhs=rowmax_est, _out_fp32=out_fp32_exact, _corr=corr)
     o = o.permute(0, 2, 1, 3).contiguous()                    # (B, S, H, D)
     o = o if out_fp32_exact else o.to(out_dtype)
     if q_kmeans is not None:

@@ -278,6 +278,7 @@ def fake_quant_attention_triton(
     blasst_uta_bins: int = 16,
     return_blasst_stats: bool = False,
     _out_fp32: bool = False,
+    _corr: Optional[torch.Tensor] = None,
 ):
     """The reference's direct-launch entry (src/low_bit_fake_quant/attention_triton.py:410-671), same signature.
 
@@ -322,8 +323,11 @@ def fake_quant_attention_triton(
                              "and an integer multiple of block_m")
         if M % q_smooth_block != 0:
             raise ValueError(f"S ({M}) must be divisible by q_smooth_block ({q_smooth_block})")
-        corr, _ = qm_corr(qm_bhgd.permute(0, 2, 1, 3).contiguous().float(), k_smooth_bhsd.permute(0, 2, 1, 3).contiguous(),
-                          sm_scale=sm_scale, s_pad=n_pad, want_rowmax=False)
+        if _corr is not None and tuple(_corr.shape) == (B, H, qm_bhgd.shape[2], n_pad):
+            corr = _corr                                  # the caller has formed the product already
+        else:
+            corr, _ = qm_corr(qm_bhgd.permute(0, 2, 1, 3).contiguous().float(), k_smooth_bhsd.permute(0, 2, 1, 3).contiguous(),
+                              sm_scale=sm_scale, s_pad=n_pad, want_rowmax=False)
 
     def pad_rows(t, rows):       # (B, H, S, D) -> (B, H, rows, D), zero rows appended
         if t.shape[2] == rows:
