@@ -47,12 +47,16 @@ __global__ void split_centroids_kernel(const float* __restrict__ cent, int BH, i
 }
 
 // One CTA walks kTcTiles consecutive 128-token tiles of one (b, h): the centroid pieces are loaded once, the token
-// tiles go through two shared-memory buffers and two 64-column TMEM buffers, so that the TMA load of tile i + 2 and
-// the MMAs of tile i + 1 run while the threads take the argmin of tile i.
+// tiles go through two shared-memory buffers and two 64-column TMEM buffers. A producer warp (one thread) issues the
+// TMA loads two tiles ahead and the MMAs; four consumer warps take the argmin of a tile while the next one is being
+// multiplied. No CTA-wide barrier inside the loop: a TMEM buffer is handed back through an mbarrier the 128
+// consumer threads arrive on, a shared-memory buffer through the MMAs' own commit.
 constexpr int kTcTiles = 8;
+constexpr int kTcWarps = 4;                        // consumer warps (128 tokens); one more warp loads and issues
+constexpr int kTcThreads = (kTcWarps + 1) * 32;
 
 template <int D>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(kTcThreads)
 assign_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_c, int S, int H, int k,
                  const float* __restrict__ cnorm, int32_t* __restrict__ labels, int32_t* __restrict__ hist) {
   constexpr int NP = D / 64;                         // 64-channel panels (one 128-byte swizzle row each)
@@ -67,7 +71,8 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
   const uint32_t offA = 0, offB = 2 * NP * kA, offBar = offB + NP * kB;
   auto bar_full = [&](int buf) { return sbase + offBar + 8u * buf; };          // token tile (and, first, centroids) landed
   auto bar_done = [&](int buf) { return sbase + offBar + 16u + 8u * buf; };    // MMAs of the tile in this buffer done
-  volatile int* misc = (volatile int*)(smem + offBar + 32);       // [0] tmem base, [1] abort
+  auto bar_tfree = [&](int buf) { return sbase + offBar + 32u + 8u * buf; };   // the tile's TMEM buffer has been read out
+  volatile int* misc = (volatile int*)(smem + offBar + 48);       // [0] tmem base, [1] abort
   volatile int* abort_flag = misc + 1;
   // labels of this CTA's tokens, counted for the sort that follows (kept in the dynamic area: a static array would
   // push the 1 KB-aligned dynamic base up and cost the second CTA per SM)
@@ -87,7 +92,7 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
     // never expected; the labels are marked invalid so that the caller's checks see it
     for (int i = 0; i < n; ++i) {
       const int tok = (tile0 + i) * kTcTok + (int)threadIdx.x;
-      if (tok < S) labels[(size_t)bh * S + tok] = -1;
+      if ((int)threadIdx.x < kTcTok && tok < S) labels[(size_t)bh * S + tok] = -1;
     }
     return;
   }
@@ -98,11 +103,13 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
     mbar_init(bar_full(1), 1);
     mbar_init(bar_done(0), 1);
     mbar_init(bar_done(1), 1);
+    mbar_init(bar_tfree(0), kTcWarps * 32);
+    mbar_init(bar_tfree(1), kTcWarps * 32);
     misc[1] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 0) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 128;" ::"r"(sbase + offBar + 32) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 128;" ::"r"(sbase + offBar + 48) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   tc_fence_before();
@@ -138,41 +145,48 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
     return true;
   };
 
-  if (threadIdx.x == 0) {
-    mbar_expect_tx(bar_full(0), NP * (kA + kB));
+  if (warp == kTcWarps) {
+    // ---- producer: TMA loads and MMA issue, one thread ----
+    if (lane == 0) {
+      mbar_expect_tx(bar_full(0), NP * (kA + kB));
 #pragma unroll
-    for (int pn = 0; pn < NP; ++pn) tma_load_3d(sbase + offB + pn * kB, &tm_c, pn * 64, 0, bh, bar_full(0));
-    load_tile(0);
-    if (n > 1) {
-      mbar_expect_tx(bar_full(1), NP * kA);
-      load_tile(1);
+      for (int pn = 0; pn < NP; ++pn) tma_load_3d(sbase + offB + pn * kB, &tm_c, pn * 64, 0, bh, bar_full(0));
+      load_tile(0);
+      if (n > 1) {
+        mbar_expect_tx(bar_full(1), NP * kA);
+        load_tile(1);
+      }
+      for (int i = 0; i < n; ++i) {
+        const int buf = i & 1;
+        // the TMEM buffer is free once every consumer thread has read tile i - 2 out of it
+        if (i >= 2 && !mbar_wait(bar_tfree(buf), (uint32_t)(((i - 2) >> 1) & 1), abort_flag, nullptr, 3)) break;
+        if (!issue_mma(i)) break;
+        if (i + 2 < n) {
+          // the tile's shared-memory buffer is free once its MMAs have completed: refill it two tiles ahead
+          if (!mbar_wait(bar_done(buf), (uint32_t)((i >> 1) & 1), abort_flag, nullptr, 4)) break;
+          mbar_expect_tx(bar_full(buf), NP * kA);
+          load_tile(i + 2);
+        }
+      }
     }
-    issue_mma(0);
-  }
-  // |c|^2 of the slab's centroids, once per CTA; +inf above k, so that the argmin needs no bound check
-  float cn[kTcCen];
+  } else {
+    // ---- consumers: thread == token == TMEM lane ----
+    // |c|^2 of the slab's centroids, once per CTA; +inf above k, so that the argmin needs no bound check
+    float cn[kTcCen];
 #pragma unroll
-  for (int c = 0; c < kTcCen; ++c) cn[c] = c < k ? cnorm[(size_t)bh * k + c] : INFINITY;
-  for (int i = 0; i < n; ++i) {
-    const int buf = i & 1;
-    // the next tile's MMAs first (its TMEM buffer was read out two tiles ago, before the last barrier)
-    if (threadIdx.x == 0 && i + 1 < n) issue_mma(i + 1);
-    __syncwarp();
-    // thread == token == TMEM lane
-    const bool ok = mbar_wait(bar_done(buf), (uint32_t)((i >> 1) & 1), abort_flag, nullptr, 2);
-    const bool all_ok = __all_sync(0xffffffffu, ok);
-    if (threadIdx.x == 0 && ok && i + 2 < n) {         // the tile's shared-memory buffer is free again
-      mbar_expect_tx(bar_full(buf), NP * kA);
-      load_tile(i + 2);
-    }
-    __syncwarp();
-    if (all_ok) {
+    for (int c = 0; c < kTcCen; ++c) cn[c] = c < k ? cnorm[(size_t)bh * k + c] : INFINITY;
+    for (int i = 0; i < n; ++i) {
+      const int buf = i & 1;
+      const bool ok = mbar_wait(bar_done(buf), (uint32_t)((i >> 1) & 1), abort_flag, nullptr, 2);
+      if (!__all_sync(0xffffffffu, ok)) break;           // a given-up wait ends every role's loop
       tc_fence_after();
       const uint32_t trow = tmem + buf * kTcCen + ((uint32_t)(warp * 32) << 16);
       uint32_t r0[32], r1[32];
       LBFQ_TMEM_LD32(r0, trow);
       LBFQ_TMEM_LD32(r1, trow + 32);
       tc_wait_ld();
+      tc_fence_before();
+      mbar_arrive(bar_tfree(buf));                       // the dot products are in registers
       float best = INFINITY;
       int best_i = 0;
 #pragma unroll
@@ -191,10 +205,6 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
         atomicAdd(&cnt[best_i], 1);
       }
     }
-    tc_fence_before();
-    // every thread has read this tile's TMEM buffer before tile i + 2 is multiplied into it; a given-up wait ends
-    // the loop for all threads together
-    if (__syncthreads_or(all_ok ? 0 : 1)) break;
   }
   tc_fence_before();
   __syncthreads();
@@ -234,7 +244,7 @@ int launch_assign(const CUtensorMap& mx, const CUtensorMap& mc, int BH, int S, i
   LBFQ_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
   const int ntile = (S + kTcTok - 1) / kTcTok;
   const int per_bh = (ntile + kTcTiles - 1) / kTcTiles;
-  kern<<<BH * per_bh, 128, smem_bytes, st>>>(mx, mc, S, H, k, cnorm, labels, hist);
+  kern<<<BH * per_bh, kTcThreads, smem_bytes, st>>>(mx, mc, S, H, k, cnorm, labels, hist);
   return check_launch("kmeans assign (tensor cores)");
 }
 
