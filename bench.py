@@ -239,6 +239,9 @@ def main():
                     help="run path B on the reference's own BF16 operands (BF16 MMAs) instead of the FP8 codes; not the headline")
     ap.add_argument("--blasst-lambda", type=float, default=None, help="override the BLASST threshold of a BLASST workload")
     ap.add_argument("--blasst-fill", default=None, help="override the BLASST fill of a BLASST workload (zero, mean_a1.5, uta16_a1.5 ...)")
+    ap.add_argument("--brick", default=None,
+                    help="ts,hs,ws: take the video workload's tokens brick by brick over its (21, 30, 52) grid (the reference's "
+                         "space-time block reorder); the permutation of Q / K / V and of the result is inside the timed step")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     cfg_kwargs, batch = WORKLOADS[args.workload][:2]
@@ -291,7 +294,19 @@ def main():
         args.no_cpu_baseline = True
     lib = L.lib()
 
+    brick_order = None
+    if args.brick is not None:
+        if not args.workload.startswith("wan14b_video"):
+            raise SystemExit("--brick applies to the video workload (tokens on a (t, h, w) grid)")
+        from low_bit_fake_quant.hook import fake_quant_attention_reordered, space_time_block_order
+        bt, bh_, bw = (int(x) for x in args.brick.split(","))
+        gt, gh, gw = VIDEO_GRID
+        args.no_e2e = True                                              # the host-buffer entry has no reorder
+        brick_order = space_time_block_order(gt, gh, gw, ts=bt, hs=bh_, ws=bw, tail=qp.shape[1] - gt * gh * gw, device=dev)
+
     def step(qq, kk, vv):
+        if brick_order is not None:
+            return fake_quant_attention_reordered(qq, kk, vv, cfg, brick_order)[:, :seq]
         if seq_k is not None:
             from low_bit_fake_quant.hook import fake_quant_cross_attention
             return fake_quant_cross_attention(qq, kk, vv, cfg)[:, :seq]
@@ -395,7 +410,10 @@ def main():
                              "oracle port on the host cores"}
         blasst = None
         if cfg.blasst_lambda is not None and cfg.smoothing != "full" and cfg.q_kmeans_k is None and cfg.v_kmeans_k is None:
-            blasst = dict(blasst_skip_ratios(qp, kp, vp, cfg), blasst_lambda=cfg.blasst_lambda, blasst_fill=cfg.blasst_fill)
+            sq, sk_, sv = (qp, kp, vp) if brick_order is None else (x[:, brick_order].contiguous() for x in (qp, kp, vp))
+            blasst = dict(blasst_skip_ratios(sq, sk_, sv, cfg), blasst_lambda=cfg.blasst_lambda, blasst_fill=cfg.blasst_fill)
+            if args.brick is not None:
+                blasst["brick"] = args.brick
         line = {
             "metric": "fused FP8 fake-quant attn TFLOP/s at 40x32760x128", "value": value, "unit": "TFLOP/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,

@@ -65,3 +65,45 @@ def fake_quant_cross_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor
     if cfg is None:
         cfg = QuantConfig()
     return fake_quant_attention(q, k, v, cfg, sm_scale=sm_scale, _cross=True)
+
+
+# --- space-time block order (bench/eval_blasst_quant.py:101-134 of the reference) ---------------------------------
+#
+# Video tokens arrive flattened row-major over a (t, h, w) grid, so 64 consecutive tokens are a thin strip of one
+# row. Grouping the tokens of each (ts, hs, ws) brick together makes every block of queries and keys spatially
+# compact, which is what lets BLASST skip whole blocks for whole groups of rows. The order is a plain permutation
+# applied to Q, K and V alike; the attention output is brought back to the original order afterwards.
+
+def space_time_block_order(t: int, h: int, w: int, *, ts: int, hs: int, ws: int, tail: int = 0,
+                           device: Optional[torch.device] = None) -> torch.Tensor:
+    """Token order, brick by brick (bricks row-major over the grid, tokens row-major inside a brick; bricks cut by
+    the grid's edge keep the tokens they have). ``tail`` tokens beyond the grid stay at the end, in place."""
+    if min(t, h, w, ts, hs, ws) <= 0 or tail < 0:
+        raise ValueError("grid and brick sizes must be positive")
+    tt, hh, ww = torch.meshgrid(torch.arange(t, device=device), torch.arange(h, device=device),
+                                torch.arange(w, device=device), indexing="ij")
+    n_h, n_w = -(-h // hs), -(-w // ws)
+    brick = ((tt // ts) * n_h + hh // hs) * n_w + ww // ws
+    inner = ((tt % ts) * hs + hh % hs) * ws + ww % ws
+    order = torch.argsort((brick * (ts * hs * ws) + inner).reshape(-1), stable=True)
+    if tail > 0:
+        order = torch.cat((order, torch.arange(t * h * w, t * h * w + tail, device=order.device)))
+    return order.contiguous()
+
+
+def fake_quant_attention_reordered(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cfg: Optional[QuantConfig],
+                                   order: torch.Tensor, *, sm_scale: Optional[float] = None) -> torch.Tensor:
+    """``fake_quant_attention`` on the tokens taken in ``order`` (a permutation of range(S), e.g.
+    ``space_time_block_order``), result returned in the original token order. Exact attention does not depend on the
+    order; the fake-quant one does through its per-block scales, and BLASST through which rows share a block."""
+    from .kmeans import apply_kv_permutation
+    b, s, h, _ = q.shape
+    if order.ndim != 1 or order.numel() != s:
+        raise ValueError(f"order must be a permutation of the {s} tokens; got shape {tuple(order.shape)}")
+    order = order.to(device=q.device, dtype=torch.int64)
+    inverse = torch.empty_like(order)
+    inverse[order] = torch.arange(s, device=q.device, dtype=torch.int64)
+    fwd = order.unsqueeze(0).expand(b * h, s).contiguous()
+    out = fake_quant_attention(apply_kv_permutation(q, fwd), apply_kv_permutation(k, fwd), apply_kv_permutation(v, fwd),
+                               cfg, sm_scale=sm_scale)
+    return apply_kv_permutation(out, inverse.unsqueeze(0).expand(b * h, s).contiguous())

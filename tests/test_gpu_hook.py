@@ -92,3 +92,25 @@ def test_cross_attention_errors():
                                                         q_kmeans_k=None, p_requant=False))
     with pytest.raises(ValueError, match="shapes must match"):
         fq.fake_quant_attention(q, k, k, cfg)                 # the reference's entry keeps its equal-shape rule
+
+
+def test_reordered_entry_is_a_permutation_round_trip():
+    """Tokens taken brick by brick (bench/eval_blasst_quant.py:101-134 of the reference), result back in the original
+    order: equal to permuting by hand, and as close to full-precision attention as the plain call."""
+    from low_bit_fake_quant.hook import fake_quant_attention_reordered, space_time_block_order
+    cfg = QuantConfig(qk_quant="fp8_block", v_quant="fp8_channel", fp8_block_size=64, smoothing="k_only", q_kmeans_k=None,
+                      p_quant="dynamic", blasst_lambda=1e-2, blasst_fill="mean_a1.5")
+    torch.manual_seed(6)
+    t, h, w = 4, 8, 16                                   # 512 tokens
+    q, k, v = (torch.randn(1, t * h * w, 2, 128, device=DEV).bfloat16() for _ in range(3))
+    order = space_time_block_order(t, h, w, ts=2, hs=4, ws=8, device=DEV)
+    got = fake_quant_attention_reordered(q, k, v, cfg, order)
+    by_hand = fq.fake_quant_attention(q[:, order].contiguous(), k[:, order].contiguous(), v[:, order].contiguous(), cfg)
+    want = torch.empty_like(by_hand)
+    want[:, order] = by_hand
+    assert torch.equal(got, want)
+    ref = fq.reference_attention(q, k, v).float()
+    cos = torch.nn.functional.cosine_similarity(got.float().flatten(), ref.flatten(), dim=0)
+    assert cos > 0.99
+    with pytest.raises(ValueError, match="permutation"):
+        fake_quant_attention_reordered(q, k, v, cfg, order[:-1])

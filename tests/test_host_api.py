@@ -127,3 +127,25 @@ def test_hook_padding_policy():
     assert torch.equal(vp[:, 100:], (q + 2)[:, -1:].expand(-1, 28, -1, -1))
     same = pad_qkv(q[:, :64], q[:, :64], q[:, :64], QuantConfig(fp8_block_size=64, smoothing="k_only", q_kmeans_k=None))
     assert same[3] == 0 and same[0] is not None and same[0].shape[1] == 64
+
+
+def test_space_time_block_order():
+    """bench/eval_blasst_quant.py:101-134 of the reference: bricks of (ts, hs, ws) tokens made contiguous."""
+    from low_bit_fake_quant.hook import space_time_block_order
+    t, h, w, ts, hs, ws = 4, 6, 8, 2, 3, 4
+    order = space_time_block_order(t, h, w, ts=ts, hs=hs, ws=ws)
+    ids = torch.arange(t * h * w).reshape(t // ts, ts, h // hs, hs, w // ws, ws)
+    assert torch.equal(order, ids.permute(0, 2, 4, 1, 3, 5).reshape(-1))           # divisible grid: a reshape / permute
+    # ragged grid + tail: still a permutation, the tail stays in place, every brick's tokens are contiguous
+    t, h, w = 3, 5, 7
+    order = space_time_block_order(t, h, w, ts=2, hs=2, ws=4, tail=5)
+    n = t * h * w
+    assert torch.equal(torch.sort(order).values, torch.arange(n + 5)) and torch.equal(order[n:], torch.arange(n, n + 5))
+    tt, hh, ww = order[:n] // (h * w), (order[:n] // w) % h, order[:n] % w
+    brick = ((tt // 2) * 3 + hh // 2) * 2 + ww // 4
+    assert torch.equal(brick, torch.sort(brick, stable=True).values)               # bricks in order, never interleaved
+    # the order the reference's block_shuffle_order returns for this ragged grid (generated from it)
+    want = [0, 1, 3, 4, 2, 5, 6, 7, 8, 9, 10, 12, 13, 11, 14, 15, 16, 17, 18, 19]
+    assert space_time_block_order(2, 3, 3, ts=1, hs=2, ws=2, tail=2).tolist() == want
+    with pytest.raises(ValueError):
+        space_time_block_order(0, 1, 1, ts=1, hs=1, ws=1)
