@@ -224,3 +224,15 @@ def test_qm_corr_tensor_core_kernel_agrees_with_fp32_kernel(S, G, D, monkeypatch
     torch.testing.assert_close(c_tc, c_ff, rtol=1e-5, atol=2e-5)
     torch.testing.assert_close(r_tc, c_tc[..., :S].amax(-1), rtol=0, atol=0)   # the row max is the max of what was stored
     torch.testing.assert_close(r_tc, r_ff, rtol=1e-5, atol=2e-5)
+
+
+@pytest.mark.parametrize("S,D,k", [(96, 64, 4), (130, 128, 5), (1025, 128, 64)])
+def test_kmeans_short_and_ragged_slabs(S, D, k):
+    """A slab shorter than one 128-token tile, one token past a tile, one token past a CTA's eight tiles: the
+    tensor-core assignment, the chunked sort and the two-step means against the oracle's Lloyd loop."""
+    torch.manual_seed(S)
+    x = torch.randn(2, S, 3, D).bfloat16()
+    got = kmeans_labels(x.to(DEV), n_clusters=k, max_iters=4, seed=1)
+    want = OA.lloyd_labels(x.permute(0, 2, 1, 3).reshape(6, S, D).float(), k, 4, 1)
+    assert int(got.min()) >= 0 and int(got.max()) < k
+    assert (got.cpu().long() == want).float().mean().item() > 0.99
