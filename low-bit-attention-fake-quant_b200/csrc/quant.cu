@@ -15,6 +15,16 @@
 
 namespace lbfq {
 
+// a / b rounded to nearest, for a divisor whose correctly rounded reciprocal rb = __frcp_rn(b) is at hand (one
+// scale serves a whole block or column): q = RN(a * rb) is within an ulp of the quotient, the remainder a - q * b is
+// exact in one FMA, and RN(q + rem * rb) is the correctly rounded quotient (Markstein's correction step) -- three
+// instructions instead of a full division per element. Non-finite intermediates take the plain division.
+__device__ __forceinline__ float div_rn_rcp(float a, float b, float rb) {
+  const float q = a * rb;
+  if (!(fabsf(q) <= 3.0e38f)) return __fdiv_rn(a, b);
+  return fmaf(fmaf(-q, b, a), rb, q);
+}
+
 constexpr int kThreads = 256;
 constexpr int kVec = 8;          // elements of D per thread access
 constexpr int kTChunk = 64;      // rows staged per transposed store
@@ -152,11 +162,12 @@ fp8_block_quant_kernel(const T* __restrict__ x, CodeDst dst, float* __restrict__
   }
   __syncthreads();
   const float sc = s_scale;
+  const float rsc = __frcp_rn(sc);
   store_tile(dst, b, h, s0, block_s, tbuf, [&](int r, int dd, float (&q)[kVec]) {
     float v[kVec];
     load8<T>(src + r * rstride + dd, v);
 #pragma unroll
-    for (int i = 0; i < kVec; ++i) q[i] = fminf(fmaxf(__fdiv_rn(v[i], sc), -kFp8Max), kFp8Max);
+    for (int i = 0; i < kVec; ++i) q[i] = fminf(fmaxf(div_rn_rcp(v[i], sc, rsc), -kFp8Max), kFp8Max);
   });
 }
 
@@ -319,6 +330,7 @@ template <typename T>
 __global__ void __launch_bounds__(kThreads)
 channel_quant_kernel(const T* __restrict__ x, CodeDst dst, const float* __restrict__ scale) {
   __shared__ float col_scale[128];
+  __shared__ float col_rcp[128];
   __shared__ __align__(16) uint8_t tbuf[128 * (kTChunk + 16)];
   const int ntile = (dst.S + kTChunk - 1) / kTChunk;
   const int tile = blockIdx.x % ntile;
@@ -329,14 +341,18 @@ channel_quant_kernel(const T* __restrict__ x, CodeDst dst, const float* __restri
   const int nrows = min(kTChunk, dst.S - s0);
   const T* src = x + (((size_t)b * dst.S + s0) * dst.H + h) * D;
   const size_t rstride = (size_t)dst.H * D;
-  if (threadIdx.x < D) col_scale[threadIdx.x] = scale[((size_t)b * dst.H + h) * D + threadIdx.x];
+  if (threadIdx.x < D) {
+    const float sc = scale[((size_t)b * dst.H + h) * D + threadIdx.x];
+    col_scale[threadIdx.x] = sc;
+    col_rcp[threadIdx.x] = __frcp_rn(sc);
+  }
   __syncthreads();
   store_tile(dst, b, h, s0, nrows, tbuf, [&](int r, int dd, float (&q)[kVec]) {
     float v[kVec];
     load8<T>(src + r * rstride + dd, v);
 #pragma unroll
     for (int i = 0; i < kVec; ++i)
-      q[i] = fminf(fmaxf(__fdiv_rn(v[i], col_scale[dd + i]), -kFp8Max), kFp8Max);
+      q[i] = fminf(fmaxf(div_rn_rcp(v[i], col_scale[dd + i], col_rcp[dd + i]), -kFp8Max), kFp8Max);
   });
 }
 
