@@ -27,7 +27,8 @@ __device__ __forceinline__ float div_rn_rcp(float a, float b, float rb) {
 
 constexpr int kThreads = 256;
 constexpr int kVec = 8;          // elements of D per thread access
-constexpr int kTChunk = 64;      // rows staged per transposed store
+constexpr int kTChunk = 128;     // tokens staged per transposed store: 128-byte rows of the transposed codes
+constexpr int kTPitch = kTChunk + 4;   // bytes between the channels' rows in the staging buffer
 
 template <typename T>
 __device__ __forceinline__ void load8(const T* p, float (&v)[kVec]) {
@@ -77,6 +78,16 @@ struct CodeDst {
 };
 
 // Store the codes of rows [s0, s0 + nrows) of slab (b, h); `quant(r, d0, q)`
+// 4 x 4 byte transpose: a0..a3 hold bytes [c0 c1 c2 c3] of tokens 0..3; out[c] = [t0 t1 t2 t3] of channel c
+__device__ __forceinline__ void transpose4x4(uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t* out) {
+  const uint32_t t0 = __byte_perm(a0, a1, 0x5140), t1 = __byte_perm(a2, a3, 0x5140);   // channels 0, 1 of two tokens
+  const uint32_t t2 = __byte_perm(a0, a1, 0x7362), t3 = __byte_perm(a2, a3, 0x7362);   // channels 2, 3
+  out[0] = __byte_perm(t0, t1, 0x5410);
+  out[1] = __byte_perm(t0, t1, 0x7632);
+  out[2] = __byte_perm(t2, t3, 0x5410);
+  out[3] = __byte_perm(t2, t3, 0x7632);
+}
+
 // fills the 8 quantised-and-clamped fp32 values of row r, columns d0..d0+7.
 // NHD / BHSD are written directly (8-byte stores); BHDS goes through a
 // shared-memory transpose so that global stores stay 16 bytes wide.
@@ -99,23 +110,32 @@ __device__ __forceinline__ void store_tile(const CodeDst& dst, int b, int h, int
     }
     return;
   }
-  constexpr int kPitch = kTChunk + 16;
+  // Transposed layout: the codes of up to kTChunk tokens go through shared memory as [channel][token]. A thread
+  // quantises four consecutive tokens of its eight channels and transposes the 4 x 8 bytes in registers
+  // (byte permutes), so that it stores one 32-bit word per channel instead of four single bytes.
   for (int c0 = 0; c0 < nrows; c0 += kTChunk) {
-    const int cn = min(kTChunk, nrows - c0);
-    for (int r = tr; r < cn; r += rows_per_iter) {
-      float q[kVec];
-      quant(c0 + r, d0, q);
-      uint2 pk = pack8(q);
-      const uint8_t* pb = reinterpret_cast<const uint8_t*>(&pk);
+    const int cn = min(kTChunk, nrows - c0);           // a multiple of 16 (checked on the host)
+    for (int qd = tr; qd * 4 < cn; qd += rows_per_iter) {
+      uint2 pk[4];
 #pragma unroll
-      for (int i = 0; i < kVec; ++i) tbuf[(d0 + i) * kPitch + r] = pb[i];
+      for (int j = 0; j < 4; ++j) {
+        float q[kVec];
+        quant(c0 + qd * 4 + j, d0, q);
+        pk[j] = pack8(q);
+      }
+      uint32_t w[8];
+      transpose4x4(pk[0].x, pk[1].x, pk[2].x, pk[3].x, w);
+      transpose4x4(pk[0].y, pk[1].y, pk[2].y, pk[3].y, w + 4);
+#pragma unroll
+      for (int i = 0; i < kVec; ++i) *reinterpret_cast<uint32_t*>(tbuf + (d0 + i) * kTPitch + qd * 4) = w[i];
     }
     __syncthreads();
-    // cn is a multiple of 16 (checked on the host): 16-byte row segments.
+    // 16-byte row segments, read back as four words (the pitch keeps rows a word, not 16 bytes, apart)
     const int segs = cn / 16;
     for (int idx = threadIdx.x; idx < D * segs; idx += kThreads) {
       int d = idx / segs, sg = idx % segs;
-      uint4 val = *reinterpret_cast<const uint4*>(tbuf + d * kPitch + sg * 16);
+      const uint32_t* src = reinterpret_cast<const uint32_t*>(tbuf + d * kTPitch + sg * 16);
+      uint4 val = make_uint4(src[0], src[1], src[2], src[3]);
       size_t off = (((size_t)b * dst.H + h) * D + d) * dst.s_pad + (s0 + c0 + sg * 16);
       *reinterpret_cast<uint4*>(dst.base + off) = val;
     }
@@ -131,7 +151,7 @@ __global__ void __launch_bounds__(kThreads)
 fp8_block_quant_kernel(const T* __restrict__ x, CodeDst dst, float* __restrict__ scale, int block_s) {
   __shared__ float red[kThreads / 32];
   __shared__ float s_scale;
-  __shared__ __align__(16) uint8_t tbuf[128 * (kTChunk + 16)];
+  __shared__ __align__(16) uint8_t tbuf[128 * kTPitch];
   const int nblk = dst.S / block_s;
   const int blk = blockIdx.x % nblk;
   const int h = (blockIdx.x / nblk) % dst.H;
@@ -179,7 +199,7 @@ __global__ void __launch_bounds__(kThreads)
 mxfp8_v_quant_kernel(const T* __restrict__ x, CodeDst dst, float* __restrict__ scale, int block_s) {
   __shared__ float col_amax[kThreads / 8][128 + 1];   // [row-lane][d]
   __shared__ float col_scale[128];
-  __shared__ __align__(16) uint8_t tbuf[128 * (kTChunk + 16)];
+  __shared__ __align__(16) uint8_t tbuf[128 * kTPitch];
   const int nblk = dst.S / block_s;
   const int blk = blockIdx.x % nblk;
   const int h = (blockIdx.x / nblk) % dst.H;
@@ -231,7 +251,7 @@ __global__ void __launch_bounds__(kThreads)
 mxfp8_qk_quant_kernel(const T* __restrict__ x, CodeDst dst, float* __restrict__ scale,
                       uint8_t* __restrict__ scale_e8, int block_d) {
   __shared__ float grp_scale[kMxRows][128 / 8 + 1];   // scale of the group owning d0, per row
-  __shared__ __align__(16) uint8_t tbuf[128 * (kTChunk + 16)];
+  __shared__ __align__(16) uint8_t tbuf[128 * kTPitch];
   const int ntile = (dst.S + kMxRows - 1) / kMxRows;
   const int tile = blockIdx.x % ntile;
   const int h = (blockIdx.x / ntile) % dst.H;
@@ -331,7 +351,7 @@ __global__ void __launch_bounds__(kThreads)
 channel_quant_kernel(const T* __restrict__ x, CodeDst dst, const float* __restrict__ scale) {
   __shared__ float col_scale[128];
   __shared__ float col_rcp[128];
-  __shared__ __align__(16) uint8_t tbuf[128 * (kTChunk + 16)];
+  __shared__ __align__(16) uint8_t tbuf[128 * kTPitch];
   const int ntile = (dst.S + kTChunk - 1) / kTChunk;
   const int tile = blockIdx.x % ntile;
   const int h = (blockIdx.x / ntile) % dst.H;
