@@ -61,6 +61,12 @@ unsigned long long lbfq_launch_count(void);
  * `s_pad` rows per (b,h) when layout != NHD. */
 int lbfq_fp8_block_quant(const void* x, int dtype, int B, int S, int H, int D, int block_s,
                          uint8_t* codes, int layout, int s_pad, float* scale, void* stream);
+/* The same quantizer applied to round_dtype(x - mean[b, h, :]), mean fp32 (B, H, D): smooth_k
+ * (src/low_bit_fake_quant/preprocess.py:10-57) followed by fp8_block_quant without storing the smoothed tensor;
+ * codes and scales are those of the two-step sequence, bit for bit. */
+int lbfq_fp8_block_quant_centered(const void* x, int dtype, int B, int S, int H, int D, int block_s,
+                                  const float* mean, uint8_t* codes, int layout, int s_pad, float* scale,
+                                  void* stream);
 
 /* fp8_block_dequant, quant_triton.py:80-131. codes NHD -> out NHD of out_dtype. */
 int lbfq_fp8_block_dequant(const uint8_t* codes, const float* scale, int B, int S, int H, int D,
@@ -100,7 +106,8 @@ int lbfq_mxfp8_v_dequant(const uint8_t* codes, const float* scale, int B, int S,
 
 /* smooth_k, src/low_bit_fake_quant/preprocess.py:10-57. k, out: NHD of dtype;
  * mean: fp32 (B, H, D). `partial` is caller scratch of
- * lbfq_smooth_k_scratch_floats(B,S,H,D) floats. */
+ * lbfq_smooth_k_scratch_floats(B,S,H,D) floats. `out` may be NULL: the mean alone is computed
+ * (for lbfq_fp8_block_quant_centered). */
 int64_t lbfq_smooth_k_scratch_floats(int B, int S, int H, int D);
 int lbfq_smooth_k(const void* k, int dtype, int B, int S, int H, int D, void* out, float* mean,
                   float* partial, void* stream);

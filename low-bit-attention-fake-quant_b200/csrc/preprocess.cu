@@ -408,6 +408,7 @@ extern "C" int lbfq_smooth_k(const void* k, int dtype, int B, int S, int H, int 
   if (int rc = check_launch("k_partial_sum")) return rc;
   k_mean_kernel<<<B * H, 128, 0, st>>>(partial, ntile, D, S, mean);
   if (int rc = check_launch("k_mean")) return rc;
+  if (out == nullptr) return LBFQ_OK;                // the mean alone (the caller centres while quantising)
   const size_t total = (size_t)B * S * H * D / kVec;
   LBFQ_DISPATCH_DTYPE(dtype, T,
       sub_channel_mean_kernel<T><<<grid_for(total, kThreads), kThreads, 0, st>>>((const T*)k, (T*)out, mean, B, S, H, D));

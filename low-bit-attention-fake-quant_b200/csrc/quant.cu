@@ -148,7 +148,8 @@ __device__ __forceinline__ void store_tile(const CodeDst& dst, int b, int h, int
 // ---------------------------------------------------------------------------
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
-fp8_block_quant_kernel(const T* __restrict__ x, CodeDst dst, float* __restrict__ scale, int block_s) {
+fp8_block_quant_kernel(const T* __restrict__ x, CodeDst dst, float* __restrict__ scale, int block_s,
+                       const float* __restrict__ mean) {
   __shared__ float red[kThreads / 32];
   __shared__ float s_scale;
   __shared__ __align__(16) uint8_t tbuf[128 * kTPitch];
@@ -162,10 +163,19 @@ fp8_block_quant_kernel(const T* __restrict__ x, CodeDst dst, float* __restrict__
   const T* src = x + (((size_t)b * dst.S + s0) * dst.H + h) * D;
   const size_t rstride = (size_t)dst.H * D;
 
+  // optional centring: the tensor that is quantised is round_T(x - mean[b, h, :]), what smooth_k would have stored
+  auto centre = [&](float (&v)[kVec], int dd) {
+    if (mean != nullptr) {
+      const float* m = mean + ((size_t)b * dst.H + h) * D + dd;
+#pragma unroll
+      for (int i = 0; i < kVec; ++i) v[i] = round_through<T>(v[i] - m[i]);
+    }
+  };
   float amax = 0.f;
   for (int r = tr; r < block_s; r += rpi) {
     float v[kVec];
     load8<T>(src + r * rstride + d0, v);
+    centre(v, d0);
 #pragma unroll
     for (int i = 0; i < kVec; ++i) amax = fmaxf(amax, fabsf(v[i]));
   }
@@ -186,6 +196,7 @@ fp8_block_quant_kernel(const T* __restrict__ x, CodeDst dst, float* __restrict__
   store_tile(dst, b, h, s0, block_s, tbuf, [&](int r, int dd, float (&q)[kVec]) {
     float v[kVec];
     load8<T>(src + r * rstride + dd, v);
+    centre(v, dd);
 #pragma unroll
     for (int i = 0; i < kVec; ++i) q[i] = fminf(fmaxf(div_rn_rcp(v[i], sc, rsc), -kFp8Max), kFp8Max);
   });
@@ -435,8 +446,23 @@ static int zero_pad(uint8_t* codes, int layout, int B, int S, int H, int D, int 
 
 using namespace lbfq;
 
+static int fp8_block_quant_impl(const void* x, int dtype, int B, int S, int H, int D, int block_s, const float* mean,
+                                uint8_t* codes, int layout, int s_pad, float* scale, void* stream);
+
 extern "C" int lbfq_fp8_block_quant(const void* x, int dtype, int B, int S, int H, int D, int block_s,
                                     uint8_t* codes, int layout, int s_pad, float* scale, void* stream) {
+  return fp8_block_quant_impl(x, dtype, B, S, H, D, block_s, nullptr, codes, layout, s_pad, scale, stream);
+}
+
+extern "C" int lbfq_fp8_block_quant_centered(const void* x, int dtype, int B, int S, int H, int D, int block_s,
+                                             const float* mean, uint8_t* codes, int layout, int s_pad, float* scale,
+                                             void* stream) {
+  LBFQ_REQUIRE(mean != nullptr, LBFQ_ERR_ARG, "fp8_block_quant_centered: mean (B, H, D) is required");
+  return fp8_block_quant_impl(x, dtype, B, S, H, D, block_s, mean, codes, layout, s_pad, scale, stream);
+}
+
+static int fp8_block_quant_impl(const void* x, int dtype, int B, int S, int H, int D, int block_s, const float* mean,
+                                uint8_t* codes, int layout, int s_pad, float* scale, void* stream) {
   if (int rc = check_common(B, S, H, D, layout, s_pad)) return rc;
   LBFQ_REQUIRE(block_s > 0 && S % block_s == 0, LBFQ_ERR_ARG, "S=%d must be divisible by block_s=%d", S, block_s);
   if (layout == LBFQ_LAYOUT_BHDS)
@@ -445,7 +471,7 @@ extern "C" int lbfq_fp8_block_quant(const void* x, int dtype, int B, int S, int 
   CodeDst dst{codes, layout, S, H, D, s_pad};
   const int grid = B * (S / block_s) * H;
   LBFQ_DISPATCH_DTYPE(dtype, T,
-      fp8_block_quant_kernel<T><<<grid, kThreads, 0, st>>>((const T*)x, dst, scale, block_s));
+      fp8_block_quant_kernel<T><<<grid, kThreads, 0, st>>>((const T*)x, dst, scale, block_s, mean));
   if (int rc = check_launch("fp8_block_quant")) return rc;
   return zero_pad(codes, layout, B, S, H, D, s_pad, st);
 }

@@ -74,6 +74,7 @@ _SIGS = {
     "lbfq_attention_last_variant": (_I, []),
     "lbfq_copy_rows_async": (_I, [_P, C.c_size_t, _P, C.c_size_t, C.c_size_t, C.c_size_t, _I, _P]),
     "lbfq_fp8_block_quant": (_I, [_P, _I, _I, _I, _I, _I, _I, _P, _I, _I, _P, _P]),
+    "lbfq_fp8_block_quant_centered": (_I, [_P, _I, _I, _I, _I, _I, _I, _P, _P, _I, _I, _P, _P]),
     "lbfq_fp8_block_dequant": (_I, [_P, _P, _I, _I, _I, _I, _I, _P, _I, _P]),
     "lbfq_fp8_channel_quant": (_I, [_P, _I, _I, _I, _I, _I, _P, _I, _I, _P, _P]),
     "lbfq_fp8_channel_dequant": (_I, [_P, _P, _I, _I, _I, _I, _P, _I, _P]),

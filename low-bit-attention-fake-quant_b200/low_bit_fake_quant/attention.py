@@ -29,7 +29,7 @@ from .attention_triton import fake_quant_attention_fp8, fake_quant_attention_tri
 from .config import QuantConfig
 from .hadamard import apply_qk_hadamard
 from .kmeans import KMeansReorderResult, _gather, apply_kv_permutation, kmeans_reorder_tokens
-from .preprocess import group_mean_q, smooth_k, smooth_v_per_block
+from .preprocess import group_mean_q, k_channel_mean, smooth_k, smooth_v_per_block
 from .quant_triton import (
     fp8_block_dequant,
     fp8_block_quant,
@@ -82,11 +82,31 @@ def _round_up(x: int, m: int) -> int:
 # preprocess: Q k-means -> K smooth -> Q smooth -> V k-means (+K) -> V smooth
 # ---------------------------------------------------------------------------
 
-def _preprocess(q, k, v, cfg: QuantConfig, *, head_offset: int = 0, total_heads: int = 0):
-    """The reference's fixed preprocessing order (attention.py:166-239)."""
+def _k_smoothing_can_ride_on_the_quantizer(cfg: QuantConfig) -> bool:
+    """K smoothing alone, fp8_block K, nothing between the two that needs the smoothed K as a tensor (no score bias,
+    no K / V co-permutation, no rotation): the K quantizer subtracts the mean itself."""
+    return (cfg.smoothing == "k_only" and cfg.qk_quant == "fp8_block" and cfg.v_kmeans_k is None
+            and not cfg.qk_hadamard and cfg.p_requant)
+
+
+def _preprocess(q, k, v, cfg: QuantConfig, *, head_offset: int = 0, total_heads: int = 0, defer_k_smoothing: bool = False):
+    """The reference's fixed preprocessing order (attention.py:166-239).
+
+    ``defer_k_smoothing`` (only with ``_k_smoothing_can_ride_on_the_quantizer``): K is returned as it came and its
+    channel mean as an eighth value, for the quantizer to subtract."""
     q_work, k_work, v_work = q.contiguous(), k.contiguous(), v.contiguous()
     q_km = v_km = None
     qm = v_alpha = None
+    if defer_k_smoothing:
+        if cfg.q_kmeans_k is not None:
+            q_km = kmeans_reorder_tokens(q_work, n_clusters=cfg.q_kmeans_k, max_iters=cfg.q_kmeans_iters,
+                                         seed=cfg.q_kmeans_seed, head_offset=head_offset, total_heads=total_heads)
+            q_work = q_km.tensor_reordered
+        if cfg.v_smooth_mode == "per_block":
+            v_work, v_alpha = smooth_v_per_block(v_work, block_s=cfg.v_smooth_block_size)
+        elif cfg.v_smooth_mode != "off":
+            raise ValueError(f"unsupported v_smooth_mode: {cfg.v_smooth_mode!r}")
+        return q_work, k_work, v_work, None, v_alpha, q_km, None, k_channel_mean(k_work)
 
     if cfg.q_kmeans_k is not None:
         q_km = kmeans_reorder_tokens(q_work, n_clusters=cfg.q_kmeans_k, max_iters=cfg.q_kmeans_iters,
@@ -192,7 +212,7 @@ def _fake_quant_attention_sdpa(q_work, k_work, v_work, qm, v_alpha, cfg: QuantCo
 def _fake_quant_attention_p_requant(q_work, k_work, v_work, qm, v_alpha, q_kmeans, cfg: QuantConfig,
                                     sm_scale, out_dtype, *, return_stats: bool = False,
                                     out_fp32_exact: bool = False, head_offset: int = 0, total_heads: int = 0,
-                                    rowmax_counters=None):
+                                    rowmax_counters=None, k_mean=None):
     """Quantise straight into the kernel's layouts and launch it. Returns the
     output in NHD, rows already back in the original Q order."""
     # K / V may have their own length (cross-attention, an extension: the reference's entry takes equal shapes only)
@@ -204,7 +224,8 @@ def _fake_quant_attention_p_requant(q_work, k_work, v_work, qm, v_alpha, q_kmean
     q_sf = k_sf = None
     if cfg.qk_quant == "fp8_block":
         q_codes, q_scale = fp8_block_quant(q_in, block_s=cfg.fp8_block_size, _layout=L.LAYOUT_BHSD, _s_pad=sq_pad)
-        k_codes, k_scale = fp8_block_quant(k_in, block_s=cfg.fp8_block_size, _layout=L.LAYOUT_BHSD, _s_pad=s_pad)
+        # `k_mean`: K arrives unsmoothed and the quantizer subtracts its channel mean (smooth_k fused in)
+        k_codes, k_scale = fp8_block_quant(k_in, block_s=cfg.fp8_block_size, _layout=L.LAYOUT_BHSD, _s_pad=s_pad, _mean=k_mean)
     elif cfg.qk_quant == "mxfp8":
         # codes + UE8M0 scale tiles for the block-scaled MMA (the FP32 scale tensors are by-products here)
         q_sf = torch.empty((b * h * sq_pad * 4,), dtype=torch.uint8, device=q_in.device)
@@ -397,9 +418,13 @@ def fake_quant_attention(
         if not same:
             raise ValueError("preprocess_cache does not match cfg's smoothing/kmeans/v_smooth settings")
         q_work, k_work, v_work, qm, v_alpha, q_km = pc.q_work, pc.k_work, pc.v_work, pc.qm, pc.v_alpha, pc.q_kmeans
+        k_mean = None
     else:
-        q_work, k_work, v_work, qm, v_alpha, q_km, _ = _preprocess(q, k, v, cfg, head_offset=_head_offset,
-                                                                   total_heads=_total_heads)
+        # where nothing else needs the smoothed K, it is never stored: the K quantizer subtracts the mean
+        defer = _k_smoothing_can_ride_on_the_quantizer(cfg) and not _reference_operands
+        pre = _preprocess(q, k, v, cfg, head_offset=_head_offset, total_heads=_total_heads, defer_k_smoothing=defer)
+        q_work, k_work, v_work, qm, v_alpha, q_km = pre[:6]
+        k_mean = pre[7] if defer else None
 
     # mxfp8 Q / K de-quantise to BF16 exactly (power-of-two scales), so for them the BF16-operand kernel computes
     # the same products as a block-scaled FP8 MMA and, unlike the general kernel, keeps the accumulator in tensor
@@ -417,7 +442,7 @@ def fake_quant_attention(
         # the kernel scatters its rows through q_km.order: no separate inverse gather
         o = _fake_quant_attention_p_requant(q_work, k_work, v_work, qm, v_alpha, q_km, cfg, sm_scale, out_dtype,
                                             out_fp32_exact=_debug_fp32, head_offset=_head_offset,
-                                            total_heads=_total_heads)
+                                            total_heads=_total_heads, k_mean=k_mean)
     else:
         o = _fake_quant_attention_sdpa(q_work, k_work, v_work, qm, v_alpha, cfg, sm_scale, sdpa_dtype,
                                        _head_offset, _total_heads)

@@ -30,6 +30,22 @@ def smooth_k(k: torch.Tensor, block_s: int = 256) -> Tuple[torch.Tensor, torch.T
     return out, mean
 
 
+def k_channel_mean(k: torch.Tensor) -> torch.Tensor:
+    """The mean ``smooth_k`` subtracts, (B, H, D) fp32, without the smoothed tensor (internal: the K quantizer can
+    centre on the fly)."""
+    if k.ndim != 4 or not k.is_cuda:
+        raise ValueError(f"k must be 4-D NHD on CUDA; got {tuple(k.shape)} on {k.device}")
+    b, s, h, d = k.shape
+    k = k.contiguous()
+    mean = torch.empty((b, h, d), dtype=torch.float32, device=k.device)
+    with torch.cuda.device(k.device):
+        n = L.lib().lbfq_smooth_k_scratch_floats(b, s, h, d)
+        partial = torch.empty((n,), dtype=torch.float32, device=k.device)
+        L.check(L.lib().lbfq_smooth_k(k.data_ptr(), L.dtype_code(k.dtype), b, s, h, d, None,
+                                      mean.data_ptr(), partial.data_ptr(), L.stream_ptr(k.device)))
+    return mean
+
+
 def _block_mean_sub(x: torch.Tensor, block: int, name: str) -> Tuple[torch.Tensor, torch.Tensor]:
     if x.ndim != 4 or not x.is_cuda:
         raise ValueError(f"{name} must be 4-D NHD on CUDA; got {tuple(x.shape)} on {x.device}")

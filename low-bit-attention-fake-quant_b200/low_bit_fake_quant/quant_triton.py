@@ -39,8 +39,11 @@ def _codes_like(t: torch.Tensor, layout: int, s_pad: int) -> torch.Tensor:
 
 
 def fp8_block_quant(t: torch.Tensor, block_s: int = 128, *, _layout: int = L.LAYOUT_NHD,
-                    _s_pad: int = 0) -> Tuple[torch.Tensor, torch.Tensor]:
-    """FP32-scale FP8 e4m3fn quantization per (B, S/block_s, H)."""
+                    _s_pad: int = 0, _mean: torch.Tensor | None = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """FP32-scale FP8 e4m3fn quantization per (B, S/block_s, H).
+
+    ``_mean`` (fp32 (B, H, D), internal): quantise ``(t - mean).to(t.dtype)`` without storing it (K smoothing fused
+    into the K quantizer; the same codes and scales as the two steps)."""
     b, s, h, d = _check_nhd(t)
     if s % block_s != 0:
         raise ValueError(f"S={s} must be divisible by block_s={block_s}")
@@ -48,9 +51,16 @@ def fp8_block_quant(t: torch.Tensor, block_s: int = 128, *, _layout: int = L.LAY
     out = _codes_like(t, _layout, _s_pad)
     scale = torch.empty((b, s // block_s, h), dtype=torch.float32, device=t.device)
     with torch.cuda.device(t.device):
-        L.check(L.lib().lbfq_fp8_block_quant(t.data_ptr(), L.dtype_code(t.dtype), b, s, h, d, block_s,
-                                             out.data_ptr(), _layout, _s_pad, scale.data_ptr(),
-                                             L.stream_ptr(t.device)))
+        if _mean is not None:
+            if tuple(_mean.shape) != (b, h, d) or _mean.dtype != torch.float32:
+                raise ValueError(f"mean must be fp32 {(b, h, d)}; got {_mean.dtype} {tuple(_mean.shape)}")
+            L.check(L.lib().lbfq_fp8_block_quant_centered(t.data_ptr(), L.dtype_code(t.dtype), b, s, h, d, block_s,
+                                                          _mean.contiguous().data_ptr(), out.data_ptr(), _layout, _s_pad,
+                                                          scale.data_ptr(), L.stream_ptr(t.device)))
+        else:
+            L.check(L.lib().lbfq_fp8_block_quant(t.data_ptr(), L.dtype_code(t.dtype), b, s, h, d, block_s,
+                                                 out.data_ptr(), _layout, _s_pad, scale.data_ptr(),
+                                                 L.stream_ptr(t.device)))
     return out, scale
 
 

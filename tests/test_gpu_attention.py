@@ -428,3 +428,24 @@ def test_errors():
         fq.fake_quant_attention(x, x, x, QuantConfig(**COMMON, smoothing="k_only", q_kmeans_k=None), preprocess_cache=pc)
     with pytest.raises(TypeError):
         fq.fake_quant_attention(x.to(torch.float64), x.to(torch.float64), x.to(torch.float64), QuantConfig())
+
+
+@pytest.mark.parametrize("extra", [dict(), dict(q_kmeans_k=8), dict(v_smooth_mode="per_block", p_quant="dynamic"),
+                                   dict(blasst_lambda=1e-2, p_quant="dynamic")])
+def test_k_smoothing_fused_into_the_k_quantizer_changes_nothing(extra):
+    """With K smoothing alone the smoothed K is never stored: the K quantizer subtracts the mean. Through a preprocess
+    cache the smoothed K is a tensor and the plain quantizer reads it: both give the same bits."""
+    cfg = QuantConfig(**{**COMMON, **dict(smoothing="k_only", q_kmeans_k=None), **extra})
+    q, k, v = (t.to(DEV) for t in _qkv(2, 768, 3, 128, seed=77, outliers=True))
+    fused = fq.fake_quant_attention(q, k, v, cfg)
+    cache = fq.prepare_for_attention(q, k, v, cfg)
+    two_step = fq.fake_quant_attention(q, k, v, cfg, preprocess_cache=cache)
+    raise_if_device_error(torch.device(DEV))
+    assert torch.equal(fused, two_step)
+    # and the codes themselves
+    from low_bit_fake_quant.preprocess import k_channel_mean, smooth_k
+    ks, mean = smooth_k(k)
+    assert torch.equal(mean, k_channel_mean(k))
+    c2, s2 = fq.fp8_block_quant(ks, 64)
+    c1, s1 = fq.fp8_block_quant(k, 64, _mean=mean)
+    assert torch.equal(c1.view(torch.uint8), c2.view(torch.uint8)) and torch.equal(s1, s2)
