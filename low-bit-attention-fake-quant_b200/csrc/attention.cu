@@ -838,24 +838,22 @@ static int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMa
 
 using namespace lbfq;
 
-// v_alpha' = v_alpha / (the V scale that multiplies the same PV term)
+// v_alpha' = v_alpha / (the V scale that multiplies the same PV term), written at granularity `g` keys: the smoothing
+// block itself, or -- with a per-block V scale whose blocks are not the smoothing blocks -- their common divisor, so
+// that every entry has one smoothing value and one scale
 __global__ void alpha_prep_kernel(const float* __restrict__ alpha, float* __restrict__ out, const float* __restrict__ vscale,
-                                  int v_kind, int B, int NB, int H, int D, int blocks_per_vblock_num, int blocks_per_vblock_den) {
+                                  int v_kind, int B, int N, int H, int D, int g, int v_smooth_block, int v_block) {
+  const int NB = N / g;
   const size_t total = (size_t)B * NB * H * D;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
     const int d = (int)(i % D);
     const int h = (int)((i / D) % H);
     const int nb = (int)((i / D / H) % NB);
     const int b = (int)(i / D / H / NB);
-    float a = alpha[i];
-    if (v_kind == LBFQ_V_CHANNEL) {
-      a = __fdiv_rn(a, vscale[((size_t)b * H + h) * D + d]);
-    } else if (v_kind == LBFQ_V_BLOCK) {
-      // smoothing block nb covers keys [nb * vsb, ...); its V-scale block index = nb * vsb / v_block
-      const int vb = (int)(((int64_t)nb * blocks_per_vblock_num) / blocks_per_vblock_den);
-      const int nvb = (int)(((int64_t)NB * blocks_per_vblock_num) / blocks_per_vblock_den);
-      a = __fdiv_rn(a, vscale[((size_t)b * nvb + vb) * H + h]);
-    }
+    const int key = nb * g;
+    float a = alpha[(((size_t)b * (N / v_smooth_block) + key / v_smooth_block) * H + h) * D + d];
+    if (v_kind == LBFQ_V_CHANNEL) a = __fdiv_rn(a, vscale[((size_t)b * H + h) * D + d]);
+    else if (v_kind == LBFQ_V_BLOCK) a = __fdiv_rn(a, vscale[((size_t)b * (N / v_block) + key / v_block) * H + h]);
     out[i] = a;
   }
 }
@@ -905,9 +903,19 @@ __global__ void alpha_ext_kernel(const float* __restrict__ alpha, __nv_bfloat16*
 }
 
 static size_t align256(size_t v) { return (v + 255) / 256 * 256; }
+// keys per entry of the prepared V-smoothing vector (see alpha_prep_kernel)
+static int alpha_granularity(const lbfq_attn_args* a) {
+  int g = a->v_smooth_block > 0 ? a->v_smooth_block : 1;
+  if (a->v_kind == LBFQ_V_BLOCK && a->v_block > 0) {
+    int x = g, y = a->v_block;
+    while (y) { const int t = x % y; x = y; y = t; }
+    g = x;
+  }
+  return g;
+}
 static size_t alpha_ws_bytes(const lbfq_attn_args* a) {
   if (!a->v_alpha) return 0;
-  return align256((size_t)a->B * (a->N / (a->v_smooth_block > 0 ? a->v_smooth_block : 1)) * a->H * a->D * 4);
+  return align256((size_t)a->B * (a->N / alpha_granularity(a)) * a->H * a->D * 4);
 }
 // mx / dynamic P, or any P with the V-smoothing term, on FP8-block Q/K may take the BF16-P kernel, which wants a BF16
 // copy of V^T (and the alpha' pieces) in the workspace
@@ -1049,13 +1057,15 @@ extern "C" int lbfq_attention_fwd(const lbfq_attn_args* a, void* workspace, void
   LBFQ_REQUIRE(p.out_dtype >= 0 && p.out_dtype <= 2, LBFQ_ERR_DTYPE, "unsupported dtype code %d", p.out_dtype);
 
   if (a->v_alpha) {
-    const int NB = a->N / a->v_smooth_block;
-    const size_t total = (size_t)a->B * NB * a->H * a->D;
+    const int gran = alpha_granularity(a);
+    const size_t total = (size_t)a->B * (a->N / gran) * a->H * a->D;
     int g = (int)((total + 255) / 256); if (g > 148 * 8) g = 148 * 8;
-    alpha_prep_kernel<<<g, 256, 0, st>>>(a->v_alpha, (float*)workspace, a->v_scale, a->v_kind, a->B, NB, a->H, a->D,
-                                        a->v_smooth_block, a->v_kind == LBFQ_V_BLOCK ? a->v_block : 1);
+    alpha_prep_kernel<<<g, 256, 0, st>>>(a->v_alpha, (float*)workspace, a->v_scale, a->v_kind, a->B, a->N, a->H, a->D,
+                                        gran, a->v_smooth_block, a->v_kind == LBFQ_V_BLOCK ? a->v_block : 1);
     if (int rc = check_launch("alpha_prep")) return rc;
     p.v_alpha = (const float*)workspace;
+    p.v_smooth_block = gran;                      // the kernels index the prepared vector, not the caller's
+    p.n_v_alpha = (long long)total;
   }
 
   CUtensorMap mq, mk, mv;

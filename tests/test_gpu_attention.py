@@ -449,3 +449,15 @@ def test_k_smoothing_fused_into_the_k_quantizer_changes_nothing(extra):
     c2, s2 = fq.fp8_block_quant(ks, 64)
     c1, s1 = fq.fp8_block_quant(k, 64, _mean=mean)
     assert torch.equal(c1.view(torch.uint8), c2.view(torch.uint8)) and torch.equal(s1, s2)
+
+
+@pytest.mark.parametrize("vsb,vfb", [(128, 64), (64, 128), (192, 64)])
+def test_v_smoothing_blocks_that_are_not_the_v_scale_blocks(vsb, vfb):
+    """fp8_block V with the V-smoothing term: a smoothing block may span several scale blocks (or the other way
+    round); every key block must meet its own scale and its own smoothing value."""
+    cfg = QuantConfig(**{**COMMON, **dict(smoothing="k_only", q_kmeans_k=None, v_quant="fp8_block", v_fp8_block_size=vfb,
+                                          v_smooth_mode="per_block", v_smooth_block_size=vsb, p_quant="dynamic")})
+    q, k, v = _qkv(1, 768, 2, 128, seed=vsb + vfb, outliers=True)
+    v = v * (1.0 + 3.0 * torch.rand(1, 768, 1, 1)).to(v.dtype) + 2.0         # block scales and block means that differ
+    g, o = _run_both(q, k, v, cfg)
+    _check(g, o)
