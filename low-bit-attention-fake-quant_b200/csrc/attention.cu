@@ -1076,7 +1076,7 @@ extern "C" int lbfq_attention_fwd(const lbfq_attn_args* a, void* workspace, void
     const int fvb = fast_variant(p, a->use_blasst != 0, false);
     LBFQ_REQUIRE(fvb == 2, LBFQ_ERR_UNSUPPORTED,
                  "BF16 operands are served for V per channel / pre-dequantised, without BLASST, with q_smooth_block a "
-                 "multiple of 128 and v_smooth_block >= 64; the FP8-code entry covers the rest");
+                 "multiple of 128 and v_smooth_block 64 or a multiple of 128; the FP8-code entry covers the rest");
     if (int rc = make_map_bf16(&mq, a->q_codes, a->D, a->m_pad, BH, 64, kTileM)) return rc;
     if (int rc = make_map_bf16(&mk, a->k_codes, a->D, a->n_pad, BH, 64, kChunk)) return rc;
     if (int rc = make_map_bf16(&mv, a->v_codes, a->n_pad, a->D, BH, 64, a->D)) return rc;

@@ -842,7 +842,8 @@ int fast_variant(const Params& p, bool blasst, bool qk_mx) {
     if (p.p_kind == LBFQ_P_ELEMENTWISE) return p.v_kind == LBFQ_V_CHANNEL ? 1 : 0;
     return v_ok ? 2 : 0;
   }
-  const bool alpha_ok = p.v_alpha == nullptr || p.v_smooth_block >= 64;
+  // a 128-key stage holds whole V-smoothing tiles: blocks of 64 keys, or of a multiple of 128
+  const bool alpha_ok = p.v_alpha == nullptr || p.v_smooth_block == 64 || p.v_smooth_block % 128 == 0;
   if (p.qk_bf16) return (v_ok && alpha_ok && (p.p_kind == LBFQ_P_DYNAMIC || p.rm_mode != 2)) ? 2 : 0;
   if (p.v_alpha != nullptr) return (v_ok && alpha_ok && (p.p_kind != LBFQ_P_ELEMENTWISE || p.rm_mode != 2)) ? 2 : 0;
   if (p.p_kind == LBFQ_P_ELEMENTWISE) return (p.v_kind == LBFQ_V_CHANNEL && (p.rm_mode == 0 || p.rm_mode == 1)) ? 1 : 0;

@@ -256,6 +256,10 @@ def _fake_quant_attention_p_requant(q_work, k_work, v_work, qm, v_alpha, q_kmean
     if qm is not None:
         want_est = cfg.rowmax_mode == "qm_k"
         corr, rowmax_g = qm_corr(qm, k_work.to(torch.bfloat16), sm_scale=sm_scale, s_pad=s_pad, want_rowmax=want_est)
+        if want_est and k_work.dtype != torch.bfloat16:
+            # the kernel's bias is formed from the BF16 K, the reference's estimate from K in its own dtype
+            # (attention.py:603-608): for FP16 / FP32 inputs the two products differ
+            _, rowmax_g = qm_corr(qm, k_work, sm_scale=sm_scale, s_pad=s_pad, want_rowmax=True)
         if want_est:
             rowmax_est = rowmax_g.repeat_interleave(cfg.q_smooth_block_size, dim=2).contiguous()
 
@@ -336,6 +340,8 @@ def _fake_quant_attention_p_requant_reference_operands(q_work, k_work, v_work, q
         want_est = cfg.rowmax_mode == "qm_k"
         corr, rowmax_g = qm_corr(qm, k_work.to(torch.bfloat16), sm_scale=sm_scale, s_pad=_round_up(k_work.shape[1], 128),
                                  want_rowmax=want_est)
+        if want_est and k_work.dtype != torch.bfloat16:       # the estimate comes from K in its own dtype
+            _, rowmax_g = qm_corr(qm, k_work, sm_scale=sm_scale, s_pad=_round_up(k_work.shape[1], 128), want_rowmax=True)
         if want_est:
             rowmax_est = rowmax_g.repeat_interleave(cfg.q_smooth_block_size, dim=2).contiguous()
     p_mode = cfg.p_quant
@@ -433,7 +439,7 @@ def fake_quant_attention(
     mx_as_bf16 = (cfg.qk_quant == "mxfp8" and cfg.v_quant != "fp8_block" and cfg.blasst_lambda is None
                   and os.environ.get("LBFQ_ATTN_GENERIC") != "1"
                   and (qm is None or cfg.q_smooth_block_size % 128 == 0)
-                  and (v_alpha is None or cfg.v_smooth_block_size >= 64))
+                  and (v_alpha is None or cfg.v_smooth_block_size == 64 or cfg.v_smooth_block_size % 128 == 0))
     if cfg.p_requant and (_reference_operands or mx_as_bf16):
         o = _fake_quant_attention_p_requant_reference_operands(
             q_work, k_work, v_work, qm, v_alpha, q_km, cfg, sm_scale, out_dtype, out_fp32_exact=_debug_fp32,

@@ -461,3 +461,28 @@ def test_v_smoothing_blocks_that_are_not_the_v_scale_blocks(vsb, vfb):
     v = v * (1.0 + 3.0 * torch.rand(1, 768, 1, 1)).to(v.dtype) + 2.0         # block scales and block means that differ
     g, o = _run_both(q, k, v, cfg)
     _check(g, o)
+
+
+@pytest.mark.parametrize("extra", [dict(), dict(p_quant="dynamic"), dict(qk_quant="mxfp8", v_quant="mxfp8", p_quant="auto")])
+def test_v_smoothing_blocks_that_do_not_tile_a_key_stage(extra):
+    """V-smoothing blocks of 192 keys straddle the 128-key stages of the TMEM-resident kernel: such configurations
+    stay on the general kernel (a randomised sweep found them mis-served)."""
+    cfg = QuantConfig(**{**COMMON, **dict(smoothing="k_only", q_kmeans_k=None, v_smooth_mode="per_block",
+                                          v_smooth_block_size=192), **extra})
+    q, k, v = _qkv(1, 1344, 2, 128, seed=192, outliers=True)
+    v = v + 2.0 * torch.randn(1, 7, 1, 128).repeat_interleave(192, dim=1).to(v.dtype)      # block means that differ
+    g, o = _run_both(q, k, v, cfg)
+    _check(g, o)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+@pytest.mark.parametrize("p_quant", ["elementwise", "mx", "dynamic"])
+def test_rowmax_estimate_for_inputs_that_are_not_bf16(dtype, p_quant):
+    """The reference takes the row-max estimate from K in its own dtype (attention.py:603-608) while the kernel's
+    score bias uses the BF16 K: for FP16 / FP32 inputs the two products differ, and with the estimate frozen
+    (element-wise / mx P) every P value depends on it. A randomised sweep found one product serving both."""
+    cfg = QuantConfig(**{**COMMON, **dict(smoothing="full", q_smooth_block_size=64, q_kmeans_k=None, rowmax_mode="qm_k",
+                                          p_quant=p_quant, p_mx_block_n=64)})
+    q, k, v = _qkv(1, 576, 2, 128, seed=31, outliers=True, dtype=dtype)
+    g, o = _run_both(q, k, v, cfg)
+    _check(g, o)
