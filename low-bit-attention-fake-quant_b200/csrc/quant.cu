@@ -18,10 +18,11 @@ namespace lbfq {
 // a / b rounded to nearest, for a divisor whose correctly rounded reciprocal rb = __frcp_rn(b) is at hand (one
 // scale serves a whole block or column): q = RN(a * rb) is within an ulp of the quotient, the remainder a - q * b is
 // exact in one FMA, and RN(q + rem * rb) is the correctly rounded quotient (Markstein's correction step) -- three
-// instructions instead of a full division per element. Non-finite intermediates take the plain division.
+// instructions instead of a full division per element. Non-finite operands or quotients take the plain division.
 __device__ __forceinline__ float div_rn_rcp(float a, float b, float rb) {
   const float q = a * rb;
-  if (!(fabsf(q) <= 3.0e38f)) return __fdiv_rn(a, b);
+  // inf / NaN operands (e.g. an FP16 overflow) and zero quotients (the correction step would turn -0 into +0)
+  if (!(fabsf(q) <= 3.0e38f) || !(fabsf(b) <= 3.0e38f) || q == 0.f) return __fdiv_rn(a, b);
   return fmaf(fmaf(-q, b, a), rb, q);
 }
 

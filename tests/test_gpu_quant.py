@@ -236,3 +236,21 @@ def test_kmeans_short_and_ragged_slabs(S, D, k):
     want = OA.lloyd_labels(x.permute(0, 2, 1, 3).reshape(6, S, D).float(), k, 4, 1)
     assert int(got.min()) >= 0 and int(got.max()) < k
     assert (got.cpu().long() == want).float().mean().item() > 0.99
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+def test_quantizers_keep_the_sign_of_zero_and_small_values(dtype):
+    """FP16 inputs underflow to +-0; -0 / scale is -0 (code 0x80), which the reciprocal-and-correction division has to
+    hand to the plain division to get right. Codes are compared as bytes."""
+    torch.manual_seed(5)
+    x = (torch.randn(2, 128, 2, 128) * 1e-4)
+    x[:, ::3] = -0.0
+    x[:, 1::7] *= 1e-5                                   # below the FP16 range: +-0 after the cast
+    x = x.to(dtype)
+    c, s = fq.fp8_block_quant(x.to(DEV), 64)
+    oc, os_ = OQ.fp8_block_quant(x, 64)
+    assert torch.equal(c.cpu().view(torch.uint8), oc.view(torch.uint8)) and torch.equal(s.cpu(), os_)
+    c, s = fq.fp8_per_channel_quant(x.to(DEV))
+    oc, os_ = OQ.fp8_per_channel_quant(x)
+    assert torch.equal(c.cpu().view(torch.uint8), oc.view(torch.uint8)) and torch.equal(s.cpu(), os_)
+    assert int((oc.view(torch.uint8) == 0x80).sum()) > 0          # the case does hold negative zeros
