@@ -1,9 +1,8 @@
 """Generates the golden fixtures of this folder from the reference project.
 
-Run once, in a container that has the reference checked out (default
-/root/reference), with no GPU:
+Run once, in a container that has the reference checked out, with no GPU:
 
-    python tests/golden/make_golden.py [/path/to/reference]
+    python tests/golden/make_golden.py /path/to/reference
 
 It imports the reference package (with a stub for its un-vendored
 ``flash_kmeans`` dependency, which is only needed at import time) and calls
@@ -30,7 +29,9 @@ import types
 
 import torch
 
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) < 2:
+    raise SystemExit("usage: make_golden.py /path/to/reference")
+REF = sys.argv[1]
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, ROOT)
