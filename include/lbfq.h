@@ -48,7 +48,9 @@ extern "C" {
 #define LBFQ_LAYOUT_BHDS 2
 
 const char* lbfq_last_error(void);
-/* ABI version of this header; bumped when a signature changes. */
+/* ABI version of this header; bumped when a signature or a struct layout changes.
+ * 2: lbfq_attn_args gained `rowmax_counters` (appended); lbfq_fp8_block_quant_centered added; lbfq_smooth_k takes
+ *    out = NULL. */
 int lbfq_abi_version(void);
 /* Number of kernels this library has launched in the calling process (a plain counter,
  * not thread-safe; used by the benchmark to report its launch count). */
