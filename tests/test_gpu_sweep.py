@@ -82,3 +82,31 @@ def test_random_configurations_match_the_oracle(seed):
         assert torch.isfinite(g).all() and OA.parity_ok(rep), (it, fast, sh, kw, rep)
         ran += 1
     assert ran >= 8
+
+
+@pytest.mark.parametrize("seed", [5, 54])
+def test_random_configurations_host_entry_equals_device_entry(seed):
+    """The host-buffer entry (heads chunks pipelined over three streams) against one device-resident call, bit for
+    bit, over drawn configurations, head counts and chunk sizes."""
+    rnd = random.Random(seed)
+    ran = 0
+    for it in range(60):
+        kw, sh = _draw(rnd)
+        S = sh["S"]
+        if any(S % kw[n] for n in ("q_smooth_block_size", "fp8_block_size", "v_smooth_block_size", "v_fp8_block_size")):
+            continue
+        heads, chunk = rnd.choice([3, 5, 6]), rnd.choice([1, 2, 4])
+        cfg = QuantConfig(**kw)
+        torch.manual_seed(1000 * seed + it)
+        q, k, v = (torch.randn(sh["B"], S, heads, sh["D"]).to(sh["dtype"]) for _ in range(3))
+        k = k + 1
+        try:
+            want = fq.fake_quant_attention(q.to(DEV), k.to(DEV), v.to(DEV), cfg, sm_scale=sh["sm_scale"]).cpu()
+        except (ValueError, NotImplementedError):
+            continue
+        got = fq.fake_quant_attention_host(q.pin_memory(), k.pin_memory(), v.pin_memory(), cfg, sm_scale=sh["sm_scale"],
+                                           heads_per_chunk=chunk)
+        raise_if_device_error(torch.device(DEV))
+        assert torch.equal(got, want), (it, heads, chunk, sh, kw)
+        ran += 1
+    assert ran >= 8
