@@ -181,3 +181,23 @@ def test_rowmax_counters_of_the_oracle():
     assert 1 <= on["max_updates_per_row"] <= 512 // 64
     assert fr == dict(updates=0, rescales=0, upward_updates=0, downward_updates=0, rows_with_update=0, max_updates_per_row=0)
     assert th["updates"] == th["upward_updates"] + th["downward_updates"] and th["rescales"] * 4 < on["rescales"]
+
+
+def test_cross_attention_extension_of_the_oracle():
+    """K / V of their own length: the oracle's extension (the reference's entry takes equal shapes) tracks plain
+    attention over the same keys, and with equal lengths it is the ordinary path."""
+    torch.manual_seed(8)
+    q = torch.randn(1, 256, 2, 64).bfloat16()
+    k = (torch.randn(1, 128, 2, 64) + 1.0).bfloat16()
+    v = torch.randn(1, 128, 2, 64).bfloat16()
+    cfg = QuantConfig(fp8_block_size=64, q_smooth_block_size=64, q_kmeans_k=None, smoothing="full", p_quant="dynamic",
+                      rowmax_mode="qm_k", v_smooth_mode="per_block")
+    o = OA.fake_quant_attention(q, k, v, cfg, faithful=False, cross=True)
+    assert o.shape == q.shape and torch.isfinite(o.float()).all()
+    assert OA.compute_metrics(o, OA.reference_attention(q, k, v))["cosine"] > 0.99
+    same = OA.fake_quant_attention(q, q, q, cfg, faithful=False, cross=True)
+    assert torch.equal(same, OA.fake_quant_attention(q, q, q, cfg, faithful=False))
+    with pytest.raises(ValueError, match="shapes must match"):
+        OA.fake_quant_attention(q, k, v, cfg)
+    with pytest.raises(ValueError, match="cross-attention wants"):
+        OA.fake_quant_attention(q, k, v[:, :64], cfg, cross=True)
