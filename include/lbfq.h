@@ -50,8 +50,21 @@ extern "C" {
 const char* lbfq_last_error(void);
 /* ABI version of this header; bumped when a signature or a struct layout changes.
  * 2: lbfq_attn_args gained `rowmax_counters` (appended); lbfq_fp8_block_quant_centered added; lbfq_smooth_k takes
- *    out = NULL. */
+ *    out = NULL.
+ * 3: lbfq_kmeans_labels and lbfq_qm_corr take a `status` word (bounded waits of their tensor-core kernels report
+ *    there); lbfq_get_flags / lbfq_set_flags replace per-call reads of the LBFQ_* environment variables. */
 int lbfq_abi_version(void);
+
+/* Debug overrides. They are read from the environment (LBFQ_ATTN_GENERIC=1, LBFQ_KMEANS_FFMA=1,
+ * LBFQ_QM_CORR_FFMA=1, LBFQ_UNFUSED_PREPROCESS=1) once, when the library is first used; afterwards they change only
+ * through lbfq_set_flags(). Each keeps a slower cross-check path in use: the general attention kernel, the FP32 FFMA
+ * k-means assignment, the FP32 FFMA qm.K product, the one-kernel-per-step preprocessing. Process-wide, not per thread. */
+#define LBFQ_FLAG_ATTN_GENERIC 1
+#define LBFQ_FLAG_KMEANS_FFMA 2
+#define LBFQ_FLAG_QM_CORR_FFMA 4
+#define LBFQ_FLAG_UNFUSED_PREPROCESS 8
+int lbfq_get_flags(void);
+void lbfq_set_flags(int flags);
 /* Number of kernels this library has launched in the calling process (a plain counter,
  * not thread-safe; used by the benchmark to report its launch count). */
 unsigned long long lbfq_launch_count(void);
@@ -126,6 +139,10 @@ int lbfq_smooth_k(const void* k, int dtype, int B, int S, int H, int D, void* ou
  *    device current); make that first call before any stream capture;
  *  - all calls on a device share the one array: calls that may overlap on the GPU
  *    (different streams) race; serialise them. Nothing needs clearing between calls;
+ *  - the looked-up address is kept per device ordinal for the life of the process: after
+ *    cudaDeviceReset() in the same process it is stale, so do not reset a device this
+ *    entry has been used on. Concurrent first calls from several threads are harmless
+ *    (they look up the same address);
  *  - it calls no cudaMalloc / cudaFree / allocating library routine. */
 int64_t lbfq_smooth_k_static_max_floats(void);
 int lbfq_smooth_k_static(const void* k, int dtype, int B, int S, int H, int D, void* out, float* mean,
@@ -149,11 +166,13 @@ int lbfq_hadamard(const void* x, int dtype, int64_t rows, int H, int D, const in
  * src/low_bit_fake_quant/kmeans.py:77-81. x: NHD of dtype. labels: int32
  * (B*H, S). The centroid seeding hashes the slab index of the unsharded problem,
  * b * total_heads + head_offset + h, so a heads shard reproduces the full run
- * (total_heads <= 0 means "not sharded"). scratch: lbfq_kmeans_scratch_bytes(...) bytes. */
+ * (total_heads <= 0 means "not sharded"). scratch: lbfq_kmeans_scratch_bytes(...) bytes.
+ * status: device int (may be NULL) that the tensor-core assignment sets non-zero when one of its bounded waits
+ * expires; the labels of such a call are valid cluster indices but not a k-means result. */
 int64_t lbfq_kmeans_scratch_bytes(int B, int S, int H, int D, int k);
 int lbfq_kmeans_labels(const void* x, int dtype, int B, int S, int H, int D, int k, int iters,
                        int seed, int head_offset, int total_heads, int32_t* labels, void* scratch,
-                       void* stream);
+                       int32_t* status, void* stream);
 
 /* kmeans.py:84-88: order = stable argsort(labels), inverse[order[j]] = j.
  * labels int32 (BH, S), values in [0, k); order / inverse int64 (BH, S). */
@@ -172,9 +191,10 @@ int lbfq_gather_rows(const void* x, int dtype, int B, int S, int H, int D, const
  *   corr[b,h,g,n]   = (sum_d qm[b,g,h,d] * k_smooth[b,n,h,d]) * sm_scale   (fp32)
  *   rowmax[b,h,g]   = max_n corr[b,h,g,n]
  * qm: fp32 (B, G, H, D); k_smooth: NHD of dtype; corr: fp32 (B, H, G, s_pad),
- * columns >= S zero-filled; rowmax: fp32 (B, H, G), may be NULL. */
+ * columns >= S zero-filled; rowmax: fp32 (B, H, G), may be NULL. status: device int (may be NULL), set non-zero
+ * when a bounded wait of the tensor-core kernel expires. */
 int lbfq_qm_corr(const float* qm, const void* k_smooth, int dtype, int B, int S, int H, int D, int G,
-                 float sm_scale, float* corr, int s_pad, float* rowmax, void* stream);
+                 float sm_scale, float* corr, int s_pad, float* rowmax, int32_t* status, void* stream);
 
 /* ========================= streaming attention ============================ */
 
@@ -270,9 +290,11 @@ int64_t lbfq_attention_workspace_bytes(const lbfq_attn_args* args);
 int lbfq_attention_fwd(const lbfq_attn_args* args, void* workspace, void* stream);
 
 /* Which kernel the calling thread's last lbfq_attention_fwd launched: 0 = the general kernel (P.V folded in
- * registers per key block), 1 = the variant whose output accumulator stays in tensor memory (element-wise P,
- * per-channel V, FP8-block Q/K, no V smoothing, no score bias, no BLASST). Setting the environment variable
- * LBFQ_ATTN_GENERIC=1 keeps every configuration on the general kernel. No counterpart in the reference. */
+ * registers per key block: fp8_block V, the logn / sample8 fills, BLASST combined with a score bias or a
+ * V-smoothing term, the row-max counters), 1 = the kernel whose output accumulator stays in tensor memory (every P
+ * mode, per-channel and mxfp8 V, FP8-block, mxfp8 or BF16 Q / K, score bias, V-smoothing term, the constant and
+ * per-bin BLASST fills). LBFQ_FLAG_ATTN_GENERIC keeps every configuration on the general kernel. No counterpart in
+ * the reference. */
 int lbfq_attention_last_variant(void);
 
 /* ======================= host-buffer plumbing ============================== */

@@ -1,6 +1,9 @@
 // Error text and ABI version of the library.
 #include <stdarg.h>
+#include <stdlib.h>
 #include <string.h>
+
+#include <atomic>
 
 #include "common.cuh"
 
@@ -15,7 +18,39 @@ void set_error(const char* fmt, ...) {
 }  // namespace lbfq
 
 extern "C" const char* lbfq_last_error(void) { return lbfq::g_err; }
-extern "C" int lbfq_abi_version(void) { return 2; }
+extern "C" int lbfq_abi_version(void) { return 3; }
+
+namespace lbfq {
+int sm_count() {
+  static std::atomic<int> cached[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  int n = cached[dev].load(std::memory_order_relaxed);
+  if (n == 0) {
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev].store(n, std::memory_order_relaxed);
+  }
+  return n;
+}
+
+static std::atomic<int> g_flags{-1};
+static int flags_from_env() {
+  auto on = [](const char* name) { const char* v = getenv(name); return v != nullptr && v[0] == '1'; };
+  return (on("LBFQ_ATTN_GENERIC") ? LBFQ_FLAG_ATTN_GENERIC : 0) | (on("LBFQ_KMEANS_FFMA") ? LBFQ_FLAG_KMEANS_FFMA : 0) |
+         (on("LBFQ_QM_CORR_FFMA") ? LBFQ_FLAG_QM_CORR_FFMA : 0) | (on("LBFQ_UNFUSED_PREPROCESS") ? LBFQ_FLAG_UNFUSED_PREPROCESS : 0);
+}
+int debug_flags() {
+  int f = g_flags.load(std::memory_order_relaxed);
+  if (f < 0) {
+    f = flags_from_env();
+    g_flags.store(f, std::memory_order_relaxed);
+  }
+  return f;
+}
+}  // namespace lbfq
+
+extern "C" int lbfq_get_flags(void) { return lbfq::debug_flags(); }
+extern "C" void lbfq_set_flags(int flags) { lbfq::g_flags.store(flags & 0x7fffffff, std::memory_order_relaxed); }
 
 // Kernels launched by this library since load (all entry points count through check_launch()).
 namespace lbfq { unsigned long long g_launches = 0; }

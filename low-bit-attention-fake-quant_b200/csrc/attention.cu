@@ -35,8 +35,6 @@
 // Every mbarrier wait is bounded; on expiry the kernel raises `*status`, all
 // roles leave their loops, TMEM is released and the launch returns.
 
-#include <cstdlib>
-
 #include "attn_prims.cuh"
 
 namespace lbfq {
@@ -523,8 +521,8 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
             c_blk = pow2f(e);
             inv = pow2f(-e);
           } else {
-            c_blk = __fdiv_rn(fmaxf(pmax, 1e-12f), kFp8Max);
-            inv = __fdiv_rn(1.0f, c_blk);
+            c_blk = scale_from_amax(fmaxf(pmax, 1e-12f));      // the reference's `amax / 448` and `p / s` (common.cuh)
+            inv = rcp_approx(c_blk);
           }
           // the conversion saturates at 448, which is the reference's clamp
           const float2 inv2 = make_float2(inv, inv);
@@ -568,7 +566,7 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
 
     // ---- epilogue (attention_triton.py:387-407) ---------------------------------
     if (alive && row_ok) {
-      const float inv_l = __fdiv_rn(1.0f, l_i);
+      const float inv_l = rcp_approx(l_i);                       // the reference's `1.0 / l_i` (attention_triton.py:387)
       const bool has_vsc = p.v_kind == LBFQ_V_CHANNEL;             // selected by flag; the pointer is always valid
       const float* vsc = has_vsc ? p.v_scale + (size_t)bh * D : p.v_scale;
       int64_t drow = row;
@@ -946,7 +944,7 @@ static int make_alpha_ext(const lbfq_attn_args* a, const lbfq::attn::Params& p, 
   using namespace lbfq::attn;
   __nv_bfloat16* ext = reinterpret_cast<__nv_bfloat16*>(dst);
   const size_t total = (size_t)a->B * (a->N / a->v_smooth_block) * a->H * a->D;
-  int ge = (int)((total + 255) / 256); if (ge > 148 * 16) ge = 148 * 16;
+  int ge = (int)((total + 255) / 256); if (ge > sm_count() * 16) ge = sm_count() * 16;
   alpha_ext_kernel<<<ge, 256, 0, st>>>(p.v_alpha, ext, total);
   if (int rc = check_launch("alpha_ext")) return rc;
   auto enc = get_encode();
@@ -1059,7 +1057,7 @@ extern "C" int lbfq_attention_fwd(const lbfq_attn_args* a, void* workspace, void
   if (a->v_alpha) {
     const int gran = alpha_granularity(a);
     const size_t total = (size_t)a->B * (a->N / gran) * a->H * a->D;
-    int g = (int)((total + 255) / 256); if (g > 148 * 8) g = 148 * 8;
+    int g = (int)((total + 255) / 256); if (g > sm_count() * 8) g = sm_count() * 8;
     alpha_prep_kernel<<<g, 256, 0, st>>>(a->v_alpha, (float*)workspace, a->v_scale, a->v_kind, a->B, a->N, a->H, a->D,
                                         gran, a->v_smooth_block, a->v_kind == LBFQ_V_BLOCK ? a->v_block : 1);
     if (int rc = check_launch("alpha_prep")) return rc;
@@ -1091,10 +1089,9 @@ extern "C" int lbfq_attention_fwd(const lbfq_attn_args* a, void* workspace, void
   if (int rc = make_map(&mv, a->v_codes, a->n_pad, a->D, BH, kChunk, a->D)) return rc;
 
   const bool bl = a->use_blasst != 0;
-  // LBFQ_ATTN_GENERIC=1 keeps every configuration on the general kernel (used to cross-check the two)
-  const char* force_generic = getenv("LBFQ_ATTN_GENERIC");
+  // LBFQ_FLAG_ATTN_GENERIC keeps every configuration on the general kernel (used to cross-check the two)
   g_last_variant = 0;
-  const int fv = ((force_generic && force_generic[0] == '1') || p.counters != nullptr) ? 0 : fast_variant(p, bl, mx);
+  const int fv = ((debug_flags() & LBFQ_FLAG_ATTN_GENERIC) || p.counters != nullptr) ? 0 : fast_variant(p, bl, mx);
   if (fv == 1) {
     g_last_variant = 1;
     return launch_fast(mq, mk, mv, mv, p, a->block_n, 1, st);
@@ -1103,7 +1100,7 @@ extern "C" int lbfq_attention_fwd(const lbfq_attn_args* a, void* workspace, void
     LBFQ_REQUIRE(workspace != nullptr, LBFQ_ERR_ARG, "this configuration needs the workspace of lbfq_attention_workspace_bytes");
     __nv_bfloat16* vb = reinterpret_cast<__nv_bfloat16*>((uint8_t*)workspace + alpha_ws_bytes(a));
     const size_t total8 = (size_t)a->B * a->H * a->D * a->n_pad / 8;
-    int g = (int)((total8 + 255) / 256); if (g > 148 * 16) g = 148 * 16;
+    int g = (int)((total8 + 255) / 256); if (g > sm_count() * 16) g = sm_count() * 16;
     v_codes_to_bf16_kernel<<<g, 256, 0, st>>>((const uint8_t*)a->v_codes, vb, a->v_kind, a->v_scale, a->B, a->H, a->D, a->N,
                                               a->n_pad, p.v_block);
     if (int rc = check_launch("v_codes_to_bf16")) return rc;

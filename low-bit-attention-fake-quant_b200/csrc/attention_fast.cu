@@ -452,8 +452,8 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           s_p = pow2f(e);
           inv_p = pow2f(-e);
         } else {
-          s_p = __fdiv_rn(fmaxf(pmax, 1e-12f), kFp8Max);
-          inv_p = __fdiv_rn(1.0f, s_p);
+          s_p = scale_from_amax(fmaxf(pmax, 1e-12f));          // the reference's `amax / 448` and `p / s` (common.cuh)
+          inv_p = rcp_approx(s_p);
         }
       }
       const float2 inv2 = make_float2(inv_p, inv_p);
@@ -581,7 +581,8 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const bool store_ok = row_ok && *abort_flag == 0;          // the loads below are collective, the stores are not
     {
       tc_fence_after();
-      const float inv_l = __fdiv_rn(1.0f, lsum[(t * 2) * kTileM + row_in_tile] + lsum[(t * 2 + 1) * kTileM + row_in_tile]);
+      // the reference's `1.0 / l_i` (attention_triton.py:387)
+      const float inv_l = rcp_approx(lsum[(t * 2) * kTileM + row_in_tile] + lsum[(t * 2 + 1) * kTileM + row_in_tile]);
       const bool has_vsc = p.v_kind == LBFQ_V_CHANNEL;
       const float* vsc = (has_vsc ? p.v_scale + (size_t)bh * D : p.v_scale) + half * HD;
       int64_t drow = rowc;

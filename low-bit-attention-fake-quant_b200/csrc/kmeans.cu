@@ -17,8 +17,6 @@
 // The update uses the same stable counting sort that later produces the token
 // order: tokens of one cluster become one contiguous segment, reduced by one CTA.
 
-#include <cstdlib>
-
 #include "common.cuh"
 #include "kmeans_tc.h"
 
@@ -151,7 +149,8 @@ sort_segments_kernel(const int32_t* __restrict__ labels, int S, int k, int32_t* 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   for (int i = threadIdx.x; i < k; i += blockDim.x) counts[i] = 0;
   __syncthreads();
-  for (int i = threadIdx.x; i < S; i += blockDim.x) atomicAdd(&counts[lab[i]], 1);
+  for (int i = threadIdx.x; i < S; i += blockDim.x)
+    if ((unsigned)lab[i] < (unsigned)k) atomicAdd(&counts[lab[i]], 1);     // a label outside [0, k) is never an index
   __syncthreads();
   if (threadIdx.x == 0) {
     int run = 0;
@@ -162,8 +161,9 @@ sort_segments_kernel(const int32_t* __restrict__ labels, int S, int k, int32_t* 
     for (int i = threadIdx.x; i < 32 * kSortMaxK; i += blockDim.x) (&wc[0][0])[i] = 0;
     __syncthreads();                                          // also orders `offsets` (first pass: thread 0's scan)
     const int i = base + (int)threadIdx.x;
-    const bool valid = i < S;
-    const int lbl = valid ? lab[i] : -1;
+    int lbl = i < S ? lab[i] : -1;
+    const bool valid = (unsigned)lbl < (unsigned)k;
+    if (!valid) lbl = -1;
     const unsigned peers = __match_any_sync(0xffffffffu, lbl);
     const int rank = __popc(peers & ((1u << lane) - 1u));
     if (valid && rank == 0) wc[warp][lbl] = __popc(peers);
@@ -218,8 +218,9 @@ sort_chunks_kernel(const int32_t* __restrict__ labels, const int32_t* __restrict
     if (chunk == 0) seg[bh * (k + 1) + k] = run;
   }
   const int i = chunk * 1024 + (int)threadIdx.x;
-  const bool valid = i < S;
-  const int lbl = valid ? lab[i] : -1;
+  int lbl = i < S ? lab[i] : -1;
+  const bool valid = (unsigned)lbl < (unsigned)k;
+  if (!valid) lbl = -1;
   const unsigned peers = __match_any_sync(0xffffffffu, lbl);
   const int rank = __popc(peers & ((1u << lane) - 1u));
   if (valid && rank == 0) wc[warp][lbl] = __popc(peers);
@@ -229,7 +230,11 @@ sort_chunks_kernel(const int32_t* __restrict__ labels, const int32_t* __restrict
     for (int w = 0; w < 32; ++w) { const int c = wc[w][threadIdx.x]; wc[w][threadIdx.x] = run; run += c; }
   }
   __syncthreads();
-  if (valid) ord[wc[warp][lbl] + rank] = i;
+  // the counts came from the assignment launch: a position is only used while it lies inside the slab
+  if (valid) {
+    const int pos = wc[warp][lbl] + rank;
+    if ((unsigned)pos < (unsigned)S) ord[pos] = i;
+  }
 }
 
 // the same sort for more labels than the shared-memory tables above hold: one warp per label scans the slab
@@ -243,7 +248,8 @@ sort_segments_scan_kernel(const int32_t* __restrict__ labels, int S, int k, int3
   int32_t* ord = order32 + (size_t)blockIdx.x * S;
   for (int i = threadIdx.x; i < k; i += blockDim.x) counts[i] = 0;
   __syncthreads();
-  for (int i = threadIdx.x; i < S; i += blockDim.x) atomicAdd(&counts[lab[i]], 1);
+  for (int i = threadIdx.x; i < S; i += blockDim.x)
+    if ((unsigned)lab[i] < (unsigned)k) atomicAdd(&counts[lab[i]], 1);
   __syncthreads();
   if (threadIdx.x == 0) {
     int run = 0;
@@ -383,7 +389,7 @@ extern "C" int64_t lbfq_kmeans_scratch_bytes(int B, int S, int H, int D, int k) 
 
 extern "C" int lbfq_kmeans_labels(const void* x, int dtype, int B, int S, int H, int D, int k, int iters,
                                   int seed, int head_offset, int total_heads, int32_t* labels, void* scratch,
-                                  void* stream) {
+                                  int32_t* status, void* stream) {
   LBFQ_REQUIRE(B > 0 && S > 0 && H > 0, LBFQ_ERR_ARG, "kmeans: empty input");
   LBFQ_REQUIRE(D == 64 || D == 128, LBFQ_ERR_ARG, "kmeans: D must be 64 or 128; got %d", D);
   LBFQ_REQUIRE(k > 0 && k <= S, LBFQ_ERR_ARG, "n_clusters must be in [1, S]; got %d for S=%d", k, S);
@@ -396,17 +402,20 @@ extern "C" int lbfq_kmeans_labels(const void* x, int dtype, int B, int S, int H,
   KmScratch sc;
   scratch_layout(BH, S, D, k, (uint8_t*)scratch, &sc);
   if (iters < 1) iters = 1;
+  // every label is a valid cluster index from here on, whatever happens to an assignment launch (a launch whose
+  // bounded wait expires leaves some labels unwritten and says so in `status`; the sorts index by label)
+  LBFQ_CUDA_OK(cudaMemsetAsync(labels, 0, sizeof(int32_t) * (size_t)BH * S, st));
+  LBFQ_CUDA_OK(cudaMemsetAsync(sc.order32, 0, sizeof(int32_t) * (size_t)BH * S, st));     // likewise every sorted position
   LBFQ_DISPATCH_DTYPE(dtype, T,
       init_centroids_kernel<T><<<BH * k, 128, 0, st>>>((const T*)x, S, H, D, k, (uint32_t)seed, head_offset, total_heads, sc.cent, sc.cnorm));
   if (int rc = check_launch("kmeans init")) return rc;
   const int ntile = (S + kTok - 1) / kTok;
-  // LBFQ_KMEANS_FFMA=1 keeps the FP32 FFMA assignment (used to cross-check the two)
-  const char* force_ffma = getenv("LBFQ_KMEANS_FFMA");
-  const bool tc = kmeans_tc_eligible(dtype, D, k) && !(force_ffma && force_ffma[0] == '1');
+  // LBFQ_FLAG_KMEANS_FFMA keeps the FP32 FFMA assignment (used to cross-check the two)
+  const bool tc = kmeans_tc_eligible(dtype, D, k) && !(debug_flags() & LBFQ_FLAG_KMEANS_FFMA);
   for (int it = 0; it < iters; ++it) {
     if (tc) {
       // the counts are only wanted when a sort follows (not after the last assignment)
-      if (int rc = kmeans_tc_assign(x, B, S, H, D, k, sc.cent, sc.cnorm, sc.split, labels, it + 1 < iters ? sc.hist : nullptr, st)) return rc;
+      if (int rc = kmeans_tc_assign(x, B, S, H, D, k, sc.cent, sc.cnorm, sc.split, labels, it + 1 < iters ? sc.hist : nullptr, status, st)) return rc;
     } else {
       LBFQ_DISPATCH_DTYPE(dtype, T,
           assign_kernel<T><<<BH * ntile, kThreads, 0, st>>>((const T*)x, S, H, D, k, sc.cent, sc.cnorm, labels));

@@ -58,7 +58,8 @@ constexpr int kTcThreads = (kTcWarps + 1) * 32;
 template <int D>
 __global__ void __launch_bounds__(kTcThreads)
 assign_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_c, int S, int H, int k,
-                 const float* __restrict__ cnorm, int32_t* __restrict__ labels, int32_t* __restrict__ hist) {
+                 const float* __restrict__ cnorm, int32_t* __restrict__ labels, int32_t* __restrict__ hist,
+                 int32_t* __restrict__ status) {
   constexpr int NP = D / 64;                         // 64-channel panels (one 128-byte swizzle row each)
   constexpr int kA = kTcTok * 128;                   // bytes per token panel
   constexpr int kB = 3 * kTcCen * 128;               // bytes per centroid panel (three pieces)
@@ -89,11 +90,8 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
   const int n = min(kTcTiles, ntile - tile0);        // tiles of this CTA (>= 1)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if ((sbase & 1023u) != 0) {
-    // never expected; the labels are marked invalid so that the caller's checks see it
-    for (int i = 0; i < n; ++i) {
-      const int tok = (tile0 + i) * kTcTok + (int)threadIdx.x;
-      if ((int)threadIdx.x < kTcTok && tok < S) labels[(size_t)bh * S + tok] = -1;
-    }
+    // never expected: reported through the status word (the labels keep the valid values they held)
+    if (threadIdx.x == 0 && status != nullptr) atomicCAS(status, 0, 55);
     return;
   }
 
@@ -125,7 +123,7 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
   };
   auto issue_mma = [&](int i) -> bool {               // thread 0: Gram block of tile i into TMEM buffer i & 1
     const int buf = i & 1;
-    if (!mbar_wait(bar_full(buf), (uint32_t)((i >> 1) & 1), abort_flag, nullptr, 1)) return false;
+    if (!mbar_wait(bar_full(buf), (uint32_t)((i >> 1) & 1), abort_flag, status, 51)) return false;
     tc_fence_after();
     const uint32_t idesc = make_idesc_bf16(kTcCen);
     bool first = true;
@@ -159,11 +157,11 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
       for (int i = 0; i < n; ++i) {
         const int buf = i & 1;
         // the TMEM buffer is free once every consumer thread has read tile i - 2 out of it
-        if (i >= 2 && !mbar_wait(bar_tfree(buf), (uint32_t)(((i - 2) >> 1) & 1), abort_flag, nullptr, 3)) break;
+        if (i >= 2 && !mbar_wait(bar_tfree(buf), (uint32_t)(((i - 2) >> 1) & 1), abort_flag, status, 53)) break;
         if (!issue_mma(i)) break;
         if (i + 2 < n) {
           // the tile's shared-memory buffer is free once its MMAs have completed: refill it two tiles ahead
-          if (!mbar_wait(bar_done(buf), (uint32_t)((i >> 1) & 1), abort_flag, nullptr, 4)) break;
+          if (!mbar_wait(bar_done(buf), (uint32_t)((i >> 1) & 1), abort_flag, status, 54)) break;
           mbar_expect_tx(bar_full(buf), NP * kA);
           load_tile(i + 2);
         }
@@ -177,7 +175,7 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
     for (int c = 0; c < kTcCen; ++c) cn[c] = c < k ? cnorm[(size_t)bh * k + c] : INFINITY;
     for (int i = 0; i < n; ++i) {
       const int buf = i & 1;
-      const bool ok = mbar_wait(bar_done(buf), (uint32_t)((i >> 1) & 1), abort_flag, nullptr, 2);
+      const bool ok = mbar_wait(bar_done(buf), (uint32_t)((i >> 1) & 1), abort_flag, status, 52);
       if (!__all_sync(0xffffffffu, ok)) break;           // a given-up wait ends every role's loop
       tc_fence_after();
       const uint32_t trow = tmem + buf * kTcCen + ((uint32_t)(warp * 32) << 16);
@@ -237,14 +235,14 @@ PFN_cuTensorMapEncodeTiled_v12000 encoder() {
 
 template <int D>
 int launch_assign(const CUtensorMap& mx, const CUtensorMap& mc, int BH, int S, int H, int k, const float* cnorm,
-                  int32_t* labels, int32_t* hist, cudaStream_t st) {
+                  int32_t* labels, int32_t* hist, int32_t* status, cudaStream_t st) {
   constexpr int NP = D / 64;
   const int smem_bytes = NP * (2 * kTcTok * 128 + 3 * kTcCen * 128) + 64 + kTcCen * 4;
   auto kern = assign_tc_kernel<D>;
   LBFQ_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
   const int ntile = (S + kTcTok - 1) / kTcTok;
   const int per_bh = (ntile + kTcTiles - 1) / kTcTiles;
-  kern<<<BH * per_bh, kTcThreads, smem_bytes, st>>>(mx, mc, S, H, k, cnorm, labels, hist);
+  kern<<<BH * per_bh, kTcThreads, smem_bytes, st>>>(mx, mc, S, H, k, cnorm, labels, hist, status);
   return check_launch("kmeans assign (tensor cores)");
 }
 
@@ -257,11 +255,11 @@ int kmeans_tc_chunk_tokens() { return kTcTiles * kTcTok; }
 size_t kmeans_tc_split_bytes(int BH, int D) { return (size_t)BH * 3 * kTcCen * D * sizeof(__nv_bfloat16); }
 
 int kmeans_tc_assign(const void* x, int B, int S, int H, int D, int k, const float* cent, const float* cnorm,
-                     void* split, int32_t* labels, int32_t* hist, cudaStream_t st) {
+                     void* split, int32_t* labels, int32_t* hist, int32_t* status, cudaStream_t st) {
   const int BH = B * H;
   const size_t total = (size_t)BH * kTcCen * D;
   int g = (int)((total + 255) / 256);
-  if (g > 148 * 8) g = 148 * 8;
+  if (g > sm_count() * 8) g = sm_count() * 8;
   split_centroids_kernel<<<g, 256, 0, st>>>(cent, BH, k, D, (__nv_bfloat16*)split);
   if (int rc = check_launch("kmeans centroid split")) return rc;
 
@@ -290,8 +288,8 @@ int kmeans_tc_assign(const void* x, int B, int S, int H, int D, int k, const flo
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     LBFQ_REQUIRE(r == CUDA_SUCCESS, LBFQ_ERR_CUDA, "cuTensorMapEncodeTiled (centroids) failed with code %d", (int)r);
   }
-  if (D == 128) return launch_assign<128>(mx, mc, BH, S, H, k, cnorm, labels, hist, st);
-  return launch_assign<64>(mx, mc, BH, S, H, k, cnorm, labels, hist, st);
+  if (D == 128) return launch_assign<128>(mx, mc, BH, S, H, k, cnorm, labels, hist, status, st);
+  return launch_assign<64>(mx, mc, BH, S, H, k, cnorm, labels, hist, status, st);
 }
 
 }  // namespace lbfq

@@ -10,7 +10,8 @@ size_t kmeans_tc_split_bytes(int BH, int D);
 // tokens per assignment CTA: the granularity of the per-chunk label counts
 int kmeans_tc_chunk_tokens();
 // x: (B, S, H, D) bf16; cent (B*H, k, D) fp32; cnorm (B*H, k) fp32; split: kmeans_tc_split_bytes scratch;
-// hist: (B*H, ceil(S / chunk_tokens), 64) int32 per-chunk label counts, or NULL
+// hist: (B*H, ceil(S / chunk_tokens), 64) int32 per-chunk label counts, or NULL; status: device word raised when
+// a bounded wait expires (the labels of that call are then incomplete), or NULL
 int kmeans_tc_assign(const void* x, int B, int S, int H, int D, int k, const float* cent, const float* cnorm,
-                     void* split, int32_t* labels, int32_t* hist, cudaStream_t st);
+                     void* split, int32_t* labels, int32_t* hist, int32_t* status, cudaStream_t st);
 }  // namespace lbfq

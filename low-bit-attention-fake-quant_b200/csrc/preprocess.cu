@@ -9,7 +9,7 @@
 // D, one read of the source per pass, means kept in fp32 and the centred
 // values rounded once into the input dtype exactly as the reference stores them.
 
-#include <cstdlib>
+#include <atomic>
 
 #include "common.cuh"
 #include "qm_corr_tc.h"
@@ -98,7 +98,7 @@ __global__ void k_mean_kernel(const float* __restrict__ partial, int ntile, int 
   if (d >= D) return;
   float acc = 0.f;
   for (int t = 0; t < ntile; ++t) acc += partial[((size_t)bh * ntile + t) * D + d];
-  mean[(size_t)bh * D + d] = __fdiv_rn(acc, (float)S);
+  mean[(size_t)bh * D + d] = acc * rcp_approx((float)S);        // the reference's `acc / S` (preprocess.py:29)
 }
 
 template <typename T>
@@ -137,7 +137,7 @@ block_mean_sub_kernel(const T* __restrict__ x, T* __restrict__ out, float* __res
   const size_t rstride = (size_t)H * D;
   column_sums<T>(x + base, rstride, block, D, buf, sums);
   if (threadIdx.x < D) {
-    float m = __fdiv_rn(sums[threadIdx.x], (float)block);
+    float m = sums[threadIdx.x] * rcp_approx((float)block);      // the reference's `sum / BLK` (preprocess.py:82,117)
     sums[threadIdx.x] = m;
     mean[(((size_t)b * nblk + blk) * H + h) * D + threadIdx.x] = m;
   }
@@ -219,7 +219,9 @@ label_order_kernel(const int32_t* __restrict__ labels, int S, int k, int64_t* __
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   for (int i = threadIdx.x; i < k; i += blockDim.x) counts[i] = 0;
   __syncthreads();
-  for (int i = threadIdx.x; i < S; i += blockDim.x) atomicAdd(&counts[lab[i]], 1);
+  // a label outside [0, k) (never produced by this library) is skipped, not used as an index
+  for (int i = threadIdx.x; i < S; i += blockDim.x)
+    if ((unsigned)lab[i] < (unsigned)k) atomicAdd(&counts[lab[i]], 1);
   __syncthreads();
   if (threadIdx.x == 0) {
     int run = 0;
@@ -229,8 +231,9 @@ label_order_kernel(const int32_t* __restrict__ labels, int S, int k, int64_t* __
     for (int i = threadIdx.x; i < 32 * kOrderMaxK; i += blockDim.x) (&wc[0][0])[i] = 0;
     __syncthreads();
     const int i = base + (int)threadIdx.x;
-    const bool valid = i < S;
-    const int lbl = valid ? lab[i] : -1;
+    int lbl = i < S ? lab[i] : -1;
+    const bool valid = (unsigned)lbl < (unsigned)k;
+    if (!valid) lbl = -1;
     const unsigned peers = __match_any_sync(0xffffffffu, lbl);
     const int rank = __popc(peers & ((1u << lane) - 1u));
     if (valid && rank == 0) wc[warp][lbl] = __popc(peers);
@@ -261,7 +264,8 @@ label_order_scan_kernel(const int32_t* __restrict__ labels, int S, int k, int64_
   int64_t* inv = inverse + (size_t)blockIdx.x * S;
   for (int i = threadIdx.x; i < k; i += blockDim.x) counts[i] = 0;
   __syncthreads();
-  for (int i = threadIdx.x; i < S; i += blockDim.x) atomicAdd(&counts[lab[i]], 1);
+  for (int i = threadIdx.x; i < S; i += blockDim.x)
+    if ((unsigned)lab[i] < (unsigned)k) atomicAdd(&counts[lab[i]], 1);
   __syncthreads();
   if (threadIdx.x == 0) {
     int run = 0;
@@ -389,7 +393,7 @@ using namespace lbfq;
 
 static int grid_for(size_t work_items, int threads) {
   size_t g = (work_items + threads - 1) / threads;
-  const size_t cap = 148 * 16;
+  const size_t cap = (size_t)sm_count() * 16;
   return (int)(g < cap ? (g ? g : 1) : cap);
 }
 
@@ -399,8 +403,9 @@ extern "C" int64_t lbfq_smooth_k_scratch_floats(int B, int S, int H, int D) {
 
 extern "C" int lbfq_smooth_k(const void* k, int dtype, int B, int S, int H, int D, void* out, float* mean,
                              float* partial, void* stream) {
-  LBFQ_REQUIRE(B > 0 && S > 0 && H > 0 && D > 0 && D % 8 == 0 && D <= 128, LBFQ_ERR_ARG,
-               "smooth_k: unsupported shape (%d,%d,%d,%d)", B, S, H, D);
+  LBFQ_REQUIRE(B > 0 && S > 0 && H > 0, LBFQ_ERR_ARG, "smooth_k: unsupported shape (%d,%d,%d,%d)", B, S, H, D);
+  // the column-sum tiles are laid out for 8 or 16 threads per row: other head dimensions would run past them
+  LBFQ_REQUIRE(D == 64 || D == 128, LBFQ_ERR_ARG, "smooth_k: D must be 64 or 128; got %d", D);
   cudaStream_t st = (cudaStream_t)stream;
   const int ntile = (S + kSumRows - 1) / kSumRows;
   LBFQ_DISPATCH_DTYPE(dtype, T,
@@ -431,7 +436,9 @@ constexpr int64_t kStaticScratchFloats = 1 << 20;
 static __device__ __align__(256) float g_smooth_k_scratch[kStaticScratchFloats];
 
 constexpr int kMaxDevices = 64;
-static float* g_scratch_ptr[kMaxDevices] = {};      // device address of the array, per device ordinal
+// device address of the array, per device ordinal (threads that make the first call on a device together all look
+// up, and store, the same address)
+static std::atomic<float*> g_scratch_ptr[kMaxDevices];
 
 // Host code must not pass `g_smooth_k_scratch` itself to a kernel: in host code that
 // name is only a handle. The device address is asked for once per device, with that
@@ -440,13 +447,15 @@ static int static_scratch_for_current_device(float** out) {
   int dev = -1;
   LBFQ_CUDA_OK(cudaGetDevice(&dev));
   LBFQ_REQUIRE(dev >= 0 && dev < kMaxDevices, LBFQ_ERR_UNSUPPORTED, "device ordinal %d outside the supported 0..%d", dev, kMaxDevices - 1);
-  if (g_scratch_ptr[dev] == nullptr) {
+  float* cached = g_scratch_ptr[dev].load(std::memory_order_acquire);
+  if (cached == nullptr) {
     void* ptr = nullptr;
     LBFQ_CUDA_OK(cudaGetSymbolAddress(&ptr, g_smooth_k_scratch));
     LBFQ_REQUIRE(ptr != nullptr, LBFQ_ERR_CUDA, "cudaGetSymbolAddress returned a null address");
-    g_scratch_ptr[dev] = static_cast<float*>(ptr);
+    cached = static_cast<float*>(ptr);
+    g_scratch_ptr[dev].store(cached, std::memory_order_release);
   }
-  *out = g_scratch_ptr[dev];
+  *out = cached;
   return LBFQ_OK;
 }
 
@@ -455,7 +464,8 @@ extern "C" int64_t lbfq_smooth_k_static_max_floats(void) { return kStaticScratch
 extern "C" int lbfq_smooth_k_static(const void* k, int dtype, int B, int S, int H, int D, void* out, float* mean,
                                     void* stream) {
   const int64_t need = lbfq_smooth_k_scratch_floats(B, S, H, D);
-  LBFQ_REQUIRE(B > 0 && S > 0 && H > 0 && D > 0, LBFQ_ERR_ARG, "smooth_k: unsupported shape (%d,%d,%d,%d)", B, S, H, D);
+  LBFQ_REQUIRE(B > 0 && S > 0 && H > 0, LBFQ_ERR_ARG, "smooth_k: unsupported shape (%d,%d,%d,%d)", B, S, H, D);
+  LBFQ_REQUIRE(D == 64 || D == 128, LBFQ_ERR_ARG, "smooth_k: D must be 64 or 128; got %d", D);
   LBFQ_REQUIRE(need <= kStaticScratchFloats, LBFQ_ERR_ARG,
                "smooth_k_static: this shape needs %lld scratch floats (B*H*ceil(S/256)*D) but the built-in array holds "
                "%lld; use lbfq_smooth_k with caller scratch", (long long)need, (long long)kStaticScratchFloats);
@@ -518,7 +528,7 @@ extern "C" int lbfq_gather_rows(const void* x, int dtype, int B, int S, int H, i
 }
 
 extern "C" int lbfq_qm_corr(const float* qm, const void* k_smooth, int dtype, int B, int S, int H, int D, int G,
-                            float sm_scale, float* corr, int s_pad, float* rowmax, void* stream) {
+                            float sm_scale, float* corr, int s_pad, float* rowmax, int32_t* status, void* stream) {
   LBFQ_REQUIRE(D % 32 == 0 && D <= 128, LBFQ_ERR_ARG, "qm_corr: D must be 64 or 128; got %d", D);
   LBFQ_REQUIRE(s_pad >= S && s_pad % kCT == 0, LBFQ_ERR_ARG, "qm_corr: s_pad=%d must be >= S and a multiple of %d", s_pad, kCT);
   LBFQ_REQUIRE(G > 0, LBFQ_ERR_ARG, "qm_corr: G must be positive");
@@ -527,10 +537,9 @@ extern "C" int lbfq_qm_corr(const float* qm, const void* k_smooth, int dtype, in
     fill_kernel<<<grid_for((size_t)B * H * G, 256), 256, 0, st>>>(rowmax, (size_t)B * H * G, -INFINITY);
     if (int rc = check_launch("fill")) return rc;
   }
-  // BF16 keys take the tensor-core kernel; LBFQ_QM_CORR_FFMA=1 keeps the FP32 FFMA kernel (the cross-check)
-  const char* force_ffma = getenv("LBFQ_QM_CORR_FFMA");
-  if (qm_corr_tc_eligible(dtype, D, S, k_smooth) && !(force_ffma && force_ffma[0] == '1'))
-    return qm_corr_tc(qm, k_smooth, B, S, H, D, G, sm_scale, corr, s_pad, rowmax, st);
+  // BF16 keys take the tensor-core kernel; LBFQ_FLAG_QM_CORR_FFMA keeps the FP32 FFMA kernel (the cross-check)
+  if (qm_corr_tc_eligible(dtype, D, S, k_smooth) && !(debug_flags() & LBFQ_FLAG_QM_CORR_FFMA))
+    return qm_corr_tc(qm, k_smooth, B, S, H, D, G, sm_scale, corr, s_pad, rowmax, status, st);
   const int grid = B * H * ((G + kCT - 1) / kCT) * (s_pad / kCT);
   LBFQ_DISPATCH_DTYPE(dtype, T,
       qm_corr_kernel<T><<<grid, kThreads, 0, st>>>(qm, (const T*)k_smooth, B, S, H, D, G, sm_scale, corr, s_pad, rowmax));

@@ -45,7 +45,8 @@ __device__ __forceinline__ void atomic_max_f32(float* addr, float v) {
 template <int D>
 __global__ void __launch_bounds__(kQcThreads, 1)
 qm_corr_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const float* __restrict__ qm, int S, int H, int G,
-                  float sm_scale, float* __restrict__ corr, int s_pad, float* __restrict__ rowmax) {
+                  float sm_scale, float* __restrict__ corr, int s_pad, float* __restrict__ rowmax,
+                  int32_t* __restrict__ status) {
   constexpr int NP = D / 64;                         // 64-channel panels (one 128-byte swizzle row each)
   constexpr int kA = kKeys * 128;                    // bytes per key panel
   constexpr int kB = kGroups * 128;                  // bytes per (piece, panel) of the group means
@@ -128,7 +129,7 @@ qm_corr_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const float* __restr
   };
   auto issue_mma = [&](int i) -> bool {               // thread 0: products of tile i into TMEM buffer i & 1
     const int buf = i & 1;
-    if (!mbar_wait(bar_full(buf), (uint32_t)((i >> 1) & 1), abort_flag, nullptr, 1)) return false;
+    if (!mbar_wait(bar_full(buf), (uint32_t)((i >> 1) & 1), abort_flag, status, 61)) return false;
     tc_fence_after();
     const uint32_t idesc = make_idesc_bf16(kGroups);
     bool first = true;
@@ -165,7 +166,7 @@ qm_corr_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const float* __restr
     // the next tile's MMAs first (its TMEM buffer was read out two tiles ago, before the last barrier)
     if (threadIdx.x == 0 && i + 1 < n_tiles) issue_mma(i + 1);
     __syncwarp();
-    const bool ok = mbar_wait(bar_done(buf), (uint32_t)((i >> 1) & 1), abort_flag, nullptr, 2);
+    const bool ok = mbar_wait(bar_done(buf), (uint32_t)((i >> 1) & 1), abort_flag, status, 62);
     const bool all_ok = __all_sync(0xffffffffu, ok);
     if (threadIdx.x == 0 && ok && i + 2 < n_tiles) load_tile(i + 2);   // the tile's shared-memory buffer is free again
     __syncwarp();
@@ -233,7 +234,7 @@ PFN_cuTensorMapEncodeTiled_v12000 qc_encoder() {
 
 template <int D>
 int launch_qm_corr(const CUtensorMap& mk, const float* qm, int B, int S, int H, int G, float sm_scale, float* corr,
-                   int s_pad, float* rowmax, cudaStream_t st) {
+                   int s_pad, float* rowmax, int32_t* status, cudaStream_t st) {
   constexpr int NP = D / 64;
   const int smem_bytes = NP * (2 * kKeys * 128 + 3 * kGroups * 128) + 64 + 1024;
   auto kern = qm_corr_tc_kernel<D>;
@@ -241,7 +242,7 @@ int launch_qm_corr(const CUtensorMap& mk, const float* qm, int B, int S, int H, 
   const int ntile = (s_pad + kKeys - 1) / kKeys;
   const int per_bh = (ntile + kTiles - 1) / kTiles;
   dim3 grid(B * H * per_bh, (G + kGroups - 1) / kGroups, 1);
-  kern<<<grid, kQcThreads, smem_bytes, st>>>(mk, qm, S, H, G, sm_scale, corr, s_pad, rowmax);
+  kern<<<grid, kQcThreads, smem_bytes, st>>>(mk, qm, S, H, G, sm_scale, corr, s_pad, rowmax, status);
   return check_launch("qm_corr (tensor cores)");
 }
 
@@ -253,7 +254,7 @@ bool qm_corr_tc_eligible(int dtype, int D, int S, const void* k_smooth) {
 }
 
 int qm_corr_tc(const float* qm, const void* k_smooth, int B, int S, int H, int D, int G, float sm_scale, float* corr,
-               int s_pad, float* rowmax, cudaStream_t st) {
+               int s_pad, float* rowmax, int32_t* status, cudaStream_t st) {
   auto enc = qc_encoder();
   LBFQ_REQUIRE(enc != nullptr, LBFQ_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
   CUtensorMap mk;
@@ -266,8 +267,8 @@ int qm_corr_tc(const float* qm, const void* k_smooth, int B, int S, int H, int D
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   LBFQ_REQUIRE(r == CUDA_SUCCESS, LBFQ_ERR_CUDA, "cuTensorMapEncodeTiled (keys) failed with code %d", (int)r);
-  if (D == 128) return launch_qm_corr<128>(mk, qm, B, S, H, G, sm_scale, corr, s_pad, rowmax, st);
-  return launch_qm_corr<64>(mk, qm, B, S, H, G, sm_scale, corr, s_pad, rowmax, st);
+  if (D == 128) return launch_qm_corr<128>(mk, qm, B, S, H, G, sm_scale, corr, s_pad, rowmax, status, st);
+  return launch_qm_corr<64>(mk, qm, B, S, H, G, sm_scale, corr, s_pad, rowmax, status, st);
 }
 
 }  // namespace lbfq

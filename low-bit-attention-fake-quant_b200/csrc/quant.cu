@@ -8,23 +8,13 @@
 // quantising read of the same <= 64 KB tile is served by L1/L2) and writes the
 // e4m3 codes straight into the layout the consumer wants: NHD for the public
 // API, BHSD / BHDS (transposed through shared memory) for the attention kernel.
-// Arithmetic is the reference's: amax floored at 1e-4, scale = amax / 448 by
-// IEEE division, code = e4m3_rn_sat(clamp(x / scale, +-448)).
+// Arithmetic is the reference's as its Triton kernels execute it on the GPU: amax floored at 1e-4,
+// scale = amax * fl32(1/448), code = e4m3_rn_sat(clamp(x * rcp.approx(scale), +-448)) -- see common.cuh. One
+// reciprocal per scale block, one multiplication per element.
 
 #include "common.cuh"
 
 namespace lbfq {
-
-// a / b rounded to nearest, for a divisor whose correctly rounded reciprocal rb = __frcp_rn(b) is at hand (one
-// scale serves a whole block or column): q = RN(a * rb) is within an ulp of the quotient, the remainder a - q * b is
-// exact in one FMA, and RN(q + rem * rb) is the correctly rounded quotient (Markstein's correction step) -- three
-// instructions instead of a full division per element. Non-finite operands or quotients take the plain division.
-__device__ __forceinline__ float div_rn_rcp(float a, float b, float rb) {
-  const float q = a * rb;
-  // inf / NaN operands (e.g. an FP16 overflow) and zero quotients (the correction step would turn -0 into +0)
-  if (!(fabsf(q) <= 3.0e38f) || !(fabsf(b) <= 3.0e38f) || q == 0.f) return __fdiv_rn(a, b);
-  return fmaf(fmaf(-q, b, a), rb, q);
-}
 
 constexpr int kThreads = 256;
 constexpr int kVec = 8;          // elements of D per thread access
@@ -187,19 +177,19 @@ fp8_block_quant_kernel(const T* __restrict__ x, CodeDst dst, float* __restrict__
     float m = red[0];
 #pragma unroll
     for (int i = 1; i < kThreads / 32; ++i) m = fmaxf(m, red[i]);
-    float sc = __fdiv_rn(fmaxf(m, kAmaxFloor), kFp8Max);
+    float sc = scale_from_amax(fmaxf(m, kAmaxFloor));
     s_scale = sc;
     scale[((size_t)b * nblk + blk) * dst.H + h] = sc;
   }
   __syncthreads();
   const float sc = s_scale;
-  const float rsc = __frcp_rn(sc);
+  const float rsc = rcp_approx(sc);
   store_tile(dst, b, h, s0, block_s, tbuf, [&](int r, int dd, float (&q)[kVec]) {
     float v[kVec];
     load8<T>(src + r * rstride + dd, v);
     centre(v, dd);
 #pragma unroll
-    for (int i = 0; i < kVec; ++i) q[i] = fminf(fmaxf(div_rn_rcp(v[i], sc, rsc), -kFp8Max), kFp8Max);
+    for (int i = 0; i < kVec; ++i) q[i] = fminf(fmaxf(v[i] * rsc, -kFp8Max), kFp8Max);
   });
 }
 
@@ -210,7 +200,7 @@ template <typename T>
 __global__ void __launch_bounds__(kThreads)
 mxfp8_v_quant_kernel(const T* __restrict__ x, CodeDst dst, float* __restrict__ scale, int block_s) {
   __shared__ float col_amax[kThreads / 8][128 + 1];   // [row-lane][d]
-  __shared__ float col_scale[128];
+  __shared__ float col_scale[128];                    // 2^-e: the exact reciprocal of the power-of-two scale
   __shared__ __align__(16) uint8_t tbuf[128 * kTPitch];
   const int nblk = dst.S / block_s;
   const int blk = blockIdx.x % nblk;
@@ -237,9 +227,9 @@ mxfp8_v_quant_kernel(const T* __restrict__ x, CodeDst dst, float* __restrict__ s
   if (threadIdx.x < D) {
     float m = 0.f;
     for (int r = 0; r < rpi; ++r) m = fmaxf(m, col_amax[r][threadIdx.x]);
-    float sc = pow2f(pow2_scale_exp(fmaxf(m, kAmaxFloor)));
-    col_scale[threadIdx.x] = sc;
-    scale[(((size_t)b * nblk + blk) * dst.H + h) * D + threadIdx.x] = sc;
+    const int e = pow2_scale_exp(fmaxf(m, kAmaxFloor));
+    col_scale[threadIdx.x] = pow2f(-e);
+    scale[(((size_t)b * nblk + blk) * dst.H + h) * D + threadIdx.x] = pow2f(e);
   }
   __syncthreads();
   store_tile(dst, b, h, s0, block_s, tbuf, [&](int r, int dd, float (&q)[kVec]) {
@@ -247,7 +237,7 @@ mxfp8_v_quant_kernel(const T* __restrict__ x, CodeDst dst, float* __restrict__ s
     load8<T>(src + r * rstride + dd, v);
 #pragma unroll
     for (int i = 0; i < kVec; ++i)
-      q[i] = fminf(fmaxf(__fdiv_rn(v[i], col_scale[dd + i]), -kFp8Max), kFp8Max);
+      q[i] = fminf(fmaxf(v[i] * col_scale[dd + i], -kFp8Max), kFp8Max);     // x / 2^e, exact
   });
 }
 
@@ -289,7 +279,7 @@ mxfp8_qk_quant_kernel(const T* __restrict__ x, CodeDst dst, float* __restrict__ 
     if (r < nrows) {
       int e = pow2_scale_exp(fmaxf(am, kAmaxFloor));
       float sc = pow2f(e);
-      grp_scale[r][d0 / kVec] = sc;
+      grp_scale[r][d0 / kVec] = pow2f(-e);          // the exact reciprocal
       if ((d0 % block_d) == 0) {
         int g = d0 / block_d;
         scale[((((size_t)b * dst.S + s0 + r) * dst.H + h)) * ngrp + g] = sc;
@@ -307,9 +297,9 @@ mxfp8_qk_quant_kernel(const T* __restrict__ x, CodeDst dst, float* __restrict__ 
   store_tile(dst, b, h, s0, nrows, tbuf, [&](int r, int dd, float (&q)[kVec]) {
     float v[kVec];
     load8<T>(src + r * rstride + dd, v);
-    const float sc = grp_scale[r][dd / kVec];
+    const float rsc = grp_scale[r][dd / kVec];
 #pragma unroll
-    for (int i = 0; i < kVec; ++i) q[i] = fminf(fmaxf(__fdiv_rn(v[i], sc), -kFp8Max), kFp8Max);
+    for (int i = 0; i < kVec; ++i) q[i] = fminf(fmaxf(v[i] * rsc, -kFp8Max), kFp8Max);      // x / 2^e, exact
   });
 }
 
@@ -355,13 +345,12 @@ channel_amax_kernel(const T* __restrict__ x, int S, int H, int D, unsigned int* 
 
 __global__ void channel_scale_kernel(float* scale, int n) {
   int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i < n) scale[i] = __fdiv_rn(fmaxf(scale[i], kAmaxFloor), kFp8Max);   // in place: amax -> scale
+  if (i < n) scale[i] = scale_from_amax(fmaxf(scale[i], kAmaxFloor));      // in place: amax -> scale
 }
 
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
 channel_quant_kernel(const T* __restrict__ x, CodeDst dst, const float* __restrict__ scale) {
-  __shared__ float col_scale[128];
   __shared__ float col_rcp[128];
   __shared__ __align__(16) uint8_t tbuf[128 * kTPitch];
   const int ntile = (dst.S + kTChunk - 1) / kTChunk;
@@ -374,9 +363,7 @@ channel_quant_kernel(const T* __restrict__ x, CodeDst dst, const float* __restri
   const T* src = x + (((size_t)b * dst.S + s0) * dst.H + h) * D;
   const size_t rstride = (size_t)dst.H * D;
   if (threadIdx.x < D) {
-    const float sc = scale[((size_t)b * dst.H + h) * D + threadIdx.x];
-    col_scale[threadIdx.x] = sc;
-    col_rcp[threadIdx.x] = __frcp_rn(sc);
+    col_rcp[threadIdx.x] = rcp_approx(scale[((size_t)b * dst.H + h) * D + threadIdx.x]);
   }
   __syncthreads();
   store_tile(dst, b, h, s0, nrows, tbuf, [&](int r, int dd, float (&q)[kVec]) {
@@ -384,7 +371,7 @@ channel_quant_kernel(const T* __restrict__ x, CodeDst dst, const float* __restri
     load8<T>(src + r * rstride + dd, v);
 #pragma unroll
     for (int i = 0; i < kVec; ++i)
-      q[i] = fminf(fmaxf(div_rn_rcp(v[i], col_scale[dd + i], col_rcp[dd + i]), -kFp8Max), kFp8Max);
+      q[i] = fminf(fmaxf(v[i] * col_rcp[dd + i], -kFp8Max), kFp8Max);
   });
 }
 
@@ -545,7 +532,7 @@ static int dequant_launch(const uint8_t* codes, const float* scale, int B, int S
   LBFQ_REQUIRE(blk > 0, LBFQ_ERR_ARG, "block size must be positive");
   cudaStream_t st = (cudaStream_t)stream;
   const size_t total = (size_t)B * S * H * D / kVec;
-  const int grid = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+  const int grid = (int)((total + 255) / 256 < (size_t)sm_count() * 16 ? (total + 255) / 256 : (size_t)sm_count() * 16);
   LBFQ_DISPATCH_DTYPE(out_dtype, T,
       dequant_kernel<T><<<grid, 256, 0, st>>>(codes, scale, (T*)out, B, S, H, D, kind, blk));
   return check_launch("dequant");

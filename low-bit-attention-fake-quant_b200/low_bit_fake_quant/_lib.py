@@ -23,6 +23,8 @@ V_CHANNEL, V_BLOCK, V_MX = 0, 1, 2
 QK_FP8_BLOCK, QK_MX, QK_BF16 = 0, 1, 2
 
 ERR_ARG, ERR_DTYPE, ERR_UNSUPPORTED, ERR_CUDA, ERR_DEVICE = -1, -2, -3, -4, -5
+# debug overrides (LBFQ_FLAG_* of include/lbfq.h)
+FLAG_ATTN_GENERIC, FLAG_KMEANS_FFMA, FLAG_QM_CORR_FFMA, FLAG_UNFUSED_PREPROCESS = 1, 2, 4, 8
 
 _DTYPES = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}
 
@@ -71,6 +73,8 @@ _SIGS = {
     "lbfq_last_error": (C.c_char_p, []),
     "lbfq_abi_version": (_I, []),
     "lbfq_launch_count": (C.c_ulonglong, []),
+    "lbfq_get_flags": (_I, []),
+    "lbfq_set_flags": (None, [_I]),
     "lbfq_attention_last_variant": (_I, []),
     "lbfq_copy_rows_async": (_I, [_P, C.c_size_t, _P, C.c_size_t, C.c_size_t, C.c_size_t, _I, _P]),
     "lbfq_fp8_block_quant": (_I, [_P, _I, _I, _I, _I, _I, _I, _P, _I, _I, _P, _P]),
@@ -89,10 +93,10 @@ _SIGS = {
     "lbfq_block_mean_sub": (_I, [_P, _I, _I, _I, _I, _I, _I, _P, _P, _P]),
     "lbfq_hadamard": (_I, [_P, _I, C.c_int64, _I, _I, _P, C.c_float, _P, _P]),
     "lbfq_kmeans_scratch_bytes": (C.c_int64, [_I, _I, _I, _I, _I]),
-    "lbfq_kmeans_labels": (_I, [_P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P]),
+    "lbfq_kmeans_labels": (_I, [_P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P]),
     "lbfq_label_order": (_I, [_P, _I, _I, _I, _P, _P, _P]),
     "lbfq_gather_rows": (_I, [_P, _I, _I, _I, _I, _I, _P, _P, _P]),
-    "lbfq_qm_corr": (_I, [_P, _P, _I, _I, _I, _I, _I, _I, C.c_float, _P, _I, _P, _P]),
+    "lbfq_qm_corr": (_I, [_P, _P, _I, _I, _I, _I, _I, _I, C.c_float, _P, _I, _P, _P, _P]),
     "lbfq_attention_workspace_bytes": (C.c_int64, [C.POINTER(AttnArgs)]),
     "lbfq_attention_fwd": (_I, [C.POINTER(AttnArgs), _P, _P]),
 }
@@ -147,3 +151,73 @@ def ptr(t: Optional[torch.Tensor]) -> Optional[int]:
 
 def stream_ptr(device: torch.device) -> int:
     return torch.cuda.current_stream(device).cuda_stream
+
+
+# ---------------------------------------------------------------------------
+# debug overrides
+# ---------------------------------------------------------------------------
+
+def flags() -> int:
+    """The library's debug overrides (``FLAG_*``); initialised from the ``LBFQ_*`` environment variables once."""
+    return int(lib().lbfq_get_flags())
+
+
+def set_flag(flag: int, on: bool) -> None:
+    """Switch one debug override on or off (process-wide)."""
+    cur = flags()
+    lib().lbfq_set_flags((cur | flag) if on else (cur & ~flag))
+
+
+class override:
+    """Context manager that switches debug overrides on (``override(FLAG_ATTN_GENERIC)``) for the enclosed calls and
+    restores the previous set afterwards. Process-wide: meant for tests and measurements, not for concurrent use."""
+
+    def __init__(self, on: int = 0, off: int = 0):
+        self.on, self.off = int(on), int(off)
+
+    def __enter__(self):
+        self.saved = flags()
+        lib().lbfq_set_flags((self.saved | self.on) & ~self.off)
+        return self
+
+    def __exit__(self, *exc):
+        lib().lbfq_set_flags(self.saved)
+        return False
+
+
+# ---------------------------------------------------------------------------
+# device status word: kernels with bounded waits raise it instead of hanging
+# ---------------------------------------------------------------------------
+
+_status_dev: dict[int, torch.Tensor] = {}
+_status_host: dict[int, torch.Tensor] = {}
+
+
+def status_for(device: torch.device) -> torch.Tensor:
+    """The int32 status word of ``device`` (created on first use). Raises ``RuntimeError`` if an earlier launch on
+    that device reported an expired wait (the word is read back asynchronously after every launch that takes it)."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx not in _status_dev:
+        _status_dev[idx] = torch.zeros(1, dtype=torch.int32, device=device)
+        _status_host[idx] = torch.zeros(1, dtype=torch.int32).pin_memory()
+    host = _status_host[idx]
+    if int(host[0]) != 0:
+        code = int(host[0])
+        host.zero_()
+        _status_dev[idx].zero_()
+        raise RuntimeError(f"a kernel of liblbfq gave up a bounded wait (code {code}); its results are invalid")
+    return _status_dev[idx]
+
+
+def fetch_status(device: torch.device) -> None:
+    """Enqueue the copy of the device's status word to its pinned host mirror (no synchronisation)."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx in _status_dev:
+        _status_host[idx].copy_(_status_dev[idx], non_blocking=True)
+
+
+def raise_if_device_error(device: Optional[torch.device] = None) -> None:
+    """Synchronise ``device`` and raise if any launch on it reported an expired wait."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+    torch.cuda.synchronize(device)
+    status_for(device)

@@ -17,7 +17,6 @@ kernel's output store.
 from __future__ import annotations
 
 import math
-import os
 from dataclasses import dataclass
 from typing import Optional
 
@@ -89,18 +88,21 @@ def _k_smoothing_can_ride_on_the_quantizer(cfg: QuantConfig) -> bool:
             and not cfg.qk_hadamard and cfg.p_requant)
 
 
-def _preprocess(q, k, v, cfg: QuantConfig, *, head_offset: int = 0, total_heads: int = 0, defer_k_smoothing: bool = False):
+def _preprocess(q, k, v, cfg: QuantConfig, *, head_offset: int = 0, total_heads: int = 0, defer_k_smoothing: bool = False,
+                q_labels=None, v_labels=None):
     """The reference's fixed preprocessing order (attention.py:166-239).
 
     ``defer_k_smoothing`` (only with ``_k_smoothing_can_ride_on_the_quantizer``): K is returned as it came and its
-    channel mean as an eighth value, for the quantizer to subtract."""
+    channel mean as an eighth value, for the quantizer to subtract. ``q_labels`` / ``v_labels`` (B*H, S) replace the
+    Lloyd iterations of the corresponding k-means reorder by given cluster assignments (testing aid)."""
     q_work, k_work, v_work = q.contiguous(), k.contiguous(), v.contiguous()
     q_km = v_km = None
     qm = v_alpha = None
     if defer_k_smoothing:
         if cfg.q_kmeans_k is not None:
             q_km = kmeans_reorder_tokens(q_work, n_clusters=cfg.q_kmeans_k, max_iters=cfg.q_kmeans_iters,
-                                         seed=cfg.q_kmeans_seed, head_offset=head_offset, total_heads=total_heads)
+                                         seed=cfg.q_kmeans_seed, head_offset=head_offset, total_heads=total_heads,
+                                         labels=q_labels)
             q_work = q_km.tensor_reordered
         if cfg.v_smooth_mode == "per_block":
             v_work, v_alpha = smooth_v_per_block(v_work, block_s=cfg.v_smooth_block_size)
@@ -110,7 +112,8 @@ def _preprocess(q, k, v, cfg: QuantConfig, *, head_offset: int = 0, total_heads:
 
     if cfg.q_kmeans_k is not None:
         q_km = kmeans_reorder_tokens(q_work, n_clusters=cfg.q_kmeans_k, max_iters=cfg.q_kmeans_iters,
-                                     seed=cfg.q_kmeans_seed, head_offset=head_offset, total_heads=total_heads)
+                                     seed=cfg.q_kmeans_seed, head_offset=head_offset, total_heads=total_heads,
+                                     labels=q_labels)
         q_work = q_km.tensor_reordered
 
     if cfg.smoothing in ("k_only", "full"):
@@ -122,7 +125,8 @@ def _preprocess(q, k, v, cfg: QuantConfig, *, head_offset: int = 0, total_heads:
 
     if cfg.v_kmeans_k is not None:
         v_km = kmeans_reorder_tokens(v_work, n_clusters=cfg.v_kmeans_k, max_iters=cfg.v_kmeans_iters,
-                                     seed=cfg.v_kmeans_seed, head_offset=head_offset, total_heads=total_heads)
+                                     seed=cfg.v_kmeans_seed, head_offset=head_offset, total_heads=total_heads,
+                                     labels=v_labels)
         v_work = v_km.tensor_reordered
         k_work = apply_kv_permutation(k_work, v_km.order)      # keep every (K[n], V[n]) pair together
 
@@ -378,17 +382,23 @@ def fake_quant_attention(
     _head_offset: int = 0,
     _total_heads: int = 0,
     _reference_operands: bool = False,
+    _q_labels: Optional[torch.Tensor] = None,
+    _v_labels: Optional[torch.Tensor] = None,
 ):
     """Fake-quant attention with FP8/MXFP8 Q/K/V (and optional P requant).
 
     ``q, k, v``: (B, S, H, D), D in {64, 128}, BF16/FP16/FP32 on CUDA.
-    Returns the (B, S, H, D) output in ``q``'s dtype (and the artifacts).
+    Returns the (B, S, H, D) output in ``q``'s dtype (and the artifacts). The launches are asynchronous; a kernel
+    that gives up one of its bounded waits (which only a stalled device can cause) reports it through a status word
+    that is examined on the next call on that device and by ``attention_triton.raise_if_device_error()``: call the
+    latter before trusting a result if such a stall is a possibility.
     ``_debug_fp32`` (testing aid) returns the kernel's FP32 result without the
     BF16 rounding of the store. ``_head_offset`` / ``_total_heads`` tell a heads
     shard where it sits in the unsharded problem (Hadamard signs and k-means
     seeding are indexed by global head), so that sharded == unsharded.
     ``_reference_operands`` runs path B on the reference's own BF16 operands
     (BF16 MMAs) instead of the FP8 codes: the reference's numerics, at BF16 speed.
+    ``_q_labels`` / ``_v_labels`` (testing aid) give the k-means reorders their cluster assignments.
     """
     if cfg is None:
         cfg = QuantConfig()
@@ -411,6 +421,10 @@ def fake_quant_attention(
         raise TypeError(f"unsupported dtype {out_dtype}")
     sdpa_dtype = torch.float16 if out_dtype == torch.float16 else torch.bfloat16
     d = q.shape[-1]
+    if d not in (64, 128):
+        # every operator under this entry is built for these two head dimensions (quant_triton.py:21-22 of the
+        # reference refuses the others at its first quantizer; here nothing is launched at all)
+        raise ValueError(f"tensor.shape[-1] must be 64 or 128; got {d}")
     if sm_scale is None:
         sm_scale = 1.0 / math.sqrt(d)
     if cfg.blasst_lambda is not None and not cfg.p_requant:
@@ -428,16 +442,17 @@ def fake_quant_attention(
     else:
         # where nothing else needs the smoothed K, it is never stored: the K quantizer subtracts the mean
         defer = _k_smoothing_can_ride_on_the_quantizer(cfg) and not _reference_operands
-        pre = _preprocess(q, k, v, cfg, head_offset=_head_offset, total_heads=_total_heads, defer_k_smoothing=defer)
+        pre = _preprocess(q, k, v, cfg, head_offset=_head_offset, total_heads=_total_heads, defer_k_smoothing=defer,
+                          q_labels=_q_labels, v_labels=_v_labels)
         q_work, k_work, v_work, qm, v_alpha, q_km = pre[:6]
         k_mean = pre[7] if defer else None
 
     # mxfp8 Q / K de-quantise to BF16 exactly (power-of-two scales), so for them the BF16-operand kernel computes
     # the same products as a block-scaled FP8 MMA and, unlike the general kernel, keeps the accumulator in tensor
     # memory; it takes them whenever it serves the rest of the configuration
-    # (LBFQ_ATTN_GENERIC=1 keeps them on the general kernel's block-scaled Q.K^T, the cross-check)
+    # (the FLAG_ATTN_GENERIC override keeps them on the general kernel's block-scaled Q.K^T, the cross-check)
     mx_as_bf16 = (cfg.qk_quant == "mxfp8" and cfg.v_quant != "fp8_block" and cfg.blasst_lambda is None
-                  and os.environ.get("LBFQ_ATTN_GENERIC") != "1"
+                  and not (L.flags() & L.FLAG_ATTN_GENERIC)
                   and (qm is None or cfg.q_smooth_block_size % 128 == 0)
                   and (v_alpha is None or cfg.v_smooth_block_size == 64 or cfg.v_smooth_block_size % 128 == 0))
     if cfg.p_requant and (_reference_operands or mx_as_bf16):

@@ -34,29 +34,8 @@ _BLASST_FILL_UTA = 6
 # on the launching stream around the attention kernel (used by bench.py for the roofline).
 KERNEL_EVENTS: Optional[list] = None
 
-_status_dev: dict[int, torch.Tensor] = {}
-_status_host: dict[int, torch.Tensor] = {}
-
-
-def _status_for(device: torch.device) -> torch.Tensor:
-    idx = device.index if device.index is not None else torch.cuda.current_device()
-    if idx not in _status_dev:
-        _status_dev[idx] = torch.zeros(1, dtype=torch.int32, device=device)
-        _status_host[idx] = torch.zeros(1, dtype=torch.int32).pin_memory()
-    host = _status_host[idx]
-    if int(host[0]) != 0:          # set by an earlier launch whose bounded wait expired
-        code = int(host[0])
-        host.zero_()
-        _status_dev[idx].zero_()
-        raise RuntimeError(f"fake-quant attention kernel gave up a bounded wait (code {code})")
-    return _status_dev[idx]
-
-
-def raise_if_device_error(device: Optional[torch.device] = None) -> None:
-    """Synchronise and raise if any launch on ``device`` reported a timeout."""
-    device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
-    torch.cuda.synchronize(device)
-    _status_for(device)
+_status_for = L.status_for
+raise_if_device_error = L.raise_if_device_error
 
 
 def _parse_blasst_fill(mode: Optional[str], *, alpha: float, uta_bins: int) -> tuple[int, float, int]:
@@ -221,8 +200,7 @@ def fake_quant_attention_fp8(
         if KERNEL_EVENTS is not None:
             ev1.record()
             KERNEL_EVENTS.append((ev0, ev1))
-        idx = dev.index if dev.index is not None else torch.cuda.current_device()
-        _status_host[idx].copy_(status, non_blocking=True)
+        L.fetch_status(dev)
     if return_blasst_stats:
         return out, stats
     return out
@@ -242,9 +220,11 @@ def qm_corr(qm: torch.Tensor, k_smooth: torch.Tensor, *, sm_scale: float, s_pad:
     corr = torch.empty((b, h, g, s_pad), dtype=torch.float32, device=qm.device)
     rowmax = torch.empty((b, h, g), dtype=torch.float32, device=qm.device) if want_rowmax else None
     with torch.cuda.device(qm.device):
+        status = L.status_for(qm.device)
         L.check(L.lib().lbfq_qm_corr(qm.data_ptr(), k_smooth.data_ptr(), L.dtype_code(k_smooth.dtype), b, s, h, d, g,
-                                     float(sm_scale), corr.data_ptr(), s_pad, L.ptr(rowmax),
+                                     float(sm_scale), corr.data_ptr(), s_pad, L.ptr(rowmax), status.data_ptr(),
                                      L.stream_ptr(qm.device)))
+        L.fetch_status(qm.device)
     return corr, rowmax
 
 

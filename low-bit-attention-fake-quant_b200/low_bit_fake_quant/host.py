@@ -119,4 +119,5 @@ def fake_quant_attention_host(
             results.append(o)
         s_back.synchronize()
         comp.synchronize()
+        L.status_for(dev)                 # everything has completed: raise if any launch gave up a bounded wait
     return out

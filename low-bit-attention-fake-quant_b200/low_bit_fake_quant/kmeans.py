@@ -43,9 +43,11 @@ def kmeans_labels(t: torch.Tensor, *, n_clusters: int, max_iters: int = 10, seed
     with torch.cuda.device(t.device):
         nbytes = L.lib().lbfq_kmeans_scratch_bytes(b, s, h, d, n_clusters)
         scratch = torch.empty((nbytes,), dtype=torch.uint8, device=t.device)
+        status = L.status_for(t.device)
         L.check(L.lib().lbfq_kmeans_labels(t.data_ptr(), L.dtype_code(t.dtype), b, s, h, d, n_clusters,
                                            max_iters, seed, head_offset, total_heads, labels.data_ptr(), scratch.data_ptr(),
-                                           L.stream_ptr(t.device)))
+                                           status.data_ptr(), L.stream_ptr(t.device)))
+        L.fetch_status(t.device)
     return labels
 
 

@@ -31,7 +31,7 @@ from typing import Optional, Tuple
 
 import torch
 
-from .quant_ops import FP8_MAX, pow2_scale, to_e4m3
+from .quant_ops import FP8_MAX, INV_FP8_MAX, pow2_scale, to_e4m3
 
 LOG2E = 1.4426950408889634
 
@@ -275,7 +275,7 @@ def k12_attention(
             p_rec = to_e4m3(p / s_p[..., None]).float() * s_p[..., None]
         else:                                                              # :353-360
             amax = p.abs().amax(dim=-1).clamp_min(1e-12)
-            s_p = amax / _f32(FP8_MAX)
+            s_p = amax * INV_FP8_MAX              # the GPU's `amax / 448` (see oracle/quant_ops.py)
             p_rec = to_e4m3(p / s_p[..., None]).float() * s_p[..., None]
         if p_bf16:
             p_rec = p_rec.to(torch.bfloat16).float()

@@ -17,16 +17,33 @@ the reference (paths relative to the reference project root):
 * ``hadamard_transform_last_dim`` / ``apply_qk_hadamard``
                                             src/low_bit_fake_quant/hadamard.py:25-117
 
-Pinning. The reference holds no golden vectors for codes or scales and its
-Triton kernels cannot execute without a GPU, so the arithmetic contract of
-this restatement is: IEEE fp32 for every ``/`` and ``*``; fp32 -> e4m3 by
-round-to-nearest-even with saturation to +-448 (the behaviour of the GPU
-``cvt.rn.satfinite`` the Triton cast lowers to; torch's CPU cast returns NaN
-above 448, hence the clamp in :func:`to_e4m3`); the power-of-two scale
-``2**ceil(log2(amax/448))`` by exact exponent arithmetic on the fp32 quotient.
-The pieces of the reference that do run on CPU (its torch FWHT, the sign
-generator, the row-max estimate, the SDPA glue and the torch mirrors in its
-own tests) pin this module through ``tests/golden``.
+Pinning. The reference holds no golden vectors for codes or scales, so they
+were recorded from its own Triton kernels run on a B200
+(``tests/golden/make_golden_gpu.py`` -> ``tests/golden/reference_gpu_vectors.pt``)
+and this module is held to them by ``tests/test_oracle_vs_reference_gpu.py``.
+What the recording showed, and the arithmetic contract that follows from it:
+
+* Triton's ``/`` is not an IEEE division: on the GPU ``a / b`` is exactly
+  ``a * rcp.approx(b)`` (``div.full.f32``). With the constant divisor 448 that is
+  ``amax * fl32(1/448)``, which a CPU reproduces bit for bit: every scale below is
+  formed that way (an IEEE ``amax / 448`` differs by one ulp in half of the scales).
+* ``x / scale`` uses the GPU's approximate reciprocal of ``scale``, a table a CPU
+  cannot restate; the IEEE quotient used here rounds to the same e4m3 code except
+  where the two land on opposite sides of a rounding boundary -- measured: 3 codes
+  in 4.2 M. The CUDA library follows the GPU arithmetic and is bit-identical to
+  the recorded codes; tests against this module allow that rate.
+* fp32 -> e4m3 is round-to-nearest-even with saturation to +-448 (the GPU's
+  ``cvt.rn.satfinite``; torch's CPU cast returns NaN above 448, hence the clamp in
+  :func:`to_e4m3`); the power-of-two scale ``2**ceil(log2(amax/448))`` is taken by
+  exact exponent arithmetic on ``amax * fl32(1/448)`` (identical to the recorded
+  scales; ``fl32(1/448) * 1.75 * 2**j`` rounds to ``2**(j-8)`` exactly).
+* the means of the smoothing kernels are fp32 sums in an unspecified tree order
+  on the GPU; the recorded means differ from the sequential sums here by one ulp
+  in under 1 % of the entries, the smoothed tensors not at all.
+
+The pieces of the reference that run on CPU (its torch FWHT, the sign generator,
+the row-max estimate, the SDPA glue and the torch mirrors in its own tests) pin
+this module through ``tests/golden/reference_cpu_vectors.pt`` as well.
 """
 
 from __future__ import annotations
@@ -37,6 +54,8 @@ from typing import Optional, Tuple
 import torch
 
 FP8_MAX = 448.0
+# fl32(1/448): what the GPU's ``amax / 448`` multiplies by (see the module docstring)
+INV_FP8_MAX = torch.tensor(1.0, dtype=torch.float32) / torch.tensor(448.0, dtype=torch.float32)
 AMAX_FLOOR = 1e-4
 UE8M0_MIN = -127
 UE8M0_MAX = 127
@@ -59,10 +78,10 @@ def pow2_scale(amax: torch.Tensor) -> torch.Tensor:
     """``2**clamp(ceil(log2(amax/448)), -127, 127)`` as fp32, exactly.
 
     quant_triton.py:240-243. ``amax`` is already floored at 1e-4. The
-    quotient is the IEEE fp32 division; ``ceil(log2(r))`` of an fp32 ``r`` is
-    its exponent, minus one when ``r`` is itself a power of two.
+    quotient is ``amax * fl32(1/448)`` as on the GPU; ``ceil(log2(r))`` of an
+    fp32 ``r`` is its exponent, minus one when ``r`` is itself a power of two.
     """
-    r = amax.float() / torch.tensor(FP8_MAX, dtype=torch.float32)
+    r = amax.float() * INV_FP8_MAX
     mant, expo = torch.frexp(r)            # r = mant * 2**expo, mant in [0.5, 1)
     e = torch.where(mant == 0.5, expo - 1, expo)
     e = e.clamp(UE8M0_MIN, UE8M0_MAX).to(torch.float32)
@@ -90,7 +109,7 @@ def fp8_block_quant(t: torch.Tensor, block_s: int = 128):
     n = s // block_s
     x = t.float().reshape(b, n, block_s, h, d)
     amax = x.abs().amax(dim=(2, 4)).clamp_min(AMAX_FLOOR)          # (b, n, h)
-    sc = amax / torch.tensor(FP8_MAX, dtype=torch.float32)
+    sc = amax * INV_FP8_MAX
     codes = to_e4m3(x / sc[:, :, None, :, None]).reshape(b, s, h, d)
     return codes, sc
 
@@ -107,7 +126,7 @@ def fp8_per_channel_quant(t: torch.Tensor, block_s: int = 128):
     b, s, h, d = _check_nhd(t)
     x = t.float()
     amax = x.abs().amax(dim=1).clamp_min(AMAX_FLOOR)               # (b, h, d)
-    sc = amax / torch.tensor(FP8_MAX, dtype=torch.float32)
+    sc = amax * INV_FP8_MAX
     codes = to_e4m3(x / sc[:, None])
     return codes, sc
 

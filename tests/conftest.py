@@ -36,3 +36,15 @@ def golden():
     import torch
 
     return torch.load(os.path.join(ROOT, "tests", "golden", "reference_cpu_vectors.pt"), weights_only=False)
+
+
+@pytest.fixture(autouse=True)
+def _reset_debug_overrides():
+    """Tests switch the library's debug overrides (general attention kernel, FFMA cross-check kernels) on and off;
+    every test starts and ends with none of them set."""
+    yield
+    import torch
+
+    if torch.cuda.is_available():
+        from low_bit_fake_quant import _lib as L
+        L.lib().lbfq_set_flags(0)

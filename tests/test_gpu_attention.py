@@ -19,6 +19,7 @@ import pytest
 import torch
 
 import low_bit_fake_quant as fq
+from low_bit_fake_quant import _lib as L
 from low_bit_fake_quant.attention_triton import raise_if_device_error
 from low_bit_fake_quant.config import QuantConfig
 from oracle import api as OA
@@ -245,10 +246,10 @@ def _variant():
 
 
 def _fast_and_general(q, k, v, cfg, monkeypatch):
-    monkeypatch.delenv("LBFQ_ATTN_GENERIC", raising=False)
+    L.set_flag(L.FLAG_ATTN_GENERIC, False)
     fast = fq.fake_quant_attention(q.to(DEV), k.to(DEV), v.to(DEV), cfg, _debug_fp32=True).float().cpu()
     assert _variant() == 1
-    monkeypatch.setenv("LBFQ_ATTN_GENERIC", "1")
+    L.set_flag(L.FLAG_ATTN_GENERIC, True)
     gen = fq.fake_quant_attention(q.to(DEV), k.to(DEV), v.to(DEV), cfg, _debug_fp32=True).float().cpu()
     assert _variant() == 0
     raise_if_device_error(torch.device(DEV))
@@ -324,10 +325,10 @@ def test_tmem_resident_variant_blasst(S, D, bn, lam, extra, monkeypatch):
         raise_if_device_error(torch.device(DEV))
         return out.float().cpu(), st.cpu()
 
-    monkeypatch.delenv("LBFQ_ATTN_GENERIC", raising=False)
+    L.set_flag(L.FLAG_ATTN_GENERIC, False)
     fast, st_fast = run()
     assert _variant() == 1
-    monkeypatch.setenv("LBFQ_ATTN_GENERIC", "1")
+    L.set_flag(L.FLAG_ATTN_GENERIC, True)
     gen, st_gen = run()
     assert _variant() == 0
     assert torch.equal(st_fast, st_gen)
@@ -391,7 +392,7 @@ def test_tmem_resident_variant_row_max_seeds(mode, monkeypatch):
 def test_block_scaled_general_kernel_matches_oracle(name, monkeypatch):
     """mxfp8 Q / K normally run as exact BF16 operands on the TMEM-resident kernel; the general kernel's block-scaled
     Q.K^T (kind::mxf8f6f4 with UE8M0 scales in tensor memory) stays covered through the override."""
-    monkeypatch.setenv("LBFQ_ATTN_GENERIC", "1")
+    L.set_flag(L.FLAG_ATTN_GENERIC, True)
     cfg = QuantConfig(**{**COMMON, **CASES[name]})
     q, k, v = _qkv(1, 512, 2, 128, seed=zlib.crc32(name.encode()) % 1000)
     g, o = _run_both(q, k, v, cfg)

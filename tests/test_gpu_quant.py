@@ -1,8 +1,12 @@
 """GPU parity of the quantizer / preprocess kernels against the CPU oracle.
 
-Codes and scales must be BIT-EXACT on identical inputs (integer / byte work);
-means are FP32 sums whose order differs from the oracle's, so they get an ulp
-bound and the centred tensors a mismatch-count bound.
+Scales must be BIT-EXACT on identical inputs. Codes: the library follows the arithmetic of the reference's kernels
+on the GPU (``x * rcp.approx(scale)``; it is bit-identical to codes recorded from them, see
+``test_gpu_vs_reference_vectors.py``), the oracle divides by IEEE rules because a CPU cannot restate the GPU's
+reciprocal table: the two round to the same e4m3 code except where they land on opposite sides of a rounding
+boundary (measured rate 7e-7), so the code comparison allows a few such neighbours per million. Power-of-two scales
+(mxfp8) leave no such freedom and stay exact. Means are FP32 sums whose order differs from the oracle's, so they get
+an ulp bound and the centred tensors a mismatch-count bound.
 """
 import pytest
 import torch
@@ -27,8 +31,18 @@ def _inputs(B, S, H, D, dtype, seed=0):
     return x.to(dtype)
 
 
-def _same_codes(got, want):
-    return torch.equal(got.view(torch.uint8).cpu(), want.view(torch.uint8))
+def _same_codes(got, want, max_frac=0.0):
+    """Equal codes; with ``max_frac`` > 0, at most that fraction may differ, each by one code step (same sign)."""
+    g, w = got.view(torch.uint8).cpu().to(torch.int16), want.view(torch.uint8).to(torch.int16)
+    diff = g != w
+    if not diff.any():
+        return True
+    if max_frac <= 0.0 or diff.float().mean().item() > max_frac:
+        return False
+    return bool(((g[diff] - w[diff]).abs() == 1).all())
+
+
+FP32_SCALE_CODES = 2e-5          # see the module docstring
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
@@ -37,19 +51,19 @@ def test_fp8_block_bit_exact(dtype, D, blk):
     x = _inputs(2, 256, 3, D, dtype)
     c, s = fq.fp8_block_quant(x.to(DEV), blk)
     oc, os_ = OQ.fp8_block_quant(x, blk)
-    assert _same_codes(c, oc) and torch.equal(s.cpu(), os_)
+    assert _same_codes(c, oc, FP32_SCALE_CODES) and torch.equal(s.cpu(), os_)
     for out_dt in (torch.bfloat16, torch.float32):
-        assert torch.equal(fq.fp8_block_dequant(c, s, blk, dtype=out_dt).cpu(), OQ.fp8_block_dequant(oc, os_, blk, dtype=out_dt))
+        assert torch.equal(fq.fp8_block_dequant(c, s, blk, dtype=out_dt).cpu(), OQ.fp8_block_dequant(c.cpu(), os_, blk, dtype=out_dt))
 
 
 def test_fp8_block_layouts_and_padding():
     x = _inputs(1, 192, 2, 128, torch.bfloat16, seed=1)
     oc, _ = OQ.fp8_block_quant(x, 64)
     c, _ = fq.fp8_block_quant(x.to(DEV), 64, _layout=L.LAYOUT_BHSD, _s_pad=256)
-    assert _same_codes(c[:, :, :192].permute(0, 2, 1, 3).contiguous(), oc)
+    assert _same_codes(c[:, :, :192].permute(0, 2, 1, 3).contiguous(), oc, FP32_SCALE_CODES)
     assert int(c.view(torch.uint8)[:, :, 192:].sum()) == 0
     c, _ = fq.fp8_block_quant(x.to(DEV), 64, _layout=L.LAYOUT_BHDS, _s_pad=256)
-    assert _same_codes(c[..., :192].permute(0, 3, 1, 2).contiguous(), oc)
+    assert _same_codes(c[..., :192].permute(0, 3, 1, 2).contiguous(), oc, FP32_SCALE_CODES)
     assert int(c.view(torch.uint8)[..., 192:].sum()) == 0
 
 
@@ -58,10 +72,10 @@ def test_fp8_channel_bit_exact(dtype):
     x = _inputs(2, 320, 2, 128, dtype, seed=2)        # S not a multiple of the kernel's row tiles
     c, s = fq.fp8_per_channel_quant(x.to(DEV))
     oc, os_ = OQ.fp8_per_channel_quant(x)
-    assert _same_codes(c, oc) and torch.equal(s.cpu(), os_)
-    assert torch.equal(fq.fp8_per_channel_dequant(c, s, dtype=torch.bfloat16).cpu(), OQ.fp8_per_channel_dequant(oc, os_, dtype=torch.bfloat16))
+    assert _same_codes(c, oc, FP32_SCALE_CODES) and torch.equal(s.cpu(), os_)
+    assert torch.equal(fq.fp8_per_channel_dequant(c, s, dtype=torch.bfloat16).cpu(), OQ.fp8_per_channel_dequant(c.cpu(), os_, dtype=torch.bfloat16))
     ct, _ = fq.fp8_per_channel_quant(x.to(DEV), _layout=L.LAYOUT_BHDS, _s_pad=384)
-    assert _same_codes(ct[..., :320].permute(0, 3, 1, 2).contiguous(), oc)
+    assert _same_codes(ct[..., :320].permute(0, 3, 1, 2).contiguous(), c.cpu())
 
 
 @pytest.mark.parametrize("D,blk", [(128, 32), (64, 32), (128, 64), (128, 16)])
@@ -179,10 +193,10 @@ def test_kmeans_tensor_core_assignment_agrees_with_fp32_assignment(k, D, monkeyp
     assignment is the cross-check. They differ only in summation order, i.e. on near-ties."""
     torch.manual_seed(k + D)
     x = (torch.randn(2, 1000, 3, D) + 2.0 * torch.randn(1, 1, 3, D)).bfloat16().to(DEV)      # ragged last tile
-    monkeypatch.delenv("LBFQ_KMEANS_FFMA", raising=False)
+    L.set_flag(L.FLAG_KMEANS_FFMA, False)
     tc = kmeans_labels(x, n_clusters=k, max_iters=5, seed=1)
     assert torch.equal(tc, kmeans_labels(x, n_clusters=k, max_iters=5, seed=1))               # reproducible
-    monkeypatch.setenv("LBFQ_KMEANS_FFMA", "1")
+    L.set_flag(L.FLAG_KMEANS_FFMA, True)
     ff = kmeans_labels(x, n_clusters=k, max_iters=5, seed=1)
     assert int(tc.min()) >= 0 and int(tc.max()) < k
     assert (tc == ff).float().mean().item() > 0.995
@@ -210,11 +224,11 @@ def test_qm_corr_tensor_core_kernel_agrees_with_fp32_kernel(S, G, D, monkeypatch
     qm = torch.randn(2, G, 3, D, device=DEV)
     ks = (torch.randn(2, S, 3, D, device=DEV) * 2).bfloat16()
     s_pad = (S + 63) // 64 * 64
-    monkeypatch.delenv("LBFQ_QM_CORR_FFMA", raising=False)
+    L.set_flag(L.FLAG_QM_CORR_FFMA, False)
     c_tc, r_tc = qm_corr(qm, ks, sm_scale=0.0884, s_pad=s_pad, want_rowmax=True)
     c_tc2, _ = qm_corr(qm, ks, sm_scale=0.0884, s_pad=s_pad)
     assert torch.equal(c_tc, c_tc2)                                            # reproducible
-    monkeypatch.setenv("LBFQ_QM_CORR_FFMA", "1")
+    L.set_flag(L.FLAG_QM_CORR_FFMA, True)
     c_ff, r_ff = qm_corr(qm, ks, sm_scale=0.0884, s_pad=s_pad, want_rowmax=True)
     ref = torch.einsum("bghd,bshd->bhgs", qm.double(), ks.double()) * 0.0884
     assert float(c_tc[..., S:].abs().sum()) == 0.0
