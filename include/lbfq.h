@@ -297,6 +297,14 @@ int lbfq_attention_fwd(const lbfq_attn_args* args, void* workspace, void* stream
  * the reference. */
 int lbfq_attention_last_variant(void);
 
+/* ============================ test utility ================================= */
+
+/* y[i] = rcp.approx.f32(x[i]) on the device. The reference's Triton kernels divide by multiplying with the GPU's
+ * approximate reciprocal (quant_triton.py:49,155; attention_triton.py:357,387), and so do the kernels here; the value
+ * comes from a hardware table, so a CPU restatement that wants to follow the quantizers bit for bit asks the GPU for
+ * it through this entry. No counterpart in the reference. */
+int lbfq_rcp_approx(const float* x, float* y, long long n, void* stream);
+
 /* ======================= host-buffer plumbing ============================== */
 
 /* `rows` rows of `width` bytes between a pitched host buffer and a pitched device buffer, enqueued on `stream`

@@ -67,3 +67,21 @@ extern "C" int lbfq_copy_rows_async(void* dst, size_t dst_pitch, const void* src
                                  to_device ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToHost, (cudaStream_t)stream));
   return LBFQ_OK;
 }
+
+// The GPU's approximate reciprocal, element-wise. A test utility: the reference's quantizers divide by multiplying
+// with this value (common.cuh), which a CPU cannot compute itself; a CPU restatement fetches it here.
+namespace lbfq {
+__global__ void rcp_approx_kernel(const float* __restrict__ x, float* __restrict__ y, long long n) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    y[i] = rcp_approx(x[i]);
+}
+}  // namespace lbfq
+extern "C" int lbfq_rcp_approx(const float* x, float* y, long long n, void* stream) {
+  LBFQ_REQUIRE(n >= 0, LBFQ_ERR_ARG, "negative element count");
+  if (n == 0) return LBFQ_OK;
+  LBFQ_REQUIRE(x != nullptr && y != nullptr, LBFQ_ERR_ARG, "null pointer");
+  long long g = (n + 255) / 256;
+  if (g > (long long)lbfq::sm_count() * 16) g = (long long)lbfq::sm_count() * 16;
+  lbfq::rcp_approx_kernel<<<(int)g, 256, 0, (cudaStream_t)stream>>>(x, y, n);
+  return lbfq::check_launch("rcp_approx");
+}

@@ -76,6 +76,7 @@ _SIGS = {
     "lbfq_get_flags": (_I, []),
     "lbfq_set_flags": (None, [_I]),
     "lbfq_attention_last_variant": (_I, []),
+    "lbfq_rcp_approx": (_I, [_P, _P, C.c_longlong, _P]),
     "lbfq_copy_rows_async": (_I, [_P, C.c_size_t, _P, C.c_size_t, C.c_size_t, C.c_size_t, _I, _P]),
     "lbfq_fp8_block_quant": (_I, [_P, _I, _I, _I, _I, _I, _I, _P, _I, _I, _P, _P]),
     "lbfq_fp8_block_quant_centered": (_I, [_P, _I, _I, _I, _I, _I, _I, _P, _P, _I, _I, _P, _P]),
@@ -221,3 +222,14 @@ def raise_if_device_error(device: Optional[torch.device] = None) -> None:
     device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
     torch.cuda.synchronize(device)
     status_for(device)
+
+
+def rcp_approx(x: torch.Tensor, device: Optional[torch.device] = None) -> torch.Tensor:
+    """Element-wise ``rcp.approx.f32`` of an FP32 tensor, computed on the GPU and returned on ``x``'s device: the
+    reciprocal the quantizers multiply by. A utility for CPU restatements of the path (see ``lbfq_rcp_approx``)."""
+    dev = x.device if x.is_cuda else (torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device()))
+    xd = x.detach().to(device=dev, dtype=torch.float32).contiguous()
+    yd = torch.empty_like(xd)
+    with torch.cuda.device(dev):
+        check(lib().lbfq_rcp_approx(xd.data_ptr(), yd.data_ptr(), xd.numel(), stream_ptr(dev)))
+    return yd.to(x.device)

@@ -358,7 +358,7 @@ def _fake_quant_attention_p_requant_reference_operands(q_work, k_work, v_work, q
         block_m=cfg.p_requant_block_m, block_n=cfg.p_requant_block_n,
         v_alpha=v_alpha, v_smooth_block=cfg.v_smooth_block_size if v_alpha is not None else 0,
         k_smooth_bhsd=to_bh(k_work.to(torch.bfloat16)) if qm is not None else None,
-        qm_bhgd=to_bh(qm) if qm is not None else None,
+        qm_bhgd=qm.float().contiguous() if qm is not None else None,      # (B, G, H, D), as group_mean_q returns it
         q_smooth_block=cfg.q_smooth_block_size if qm is not None else 0,
         p_quant_mode=p_mode, p_mx_block_n=p_mx_block_n, rowmax_est_bhs=rowmax_est, _out_fp32=out_fp32_exact, _corr=corr)
     o = o.permute(0, 2, 1, 3).contiguous()                    # (B, S, H, D)

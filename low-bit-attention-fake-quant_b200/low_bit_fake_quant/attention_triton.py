@@ -303,10 +303,17 @@ def fake_quant_attention_triton(
                              "and an integer multiple of block_m")
         if M % q_smooth_block != 0:
             raise ValueError(f"S ({M}) must be divisible by q_smooth_block ({q_smooth_block})")
-        if _corr is not None and tuple(_corr.shape) == (B, H, qm_bhgd.shape[2], n_pad):
+        # despite its name the reference takes this tensor as group_mean_q returns it: (B, S / q_smooth_block, H, D)
+        # (attention_triton.py:511)
+        n_groups = M // q_smooth_block
+        if tuple(qm_bhgd.shape) != (B, n_groups, H, D):
+            raise ValueError(f"qm_bhgd must be (B, S // q_smooth_block, H, D) = {(B, n_groups, H, D)}; got {tuple(qm_bhgd.shape)}")
+        if tuple(k_smooth_bhsd.shape) != (B, H, N, D):
+            raise ValueError(f"k_smooth_bhsd must be {(B, H, N, D)}; got {tuple(k_smooth_bhsd.shape)}")
+        if _corr is not None and tuple(_corr.shape) == (B, H, n_groups, n_pad):
             corr = _corr                                  # the caller has formed the product already
         else:
-            corr, _ = qm_corr(qm_bhgd.permute(0, 2, 1, 3).contiguous().float(), k_smooth_bhsd.permute(0, 2, 1, 3).contiguous(),
+            corr, _ = qm_corr(qm_bhgd.float().contiguous(), k_smooth_bhsd.permute(0, 2, 1, 3).contiguous(),
                               sm_scale=sm_scale, s_pad=n_pad, want_rowmax=False)
 
     def pad_rows(t, rows):       # (B, H, S, D) -> (B, H, rows, D), zero rows appended

@@ -31,7 +31,7 @@ from typing import Optional, Tuple
 
 import torch
 
-from .quant_ops import FP8_MAX, INV_FP8_MAX, pow2_scale, to_e4m3
+from .quant_ops import FP8_MAX, INV_FP8_MAX, divide, pow2_scale, to_e4m3
 
 LOG2E = 1.4426950408889634
 
@@ -276,7 +276,7 @@ def k12_attention(
         else:                                                              # :353-360
             amax = p.abs().amax(dim=-1).clamp_min(1e-12)
             s_p = amax * INV_FP8_MAX              # the GPU's `amax / 448` (see oracle/quant_ops.py)
-            p_rec = to_e4m3(p / s_p[..., None]).float() * s_p[..., None]
+            p_rec = to_e4m3(divide(p, s_p[..., None])).float() * s_p[..., None]
         if p_bf16:
             p_rec = p_rec.to(torch.bfloat16).float()
 
@@ -294,7 +294,7 @@ def k12_attention(
         n_upd = int(upd_cnt.sum())
         rowmax_counters.update(updates=n_upd, rescales=n_resc, upward_updates=n_upd - n_down, downward_updates=n_down,
                                rows_with_update=int((upd_cnt > 0).sum()), max_updates_per_row=int(upd_cnt.max()))
-    inv_l = 1.0 / l_i[..., None]                                           # :387-399
+    inv_l = divide(torch.ones(()), l_i[..., None])                                        # :387-399
     out_main = acc * v_scale_bhd.float()[:, :, None, :] if v_block_scale is None else acc
     out = (out_main + c_acc) * inv_l if v_alpha is not None else out_main * inv_l
     if return_stats:

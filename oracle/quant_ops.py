@@ -65,6 +65,25 @@ UE8M0_MAX = 127
 # element helpers
 # --------------------------------------------------------------------------
 
+# The reference's ``a / b`` is ``a * rcp.approx(b)`` on the GPU (module docstring). A test that has a GPU at hand can
+# install that reciprocal (``low_bit_fake_quant._lib.rcp_approx``) and the restatement then follows the GPU arithmetic
+# bit for bit; without it the IEEE quotient is used.
+_RECIPROCAL = None
+
+
+def set_reciprocal(fn) -> None:
+    """``fn``: fp32 CPU tensor -> its element-wise reciprocal as the GPU's ``rcp.approx.f32`` returns it, or None."""
+    global _RECIPROCAL
+    _RECIPROCAL = fn
+
+
+def divide(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """The reference kernels' ``a / b`` (``b`` broadcasts against ``a``)."""
+    if _RECIPROCAL is None:
+        return a / b
+    return a * _RECIPROCAL(b.float().contiguous()).reshape(b.shape)
+
+
 def to_e4m3(x: torch.Tensor) -> torch.Tensor:
     """fp32 -> e4m3 codes, round-to-nearest-even, saturating at +-448."""
     return x.float().clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn)
@@ -110,7 +129,7 @@ def fp8_block_quant(t: torch.Tensor, block_s: int = 128):
     x = t.float().reshape(b, n, block_s, h, d)
     amax = x.abs().amax(dim=(2, 4)).clamp_min(AMAX_FLOOR)          # (b, n, h)
     sc = amax * INV_FP8_MAX
-    codes = to_e4m3(x / sc[:, :, None, :, None]).reshape(b, s, h, d)
+    codes = to_e4m3(divide(x, sc[:, :, None, :, None])).reshape(b, s, h, d)
     return codes, sc
 
 
@@ -127,7 +146,7 @@ def fp8_per_channel_quant(t: torch.Tensor, block_s: int = 128):
     x = t.float()
     amax = x.abs().amax(dim=1).clamp_min(AMAX_FLOOR)               # (b, h, d)
     sc = amax * INV_FP8_MAX
-    codes = to_e4m3(x / sc[:, None])
+    codes = to_e4m3(divide(x, sc[:, None]))
     return codes, sc
 
 
@@ -195,7 +214,7 @@ def smooth_k(k: torch.Tensor, block_s: int = 256):
     acc = torch.zeros((b, h, d), dtype=torch.float32)
     for s0 in range(0, s, block_s):
         acc = acc + x[:, s0:s0 + block_s].sum(dim=1)
-    mean = acc / torch.tensor(float(s), dtype=torch.float32)
+    mean = divide(acc, torch.tensor(float(s), dtype=torch.float32))
     return (x - mean[:, None]).to(k.dtype), mean
 
 
@@ -207,7 +226,7 @@ def _block_mean_sub(t: torch.Tensor, block: int):
         raise ValueError(f"D must be 64 or 128; got {d}")
     n = s // block
     x = t.float().reshape(b, n, block, h, d)
-    mean = x.sum(dim=2) / torch.tensor(float(block), dtype=torch.float32)   # (b, n, h, d)
+    mean = divide(x.sum(dim=2), torch.tensor(float(block), dtype=torch.float32))   # (b, n, h, d)
     out = (x - mean[:, :, None]).reshape(b, s, h, d).to(t.dtype)
     return out, mean
 

@@ -48,3 +48,16 @@ def _reset_debug_overrides():
     if torch.cuda.is_available():
         from low_bit_fake_quant import _lib as L
         L.lib().lbfq_set_flags(0)
+
+
+@pytest.fixture(autouse=True, scope="session")
+def _oracle_follows_the_gpu_reciprocal():
+    """With a GPU at hand the oracle divides as the GPU does (``a * rcp.approx(b)``, fetched through the library's
+    test utility), so that quantizer codes can be compared bit for bit; without one it uses IEEE division."""
+    import torch
+
+    if torch.cuda.is_available():
+        from low_bit_fake_quant import _lib as L
+        from oracle import quant_ops as OQ
+        OQ.set_reciprocal(lambda t: L.rcp_approx(t, device="cuda:0"))
+    yield

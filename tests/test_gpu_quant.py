@@ -1,12 +1,11 @@
 """GPU parity of the quantizer / preprocess kernels against the CPU oracle.
 
-Scales must be BIT-EXACT on identical inputs. Codes: the library follows the arithmetic of the reference's kernels
-on the GPU (``x * rcp.approx(scale)``; it is bit-identical to codes recorded from them, see
-``test_gpu_vs_reference_vectors.py``), the oracle divides by IEEE rules because a CPU cannot restate the GPU's
-reciprocal table: the two round to the same e4m3 code except where they land on opposite sides of a rounding
-boundary (measured rate 7e-7), so the code comparison allows a few such neighbours per million. Power-of-two scales
-(mxfp8) leave no such freedom and stay exact. Means are FP32 sums whose order differs from the oracle's, so they get
-an ulp bound and the centred tensors a mismatch-count bound.
+Codes and scales must be BIT-EXACT on identical inputs. The library follows the arithmetic of the reference's
+kernels on the GPU (``x * rcp.approx(scale)``; it is bit-identical to codes recorded from them, see
+``test_gpu_vs_reference_vectors.py``); the oracle does the same here because ``conftest.py`` hands it the GPU's
+reciprocal (``oracle.quant_ops.set_reciprocal``) -- on a machine without a GPU it divides by IEEE rules, which rounds
+to a neighbouring code in about one element per million. Means are FP32 sums whose order differs from the oracle's,
+so they get an ulp bound and the centred tensors a mismatch-count bound.
 """
 import pytest
 import torch
@@ -42,7 +41,7 @@ def _same_codes(got, want, max_frac=0.0):
     return bool(((g[diff] - w[diff]).abs() == 1).all())
 
 
-FP32_SCALE_CODES = 2e-5          # see the module docstring
+FP32_SCALE_CODES = 0.0           # see the module docstring: exact, as long as the oracle has the GPU's reciprocal
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])

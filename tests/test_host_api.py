@@ -97,6 +97,45 @@ def test_c_abi_argument_errors_without_a_gpu():
         L.check(rc)
     a = L.AttnArgs()
     assert lib.lbfq_attention_fwd(ctypes.byref(a), None, None) == L.ERR_ARG
+    # smooth_k's column-sum tiles are laid out for D = 64 / 128: any other head dimension is refused before a launch,
+    # through both entries (the shape is checked before the size of the built-in scratch, and before any pointer)
+    for d in (8, 32, 96, 256):
+        rc = lib.lbfq_smooth_k(None, L.BF16, 1, 256, 1, d, None, None, None, None)
+        assert rc == L.ERR_ARG and b"64 or 128" in lib.lbfq_last_error()
+        rc = lib.lbfq_smooth_k_static(None, L.BF16, 1, 256, 1, d, None, None, None)
+        assert rc == L.ERR_ARG and b"64 or 128" in lib.lbfq_last_error()
+    # an unknown element type is a dtype error (TypeError in the host mirror) in every entry
+    rc = lib.lbfq_fp8_block_quant(None, 7, 1, 128, 1, 128, 64, None, 0, 0, None, None)
+    assert rc == L.ERR_DTYPE
+    with pytest.raises(TypeError):
+        L.check(rc)
+    rc = lib.lbfq_gather_rows(None, 7, 1, 128, 1, 128, None, None, None)
+    assert rc == L.ERR_DTYPE
+
+
+def test_debug_flags_round_trip():
+    lib = L.lib()
+    before = L.flags()
+    with L.override(L.FLAG_ATTN_GENERIC | L.FLAG_QM_CORR_FFMA):
+        assert L.flags() & L.FLAG_ATTN_GENERIC and L.flags() & L.FLAG_QM_CORR_FFMA
+        L.set_flag(L.FLAG_QM_CORR_FFMA, False)
+        assert not (L.flags() & L.FLAG_QM_CORR_FFMA)
+    assert L.flags() == before
+    assert lib.lbfq_get_flags() == before
+
+
+def test_head_dimension_is_checked_before_any_launch():
+    x = torch.zeros(1, 256, 1, 32, dtype=torch.bfloat16)
+
+    class FakeCuda(torch.Tensor):
+        """A CPU tensor that claims to live on CUDA: reaches the checks behind the device check without a GPU."""
+        @property
+        def is_cuda(self):
+            return True
+
+    y = x.as_subclass(FakeCuda)
+    with pytest.raises(ValueError, match="64 or 128"):
+        fq.fake_quant_attention(y, y, y, fq.QuantConfig(smoothing="k_only", q_kmeans_k=None))
 
 
 def test_slab_ranges_partition_the_heads():
