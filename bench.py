@@ -5,17 +5,22 @@
 
 One "step" is one call of ``low_bit_fake_quant.fake_quant_attention`` on the
 Wan-14B self-attention shape (B=1, H=40, S=32760 padded to 32768 by the
-reference hook's rule, D=128, BF16) with the ``k_smooth_static`` stack
-(fp8_block 64 Q/K, fp8_channel V, K smoothing, elementwise P*256, online row
-max, 64x64 blocks) -- quantizers and the attention kernel together. With N > 1
-(launched under torchrun) every rank runs one such problem on its own GPU: the
-path has no collective, so scaling is weak (global batch = N).
+reference hook's rule, D=128, BF16) with the ``full_dynamic`` stack -- Q k-means
+32 + V k-means 64 with K co-permuted, full Q/K smoothing, per-block V
+smoothing, fp8_block 64 Q/K, fp8_channel V, dynamic P, qm_k estimated row max,
+64x64 blocks: k-means, smoothing, quantizers and the attention kernel
+together. The ``k_smooth_static`` stack of the same shape is timed in the same
+run and reported under ``config.also``. With N > 1 (launched under torchrun)
+every rank runs one such problem on its own GPU (weak scaling, global batch =
+N: ``value``); the same run also times ONE problem partitioned over the ranks,
+40/N heads each (``strong_scaling``). The path has no collective.
 
 Printed JSON (rank 0): throughput in TFLOP/s with the algorithmic flop count
 4*B*H*Sq*Sk*D on the unpadded shape; ``e2e`` is the same call fed from pinned
 host buffers with the result copied back; ``roofline`` describes the
-attention kernel against the dense-FP8 tensor peak; ``cpu_baseline`` is the
-CPU restatement of the reference timed on a bounded sample.
+attention kernel against the dense-FP8 tensor peak; ``parity`` compares one
+head of the very tensors that were timed with the CPU oracle; ``cpu_baseline``
+is the CPU restatement of the reference timed on a bounded sample.
 """
 import argparse
 import json
@@ -62,6 +67,10 @@ WORKLOADS = {
         p_quant="dynamic", rowmax_mode="online", blasst_lambda=1e-2, blasst_fill="mean_a1.5"), 2),
 }
 VIDEO_GRID = (21, 30, 52)       # (t, h, w) of the 32760 latent tokens, flattened t-major
+# the stack the project's target is stated on; the other stack of the same shape is timed beside it
+DEFAULT_WORKLOAD = "wan14b_self_attn_full_dynamic"
+ALSO = {"wan14b_self_attn_full_dynamic": "wan14b_self_attn_k_smooth_static",
+        "wan14b_self_attn_k_smooth_static": "wan14b_self_attn_full_dynamic"}
 
 
 def make_video_inputs(batch, heads, seq, dim, seed, device, dtype=torch.bfloat16):
@@ -121,6 +130,54 @@ def blasst_skip_ratios(qp, kp, vp, cfg):
     return {"row_skip_ratio": skipped / total if total > 0 else 0.0,
             "tile_skip_ratio": tile_skipped / float(tiles.sum().item()) if tiles.any() else 0.0,
             "skipped_row_blocks": skipped, "total_row_blocks": total}
+
+
+def load_traffic_table():
+    """DRAM bytes per attention launch measured by ncu (profiles/dram_traffic.json): small 4-head captures, scaled
+    here by heads (each head's traffic is independent)."""
+    try:
+        with open(os.path.join(ROOT, "profiles", "dram_traffic.json")) as f:
+            return json.load(f)
+    except (OSError, ValueError):
+        return {}
+
+
+def verify_one_head(qp, kp, vp, cfg, head=0, reference_operands=False):
+    """Parity of the timed inputs themselves: one head of the padded Q / K / V through the library (same k-means
+    labels injected on both sides) against the CPU oracle in the reference's own operand convention
+    (``faithful=True``), plus MSE / cosine of both against BF16 SDPA. Outside every timed region."""
+    import low_bit_fake_quant as fq
+    from low_bit_fake_quant import _lib as L
+    from low_bit_fake_quant.kmeans import kmeans_labels
+    from oracle import api as OA
+    from oracle import quant_ops as OQ
+
+    dev = qp.device
+    OQ.set_reciprocal(lambda t: L.rcp_approx(t, device=dev))          # the oracle divides as the GPU does
+    q1, k1, v1 = (t[:, :, head:head + 1].contiguous() for t in (qp, kp, vp))
+    kw, okw = {}, {}
+    if cfg.q_kmeans_k is not None:
+        kw["_q_labels"] = kmeans_labels(q1, n_clusters=cfg.q_kmeans_k, max_iters=cfg.q_kmeans_iters, seed=cfg.q_kmeans_seed)
+        okw["q_labels"] = kw["_q_labels"].cpu().long()
+    if cfg.v_kmeans_k is not None:
+        kw["_v_labels"] = kmeans_labels(v1, n_clusters=cfg.v_kmeans_k, max_iters=cfg.v_kmeans_iters, seed=cfg.v_kmeans_seed)
+        okw["v_labels"] = kw["_v_labels"].cpu().long()
+    got = fq.fake_quant_attention(q1, k1, v1, cfg, _debug_fp32=True, _reference_operands=reference_operands, **kw).float().cpu()
+    sdpa = fq.reference_attention(q1, k1, v1).float().cpu()
+    torch.set_num_threads(os.cpu_count() or 1)
+    t0 = time.perf_counter()
+    want = OA.fake_quant_attention(q1.cpu(), k1.cpu(), v1.cpu(), cfg, faithful=True, out_fp32=True, **okw)
+    dt = time.perf_counter() - t0
+    m = OA.compute_metrics(got, want)
+    rms = float(want.pow(2).mean().sqrt())
+    row_err = (got - want).abs().amax(dim=-1)
+    a, b = OA.compute_metrics(got, sdpa), OA.compute_metrics(want, sdpa)
+    return {"convention": ("reference BF16 operands" if reference_operands else "e4m3 codes multiplied directly")
+                          + " vs the oracle in the reference's BF16-operand convention",
+            "sample": f"head {head} of the timed tensors, S={qp.shape[1]}", "cos": m["cosine"],
+            "max_abs_over_rms": m["max_abs"] / rms, "rows_over_2e-3_rms": float((row_err > 2e-3 * rms).float().mean()),
+            "mse_vs_sdpa": a["mse"], "mse_vs_sdpa_oracle": b["mse"], "cos_vs_sdpa": a["cosine"], "cos_vs_sdpa_oracle": b["cosine"],
+            "oracle_seconds": dt}
 
 
 class ClockSampler:
@@ -201,7 +258,7 @@ def run_reference_arm(args, workload, cfg_kwargs):
     if rank != 0:
         return
     torch.set_num_threads(os.cpu_count() or 1)
-    seq, heads = 16384, 1
+    seq, heads = 32768, 1                      # the sample the `cpu_baseline` leg of the other arm times
     vals = []
     for i in range(args.warmup + args.steps):
         tf, dt = cpu_oracle_sample(cfg_kwargs, seq=seq, heads=heads, steps=1, seed=i)
@@ -228,11 +285,14 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="wan14b_self_attn_k_smooth_static", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--heads", type=int, default=H_FULL, help="heads per GPU (smaller values are for profiling runs only)")
     ap.add_argument("--seq", type=int, default=S_REAL)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-also", action="store_true", help="skip the second timed stack (config.also)")
+    ap.add_argument("--no-verify", action="store_true", help="skip the one-head parity check against the CPU oracle")
+    ap.add_argument("--no-strong", action="store_true", help="N > 1: skip the one-problem-over-N-ranks partition")
     ap.add_argument("--e2e-heads-per-chunk", type=int, default=None,
                     help="heads per pipelined chunk of the host-buffer entry (default: the entry's own choice)")
     ap.add_argument("--reference-operands", action="store_true",
@@ -261,6 +321,7 @@ def main():
     from low_bit_fake_quant import _lib as L
     from low_bit_fake_quant import attention_triton as K12
     from low_bit_fake_quant.config import QuantConfig
+    from low_bit_fake_quant.sharding import attention_on_shard, slab_range
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -292,6 +353,7 @@ def main():
         flops_per_step = 4.0 * batch * heads * seq * seq_k * D_HEAD
         args.no_e2e = True                                              # the host-buffer entry takes equal shapes
         args.no_cpu_baseline = True
+        args.no_verify = True
     lib = L.lib()
 
     brick_order = None
@@ -304,13 +366,13 @@ def main():
         args.no_e2e = True                                              # the host-buffer entry has no reorder
         brick_order = space_time_block_order(gt, gh, gw, ts=bt, hs=bh_, ws=bw, tail=qp.shape[1] - gt * gh * gw, device=dev)
 
-    def step(qq, kk, vv):
+    def step(qq, kk, vv, c=cfg):
         if brick_order is not None:
-            return fake_quant_attention_reordered(qq, kk, vv, cfg, brick_order)[:, :seq]
+            return fake_quant_attention_reordered(qq, kk, vv, c, brick_order)[:, :seq]
         if seq_k is not None:
             from low_bit_fake_quant.hook import fake_quant_cross_attention
-            return fake_quant_cross_attention(qq, kk, vv, cfg)[:, :seq]
-        o = fq.fake_quant_attention(qq, kk, vv, cfg, _reference_operands=args.reference_operands)
+            return fake_quant_cross_attention(qq, kk, vv, c)[:, :seq]
+        o = fq.fake_quant_attention(qq, kk, vv, c, _reference_operands=args.reference_operands)
         return o[:, :seq]
 
     def barrier():
@@ -319,39 +381,77 @@ def main():
             dist.barrier()
             torch.cuda.synchronize(dev)
 
+    def timed(fn, steps, warmup):
+        """`warmup` untimed and `steps` timed calls of fn, bracketed by barriers; returns (max-over-ranks ms per step,
+        per-launch ms of the attention kernel, library launches per step)."""
+        for _ in range(warmup):
+            fn()
+        barrier()
+        K12.raise_if_device_error(dev)
+        K12.KERNEL_EVENTS = []
+        launches0 = lib.lbfq_launch_count()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        ev0.record()
+        for _ in range(steps):
+            fn()
+        ev1.record()
+        barrier()
+        ms_total = ev0.elapsed_time(ev1)
+        launches = int(lib.lbfq_launch_count() - launches0)
+        kernel_ms = [a.elapsed_time(b) for a, b in K12.KERNEL_EVENTS]
+        K12.KERNEL_EVENTS = None
+        K12.raise_if_device_error(dev)
+        t = torch.tensor([ms_total], device=dev)
+        if dist is not None:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item()) / steps, (sum(kernel_ms) / max(len(kernel_ms), 1)), launches // max(steps, 1)
+
     # the clock sampler (an nvidia-smi child) is started before the warm-up: its start-up takes the driver's
     # locks for a few hundred ms, which would otherwise stall kernel launches inside a short timed region
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
     for _ in range(args.warmup):
-        out = step(qp, kp, vp)
+        step(qp, kp, vp)
     barrier()
-    K12.raise_if_device_error(dev)
     if rank == 0:
-        sampler.lines.clear()                      # keep only the samples taken during the timed region
+        sampler.lines.clear()                      # keep only the samples taken during the timed regions
 
     # ---- timed region: inputs resident in HBM --------------------------------
-    K12.KERNEL_EVENTS = []
-    launches0 = lib.lbfq_launch_count()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    ev0.record()
-    for _ in range(args.steps):
-        out = step(qp, kp, vp)
-    ev1.record()
-    barrier()
-    ms_total = ev0.elapsed_time(ev1)
-    launches = int(lib.lbfq_launch_count() - launches0)
-    kernel_ms = [a.elapsed_time(b) for a, b in K12.KERNEL_EVENTS]
-    K12.KERNEL_EVENTS = None
-    clocks = sampler.stop() if rank == 0 else None
-    K12.raise_if_device_error(dev)
-    t = torch.tensor([ms_total], device=dev)
-    if dist is not None:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_step = float(t.item()) / args.steps
+    ms_step, k_ms, launches = timed(lambda: step(qp, kp, vp), args.steps, 0)
+    fast = lib.lbfq_attention_last_variant() == 1
     value = world * flops_per_step / (ms_step * 1e-3) / 1e12
+
+    # ---- the second stack of the same shape, same tensors (config.also) -------
+    also = None
+    if not args.no_also and args.workload in ALSO and seq_k is None and brick_order is None:
+        a_name = ALSO[args.workload]
+        a_cfg = QuantConfig(**WORKLOADS[a_name][0])
+        if pad_like_hook(qp[:, :seq], kp[:, :seq], vp[:, :seq], a_cfg)[3] == pad:      # same padded length
+            a_ms, a_kms, a_launches = timed(lambda: step(qp, kp, vp, a_cfg), args.steps, args.warmup)
+            also = {"workload": a_name, "value": world * flops_per_step / (a_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+                    "ms_per_step": a_ms, "kernel_ms": a_kms, "gpu_launches_per_step": a_launches,
+                    "roofline_frac": None}
+    clocks = sampler.stop() if rank == 0 else None
+
+    # ---- strong scaling: ONE problem (batch element 0) over the ranks, 40/N heads each --------------
+    strong = None
+    if world > 1 and not args.no_strong and seq_k is None and brick_order is None:
+        lo, hi = slab_range(heads, world, rank)
+        sq, sk, sv = (t[:, :, lo:hi].contiguous() for t in maker(batch, heads, seq, D_HEAD, 1234, dev))   # element 0 everywhere
+        sq, sk, sv, _ = pad_like_hook(sq, sk, sv, cfg)
+
+        def strong_step():
+            o, _ = attention_on_shard(sq, sk, sv, cfg, world=world, rank=rank, sliced=True, total_heads=heads,
+                                      _reference_operands=args.reference_operands)
+            return o
+
+        s_ms, _, _ = timed(strong_step, args.steps, args.warmup)
+        strong = {"value": flops_per_step / (s_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": s_ms,
+                  "heads_per_gpu": [b_ - a_ for a_, b_ in (slab_range(heads, world, r) for r in range(world))],
+                  "note": "one 40-head problem partitioned over the ranks (sharding.attention_on_shard), no collective"}
+        del sq, sk, sv
 
     # ---- end to end: pinned host buffers in, result back ----------------------
     e2e = None
@@ -363,47 +463,46 @@ def main():
         def e2e_step():
             fq.fake_quant_attention_host(hq, hk, hv, cfg, out=hout, device=dev, heads_per_chunk=args.e2e_heads_per_chunk)
 
-        for _ in range(2):
-            e2e_step()
-        barrier()
-        n_e2e = max(2, min(args.steps, 5))
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(n_e2e):
-            e2e_step()
-        e1.record()
-        barrier()
-        te = torch.tensor([e0.elapsed_time(e1)], device=dev)
-        if dist is not None:
-            dist.all_reduce(te, op=dist.ReduceOp.MAX)
-        ms_e2e = float(te.item()) / n_e2e
+        n_e2e = max(3, args.steps)
+        ms_e2e, _, _ = timed(e2e_step, n_e2e, 2)
+
+        # what the host's memory and links allow for these bytes: plain contiguous copies, all ranks at once
+        def copy_only():
+            qp.copy_(hq, non_blocking=True); kp.copy_(hk, non_blocking=True); vp.copy_(hv, non_blocking=True)
+            hout.copy_(qp[:, :seq], non_blocking=True)
+
+        ms_copy, _, _ = timed(copy_only, 3, 1)
+        h2d = int(3 * hq.numel() * hq.element_size())
+        d2h = int(hout.numel() * hout.element_size())
         e2e = {"value": world * flops_per_step / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s",
-               "h2d_bytes_per_step": int(3 * hq.numel() * hq.element_size()),
-               "d2h_bytes_per_step": int(hout.numel() * hout.element_size()), "ms_per_step": ms_e2e}
+               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e, "steps": n_e2e,
+               "copy_ceiling": {"ms_per_step": ms_copy, "gb_per_s_per_gpu": (h2d + d2h) / (ms_copy * 1e-3) / 1e9,
+                                "note": "the same bytes as plain copies from / to pinned memory, every rank at once, no compute: "
+                                        "the lower bound of an unpipelined host-buffer step is this plus the device time"}}
         del hq, hk, hv
+
+    parity = None
+    if rank == 0 and not args.no_verify and brick_order is None and world == 1:
+        parity = verify_one_head(qp, kp, vp, cfg, reference_operands=args.reference_operands)
 
     if rank == 0:
         bf16_peak, hbm_peak, peak_src = load_peaks()
         fp8_peak = 2.0 * bf16_peak          # dense FP8 tensor rate = 2 x the measured dense BF16 rate
-        k_ms = sum(kernel_ms) / max(len(kernel_ms), 1)
         achieved = flops_per_step / (k_ms * 1e-3) / 1e12 if k_ms > 0 else 0.0
-        # DRAM bytes of one attention launch, measured by ncu on a 4-head launch of the same S and scaled by heads
-        # (each head's traffic is independent): 55.5 MB for the TMEM-resident kernel on the k_smooth_static stack, 171.1 MB
-        # on the full_dynamic stack (profiles/attn_fast_kernel_wan14b_*.md), 136.6 MB for the general kernel on the
-        # full_dynamic stack (profiles/attn_kernel_wan14b_full_dynamic.md)
-        fast = lib.lbfq_attention_last_variant() == 1
-        traffic = None
-        if seq == S_REAL and fast and args.workload == "wan14b_self_attn_k_smooth_static":
-            traffic = 55.47e6 * heads / 4.0
-        elif seq == S_REAL and args.workload == "wan14b_self_attn_full_dynamic":
-            traffic = (171.1e6 if fast else 136.6e6) * heads / 4.0
+        kernel_name = "attn_fast_kernel<128,64>" if fast else "attn_kernel<128,64>"
+        # DRAM bytes of one attention launch: ncu captures of 4-head launches of the same S, scaled by heads
+        ent = load_traffic_table().get(f"{args.workload}:{'fast' if fast else 'general'}")
+        traffic = ent["bytes_per_4_heads"] * heads / 4.0 if (ent and seq == S_REAL) else None
         roofline = {"bound": "tensor", "achieved": achieved, "peak": fp8_peak, "unit": "TFLOP/s",
-                    "frac": achieved / fp8_peak, "traffic": traffic, "kernel": "attn_fast_kernel<128,64>" if lib.lbfq_attention_last_variant() == 1 else "attn_kernel<128,64>",
-                    "kernel_ms": k_ms, "peak_source": f"2 x bf16_tflops ({peak_src})"}
+                    "frac": achieved / fp8_peak, "traffic": traffic, "kernel": kernel_name,
+                    "kernel_ms": k_ms, "peak_source": f"2 x bf16_tflops ({peak_src})",
+                    "step_frac": (flops_per_step / (ms_step * 1e-3) / 1e12) / fp8_peak}
+        if also is not None:
+            also["roofline_frac"] = (flops_per_step / (also["kernel_ms"] * 1e-3) / 1e12) / fp8_peak if also["kernel_ms"] > 0 else None
         cpu = None
         if not args.no_cpu_baseline and world == 1:
             torch.set_num_threads(os.cpu_count() or 1)
-            reps = 8                                   # about 10-20 s of host work
+            reps = 8 if cfg.q_kmeans_k is None else 4                  # about 10-30 s of host work
             tf, dt = cpu_oracle_sample(cfg_kwargs, seq=32768, heads=1, steps=reps)
             cpu = {"value": tf, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
                    "sample": f"1 head x S=32768 of the workload (1/40 of a step) x {reps} repeats, {dt:.2f} s each, "
@@ -414,16 +513,19 @@ def main():
             blasst = dict(blasst_skip_ratios(sq, sk_, sv, cfg), blasst_lambda=cfg.blasst_lambda, blasst_fill=cfg.blasst_fill)
             if args.brick is not None:
                 blasst["brick"] = args.brick
+        p_note = {"dynamic": "P re-scaled per (row, block) and handed to a BF16 P.V as the reference rounds it",
+                  "elementwise": "P as e4m3 codes, FP8 P.V"}.get(cfg.p_quant, "P per the V kind")
         line = {
             "metric": "fused FP8 fake-quant attn TFLOP/s at 40x32760x128", "value": value, "unit": "TFLOP/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "bf16 (reference-operand mode)" if args.reference_operands else "fp8_e4m3", "data": "synthetic",
+            "dtype": "bf16 (reference-operand mode)" if args.reference_operands else f"fp8_e4m3 Q.K^T; {p_note}", "data": "synthetic",
             "config": {"workload": args.workload + ("+reference_operands" if args.reference_operands else ""), "B_per_gpu": batch, "global_batch": batch * world, "H": heads,
                        "S": seq, "S_padded": seq + pad, "S_keys": seq_k if seq_k is not None else seq, "D": D_HEAD, "input_dtype": "bf16",
                        "l2": "inputs (3 x %.0f MB) exceed the 126 MB L2" % (qp.numel() * 2 / 1e6),
-                       "parallelism": f"batch x heads sharded over {world} GPU(s), no collective"},
-            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
+                       "parallelism": f"batch x heads sharded over {world} GPU(s), no collective", "also": also},
+            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches * args.steps,
+            "gpu_launches_per_step": launches, "clocks": clocks, "parity": parity, "strong_scaling": strong,
         }
         if blasst is not None:
             line["config"]["blasst"] = blasst       # flops are not reduced for skipped row-blocks

@@ -117,6 +117,45 @@ int lbfq_mxfp8_v_quant(const void* x, int dtype, int B, int S, int H, int D, int
 int lbfq_mxfp8_v_dequant(const uint8_t* codes, const float* scale, int B, int S, int H, int D,
                          int block_s, void* out, int out_dtype, void* stream);
 
+/* ============ fused preprocessing: gather + smooth + rotate + quantise ===== */
+
+/* Quantizer of a fused call */
+#define LBFQ_PREP_FP8_BLOCK 0     /* fp8_block_quant: one FP32 scale per (b, scale_block rows, h) */
+#define LBFQ_PREP_FP8_CHANNEL 1   /* fp8_per_channel_quant: one FP32 scale per (b, h, d); runs two passes */
+#define LBFQ_PREP_MXFP8_V 2       /* mxfp8_v_quant: power-of-two scale per (b, scale_block rows, h, d) */
+#define LBFQ_PREP_MXFP8_QK 3      /* mxfp8_qk_quant: power-of-two scale per (b, s, h, scale_block channels) */
+
+/* One of Q, K, V prepared for the attention kernel in a single pass over the tensor. Replaces, for that tensor, the
+ * chain of src/low_bit_fake_quant/attention.py:166-239,505-591: the k-means gather (kmeans.py:89-90,126-135), K / Q / V
+ * smoothing (preprocess.py:10-193), apply_qk_hadamard (hadamard.py:77-117), a quantizer of quant_triton.py and the
+ * NHD -> BHSD copy, applied in that order with the reference's intermediate roundings into the input dtype. Codes,
+ * scales and means equal those of the separate entry points above and below, bit for bit. */
+typedef struct lbfq_prep_args {
+  const void* x;              /* NHD (B, S, H, D) of dtype */
+  int dtype;
+  int B, S, H, D;
+  const int64_t* order;       /* (B*H, S): source row of each output row (a k-means order), or NULL */
+  const float* chan_mean;     /* (B, H, D): subtracted from every row (the K mean of lbfq_smooth_k), or NULL */
+  int smooth_block;           /* > 0: subtract the column mean of every smooth_block output rows (Q groups, V blocks) */
+  float* block_mean;          /* (B, S/smooth_block, H, D) fp32 receiving those means (qm / v_alpha), or NULL */
+  int hadamard;               /* 1: rotate every row (after the smoothing) */
+  const int8_t* signs;        /* (H, D) of +-1 on the device for this call's heads, or NULL */
+  float had_scale;            /* 1 / sqrt(D) */
+  int kind;                   /* LBFQ_PREP_* */
+  int scale_block;            /* rows per scale (FP8_BLOCK, MXFP8_V) or channels per scale (MXFP8_QK) */
+  uint8_t* codes;             /* `layout` with s_pad rows per (b, h) when layout != NHD */
+  int layout;
+  int s_pad;
+  float* scale;               /* shape of the corresponding quantizer's scale tensor */
+  uint8_t* scale_e8;          /* MXFP8_QK only: UE8M0 tiles as lbfq_mxfp8_qk_quant writes them, or NULL */
+  void* smooth_out;           /* NHD of dtype receiving the re-ordered, smoothed rows as they are before the rotation, or NULL */
+} lbfq_prep_args;
+
+/* Rows one CTA of lbfq_prep_fused would take for these block sizes, or 0 when no group fits shared memory (the
+ * caller then uses the separate entry points). */
+int lbfq_prep_group_rows(int kind, int smooth_block, int scale_block, int S, int D, int dtype);
+int lbfq_prep_fused(const lbfq_prep_args* args, void* stream);
+
 /* ================= smoothing / rotation (preprocess.py, hadamard.py) ====== */
 
 /* smooth_k, src/low_bit_fake_quant/preprocess.py:10-57. k, out: NHD of dtype;

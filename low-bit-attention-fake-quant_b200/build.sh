@@ -7,9 +7,9 @@ FLAGS=(-gencode arch=compute_100a,code=sm_100a -lineinfo -O3 -std=c++17 --expt-r
        -Xcompiler -fPIC -I"$here/../include" ${LBFQ_NVCC_EXTRA:-})
 mkdir -p "$here/build"
 objs=()
-for f in api quant preprocess qm_corr_tc kmeans kmeans_tc attention attention_fast; do
+for f in api quant preprocess prep_fused qm_corr_tc kmeans kmeans_tc attention attention_fast; do
   src="$here/csrc/$f.cu"; obj="$here/build/$f.o"
-  if [[ ! -f "$obj" || "$src" -nt "$obj" || "$here/csrc/common.cuh" -nt "$obj" || "$here/csrc/attn_prims.cuh" -nt "$obj" || "$here/csrc/kmeans_tc.h" -nt "$obj" || "$here/csrc/qm_corr_tc.h" -nt "$obj" || "$here/../include/lbfq.h" -nt "$obj" ]]; then
+  if [[ ! -f "$obj" || "$src" -nt "$obj" || "$here/csrc/common.cuh" -nt "$obj" || "$here/csrc/attn_prims.cuh" -nt "$obj" || "$here/csrc/tile_ops.cuh" -nt "$obj" || "$here/csrc/kmeans_tc.h" -nt "$obj" || "$here/csrc/qm_corr_tc.h" -nt "$obj" || "$here/../include/lbfq.h" -nt "$obj" ]]; then
     "$NVCC" "${FLAGS[@]}" -c "$src" -o "$obj" &
   fi
   objs+=("$obj")

@@ -55,9 +55,14 @@ static_assert(kFastRegsSoftmax % 8 == 0 && kFastRegsService % 8 == 0, "setmaxnre
 //         over a BF16 copy of V^T (3 key stages: a V stage is twice as large).
 // QB = 1: Q and K are BF16 tensors (the reference's de-quantised operands) and Q.K^T a BF16 MMA; two key stages.
 // BL = 1: BLASST; the row-pair exchange carries three values per block (maximum, sum of scores, largest fill).
+// Key stages of the BF16-P instantiations. A build with fewer stages (-DLBFQ_FAST_PK_STAGES=2) leaves the shared
+// memory that instruction-level profiling needs; it is not a shipped configuration.
+#ifndef LBFQ_FAST_PK_STAGES
+#define LBFQ_FAST_PK_STAGES 3
+#endif
 template <int D, int PK, int QB, int BL = 0>
 struct FastSmem {
-  static constexpr int kStages = QB ? 2 : (PK ? 3 : 4);
+  static constexpr int kStages = QB ? 2 : (PK ? LBFQ_FAST_PK_STAGES : 4);
   static constexpr int kQ = kTileM * D * (QB ? 2 : 1);         // bytes per Q tile
   static constexpr int kK = kChunk * D * (QB ? 2 : 1);         // bytes per K stage
   static constexpr int kV = D * kChunk * (PK ? 2 : 1);        // bytes per V^T stage
@@ -138,8 +143,9 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       mbar_init(BAR_QFULL(t), 1);
       mbar_init(BAR_SFULL(t, 0), 1);
       mbar_init(BAR_SFULL(t, 1), 1);
-      mbar_init(BAR_PRDY(t, 0), 2 * kTileM);
-      mbar_init(BAR_PRDY(t, 1), 2 * kTileM);
+      // arrivals per block: every thread of the tile (e4m3 P) or one per softmax warp of the tile (BF16 P), see below
+      mbar_init(BAR_PRDY(t, 0), PK == 0 ? 2 * kTileM : kFastSoftmaxWarps / 2);
+      mbar_init(BAR_PRDY(t, 1), PK == 0 ? 2 * kTileM : kFastSoftmaxWarps / 2);
       mbar_init(BAR_PENULT(t), 1);
       mbar_init(BAR_ODONE(t), 1);
     }
@@ -149,7 +155,7 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       mbar_init(BAR_KFREE(s), 2);
       mbar_init(BAR_VFREE(s), 2);
       mbar_init(BAR_SIDEFULL(s), 1);
-      mbar_init(BAR_SIDEFREE(s), (CORR ? kFastSoftmaxWarps * 32 : 0) + (VALPHA ? 2 : 0) + ((CORR || VALPHA) ? 0 : 1));
+      mbar_init(BAR_SIDEFREE(s), (CORR ? kFastSoftmaxWarps : 0) + (VALPHA ? 2 : 0) + ((CORR || VALPHA) ? 0 : 1));
     }
     misc[1] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -226,8 +232,11 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     bool s_seen = false;                     // this block's S-ready barrier was already observed (warp-uniform)
     uint32_t par = 0;                        // parity of the S-ready phases of the current pair of blocks
 
-    auto body = [&](auto buf_c, const int it) {
+    // LAST: the sequence's final key block (the only one that can be ragged, has no successor to prefetch for or to
+    // wait on); every other block runs the instantiation without those tests
+    auto body = [&](auto buf_c, auto last_c, const int it) {
       constexpr int BUF = decltype(buf_c)::value;
+      constexpr bool LAST = decltype(last_c)::value;
       if (!s_seen) mbar_wait_cont(bar_s[BUF], par, abort_flag, p.status, 12);
       s_seen = false;
       tc_fence_after();
@@ -237,7 +246,7 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       // (sq * sk) * sm_scale in the reference's order; without a score bias straight into the log2 domain
       const float f = (sq * sk) * sm_scale;
       const float c = NAT ? 1.0f : f * kLog2e;
-      const bool more = it != last;
+      constexpr bool more = !LAST;
       if (++scale_sub == blocks_per_scale) {   // next block's scale, off the critical path
         scale_sub = 0;
         if constexpr (!QB) {
@@ -245,10 +254,12 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           if (more) sk = *ksc;
         }
       }
+      // key block within its 128-key stage: with two blocks per stage it is the S buffer's index, a constant here
+      [[maybe_unused]] const int sub_in_stage = (NSUB == 2) ? BUF : side_sub;
       if constexpr (CORR) {
         // scores = dot * f + corr (attention_triton.py:154-160)
-        if (side_sub == 0) mbar_wait_cont(BAR_SIDEFULL(side_stage), side_par, abort_flag, p.status, 15);
-        const float* crow = corr_sm + side_stage * (2 * kChunk) + side_sub * BN;
+        if (sub_in_stage == 0) mbar_wait_cont(BAR_SIDEFULL(side_stage), side_par, abort_flag, p.status, 15);
+        const float* crow = corr_sm + side_stage * (2 * kChunk) + sub_in_stage * BN;
         const float4* cm = reinterpret_cast<const float4*>(crow + half * HB);
         const float2 f2 = make_float2(f, f);
 #pragma unroll
@@ -269,7 +280,7 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           mine[i] = __float_as_uint(v.x); mine[i + 1] = __float_as_uint(v.y);
         }
       }
-      const bool ragged = !more && tail_valid < BN;
+      const bool ragged = LAST && tail_valid < BN;
       if (ragged) {                            // ragged tail: only the last block of a sequence
 #pragma unroll
         for (int i = 0; i < HB; ++i)
@@ -363,6 +374,10 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       // row know it without talking to each other
       [[maybe_unused]] float pmax = 1.f;
       [[maybe_unused]] float s_p = 1.f, inv_p = 1.f;
+      // Without BLASST the scaled P modes never form p itself: q = p / s_P = exp2(z - log2 s_P) comes straight out of the
+      // exponential (one multiplication per element less), and the row sum is s_P * sum(q).
+      constexpr bool FOLD = PK != 0 && !BL;
+      [[maybe_unused]] float bias_q = bias;
       [[maybe_unused]] float fill_const = 0.f;          // BLASST: the value a skipped row fills every column with
       if constexpr (BL) {
         // A skipped row contributes a softmax-free fill instead of its exponentials (attention_triton.py:231-324):
@@ -451,11 +466,25 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           const int e = pow2_scale_exp(fmaxf(pmax, 1e-4f));
           s_p = pow2f(e);
           inv_p = pow2f(-e);
+          if constexpr (FOLD) bias_q = bias - (float)e;                    // p * 2^-e = exp2(z - e)
         } else {
           s_p = scale_from_amax(fmaxf(pmax, 1e-12f));          // the reference's `amax / 448` and `p / s` (common.cuh)
-          inv_p = rcp_approx(s_p);
+          if constexpr (FOLD) {
+            // p / s_P = 448 * exp2(z - z_max): the running max drops out of the quotient. (Blocks whose largest P is
+            // under the 1e-12 floor keep the floored scale: exp2(z - log2(1e-12 / 448)).)
+            constexpr float kLog2Fp8Max = 8.807354922057604f;              // log2(448)
+            constexpr float kLog2Floor = -48.67133070387592f;              // log2(1e-12 / 448)
+            if (pmax >= 1e-12f) bias_q = CORR ? fmaf(-bmax, kLog2e, kLog2Fp8Max) : fmaf(-bmax_raw, c, kLog2Fp8Max);
+            else bias_q = bias - kLog2Floor;
+          } else {
+            inv_p = rcp_approx(s_p);
+          }
         }
       }
+      const float2 bias_q2 = make_float2(bias_q, bias_q);
+      auto arg_q = [&](uint32_t x0, uint32_t x1) -> float2 {
+        return __ffma2_rn(make_float2(__uint_as_float(x0), __uint_as_float(x1)), c2, bias_q2);
+      };
       const float2 inv2 = make_float2(inv_p, inv_p);
       // row sum over the unquantised P, then the P operand of the block's P.V
       auto emit = [&](const int i, const float2 pa, const float2 pb) {
@@ -466,7 +495,8 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           pk[i / 4] = f32x4_to_e4m3x4(pa.x, pa.y, pb.x, pb.y);
         } else {
           // e4m3(p / s) * s, rounded to BF16: the operand the reference gives its P.V product
-          const float2 qa = __fmul2_rn(pa, inv2), qb = __fmul2_rn(pb, inv2);
+          float2 qa = pa, qb = pb;                                        // FOLD: pa, pb are the quotients already
+          if constexpr (!FOLD) { qa = __fmul2_rn(pa, inv2); qb = __fmul2_rn(pb, inv2); }
           pk[i / 2] = e4m3_round_scale_bf16x2(qa.x, qa.y, s_p);
           pk[i / 2 + 1] = e4m3_round_scale_bf16x2(qb.x, qb.y, s_p);
         }
@@ -492,12 +522,13 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       } else {
 #pragma unroll
         for (int i = 0; i < HB; i += 4) {
-          const float2 za = arg(mine[i], mine[i + 1]);
-          const float2 zb = arg(mine[i + 2], mine[i + 3]);
+          const float2 za = FOLD ? arg_q(mine[i], mine[i + 1]) : arg(mine[i], mine[i + 1]);
+          const float2 zb = FOLD ? arg_q(mine[i + 2], mine[i + 3]) : arg(mine[i + 2], mine[i + 3]);
           emit(i, make_float2(ex2(za.x), ex2(za.y)), make_float2(ex2(zb.x), ex2(zb.y)));
         }
       }
-      l_i = l_i * alpha + ((psa.x + psa.y) + (psb.x + psb.y));
+      if constexpr (FOLD) l_i = fmaf(l_i, alpha, s_p * ((psa.x + psa.y) + (psb.x + psb.y)));     // sum(p) = s_P * sum(q)
+      else l_i = l_i * alpha + ((psa.x + psa.y) + (psb.x + psb.y));
       if constexpr (PK != 0) l_pos = pmax > 0.f || (l_pos && alpha != 0.f);
       if (it > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
         // Some row of this warp raised its max: the accumulator must be rescaled before this block's P.V,
@@ -531,6 +562,8 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         // c_acc += rowsum(P) * alpha_v (attention_triton.py:378-383) as one more K step of P.V: this thread's part of
         // the row sum of the BF16 P, split into three BF16 pieces, against the pieces of alpha' staged by the
         // producer: (h + m + l) * (h' + m' + l') without the three smallest cross terms
+        // (the sum has to see the BF16 rounding of P: summing the FP32 products instead moved the result by up to
+        // 4e-3 of its RMS with dynamic P, whose few distinct codes per row and block round alike)
         float2 rs2 = make_float2(0.f, 0.f);
 #pragma unroll
         for (int w = 0; w < PW; ++w)
@@ -548,13 +581,20 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       if constexpr (PW == 16) { LBFQ_TMEM_ST16(tP[BUF], pk); }
       else if constexpr (PW == 8) tmem_st8(tP[BUF], pk);
       else tmem_st4(tP[BUF], pk);
-      tc_wait_st();
+      tc_wait_st();                            // warp-collective: every lane's P is in tensor memory
       tc_fence_before();
-      mbar_arrive(bar_prdy + 8u * BUF);
+      // the e4m3-P instantiations are faster with every thread arriving, the BF16-P ones with one arrival per warp
+      // (measured on the two benchmark stacks: 1.3 % and 1.0 %)
+      if constexpr (PK == 0) {
+        mbar_arrive(bar_prdy + 8u * BUF);
+      } else {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_prdy + 8u * BUF);
+      }
       m2 = m_new;
       if constexpr (CORR) {
-        // the stage's bias rows are dead once its last key block has read them
-        if (side_sub == NSUB - 1 || !more) mbar_arrive(BAR_SIDEFREE(side_stage));
+        // the stage's bias rows are dead once its last key block has read them (every lane has: __syncwarp above)
+        if ((sub_in_stage == NSUB - 1 || !more) && lane == 0) mbar_arrive(BAR_SIDEFREE(side_stage));
         if (++side_sub == NSUB) {
           side_sub = 0;
           if (++side_stage == kFastStages) { side_stage = 0; side_par ^= 1u; }
@@ -562,14 +602,21 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       }
     };
     {
+      using B0 = std::integral_constant<int, 0>;
+      using B1 = std::integral_constant<int, 1>;
       int it = 0;
 #pragma unroll 1
-      for (; it + 1 < nblk; it += 2) {
-        body(std::integral_constant<int, 0>{}, it);
-        body(std::integral_constant<int, 1>{}, it + 1);
+      for (; it + 2 < nblk; it += 2) {
+        body(B0{}, std::false_type{}, it);
+        body(B1{}, std::false_type{}, it + 1);
         par ^= 1u;
       }
-      if (it < nblk) body(std::integral_constant<int, 0>{}, it);
+      if (it + 1 < nblk) {
+        body(B0{}, std::false_type{}, it);
+        body(B1{}, std::true_type{}, it + 1);
+      } else {
+        body(B0{}, std::true_type{}, it);
+      }
     }
 
     // ---- epilogue (attention_triton.py:387-407) ---------------------------------

@@ -11,69 +11,12 @@
 
 #include <atomic>
 
-#include "common.cuh"
+#include "tile_ops.cuh"
 #include "qm_corr_tc.h"
 
 namespace lbfq {
 
-constexpr int kThreads = 256;
-constexpr int kVec = 8;
 constexpr int kSumRows = 256;     // rows per partial sum of smooth_k (the reference's BLK_S)
-
-template <typename T>
-__device__ __forceinline__ void load8(const T* p, float (&v)[kVec]) {
-#pragma unroll
-  for (int i = 0; i < kVec; ++i) v[i] = Elem<T>::load(p + i);
-}
-template <typename T>
-__device__ __forceinline__ void store8(T* p, const float (&v)[kVec]) {
-#pragma unroll
-  for (int i = 0; i < kVec; ++i) Elem<T>::store(p + i, v[i]);
-}
-template <>
-__device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[kVec]) {
-  uint4 raw = *reinterpret_cast<const uint4*>(p);
-  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    float2 f = __bfloat1622float2(h[i]);
-    v[2 * i] = f.x; v[2 * i + 1] = f.y;
-  }
-}
-template <>
-__device__ __forceinline__ void store8<__nv_bfloat16>(__nv_bfloat16* p, const float (&v)[kVec]) {
-  uint4 raw;
-  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
-  *reinterpret_cast<uint4*>(p) = raw;
-}
-
-// ---- column sums of a row range of one (b, h), reduced in a fixed order -----
-template <typename T>
-__device__ __forceinline__ void column_sums(const T* src, size_t rstride, int nrows, int D,
-                                            float (*buf)[128 + 1], float* out /* smem[D] */) {
-  const int tpr = D / kVec, rpi = kThreads / tpr;
-  const int tr = threadIdx.x / tpr, d0 = (threadIdx.x % tpr) * kVec;
-  float acc[kVec];
-#pragma unroll
-  for (int i = 0; i < kVec; ++i) acc[i] = 0.f;
-  for (int r = tr; r < nrows; r += rpi) {
-    float v[kVec];
-    load8<T>(src + r * rstride + d0, v);
-#pragma unroll
-    for (int i = 0; i < kVec; ++i) acc[i] += v[i];
-  }
-#pragma unroll
-  for (int i = 0; i < kVec; ++i) buf[tr][d0 + i] = acc[i];
-  __syncthreads();
-  if (threadIdx.x < D) {
-    float s = 0.f;
-    for (int r = 0; r < rpi; ++r) s += buf[r][threadIdx.x];
-    out[threadIdx.x] = s;
-  }
-  __syncthreads();
-}
 
 // ---- K9 smooth_k -------------------------------------------------------------
 template <typename T>
@@ -168,33 +111,7 @@ hadamard_kernel(const T* __restrict__ x, T* __restrict__ out, const int8_t* __re
     float v[E];
 #pragma unroll
     for (int j = 0; j < E; ++j) v[j] = Elem<T>::load(src + j);
-    if (signs) {
-      const int8_t* sg = signs + (size_t)(row % H) * D + lane * E;
-#pragma unroll
-      for (int j = 0; j < E; ++j) v[j] = round_through<T>(v[j] * (float)sg[j]);
-    }
-    // strides inside a lane
-#pragma unroll
-    for (int st = 1; st < E; st <<= 1) {
-#pragma unroll
-      for (int j = 0; j < E; ++j) {
-        if ((j & st) == 0) {
-          float a = v[j], b = v[j + st];
-          v[j] = a + b;
-          v[j + st] = a - b;
-        }
-      }
-    }
-    // strides across lanes: element stride E * m <-> lane stride m
-#pragma unroll
-    for (int m = 1; m < 32; m <<= 1) {
-      const bool upper = (lane & m) != 0;
-#pragma unroll
-      for (int j = 0; j < E; ++j) {
-        float other = __shfl_xor_sync(0xffffffffu, v[j], m);
-        v[j] = upper ? (other - v[j]) : (v[j] + other);
-      }
-    }
+    hadamard_row<T, E>(v, signs ? signs + (size_t)(row % H) * D + lane * E : nullptr, lane);
     T* dst = out + row * D + lane * E;
 #pragma unroll
     for (int j = 0; j < E; ++j) Elem<T>::store(dst + j, v[j] * scale);

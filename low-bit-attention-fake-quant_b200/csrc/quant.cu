@@ -12,127 +12,9 @@
 // scale = amax * fl32(1/448), code = e4m3_rn_sat(clamp(x * rcp.approx(scale), +-448)) -- see common.cuh. One
 // reciprocal per scale block, one multiplication per element.
 
-#include "common.cuh"
+#include "tile_ops.cuh"
 
 namespace lbfq {
-
-constexpr int kThreads = 256;
-constexpr int kVec = 8;          // elements of D per thread access
-constexpr int kTChunk = 128;     // tokens staged per transposed store: 128-byte rows of the transposed codes
-constexpr int kTPitch = kTChunk + 4;   // bytes between the channels' rows in the staging buffer
-
-template <typename T>
-__device__ __forceinline__ void load8(const T* p, float (&v)[kVec]) {
-#pragma unroll
-  for (int i = 0; i < kVec; ++i) v[i] = Elem<T>::load(p + i);
-}
-template <>
-__device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[kVec]) {
-  uint4 raw = *reinterpret_cast<const uint4*>(p);
-  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    float2 f = __bfloat1622float2(h[i]);
-    v[2 * i] = f.x;
-    v[2 * i + 1] = f.y;
-  }
-}
-template <>
-__device__ __forceinline__ void load8<__half>(const __half* p, float (&v)[kVec]) {
-  uint4 raw = *reinterpret_cast<const uint4*>(p);
-  const __half2* h = reinterpret_cast<const __half2*>(&raw);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    float2 f = __half22float2(h[i]);
-    v[2 * i] = f.x;
-    v[2 * i + 1] = f.y;
-  }
-}
-template <>
-__device__ __forceinline__ void load8<float>(const float* p, float (&v)[kVec]) {
-  float4 a = *reinterpret_cast<const float4*>(p);
-  float4 b = *reinterpret_cast<const float4*>(p + 4);
-  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
-  v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-}
-
-__device__ __forceinline__ uint2 pack8(const float (&q)[kVec]) {
-  uint32_t lo = (uint32_t)f32x2_to_e4m3x2(q[0], q[1]) | ((uint32_t)f32x2_to_e4m3x2(q[2], q[3]) << 16);
-  uint32_t hi = (uint32_t)f32x2_to_e4m3x2(q[4], q[5]) | ((uint32_t)f32x2_to_e4m3x2(q[6], q[7]) << 16);
-  return make_uint2(lo, hi);
-}
-
-struct CodeDst {
-  uint8_t* base;
-  int layout;
-  int S, H, D, s_pad;
-};
-
-// Store the codes of rows [s0, s0 + nrows) of slab (b, h); `quant(r, d0, q)`
-// 4 x 4 byte transpose: a0..a3 hold bytes [c0 c1 c2 c3] of tokens 0..3; out[c] = [t0 t1 t2 t3] of channel c
-__device__ __forceinline__ void transpose4x4(uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t* out) {
-  const uint32_t t0 = __byte_perm(a0, a1, 0x5140), t1 = __byte_perm(a2, a3, 0x5140);   // channels 0, 1 of two tokens
-  const uint32_t t2 = __byte_perm(a0, a1, 0x7362), t3 = __byte_perm(a2, a3, 0x7362);   // channels 2, 3
-  out[0] = __byte_perm(t0, t1, 0x5410);
-  out[1] = __byte_perm(t0, t1, 0x7632);
-  out[2] = __byte_perm(t2, t3, 0x5410);
-  out[3] = __byte_perm(t2, t3, 0x7632);
-}
-
-// fills the 8 quantised-and-clamped fp32 values of row r, columns d0..d0+7.
-// NHD / BHSD are written directly (8-byte stores); BHDS goes through a
-// shared-memory transpose so that global stores stay 16 bytes wide.
-template <typename QuantFn>
-__device__ __forceinline__ void store_tile(const CodeDst& dst, int b, int h, int s0, int nrows,
-                                           uint8_t* tbuf, QuantFn quant) {
-  const int D = dst.D;
-  const int tpr = D / kVec;                   // threads per row
-  const int rows_per_iter = kThreads / tpr;
-  const int tr = threadIdx.x / tpr;
-  const int d0 = (threadIdx.x % tpr) * kVec;
-  if (dst.layout != LBFQ_LAYOUT_BHDS) {
-    for (int r = tr; r < nrows; r += rows_per_iter) {
-      float q[kVec];
-      quant(r, d0, q);
-      size_t off = dst.layout == LBFQ_LAYOUT_NHD
-                       ? (((size_t)b * dst.S + (s0 + r)) * dst.H + h) * D + d0
-                       : (((size_t)b * dst.H + h) * dst.s_pad + (s0 + r)) * D + d0;
-      *reinterpret_cast<uint2*>(dst.base + off) = pack8(q);
-    }
-    return;
-  }
-  // Transposed layout: the codes of up to kTChunk tokens go through shared memory as [channel][token]. A thread
-  // quantises four consecutive tokens of its eight channels and transposes the 4 x 8 bytes in registers
-  // (byte permutes), so that it stores one 32-bit word per channel instead of four single bytes.
-  for (int c0 = 0; c0 < nrows; c0 += kTChunk) {
-    const int cn = min(kTChunk, nrows - c0);           // a multiple of 16 (checked on the host)
-    for (int qd = tr; qd * 4 < cn; qd += rows_per_iter) {
-      uint2 pk[4];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        float q[kVec];
-        quant(c0 + qd * 4 + j, d0, q);
-        pk[j] = pack8(q);
-      }
-      uint32_t w[8];
-      transpose4x4(pk[0].x, pk[1].x, pk[2].x, pk[3].x, w);
-      transpose4x4(pk[0].y, pk[1].y, pk[2].y, pk[3].y, w + 4);
-#pragma unroll
-      for (int i = 0; i < kVec; ++i) *reinterpret_cast<uint32_t*>(tbuf + (d0 + i) * kTPitch + qd * 4) = w[i];
-    }
-    __syncthreads();
-    // 16-byte row segments, read back as four words (the pitch keeps rows a word, not 16 bytes, apart)
-    const int segs = cn / 16;
-    for (int idx = threadIdx.x; idx < D * segs; idx += kThreads) {
-      int d = idx / segs, sg = idx % segs;
-      const uint32_t* src = reinterpret_cast<const uint32_t*>(tbuf + d * kTPitch + sg * 16);
-      uint4 val = make_uint4(src[0], src[1], src[2], src[3]);
-      size_t off = (((size_t)b * dst.H + h) * D + d) * dst.s_pad + (s0 + c0 + sg * 16);
-      *reinterpret_cast<uint4*>(dst.base + off) = val;
-    }
-    __syncthreads();
-  }
-}
 
 // ---------------------------------------------------------------------------
 // K1: fp8_block -- one scale per (b, S-block, h) tile of block_s x D.
@@ -434,6 +316,8 @@ static int zero_pad(uint8_t* codes, int layout, int B, int S, int H, int D, int 
 
 using namespace lbfq;
 
+namespace lbfq { int channel_scale_launch(float* scale, int n, cudaStream_t st); }
+
 static int fp8_block_quant_impl(const void* x, int dtype, int B, int S, int H, int D, int block_s, const float* mean,
                                 uint8_t* codes, int layout, int s_pad, float* scale, void* stream);
 
@@ -516,15 +400,20 @@ extern "C" int lbfq_fp8_channel_quant(const void* x, int dtype, int B, int S, in
   LBFQ_DISPATCH_DTYPE(dtype, T,
       channel_amax_kernel<T><<<grid_a, kThreads, 0, st>>>((const T*)x, S, H, D, (unsigned int*)scale));
   if (int rc = check_launch("channel_amax")) return rc;
-  const int n = B * H * D;
-  channel_scale_kernel<<<(n + 255) / 256, 256, 0, st>>>(scale, n);
-  if (int rc = check_launch("channel_scale")) return rc;
+  if (int rc = channel_scale_launch(scale, B * H * D, st)) return rc;
   const int grid_q = B * ((S + kTChunk - 1) / kTChunk) * H;
   LBFQ_DISPATCH_DTYPE(dtype, T,
       channel_quant_kernel<T><<<grid_q, kThreads, 0, st>>>((const T*)x, dst, scale));
   if (int rc = check_launch("channel_quant")) return rc;
   return zero_pad(codes, layout, B, S, H, D, s_pad, st);
 }
+
+namespace lbfq {
+int channel_scale_launch(float* scale, int n, cudaStream_t st) {
+  channel_scale_kernel<<<(n + 255) / 256, 256, 0, st>>>(scale, n);
+  return check_launch("channel_scale");
+}
+}  // namespace lbfq
 
 static int dequant_launch(const uint8_t* codes, const float* scale, int B, int S, int H, int D, int kind,
                           int blk, void* out, int out_dtype, void* stream) {

@@ -67,6 +67,23 @@ class AttnArgs(C.Structure):
     ]
 
 
+class PrepArgs(C.Structure):
+    """Mirror of ``lbfq_prep_args`` (include/lbfq.h)."""
+
+    _fields_ = [
+        ("x", C.c_void_p), ("dtype", C.c_int),
+        ("B", C.c_int), ("S", C.c_int), ("H", C.c_int), ("D", C.c_int),
+        ("order", C.c_void_p), ("chan_mean", C.c_void_p),
+        ("smooth_block", C.c_int), ("block_mean", C.c_void_p),
+        ("hadamard", C.c_int), ("signs", C.c_void_p), ("had_scale", C.c_float),
+        ("kind", C.c_int), ("scale_block", C.c_int),
+        ("codes", C.c_void_p), ("layout", C.c_int), ("s_pad", C.c_int),
+        ("scale", C.c_void_p), ("scale_e8", C.c_void_p), ("smooth_out", C.c_void_p),
+    ]
+
+
+PREP_FP8_BLOCK, PREP_FP8_CHANNEL, PREP_MXFP8_V, PREP_MXFP8_QK = 0, 1, 2, 3
+
 _P = C.c_void_p
 _I = C.c_int
 _SIGS = {
@@ -87,6 +104,8 @@ _SIGS = {
     "lbfq_mxfp8_qk_dequant": (_I, [_P, _P, _I, _I, _I, _I, _I, _P, _I, _P]),
     "lbfq_mxfp8_v_quant": (_I, [_P, _I, _I, _I, _I, _I, _I, _P, _I, _I, _P, _P]),
     "lbfq_mxfp8_v_dequant": (_I, [_P, _P, _I, _I, _I, _I, _I, _P, _I, _P]),
+    "lbfq_prep_group_rows": (_I, [_I, _I, _I, _I, _I, _I]),
+    "lbfq_prep_fused": (_I, [C.POINTER(PrepArgs), _P]),
     "lbfq_smooth_k_scratch_floats": (C.c_int64, [_I, _I, _I, _I]),
     "lbfq_smooth_k": (_I, [_P, _I, _I, _I, _I, _I, _P, _P, _P, _P]),
     "lbfq_smooth_k_static_max_floats": (C.c_int64, []),

@@ -216,17 +216,26 @@ def _fake_quant_attention_sdpa(q_work, k_work, v_work, qm, v_alpha, cfg: QuantCo
 def _fake_quant_attention_p_requant(q_work, k_work, v_work, qm, v_alpha, q_kmeans, cfg: QuantConfig,
                                     sm_scale, out_dtype, *, return_stats: bool = False,
                                     out_fp32_exact: bool = False, head_offset: int = 0, total_heads: int = 0,
-                                    rowmax_counters=None, k_mean=None):
+                                    rowmax_counters=None, k_mean=None, prepared=None):
     """Quantise straight into the kernel's layouts and launch it. Returns the
-    output in NHD, rows already back in the original Q order."""
+    output in NHD, rows already back in the original Q order.
+
+    ``prepared`` (from ``_prepare_fused``): the codes and scales are there already; ``q_work`` / ``v_work`` are then
+    only looked at for their shapes and ``k_work`` is the smoothed K of the score bias (or the input K)."""
     # K / V may have their own length (cross-attention, an extension: the reference's entry takes equal shapes only)
     b, s, h, d = q_work.shape
     s_k = k_work.shape[1]
     sq_pad, s_pad = _round_up(s, 128), _round_up(s_k, 128)
-    q_in, k_in = _rotated(q_work, k_work, cfg, head_offset, total_heads)
-
     q_sf = k_sf = None
-    if cfg.qk_quant == "fp8_block":
+    if prepared is not None:
+        q_codes, q_scale, q_sf = prepared["q"]
+        k_codes, k_scale, k_sf = prepared["k"]
+    else:
+        q_in, k_in = _rotated(q_work, k_work, cfg, head_offset, total_heads)
+
+    if prepared is not None:
+        pass
+    elif cfg.qk_quant == "fp8_block":
         q_codes, q_scale = fp8_block_quant(q_in, block_s=cfg.fp8_block_size, _layout=L.LAYOUT_BHSD, _s_pad=sq_pad)
         # `k_mean`: K arrives unsmoothed and the quantizer subtracts its channel mean (smooth_k fused in)
         k_codes, k_scale = fp8_block_quant(k_in, block_s=cfg.fp8_block_size, _layout=L.LAYOUT_BHSD, _s_pad=s_pad, _mean=k_mean)
@@ -240,7 +249,10 @@ def _fake_quant_attention_p_requant(q_work, k_work, v_work, qm, v_alpha, q_kmean
         raise ValueError(f"unsupported qk_quant: {cfg.qk_quant!r}")
 
     v_block = 0
-    if cfg.v_quant == "fp8_channel":
+    if prepared is not None:
+        v_codes, v_scale = prepared["v"]
+        v_block = {"fp8_channel": 0, "fp8_block": cfg.v_fp8_block_size, "mxfp8": cfg.v_mxfp8_block_size}[cfg.v_quant]
+    elif cfg.v_quant == "fp8_channel":
         v_codes, v_scale = fp8_per_channel_quant(v_work, _layout=L.LAYOUT_BHDS, _s_pad=s_pad)
     elif cfg.v_quant == "fp8_block":
         v_block = cfg.v_fp8_block_size
@@ -293,6 +305,75 @@ def _fake_quant_attention_p_requant(q_work, k_work, v_work, qm, v_alpha, q_kmean
         out_fp32_exact=out_fp32_exact,
         rowmax_counters=rowmax_counters,
     )
+
+
+def _prepare_fused(q, k, v, cfg: QuantConfig, *, head_offset: int = 0, total_heads: int = 0, q_labels=None, v_labels=None):
+    """Preprocessing (attention.py:166-239 of the reference) and quantisation (:531-570) of all three tensors with one
+    fused pass per tensor (``prepare.prep_fused``): the k-means orders and the K channel mean are found first, then
+    each tensor is gathered, smoothed, rotated and quantised straight into the kernel's layout. Returns the dictionary
+    ``_fake_quant_attention_p_requant`` takes as ``prepared`` (plus qm, v_alpha, the Q reorder and the smoothed K), or
+    ``None`` when some block size combination is not served by the fused kernel (the caller then runs the separate
+    kernels). Every value equals the separate kernels' bit for bit."""
+    from .kmeans import kmeans_labels, order_from_labels
+    from .prepare import group_rows, hadamard_signs, prep_fused
+
+    b, s, h, d = q.shape
+    s_k = k.shape[1]
+    if cfg.qk_quant not in ("fp8_block", "mxfp8") or cfg.v_quant not in ("fp8_channel", "fp8_block", "mxfp8"):
+        return None
+    if cfg.smoothing not in ("off", "k_only", "full") or cfg.v_smooth_mode not in ("off", "per_block"):
+        return None
+    full = cfg.smoothing == "full"
+    qk_kind = "fp8_block" if cfg.qk_quant == "fp8_block" else "mxfp8_qk"
+    qk_block = cfg.fp8_block_size if cfg.qk_quant == "fp8_block" else cfg.mxfp8_block_size
+    v_kind = {"fp8_channel": "fp8_channel", "fp8_block": "fp8_block", "mxfp8": "mxfp8_v"}[cfg.v_quant]
+    v_block = {"fp8_channel": 0, "fp8_block": cfg.v_fp8_block_size, "mxfp8": cfg.v_mxfp8_block_size}[cfg.v_quant]
+    q_sb = cfg.q_smooth_block_size if full else 0
+    v_sb = cfg.v_smooth_block_size if cfg.v_smooth_mode == "per_block" else 0
+    for kind, sb, blk, seq in ((qk_kind, q_sb, qk_block, s), (qk_kind, 0, qk_block, s_k), (v_kind, v_sb, v_block, s_k)):
+        if (sb > 0 and seq % sb != 0) or (kind in ("fp8_block", "mxfp8_v") and (blk <= 0 or seq % blk != 0)):
+            return None                                   # the separate kernels raise the reference's errors for these
+        if kind == "mxfp8_qk" and (blk <= 0 or d % blk != 0 or blk % 8 != 0 or (blk & (blk - 1)) != 0 or d // blk > 4):
+            return None
+        if group_rows(kind, smooth_block=sb, scale_block=blk, seq=seq, dim=d, dtype=q.dtype) <= 0:
+            return None
+    if s % 16 != 0 or s_k % 16 != 0:
+        return None
+    sq_pad, s_pad = _round_up(s, 128), _round_up(s_k, 128)
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+
+    q_km = None
+    q_order = v_order = None
+    if cfg.q_kmeans_k is not None:
+        if cfg.q_kmeans_k <= 0 or cfg.q_kmeans_k > s:
+            return None
+        lab = q_labels if q_labels is not None else kmeans_labels(
+            q, n_clusters=cfg.q_kmeans_k, max_iters=cfg.q_kmeans_iters, seed=cfg.q_kmeans_seed, head_offset=head_offset,
+            total_heads=total_heads)
+        q_order, q_inv = order_from_labels(lab, cfg.q_kmeans_k)
+        q_km = KMeansReorderResult(tensor_reordered=None, order=q_order, inverse_order=q_inv, labels=lab.to(torch.int64))
+    k_mean = k_channel_mean(k) if cfg.smoothing in ("k_only", "full") else None       # over K in its own order
+    if cfg.v_kmeans_k is not None:
+        if cfg.v_kmeans_k <= 0 or cfg.v_kmeans_k > s_k:
+            return None
+        lab = v_labels if v_labels is not None else kmeans_labels(
+            v, n_clusters=cfg.v_kmeans_k, max_iters=cfg.v_kmeans_iters, seed=cfg.v_kmeans_seed, head_offset=head_offset,
+            total_heads=total_heads)
+        v_order, _ = order_from_labels(lab, cfg.v_kmeans_k)
+    signs = None
+    if cfg.qk_hadamard and cfg.qk_hadamard_random_sign:
+        signs = hadamard_signs(h, d, cfg.qk_hadamard_seed, q.device, head_offset=head_offset,
+                               total_heads=total_heads if total_heads > 0 else None)
+    mx = cfg.qk_quant == "mxfp8"
+    qc, qs, qm, q_sf, _ = prep_fused(q, kind=qk_kind, scale_block=qk_block, order=q_order, smooth_block=q_sb,
+                                     hadamard=cfg.qk_hadamard, signs=signs, layout=L.LAYOUT_BHSD, s_pad=sq_pad, want_scale_e8=mx)
+    kc, ks, _, k_sf, k_smooth = prep_fused(k, kind=qk_kind, scale_block=qk_block, order=v_order, chan_mean=k_mean,
+                                           hadamard=cfg.qk_hadamard, signs=signs, layout=L.LAYOUT_BHSD, s_pad=s_pad,
+                                           want_scale_e8=mx, want_prepared=full)
+    vc, vs, v_alpha, _, _ = prep_fused(v, kind=v_kind, scale_block=v_block, order=v_order, smooth_block=v_sb,
+                                       layout=L.LAYOUT_BHDS, s_pad=s_pad)
+    return {"q": (qc, qs, q_sf), "k": (kc, ks, k_sf), "v": (vc, vs), "qm": qm, "v_alpha": v_alpha, "q_kmeans": q_km,
+            "k_smooth": k_smooth if full else k}
 
 
 # ---------------------------------------------------------------------------
@@ -429,6 +510,19 @@ def fake_quant_attention(
         sm_scale = 1.0 / math.sqrt(d)
     if cfg.blasst_lambda is not None and not cfg.p_requant:
         raise ValueError("BLASST skip/fill requires cfg.p_requant=True")
+
+    # everything in front of the streaming kernel as one fused pass per tensor, when nothing asks for the
+    # intermediate tensors (a cache, the artifacts, the reference's own operands) and the kernel takes the codes
+    if (preprocess_cache is None and cfg.p_requant and not _reference_operands and not return_artifacts
+            and not (L.flags() & L.FLAG_UNFUSED_PREPROCESS)
+            and not (cfg.qk_quant == "mxfp8" and cfg.v_quant != "fp8_block" and cfg.blasst_lambda is None
+                     and not (L.flags() & L.FLAG_ATTN_GENERIC))):
+        prep = _prepare_fused(q, k, v, cfg, head_offset=_head_offset, total_heads=_total_heads, q_labels=_q_labels,
+                              v_labels=_v_labels)
+        if prep is not None:
+            return _fake_quant_attention_p_requant(
+                q, prep["k_smooth"], v, prep["qm"], prep["v_alpha"], prep["q_kmeans"], cfg, sm_scale, out_dtype,
+                out_fp32_exact=_debug_fp32, head_offset=_head_offset, total_heads=_total_heads, prepared=prep)
 
     if preprocess_cache is not None:
         pc = preprocess_cache
