@@ -252,6 +252,11 @@ int lbfq_qm_corr(const float* qm, const void* k_smooth, int dtype, int B, int S,
  * reference's own launcher receives (attention_triton.py:410-436): q_codes, k_codes, v_codes then point to BF16 data
  * of the same shapes, Q.K^T and P.V run as BF16 MMAs, and q_scale / k_scale are not read. */
 #define LBFQ_QK_BF16 2
+/* Q and K are BF16 tensors as above, V^T stays e4m3 codes with its v_kind / v_scale (the reference's launcher is given
+ * V as "FP8 cast to BF16", attention_triton.py:440-446: the values are e4m3 codes, so nothing is lost). Served by the
+ * general kernel: Q.K^T a BF16 MMA, P.V an FP8 MMA with every scale applied in FP32 around it -- the route for the
+ * per-block V scale (v_block_scale_bsh) and for BLASST through the reference's direct-launch signature. */
+#define LBFQ_QK_BF16_V_CODES 3
 /* BLASST fill kinds (attention_triton.py:39-45) */
 #define LBFQ_FILL_ZERO 0
 #define LBFQ_FILL_MAX 1

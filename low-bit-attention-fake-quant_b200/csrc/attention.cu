@@ -41,25 +41,27 @@ namespace lbfq {
 namespace attn {
 
 
-template <int D, int BN>
+template <int D, int BN, bool QKBF = false>
 struct Smem {
-  static constexpr int kQ = kTileM * D;                       // bytes per Q tile
-  static constexpr int kK = kChunk * D;                       // bytes per K stage
+  // BF16 Q / K (the reference's de-quantised operands) double the Q tile and the K stages: two key stages then
+  static constexpr int kNst = QKBF ? 2 : kStages;
+  static constexpr int kQ = kTileM * D * (QKBF ? 2 : 1);      // bytes per Q tile
+  static constexpr int kK = kChunk * D * (QKBF ? 2 : 1);      // bytes per K stage
   static constexpr int kV = (D + kOnesRows) * kChunk;         // bytes per V^T stage (with the rows of ones)
   static constexpr int offQ = 0;
   static constexpr int offK = offQ + 2 * kQ;
-  static constexpr int offV = offK + kStages * kK;
-  static constexpr int offQS = offV + kStages * kV;            // Q scale-factor tiles (block-scaled Q/K only)
+  static constexpr int offV = offK + kNst * kK;
+  static constexpr int offQS = offV + kNst * kV;            // Q scale-factor tiles (block-scaled Q/K only)
   static constexpr int offKS = offQS + 2 * 512;                // K scale-factor tile per stage
   // side vectors staged per 128-key stage for the softmax threads (read with broadcast shared loads
   // instead of per-thread global loads): the score bias `corr` of each tile's Q group (128 floats per
   // tile), and per key block the V-smoothing vector alpha' and the mxfp8 V scales (D floats each)
   static constexpr int kSub = kChunk / BN;
-  static constexpr int offCorr = offKS + kStages * 512;
-  static constexpr int offAlpha = offCorr + kStages * 2 * kChunk * 4;
-  static constexpr int offVs = offAlpha + kStages * kSub * D * 4;
-  static constexpr int offBar = offVs + kStages * kSub * D * 4;
-  static constexpr int kNumBar = 2 + 4 * kStages + 12 + 2 * kStages;
+  static constexpr int offCorr = offKS + kNst * 512;
+  static constexpr int offAlpha = offCorr + kNst * 2 * kChunk * 4;
+  static constexpr int offVs = offAlpha + kNst * kSub * D * 4;
+  static constexpr int offBar = offVs + kNst * kSub * D * 4;
+  static constexpr int kNumBar = 2 + 4 * kNst + 12 + 2 * kNst;
   static constexpr int offMisc = offBar + kNumBar * 8;
   static constexpr int offL = offMisc + 64;                   // partial row sums [tile][half][row]
   static constexpr int total = offL + 2 * 2 * kTileM * 4;
@@ -68,11 +70,13 @@ struct Smem {
 // ---------------------------------------------------------------------------
 // the kernel
 // ---------------------------------------------------------------------------
-template <int D, int BN, bool BLASST, bool QKMX>
+template <int D, int BN, bool BLASST, bool QKMX, bool QKBF = false>
 __global__ void __launch_bounds__(kThreads, 1)
 attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
             const __grid_constant__ CUtensorMap tm_v, const Params p) {
-  using SM = Smem<D, BN>;
+  static_assert(!(QKMX && QKBF), "one Q / K operand format per instantiation");
+  using SM = Smem<D, BN, QKBF>;
+  constexpr int NST = SM::kNst;                    // key stages
   constexpr int NSUB = kChunk / BN;                // key blocks per stage
   constexpr int PV_N = D + kOnesRows;              // PV accumulator columns
   constexpr int TCOLS = 256;                       // TMEM columns per tile
@@ -88,20 +92,20 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
   // barrier map
   auto BAR_QFULL = [&](int t) { return bar0 + 8u * t; };
   auto BAR_KFULL = [&](int s) { return bar0 + 8u * (2 + s); };
-  auto BAR_VFULL = [&](int s) { return bar0 + 8u * (2 + kStages + s); };
-  auto BAR_KFREE = [&](int s) { return bar0 + 8u * (2 + 2 * kStages + s); };
-  auto BAR_VFREE = [&](int s) { return bar0 + 8u * (2 + 3 * kStages + s); };
-  auto BAR_SFULL = [&](int t) { return bar0 + 8u * (2 + 4 * kStages + t); };
-  auto BAR_SFREE = [&](int t) { return bar0 + 8u * (2 + 4 * kStages + 2 + t); };
+  auto BAR_VFULL = [&](int s) { return bar0 + 8u * (2 + NST + s); };
+  auto BAR_KFREE = [&](int s) { return bar0 + 8u * (2 + 2 * NST + s); };
+  auto BAR_VFREE = [&](int s) { return bar0 + 8u * (2 + 3 * NST + s); };
+  auto BAR_SFULL = [&](int t) { return bar0 + 8u * (2 + 4 * NST + t); };
+  auto BAR_SFREE = [&](int t) { return bar0 + 8u * (2 + 4 * NST + 2 + t); };
   // P ready, one barrier per block parity: a warp can finish block j + 1 (whose S only waits for every thread to have
   // copied S of block j out) before a slower warp has delivered P of block j; with a single barrier that second
   // arrival would be counted into block j's phase. Two blocks ahead is impossible (S of block j + 2 waits for every
   // thread's copy of block j + 1).
-  auto BAR_PRDY = [&](int t, int par) { return bar0 + 8u * (2 + 4 * kStages + 4 + 2 * t + par); };
-  auto BAR_PVFULL = [&](int t) { return bar0 + 8u * (2 + 4 * kStages + 8 + t); };
-  auto BAR_OFREE = [&](int t) { return bar0 + 8u * (2 + 4 * kStages + 10 + t); };
-  auto BAR_SIDEFULL = [&](int s) { return bar0 + 8u * (2 + 4 * kStages + 12 + s); };
-  auto BAR_SIDEFREE = [&](int s) { return bar0 + 8u * (2 + 4 * kStages + 12 + kStages + s); };
+  auto BAR_PRDY = [&](int t, int par) { return bar0 + 8u * (2 + 4 * NST + 4 + 2 * t + par); };
+  auto BAR_PVFULL = [&](int t) { return bar0 + 8u * (2 + 4 * NST + 8 + t); };
+  auto BAR_OFREE = [&](int t) { return bar0 + 8u * (2 + 4 * NST + 10 + t); };
+  auto BAR_SIDEFULL = [&](int s) { return bar0 + 8u * (2 + 4 * NST + 12 + s); };
+  auto BAR_SIDEFREE = [&](int s) { return bar0 + 8u * (2 + 4 * NST + 12 + NST + s); };
   volatile int* misc = (volatile int*)(smem + SM::offMisc);   // [0] tmem base, [1] abort, [2..5] elide flags, [6] early exit
   volatile int* abort_flag = misc + 1;
 
@@ -128,7 +132,7 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
       mbar_init(BAR_PVFULL(t), 1);
       mbar_init(BAR_OFREE(t), kTileM);
     }
-    for (int s = 0; s < kStages; ++s) {
+    for (int s = 0; s < NST; ++s) {
       mbar_init(BAR_KFULL(s), 1);
       mbar_init(BAR_VFULL(s), 1);
       mbar_init(BAR_KFREE(s), 2);
@@ -140,7 +144,7 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   // rows of 1.0 (e4m3 0x38) under every V^T stage
-  for (int i = threadIdx.x; i < kStages * kOnesRows * kChunk / 16; i += kThreads) {
+  for (int i = threadIdx.x; i < NST * kOnesRows * kChunk / 16; i += kThreads) {
     const int s = i / (kOnesRows * kChunk / 16), r = i % (kOnesRows * kChunk / 16);
     *reinterpret_cast<uint4*>(smem + SM::offV + s * SM::kV + D * kChunk + r * 16) =
         make_uint4(0x38383838u, 0x38383838u, 0x38383838u, 0x38383838u);
@@ -239,7 +243,7 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
       float rs = 0.f;
       if (has_av) rs = __uint_as_float(tmem_ld1(tO + D));
       // both vectors were staged by the producer with the stage that holds key block jb
-      const int slot = ((jb / NSUB) % kStages) * NSUB + (jb % NSUB);
+      const int slot = ((jb / NSUB) % NST) * NSUB + (jb % NSUB);
       const float* av = reinterpret_cast<const float*>(smem + SM::offAlpha) + slot * D;
       const float* vs = reinterpret_cast<const float*>(smem + SM::offVs) + slot * D;
 #pragma unroll
@@ -322,12 +326,12 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
       }
       if (side && (it % NSUB) == 0) {        // first key block of a stage: its side vectors must have landed
         const int c = it / NSUB;
-        if (!mbar_wait(BAR_SIDEFULL(c % kStages), (c / kStages) & 1, abort_flag, p.status, 15)) { alive = false; break; }
+        if (!mbar_wait(BAR_SIDEFULL(c % NST), (c / NST) & 1, abort_flag, p.status, 15)) { alive = false; break; }
       }
       const float2 f2 = make_float2(f, f);
       if (corr_smem) {
         const float4* c4 = reinterpret_cast<const float4*>(
-            smem + SM::offCorr + (((it / NSUB) % kStages) * 2 + t) * (kChunk * 4) + (it % NSUB) * (BN * 4));
+            smem + SM::offCorr + (((it / NSUB) % NST) * 2 + t) * (kChunk * 4) + (it % NSUB) * (BN * 4));
 #pragma unroll
         for (int i = 0; i < BN / 4; ++i) {
           const float4 cv = c4[i];               // same address in every lane: one broadcast wavefront
@@ -551,7 +555,7 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         tc_fence_before();
         mbar_arrive(BAR_OFREE(t));
         // the side vectors of a stage are dead once its last key block has been folded
-        if (side && (blk_prev % NSUB) == NSUB - 1) mbar_arrive(BAR_SIDEFREE((blk_prev / NSUB) % kStages));
+        if (side && (blk_prev % NSUB) == NSUB - 1) mbar_arrive(BAR_SIDEFREE((blk_prev / NSUB) % NST));
       }
       a_prev = alpha; c_prev = c_blk; elided_prev = elide; blk_prev = it;
       m_i = m_new;
@@ -647,7 +651,12 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
     if (lane == 0) {
       for (int t = 0; t < 2; ++t) {
         mbar_expect_tx(BAR_QFULL(t), SM::kQ + (QKMX ? 512 : 0));
-        tma_load_3d(sbase + SM::offQ + t * SM::kQ, &tm_q, 0, m0 + t * kTileM, bh, BAR_QFULL(t));
+        if constexpr (QKBF) {                               // BF16: D / 64 panels of 128 rows x 128 bytes
+          for (int pn = 0; pn < D / 64; ++pn)
+            tma_load_3d(sbase + SM::offQ + t * SM::kQ + pn * (kTileM * 128), &tm_q, pn * 64, m0 + t * kTileM, bh, BAR_QFULL(t));
+        } else {
+          tma_load_3d(sbase + SM::offQ + t * SM::kQ, &tm_q, 0, m0 + t * kTileM, bh, BAR_QFULL(t));
+        }
         if (QKMX) {
           // a tile beyond the padded rows has no scale tile: re-read the last one (its codes are zero-filled)
           const int tile128 = min((m0 + t * kTileM) >> 7, (p.m_pad >> 7) - 1);
@@ -655,19 +664,24 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         }
       }
       for (int c = 0; c < nchunk; ++c) {
-        const int st = c % kStages;
-        if (c >= kStages) {
-          const uint32_t par = ((c / kStages) - 1) & 1;
+        const int st = c % NST;
+        if (c >= NST) {
+          const uint32_t par = ((c / NST) - 1) & 1;
           if (!mbar_wait(BAR_KFREE(st), par, abort_flag, p.status, 21)) break;
           if (!mbar_wait(BAR_VFREE(st), par, abort_flag, p.status, 22)) break;
         }
         mbar_expect_tx(BAR_KFULL(st), SM::kK + (QKMX ? 512 : 0));
-        tma_load_3d(sbase + SM::offK + st * SM::kK, &tm_k, 0, c * kChunk, bh, BAR_KFULL(st));
+        if constexpr (QKBF) {
+          for (int pn = 0; pn < D / 64; ++pn)
+            tma_load_3d(sbase + SM::offK + st * SM::kK + pn * (kChunk * 128), &tm_k, pn * 64, c * kChunk, bh, BAR_KFULL(st));
+        } else {
+          tma_load_3d(sbase + SM::offK + st * SM::kK, &tm_k, 0, c * kChunk, bh, BAR_KFULL(st));
+        }
         if (QKMX) bulk_load(sbase + SM::offKS + st * 512, p.k_sf + ((size_t)bh * (p.n_pad >> 7) + c) * 512, 512, BAR_KFULL(st));
         mbar_expect_tx(BAR_VFULL(st), D * kChunk);
         tma_load_3d(sbase + SM::offV + st * SM::kV, &tm_v, c * kChunk, 0, bh, BAR_VFULL(st));
         if (p.side_bytes > 0) {
-          if (c >= kStages && !mbar_wait(BAR_SIDEFREE(st), ((c / kStages) - 1) & 1, abort_flag, p.status, 23)) break;
+          if (c >= NST && !mbar_wait(BAR_SIDEFREE(st), ((c / NST) - 1) & 1, abort_flag, p.status, 23)) break;
           mbar_expect_tx(BAR_SIDEFULL(st), p.side_bytes);
           if (p.corr != nullptr && p.corr_staged) {
             for (int t = 0; t < 2; ++t) {
@@ -705,8 +719,8 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
       bool ok = mbar_wait(BAR_QFULL(t), 0, abort_flag, p.status, 31);
       if (QKMX && ok) tc_cp_32x128b(tSFA, make_desc_sf(sbase + SM::offQS + t * 512));
       auto issue_qk = [&](int j) -> bool {
-        const int c = j / NSUB, sub = j % NSUB, st = c % kStages;
-        if (sub == 0 && !mbar_wait(BAR_KFULL(st), (c / kStages) & 1, abort_flag, p.status, 32)) return false;
+        const int c = j / NSUB, sub = j % NSUB, st = c % NST;
+        if (sub == 0 && !mbar_wait(BAR_KFULL(st), (c / NST) & 1, abort_flag, p.status, 32)) return false;
         tc_fence_after();
         const uint64_t dk = make_desc(sbase + SM::offK + st * SM::kK + sub * BN * D, D);
         if constexpr (QKMX) {
@@ -717,6 +731,16 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
           for (int kk = 0; kk < D / 32; ++kk)
             mma_mxf8_ss(tS, dq + (uint64_t)(kk * 2), dk + (uint64_t)(kk * 2), make_idesc_mx(BN, kk), tSFA,
                         tSFB + sub * (BN / 32), kk > 0 ? 1u : 0u);
+        } else if constexpr (QKBF) {
+          // BF16 operands: K steps of 16 channels, four per 64-channel panel
+          const uint32_t id_qk_bf16 = make_idesc_bf16(BN);
+#pragma unroll
+          for (int kk = 0; kk < D / 16; ++kk) {
+            const uint64_t da = make_desc(sbase + SM::offQ + t * SM::kQ + (kk >> 2) * (kTileM * 128), 128) + (uint64_t)((kk & 3) * 2);
+            const uint64_t db = make_desc(sbase + SM::offK + st * SM::kK + (kk >> 2) * (kChunk * 128) + sub * BN * 128, 128) +
+                                (uint64_t)((kk & 3) * 2);
+            mma_bf16_ss(tS, da, db, id_qk_bf16, kk > 0 ? 1u : 0u);
+          }
         } else {
 #pragma unroll
           for (int kk = 0; kk < D / 32; ++kk)
@@ -727,8 +751,8 @@ attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CU
         return true;
       };
       auto issue_pv = [&](int j) -> bool {
-        const int c = j / NSUB, sub = j % NSUB, st = c % kStages;
-        if (sub == 0 && !mbar_wait(BAR_VFULL(st), (c / kStages) & 1, abort_flag, p.status, 33)) return false;
+        const int c = j / NSUB, sub = j % NSUB, st = c % NST;
+        if (sub == 0 && !mbar_wait(BAR_VFULL(st), (c / NST) & 1, abort_flag, p.status, 33)) return false;
         tc_fence_after();
         const bool elide = BLASST && misc[2 + 2 * t + (j & 1)] != 0;
         if (!elide) {
@@ -820,11 +844,12 @@ static int make_map_bf16(CUtensorMap* map, const void* base, uint64_t inner, uin
   return LBFQ_OK;
 }
 
-template <int D, int BN, bool BLASST, bool QKMX>
+template <int D, int BN, bool BLASST, bool QKMX, bool QKBF = false>
 static int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const Params& p, cudaStream_t st) {
-  using SM = Smem<D, BN>;
+  using SM = Smem<D, BN, QKBF>;
   const int smem_bytes = SM::total + 1024;
-  auto kern = attn_kernel<D, BN, BLASST, QKMX>;
+  static_assert(SM::total + 1024 <= 227 * 1024, "shared memory of one CTA");
+  auto kern = attn_kernel<D, BN, BLASST, QKMX, QKBF>;
   LBFQ_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
   dim3 grid((p.M + kCtaM - 1) / kCtaM, p.B * p.H, 1);
   kern<<<grid, kThreads, smem_bytes, st>>>(mq, mk, mv, p);
@@ -970,10 +995,11 @@ extern "C" int lbfq_attention_fwd(const lbfq_attn_args* a, void* workspace, void
   LBFQ_REQUIRE(a->m_pad >= a->M && a->m_pad % 128 == 0 && a->n_pad >= a->N && a->n_pad % 128 == 0, LBFQ_ERR_ARG,
                "m_pad / n_pad must cover M / N and be multiples of 128");
   LBFQ_REQUIRE(a->q_codes && a->k_codes && a->v_codes && a->out, LBFQ_ERR_ARG, "null operand pointer");
-  LBFQ_REQUIRE(a->qk_kind == LBFQ_QK_FP8_BLOCK || a->qk_kind == LBFQ_QK_MX || a->qk_kind == LBFQ_QK_BF16, LBFQ_ERR_ARG,
+  LBFQ_REQUIRE(a->qk_kind >= LBFQ_QK_FP8_BLOCK && a->qk_kind <= LBFQ_QK_BF16_V_CODES, LBFQ_ERR_ARG,
                "unknown qk_kind %d", a->qk_kind);
   const bool mx = a->qk_kind == LBFQ_QK_MX;
-  const bool bf = a->qk_kind == LBFQ_QK_BF16;
+  const bool bfv = a->qk_kind == LBFQ_QK_BF16_V_CODES;        // BF16 Q / K, e4m3 V codes: the general kernel
+  const bool bf = a->qk_kind == LBFQ_QK_BF16 || bfv;
   if (bf) {
     // nothing to check: the operands carry their scales already
   } else if (mx) {
@@ -1068,6 +1094,22 @@ extern "C" int lbfq_attention_fwd(const lbfq_attn_args* a, void* workspace, void
 
   CUtensorMap mq, mk, mv;
   const uint64_t BH = (uint64_t)a->B * a->H;
+  if (bfv) {
+    // BF16 Q / K with V as e4m3 codes: the general kernel (every V kind, every BLASST fill, the stats tensor)
+    LBFQ_REQUIRE(a->rowmax_counters == nullptr, LBFQ_ERR_UNSUPPORTED, "rowmax_counters are served on FP8-code operands only");
+    if (int rc = make_map_bf16(&mq, a->q_codes, a->D, a->m_pad, BH, 64, kTileM)) return rc;
+    if (int rc = make_map_bf16(&mk, a->k_codes, a->D, a->n_pad, BH, 64, kChunk)) return rc;
+    if (int rc = make_map(&mv, a->v_codes, a->n_pad, a->D, BH, kChunk, a->D)) return rc;
+    g_last_variant = 0;
+    const bool blq = a->use_blasst != 0;
+#define LBFQ_LAUNCH_BF(DD, NN)                                                                      \
+  return blq ? launch<DD, NN, true, false, true>(mq, mk, mv, p, st) : launch<DD, NN, false, false, true>(mq, mk, mv, p, st)
+    if (a->D == 128 && a->block_n == 64) { LBFQ_LAUNCH_BF(128, 64); }
+    if (a->D == 128 && a->block_n == 32) { LBFQ_LAUNCH_BF(128, 32); }
+    if (a->D == 64 && a->block_n == 64) { LBFQ_LAUNCH_BF(64, 64); }
+    LBFQ_LAUNCH_BF(64, 32);
+#undef LBFQ_LAUNCH_BF
+  }
   if (bf) {
     // BF16 operands: only the TMEM-resident kernel multiplies them
     LBFQ_REQUIRE(a->rowmax_counters == nullptr, LBFQ_ERR_UNSUPPORTED, "rowmax_counters are served on FP8-code operands only");

@@ -20,7 +20,7 @@ F32, F16, BF16 = 0, 1, 2
 LAYOUT_NHD, LAYOUT_BHSD, LAYOUT_BHDS = 0, 1, 2
 P_KINDS = {"elementwise": 0, "mx": 1, "dynamic": 2}
 V_CHANNEL, V_BLOCK, V_MX = 0, 1, 2
-QK_FP8_BLOCK, QK_MX, QK_BF16 = 0, 1, 2
+QK_FP8_BLOCK, QK_MX, QK_BF16, QK_BF16_V_CODES = 0, 1, 2, 3
 
 ERR_ARG, ERR_DTYPE, ERR_UNSUPPORTED, ERR_CUDA, ERR_DEVICE = -1, -2, -3, -4, -5
 # debug overrides (LBFQ_FLAG_* of include/lbfq.h)

@@ -410,16 +410,24 @@ def _fake_quant_attention_p_requant_reference_operands(q_work, k_work, v_work, q
     elif cfg.v_quant == "mxfp8":
         v_bf = _quant_dequant_v(v_work, cfg, torch.bfloat16)  # codes x 2^e, exact in BF16
         v_scale = torch.ones((b, h, d), dtype=torch.float32, device=v_work.device)
+    elif cfg.v_quant == "fp8_block":
+        codes, v_block_scale = fp8_block_quant(v_work, block_s=cfg.v_fp8_block_size)
+        v_bf = codes.to(torch.bfloat16)
+        v_scale = torch.ones((b, h, d), dtype=torch.float32, device=v_work.device)
     else:
-        raise NotImplementedError("fp8_block V with the reference's BF16 operands is not built; use the FP8-code path")
-    if cfg.blasst_lambda is not None:
-        raise NotImplementedError("BLASST with the reference's BF16 operands is not built; use the FP8-code path")
+        raise ValueError(f"unsupported v_quant: {cfg.v_quant!r}")
     if cfg.rowmax_mode not in ("online", "qm_k"):
         raise ValueError(f"unsupported rowmax_mode: {cfg.rowmax_mode!r}")
     if cfg.rowmax_mode == "qm_k" and qm is None:
         raise ValueError("rowmax_mode='qm_k' requires smoothing='full' so qm exists")
     to_bh = lambda t: t.permute(0, 2, 1, 3).contiguous()
     rowmax_est = corr = None
+    block_kw = {}
+    if cfg.v_quant == "fp8_block":
+        block_kw.update(v_block_scale_bsh=v_block_scale.float().contiguous(), v_block_size=cfg.v_fp8_block_size)
+    if cfg.blasst_lambda is not None:
+        block_kw.update(blasst_lambda=cfg.blasst_lambda, blasst_fill_mode=cfg.blasst_fill,
+                        blasst_fill_alpha=cfg.blasst_fill_alpha, blasst_uta_bins=cfg.blasst_uta_bins)
     if qm is not None:
         # one product serves the score bias and the row-max estimate; the launcher takes it instead of forming it again
         want_est = cfg.rowmax_mode == "qm_k"
@@ -441,7 +449,8 @@ def _fake_quant_attention_p_requant_reference_operands(q_work, k_work, v_work, q
         k_smooth_bhsd=to_bh(k_work.to(torch.bfloat16)) if qm is not None else None,
         qm_bhgd=qm.float().contiguous() if qm is not None else None,      # (B, G, H, D), as group_mean_q returns it
         q_smooth_block=cfg.q_smooth_block_size if qm is not None else 0,
-        p_quant_mode=p_mode, p_mx_block_n=p_mx_block_n, rowmax_est_bhs=rowmax_est, _out_fp32=out_fp32_exact, _corr=corr)
+        p_quant_mode=p_mode, p_mx_block_n=p_mx_block_n, rowmax_est_bhs=rowmax_est, _out_fp32=out_fp32_exact, _corr=corr,
+        **block_kw)
     o = o.permute(0, 2, 1, 3).contiguous()                    # (B, S, H, D)
     o = o if out_fp32_exact else o.to(out_dtype)
     if q_kmeans is not None:

@@ -74,6 +74,7 @@ def fake_quant_attention_fp8(
     k_scale: Optional[torch.Tensor],   # (B, N/qk_block, H) fp32
     qk_block: int,
     operands_bf16: bool = False,    # q/k/v are BF16 (de-quantised Q/K, BF16 V^T): the reference's own operand convention
+    qk_bf16_v_codes: bool = False,  # q/k are BF16 as above, v_codes_t stays e4m3 codes with its v_kind / v_scale (general kernel)
     q_scale_e8: Optional[torch.Tensor] = None,   # block-scaled (mxfp8) Q/K: UE8M0 scale tiles from mxfp8_qk_quant
     k_scale_e8: Optional[torch.Tensor] = None,
     v_kind: str,                    # "fp8_channel" | "fp8_block" | "mxfp8"
@@ -166,7 +167,8 @@ def fake_quant_attention_fp8(
         a.B, a.H, a.M, a.N, a.D = B, H, M, N, D
         a.m_pad, a.n_pad = m_pad, n_pad
         a.q_codes, a.k_codes, a.v_codes = q_codes.data_ptr(), k_codes.data_ptr(), v_codes_t.data_ptr()
-        a.qk_kind = L.QK_BF16 if operands_bf16 else (L.QK_MX if q_scale_e8 is not None else L.QK_FP8_BLOCK)
+        a.qk_kind = (L.QK_BF16_V_CODES if qk_bf16_v_codes else L.QK_BF16 if operands_bf16
+                     else (L.QK_MX if q_scale_e8 is not None else L.QK_FP8_BLOCK))
         a.q_scale, a.k_scale, a.qk_block = L.ptr(q_scale), L.ptr(k_scale), int(qk_block)
         a.q_scale_e8, a.k_scale_e8 = L.ptr(q_scale_e8), L.ptr(k_scale_e8)
         a.v_kind, a.v_scale, a.v_block = v_kind_code, L.ptr(v_scale), int(v_block)
@@ -263,10 +265,15 @@ def fake_quant_attention_triton(
     """The reference's direct-launch entry (src/low_bit_fake_quant/attention_triton.py:410-671), same signature.
 
     ``q_bhsd`` / ``k_bhsd``: the de-quantised BF16 operands (B, H, S, D); ``v_bhsd_bf16``: V as BF16 (code values or
-    pre-de-quantised) with its per-channel post-scale ``v_scale_bhd`` (FP32 ones when unused). Q.K^T and P.V run as
-    BF16 MMAs on exactly these operands, i.e. in the reference's own numerics. Returns (B, H, S, D) BF16.
-    Not served through this entry (``NotImplementedError``): ``v_block_scale_bsh`` (fp8_block V) and BLASST, which
-    only the FP8-code kernel behind ``fake_quant_attention`` implements.
+    pre-de-quantised) with its per-channel post-scale ``v_scale_bhd`` (FP32 ones when unused). Returns (B, H, S, D)
+    BF16, and the stats tensor (ceil(S / block_m), B * H, 2) with ``return_blasst_stats``.
+
+    Two kernels serve it. Without BLASST and without a per-block V scale, Q.K^T and P.V run as BF16 MMAs on exactly
+    these operands with the accumulator in tensor memory. With ``v_block_scale_bsh`` (fp8_block V), ``blasst_lambda``
+    or ``return_blasst_stats`` the general kernel takes over: Q.K^T is still a BF16 MMA on the given Q / K, V goes back
+    to the e4m3 codes it came from (the cast is checked to be exact; a pre-de-quantised mxfp8 V is re-quantised in
+    blocks of ``block_n`` keys, which is exact too) and P.V is an FP8 MMA with the V scale, the P scale and the
+    V-smoothing term applied in FP32 around it.
     """
     if q_bhsd.ndim != 4 or k_bhsd.shape[:2] != q_bhsd.shape[:2] or v_bhsd_bf16.shape != k_bhsd.shape:
         raise ValueError("q/k/v must be (B, H, S, D) with matching batch, heads and key length")
@@ -275,10 +282,8 @@ def fake_quant_attention_triton(
             raise TypeError("q_bhsd, k_bhsd and v_bhsd_bf16 must be BF16")
     if v_scale_bhd.dtype != torch.float32:
         raise TypeError("v_scale_bhd must be FP32")
-    if v_block_scale_bsh is not None:
-        raise NotImplementedError("v_block_scale_bsh (fp8_block V) is served by fake_quant_attention only")
-    if blasst_lambda is not None or return_blasst_stats:
-        raise NotImplementedError("BLASST is served by fake_quant_attention only")
+    if blasst_lambda is None and blasst_fill_mode not in ("zero", None):
+        raise ValueError("blasst_fill_mode requires blasst_lambda")
     B, H, M, D = q_bhsd.shape
     N = k_bhsd.shape[2]
     if v_scale_bhd.shape != (B, H, D):
@@ -324,6 +329,51 @@ def fake_quant_attention_triton(
         return out
 
     q_p, k_p = pad_rows(q_bhsd, m_pad), pad_rows(k_bhsd, n_pad)
+    if v_block_scale_bsh is not None or blasst_lambda is not None or return_blasst_stats:
+        # ---- the general kernel: V as e4m3 codes again ----
+        if v_block_scale_bsh is not None:
+            if v_block_size <= 0:
+                raise ValueError("v_block_size must be > 0 when v_block_scale_bsh is given")
+            if v_block_size < block_n or v_block_size % block_n != 0:
+                raise ValueError(f"v_block_size ({v_block_size}) must be >= block_n ({block_n}) "
+                                 "and an integer multiple of block_n")
+            if N % v_block_size != 0:
+                raise ValueError(f"S ({N}) must be divisible by v_block_size ({v_block_size})")
+            if tuple(v_block_scale_bsh.shape) != (B, N // v_block_size, H) or v_block_scale_bsh.dtype != torch.float32:
+                raise ValueError(f"v_block_scale_bsh must be FP32 {(B, N // v_block_size, H)}")
+        codes = v_bhsd_bf16.to(torch.float8_e4m3fn)
+        exact = bool((codes.to(torch.bfloat16) == v_bhsd_bf16).all())
+        if v_block_scale_bsh is not None:
+            if not exact:
+                raise ValueError("with v_block_scale_bsh, v_bhsd_bf16 must hold e4m3 code values (FP8 cast to BF16)")
+            v_kind, v_scale, v_blk = "fp8_block", v_block_scale_bsh, v_block_size
+        elif exact:
+            v_kind, v_scale, v_blk = "fp8_channel", v_scale_bhd, 0
+        else:
+            # a pre-de-quantised mxfp8 V (codes x 2^e per channel and key block): re-quantising any sub-block of the
+            # original blocks recovers codes and power-of-two scales exactly
+            from .quant_triton import mxfp8_v_dequant, mxfp8_v_quant
+            if not bool((v_scale_bhd == 1.0).all()) or N % block_n != 0:
+                raise NotImplementedError("this V is neither e4m3 code values nor a de-quantised mxfp8 tensor with unit v_scale")
+            v_nhd = v_bhsd_bf16.permute(0, 2, 1, 3).contiguous()
+            c_nhd, v_scale = mxfp8_v_quant(v_nhd, block_s=block_n)
+            if not bool((mxfp8_v_dequant(c_nhd, v_scale, block_s=block_n, dtype=torch.bfloat16) == v_nhd).all()):
+                raise NotImplementedError("this V is neither e4m3 code values nor a de-quantised mxfp8 tensor")
+            codes = c_nhd.permute(0, 2, 1, 3)
+            v_kind, v_blk = "mxfp8", block_n
+        v_t = torch.zeros((B, H, D, n_pad), dtype=torch.float8_e4m3fn, device=q_bhsd.device)
+        v_t.view(torch.uint8)[..., :N] = codes.contiguous().view(torch.uint8).transpose(2, 3)
+        return fake_quant_attention_fp8(
+            q_p, k_p, v_t, seq_q=M, seq_k=N, q_scale=None, k_scale=None, qk_block=block_n, qk_bf16_v_codes=True,
+            v_kind=v_kind, v_scale=v_scale, v_block=v_blk,
+            sm_scale=float(sm_scale), p_max_offset=int(p_max_offset), block_m=block_m, block_n=block_n,
+            v_alpha=v_alpha, v_smooth_block=v_smooth_block, qm_corr=corr, q_smooth_block=q_smooth_block,
+            p_quant_mode=p_quant_mode, p_mx_block_n=p_mx_block_n,
+            rowmax_est_bhs=rowmax_est_bhs, rowmax_init_bhs=rowmax_init_bhs,
+            blasst_lambda=blasst_lambda, blasst_fill_mode=blasst_fill_mode, blasst_fill_alpha=blasst_fill_alpha,
+            blasst_uta_bins=blasst_uta_bins, return_blasst_stats=return_blasst_stats,
+            out_dtype=torch.float32 if _out_fp32 else torch.bfloat16, out_nhd=False, out_fp32_exact=_out_fp32,
+        )
     v_t = pad_rows(v_bhsd_bf16, n_pad).transpose(2, 3).contiguous()              # (B, H, D, n_pad), keys contiguous
     return fake_quant_attention_fp8(
         q_p, k_p, v_t, seq_q=M, seq_k=N, q_scale=None, k_scale=None, qk_block=block_n, operands_bf16=True,

@@ -75,11 +75,22 @@ def test_direct_launch_signature_and_errors():
     ones = torch.ones(B, H, D, device=DEV)
     out = fake_quant_attention_triton(q, k, v, ones, sm_scale=D ** -0.5, p_max_offset=8)
     assert out.shape == (B, H, S, D) and out.dtype == torch.bfloat16 and torch.isfinite(out.float()).all()
-    with pytest.raises(NotImplementedError, match="fp8_block V"):
+    # a per-block V scale wants V as e4m3 code values (random BF16 values are not)
+    with pytest.raises(ValueError, match="e4m3 code values"):
         fake_quant_attention_triton(q, k, v, ones, sm_scale=1.0, p_max_offset=8,
                                     v_block_scale_bsh=torch.ones(B, S // 64, H, device=DEV), v_block_size=64)
-    with pytest.raises(NotImplementedError, match="BLASST"):
-        fake_quant_attention_triton(q, k, v, ones, sm_scale=1.0, p_max_offset=8, blasst_lambda=0.1)
+    with pytest.raises(ValueError, match="multiple of block_n"):
+        fake_quant_attention_triton(q, k, v, ones, sm_scale=1.0, p_max_offset=8,
+                                    v_block_scale_bsh=torch.ones(B, S // 32, H, device=DEV), v_block_size=32)
+    # BLASST and the stats tensor through the direct-launch signature: V as code values
+    vc = v.to(torch.float8_e4m3fn).to(torch.bfloat16)
+    out, stats = fake_quant_attention_triton(q, k, vc, ones, sm_scale=D ** -0.5, p_max_offset=8, blasst_lambda=0.1,
+                                             blasst_fill_mode="mean_a1.5", return_blasst_stats=True)
+    assert out.shape == (B, H, S, D) and stats.shape == (S // 64, B * H, 2) and float(stats[..., 1].sum()) == B * H * S * (S // 64)
+    with pytest.raises(ValueError, match="blasst_lambda must be in"):
+        fake_quant_attention_triton(q, k, vc, ones, sm_scale=1.0, p_max_offset=8, blasst_lambda=1.5)
+    with pytest.raises(ValueError, match="requires blasst_lambda"):
+        fake_quant_attention_triton(q, k, vc, ones, sm_scale=1.0, p_max_offset=8, blasst_fill_mode="mean")
     with pytest.raises(ValueError, match="v_smooth_block must be > 0"):
         fake_quant_attention_triton(q, k, v, ones, sm_scale=1.0, p_max_offset=8, v_alpha=torch.zeros(B, S // 64, H, D, device=DEV))
     with pytest.raises(ValueError, match="k_smooth_bhsd required"):
