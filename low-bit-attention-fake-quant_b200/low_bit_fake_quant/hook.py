@@ -4,18 +4,25 @@ The reference's Wan2.1 attention hook (bench/wan_attention_hook.py:248-294) pads
 the block sizes the path needs before calling ``fake_quant_attention`` and strips the padded rows afterwards: Q rows
 are padded with zeros (their outputs are dropped), K / V rows replicate the last real token, so that the attention
 weight falling on a padded key flows to the value of the last real token (a perturbation bounded by pad / S).
-This module provides that policy for the drop-in package, and the cross-attention entry the hook has no
-fake-quant form of; both are extensions, kept out of ``__all__``.
+This module provides that policy for the drop-in package, the cross-attention entry the hook has no fake-quant form
+of, the space-time block reorder of the reference's BLASST evaluation, and the hook itself: the dispatcher that
+replaces Wan2.1's attention function, its call log and its environment-driven dump / compare switches. All of it sits
+outside the reference's package (in its ``bench/``), so it is kept out of ``__all__`` here.
 """
 from __future__ import annotations
 
 import math
+import os
+import threading
+from dataclasses import replace
 from functools import reduce
-from typing import Optional
+from pathlib import Path
+from typing import Callable, Optional
 
 import torch
+import torch.nn.functional as F
 
-from .attention import fake_quant_attention
+from .attention import fake_quant_attention, prepare_for_attention
 from .config import QuantConfig
 
 
@@ -107,3 +114,139 @@ def fake_quant_attention_reordered(q: torch.Tensor, k: torch.Tensor, v: torch.Te
     out = fake_quant_attention(apply_kv_permutation(q, fwd), apply_kv_permutation(k, fwd), apply_kv_permutation(v, fwd),
                                cfg, sm_scale=sm_scale)
     return apply_kv_permutation(out, inverse.unsqueeze(0).expand(b * h, s).contiguous())
+
+
+# --- the Wan2.1 attention hook itself (bench/wan_attention_hook.py:36-348 of the reference) ------------------------
+#
+# The reference patches ``wan.modules.attention.{attention, flash_attention}`` with a dispatcher that sends video
+# self-attention (Lq == Lk > 1024) through ``fake_quant_attention`` -- padded by the policy above -- and everything
+# else (cross-attention; self-attention while no configuration is set) through plain SDPA, keeps a log of every call
+# and, driven by environment variables, dumps the Q / K / V of chosen calls and compares each result with SDPA or
+# with the same configuration on the online row max. The same dispatcher, state, record keys and switches:
+#   WAN_ATTENTION_DUMP_DIR / WAN_ATTENTION_DUMP_CALLS / WAN_ATTENTION_DUMP_LIMIT   (:58-90)
+#   WAN_ATTENTION_COMPARE_SDPA=1                                                    (:93-131)
+#   WAN_ATTENTION_COMPARE_ONLINE_ROWMAX=1                                           (:134-182)
+
+_state_lock = threading.Lock()
+_current_cfg: Optional[QuantConfig] = None
+_call_log: list = []
+NO_QUANT: Optional[QuantConfig] = None          # "no quantisation: plain SDPA"
+# what runs a fake-quant call; tests on machines without a GPU substitute a stand-in of the same signature
+_attention_fn: Callable = fake_quant_attention
+_prepare_fn: Callable = prepare_for_attention
+
+
+def set_quant_cfg(cfg: Optional[QuantConfig]) -> None:
+    """Set the active QuantConfig (``None``: plain SDPA) and clear the call log (wan_attention_hook.py:43-48)."""
+    global _current_cfg
+    with _state_lock:
+        _current_cfg = cfg
+        _call_log.clear()
+
+
+def get_call_log() -> list:
+    with _state_lock:
+        return list(_call_log)
+
+
+def _log_call(record: dict) -> None:
+    with _state_lock:
+        _call_log.append(record)
+
+
+def _maybe_dump_qkv(q, k, v, record: dict) -> None:
+    dump_dir = os.environ.get("WAN_ATTENTION_DUMP_DIR")
+    if not dump_dir:
+        return
+    with _state_lock:
+        log_idx = len(_call_log)
+        dump_idx = sum(1 for item in _call_log if item.get("dumped_qkv"))
+    dump_calls = os.environ.get("WAN_ATTENTION_DUMP_CALLS")
+    if dump_calls:
+        if log_idx not in {int(item) for item in dump_calls.split(",") if item.strip()}:
+            return
+    elif dump_idx >= int(os.environ.get("WAN_ATTENTION_DUMP_LIMIT", "1")):
+        return
+    if dump_idx >= int(os.environ.get("WAN_ATTENTION_DUMP_LIMIT", "1000000")):
+        return
+    out_dir = Path(dump_dir)
+    out_dir.mkdir(parents=True, exist_ok=True)
+    path = out_dir / f"call_{log_idx:03d}.pt"
+    torch.save({"query": q.detach().cpu(), "key": k.detach().cpu(), "value": v.detach().cpu(), "record": record}, path)
+    record["dumped_qkv"] = str(path)
+
+
+def _difference(out: torch.Tensor, ref: torch.Tensor) -> dict:
+    a, b = out.float().flatten(), ref.float().flatten()
+    diff = a - b
+    a_norm, b_norm = torch.linalg.vector_norm(a), torch.linalg.vector_norm(b)
+    return {"mse": float(diff.pow(2).mean().item()),
+            "cosine": float((torch.dot(a, b) / torch.clamp(a_norm * b_norm, min=1e-12)).item()),
+            "max_abs": float(diff.abs().max().item()), "out_norm": float(a_norm.item()), "ref_norm": float(b_norm.item()),
+            "out_has_nan": bool(torch.isnan(out).any().item()), "out_has_inf": bool(torch.isinf(out).any().item())}
+
+
+def _sdpa(q, k, v, *, dropout_p: float, causal: bool, scale: float) -> torch.Tensor:
+    out = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), dropout_p=dropout_p,
+                                         is_causal=causal, scale=scale)
+    return out.transpose(1, 2).contiguous()
+
+
+def wan_attention(q, k, v, q_lens=None, k_lens=None, dropout_p: float = 0.0, softmax_scale: Optional[float] = None,
+                  q_scale: Optional[float] = None, causal: bool = False, window_size=(-1, -1), deterministic: bool = False,
+                  dtype: torch.dtype = torch.bfloat16, fa_version=None, version=None) -> torch.Tensor:
+    """Replacement for ``wan.modules.attention.attention`` / ``flash_attention`` (wan_attention_hook.py:203-327).
+
+    ``q, k, v``: (B, L, N, C), the NHD layout. Video self-attention (``Lq == Lk > 1024``) with a configuration set goes
+    through the fake-quant path, padded to the block sizes and stripped again; everything else through plain SDPA."""
+    b, lq, nq, c = q.shape
+    lk = k.shape[1]
+    cfg = _current_cfg
+    is_self = lq == lk and lq > 1024
+    half = (torch.float16, torch.bfloat16)
+    q, k, v = (t if t.dtype in half else t.to(dtype) for t in (q, k, v))
+    if q_scale is not None:
+        q = q * q_scale
+    if softmax_scale is None:
+        softmax_scale = 1.0 / math.sqrt(c)
+    if is_self and cfg is not None:
+        q_p, k_p, v_p, pad = pad_qkv(q, k, v, cfg)
+        record = {"kind": "self-fq", "Lq": lq, "Lk": lk, "D": c, "H": nq, "pad": pad}
+        _maybe_dump_qkv(q, k, v, record)
+        compare_online = os.environ.get("WAN_ATTENTION_COMPARE_ONLINE_ROWMAX") == "1" and cfg.rowmax_mode == "qm_k"
+        cache = _prepare_fn(q_p, k_p, v_p, cfg) if compare_online else None
+        out = _attention_fn(q_p, k_p, v_p, cfg, sm_scale=softmax_scale, preprocess_cache=cache)[:, :lq]
+        if os.environ.get("WAN_ATTENTION_COMPARE_SDPA") == "1":
+            record["compare_sdpa"] = _difference(out, _sdpa(q, k, v, dropout_p=dropout_p, causal=causal, scale=softmax_scale))
+        if compare_online:
+            ref = _attention_fn(q_p, k_p, v_p, replace(cfg, rowmax_mode="online"), sm_scale=softmax_scale,
+                                preprocess_cache=cache)[:, :lq]
+            rec = _difference(out, ref)
+            rec.update(ref_has_nan=bool(torch.isnan(ref).any().item()), ref_has_inf=bool(torch.isinf(ref).any().item()))
+            record["compare_online_rowmax"] = rec
+        _log_call(record)
+        return out.to(q.dtype)
+    out = _sdpa(q, k, v, dropout_p=dropout_p, causal=causal, scale=softmax_scale)
+    _log_call({"kind": "self-sdpa" if is_self else "cross-sdpa", "Lq": lq, "Lk": lk, "D": c, "H": nq})
+    return out.to(q.dtype)
+
+
+_installed = False
+
+
+def install_hook(attention_module=None, model_module=None) -> None:
+    """Patch Wan2.1's attention entry points with :func:`wan_attention` (wan_attention_hook.py:336-348).
+
+    Without arguments the modules ``wan.modules.attention`` and ``wan.modules.model`` are imported (the Wan2.1 code
+    base has to be installed); a caller may hand them in instead."""
+    global _installed
+    if _installed and attention_module is None:
+        return
+    if attention_module is None:
+        import wan.modules.attention as attention_module      # noqa: F811
+        import wan.modules.model as model_module               # noqa: F811
+    attention_module.attention = wan_attention
+    attention_module.flash_attention = wan_attention
+    if model_module is not None:
+        model_module.flash_attention = wan_attention
+    _installed = True

@@ -188,3 +188,57 @@ def test_space_time_block_order():
     assert space_time_block_order(2, 3, 3, ts=1, hs=2, ws=2, tail=2).tolist() == want
     with pytest.raises(ValueError):
         space_time_block_order(0, 1, 1, ts=1, hs=1, ws=1)
+
+
+def test_wan_hook_routing_log_dump_and_compare(tmp_path, monkeypatch):
+    """bench/wan_attention_hook.py of the reference: routing by shape, call log, dump and compare switches. The
+    fake-quant call itself needs a GPU; a CPU stand-in of the same signature takes its place here."""
+    import types
+    from low_bit_fake_quant import hook
+    from low_bit_fake_quant.config import QuantConfig
+    from oracle import api as OA
+
+    calls = []
+
+    def stand_in(q, k, v, cfg, *, sm_scale=None, preprocess_cache=None):
+        calls.append((tuple(q.shape), cfg.rowmax_mode, preprocess_cache))
+        return OA.reference_attention(q, k, v, sm_scale=sm_scale)
+
+    monkeypatch.setattr(hook, "_attention_fn", stand_in)
+    monkeypatch.setattr(hook, "_prepare_fn", lambda q, k, v, cfg: "cache")
+    fake_wan = types.SimpleNamespace(attention=None, flash_attention=None)
+    fake_model = types.SimpleNamespace(flash_attention=None)
+    hook.install_hook(fake_wan, fake_model)
+    assert fake_wan.attention is hook.wan_attention and fake_model.flash_attention is hook.wan_attention
+
+    g = torch.Generator().manual_seed(0)
+    q = torch.randn(1, 1100, 2, 64, generator=g).bfloat16()
+    text = torch.randn(1, 512, 2, 64, generator=g).bfloat16()
+    cfg = QuantConfig(fp8_block_size=64, smoothing="full", q_smooth_block_size=256, q_kmeans_k=None, rowmax_mode="qm_k")
+    # no configuration: everything is plain SDPA
+    hook.set_quant_cfg(hook.NO_QUANT)
+    ref = fake_wan.attention(q, q, q)
+    fake_wan.attention(q, text, text)
+    assert [r["kind"] for r in hook.get_call_log()] == ["self-sdpa", "cross-sdpa"] and not calls
+    # with a configuration: self-attention is padded to the block sizes (lcm 256 -> 1280 rows), stripped and logged
+    monkeypatch.setenv("WAN_ATTENTION_DUMP_DIR", str(tmp_path))
+    monkeypatch.setenv("WAN_ATTENTION_COMPARE_SDPA", "1")
+    monkeypatch.setenv("WAN_ATTENTION_COMPARE_ONLINE_ROWMAX", "1")
+    hook.set_quant_cfg(cfg)
+    assert hook.get_call_log() == []
+    out = fake_wan.flash_attention(q.float(), q.float(), q.float(), softmax_scale=None, dtype=torch.bfloat16)
+    fake_wan.attention(q, text, text)
+    assert out.shape == q.shape and out.dtype == torch.bfloat16
+    log = hook.get_call_log()
+    assert [r["kind"] for r in log] == ["self-fq", "cross-sdpa"]
+    assert log[0]["pad"] == 180 and log[0]["Lq"] == 1100 and log[0]["H"] == 2 and log[0]["D"] == 64
+    assert calls[0] == ((1, 1280, 2, 64), "qm_k", "cache") and calls[1] == ((1, 1280, 2, 64), "online", "cache")
+    assert set(log[0]["compare_sdpa"]) == {"mse", "cosine", "max_abs", "out_norm", "ref_norm", "out_has_nan", "out_has_inf"}
+    assert log[0]["compare_online_rowmax"]["cosine"] > 0.999 and "ref_has_nan" in log[0]["compare_online_rowmax"]
+    dumped = torch.load(log[0]["dumped_qkv"], weights_only=False)
+    assert dumped["query"].shape == q.shape and dumped["record"]["kind"] == "self-fq"
+    # the padded keys replicate the last token, so the stand-in's result is close to, not equal to, plain SDPA
+    assert torch.nn.functional.cosine_similarity(out.float().flatten()[None], ref.float().flatten()[None]).item() > 0.99
+    # the dump limit defaults to one call
+    fake_wan.attention(q, q, q)
+    assert "dumped_qkv" not in hook.get_call_log()[-1]
