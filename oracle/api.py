@@ -459,6 +459,9 @@ def parity_report(got: torch.Tensor, want: torch.Tensor, q: torch.Tensor, k: tor
     return m
 
 
-def parity_ok(rep: dict, *, cos_min: float = 0.99999, max_flip_rows: float = 0.03) -> bool:
+def parity_ok(rep: dict, *, cos_min: float = 0.99999, max_flip_rows: float = 0.01) -> bool:
+    """``max_flip_rows``: at most 1 % of the rows may exceed the tolerance through a single-code flip of a dominant P
+    (the largest fraction measured is 3.9e-3, one head of the dynamic-P stack at S = 32768 on the benchmark's inputs,
+    tests/test_gpu_baseline_shapes.py; the small cases of the other tests stay below 2e-3)."""
     return (rep["cosine"] >= cos_min and rep["rows_over_flip_bound"] == 0
             and rep["flip_row_fraction"] <= max_flip_rows)
