@@ -116,20 +116,27 @@ def pad_like_hook(q, k, v, cfg):
     return qp.contiguous(), kp.contiguous(), vp.contiguous(), pad
 
 
-def blasst_skip_ratios(qp, kp, vp, cfg):
+def blasst_skip_ratios(qp, kp, vp, cfg, tile_predicate=False):
     """Row-skip and whole-program skip ratios from the kernel's stats tensor, computed the way the reference's BLASST
-    evaluation does (bench/eval_blasst_quant.py:216-227). One extra call, outside the timed region."""
+    evaluation does (bench/eval_blasst_quant.py:216-227), and the share of (128-row tile, key block) pairs the kernel
+    did no work for (its own counter; zero fill only). One extra call, outside the timed region."""
     import low_bit_fake_quant as fq
     from low_bit_fake_quant.attention import _fake_quant_attention_p_requant
     k_work = fq.smooth_k(kp)[0] if cfg.smoothing != "off" else kp
+    elided = torch.zeros(1, dtype=torch.int64, device=qp.device)
     _, stats = _fake_quant_attention_p_requant(qp, k_work, vp, None, None, None, cfg, 1.0 / math.sqrt(qp.shape[-1]),
-                                               qp.dtype, return_stats=True)
+                                               qp.dtype, return_stats=True, blasst_tile_predicate=tile_predicate,
+                                               blasst_elided=elided)
+    b, s, h, _ = qp.shape
+    pairs = b * h * ((s + 127) // 128) * ((s + cfg.p_requant_block_n - 1) // cfg.p_requant_block_n)
     skipped, total = float(stats[..., 0].sum().item()), float(stats[..., 1].sum().item())
     tiles = stats[..., 1].gt(0)
     tile_skipped = float((stats[..., 0] == stats[..., 1]).logical_and(tiles).sum().item())
     return {"row_skip_ratio": skipped / total if total > 0 else 0.0,
             "tile_skip_ratio": tile_skipped / float(tiles.sum().item()) if tiles.any() else 0.0,
-            "skipped_row_blocks": skipped, "total_row_blocks": total}
+            "skipped_row_blocks": skipped, "total_row_blocks": total,
+            "elided_tile_blocks": int(elided.item()), "elided_tile_block_ratio": float(elided.item()) / pairs,
+            "tile_predicate": bool(tile_predicate)}
 
 
 def load_traffic_table():
@@ -295,10 +302,15 @@ def main():
     ap.add_argument("--no-strong", action="store_true", help="N > 1: skip the one-problem-over-N-ranks partition")
     ap.add_argument("--e2e-heads-per-chunk", type=int, default=None,
                     help="heads per pipelined chunk of the host-buffer entry (default: the entry's own choice)")
+    ap.add_argument("--e2e-chunks", default=None,
+                    help="the host-buffer entry's chunk sizes in heads, in order (e.g. 4,8,12,12,4); overrides the entry's own schedule")
     ap.add_argument("--reference-operands", action="store_true",
                     help="run path B on the reference's own BF16 operands (BF16 MMAs) instead of the FP8 codes; not the headline")
     ap.add_argument("--blasst-lambda", type=float, default=None, help="override the BLASST threshold of a BLASST workload")
     ap.add_argument("--blasst-fill", default=None, help="override the BLASST fill of a BLASST workload (zero, mean_a1.5, uta16_a1.5 ...)")
+    ap.add_argument("--blasst-tile-predicate", action="store_true",
+                    help="BLASST drops a key block only when all rows of a 128-row tile agree (the predicate of the "
+                         "reference's simulator) instead of row by row; zero fill")
     ap.add_argument("--brick", default=None,
                     help="ts,hs,ws: take the video workload's tokens brick by brick over its (21, 30, 52) grid (the reference's "
                          "space-time block reorder); the permutation of Q / K / V and of the result is inside the timed step")
@@ -368,11 +380,13 @@ def main():
 
     def step(qq, kk, vv, c=cfg):
         if brick_order is not None:
-            return fake_quant_attention_reordered(qq, kk, vv, c, brick_order)[:, :seq]
+            return fake_quant_attention_reordered(qq, kk, vv, c, brick_order,
+                                                  _blasst_tile_predicate=args.blasst_tile_predicate)[:, :seq]
         if seq_k is not None:
             from low_bit_fake_quant.hook import fake_quant_cross_attention
             return fake_quant_cross_attention(qq, kk, vv, c)[:, :seq]
-        o = fq.fake_quant_attention(qq, kk, vv, c, _reference_operands=args.reference_operands)
+        o = fq.fake_quant_attention(qq, kk, vv, c, _reference_operands=args.reference_operands,
+                                    _blasst_tile_predicate=args.blasst_tile_predicate and c.blasst_lambda is not None)
         return o[:, :seq]
 
     def barrier():
@@ -461,8 +475,10 @@ def main():
         hout = torch.empty((batch, seq, heads, D_HEAD), dtype=qp.dtype).pin_memory()
 
         def e2e_step():
-            fq.fake_quant_attention_host(hq, hk, hv, cfg, out=hout, device=dev, heads_per_chunk=args.e2e_heads_per_chunk)
+            fq.fake_quant_attention_host(hq, hk, hv, cfg, out=hout, device=dev, heads_per_chunk=args.e2e_heads_per_chunk,
+                                         chunk_heads=e2e_chunks)
 
+        e2e_chunks = [int(x) for x in args.e2e_chunks.split(",")] if args.e2e_chunks else None
         n_e2e = max(3, args.steps)
         ms_e2e, _, _ = timed(e2e_step, n_e2e, 2)
 
@@ -510,7 +526,7 @@ def main():
         blasst = None
         if cfg.blasst_lambda is not None and cfg.smoothing != "full" and cfg.q_kmeans_k is None and cfg.v_kmeans_k is None:
             sq, sk_, sv = (qp, kp, vp) if brick_order is None else (x[:, brick_order].contiguous() for x in (qp, kp, vp))
-            blasst = dict(blasst_skip_ratios(sq, sk_, sv, cfg), blasst_lambda=cfg.blasst_lambda, blasst_fill=cfg.blasst_fill)
+            blasst = dict(blasst_skip_ratios(sq, sk_, sv, cfg, args.blasst_tile_predicate), blasst_lambda=cfg.blasst_lambda, blasst_fill=cfg.blasst_fill)
             if args.brick is not None:
                 blasst["brick"] = args.brick
         p_note = {"dynamic": "P re-scaled per (row, block) and handed to a BF16 P.V as the reference rounds it",

@@ -52,7 +52,8 @@ const char* lbfq_last_error(void);
  * 2: lbfq_attn_args gained `rowmax_counters` (appended); lbfq_fp8_block_quant_centered added; lbfq_smooth_k takes
  *    out = NULL.
  * 3: lbfq_kmeans_labels and lbfq_qm_corr take a `status` word (bounded waits of their tensor-core kernels report
- *    there); lbfq_get_flags / lbfq_set_flags replace per-call reads of the LBFQ_* environment variables. */
+ *    there); lbfq_get_flags / lbfq_set_flags replace per-call reads of the LBFQ_* environment variables.
+ * 4: lbfq_attn_args gained `blasst_tile_predicate` and `blasst_elided` behind `blasst_stats`. */
 int lbfq_abi_version(void);
 
 /* Debug overrides. They are read from the environment (LBFQ_ATTN_GENERIC=1, LBFQ_KMEANS_FFMA=1,
@@ -311,6 +312,15 @@ typedef struct lbfq_attn_args {
   float fill_alpha;
   int uta_bins;
   float* blasst_stats;        /* (ceil(M/block_m), B*H, 2) fp32, zero-initialised by the caller, or NULL */
+  /* 0: every row decides for itself (the reference kernel, attention_triton.py:165-175). 1: a key block is dropped
+   * only when EVERY row of the 128-row tile finds it under the threshold, and then no row of the tile sees it (the
+   * tile-level predicate of the reference's simulator, blasst_skip.py:573-585); zero fill only, online row max
+   * without rowmax_init (so the first key block of a tile is always kept and the simulator's empty-tile rescue,
+   * blasst_skip.py:586-595, has nothing to do). */
+  int blasst_tile_predicate;
+  /* Optional device counter, zero-initialised by the caller, or NULL: (128-row tile, key block) pairs whose
+   * exponentials, P and P.V were not computed because every row of the tile skipped the block with zero fill. */
+  unsigned long long* blasst_elided;
   /* output */
   void* out;                  /* rows written through out_row_index when given */
   int out_dtype;              /* LBFQ_BF16 / LBFQ_F16 / LBFQ_F32 (kernel rounds to BF16 first unless F32 debug) */

@@ -18,7 +18,7 @@ void set_error(const char* fmt, ...) {
 }  // namespace lbfq
 
 extern "C" const char* lbfq_last_error(void) { return lbfq::g_err; }
-extern "C" int lbfq_abi_version(void) { return 3; }
+extern "C" int lbfq_abi_version(void) { return 4; }
 
 namespace lbfq {
 int sm_count() {

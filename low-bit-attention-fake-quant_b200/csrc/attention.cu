@@ -1046,6 +1046,12 @@ extern "C" int lbfq_attention_fwd(const lbfq_attn_args* a, void* workspace, void
       LBFQ_REQUIRE(a->uta_bins <= 16, LBFQ_ERR_UNSUPPORTED, "at most 16 UTA bins are supported; got %d", a->uta_bins);
     }
   }
+  if (a->blasst_tile_predicate) {
+    LBFQ_REQUIRE(a->use_blasst, LBFQ_ERR_ARG, "blasst_tile_predicate requires use_blasst");
+    LBFQ_REQUIRE(a->fill_kind == LBFQ_FILL_ZERO, LBFQ_ERR_ARG, "blasst_tile_predicate drops whole tiles: zero fill only");
+    LBFQ_REQUIRE(a->rowmax_init == nullptr, LBFQ_ERR_UNSUPPORTED, "blasst_tile_predicate is built for the online row max without rowmax_init");
+    LBFQ_REQUIRE(a->qk_kind == LBFQ_QK_FP8_BLOCK, LBFQ_ERR_UNSUPPORTED, "blasst_tile_predicate is served on FP8-block Q / K codes");
+  }
   cudaStream_t st = (cudaStream_t)stream;
 
   Params p{};
@@ -1069,6 +1075,14 @@ extern "C" int lbfq_attention_fwd(const lbfq_attn_args* a, void* workspace, void
   p.lambda = a->use_blasst ? a->blasst_lambda : 0.f;
   p.fill_kind = a->use_blasst ? a->fill_kind : 0; p.fill_alpha = a->fill_alpha; p.uta_bins = a->uta_bins > 0 ? a->uta_bins : 1;
   p.stats = a->use_blasst ? a->blasst_stats : nullptr;
+  // zero fill, on request (the tile predicate, or the counter of elided pairs): the rows of a tile vote on every key
+  // block, and a block they all skip is not computed at all. Not the default: the vote costs more than the elided
+  // work returns unless a large share of the (tile, block) pairs is elided.
+  // (with rowmax_init a tile could skip its first block, whose P.V initialises the accumulator: no vote then)
+  p.tile_vote = (a->use_blasst && a->fill_kind == LBFQ_FILL_ZERO && a->rowmax_init == nullptr &&
+                 (a->blasst_tile_predicate || a->blasst_elided != nullptr)) ? 1 : 0;
+  p.tile_pred = (a->use_blasst && a->blasst_tile_predicate) ? 1 : 0;
+  p.elided = a->use_blasst ? a->blasst_elided : nullptr;
   p.counters = reinterpret_cast<unsigned long long*>(a->rowmax_counters);
   p.out = a->out; p.out_dtype = a->out_dtype; p.out_layout = a->out_layout; p.out_exact = a->out_fp32_exact;
   p.out_row_index = a->out_row_index; p.status = a->status;
@@ -1154,6 +1168,9 @@ extern "C" int lbfq_attention_fwd(const lbfq_attn_args* a, void* workspace, void
     g_last_variant = 1;
     return launch_fast(mq, mk, mvb, ma, p, a->block_n, 2, st);
   }
+  LBFQ_REQUIRE(!p.tile_pred, LBFQ_ERR_UNSUPPORTED,
+               "blasst_tile_predicate is served by the kernel with the accumulator in tensor memory only (per-channel or "
+               "mxfp8 V, no score bias, no V-smoothing term)");
 #define LBFQ_LAUNCH(DD, NN, MX)                                                                    \
   return bl ? launch<DD, NN, true, MX>(mq, mk, mv, p, st) : launch<DD, NN, false, MX>(mq, mk, mv, p, st)
   if (mx) {

@@ -43,8 +43,12 @@ namespace {
 constexpr int kFastSoftmaxWarps = 16;
 constexpr int kFastThreads = (kFastSoftmaxWarps + 4) * 32;
 constexpr int kFastRegsLaunch = (65536 / kFastThreads) / 8 * 8;   // what __launch_bounds__(kFastThreads, 1) yields
-constexpr int kFastRegsSoftmax = 104;
-constexpr int kFastRegsService = 40;
+#ifndef LBFQ_FAST_REGS_SOFTMAX
+#define LBFQ_FAST_REGS_SOFTMAX 104
+#define LBFQ_FAST_REGS_SERVICE 40
+#endif
+constexpr int kFastRegsSoftmax = LBFQ_FAST_REGS_SOFTMAX;
+constexpr int kFastRegsService = LBFQ_FAST_REGS_SERVICE;
 // `setmaxnreg.inc` blocks until the CTA's register pool can satisfy it: the requests must fit in the pool
 static_assert(kFastSoftmaxWarps * 32 * kFastRegsSoftmax + 4 * 32 * kFastRegsService <= kFastThreads * kFastRegsLaunch,
               "setmaxnreg requests exceed the CTA's register pool");
@@ -55,6 +59,9 @@ static_assert(kFastRegsSoftmax % 8 == 0 && kFastRegsService % 8 == 0, "setmaxnre
 //         over a BF16 copy of V^T (3 key stages: a V stage is twice as large).
 // QB = 1: Q and K are BF16 tensors (the reference's de-quantised operands) and Q.K^T a BF16 MMA; two key stages.
 // BL = 1: BLASST; the row-pair exchange carries three values per block (maximum, sum of scores, largest fill).
+// TV = 1: BLASST with zero fill where the 256 threads of a 128-row tile vote on every key block: a block that all
+//         rows skip costs no exponentials, no P and no P.V. With `tile_pred` the vote is also the only way to skip
+//         (the tile-level predicate of the reference's simulator, blasst_skip.py:573-585).
 // Key stages of the BF16-P instantiations. A build with fewer stages (-DLBFQ_FAST_PK_STAGES=2) leaves the shared
 // memory that instruction-level profiling needs; it is not a shipped configuration.
 #ifndef LBFQ_FAST_PK_STAGES
@@ -70,7 +77,7 @@ struct FastSmem {
   static constexpr int offK = offQ + 2 * kQ;
   static constexpr int offV = offK + kStages * kK;
   static constexpr int offBar = offV + kStages * kV;
-  static constexpr int kNumBar = 2 + 4 * kStages + 4 + 4 + 2 + 2 + 2 * kStages;
+  static constexpr int kNumBar = 2 + 4 * kStages + 4 + 4 + 2 + 2 + 2 * kStages + 4;
   static constexpr int offMisc = offBar + kNumBar * 8;
   static constexpr int offL = offMisc + 64;                    // row sums of the two column halves [tile][half][row]
   // score-bias rows (`corr`) of each tile's Q group, staged per 128-key stage by the producer
@@ -84,13 +91,14 @@ struct FastSmem {
   static constexpr int total = offAext + (PK ? kStages * 2 * kAext : 0);
 };
 
-template <int D, int BN, bool CORR, int PK, bool VALPHA, int QB, bool BL = false>
+template <int D, int BN, bool CORR, int PK, bool VALPHA, int QB, bool BL = false, bool TV = false>
 __global__ void __launch_bounds__(kFastThreads, 1)
 attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                  const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_a, const Params p) {
   static_assert(!VALPHA || PK == 1, "the V-smoothing term rides on the BF16 P.V");
   static_assert(!QB || PK == 1, "BF16 Q / K come with the BF16 P.V");
   static_assert(!BL || (!CORR && !VALPHA && QB == 0), "BLASST is built without score bias, V-smoothing term, BF16 Q / K");
+  static_assert(!TV || BL, "the tile vote belongs to BLASST");
   // scores kept in the reference's own units (natural-log domain) instead of the log2 domain
   constexpr bool NAT = CORR || BL;
   using SM = FastSmem<D, PK, QB, BL ? 1 : 0>;
@@ -120,7 +128,12 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   auto BAR_ODONE = [&](int t) { return bar0 + 8u * (2 + 4 * kFastStages + 10 + t); };   // P.V of the last block done
   auto BAR_SIDEFULL = [&](int s) { return bar0 + 8u * (2 + 4 * kFastStages + 12 + s); };
   auto BAR_SIDEFREE = [&](int s) { return bar0 + 8u * (2 + 4 * kFastStages + 12 + kFastStages + s); };
+  // TV: the eight softmax warps of a tile have published their votes on a key block (one barrier per S buffer)
+  auto BAR_VOTE = [&](int t, int buf) { return bar0 + 8u * (2 + 4 * kFastStages + 12 + 2 * kFastStages + 2 * t + buf); };
   volatile int* misc = (volatile int*)(smem + SM::offMisc);   // [0] tmem base, [1] abort, [6] early exit
+  // TV: one byte per softmax warp, [block parity][tile][warp of the tile], 1 = every row of the warp skips the block
+  uint8_t* const votes = smem + SM::offMisc + 32;
+  constexpr unsigned long long kAllVotes = 0x0101010101010101ull;
   volatile int* abort_flag = misc + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -148,6 +161,8 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       mbar_init(BAR_PRDY(t, 1), PK == 0 ? 2 * kTileM : kFastSoftmaxWarps / 2);
       mbar_init(BAR_PENULT(t), 1);
       mbar_init(BAR_ODONE(t), 1);
+      mbar_init(BAR_VOTE(t, 0), kFastSoftmaxWarps / 2);
+      mbar_init(BAR_VOTE(t, 1), kFastSoftmaxWarps / 2);
     }
     for (int s = 0; s < kFastStages; ++s) {
       mbar_init(BAR_KFULL(s), 1);
@@ -320,8 +335,101 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           x_mine[BUF][SM::kXch] = row_sum;
         }
       }
+      // BLASST per-bin fill: one value per bin of BN / bins keys (a bin never straddles the two halves of the block).
+      // A row skips exactly when both halves of its columns lie under the threshold, and a skipping row keeps its
+      // running max: a thread whose own half qualifies computes its bins' fills now, against the old max, so that the
+      // largest of them travels with the half's maximum through the one barrier of the block (wasted where only one
+      // half qualifies). Only the scaled P modes need that maximum; with e4m3 P the bins are computed once the row is
+      // known to skip.
+      constexpr int kMinBin = BN / 16;                             // at most 16 bins per block are served
+      [[maybe_unused]] float binval[HB / kMinBin];
+      [[maybe_unused]] float fill_max_own = 0.f;
+      [[maybe_unused]] const bool uta = BL && p.fill_kind == LBFQ_FILL_UTA;
+      auto compute_bins = [&]() {
+            const int nvalid = more ? BN : tail_valid;
+            auto bins = [&](auto bs_c) {
+              constexpr int BS = decltype(bs_c)::value;
+              if constexpr (BS <= HB && BS >= kMinBin) {
+                constexpr float kInvBs = 1.0f / BS;                 // a power of two: multiplying by it divides exactly
+#pragma unroll
+                for (int b0 = 0; b0 < HB; b0 += BS) {
+                  float bsum = 0.f, bmx = -INFINITY, bcnt = 0.f;
+#pragma unroll
+                  for (int i = b0; i < b0 + BS; ++i) {
+                    const float x = __uint_as_float(mine[i]);
+                    if (ragged) {
+                      const bool ok = half * HB + i < nvalid;
+                      bsum += ok ? x : 0.f;
+                      bcnt += ok ? 1.f : 0.f;
+                    } else {
+                      bsum += x;
+                    }
+                    bmx = fmaxf(bmx, x);                            // masked scores are -inf already
+                  }
+                  float val;
+                  if (ragged) {
+                    const float safe_c = fmaxf(bcnt, 1.f);
+                    const float bound = safe_c * ex2(fmaf(bmx - m2, kLog2e, p_off));
+                    const float mass = p.fill_alpha * safe_c * ex2(fmaf(bsum / safe_c - m2, kLog2e, p_off));
+                    val = fminf(mass, bound) / safe_c;
+                  } else {
+                    const float bound = (float)BS * ex2(fmaf(bmx - m2, kLog2e, p_off));
+                    const float mass = p.fill_alpha * (float)BS * ex2(fmaf(bsum * kInvBs - m2, kLog2e, p_off));
+                    val = fminf(mass, bound) * kInvBs;
+                  }
+                  binval[b0 / BS] = val;
+                  fill_max_own = fmaxf(fill_max_own, val);
+                }
+              }
+            };
+            switch (BN / p.uta_bins) {
+              case 2: bins(std::integral_constant<int, 2>{}); break;
+              case 4: bins(std::integral_constant<int, 4>{}); break;
+              case 8: bins(std::integral_constant<int, 8>{}); break;
+              case 16: bins(std::integral_constant<int, 16>{}); break;
+              default: bins(std::integral_constant<int, 32>{}); break;
+            }
+      };
+      if constexpr (BL && PK != 0) {
+        if (uta) {
+          if ((own_max - m2) < p.log_lambda) compute_bins();
+          x_mine[BUF][2 * SM::kXch] = fill_max_own;
+        }
+      }
+      [[maybe_unused]] bool warp_skip = false;
+      if constexpr (TV) {
+        // (max(a, b) - m) < log(lambda) holds exactly when it holds for a and for b: each thread tests its own half
+        // of the columns and a warp publishes one byte, 1 = all of its rows' halves lie under the threshold (rows past
+        // the end of the sequence agree with anything). Every warp arrives on the vote barrier and goes on; only a
+        // warp that voted 1 waits there, further down, for the other seven votes.
+        const bool half_skip = !row_ok || (own_max - m2) < p.log_lambda;
+        warp_skip = __all_sync(0xffffffffu, half_skip);
+        if (lane == 0) {
+          votes[(BUF * 2 + t) * 8 + (warp & 7)] = warp_skip ? 1 : 0;
+          mbar_arrive(BAR_VOTE(t, BUF));
+        }
+      }
       __syncwarp();                            // a named barrier counts warps: arrive once, converged
       asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
+      if constexpr (TV) {
+        if (warp_skip) {
+          // a warp is never two blocks ahead of another one, so the barrier's phase is the block pair's parity
+          mbar_wait_cont(BAR_VOTE(t, BUF), (uint32_t)(it >> 1) & 1u, abort_flag, p.status, 16);
+          if (*reinterpret_cast<const volatile unsigned long long*>(votes + (BUF * 2 + t) * 8) == kAllVotes) {
+            // nothing of this block enters the tile: running max, row sum and accumulator stay as they are. The
+            // arrival still tells the MMA thread that S has been read (it reads the votes itself and issues no P.V).
+            n_skip += 1;
+            tc_fence_before();
+            if constexpr (PK == 0) {
+              mbar_arrive(bar_prdy + 8u * BUF);
+            } else {
+              __syncwarp();
+              if (lane == 0) mbar_arrive(bar_prdy + 8u * BUF);
+            }
+            return;
+          }
+        }
+      }
       bm0 = own_max;
       bm1 = *x_oth[BUF];
       if constexpr (BL) {
@@ -351,6 +459,9 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       [[maybe_unused]] bool skip = false;                       // BLASST: this row's block is below the threshold (attention_triton.py:165-175)
       if constexpr (BL) {
         skip = (bmax - m_new) < p.log_lambda;
+        if constexpr (TV) {
+          if (p.tile_pred) skip = false;         // the tile as a whole kept this block: every row of it computes it
+        }
         if (skip) m_new = m2;
         moved = !skip;
         n_skip += skip ? 1 : 0;
@@ -387,39 +498,42 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         if (skip) {
           const int nvalid = more ? BN : tail_valid;
           const float safe_n = (float)nvalid;                       // a block holds at least one key
-          if (p.fill_kind == LBFQ_FILL_UTA) {
-            // one value per bin of BN / bins keys; a bin never straddles the two halves of the block
-            auto bins = [&](auto bs_c) {
-              constexpr int BS = decltype(bs_c)::value;
-              if constexpr (BS <= HB) {
+          if (uta) {
+            if constexpr (PK == 0) {
+              // e4m3 P needs no largest fill: nothing to exchange, nothing to guess. The fills replace the scores.
+              auto bins = [&](auto bs_c) {
+                constexpr int BS = decltype(bs_c)::value;
+                if constexpr (BS <= HB) {
 #pragma unroll
-                for (int b0 = 0; b0 < HB; b0 += BS) {
-                  float bsum = 0.f, bmx = -INFINITY, bcnt = 0.f;
+                  for (int b0 = 0; b0 < HB; b0 += BS) {
+                    float bsum = 0.f, bmx = -INFINITY, bcnt = 0.f;
 #pragma unroll
-                  for (int i = b0; i < b0 + BS; ++i) {
-                    const bool ok = half * HB + i < nvalid;
-                    const float x = __uint_as_float(mine[i]);
-                    bsum += ok ? x : 0.f;
-                    bmx = fmaxf(bmx, x);                          // masked scores are -inf already
-                    bcnt += ok ? 1.f : 0.f;
+                    for (int i = b0; i < b0 + BS; ++i) {
+                      const bool ok = half * HB + i < nvalid;
+                      const float x = __uint_as_float(mine[i]);
+                      bsum += ok ? x : 0.f;
+                      bmx = fmaxf(bmx, x);                          // masked scores are -inf already
+                      bcnt += ok ? 1.f : 0.f;
+                    }
+                    const float safe_c = fmaxf(bcnt, 1.f);
+                    const float bound = safe_c * ex2(fmaf(bmx - m_new, kLog2e, p_off));
+                    const float mass = p.fill_alpha * safe_c * ex2(fmaf(bsum / safe_c - m_new, kLog2e, p_off));
+                    const float val = fminf(mass, bound) / safe_c;
+#pragma unroll
+                    for (int i = b0; i < b0 + BS; ++i) mine[i] = (half * HB + i < nvalid) ? __float_as_uint(val) : 0u;
                   }
-                  const float safe_c = fmaxf(bcnt, 1.f);
-                  const float bound = safe_c * ex2(fmaf(bmx - m_new, kLog2e, p_off));
-                  const float mass = p.fill_alpha * safe_c * ex2(fmaf(bsum / safe_c - m_new, kLog2e, p_off));
-                  const float val = fminf(mass, bound) / safe_c;
-#pragma unroll
-                  for (int i = b0; i < b0 + BS; ++i) mine[i] = (half * HB + i < nvalid) ? __float_as_uint(val) : 0u;
-                  fill_max = fmaxf(fill_max, val);
                 }
+              };
+              switch (BN / p.uta_bins) {
+                case 2: bins(std::integral_constant<int, 2>{}); break;
+                case 4: bins(std::integral_constant<int, 4>{}); break;
+                case 8: bins(std::integral_constant<int, 8>{}); break;
+                case 16: bins(std::integral_constant<int, 16>{}); break;
+                default: bins(std::integral_constant<int, 32>{}); break;
               }
-            };
-            switch (BN / p.uta_bins) {
-              case 2: bins(std::integral_constant<int, 2>{}); break;
-              case 4: bins(std::integral_constant<int, 4>{}); break;
-              case 8: bins(std::integral_constant<int, 8>{}); break;
-              case 16: bins(std::integral_constant<int, 16>{}); break;
-              default: bins(std::integral_constant<int, 32>{}); break;
             }
+            fill_max = fill_max_own;
+            if constexpr (PK != 0) fill_max = fmaxf(fill_max, x_oth[BUF][2 * SM::kXch]);
           } else {
             float fill_p = 0.f;
             if (p.fill_kind != LBFQ_FILL_ZERO) {
@@ -443,17 +557,7 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             }
           }
         }
-        if constexpr (PK != 0) {
-          // the per-bin fills differ between the two halves of a row: their maxima meet like the block maxima did
-          // (in every block, whatever the rows decide: the number of barriers a warp passes never depends on data)
-          if (p.fill_kind == LBFQ_FILL_UTA) {
-            x_mine[BUF][2 * SM::kXch] = fill_max;
-            __syncwarp();
-            asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
-            fill_max = fmaxf(fill_max, x_oth[BUF][2 * SM::kXch]);
-          }
-          pmax = skip ? fill_max : ex2(fmaf(bmax, kLog2e, bias));
-        }
+        if constexpr (PK != 0) pmax = skip ? fill_max : ex2(fmaf(bmax, kLog2e, bias));
       } else if constexpr (PK != 0) {
         if constexpr (CORR) pmax = ex2(fmaf(bmax, kLog2e, bias));
         else pmax = ex2(fmaf(bmax_raw, c, bias));
@@ -504,8 +608,53 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       // (Selecting fill or exponential lane by lane in one pass, so that a warp with both kinds of rows quantises
       // once, measured 20-30 % slower in the blocks where nothing skips: the scores stay live across the
       // exponentials. The two paths below diverge instead; a warp whose rows all skip computes no exponentials.)
-      if (BL && skip) {
-        if (p.fill_kind != LBFQ_FILL_UTA && !ragged) {
+      if (BL && PK != 0 && skip && uta) {
+        // a bin's value is quantised once and replicated over the bin's columns; BS times the value is exact
+        auto put = [&](auto bs_c) {
+          constexpr int BS = decltype(bs_c)::value;
+          if constexpr (BS <= HB && BS >= kMinBin) {
+            if (ragged) {
+              const int nvalid = more ? BN : tail_valid;
+#pragma unroll
+              for (int i = 0; i < HB; ++i) mine[i] = (half * HB + i < nvalid) ? __float_as_uint(binval[i / BS]) : 0u;
+#pragma unroll
+              for (int i = 0; i < HB; i += 4)
+                emit(i, make_float2(__uint_as_float(mine[i]), __uint_as_float(mine[i + 1])),
+                     make_float2(__uint_as_float(mine[i + 2]), __uint_as_float(mine[i + 3])));
+            } else {
+              float sum = 0.f;
+#pragma unroll
+              for (int b = 0; b < HB / BS; ++b) {
+                const float v = binval[b];
+                sum += v * (float)BS;
+                if constexpr (PK == 0) {
+                  if constexpr (BS >= 4) {
+                    const uint32_t w = f32x4_to_e4m3x4(v, v, v, v);
+#pragma unroll
+                    for (int j = 0; j < BS / 4; ++j) pk[b * (BS / 4) + j] = w;
+                  } else if (b % 2 == 0) {
+                    pk[b / 2] = f32x4_to_e4m3x4(v, v, binval[b + 1], binval[b + 1]);
+                  }
+                } else {
+                  const float q = v * inv_p;
+                  const uint32_t w = e4m3_round_scale_bf16x2(q, q, s_p);
+#pragma unroll
+                  for (int j = 0; j < BS / 2; ++j) pk[b * (BS / 2) + j] = w;
+                }
+              }
+              psa = make_float2(sum, 0.f);
+            }
+          }
+        };
+        switch (BN / p.uta_bins) {
+          case 2: put(std::integral_constant<int, 2>{}); break;
+          case 4: put(std::integral_constant<int, 4>{}); break;
+          case 8: put(std::integral_constant<int, 8>{}); break;
+          case 16: put(std::integral_constant<int, 16>{}); break;
+          default: put(std::integral_constant<int, 32>{}); break;
+        }
+      } else if (BL && skip) {
+        if (!ragged && !uta) {
           // one value in every column of a full block: quantised once; HB times the value is exact
           const float2 pf = make_float2(fill_const, fill_const);
           emit(0, pf, pf);
@@ -788,14 +937,25 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         if (sub == NSUB - 1 || j == nblk - 1) tc_commit(BAR_KFREE(st));
         return true;
       };
+      unsigned long long n_elided = 0;
       auto issue_pv = [&](int j) -> bool {
         const int c = j / NSUB, sub = j % NSUB, st = c % kFastStages;
+        // (the stage's V is awaited even when no P.V reads it: a stage is handed back only once its load has landed)
         if (sub == 0 && !mbar_wait(BAR_VFULL(st), (c / kFastStages) & 1, abort_flag, p.status, 33)) return false;
         if constexpr (VALPHA) {
           if (sub == 0 && !mbar_wait(BAR_SIDEFULL(st), (c / kFastStages) & 1, abort_flag, p.status, 37)) return false;
         }
         tc_fence_after();
-        if constexpr (PK == 0) {
+        bool elide = false;
+        if constexpr (TV) {
+          // every row of the tile skipped this block: there is no P. (Never the first block: a row's running max
+          // starts at -inf, which no block is below.)
+          elide = *reinterpret_cast<const volatile unsigned long long*>(votes + ((j & 1) * 2 + t) * 8) == kAllVotes;
+          n_elided += elide ? 1 : 0;
+        }
+        if (elide) {
+          // the commits below still fire: they track the operations issued so far
+        } else if constexpr (PK == 0) {
           const uint64_t dv = make_desc(sbase + SM::offV + st * SM::kV, kChunk);
 #pragma unroll
           for (int kk = 0; kk < BN / 32; ++kk)
@@ -834,6 +994,9 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         if (ok) ok = issue_pv(it);
         if (ok && it + 2 < nblk) ok = issue_qk(it + 2);
       }
+      if constexpr (TV) {
+        if (p.elided != nullptr && n_elided != 0) atomicAdd(p.elided, n_elided);
+      }
     }
   }
 
@@ -852,12 +1015,12 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   }
 }
 
-template <int D, int BN, bool CORR, int PK, bool VALPHA, int QB, bool BL = false>
+template <int D, int BN, bool CORR, int PK, bool VALPHA, int QB, bool BL = false, bool TV = false>
 int launch_fast_t(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& ma, const Params& p,
                   cudaStream_t st) {
   using SM = FastSmem<D, PK, QB, BL ? 1 : 0>;
   const int smem_bytes = SM::total + 1024;
-  auto kern = attn_fast_kernel<D, BN, CORR, PK, VALPHA, QB, BL>;
+  auto kern = attn_fast_kernel<D, BN, CORR, PK, VALPHA, QB, BL, TV>;
   LBFQ_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
   dim3 grid((p.M + kCtaM - 1) / kCtaM, p.B * p.H, 1);
   kern<<<grid, kFastThreads, smem_bytes, st>>>(mq, mk, mv, ma, p);
@@ -903,6 +1066,10 @@ int launch_fast(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap&
   const bool va = p.v_alpha != nullptr;
   if (p.blasst) {
 #define LBFQ_FAST_BL(DD, NN)                                                                                      \
+  if (p.tile_vote) {                                                                                              \
+    if (variant == 2) return launch_fast_t<DD, NN, false, 1, false, 0, true, true>(mq, mk, mv, ma, p, st);        \
+    return launch_fast_t<DD, NN, false, 0, false, 0, true, true>(mq, mk, mv, ma, p, st);                          \
+  }                                                                                                               \
   if (variant == 2) return launch_fast_t<DD, NN, false, 1, false, 0, true>(mq, mk, mv, ma, p, st);                \
   return launch_fast_t<DD, NN, false, 0, false, 0, true>(mq, mk, mv, ma, p, st)
     if (p.D == 128 && block_n == 64) { LBFQ_FAST_BL(128, 64); }

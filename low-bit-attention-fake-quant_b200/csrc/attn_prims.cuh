@@ -339,6 +339,9 @@ struct Params {
   float fill_alpha;
   int uta_bins;
   float* stats;
+  int tile_vote;               // 1: the rows of a 128-row tile vote on every key block (zero fill, no rowmax_init)
+  int tile_pred;               // 1: a block is skipped only by the whole tile (the simulator's predicate)
+  unsigned long long* elided;  // optional counter of (tile, block) pairs without P.V
   unsigned long long* counters; // optional row-max update counters (6), general kernel only
   void* out;
   int out_dtype, out_layout, out_exact;

@@ -58,6 +58,8 @@ class AttnArgs(C.Structure):
         ("fill_alpha", C.c_float),
         ("uta_bins", C.c_int),
         ("blasst_stats", C.c_void_p),
+        ("blasst_tile_predicate", C.c_int),
+        ("blasst_elided", C.c_void_p),
         ("out", C.c_void_p),
         ("out_dtype", C.c_int), ("out_layout", C.c_int),
         ("out_row_index", C.c_void_p),

@@ -216,7 +216,8 @@ def _fake_quant_attention_sdpa(q_work, k_work, v_work, qm, v_alpha, cfg: QuantCo
 def _fake_quant_attention_p_requant(q_work, k_work, v_work, qm, v_alpha, q_kmeans, cfg: QuantConfig,
                                     sm_scale, out_dtype, *, return_stats: bool = False,
                                     out_fp32_exact: bool = False, head_offset: int = 0, total_heads: int = 0,
-                                    rowmax_counters=None, k_mean=None, prepared=None):
+                                    rowmax_counters=None, k_mean=None, prepared=None,
+                                    blasst_tile_predicate: bool = False, blasst_elided=None):
     """Quantise straight into the kernel's layouts and launch it. Returns the
     output in NHD, rows already back in the original Q order.
 
@@ -300,6 +301,7 @@ def _fake_quant_attention_p_requant(q_work, k_work, v_work, qm, v_alpha, q_kmean
         blasst_lambda=cfg.blasst_lambda, blasst_fill_mode=cfg.blasst_fill,
         blasst_fill_alpha=cfg.blasst_fill_alpha, blasst_uta_bins=cfg.blasst_uta_bins,
         return_blasst_stats=return_stats,
+        blasst_tile_predicate=blasst_tile_predicate, blasst_elided=blasst_elided,
         out_dtype=torch.float32 if out_fp32_exact else out_dtype, out_nhd=True,
         out_row_index=q_kmeans.order if q_kmeans is not None else None,
         out_fp32_exact=out_fp32_exact,
@@ -474,6 +476,8 @@ def fake_quant_attention(
     _reference_operands: bool = False,
     _q_labels: Optional[torch.Tensor] = None,
     _v_labels: Optional[torch.Tensor] = None,
+    _blasst_tile_predicate: bool = False,
+    _blasst_elided: Optional[torch.Tensor] = None,
 ):
     """Fake-quant attention with FP8/MXFP8 Q/K/V (and optional P requant).
 
@@ -489,6 +493,10 @@ def fake_quant_attention(
     ``_reference_operands`` runs path B on the reference's own BF16 operands
     (BF16 MMAs) instead of the FP8 codes: the reference's numerics, at BF16 speed.
     ``_q_labels`` / ``_v_labels`` (testing aid) give the k-means reorders their cluster assignments.
+    ``_blasst_tile_predicate`` (extension): BLASST drops a key block only when every row of a 128-row tile finds it
+    under the threshold, and then for the whole tile -- the predicate of the reference's simulator
+    (blasst_skip.py:573-585) instead of the kernel's row-by-row one; zero fill. ``_blasst_elided``: one int64 zero on
+    the device that receives the number of (tile, key block) pairs the kernel did no work for.
     """
     if cfg is None:
         cfg = QuantConfig()
@@ -531,7 +539,8 @@ def fake_quant_attention(
         if prep is not None:
             return _fake_quant_attention_p_requant(
                 q, prep["k_smooth"], v, prep["qm"], prep["v_alpha"], prep["q_kmeans"], cfg, sm_scale, out_dtype,
-                out_fp32_exact=_debug_fp32, head_offset=_head_offset, total_heads=_total_heads, prepared=prep)
+                out_fp32_exact=_debug_fp32, head_offset=_head_offset, total_heads=_total_heads, prepared=prep,
+                blasst_tile_predicate=_blasst_tile_predicate, blasst_elided=_blasst_elided)
 
     if preprocess_cache is not None:
         pc = preprocess_cache
@@ -558,6 +567,8 @@ def fake_quant_attention(
                   and not (L.flags() & L.FLAG_ATTN_GENERIC)
                   and (qm is None or cfg.q_smooth_block_size % 128 == 0)
                   and (v_alpha is None or cfg.v_smooth_block_size == 64 or cfg.v_smooth_block_size % 128 == 0))
+    if (_blasst_tile_predicate or _blasst_elided is not None) and (_reference_operands or not cfg.p_requant):
+        raise ValueError("_blasst_tile_predicate / _blasst_elided belong to the streaming kernel on FP8 codes")
     if cfg.p_requant and (_reference_operands or mx_as_bf16):
         o = _fake_quant_attention_p_requant_reference_operands(
             q_work, k_work, v_work, qm, v_alpha, q_km, cfg, sm_scale, out_dtype, out_fp32_exact=_debug_fp32,
@@ -566,7 +577,9 @@ def fake_quant_attention(
         # the kernel scatters its rows through q_km.order: no separate inverse gather
         o = _fake_quant_attention_p_requant(q_work, k_work, v_work, qm, v_alpha, q_km, cfg, sm_scale, out_dtype,
                                             out_fp32_exact=_debug_fp32, head_offset=_head_offset,
-                                            total_heads=_total_heads, k_mean=k_mean)
+                                            total_heads=_total_heads, k_mean=k_mean,
+                                            blasst_tile_predicate=_blasst_tile_predicate,
+                                            blasst_elided=_blasst_elided)
     else:
         o = _fake_quant_attention_sdpa(q_work, k_work, v_work, qm, v_alpha, cfg, sm_scale, sdpa_dtype,
                                        _head_offset, _total_heads)

@@ -97,6 +97,8 @@ def fake_quant_attention_fp8(
     blasst_fill_alpha: float = 1.0,
     blasst_uta_bins: int = 16,
     return_blasst_stats: bool = False,
+    blasst_tile_predicate: bool = False,
+    blasst_elided: Optional[torch.Tensor] = None,
     out_dtype: torch.dtype = torch.bfloat16,
     out_nhd: bool = False,
     out_row_index: Optional[torch.Tensor] = None,
@@ -110,6 +112,11 @@ def fake_quant_attention_fp8(
 
     ``out_row_index`` (B*H, M) int64 scatters kernel row r to output row
     ``out_row_index[bh, r]`` (the inverse Q reorder fused into the store).
+
+    ``blasst_tile_predicate``: a key block is dropped only when every row of the 128-row tile finds it under the
+    threshold, and then for the whole tile (the predicate of the reference's simulator, blasst_skip.py:573-585) instead
+    of row by row; zero fill only. ``blasst_elided``: optional int64 tensor of one zero on the device; the kernel adds
+    the number of (128-row tile, key block) pairs it did no softmax and no P.V for.
     """
     if not q_codes.is_cuda:
         raise ValueError("operands must live on CUDA")
@@ -138,6 +145,16 @@ def fake_quant_attention_fp8(
         if blasst_fill_mode not in ("zero", None):
             raise ValueError("blasst_fill_mode requires blasst_lambda")
         fill_kind, fill_alpha, uta_bins = _BLASST_FILL_ZERO, 1.0, 1
+    if blasst_tile_predicate:
+        if not use_blasst:
+            raise ValueError("blasst_tile_predicate requires blasst_lambda")
+        if fill_kind != _BLASST_FILL_ZERO:
+            raise ValueError("blasst_tile_predicate drops whole tiles: only the zero fill applies")
+        if rowmax_init_bhs is not None:
+            raise ValueError("blasst_tile_predicate is built for the online row max without rowmax_init_bhs")
+    if blasst_elided is not None and (blasst_elided.dtype != torch.int64 or blasst_elided.numel() != 1
+                                      or blasst_elided.device != q_codes.device):
+        raise ValueError("blasst_elided must be one int64 value on the operands' device")
     if rowmax_est_bhs is not None and rowmax_init_bhs is not None:
         raise ValueError("rowmax_init_bhs and rowmax_est_bhs are mutually exclusive")
     v_kind_code = {"fp8_channel": L.V_CHANNEL, "fp8_block": L.V_BLOCK, "mxfp8": L.V_MX}[v_kind]
@@ -183,6 +200,8 @@ def fake_quant_attention_fp8(
         a.blasst_lambda = float(blasst_lambda) if use_blasst else 0.0
         a.fill_kind, a.fill_alpha, a.uta_bins = int(fill_kind), float(fill_alpha), int(uta_bins)
         a.blasst_stats = L.ptr(stats)
+        a.blasst_tile_predicate = 1 if blasst_tile_predicate else 0
+        a.blasst_elided = L.ptr(blasst_elided)
         a.out = out.data_ptr()
         a.out_dtype = L.dtype_code(out_dtype)
         a.out_layout = L.LAYOUT_NHD if out_nhd else L.LAYOUT_BHSD

@@ -99,10 +99,11 @@ def space_time_block_order(t: int, h: int, w: int, *, ts: int, hs: int, ws: int,
 
 
 def fake_quant_attention_reordered(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cfg: Optional[QuantConfig],
-                                   order: torch.Tensor, *, sm_scale: Optional[float] = None) -> torch.Tensor:
+                                   order: torch.Tensor, *, sm_scale: Optional[float] = None, **kwargs) -> torch.Tensor:
     """``fake_quant_attention`` on the tokens taken in ``order`` (a permutation of range(S), e.g.
     ``space_time_block_order``), result returned in the original token order. Exact attention does not depend on the
-    order; the fake-quant one does through its per-block scales, and BLASST through which rows share a block."""
+    order; the fake-quant one does through its per-block scales, and BLASST through which rows share a block.
+    Further keywords go to ``fake_quant_attention``."""
     from .kmeans import apply_kv_permutation
     b, s, h, _ = q.shape
     if order.ndim != 1 or order.numel() != s:
@@ -112,7 +113,7 @@ def fake_quant_attention_reordered(q: torch.Tensor, k: torch.Tensor, v: torch.Te
     inverse[order] = torch.arange(s, device=q.device, dtype=torch.int64)
     fwd = order.unsqueeze(0).expand(b * h, s).contiguous()
     out = fake_quant_attention(apply_kv_permutation(q, fwd), apply_kv_permutation(k, fwd), apply_kv_permutation(v, fwd),
-                               cfg, sm_scale=sm_scale)
+                               cfg, sm_scale=sm_scale, **kwargs)
     return apply_kv_permutation(out, inverse.unsqueeze(0).expand(b * h, s).contiguous())
 
 

@@ -11,7 +11,7 @@ Hadamard signs and k-means seeding are indexed by the global head.
 """
 from __future__ import annotations
 
-from typing import Optional
+from typing import Optional, Sequence
 
 import torch
 
@@ -35,6 +35,37 @@ def _copy_rows(dst: torch.Tensor, src: torch.Tensor, h0: int, h1: int, rows_s: i
             L.check(L.lib().lbfq_copy_rows_async(hp, h * d * es, dp, width, width, rows_s, 0, stream.cuda_stream))
 
 
+def _chunk_bounds(h: int, cfg: QuantConfig, heads_per_chunk: Optional[int], chunk_heads: Optional[Sequence[int]]):
+    """[h0, h1) of every pipelined chunk of the H heads."""
+    if chunk_heads is not None:
+        sizes = [int(n) for n in chunk_heads]
+        if not sizes or min(sizes) <= 0 or sum(sizes) != h:
+            raise ValueError(f"chunk_heads must be positive and add up to the {h} heads; got {list(chunk_heads)}")
+        edges = [0]
+        for n in sizes:
+            edges.append(edges[-1] + n)
+        return list(zip(edges[:-1], edges[1:]))
+    kmeans = cfg.q_kmeans_k is not None or cfg.v_kmeans_k is not None
+    if heads_per_chunk is None:
+        # small chunks hide more of the copies; the k-means passes want enough heads per launch to fill the GPU
+        heads_per_chunk = 8 if kmeans else 4
+    if heads_per_chunk <= 0:
+        raise ValueError("heads_per_chunk must be positive")
+    hc = min(heads_per_chunk, h)
+    bounds = [(h0, min(h0 + hc, h)) for h0 in range(0, h, hc)]
+    if len(bounds) > 2 and not kmeans:
+        # nothing overlaps the last chunk's compute and copy back: taper it (.., hc/2, hc/4, .., 1) so that the tail
+        # of the pipeline is one head long; the k-means passes keep their full chunks
+        h0, h1 = bounds.pop()
+        n = h1 - h0
+        while n > 1:
+            step = (n + 1) // 2
+            bounds.append((h0, h0 + step))
+            h0, n = h0 + step, n - step
+        bounds.append((h0, h1))
+    return bounds
+
+
 def fake_quant_attention_host(
     q: torch.Tensor,
     k: torch.Tensor,
@@ -45,6 +76,7 @@ def fake_quant_attention_host(
     out: Optional[torch.Tensor] = None,
     device: Optional[torch.device] = None,
     heads_per_chunk: Optional[int] = None,
+    chunk_heads: Optional[Sequence[int]] = None,
 ) -> torch.Tensor:
     """``fake_quant_attention`` on host tensors.
 
@@ -52,6 +84,7 @@ def fake_quant_attention_host(
     ``out``: optional contiguous (B, S_out <= S, H, D) CPU tensor of ``q``'s dtype; only its first ``S_out``
     rows are brought back (the caller's way to drop padding rows). Returns ``out``; it is complete when
     this function returns. ``heads_per_chunk``: heads per pipelined chunk (default 4, or 8 with k-means reorder).
+    ``chunk_heads``: the chunk sizes themselves, in order (they must add up to H); overrides ``heads_per_chunk``.
     """
     if cfg is None:
         cfg = QuantConfig()
@@ -74,24 +107,9 @@ def fake_quant_attention_host(
         raise ValueError(f"out must be (B, S_out <= S, H, D); got {tuple(out.shape)}")
     if out.dtype != q.dtype or out.is_cuda or not out.is_contiguous():
         raise ValueError("out must be a contiguous host tensor of q's dtype")
-    if heads_per_chunk is None:
-        # small chunks hide more of the copies; the k-means passes want enough heads per launch to fill the GPU
-        heads_per_chunk = 8 if (cfg.q_kmeans_k is not None or cfg.v_kmeans_k is not None) else 4
-    if heads_per_chunk <= 0:
-        raise ValueError("heads_per_chunk must be positive")
     dev = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
-    hc = min(heads_per_chunk, h)
-    bounds = [(h0, min(h0 + hc, h)) for h0 in range(0, h, hc)]
-    if len(bounds) > 2 and not (cfg.q_kmeans_k is not None or cfg.v_kmeans_k is not None):
-        # nothing overlaps the last chunk's compute and copy back: taper it (.., hc/2, hc/4, .., 1) so that the tail
-        # of the pipeline is one head long; the k-means passes keep their full chunks
-        h0, h1 = bounds.pop()
-        n = h1 - h0
-        while n > 1:
-            step = (n + 1) // 2
-            bounds.append((h0, h0 + step))
-            h0, n = h0 + step, n - step
-        bounds.append((h0, h1))
+    bounds = _chunk_bounds(h, cfg, heads_per_chunk, chunk_heads)
+    hc = max(h1 - h0 for h0, h1 in bounds)
     s_out = out.shape[1]
 
     with torch.cuda.device(dev):
@@ -102,14 +120,24 @@ def fake_quant_attention_host(
         loaded = [torch.cuda.Event() for _ in bounds]
         computed = [torch.cuda.Event() for _ in bounds]
         results = []
-        for i, (h0, h1) in enumerate(bounds):
-            n = h1 - h0
-            bufs = [t[:, :, :n] if n == hc else t.view(-1)[: b * s * n * d].view(b, s, n, d) for t in slots[i % 2]]
+
+        def buffers(i):
+            n = bounds[i][1] - bounds[i][0]
+            return [t[:, :, :n] if n == hc else t.view(-1)[: b * s * n * d].view(b, s, n, d) for t in slots[i % 2]]
+
+        def load(i):
+            h0, h1 = bounds[i]
             if i >= 2:
                 s_in.wait_event(computed[i - 2])            # the slot's previous occupant has been consumed
-            for dst, src in zip(bufs, (q, k, v)):
+            for dst, src in zip(buffers(i), (q, k, v)):
                 _copy_rows(dst, src, h0, h1, s, True, s_in)
             loaded[i].record(s_in)
+
+        load(0)
+        for i, (h0, h1) in enumerate(bounds):
+            if i + 1 < len(bounds):
+                load(i + 1)                                  # queued before this chunk's launches: the host never holds it back
+            bufs = buffers(i)
             comp.wait_event(loaded[i])
             o = fake_quant_attention(bufs[0], bufs[1], bufs[2], cfg, sm_scale=sm_scale, _head_offset=h0, _total_heads=h)
             computed[i].record(comp)

@@ -272,7 +272,8 @@ def attention_sdpa(qw, kw, vw, qm, v_alpha, cfg, sm_scale, sdpa_dtype, head_offs
 
 def attention_p_requant(qw, kw, vw, qm, v_alpha, cfg, sm_scale, *, faithful: bool,
                         return_stats: bool = False, head_offset: int = 0, total_heads: int = 0,
-                        p_bf16: Optional[bool] = None, rowmax_counters: Optional[dict] = None):
+                        p_bf16: Optional[bool] = None, rowmax_counters: Optional[dict] = None,
+                        blasst_tile_rows: int = 0):
     """Returns the kernel's FP32 output in NHD (B,S,H,D), before the final cast."""
     b, s, h, d = qw.shape
     qi, ki = qk_inputs_for_quant(qw, kw, cfg, head_offset, total_heads)
@@ -337,6 +338,7 @@ def attention_p_requant(qw, kw, vw, qm, v_alpha, cfg, sm_scale, *, faithful: boo
         blasst_lambda=cfg.blasst_lambda, blasst_fill_mode=cfg.blasst_fill,
         blasst_fill_alpha=cfg.blasst_fill_alpha, blasst_uta_bins=cfg.blasst_uta_bins,
         faithful=faithful, p_bf16=p_bf16, return_stats=return_stats, rowmax_counters=rowmax_counters,
+        blasst_tile_rows=blasst_tile_rows,
     )
     if return_stats:
         return res[0].permute(0, 2, 1, 3).contiguous(), res[1]
@@ -350,7 +352,7 @@ def attention_p_requant(qw, kw, vw, qm, v_alpha, cfg, sm_scale, *, faithful: boo
 def fake_quant_attention(q, k, v, cfg, *, sm_scale: Optional[float] = None, faithful: bool = True,
                          q_labels=None, v_labels=None, out_fp32: bool = False, head_offset: int = 0,
                          total_heads: int = 0, p_bf16: Optional[bool] = None, rowmax_counters: Optional[dict] = None,
-                         cross: bool = False):
+                         cross: bool = False, blasst_tile_rows: int = 0):
     """attention.py:706-806 on CPU tensors.
 
     ``cross`` (an extension the reference's entry does not have) lets K / V have their own length; every step below
@@ -383,7 +385,7 @@ def fake_quant_attention(q, k, v, cfg, *, sm_scale: Optional[float] = None, fait
     if cfg.p_requant:
         o = attention_p_requant(qw, kw, vw, qm, v_alpha, cfg, sm_scale, faithful=faithful,
                                 head_offset=head_offset, total_heads=total_heads, p_bf16=p_bf16,
-                                rowmax_counters=rowmax_counters)
+                                rowmax_counters=rowmax_counters, blasst_tile_rows=blasst_tile_rows)
         if not out_fp32:
             o = o.to(torch.bfloat16).to(out_dtype)        # kernel stores BF16, then .to(out_dtype)
     else:

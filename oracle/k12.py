@@ -92,6 +92,7 @@ def k12_attention(
     blasst_fill_mode: Optional[str] = "zero",
     blasst_fill_alpha: float = 1.0,
     blasst_uta_bins: int = 16,
+    blasst_tile_rows: int = 0,
     faithful: Optional[bool] = None,
     p_bf16: Optional[bool] = None,
     return_stats: bool = False,
@@ -101,7 +102,11 @@ def k12_attention(
 
     ``rowmax_counters``: a dict that receives the row-max update counts of this run, the events the reference's
     diagnostic kernel counts (bench/count_rowmax_updates_triton.py:118-171): an update moves a row's reference max,
-    a rescale is an update of a row that already holds mass."""
+    a rescale is an update of a row that already holds mass.
+
+    ``blasst_tile_rows`` > 0 replaces the kernel's row-by-row skip decision by the tile-level one of the reference's
+    simulator (blasst_skip.py:573-585): a key block is dropped only when every row of a tile of that many query rows
+    finds it under the threshold, and then for all of them (zero fill)."""
     B, H, M, D = q_op.shape
     N = k_op.shape[2]
     if faithful is None:
@@ -172,6 +177,11 @@ def k12_attention(
         if use_blasst:                                                     # :165-175
             m_ij = torch.maximum(m_i, block_max)
             skip_row = (block_max - m_ij) < log_lambda
+            if blasst_tile_rows:
+                tr = int(blasst_tile_rows)
+                padded = torch.nn.functional.pad(skip_row, (0, (-M) % tr), value=True)
+                whole = padded.reshape(B, H, -1, tr).all(dim=-1, keepdim=True)
+                skip_row = whole.expand(-1, -1, -1, tr).reshape(B, H, -1)[..., :M]
             alpha = torch.exp2((m_i - m_ij) * log2e)
             alpha = torch.where(skip_row, torch.ones_like(alpha), alpha)
             m_ij = torch.where(skip_row, m_i, m_ij)

@@ -148,6 +148,59 @@ def test_blasst_stats_and_whole_tile_elision():
     _check(g.float().cpu(), o, (q, k, v))
 
 
+@pytest.mark.parametrize("p_quant", ["elementwise", "dynamic"])
+def test_blasst_tile_vote_elides_blocks_and_serves_the_tile_predicate(p_quant):
+    """Zero fill: a key block that all 128 rows of a tile skip is not computed at all (the kernel counts those pairs),
+    with results and stats unchanged; with the tile-level predicate of the reference's simulator
+    (blasst_skip.py:573-585) a block is dropped only in that case. Tile 1 here holds a few rows that keep a block
+    the tile's other rows skip: row by row those others drop it, under the tile predicate nobody does."""
+    from low_bit_fake_quant.attention import _fake_quant_attention_p_requant
+    from oracle.api import attention_p_requant
+    torch.manual_seed(11)
+    B, S, H, D = 1, 1024, 2, 128
+    u, w = torch.randn(D), torch.randn(D)
+    u = u / u.norm()
+    w = w - (w @ u) * u
+    w = w / w.norm()
+    q = u.view(1, 1, 1, D) + 0.01 * torch.randn(B, S, H, D)
+    q[:, 200:230] += 1.5 * w.view(1, 1, 1, D)
+    k = 0.05 * torch.randn(B, S, H, D)
+    k[:, :64] = 40.0 * u.view(1, 1, 1, D)
+    k[:, 512:576] += 45.0 * w.view(1, 1, 1, D)
+    q, k, v = q.bfloat16(), k.bfloat16(), torch.randn(B, S, H, D).bfloat16()
+    cfg = QuantConfig(**COMMON, smoothing="off", q_kmeans_k=None, blasst_lambda=0.1, p_quant=p_quant)
+    sm = 1 / math.sqrt(D)
+    res = {}
+    for tile_pred in (False, True):
+        elided = torch.zeros(1, dtype=torch.int64, device=DEV)
+        g, stats = _fake_quant_attention_p_requant(q.to(DEV), k.to(DEV), v.to(DEV), None, None, None, cfg, sm, torch.bfloat16,
+                                                   return_stats=True, out_fp32_exact=True,
+                                                   blasst_tile_predicate=tile_pred, blasst_elided=elided)
+        raise_if_device_error(torch.device(DEV))
+        assert _variant() == 1
+        o, ostats = attention_p_requant(q, k, v, None, None, cfg, sm, faithful=False, return_stats=True, p_bf16=True,
+                                        blasst_tile_rows=128 if tile_pred else 0)
+        assert torch.equal(stats.cpu(), ostats)
+        _check(g.float().cpu(), o, (q, k, v))
+        res[tile_pred] = (int(elided.item()), stats.cpu())
+    # under the tile predicate every skipped row-block belongs to an elided (tile, block) pair: 128 rows each
+    n_tile = int(res[True][1][..., 0].sum().item())
+    assert n_tile % 128 == 0 and res[True][0] == n_tile // 128 and res[True][0] > 0
+    # row by row the same pairs are elided (a row that would skip alone computes nothing that moves its max), and more
+    # row-blocks are skipped than that
+    assert res[False][0] == res[True][0]
+    assert res[False][1][..., 0].sum().item() > n_tile
+
+
+def test_blasst_tile_predicate_refuses_what_it_does_not_serve():
+    q, k, v = (t.to(DEV) for t in _qkv(1, 256, 1, 128, seed=5))
+    cfg = QuantConfig(**COMMON, smoothing="off", q_kmeans_k=None, blasst_lambda=1e-2, blasst_fill="mean_a1.5")
+    with pytest.raises(ValueError, match="zero fill"):
+        fq.fake_quant_attention(q, k, v, cfg, _blasst_tile_predicate=True)
+    with pytest.raises(ValueError, match="requires blasst_lambda"):
+        fq.fake_quant_attention(q, k, v, QuantConfig(**COMMON, smoothing="off", q_kmeans_k=None), _blasst_tile_predicate=True)
+
+
 def test_bf16_store_is_one_rounding_of_the_fp32_result():
     cfg = QuantConfig(**COMMON, smoothing="k_only", q_kmeans_k=None)
     for dt in (torch.bfloat16, torch.float16, torch.float32):
