@@ -170,13 +170,13 @@ int lbfq_smooth_k(const void* k, int dtype, int B, int S, int H, int D, void* ou
 /* smooth_k without caller scratch. No counterpart in the reference: it exists for
  * hosts that can pass inputs and outputs but cannot allocate device memory for the
  * library (a plugin inside another framework's memory pool, an allocation-free
- * region such as work being recorded for later replay). Same result as
+ * region). Same result as
  * lbfq_smooth_k; the partial sums live in a 4 MiB array built into the library
  * (resident on every GPU that loads it, until the process exits). Limits and rules:
  *  - B*H*ceil(S/256)*D must be <= lbfq_smooth_k_static_max_floats() (1,048,576);
  *    larger shapes are refused with LBFQ_ERR_ARG;
  *  - the first call on each device looks up the array's device address (with that
- *    device current); make that first call before any stream capture;
+ *    device current);
  *  - all calls on a device share the one array: calls that may overlap on the GPU
  *    (different streams) race; serialise them. Nothing needs clearing between calls;
  *  - the looked-up address is kept per device ordinal for the life of the process: after

@@ -907,6 +907,28 @@ __global__ void v_codes_to_bf16_kernel(const uint8_t* __restrict__ codes, __nv_b
   }
 }
 
+// mxfp8 Q / K codes (B, H, s_pad, D) with their UE8M0 scale tiles (the layout lbfq_mxfp8_qk_quant writes) -> BF16
+// code * 2^e, which is exact: a power-of-two scale moves only the exponent. The TMEM-resident kernel has no columns
+// left for scale factors next to two S buffers and a 128-column accumulator per tile, so it multiplies these as BF16
+// operands: the same products as the block-scaled FP8 MMA, accumulated in FP32.
+__global__ void qk_mx_to_bf16_kernel(const uint8_t* __restrict__ codes, const uint8_t* __restrict__ sf,
+                                     __nv_bfloat16* __restrict__ out, size_t total8, int D, int block_d) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total8; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t e0 = i * 8;
+    const int d0 = (int)(e0 % D);
+    const size_t row = e0 / D;                                   // over (b, h, s_pad): 128-row tiles never straddle a slab
+    const int tt = (int)(row & 127);
+    const uint32_t e8 = sf[(row >> 7) * 512 + (tt & 31) * 16 + (tt >> 5) * 4 + d0 / block_d];
+    const float sc = __uint_as_float(e8 << 23);                  // 2^(e8 - 127)
+    const uint2 raw = *reinterpret_cast<const uint2*>(codes + e0);
+    const uint8_t* c8 = reinterpret_cast<const uint8_t*>(&raw);
+    __align__(16) __nv_bfloat16 o[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = __float2bfloat16_rn(e4m3_to_f32(c8[j]) * sc);
+    *reinterpret_cast<uint4*>(out + e0) = *reinterpret_cast<const uint4*>(o);
+  }
+}
+
 // alpha' (B, NB, H, D) fp32 -> (B, NB, H, D, 16) BF16: the three BF16 pieces h, m, l of each value laid out as
 // [h m l h m h 0 0] twice, the B operand rows of the K-extension step of P.V (see attention_fast.cu)
 __global__ void alpha_ext_kernel(const float* __restrict__ alpha, __nv_bfloat16* __restrict__ out, size_t total) {
@@ -942,7 +964,22 @@ static size_t alpha_ws_bytes(const lbfq_attn_args* a) {
 }
 // mx / dynamic P, or any P with the V-smoothing term, on FP8-block Q/K may take the BF16-P kernel, which wants a BF16
 // copy of V^T (and the alpha' pieces) in the workspace
+// mxfp8 Q / K go to the TMEM-resident kernel as BF16 operands wherever it serves the rest of the configuration
+// (everything fast_variant() asks of a BF16-operand launch, stated on the arguments)
+static bool mx_as_bf16(const lbfq_attn_args* a) {
+  if (a->qk_kind != LBFQ_QK_MX || a->use_blasst || a->rowmax_counters != nullptr) return false;
+  if (lbfq::debug_flags() & LBFQ_FLAG_ATTN_GENERIC) return false;
+  if (a->v_kind != LBFQ_V_CHANNEL && a->v_kind != LBFQ_V_MX) return false;
+  if (a->qm_corr != nullptr && a->q_smooth_block % 128 != 0) return false;
+  if (a->v_alpha != nullptr && !(a->v_smooth_block == 64 || a->v_smooth_block % 128 == 0)) return false;
+  if (a->block_n != 32 && a->block_n != 64) return false;
+  return a->sm_scale > 0.f && a->qk_block > 0 && a->D % a->qk_block == 0 && a->qk_block % 8 == 0 && a->D / a->qk_block <= 4;
+}
+static size_t qk_bf16_ws_bytes(const lbfq_attn_args* a) {
+  return mx_as_bf16(a) ? align256((size_t)a->B * a->H * a->m_pad * a->D * 2) + align256((size_t)a->B * a->H * a->n_pad * a->D * 2) : 0;
+}
 static bool may_want_v_bf16(const lbfq_attn_args* a) {
+  if (mx_as_bf16(a)) return true;
   if (a->use_blasst && (a->v_alpha || a->qm_corr || !lbfq::attn::fast_blasst_fill(a->fill_kind, a->uta_bins, a->block_n)))
     return false;
   return (a->p_kind != LBFQ_P_ELEMENTWISE || a->v_alpha) && a->v_kind != LBFQ_V_BLOCK && a->qk_kind == LBFQ_QK_FP8_BLOCK;
@@ -960,7 +997,7 @@ extern "C" int lbfq_attention_last_variant(void) { return g_last_variant; }
 
 extern "C" int64_t lbfq_attention_workspace_bytes(const lbfq_attn_args* a) {
   if (!a) return 0;
-  return (int64_t)(alpha_ws_bytes(a) + v_bf16_ws_bytes(a) + alpha_ext_ws_bytes(a));
+  return (int64_t)(alpha_ws_bytes(a) + v_bf16_ws_bytes(a) + alpha_ext_ws_bytes(a) + qk_bf16_ws_bytes(a));
 }
 
 // BF16 pieces of alpha' into `dst` and the tensor map over them: (16, D, B * NB * H) BF16, one (D x 16) tile per
@@ -1004,10 +1041,8 @@ extern "C" int lbfq_attention_fwd(const lbfq_attn_args* a, void* workspace, void
     // nothing to check: the operands carry their scales already
   } else if (mx) {
     LBFQ_REQUIRE(a->q_scale_e8 && a->k_scale_e8, LBFQ_ERR_ARG, "mxfp8 Q/K needs the UE8M0 scale tiles");
-    LBFQ_REQUIRE(a->qk_block == 32, LBFQ_ERR_UNSUPPORTED,
-                 "mxfp8_block_size=%d: the block-scaled MMA scales 32 elements of D at a time", a->qk_block);
-    // scale-factor columns of a 32-key block would start at odd TMEM columns, which the MMA rejects
-    LBFQ_REQUIRE(a->block_n == 64, LBFQ_ERR_UNSUPPORTED, "mxfp8 Q/K needs block_n = 64; got %d", a->block_n);
+    LBFQ_REQUIRE(a->qk_block > 0 && a->D % a->qk_block == 0 && a->D / a->qk_block <= 4, LBFQ_ERR_ARG,
+                 "mxfp8_block_size=%d must divide D into at most 4 groups", a->qk_block);
   } else {
     LBFQ_REQUIRE(a->q_scale && a->k_scale && a->qk_block > 0, LBFQ_ERR_ARG, "fp8_block Q/K needs scales and a block size");
     LBFQ_REQUIRE(a->M % a->qk_block == 0 && a->N % a->qk_block == 0, LBFQ_ERR_ARG,
@@ -1140,6 +1175,40 @@ extern "C" int lbfq_attention_fwd(const lbfq_attn_args* a, void* workspace, void
     g_last_variant = 1;
     return launch_fast(mq, mk, mv, ma, p, a->block_n, 2, st);
   }
+  if (mx && mx_as_bf16(a)) {
+    // mxfp8 Q / K as exact BF16 operands on the TMEM-resident kernel (see qk_mx_to_bf16_kernel)
+    Params pb = p;
+    pb.qk_bf16 = 1; pb.qk_block = a->block_n; pb.q_scale = nullptr; pb.k_scale = nullptr;
+    if (fast_variant(pb, false, false) == 2) {
+      LBFQ_REQUIRE(workspace != nullptr, LBFQ_ERR_ARG, "this configuration needs the workspace of lbfq_attention_workspace_bytes");
+      LBFQ_REQUIRE(a->q_scale_e8 != nullptr && a->k_scale_e8 != nullptr, LBFQ_ERR_ARG, "mxfp8 Q / K need their scale tiles");
+      uint8_t* ws = (uint8_t*)workspace;
+      __nv_bfloat16* vb = reinterpret_cast<__nv_bfloat16*>(ws + alpha_ws_bytes(a));
+      uint8_t* ext = ws + alpha_ws_bytes(a) + v_bf16_ws_bytes(a);
+      __nv_bfloat16* qb = reinterpret_cast<__nv_bfloat16*>(ext + alpha_ext_ws_bytes(a));
+      __nv_bfloat16* kb = reinterpret_cast<__nv_bfloat16*>((uint8_t*)qb + align256((size_t)a->B * a->H * a->m_pad * a->D * 2));
+      const int cap = sm_count() * 16;
+      auto blocks = [&](size_t n8) { const size_t g = (n8 + 255) / 256; return (int)(g > (size_t)cap ? cap : g); };
+      const size_t q8 = (size_t)a->B * a->H * a->m_pad * a->D / 8, k8 = (size_t)a->B * a->H * a->n_pad * a->D / 8;
+      qk_mx_to_bf16_kernel<<<blocks(q8), 256, 0, st>>>((const uint8_t*)a->q_codes, a->q_scale_e8, qb, q8, a->D, a->qk_block);
+      if (int rc = check_launch("qk_mx_to_bf16")) return rc;
+      qk_mx_to_bf16_kernel<<<blocks(k8), 256, 0, st>>>((const uint8_t*)a->k_codes, a->k_scale_e8, kb, k8, a->D, a->qk_block);
+      if (int rc = check_launch("qk_mx_to_bf16")) return rc;
+      const size_t v8 = (size_t)a->B * a->H * a->D * a->n_pad / 8;
+      v_codes_to_bf16_kernel<<<blocks(v8), 256, 0, st>>>((const uint8_t*)a->v_codes, vb, a->v_kind, a->v_scale, a->B, a->H, a->D, a->N,
+                                                         a->n_pad, p.v_block);
+      if (int rc = check_launch("v_codes_to_bf16")) return rc;
+      CUtensorMap mvb, ma;
+      if (int rc = make_map_bf16(&mq, qb, a->D, a->m_pad, BH, 64, kTileM)) return rc;
+      if (int rc = make_map_bf16(&mk, kb, a->D, a->n_pad, BH, 64, kChunk)) return rc;
+      if (int rc = make_map_bf16(&mvb, vb, a->n_pad, a->D, BH, 64, a->D)) return rc;
+      ma = mvb;
+      if (a->v_alpha)
+        if (int rc = make_alpha_ext(a, pb, ext, &ma, st)) return rc;
+      g_last_variant = 1;
+      return launch_fast(mq, mk, mvb, ma, pb, a->block_n, 2, st);
+    }
+  }
   if (int rc = make_map(&mq, a->q_codes, a->D, a->m_pad, BH, a->D, kTileM)) return rc;
   if (int rc = make_map(&mk, a->k_codes, a->D, a->n_pad, BH, a->D, kChunk)) return rc;
   if (int rc = make_map(&mv, a->v_codes, a->n_pad, a->D, BH, kChunk, a->D)) return rc;
@@ -1174,6 +1243,10 @@ extern "C" int lbfq_attention_fwd(const lbfq_attn_args* a, void* workspace, void
 #define LBFQ_LAUNCH(DD, NN, MX)                                                                    \
   return bl ? launch<DD, NN, true, MX>(mq, mk, mv, p, st) : launch<DD, NN, false, MX>(mq, mk, mv, p, st)
   if (mx) {
+    LBFQ_REQUIRE(a->qk_block == 32, LBFQ_ERR_UNSUPPORTED,
+                 "mxfp8_block_size=%d: the block-scaled MMA of the general kernel scales 32 elements of D at a time", a->qk_block);
+    // scale-factor columns of a 32-key block would start at odd TMEM columns, which the MMA rejects
+    LBFQ_REQUIRE(a->block_n == 64, LBFQ_ERR_UNSUPPORTED, "mxfp8 Q/K on the general kernel needs block_n = 64; got %d", a->block_n);
     if (a->D == 128) { LBFQ_LAUNCH(128, 64, true); }
     LBFQ_LAUNCH(64, 64, true);
   }

@@ -43,16 +43,18 @@ namespace {
 constexpr int kFastSoftmaxWarps = 16;
 constexpr int kFastThreads = (kFastSoftmaxWarps + 4) * 32;
 constexpr int kFastRegsLaunch = (65536 / kFastThreads) / 8 * 8;   // what __launch_bounds__(kFastThreads, 1) yields
-#ifndef LBFQ_FAST_REGS_SOFTMAX
-#define LBFQ_FAST_REGS_SOFTMAX 104
-#define LBFQ_FAST_REGS_SERVICE 40
-#endif
-constexpr int kFastRegsSoftmax = LBFQ_FAST_REGS_SOFTMAX;
-constexpr int kFastRegsService = LBFQ_FAST_REGS_SERVICE;
-// `setmaxnreg.inc` blocks until the CTA's register pool can satisfy it: the requests must fit in the pool
-static_assert(kFastSoftmaxWarps * 32 * kFastRegsSoftmax + 4 * 32 * kFastRegsService <= kFastThreads * kFastRegsLaunch,
-              "setmaxnreg requests exceed the CTA's register pool");
-static_assert(kFastRegsSoftmax % 8 == 0 && kFastRegsService % 8 == 0, "setmaxnreg granularity");
+// Registers per thread after the roles split (setmaxnreg): the softmax warps take what the service warps give up.
+// The BLASST instantiations carry more live state per block (fills, votes) and spill at 104, so they take 112 / 32;
+// the plain ones are faster at 104 / 40 (measured on the benchmark stacks).
+template <bool BL>
+struct FastRegs {
+  static constexpr int kSoftmax = BL ? 112 : 104;
+  static constexpr int kService = BL ? 32 : 40;
+  // `setmaxnreg.inc` blocks until the CTA's register pool can satisfy it: the requests must fit in the pool
+  static_assert(kFastSoftmaxWarps * 32 * kSoftmax + 4 * 32 * kService <= kFastThreads * kFastRegsLaunch,
+                "setmaxnreg requests exceed the CTA's register pool");
+  static_assert(kSoftmax % 8 == 0 && kService % 8 == 0, "setmaxnreg granularity");
+};
 
 // PK = 0: P as e4m3 codes, P.V an FP8 MMA over the V^T codes (4 key stages).
 // PK = 1: P re-scaled and rounded to BF16 as the reference does for its mx / dynamic P modes, P.V a BF16 MMA
@@ -186,7 +188,7 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 
   if (warp < kFastSoftmaxWarps) {
     // =========================== softmax warps ===========================
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kFastRegsSoftmax));
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(FastRegs<BL>::kSoftmax));
     const int t = warp >> 3;                                   // tile
     const int half = (warp >> 2) & 1;                          // which half of the columns this thread produces
     const int row_in_tile = (warp & 3) * 32 + lane;            // a warp reaches the TMEM lanes of its id mod 4
@@ -842,7 +844,7 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       }
     }
   } else {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kFastRegsService));
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(FastRegs<BL>::kService));
   }
   if (warp == kTmaWarp) {
     // =========================== TMA producer =====================================

@@ -309,6 +309,18 @@ def _fake_quant_attention_p_requant(q_work, k_work, v_work, qm, v_alpha, q_kmean
     )
 
 
+_SIDE_STREAMS: dict = {}
+
+
+def _side_stream(device: torch.device) -> "torch.cuda.Stream":
+    """One extra stream per device for work that is independent of the current stream's (kept for the process)."""
+    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+    st = _SIDE_STREAMS.get(key)
+    if st is None:
+        st = _SIDE_STREAMS[key] = torch.cuda.Stream(device)
+    return st
+
+
 def _prepare_fused(q, k, v, cfg: QuantConfig, *, head_offset: int = 0, total_heads: int = 0, q_labels=None, v_labels=None):
     """Preprocessing (attention.py:166-239 of the reference) and quantisation (:531-570) of all three tensors with one
     fused pass per tensor (``prepare.prep_fused``): the k-means orders and the K channel mean are found first, then
@@ -346,6 +358,21 @@ def _prepare_fused(q, k, v, cfg: QuantConfig, *, head_offset: int = 0, total_hea
 
     q_km = None
     q_order = v_order = None
+    if cfg.v_kmeans_k is not None and (cfg.v_kmeans_k <= 0 or cfg.v_kmeans_k > s_k):
+        return None
+    side = None
+    if cfg.q_kmeans_k is not None and cfg.v_kmeans_k is not None and q_labels is None and v_labels is None:
+        # the two clusterings are independent, and a Lloyd iteration is a chain of short kernels (assignment, sort,
+        # segment means) none of which fills the GPU to its end: V's runs on a second stream next to Q's
+        cur = torch.cuda.current_stream(q.device)
+        side = _side_stream(q.device)
+        side.wait_stream(cur)
+        with torch.cuda.stream(side):
+            lab_v = kmeans_labels(v, n_clusters=cfg.v_kmeans_k, max_iters=cfg.v_kmeans_iters, seed=cfg.v_kmeans_seed,
+                                  head_offset=head_offset, total_heads=total_heads)
+            v_order, v_inv = order_from_labels(lab_v, cfg.v_kmeans_k)
+        for t in (lab_v, v_order, v_inv):
+            t.record_stream(cur)
     if cfg.q_kmeans_k is not None:
         if cfg.q_kmeans_k <= 0 or cfg.q_kmeans_k > s:
             return None
@@ -355,9 +382,9 @@ def _prepare_fused(q, k, v, cfg: QuantConfig, *, head_offset: int = 0, total_hea
         q_order, q_inv = order_from_labels(lab, cfg.q_kmeans_k)
         q_km = KMeansReorderResult(tensor_reordered=None, order=q_order, inverse_order=q_inv, labels=lab.to(torch.int64))
     k_mean = k_channel_mean(k) if cfg.smoothing in ("k_only", "full") else None       # over K in its own order
-    if cfg.v_kmeans_k is not None:
-        if cfg.v_kmeans_k <= 0 or cfg.v_kmeans_k > s_k:
-            return None
+    if side is not None:
+        torch.cuda.current_stream(q.device).wait_stream(side)
+    elif cfg.v_kmeans_k is not None:
         lab = v_labels if v_labels is not None else kmeans_labels(
             v, n_clusters=cfg.v_kmeans_k, max_iters=cfg.v_kmeans_iters, seed=cfg.v_kmeans_seed, head_offset=head_offset,
             total_heads=total_heads)
@@ -531,9 +558,7 @@ def fake_quant_attention(
     # everything in front of the streaming kernel as one fused pass per tensor, when nothing asks for the
     # intermediate tensors (a cache, the artifacts, the reference's own operands) and the kernel takes the codes
     if (preprocess_cache is None and cfg.p_requant and not _reference_operands and not return_artifacts
-            and not (L.flags() & L.FLAG_UNFUSED_PREPROCESS)
-            and not (cfg.qk_quant == "mxfp8" and cfg.v_quant != "fp8_block" and cfg.blasst_lambda is None
-                     and not (L.flags() & L.FLAG_ATTN_GENERIC))):
+            and not (L.flags() & L.FLAG_UNFUSED_PREPROCESS)):
         prep = _prepare_fused(q, k, v, cfg, head_offset=_head_offset, total_heads=_total_heads, q_labels=_q_labels,
                               v_labels=_v_labels)
         if prep is not None:
@@ -559,17 +584,9 @@ def fake_quant_attention(
         q_work, k_work, v_work, qm, v_alpha, q_km = pre[:6]
         k_mean = pre[7] if defer else None
 
-    # mxfp8 Q / K de-quantise to BF16 exactly (power-of-two scales), so for them the BF16-operand kernel computes
-    # the same products as a block-scaled FP8 MMA and, unlike the general kernel, keeps the accumulator in tensor
-    # memory; it takes them whenever it serves the rest of the configuration
-    # (the FLAG_ATTN_GENERIC override keeps them on the general kernel's block-scaled Q.K^T, the cross-check)
-    mx_as_bf16 = (cfg.qk_quant == "mxfp8" and cfg.v_quant != "fp8_block" and cfg.blasst_lambda is None
-                  and not (L.flags() & L.FLAG_ATTN_GENERIC)
-                  and (qm is None or cfg.q_smooth_block_size % 128 == 0)
-                  and (v_alpha is None or cfg.v_smooth_block_size == 64 or cfg.v_smooth_block_size % 128 == 0))
-    if (_blasst_tile_predicate or _blasst_elided is not None) and (_reference_operands or not cfg.p_requant):
-        raise ValueError("_blasst_tile_predicate / _blasst_elided belong to the streaming kernel on FP8 codes")
-    if cfg.p_requant and (_reference_operands or mx_as_bf16):
+    # (mxfp8 Q / K codes reach the kernel with the accumulator in tensor memory as exact BF16 operands: the library
+    # converts them itself, lbfq_attention_fwd)
+    if cfg.p_requant and _reference_operands:
         o = _fake_quant_attention_p_requant_reference_operands(
             q_work, k_work, v_work, qm, v_alpha, q_km, cfg, sm_scale, out_dtype, out_fp32_exact=_debug_fp32,
             head_offset=_head_offset, total_heads=_total_heads)

@@ -11,6 +11,7 @@ Hadamard signs and k-means seeding are indexed by the global head.
 """
 from __future__ import annotations
 
+import time
 from typing import Optional, Sequence
 
 import torch
@@ -77,6 +78,7 @@ def fake_quant_attention_host(
     device: Optional[torch.device] = None,
     heads_per_chunk: Optional[int] = None,
     chunk_heads: Optional[Sequence[int]] = None,
+    trace: Optional[list] = None,
 ) -> torch.Tensor:
     """``fake_quant_attention`` on host tensors.
 
@@ -85,6 +87,8 @@ def fake_quant_attention_host(
     rows are brought back (the caller's way to drop padding rows). Returns ``out``; it is complete when
     this function returns. ``heads_per_chunk``: heads per pipelined chunk (default 4, or 8 with k-means reorder).
     ``chunk_heads``: the chunk sizes themselves, in order (they must add up to H); overrides ``heads_per_chunk``.
+    ``trace``: a list that receives one record per chunk -- its heads and the device times (ms since the call's first
+    copy was queued) at which its copy in, its kernels and its copy back ended, plus the host time its launches took.
     """
     if cfg is None:
         cfg = QuantConfig()
@@ -117,8 +121,12 @@ def fake_quant_attention_host(
         s_in, s_back = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
         s_in.wait_stream(comp)
         slots = [[torch.empty((b, s, hc, d), dtype=q.dtype, device=dev) for _ in range(3)] for _ in range(2)]
-        loaded = [torch.cuda.Event() for _ in bounds]
-        computed = [torch.cuda.Event() for _ in bounds]
+        timing = trace is not None
+        loaded = [torch.cuda.Event(enable_timing=timing) for _ in bounds]
+        computed = [torch.cuda.Event(enable_timing=timing) for _ in bounds]
+        returned = [torch.cuda.Event(enable_timing=True) for _ in bounds] if timing else None
+        start = torch.cuda.Event(enable_timing=True) if timing else None
+        host_ms = []
         results = []
 
         def buffers(i):
@@ -133,19 +141,31 @@ def fake_quant_attention_host(
                 _copy_rows(dst, src, h0, h1, s, True, s_in)
             loaded[i].record(s_in)
 
+        if timing:
+            start.record(s_in)
         load(0)
         for i, (h0, h1) in enumerate(bounds):
             if i + 1 < len(bounds):
                 load(i + 1)                                  # queued before this chunk's launches: the host never holds it back
             bufs = buffers(i)
             comp.wait_event(loaded[i])
+            t_host = time.perf_counter() if timing else 0.0
             o = fake_quant_attention(bufs[0], bufs[1], bufs[2], cfg, sm_scale=sm_scale, _head_offset=h0, _total_heads=h)
+            if timing:
+                host_ms.append((time.perf_counter() - t_host) * 1e3)
             computed[i].record(comp)
             s_back.wait_event(computed[i])
             o.record_stream(s_back)
             _copy_rows(out, o, h0, h1, s_out, False, s_back)
+            if timing:
+                returned[i].record(s_back)
             results.append(o)
         s_back.synchronize()
         comp.synchronize()
         L.status_for(dev)                 # everything has completed: raise if any launch gave up a bounded wait
+        if timing:
+            for i, (h0, h1) in enumerate(bounds):
+                trace.append({"heads": h1 - h0, "copied_in_ms": start.elapsed_time(loaded[i]),
+                              "computed_ms": start.elapsed_time(computed[i]), "copied_back_ms": start.elapsed_time(returned[i]),
+                              "host_launch_ms": host_ms[i]})
     return out
