@@ -57,13 +57,15 @@ const char* lbfq_last_error(void);
 int lbfq_abi_version(void);
 
 /* Debug overrides. They are read from the environment (LBFQ_ATTN_GENERIC=1, LBFQ_KMEANS_FFMA=1,
- * LBFQ_QM_CORR_FFMA=1, LBFQ_UNFUSED_PREPROCESS=1) once, when the library is first used; afterwards they change only
+ * LBFQ_QM_CORR_FFMA=1, LBFQ_UNFUSED_PREPROCESS=1, LBFQ_KMEANS_SORTED=1) once, when the library is first used; afterwards they change only
  * through lbfq_set_flags(). Each keeps a slower cross-check path in use: the general attention kernel, the FP32 FFMA
- * k-means assignment, the FP32 FFMA qm.K product, the one-kernel-per-step preprocessing. Process-wide, not per thread. */
+ * k-means assignment, the FP32 FFMA qm.K product, the one-kernel-per-step preprocessing, the k-means centroid update by
+ * sort + segment means. Process-wide, not per thread. */
 #define LBFQ_FLAG_ATTN_GENERIC 1
 #define LBFQ_FLAG_KMEANS_FFMA 2
 #define LBFQ_FLAG_QM_CORR_FFMA 4
 #define LBFQ_FLAG_UNFUSED_PREPROCESS 8
+#define LBFQ_FLAG_KMEANS_SORTED 16
 int lbfq_get_flags(void);
 void lbfq_set_flags(int flags);
 /* Number of kernels this library has launched in the calling process (a plain counter,

@@ -37,7 +37,8 @@ static std::atomic<int> g_flags{-1};
 static int flags_from_env() {
   auto on = [](const char* name) { const char* v = getenv(name); return v != nullptr && v[0] == '1'; };
   return (on("LBFQ_ATTN_GENERIC") ? LBFQ_FLAG_ATTN_GENERIC : 0) | (on("LBFQ_KMEANS_FFMA") ? LBFQ_FLAG_KMEANS_FFMA : 0) |
-         (on("LBFQ_QM_CORR_FFMA") ? LBFQ_FLAG_QM_CORR_FFMA : 0) | (on("LBFQ_UNFUSED_PREPROCESS") ? LBFQ_FLAG_UNFUSED_PREPROCESS : 0);
+         (on("LBFQ_QM_CORR_FFMA") ? LBFQ_FLAG_QM_CORR_FFMA : 0) | (on("LBFQ_UNFUSED_PREPROCESS") ? LBFQ_FLAG_UNFUSED_PREPROCESS : 0) |
+         (on("LBFQ_KMEANS_SORTED") ? LBFQ_FLAG_KMEANS_SORTED : 0);
 }
 int debug_flags() {
   int f = g_flags.load(std::memory_order_relaxed);

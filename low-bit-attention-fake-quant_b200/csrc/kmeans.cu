@@ -359,6 +359,29 @@ segment_mean_from_parts_kernel(const float* __restrict__ psum, const int32_t* __
   if (threadIdx.x == 0) cnorm[bh * k + c] = red[0] + red[1] + red[2] + red[3];
 }
 
+// centroids from the per-chunk sums and counts the tensor-core assignment leaves behind: chunks added in order
+__global__ void __launch_bounds__(128)
+chunk_mean_kernel(const float* __restrict__ psum, const int32_t* __restrict__ hist, int D, int k, int nchunk,
+                  float* __restrict__ cent, float* __restrict__ cnorm) {
+  __shared__ float red[4];
+  const int c = blockIdx.x % k;
+  const size_t bh = blockIdx.x / k;
+  int n = 0;
+  for (int ch = 0; ch < nchunk; ++ch) n += hist[(bh * nchunk + ch) * kSortMaxK + c];
+  if (n == 0) return;                               // empty cluster keeps centroid and norm
+  float v = 0.f;
+  if (threadIdx.x < D) {
+    float s = 0.f;
+    for (int ch = 0; ch < nchunk; ++ch) s += psum[((bh * nchunk + ch) * k + c) * D + threadIdx.x];
+    v = __fdiv_rn(s, (float)n);
+    cent[(bh * k + c) * D + threadIdx.x] = v;
+  }
+  const float s2 = warp_sum(v * v);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s2;
+  __syncthreads();
+  if (threadIdx.x == 0) cnorm[bh * k + c] = red[0] + red[1] + red[2] + red[3];
+}
+
 struct KmScratch {
   float* cent; float* cnorm; int32_t* order32; int32_t* seg; void* split; int32_t* hist; float* psum;
 };
@@ -373,7 +396,9 @@ static size_t scratch_layout(int BH, int S, int D, int k, uint8_t* base, KmScrat
   uint8_t* p4 = take(kmeans_tc_split_bytes(BH, D));       // BF16 pieces of the centroids (tensor-core assignment)
   const size_t nchunk = ((size_t)S + kmeans_tc_chunk_tokens() - 1) / kmeans_tc_chunk_tokens();
   uint8_t* p5 = take((size_t)BH * nchunk * kSortMaxK * 4);   // per-chunk label counts from the tensor-core assignment
-  uint8_t* p6 = take((size_t)BH * k * mean_parts(k) * D * 4);   // partial sums of the cluster means
+  // partial sums of the cluster means: per part of a sorted segment, or per chunk of the tensor-core assignment
+  const size_t parts = nchunk > (size_t)mean_parts(k) ? nchunk : (size_t)mean_parts(k);
+  uint8_t* p6 = take((size_t)BH * k * parts * D * 4);
   if (out) { out->split = p4; out->hist = (int32_t*)p5; out->psum = (float*)p6; }
   if (out) { out->cent = (float*)p0; out->cnorm = (float*)p1; out->order32 = (int32_t*)p2; out->seg = (int32_t*)p3; }
   return off;
@@ -412,10 +437,21 @@ extern "C" int lbfq_kmeans_labels(const void* x, int dtype, int B, int S, int H,
   const int ntile = (S + kTok - 1) / kTok;
   // LBFQ_FLAG_KMEANS_FFMA keeps the FP32 FFMA assignment (used to cross-check the two)
   const bool tc = kmeans_tc_eligible(dtype, D, k) && !(debug_flags() & LBFQ_FLAG_KMEANS_FFMA);
+  // LBFQ_FLAG_KMEANS_SORTED keeps the update by sort + segment means (the cross-check of the sums taken inside the
+  // assignment kernel)
+  const bool tcsum = tc && kmeans_tc_sums_eligible(dtype, D, k) && kmeans_tc_chunk_tokens() == 1024 &&
+                     !(debug_flags() & LBFQ_FLAG_KMEANS_SORTED);
   for (int it = 0; it < iters; ++it) {
     if (tc) {
-      // the counts are only wanted when a sort follows (not after the last assignment)
-      if (int rc = kmeans_tc_assign(x, B, S, H, D, k, sc.cent, sc.cnorm, sc.split, labels, it + 1 < iters ? sc.hist : nullptr, status, st)) return rc;
+      // the counts (and sums) are only wanted when an update follows (not after the last assignment)
+      const bool more = it + 1 < iters;
+      if (int rc = kmeans_tc_assign(x, B, S, H, D, k, sc.cent, sc.cnorm, sc.split, labels, more ? sc.hist : nullptr,
+                                    (more && tcsum) ? sc.psum : nullptr, status, st)) return rc;
+      if (more && tcsum) {
+        chunk_mean_kernel<<<BH * k, 128, 0, st>>>(sc.psum, sc.hist, D, k, (S + 1023) / 1024, sc.cent, sc.cnorm);
+        if (int rc = check_launch("kmeans update (chunk sums)")) return rc;
+        continue;
+      }
     } else {
       LBFQ_DISPATCH_DTYPE(dtype, T,
           assign_kernel<T><<<BH * ntile, kThreads, 0, st>>>((const T*)x, S, H, D, k, sc.cent, sc.cnorm, labels));

@@ -221,6 +221,253 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Assignment and, in the same pass over the tokens, the sums the centroid update needs (D = 128).
+//
+// sums^T (channels x clusters) += tokens^T (channels x tokens) . onehot (tokens x clusters) is one more GEMM over the
+// token tile that is in shared memory anyway: A is the tile read MN-major (channels contiguous: the two 64-channel
+// panels TMA delivered are its two 64-wide groups), B a 128 x 64 BF16 tile in which the thread of each token sets a
+// single 1.0 at its label. The products are exact (token x 1.0), the sums FP32, accumulated over the CTA's tiles in
+// 64 more TMEM columns and written out once per CTA as (chunk, cluster, channel) partial sums; a small kernel adds
+// the chunks in a fixed order and divides by the counts. That replaces the sort by label and the gather of the sorted
+// rows in every Lloyd iteration. One CTA per SM: four token buffers, two consumer groups of 128 threads (tile i
+// belongs to group i & 1), one producer thread.
+constexpr int kSumBufs = 4;
+constexpr int kSumThreads = (2 * 4 + 1) * 32;
+
+// shared-memory descriptor of an MN-major operand in 128-byte-swizzled rows: 64 elements (128 bytes) of the M / N
+// extent are contiguous, eight consecutive K rows form a 1 KB swizzle atom (stride between atoms along K: 1 KB),
+// `lead_bytes` separates the 64-wide groups of the M / N extent
+__device__ __forceinline__ uint64_t make_desc_mn(uint32_t saddr, uint32_t lead_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr >> 4) & 0x3fffu);
+  d |= (uint64_t)((lead_bytes >> 4) & 0x3fffu) << 16;
+  d |= (uint64_t)((1024u >> 4) & 0x3fffu) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= 2ull << 61;
+  return d;
+}
+
+__global__ void __launch_bounds__(kSumThreads)
+assign_sum_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_c, int S, int H, int k,
+                     const float* __restrict__ cnorm, int32_t* __restrict__ labels, int32_t* __restrict__ hist,
+                     float* __restrict__ psum, int32_t* __restrict__ status) {
+  constexpr int D = 128, NP = 2;
+  constexpr int kA = kTcTok * 128;                   // bytes per token panel
+  constexpr int kB = 3 * kTcCen * 128;               // bytes per centroid panel (three pieces)
+  constexpr int kOH = kTcTok * 128;                  // bytes of a one-hot tile (128 tokens x 64 clusters, BF16)
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw;
+  const uint32_t sbase = smem_u32(smem);
+  constexpr uint32_t offA = 0, offB = kSumBufs * NP * kA, offOH = offB + NP * kB, offBar = offOH + 2 * kOH;
+  auto bar_full = [&](int buf) { return sbase + offBar + 8u * buf; };            // token tile (and, first, centroids) landed
+  auto bar_gdone = [&](int g) { return sbase + offBar + 32u + 8u * g; };         // Gram block of the group's tile done
+  auto bar_tfree = [&](int g) { return sbase + offBar + 48u + 8u * g; };         // ... and read out of tensor memory
+  auto bar_oh = [&](int g) { return sbase + offBar + 64u + 8u * g; };            // the group's one-hot tile is written
+  auto bar_sdone = [&](int g) { return sbase + offBar + 80u + 8u * g; };         // the sums of the group's tile are done
+  volatile int* misc = (volatile int*)(smem + offBar + 96);                       // [0] tmem base, [1] abort
+  volatile int* abort_flag = misc + 1;
+  int* cnt = reinterpret_cast<int*>(smem + offBar + 112);
+
+  const int ntile = (S + kTcTok - 1) / kTcTok;
+  const int per_bh = (ntile + kTcTiles - 1) / kTcTiles;
+  const int h = blockIdx.x % H;
+  const int chunk = (blockIdx.x / H) % per_bh;
+  const int tile0 = chunk * kTcTiles;
+  const int b = blockIdx.x / (H * per_bh);
+  const int bh = b * H + h;
+  const int n = min(kTcTiles, ntile - tile0);        // tiles of this CTA (>= 1)
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if ((sbase & 1023u) != 0) {
+    if (threadIdx.x == 0 && status != nullptr) atomicCAS(status, 0, 55);
+    return;
+  }
+  if (threadIdx.x < kTcCen) cnt[threadIdx.x] = 0;
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kSumBufs; ++i) mbar_init(bar_full(i), 1);
+    for (int g = 0; g < 2; ++g) {
+      mbar_init(bar_gdone(g), 1);
+      mbar_init(bar_tfree(g), 4);                    // one arrival per warp of the group
+      mbar_init(bar_oh(g), 4);
+      mbar_init(bar_sdone(g), 1);
+    }
+    misc[1] = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 256;" ::"r"(sbase + offBar + 96) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = (uint32_t)misc[0];
+  const uint32_t tsum = tmem + 2 * kTcCen;           // 64 columns behind the two Gram buffers
+  const int last_g = (n - 1) & 1;
+  const uint32_t last_par = (uint32_t)(((n - 1) >> 1) & 1);
+
+  if (warp == 8) {
+    // ---- producer: TMA loads and MMA issue, one thread ----
+    if (lane == 0) {
+      auto load_tile = [&](int i) {
+        const int buf = i % kSumBufs;
+#pragma unroll
+        for (int pn = 0; pn < NP; ++pn)
+          tma_load_4d(sbase + offA + (buf * NP + pn) * kA, &tm_x, pn * 64, h, (tile0 + i) * kTcTok, b, bar_full(buf));
+      };
+      mbar_expect_tx(bar_full(0), NP * (kA + kB));
+#pragma unroll
+      for (int pn = 0; pn < NP; ++pn) tma_load_3d(sbase + offB + pn * kB, &tm_c, pn * 64, 0, bh, bar_full(0));
+      load_tile(0);
+      for (int i = 1; i < n && i < kSumBufs; ++i) {
+        mbar_expect_tx(bar_full(i), NP * kA);
+        load_tile(i);
+      }
+      const uint32_t id_gram = make_idesc_bf16(kTcCen);
+      const uint32_t id_sum = make_idesc_bf16(kTcCen) | (1u << 15) | (1u << 16);     // both operands MN-major
+      for (int i = 0; i <= n + 1; ++i) {
+        if (i < n) {
+          const int buf = i % kSumBufs, g = i & 1;
+          if (!mbar_wait(bar_full(buf), (uint32_t)((i / kSumBufs) & 1), abort_flag, status, 51)) break;
+          if (i >= 2 && !mbar_wait(bar_tfree(g), (uint32_t)(((i - 2) >> 1) & 1), abort_flag, status, 53)) break;
+          tc_fence_after();
+          bool first = true;
+#pragma unroll
+          for (int pc = 0; pc < 3; ++pc)
+#pragma unroll
+            for (int pn = 0; pn < NP; ++pn) {
+              const uint64_t da = make_desc(sbase + offA + (buf * NP + pn) * kA, 128);
+              const uint64_t db = make_desc(sbase + offB + pn * kB + pc * (kTcCen * 128), 128);
+#pragma unroll
+              for (int ks = 0; ks < 4; ++ks) {
+                mma_bf16_ss(tmem + g * kTcCen, da + (uint64_t)(ks * 2), db + (uint64_t)(ks * 2), id_gram, first ? 0u : 1u);
+                first = false;
+              }
+            }
+          tc_commit(bar_gdone(g));
+        }
+        if (i >= 1 && i - 1 < n) {
+          const int j = i - 1, g = j & 1;
+          if (!mbar_wait(bar_oh(g), (uint32_t)((j >> 1) & 1), abort_flag, status, 56)) break;
+          tc_fence_after();
+          const uint64_t da = make_desc_mn(sbase + offA + (j % kSumBufs) * NP * kA, kA);
+          const uint64_t db = make_desc_mn(sbase + offOH + g * kOH, 16);
+#pragma unroll
+          for (int ks = 0; ks < kTcTok / 16; ++ks)      // 16 tokens = two 1 KB atoms per step
+            mma_bf16_ss(tsum, da + (uint64_t)(ks * 128), db + (uint64_t)(ks * 128), id_sum, (j > 0 || ks > 0) ? 1u : 0u);
+          tc_commit(bar_sdone(g));
+        }
+        if (i >= 2) {
+          const int j = i - 2;
+          if (j + kSumBufs < n) {
+            // the tile's buffer is free once its sums are done: refill it
+            if (!mbar_wait(bar_sdone(j & 1), (uint32_t)((j >> 1) & 1), abort_flag, status, 54)) break;
+            mbar_expect_tx(bar_full(j % kSumBufs), NP * kA);
+            load_tile(j + kSumBufs);
+          }
+        }
+      }
+    }
+  } else {
+    // ---- consumers: thread == token == TMEM lane of its group's tile ----
+    const int g = warp >> 2, wq = warp & 3;
+    const int row = wq * 32 + lane;                  // token within the tile
+    float cn[kTcCen];
+#pragma unroll
+    for (int c = 0; c < kTcCen; ++c) cn[c] = c < k ? cnorm[(size_t)bh * k + c] : INFINITY;
+    uint8_t* oh_row = smem + offOH + g * kOH + row * 128;
+    for (int i = g; i < n; i += 2) {
+      bool ok = mbar_wait(bar_gdone(g), (uint32_t)((i >> 1) & 1), abort_flag, status, 52);
+      if (!__all_sync(0xffffffffu, ok)) break;
+      tc_fence_after();
+      const uint32_t trow = tmem + g * kTcCen + ((uint32_t)(wq * 32) << 16);
+      uint32_t r0[32], r1[32];
+      LBFQ_TMEM_LD32(r0, trow);
+      LBFQ_TMEM_LD32(r1, trow + 32);
+      tc_wait_ld();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_tfree(g));
+      // argmin over four independent chains of sixteen clusters (ascending within a chain, chains merged in
+      // ascending order with a strict comparison: the lowest index wins ties, as in the one-chain form)
+      float bq[4];
+      int iq[4];
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {
+        bq[q4] = INFINITY;
+        iq[q4] = q4 * 16;
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+          const int cc = q4 * 16 + c;
+          const float dot = __uint_as_float(cc < 32 ? r0[cc] : r1[cc - 32]);
+          const float dist = cn[cc] - 2.0f * dot;
+          if (dist < bq[q4]) { bq[q4] = dist; iq[q4] = cc; }
+        }
+      }
+      float best = bq[0];
+      int best_i = iq[0];
+#pragma unroll
+      for (int q4 = 1; q4 < 4; ++q4)
+        if (bq[q4] < best) { best = bq[q4]; best_i = iq[q4]; }
+      const int tok = (tile0 + i) * kTcTok + row;
+      const bool live = tok < S;
+      // the one-hot tile of the group is free once the sums of its previous tile are done
+      if (i >= 2) {
+        ok = mbar_wait(bar_sdone(g), (uint32_t)(((i - 2) >> 1) & 1), abort_flag, status, 57);
+        if (!__all_sync(0xffffffffu, ok)) break;
+      }
+      const int hot = live ? (best_i >> 3) : -1;                     // 16-byte chunk that holds the 1.0
+      const uint32_t one = 0x3f80u << ((best_i & 1) * 16);            // BF16 1.0 at element best_i & 7 of the chunk
+      const int wi = (best_i & 7) >> 1;
+      const uint4 hot_v = make_uint4(wi == 0 ? one : 0u, wi == 1 ? one : 0u, wi == 2 ? one : 0u, wi == 3 ? one : 0u);
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        const uint4 v = (c == hot) ? hot_v : make_uint4(0u, 0u, 0u, 0u);
+        *reinterpret_cast<uint4*>(oh_row + ((c ^ (row & 7)) << 4)) = v;
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");    // generic-proxy stores, read by the MMA
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_oh(g));
+      if (live) {                                                      // off the path the producer waits on
+        labels[(size_t)bh * S + tok] = best_i;
+        atomicAdd(&cnt[best_i], 1);
+      }
+    }
+    if (g == 0) {
+      // the CTA's sums: lane == channel, one column per cluster
+      const bool ok = mbar_wait(bar_sdone(last_g), last_par, abort_flag, status, 58);
+      if (__all_sync(0xffffffffu, ok && *abort_flag == 0)) {
+        tc_fence_after();
+        const uint32_t trow = tsum + ((uint32_t)(wq * 32) << 16);
+        uint32_t r0[32], r1[32];
+        LBFQ_TMEM_LD32(r0, trow);
+        LBFQ_TMEM_LD32(r1, trow + 32);
+        tc_wait_ld();
+        float* dst = psum + (((size_t)bh * per_bh + chunk) * k) * D + row;
+#pragma unroll
+        for (int c = 0; c < 32; ++c)
+          if (c < k) dst[(size_t)c * D] = __uint_as_float(r0[c]);
+#pragma unroll
+        for (int c = 0; c < 32; ++c)
+          if (32 + c < k) dst[(size_t)(32 + c) * D] = __uint_as_float(r1[c]);
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (hist != nullptr && threadIdx.x < kTcCen)
+    hist[((size_t)bh * per_bh + chunk) * kTcCen + threadIdx.x] = cnt[threadIdx.x];
+  if (warp == 0) {
+    if (*abort_flag && lane == 0) {
+      const long long t0 = wall_ns();
+      while (wall_ns() - t0 < 1000000ll) { }
+    }
+    __syncwarp();
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 256;" ::"r"(tmem) : "memory");
+  }
+}
+
 PFN_cuTensorMapEncodeTiled_v12000 encoder() {
   static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
   if (!fn) {
@@ -254,8 +501,10 @@ int kmeans_tc_chunk_tokens() { return kTcTiles * kTcTok; }
 
 size_t kmeans_tc_split_bytes(int BH, int D) { return (size_t)BH * 3 * kTcCen * D * sizeof(__nv_bfloat16); }
 
+bool kmeans_tc_sums_eligible(int dtype, int D, int k) { return kmeans_tc_eligible(dtype, D, k) && D == 128; }
+
 int kmeans_tc_assign(const void* x, int B, int S, int H, int D, int k, const float* cent, const float* cnorm,
-                     void* split, int32_t* labels, int32_t* hist, int32_t* status, cudaStream_t st) {
+                     void* split, int32_t* labels, int32_t* hist, float* psum, int32_t* status, cudaStream_t st) {
   const int BH = B * H;
   const size_t total = (size_t)BH * kTcCen * D;
   int g = (int)((total + 255) / 256);
@@ -287,6 +536,15 @@ int kmeans_tc_assign(const void* x, int B, int S, int H, int D, int k, const flo
                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     LBFQ_REQUIRE(r == CUDA_SUCCESS, LBFQ_ERR_CUDA, "cuTensorMapEncodeTiled (centroids) failed with code %d", (int)r);
+  }
+  if (psum != nullptr) {
+    LBFQ_REQUIRE(D == 128 && hist != nullptr, LBFQ_ERR_ARG, "the centroid sums ride on the D = 128 assignment and come with the counts");
+    constexpr int kSumSmem = kSumBufs * 2 * kTcTok * 128 + 2 * 3 * kTcCen * 128 + 2 * kTcTok * 128 + 112 + kTcCen * 4;
+    LBFQ_CUDA_OK(cudaFuncSetAttribute(assign_sum_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSumSmem));
+    const int ntile = (S + kTcTok - 1) / kTcTok;
+    const int per_bh = (ntile + kTcTiles - 1) / kTcTiles;
+    assign_sum_tc_kernel<<<BH * per_bh, kSumThreads, kSumSmem, st>>>(mx, mc, S, H, k, cnorm, labels, hist, psum, status);
+    return check_launch("kmeans assign + sums (tensor cores)");
   }
   if (D == 128) return launch_assign<128>(mx, mc, BH, S, H, k, cnorm, labels, hist, status, st);
   return launch_assign<64>(mx, mc, BH, S, H, k, cnorm, labels, hist, status, st);

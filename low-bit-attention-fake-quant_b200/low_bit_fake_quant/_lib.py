@@ -24,7 +24,7 @@ QK_FP8_BLOCK, QK_MX, QK_BF16, QK_BF16_V_CODES = 0, 1, 2, 3
 
 ERR_ARG, ERR_DTYPE, ERR_UNSUPPORTED, ERR_CUDA, ERR_DEVICE = -1, -2, -3, -4, -5
 # debug overrides (LBFQ_FLAG_* of include/lbfq.h)
-FLAG_ATTN_GENERIC, FLAG_KMEANS_FFMA, FLAG_QM_CORR_FFMA, FLAG_UNFUSED_PREPROCESS = 1, 2, 4, 8
+FLAG_ATTN_GENERIC, FLAG_KMEANS_FFMA, FLAG_QM_CORR_FFMA, FLAG_UNFUSED_PREPROCESS, FLAG_KMEANS_SORTED = 1, 2, 4, 8, 16
 
 _DTYPES = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}
 

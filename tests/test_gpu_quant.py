@@ -199,6 +199,12 @@ def test_kmeans_tensor_core_assignment_agrees_with_fp32_assignment(k, D, monkeyp
     ff = kmeans_labels(x, n_clusters=k, max_iters=5, seed=1)
     assert int(tc.min()) >= 0 and int(tc.max()) < k
     assert (tc == ff).float().mean().item() > 0.995
+    # D = 128: the centroid sums are taken inside the assignment kernel (one-hot x tokens on the tensor cores); the
+    # update by sort + segment means is the cross-check. Same sums up to summation order.
+    L.set_flag(L.FLAG_KMEANS_FFMA, False)
+    L.set_flag(L.FLAG_KMEANS_SORTED, True)
+    srt = kmeans_labels(x, n_clusters=k, max_iters=5, seed=1)
+    assert (tc == srt).float().mean().item() > 0.995
 
 
 def test_qm_corr_and_rowmax():
