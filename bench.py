@@ -151,8 +151,12 @@ def load_traffic_table():
 
 def verify_one_head(qp, kp, vp, cfg, head=0, reference_operands=False):
     """Parity of the timed inputs themselves: one head of the padded Q / K / V through the library (same k-means
-    labels injected on both sides) against the CPU oracle in the reference's own operand convention
-    (``faithful=True``), plus MSE / cosine of both against BF16 SDPA. Outside every timed region."""
+    labels injected on both sides) against the CPU oracle -- first in the convention the launched kernel implements
+    (e4m3 codes multiplied directly, scales in FP32 around the MMA; or, with ``--reference-operands``, the
+    reference's BF16 de-quantised operands), which is the parity claim and is held to the tests' bound, then, for
+    the code path, the distance to the reference's BF16-operand convention (the reference's own BF16 rounding of
+    its operands, amplified by the softmax: a property of multiplying real FP8 codes) -- plus the MSE / cosine of
+    each against BF16 SDPA. Outside every timed region."""
     import low_bit_fake_quant as fq
     from low_bit_fake_quant import _lib as L
     from low_bit_fake_quant.kmeans import kmeans_labels
@@ -170,21 +174,50 @@ def verify_one_head(qp, kp, vp, cfg, head=0, reference_operands=False):
         kw["_v_labels"] = kmeans_labels(v1, n_clusters=cfg.v_kmeans_k, max_iters=cfg.v_kmeans_iters, seed=cfg.v_kmeans_seed)
         okw["v_labels"] = kw["_v_labels"].cpu().long()
     got = fq.fake_quant_attention(q1, k1, v1, cfg, _debug_fp32=True, _reference_operands=reference_operands, **kw).float().cpu()
+    p_bf16 = L.lib().lbfq_attention_last_variant() == 1 and cfg.p_requant
     sdpa = fq.reference_attention(q1, k1, v1).float().cpu()
     torch.set_num_threads(os.cpu_count() or 1)
+    qc, kc, vc = q1.cpu(), k1.cpu(), v1.cpu()
     t0 = time.perf_counter()
-    want = OA.fake_quant_attention(q1.cpu(), k1.cpu(), v1.cpu(), cfg, faithful=True, out_fp32=True, **okw)
+    if reference_operands:
+        own = OA.fake_quant_attention(qc, kc, vc, cfg, faithful=True, out_fp32=True, **okw)
+    else:
+        own = OA.fake_quant_attention(qc, kc, vc, cfg, faithful=False, out_fp32=True, p_bf16=p_bf16, **okw)
     dt = time.perf_counter() - t0
-    m = OA.compute_metrics(got, want)
-    rms = float(want.pow(2).mean().sqrt())
-    row_err = (got - want).abs().amax(dim=-1)
-    a, b = OA.compute_metrics(got, sdpa), OA.compute_metrics(want, sdpa)
-    return {"convention": ("reference BF16 operands" if reference_operands else "e4m3 codes multiplied directly")
-                          + " vs the oracle in the reference's BF16-operand convention",
-            "sample": f"head {head} of the timed tensors, S={qp.shape[1]}", "cos": m["cosine"],
-            "max_abs_over_rms": m["max_abs"] / rms, "rows_over_2e-3_rms": float((row_err > 2e-3 * rms).float().mean()),
-            "mse_vs_sdpa": a["mse"], "mse_vs_sdpa_oracle": b["mse"], "cos_vs_sdpa": a["cosine"], "cos_vs_sdpa_oracle": b["cosine"],
-            "oracle_seconds": dt}
+    # the rule of oracle.api.parity_report, with the head's S x S softmax taken in row chunks: rows over 2e-3 x RMS
+    # must stay within what one e4m3 code step of their largest P value can move them, and be few
+    rms = float(own.double().pow(2).mean().sqrt())
+    row_err = (got - own).abs().amax(dim=-1)[0, :, 0]
+    qf, kf = qc.float()[0, :, 0], kc.float()[0, :, 0]
+    w_max = torch.empty(qf.shape[0])
+    for r0 in range(0, qf.shape[0], 4096):
+        w_max[r0:r0 + 4096] = torch.softmax((qf[r0:r0 + 4096] @ kf.t()) / math.sqrt(qf.shape[-1]), dim=-1).amax(dim=-1)
+    tol = 2e-3 * rms
+    flip_bound = tol + 2.0 * 0.125 * (2.0 * w_max).clamp_max(1.0) * vc.float().abs().max().item()
+    a64, b64 = got.double().flatten(), own.double().flatten()
+    rep = {"cosine": float(torch.dot(a64, b64) / (a64.norm() * b64.norm())), "max_abs_over_rms": float((a64 - b64).abs().max()) / rms,
+           "flip_row_fraction": float((row_err > tol).float().mean()), "rows_over_flip_bound": int((row_err > flip_bound).sum())}
+    ok = rep["cosine"] >= 0.99999 and rep["rows_over_flip_bound"] == 0 and rep["flip_row_fraction"] <= 0.01
+    out = {"sample": f"head {head} of the timed tensors, S={qp.shape[1]}",
+           "kernel_convention": "reference BF16 operands" if reference_operands else "e4m3 codes multiplied directly, scales in FP32",
+           "vs_oracle_in_kernel_convention": {"cosine": rep["cosine"], "max_abs_over_rms": rep["max_abs_over_rms"],
+                                              "rows_with_an_e4m3_code_flip": rep["flip_row_fraction"],
+                                              "rows_over_the_code_flip_bound": rep["rows_over_flip_bound"],
+                                              "within_bound": bool(ok),
+                                              "bound": "cosine >= 0.99999, max-abs <= 2e-3 x RMS outside rows where one P "
+                                                       "value took the neighbouring e4m3 code (<= 1 % of the rows)"},
+           "mse_vs_sdpa": OA.compute_metrics(got, sdpa)["mse"], "mse_vs_sdpa_oracle": OA.compute_metrics(own, sdpa)["mse"],
+           "oracle_seconds": dt}
+    if not reference_operands:
+        ref_conv = OA.fake_quant_attention(qc, kc, vc, cfg, faithful=True, out_fp32=True, **okw)
+        r64 = ref_conv.double().flatten()
+        rms = float(r64.pow(2).mean().sqrt())
+        out["distance_to_reference_bf16_operand_convention"] = {
+            "cosine": float(torch.dot(a64, r64) / (a64.norm() * r64.norm())), "max_abs_over_rms": float((a64 - r64).abs().max()) / rms,
+            "mse_vs_sdpa_reference_convention": OA.compute_metrics(ref_conv, sdpa)["mse"],
+            "note": "the reference rounds its de-quantised operands to BF16 before multiplying; FP8 MMAs multiply the codes "
+                    "exactly. --reference-operands runs the reference's convention itself"}
+    return out
 
 
 class ClockSampler:
