@@ -124,6 +124,32 @@ def test_debug_flags_round_trip():
     assert lib.lbfq_get_flags() == before
 
 
+def test_flag_constants_match_the_header():
+    header = open(os.path.join(ROOT, "include", "lbfq.h")).read()
+    defined = {name: int(val) for name, val in re.findall(r"#define LBFQ_(FLAG_[A-Z_]+) (\d+)", header)}
+    assert defined and all(getattr(L, name) == val for name, val in defined.items())
+    assert len(set(defined.values())) == len(defined) and all(v & (v - 1) == 0 for v in defined.values())    # distinct bits
+
+
+def test_host_entry_chunk_schedule():
+    """The heads chunks of the host-buffer entry: default sizes, the tapered tail, an explicit schedule and its checks."""
+    from low_bit_fake_quant.config import QuantConfig
+    from low_bit_fake_quant.host import _chunk_bounds
+    plain = QuantConfig(q_kmeans_k=None, v_kmeans_k=None)
+    km = QuantConfig(q_kmeans_k=8, v_kmeans_k=None)
+    for cfg, h in ((plain, 40), (km, 40), (plain, 5), (km, 3)):
+        b = _chunk_bounds(h, cfg, None, None)
+        assert b[0][0] == 0 and b[-1][1] == h and all(x[1] == y[0] for x, y in zip(b, b[1:])) and all(x[1] > x[0] for x in b)
+    assert [hi - lo for lo, hi in _chunk_bounds(40, km, None, None)] == [8] * 5
+    assert [hi - lo for lo, hi in _chunk_bounds(40, plain, None, None)][-3:] == [2, 1, 1]      # the tail tapers to one head
+    assert _chunk_bounds(40, km, None, [2, 5, 10, 19, 4]) == [(0, 2), (2, 7), (7, 17), (17, 36), (36, 40)]
+    for bad in ([], [40, 0], [20, 19], [41]):
+        with pytest.raises(ValueError, match="chunk_heads"):
+            _chunk_bounds(40, km, None, bad)
+    with pytest.raises(ValueError, match="heads_per_chunk"):
+        _chunk_bounds(40, km, 0, None)
+
+
 def test_head_dimension_is_checked_before_any_launch():
     x = torch.zeros(1, 256, 1, 32, dtype=torch.bfloat16)
 

@@ -58,3 +58,19 @@ def test_static_scratch_refuses_oversized_shapes():
     assert b"built-in array" in lib.lbfq_last_error()
     with pytest.raises(ValueError):
         L.check(rc)
+
+
+def test_static_scratch_mean_only_form():
+    """``out = NULL`` asks for the channel mean alone (the form the K quantizer with fused smoothing uses): the same
+    mean as the full call, and nothing else is written."""
+    torch.manual_seed(1)
+    with torch.cuda.device(DEV):
+        k = (torch.randn(2, 777, 3, 128) + 1.5).bfloat16().to(DEV)
+        b, s, h, d = k.shape
+        _, mean_full, _, _ = _both(k)
+        mean_only = torch.full((b, h, d), float("nan"), dtype=torch.float32, device=DEV)
+        lib = L.lib()
+        L.check(lib.lbfq_smooth_k_static(k.data_ptr(), L.dtype_code(k.dtype), b, s, h, d, None, mean_only.data_ptr(),
+                                         L.stream_ptr(k.device)))
+        torch.cuda.synchronize()
+        assert torch.equal(mean_only, mean_full)
