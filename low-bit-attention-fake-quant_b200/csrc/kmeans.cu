@@ -395,9 +395,11 @@ static size_t scratch_layout(int BH, int S, int D, int k, uint8_t* base, KmScrat
   uint8_t* p3 = take((size_t)BH * (k + 1) * 4);
   uint8_t* p4 = take(kmeans_tc_split_bytes(BH, D));       // BF16 pieces of the centroids (tensor-core assignment)
   const size_t nchunk = ((size_t)S + kmeans_tc_chunk_tokens() - 1) / kmeans_tc_chunk_tokens();
-  uint8_t* p5 = take((size_t)BH * nchunk * kSortMaxK * 4);   // per-chunk label counts from the tensor-core assignment
+  const size_t nsum = (size_t)kmeans_tc_sum_chunks_max(S);   // chunks of the assignment that also takes the sums
+  const size_t nhist = nchunk > nsum ? nchunk : nsum;
+  uint8_t* p5 = take((size_t)BH * nhist * kSortMaxK * 4);    // per-chunk label counts from the tensor-core assignment
   // partial sums of the cluster means: per part of a sorted segment, or per chunk of the tensor-core assignment
-  const size_t parts = nchunk > (size_t)mean_parts(k) ? nchunk : (size_t)mean_parts(k);
+  const size_t parts = nsum > (size_t)mean_parts(k) ? nsum : (size_t)mean_parts(k);
   uint8_t* p6 = take((size_t)BH * k * parts * D * 4);
   if (out) { out->split = p4; out->hist = (int32_t*)p5; out->psum = (float*)p6; }
   if (out) { out->cent = (float*)p0; out->cnorm = (float*)p1; out->order32 = (int32_t*)p2; out->seg = (int32_t*)p3; }
@@ -448,7 +450,7 @@ extern "C" int lbfq_kmeans_labels(const void* x, int dtype, int B, int S, int H,
       if (int rc = kmeans_tc_assign(x, B, S, H, D, k, sc.cent, sc.cnorm, sc.split, labels, more ? sc.hist : nullptr,
                                     (more && tcsum) ? sc.psum : nullptr, status, st)) return rc;
       if (more && tcsum) {
-        chunk_mean_kernel<<<BH * k, 128, 0, st>>>(sc.psum, sc.hist, D, k, (S + 1023) / 1024, sc.cent, sc.cnorm);
+        chunk_mean_kernel<<<BH * k, 128, 0, st>>>(sc.psum, sc.hist, D, k, kmeans_tc_sum_chunks(BH, S), sc.cent, sc.cnorm);
         if (int rc = check_launch("kmeans update (chunk sums)")) return rc;
         continue;
       }

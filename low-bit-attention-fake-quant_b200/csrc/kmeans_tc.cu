@@ -250,7 +250,7 @@ __device__ __forceinline__ uint64_t make_desc_mn(uint32_t saddr, uint32_t lead_b
 
 __global__ void __launch_bounds__(kSumThreads)
 assign_sum_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_c, int S, int H, int k,
-                     const float* __restrict__ cnorm, int32_t* __restrict__ labels, int32_t* __restrict__ hist,
+                     int tiles_per_cta, const float* __restrict__ cnorm, int32_t* __restrict__ labels, int32_t* __restrict__ hist,
                      float* __restrict__ psum, int32_t* __restrict__ status) {
   constexpr int D = 128, NP = 2;
   constexpr int kA = kTcTok * 128;                   // bytes per token panel
@@ -270,13 +270,13 @@ assign_sum_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_cons
   int* cnt = reinterpret_cast<int*>(smem + offBar + 112);
 
   const int ntile = (S + kTcTok - 1) / kTcTok;
-  const int per_bh = (ntile + kTcTiles - 1) / kTcTiles;
+  const int per_bh = (ntile + tiles_per_cta - 1) / tiles_per_cta;
   const int h = blockIdx.x % H;
   const int chunk = (blockIdx.x / H) % per_bh;
-  const int tile0 = chunk * kTcTiles;
+  const int tile0 = chunk * tiles_per_cta;
   const int b = blockIdx.x / (H * per_bh);
   const int bh = b * H + h;
-  const int n = min(kTcTiles, ntile - tile0);        // tiles of this CTA (>= 1)
+  const int n = min(tiles_per_cta, ntile - tile0);   // tiles of this CTA (>= 1)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if ((sbase & 1023u) != 0) {
     if (threadIdx.x == 0 && status != nullptr) atomicCAS(status, 0, 55);
@@ -503,6 +503,35 @@ size_t kmeans_tc_split_bytes(int BH, int D) { return (size_t)BH * 3 * kTcCen * D
 
 bool kmeans_tc_sums_eligible(int dtype, int D, int k) { return kmeans_tc_eligible(dtype, D, k) && D == 128; }
 
+// Tiles per CTA of the assignment-with-sums kernel. It holds one CTA per SM, so a launch is a number of waves of
+// CTAs each of which pays a prologue and a drain (about five tile times: measured 17 us per CTA of eight tiles) that
+// no neighbour hides: the count that minimises waves x (tiles + 5) for this problem and this GPU, between 4 tiles
+// (the scratch is sized for that) and one CTA per slab.
+constexpr int kSumMinTiles = 4;
+int kmeans_tc_sum_tiles(int BH, int S) {
+  const int ntile = (S + kTcTok - 1) / kTcTok;
+  const int sms = sm_count();
+  int best = kTcTiles;
+  long long best_cost = -1;
+  for (int t = kSumMinTiles; t <= ntile || t == kSumMinTiles; ++t) {
+    const long long ctas = (long long)BH * ((ntile + t - 1) / t);
+    const long long waves = (ctas + sms - 1) / sms;
+    const long long cost = waves * (t + 5);
+    if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = t; }
+    if (t >= ntile) break;
+  }
+  return best;
+}
+int kmeans_tc_sum_chunks(int BH, int S) {
+  const int ntile = (S + kTcTok - 1) / kTcTok;
+  const int t = kmeans_tc_sum_tiles(BH, S);
+  return (ntile + t - 1) / t;
+}
+int kmeans_tc_sum_chunks_max(int S) {
+  const int ntile = (S + kTcTok - 1) / kTcTok;
+  return (ntile + kSumMinTiles - 1) / kSumMinTiles;
+}
+
 int kmeans_tc_assign(const void* x, int B, int S, int H, int D, int k, const float* cent, const float* cnorm,
                      void* split, int32_t* labels, int32_t* hist, float* psum, int32_t* status, cudaStream_t st) {
   const int BH = B * H;
@@ -541,9 +570,10 @@ int kmeans_tc_assign(const void* x, int B, int S, int H, int D, int k, const flo
     LBFQ_REQUIRE(D == 128 && hist != nullptr, LBFQ_ERR_ARG, "the centroid sums ride on the D = 128 assignment and come with the counts");
     constexpr int kSumSmem = kSumBufs * 2 * kTcTok * 128 + 2 * 3 * kTcCen * 128 + 2 * kTcTok * 128 + 112 + kTcCen * 4;
     LBFQ_CUDA_OK(cudaFuncSetAttribute(assign_sum_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSumSmem));
+    const int tiles = kmeans_tc_sum_tiles(BH, S);
     const int ntile = (S + kTcTok - 1) / kTcTok;
-    const int per_bh = (ntile + kTcTiles - 1) / kTcTiles;
-    assign_sum_tc_kernel<<<BH * per_bh, kSumThreads, kSumSmem, st>>>(mx, mc, S, H, k, cnorm, labels, hist, psum, status);
+    const int per_bh = (ntile + tiles - 1) / tiles;
+    assign_sum_tc_kernel<<<BH * per_bh, kSumThreads, kSumSmem, st>>>(mx, mc, S, H, k, tiles, cnorm, labels, hist, psum, status);
     return check_launch("kmeans assign + sums (tensor cores)");
   }
   if (D == 128) return launch_assign<128>(mx, mc, BH, S, H, k, cnorm, labels, hist, status, st);
