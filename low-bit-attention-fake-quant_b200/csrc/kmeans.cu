@@ -359,29 +359,6 @@ segment_mean_from_parts_kernel(const float* __restrict__ psum, const int32_t* __
   if (threadIdx.x == 0) cnorm[bh * k + c] = red[0] + red[1] + red[2] + red[3];
 }
 
-// centroids from the per-chunk sums and counts the tensor-core assignment leaves behind: chunks added in order
-__global__ void __launch_bounds__(128)
-chunk_mean_kernel(const float* __restrict__ psum, const int32_t* __restrict__ hist, int D, int k, int nchunk,
-                  float* __restrict__ cent, float* __restrict__ cnorm) {
-  __shared__ float red[4];
-  const int c = blockIdx.x % k;
-  const size_t bh = blockIdx.x / k;
-  int n = 0;
-  for (int ch = 0; ch < nchunk; ++ch) n += hist[(bh * nchunk + ch) * kSortMaxK + c];
-  if (n == 0) return;                               // empty cluster keeps centroid and norm
-  float v = 0.f;
-  if (threadIdx.x < D) {
-    float s = 0.f;
-    for (int ch = 0; ch < nchunk; ++ch) s += psum[((bh * nchunk + ch) * k + c) * D + threadIdx.x];
-    v = __fdiv_rn(s, (float)n);
-    cent[(bh * k + c) * D + threadIdx.x] = v;
-  }
-  const float s2 = warp_sum(v * v);
-  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s2;
-  __syncthreads();
-  if (threadIdx.x == 0) cnorm[bh * k + c] = red[0] + red[1] + red[2] + red[3];
-}
-
 struct KmScratch {
   float* cent; float* cnorm; int32_t* order32; int32_t* seg; void* split; int32_t* hist; float* psum;
 };
@@ -447,11 +424,11 @@ extern "C" int lbfq_kmeans_labels(const void* x, int dtype, int B, int S, int H,
     if (tc) {
       // the counts (and sums) are only wanted when an update follows (not after the last assignment)
       const bool more = it + 1 < iters;
+      // (after an update from the sums the BF16 pieces of the centroids are current already)
       if (int rc = kmeans_tc_assign(x, B, S, H, D, k, sc.cent, sc.cnorm, sc.split, labels, more ? sc.hist : nullptr,
-                                    (more && tcsum) ? sc.psum : nullptr, status, st)) return rc;
+                                    (more && tcsum) ? sc.psum : nullptr, tcsum && it > 0, status, st)) return rc;
       if (more && tcsum) {
-        chunk_mean_kernel<<<BH * k, 128, 0, st>>>(sc.psum, sc.hist, D, k, kmeans_tc_sum_chunks(BH, S), sc.cent, sc.cnorm);
-        if (int rc = check_launch("kmeans update (chunk sums)")) return rc;
+        if (int rc = kmeans_tc_update_from_sums(sc.psum, sc.hist, BH, S, D, k, sc.cent, sc.cnorm, sc.split, st)) return rc;
         continue;
       }
     } else {

@@ -46,6 +46,42 @@ __global__ void split_centroids_kernel(const float* __restrict__ cent, int BH, i
   }
 }
 
+// centroids from the per-chunk sums and counts the assignment-with-sums kernel leaves behind (chunks added in order),
+// their squared norms, and their three BF16 pieces for the next assignment
+__global__ void __launch_bounds__(128)
+chunk_mean_kernel(const float* __restrict__ psum, const int32_t* __restrict__ hist, int D, int k, int nchunk,
+                  float* __restrict__ cent, float* __restrict__ cnorm, __nv_bfloat16* __restrict__ split) {
+  __shared__ float red[4];
+  const int c = blockIdx.x % k;
+  const size_t bh = blockIdx.x / k;
+  int n = 0;
+  for (int ch = 0; ch < nchunk; ++ch) n += hist[(bh * nchunk + ch) * kTcCen + c];
+  if (n == 0) return;                               // empty cluster keeps centroid, norm and pieces
+  float v = 0.f;
+  if (threadIdx.x < D) {
+    float s = 0.f;
+    for (int ch = 0; ch < nchunk; ++ch) s += psum[((bh * nchunk + ch) * k + c) * D + threadIdx.x];
+    v = __fdiv_rn(s, (float)n);
+    cent[(bh * k + c) * D + threadIdx.x] = v;
+    float r = v;
+    const __nv_bfloat16 hi = __float2bfloat16_rn(r);
+    r -= __bfloat162float(hi);
+    const __nv_bfloat16 mid = __float2bfloat16_rn(r);
+    r -= __bfloat162float(mid);
+    const __nv_bfloat16 lo = __float2bfloat16_rn(r);
+    __nv_bfloat16* o = split + (bh * 3 * kTcCen + c) * D + threadIdx.x;
+    o[0] = hi;
+    o[(size_t)kTcCen * D] = mid;
+    o[(size_t)2 * kTcCen * D] = lo;
+  }
+  float s2 = v * v;
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) s2 += __shfl_xor_sync(0xffffffffu, s2, off);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s2;
+  __syncthreads();
+  if (threadIdx.x == 0) cnorm[bh * k + c] = red[0] + red[1] + red[2] + red[3];
+}
+
 // One CTA walks kTcTiles consecutive 128-token tiles of one (b, h): the centroid pieces are loaded once, the token
 // tiles go through two shared-memory buffers and two 64-column TMEM buffers. A producer warp (one thread) issues the
 // TMA loads two tiles ahead and the MMAs; four consumer warps take the argmin of a tile while the next one is being
@@ -532,14 +568,23 @@ int kmeans_tc_sum_chunks_max(int S) {
   return (ntile + kSumMinTiles - 1) / kSumMinTiles;
 }
 
+int kmeans_tc_update_from_sums(const float* psum, const int32_t* hist, int BH, int S, int D, int k, float* cent,
+                               float* cnorm, void* split, cudaStream_t st) {
+  chunk_mean_kernel<<<BH * k, 128, 0, st>>>(psum, hist, D, k, kmeans_tc_sum_chunks(BH, S), cent, cnorm, (__nv_bfloat16*)split);
+  return check_launch("kmeans update (chunk sums)");
+}
+
 int kmeans_tc_assign(const void* x, int B, int S, int H, int D, int k, const float* cent, const float* cnorm,
-                     void* split, int32_t* labels, int32_t* hist, float* psum, int32_t* status, cudaStream_t st) {
+                     void* split, int32_t* labels, int32_t* hist, float* psum, bool split_current, int32_t* status,
+                     cudaStream_t st) {
   const int BH = B * H;
-  const size_t total = (size_t)BH * kTcCen * D;
-  int g = (int)((total + 255) / 256);
-  if (g > sm_count() * 8) g = sm_count() * 8;
-  split_centroids_kernel<<<g, 256, 0, st>>>(cent, BH, k, D, (__nv_bfloat16*)split);
-  if (int rc = check_launch("kmeans centroid split")) return rc;
+  if (!split_current) {
+    const size_t total = (size_t)BH * kTcCen * D;
+    int g = (int)((total + 255) / 256);
+    if (g > sm_count() * 8) g = sm_count() * 8;
+    split_centroids_kernel<<<g, 256, 0, st>>>(cent, BH, k, D, (__nv_bfloat16*)split);
+    if (int rc = check_launch("kmeans centroid split")) return rc;
+  }
 
   auto enc = encoder();
   LBFQ_REQUIRE(enc != nullptr, LBFQ_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");

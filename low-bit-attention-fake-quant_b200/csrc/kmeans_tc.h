@@ -20,6 +20,12 @@ bool kmeans_tc_sums_eligible(int dtype, int D, int k);
 // the problem size and the GPU), and the largest value that can take for a sequence length (scratch sizing)
 int kmeans_tc_sum_chunks(int BH, int S);
 int kmeans_tc_sum_chunks_max(int S);
+// split_current: the BF16 pieces in `split` already match `cent` (kmeans_tc_update_from_sums wrote both)
 int kmeans_tc_assign(const void* x, int B, int S, int H, int D, int k, const float* cent, const float* cnorm,
-                     void* split, int32_t* labels, int32_t* hist, float* psum, int32_t* status, cudaStream_t st);
+                     void* split, int32_t* labels, int32_t* hist, float* psum, bool split_current, int32_t* status,
+                     cudaStream_t st);
+// centroids, their norms and their BF16 pieces from the per-chunk sums and counts of the last kmeans_tc_assign with
+// psum: chunks added in a fixed order; an empty cluster keeps what it had
+int kmeans_tc_update_from_sums(const float* psum, const int32_t* hist, int BH, int S, int D, int k, float* cent,
+                               float* cnorm, void* split, cudaStream_t st);
 }  // namespace lbfq

@@ -72,12 +72,33 @@ prep_fused_kernel(const PrepParams p) {
   {
     constexpr int kChunkElems = 16 / sizeof(T);                // elements per 16-byte copy
     const int cpr = D / kChunkElems;                           // copies per row
-    for (int idx = threadIdx.x; idx < G * cpr; idx += kThreads) {
-      const int r = idx / cpr, c = idx % cpr;
-      const int64_t srow = p.order ? p.order[bh * p.S + s0 + r] : (int64_t)(s0 + r);
-      const uint4 v = *reinterpret_cast<const uint4*>(x + (((size_t)b * p.S + srow) * p.H + h) * D + c * kChunkElems);
-      *reinterpret_cast<uint4*>(tile + (size_t)r * D + c * kChunkElems) = v;
+    // A row is 128 or 256 bytes somewhere in a (B, S, H, D) tensor: what hides the latency of such a gather is the
+    // number of copies in flight. Eight row indices are fetched first, then eight asynchronous 16-byte copies go
+    // straight from global to shared memory; nothing waits before the whole tile has been requested.
+    constexpr int kBatch = 8;
+    const int total = G * cpr;
+    const uint32_t tile_s = (uint32_t)__cvta_generic_to_shared(tile);
+    for (int base = threadIdx.x; base < total; base += kThreads * kBatch) {
+      int64_t srow[kBatch];
+#pragma unroll
+      for (int u = 0; u < kBatch; ++u) {
+        const int idx = base + u * kThreads;
+        const int r = min(idx, total - 1) / cpr;
+        srow[u] = p.order ? p.order[bh * p.S + s0 + r] : (int64_t)(s0 + r);
+      }
+#pragma unroll
+      for (int u = 0; u < kBatch; ++u) {
+        const int idx = base + u * kThreads;
+        if (idx < total) {
+          const int r = idx / cpr, c = idx % cpr;
+          const T* src = x + (((size_t)b * p.S + srow[u]) * p.H + h) * D + c * kChunkElems;
+          const uint32_t dst = tile_s + (uint32_t)(((size_t)r * D + c * kChunkElems) * sizeof(T));
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+        }
+      }
     }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
   }
   __syncthreads();
 
