@@ -344,6 +344,9 @@ def main():
     ap.add_argument("--blasst-tile-predicate", action="store_true",
                     help="BLASST drops a key block only when all rows of a 128-row tile agree (the predicate of the "
                          "reference's simulator) instead of row by row; zero fill")
+    ap.add_argument("--blasst-sweep", action="store_true",
+                    help="BLASST workloads: also time the grid lambda in {1e-4, 1e-3, 1e-2} x fill in {zero, mean_a1.5, "
+                         "uta16_a1.5} on the same tensors (config.blasst_sweep)")
     ap.add_argument("--brick", default=None,
                     help="ts,hs,ws: take the video workload's tokens brick by brick over its (21, 30, 52) grid (the reference's "
                          "space-time block reorder); the permutation of Q / K / V and of the result is inside the timed step")
@@ -562,6 +565,16 @@ def main():
             blasst = dict(blasst_skip_ratios(sq, sk_, sv, cfg, args.blasst_tile_predicate), blasst_lambda=cfg.blasst_lambda, blasst_fill=cfg.blasst_fill)
             if args.brick is not None:
                 blasst["brick"] = args.brick
+            if args.blasst_sweep and world == 1:
+                grid = []
+                for lam in (1e-4, 1e-3, 1e-2):
+                    for fill in ("zero", "mean_a1.5", "uta16_a1.5"):
+                        c2 = QuantConfig(**{**cfg_kwargs, "blasst_lambda": lam, "blasst_fill": fill})
+                        g_ms, g_kms, _ = timed(lambda: step(qp, kp, vp, c2), max(3, args.steps // 2), 2)
+                        r = blasst_skip_ratios(sq, sk_, sv, c2, args.blasst_tile_predicate)
+                        grid.append({"blasst_lambda": lam, "blasst_fill": fill, "ms_per_step": g_ms, "kernel_ms": g_kms,
+                                     "row_skip_ratio": r["row_skip_ratio"], "tile_skip_ratio": r["tile_skip_ratio"]})
+                blasst["sweep"] = grid
         p_note = {"dynamic": "P re-scaled per (row, block) and handed to a BF16 P.V as the reference rounds it",
                   "elementwise": "P as e4m3 codes, FP8 P.V"}.get(cfg.p_quant, "P per the V kind")
         line = {
