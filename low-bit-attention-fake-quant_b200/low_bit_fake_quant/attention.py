@@ -382,9 +382,7 @@ def _prepare_fused(q, k, v, cfg: QuantConfig, *, head_offset: int = 0, total_hea
         q_order, q_inv = order_from_labels(lab, cfg.q_kmeans_k)
         q_km = KMeansReorderResult(tensor_reordered=None, order=q_order, inverse_order=q_inv, labels=lab.to(torch.int64))
     k_mean = k_channel_mean(k) if cfg.smoothing in ("k_only", "full") else None       # over K in its own order
-    if side is not None:
-        torch.cuda.current_stream(q.device).wait_stream(side)
-    elif cfg.v_kmeans_k is not None:
+    if side is None and cfg.v_kmeans_k is not None:
         lab = v_labels if v_labels is not None else kmeans_labels(
             v, n_clusters=cfg.v_kmeans_k, max_iters=cfg.v_kmeans_iters, seed=cfg.v_kmeans_seed, head_offset=head_offset,
             total_heads=total_heads)
@@ -396,6 +394,8 @@ def _prepare_fused(q, k, v, cfg: QuantConfig, *, head_offset: int = 0, total_hea
     mx = cfg.qk_quant == "mxfp8"
     qc, qs, qm, q_sf, _ = prep_fused(q, kind=qk_kind, scale_block=qk_block, order=q_order, smooth_block=q_sb,
                                      hadamard=cfg.qk_hadamard, signs=signs, layout=L.LAYOUT_BHSD, s_pad=sq_pad, want_scale_e8=mx)
+    if side is not None:
+        torch.cuda.current_stream(q.device).wait_stream(side)       # K and V follow V's order; Q did not need it
     kc, ks, _, k_sf, k_smooth = prep_fused(k, kind=qk_kind, scale_block=qk_block, order=v_order, chan_mean=k_mean,
                                            hadamard=cfg.qk_hadamard, signs=signs, layout=L.LAYOUT_BHSD, s_pad=s_pad,
                                            want_scale_e8=mx, want_prepared=full)

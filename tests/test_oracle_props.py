@@ -23,7 +23,7 @@ def test_pow2_scale_is_exact_ceil_log2():
         assert OQ.pow2_scale(amax).item() == 2.0 ** k
         up = torch.nextafter(amax, torch.tensor([float("inf")]))
         assert OQ.pow2_scale(up).item() == 2.0 ** (k + 1)
-    # the survey's edge: amax = 1.75 * 2^k is the largest bf16 mantissa below 2 -> 448 = 1.75 * 256
+    # the edge case: amax = 1.75 * 2^k is the largest bf16 mantissa below 2 -> 448 = 1.75 * 256
     assert OQ.pow2_scale(torch.tensor([1.75 * 2.0 ** 3])).item() == 2.0 ** -5
     assert OQ.pow2_scale(torch.tensor([1e-4])).item() == 2.0 ** math.ceil(math.log2(1e-4 / 448.0))
 
