@@ -93,6 +93,9 @@ def k12_attention(
     blasst_fill_alpha: float = 1.0,
     blasst_uta_bins: int = 16,
     blasst_tile_rows: int = 0,
+    row_index: Optional[torch.Tensor] = None,
+    p_probe: Optional[dict] = None,
+    p_flip=None,
     faithful: Optional[bool] = None,
     p_bf16: Optional[bool] = None,
     return_stats: bool = False,
@@ -106,7 +109,16 @@ def k12_attention(
 
     ``blasst_tile_rows`` > 0 replaces the kernel's row-by-row skip decision by the tile-level one of the reference's
     simulator (blasst_skip.py:573-585): a key block is dropped only when every row of a tile of that many query rows
-    finds it under the threshold, and then for all of them (zero fill)."""
+    finds it under the threshold, and then for all of them (zero fill).
+
+    Aids for checking a claim of the parity tests -- that a row outside the tolerance differs from this restatement
+    by ONE e4m3 code step of one P value that sits on a rounding boundary: ``row_index`` (1-D int64) computes only those
+    query rows (the result then has ``len(row_index)`` rows, in that order; no stats); ``p_probe`` (a dict) receives
+    ``quotient`` -- what went into the e4m3 rounding, ``p`` or ``p / s_P``, (B,H,rows,N) --, ``codes``, the rounded
+    values, ``p_used``, the values that entered P.V, and ``row_max``, the reference max of each key's block; ``p_flip = (row, key, step)``, or a list of such triples, moves the code of P[row, key] (row counted within the
+    computed rows) by ``step`` = +1 / -1 e4m3 code steps before it is used; ``(row, key, step, "bf16")`` moves the
+    BF16-rounded value ``bf16(code x s_P)`` of the scaled P modes by one BF16 ulp instead (the reference's second
+    rounding, attention_triton.py:353-360)."""
     B, H, M, D = q_op.shape
     N = k_op.shape[2]
     if faithful is None:
@@ -128,6 +140,21 @@ def k12_attention(
     if rowmax_est is not None and rowmax_init is not None:
         raise ValueError("rowmax_init_bhs and rowmax_est_bhs are mutually exclusive")
 
+    if row_index is not None:
+        if return_stats or blasst_tile_rows:
+            raise ValueError("row_index computes single rows: no stats tensor, no tile-level predicate")
+        row_index = row_index.to(torch.int64)
+        q_op = q_op[:, :, row_index]
+        row_scale = row_scale[:, :, row_index] if row_scale is not None else None
+        rowmax_est = rowmax_est[:, :, row_index] if rowmax_est is not None else None
+        rowmax_init = rowmax_init[:, :, row_index] if rowmax_init is not None else None
+        M = int(row_index.numel())
+    if p_probe is not None:
+        p_probe["quotient"] = torch.zeros((B, H, M, N))
+        p_probe["codes"] = torch.zeros((B, H, M, N))
+        p_probe["p_scaled"] = torch.zeros((B, H, M, N))        # codes x s_P, before the BF16 rounding of the scaled modes
+        p_probe["p_used"] = torch.zeros((B, H, M, N))          # the P values that entered P.V
+        p_probe["row_max"] = torch.zeros((B, H, M, N))         # the reference max the key's block was taken against
     q_op = q_op.float()
     k_op = k_op.float()
     v_op = v_op.float()
@@ -135,7 +162,7 @@ def k12_attention(
     off = _f32(float(p_max_offset))
     sm = _f32(float(sm_scale))
 
-    rows = torch.arange(M)
+    rows = torch.arange(M) if row_index is None else row_index
     if qm is not None:
         # attention_triton.py:121-124: one qm vector per program (M block)
         grp = ((rows // block_m) * block_m) // q_smooth_block
@@ -277,18 +304,41 @@ def k12_attention(
 
         l_i = l_i * alpha + p.sum(dim=-1)                                  # :326 (pre-quantisation p)
 
+        flips = [p_flip] if isinstance(p_flip, tuple) else (p_flip or [])
+
+        def rounded(quotient):
+            codes = to_e4m3(quotient).float()
+            for r_f, key_f, step_f, *kind_f in flips:
+                if not kind_f and n0 <= key_f < n1:
+                    c_f = key_f - n0
+                    bits = codes[..., r_f, c_f].to(torch.float8_e4m3fn).view(torch.uint8).to(torch.int16) + int(step_f)
+                    codes[..., r_f, c_f] = bits.clamp(0, 0x7E).to(torch.uint8).view(torch.float8_e4m3fn).float()
+            if p_probe is not None:
+                p_probe["quotient"][..., n0:n1] = quotient
+                p_probe["codes"][..., n0:n1] = codes
+            return codes
+
         if pk == 0:                                                        # :331
-            p_rec = to_e4m3(p).float()
+            p_rec = rounded(p)
         elif pk == 1:                                                      # :338-347
             amax = p.abs().amax(dim=-1).clamp_min(1e-4)
             s_p = pow2_scale(amax)
-            p_rec = to_e4m3(p / s_p[..., None]).float() * s_p[..., None]
+            p_rec = rounded(p / s_p[..., None]) * s_p[..., None]
         else:                                                              # :353-360
             amax = p.abs().amax(dim=-1).clamp_min(1e-12)
             s_p = amax * INV_FP8_MAX              # the GPU's `amax / 448` (see oracle/quant_ops.py)
-            p_rec = to_e4m3(divide(p, s_p[..., None])).float() * s_p[..., None]
+            p_rec = rounded(divide(p, s_p[..., None])) * s_p[..., None]
+        if p_probe is not None:
+            p_probe["p_scaled"][..., n0:n1] = p_rec
         if p_bf16:
             p_rec = p_rec.to(torch.bfloat16).float()
+            for r_f, key_f, step_f, *kind_f in flips:                      # ("bf16",): one BF16 ulp of the rounded value
+                if kind_f and kind_f[0] == "bf16" and n0 <= key_f < n1:
+                    bits = p_rec[..., r_f, key_f - n0].to(torch.bfloat16).view(torch.int16) + int(step_f)
+                    p_rec[..., r_f, key_f - n0] = bits.view(torch.bfloat16).float()
+        if p_probe is not None:
+            p_probe["p_used"][..., n0:n1] = p_rec
+            p_probe["row_max"][..., n0:n1] = m_ij[..., None]
 
         pv = torch.matmul(p_rec, v_op[:, :, n0:n1])                        # :363
         if v_block_scale is not None:                                      # :365-372

@@ -96,3 +96,106 @@ def _p_bf16(cfg):
     applies the scale in FP32."""
     from low_bit_fake_quant import _lib as L
     return L.lib().lbfq_attention_last_variant() == 1 and cfg.p_requant
+
+
+def _e4m3_neighbours(c):
+    """Next lower / higher e4m3 value of non-negative e4m3 values (FP32 tensors)."""
+    bits = c.to(torch.float8_e4m3fn).view(torch.uint8).to(torch.int16)
+    dn = (bits - 1).clamp(0, 0x7E).to(torch.uint8).view(torch.float8_e4m3fn).float()
+    up = (bits + 1).clamp(0, 0x7E).to(torch.uint8).view(torch.float8_e4m3fn).float()
+    return dn, up
+
+
+def _bf16_neighbours(x):
+    """Next lower / higher BF16 value of positive BF16 values (FP32 tensors)."""
+    bits = x.to(torch.bfloat16).view(torch.int16)
+    return (bits - 1).view(torch.bfloat16).float(), (bits + 1).view(torch.bfloat16).float()
+
+
+@pytest.mark.parametrize("name", ["wan14b_self_attn_k_smooth_static", "wan14b_self_attn_full_dynamic"])
+def test_rows_outside_the_tolerance_are_single_rounding_flips(name):
+    """The rows of the previous test that exceed 2e-3 x RMS are claimed to differ from the oracle by ONE rounding
+    decision of a P value that sits on a rounding boundary: an e4m3 code step, or -- in the scaled P modes, where the
+    reference rounds ``p_fp8 x s_P`` to BF16 before P.V (attention_triton.py:353-360) -- one BF16 ulp of a heavy P
+    value (the rows concerned are strongly peaked: one key carries most of the weight, and one BF16 ulp of its P is
+    2^-8 of the row). Checked here on the worst rows: the oracle recomputes the row with one such value moved to its
+    neighbour, and the kernel's row must then be within the tolerance (a second move is allowed for, a third is not).
+    The oracle is run on the row alone, which is itself a slightly different summation order from the full run."""
+    cfg = QuantConfig(**bench.WORKLOADS[name][0])
+    q, k, v = bench.make_inputs(1, 1, bench.S_REAL, bench.D_HEAD, 1234, DEV)
+    q, k, v, _ = bench.pad_like_hook(q, k, v, cfg)
+    kw, okw = {}, {}
+    inv = None
+    if cfg.q_kmeans_k is not None:
+        kw["_q_labels"] = kmeans_labels(q, n_clusters=cfg.q_kmeans_k)
+        okw["q_labels"] = kw["_q_labels"].cpu().long()
+        inv = OA.reorder_from_labels(q.cpu(), okw["q_labels"]).inverse_order[0]
+    if cfg.v_kmeans_k is not None:
+        kw["_v_labels"] = kmeans_labels(v, n_clusters=cfg.v_kmeans_k)
+        okw["v_labels"] = kw["_v_labels"].cpu().long()
+    got = fq.fake_quant_attention(q, k, v, cfg, _debug_fp32=True, **kw).float().cpu()
+    raise_if_device_error(torch.device(DEV))
+    p_bf16 = bool(_p_bf16(cfg)) and cfg.p_quant != "elementwise"
+    qc, kc, vc = q.cpu(), k.cpu(), v.cpu()
+    torch.set_num_threads(os.cpu_count() or 1)
+    common = dict(faithful=False, out_fp32=True, p_bf16=p_bf16, **okw)
+    want = OA.fake_quant_attention(qc, kc, vc, cfg, **common)
+    tol = 2e-3 * want.pow(2).mean().sqrt().item()
+    row_err = (got - want).abs().amax(dim=-1)[0, :, 0]
+    flagged = torch.nonzero(row_err > tol).flatten()
+    if flagged.numel() == 0:
+        pytest.skip("no row outside the tolerance on these inputs")
+    worst = flagged[torch.argsort(row_err[flagged], descending=True)][:3]
+    explained = []
+    for r in worst.tolist():
+        pos = torch.tensor([int(inv[r]) if inv is not None else r])
+        moves = []
+        for _ in range(2):                                       # at most two moves per row
+            probe = {}
+            base = _with_moves(qc, kc, vc, cfg, common, pos, moves, probe)
+            if (got[0, r, 0] - base).abs().max().item() <= tol:
+                break
+            x, c = probe["quotient"][0, 0, 0], probe["codes"][0, 0, 0]
+            dn, up = _e4m3_neighbours(c)
+            # distance of the quotient to the two rounding boundaries of its code, in code steps
+            d_up = ((c + up) / 2 - x).abs() / (up - c).clamp_min(1e-30)
+            d_dn = (x - (c + dn) / 2).abs() / (c - dn).clamp_min(1e-30)
+            d = torch.minimum(torch.where(up > c, d_up, torch.full_like(x, 9.0)), torch.where(c > dn, d_dn, torch.full_like(x, 9.0)))
+            # weight of each P value in the row's result (up to the common 1 / l): its value, brought to the row's last
+            # reference max
+            m_row = probe["row_max"][0, 0, 0]
+            weight = probe["p_used"][0, 0, 0] * torch.exp2((m_row - m_row[-1]) * 1.4426950408889634)
+            near = torch.nonzero(d < 5e-3).flatten()              # within 1/200 of a code step of a boundary
+            near = near[torch.argsort(weight[near], descending=True)][:6]
+            cands = [((n, 1 if d_up[n] <= d_dn[n] else -1), float(d[n]), "e4m3") for n in near.tolist()]
+            if p_bf16:
+                ps, pu = probe["p_scaled"][0, 0, 0], probe["p_used"][0, 0, 0]
+                lo, hi = _bf16_neighbours(pu)
+                for n in torch.argsort(weight, descending=True)[:3].tolist():     # the three heaviest values
+                    for step, nb in ((1, hi[n]), (-1, lo[n])):
+                        ulp = abs(float(nb - pu[n]))
+                        dist = abs(float(ps[n]) - (float(pu[n]) + float(nb)) / 2) / max(ulp, 1e-30)
+                        cands.append(((n, step, "bf16"), dist, "bf16"))
+            best = None
+            for move, dist, kind in cands:
+                cand = _with_moves(qc, kc, vc, cfg, common, pos, moves + [move], None)
+                err = (got[0, r, 0] - cand).abs().max().item()
+                if best is None or err < best[0]:
+                    best = (err, move, dist, kind)
+            assert best is not None, (name, r, "no P value of this row lies near a rounding boundary")
+            moves.append(best[1])
+            explained.append({"row": r, "key": best[1][0], "step": best[1][1], "rounding": best[3],
+                              "boundary_distance_in_steps": best[2], "heaviest_weight": float(weight.max() / weight.sum()),
+                              "error_over_tol_before": row_err[r].item() / tol, "after": best[0] / tol})
+        final = _with_moves(qc, kc, vc, cfg, common, pos, moves, None)
+        assert (got[0, r, 0] - final).abs().max().item() <= tol, (name, explained)
+        assert len(moves) <= 2
+    print(f"\n[rows outside the tolerance] {name}: {int(flagged.numel())} of {row_err.numel()}; worst explained by: {explained}")
+    # the values that were moved sat within 1/200 of a step of the rounding boundary in question
+    assert all(e["boundary_distance_in_steps"] < 5e-3 for e in explained), explained
+
+
+def _with_moves(qc, kc, vc, cfg, common, pos, moves, probe):
+    """Row ``pos`` (kernel row order) of the oracle with the listed rounding moves applied."""
+    flips = [(0,) + tuple(m) for m in moves] or None
+    return OA.fake_quant_attention(qc, kc, vc, cfg, rows=pos, p_probe=probe, p_flip=flips, **common)[0, 0, 0]
