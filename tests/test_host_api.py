@@ -140,7 +140,7 @@ def test_host_entry_chunk_schedule():
     for cfg, h in ((plain, 40), (km, 40), (plain, 5), (km, 3)):
         b = _chunk_bounds(h, cfg, None, None)
         assert b[0][0] == 0 and b[-1][1] == h and all(x[1] == y[0] for x, y in zip(b, b[1:])) and all(x[1] > x[0] for x in b)
-    assert [hi - lo for lo, hi in _chunk_bounds(40, km, None, None)] == [8] * 5
+    assert [hi - lo for lo, hi in _chunk_bounds(40, km, None, None)] == [2, 6, 8, 8, 8, 8]       # a short first chunk
     assert [hi - lo for lo, hi in _chunk_bounds(40, plain, None, None)][-3:] == [2, 1, 1]      # the tail tapers to one head
     assert _chunk_bounds(40, km, None, [2, 5, 10, 19, 4]) == [(0, 2), (2, 7), (7, 17), (17, 36), (36, 40)]
     for bad in ([], [40, 0], [20, 19], [41]):
