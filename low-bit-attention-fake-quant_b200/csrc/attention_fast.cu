@@ -715,11 +715,13 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         // producer: (h + m + l) * (h' + m' + l') without the three smallest cross terms
         // (the sum has to see the BF16 rounding of P: summing the FP32 products instead moved the result by up to
         // 4e-3 of its RMS with dynamic P, whose few distinct codes per row and block round alike)
-        float2 rs2 = make_float2(0.f, 0.f);
+        float r0 = 0.f, r1 = 0.f, r2 = 0.f, r3 = 0.f;
 #pragma unroll
-        for (int w = 0; w < PW; ++w)
-          rs2 = __fadd2_rn(rs2, make_float2(__uint_as_float(pk[w] << 16), __uint_as_float(pk[w] & 0xffff0000u)));
-        float rs = rs2.x + rs2.y;
+        for (int w = 0; w < PW; w += 2) {
+          add_bf16x2_f32(r0, r1, pk[w]);
+          add_bf16x2_f32(r2, r3, pk[w + 1]);
+        }
+        float rs = (r0 + r1) + (r2 + r3);
         const __nv_bfloat16 rh = __float2bfloat16_rn(rs);
         rs -= __bfloat162float(rh);
         const __nv_bfloat16 rm = __float2bfloat16_rn(rs);

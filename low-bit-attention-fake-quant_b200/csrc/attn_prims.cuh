@@ -246,18 +246,26 @@ __device__ __forceinline__ uint32_t f32x4_to_e4m3x4(float a, float b, float c, f
 // two FP32 -> e4m3 (round-to-nearest-even, saturating) -> times `scale` in FP32 -> two BF16 in one word (a low):
 // what the reference hands to its P.V product for the scaled P modes (attention_triton.py:338-360)
 __device__ __forceinline__ uint32_t e4m3_round_scale_bf16x2(float a, float b, float scale) {
-  uint32_t r;
-  asm("{\n\t.reg .b16 c, lo, hi;\n\t.reg .b32 h2;\n\t.reg .f32 fa, fb;\n\t"
-      "cvt.rn.satfinite.e4m3x2.f32 c, %2, %1;\n\t"
+  float fa, fb;
+  asm("{\n\t.reg .b16 c, lo, hi;\n\t.reg .b32 h2;\n\t"
+      "cvt.rn.satfinite.e4m3x2.f32 c, %3, %2;\n\t"
       "cvt.rn.f16x2.e4m3x2 h2, c;\n\t"
       "mov.b32 {lo, hi}, h2;\n\t"
-      "cvt.f32.f16 fa, lo;\n\t"
-      "cvt.f32.f16 fb, hi;\n\t"
-      "mul.rn.f32 fa, fa, %3;\n\t"
-      "mul.rn.f32 fb, fb, %3;\n\t"
-      "cvt.rn.bf16x2.f32 %0, fb, fa;\n\t}"
-      : "=r"(r) : "f"(a), "f"(b), "f"(scale));
+      "cvt.f32.f16 %0, lo;\n\t"
+      "cvt.f32.f16 %1, hi;\n\t}"
+      : "=f"(fa), "=f"(fb) : "f"(a), "f"(b));
+  // both products in one packed multiplication: each half rounds like mul.rn.f32
+  const float2 pr = __fmul2_rn(make_float2(fa, fb), make_float2(scale, scale));
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %2, %1;" : "=r"(r) : "f"(pr.x), "f"(pr.y));
   return r;
+}
+
+// acc += the two BF16 halves of `w`, each widened exactly (mixed-precision add, sm_100): lo into a, hi into b
+__device__ __forceinline__ void add_bf16x2_f32(float& a, float& b, uint32_t w) {
+  asm("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %2;\n\t"
+      "add.rn.f32.bf16 %0, lo, %0;\n\tadd.rn.f32.bf16 %1, hi, %1;\n\t}"
+      : "+f"(a), "+f"(b) : "r"(w));
 }
 
 // max of three (max.f32 with three inputs, sm_100): NaN operands are dropped like fmaxf does
