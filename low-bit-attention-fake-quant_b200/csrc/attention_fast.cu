@@ -915,14 +915,37 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       const uint32_t id_qk = make_idesc(BN);
       const uint32_t id_pv = make_idesc(D);
       const uint32_t id_pv_bf16 = make_idesc_bf16(D);
-      const uint64_t dq = make_desc(sbase + SM::offQ + t * SM::kQ, D);
+      // Descriptors differ from one stage / key block to the next only in their 14-bit start-address field (16-byte
+      // units; shared memory ends below 2^18 bytes, so adding to the whole word never carries out of the field).
+      const uint64_t dq = QB == 0 ? make_desc(sbase + SM::offQ + t * SM::kQ, D) : make_desc(sbase + SM::offQ + t * SM::kQ, 128);
+      const uint64_t dk0 = QB == 0 ? make_desc(sbase + SM::offK, D) : make_desc(sbase + SM::offK, 128);
+      const uint64_t dv0 = PK == 0 ? make_desc(sbase + SM::offV, kChunk) : make_desc(sbase + SM::offV, 128);
+      [[maybe_unused]] const uint64_t da0 = make_desc(sbase + SM::offAext, 32);
+      // smoothing blocks of 64 keys or of whole stages (the launcher admits nothing else here): tile index by shift
+      [[maybe_unused]] const int sl_shift = min(p.v_smooth_block, kChunk) == 64 ? 6 : 7;
       bool ok = mbar_wait(BAR_QFULL(t), 0, abort_flag, p.status, 31);
-      auto issue_qk = [&](int j) -> bool {
-        const int c = j / NSUB, sub = j % NSUB, st = c % kFastStages;
-        if (sub == 0 && !mbar_wait(BAR_KFULL(st), (c / kFastStages) & 1, abort_flag, p.status, 32)) return false;
-        tc_fence_after();
+      // The two instruction streams of this thread, each with its position in the ring of key stages: Q.K^T runs two
+      // key blocks ahead of P.V. `ready` waits for the stage a block starts (long landed when its turn comes) and
+      // forms the block's descriptors; `issue` only issues. The loop below calls `ready` for both streams *before*
+      // it waits for P, so that nothing but the MMAs themselves stands between "P is ready" and "S of block it + 2
+      // is ready", the round trip the softmax warps wait for.
+      struct Pos { int sub, st; uint32_t par; };
+      Pos qk{0, 0, 0u}, pv{0, 0, 0u};
+      auto advance = [&](Pos& x) {
+        if (++x.sub == NSUB) {
+          x.sub = 0;
+          if (++x.st == kFastStages) { x.st = 0; x.par ^= 1u; }
+        }
+      };
+      uint64_t dk = 0, dv = 0;
+      [[maybe_unused]] uint64_t da = 0;
+      auto ready_qk = [&]() -> bool {
+        if (qk.sub == 0 && !mbar_wait(BAR_KFULL(qk.st), qk.par, abort_flag, p.status, 32)) return false;
+        dk = dk0 + (uint64_t)((qk.st * SM::kK + qk.sub * BN * (QB == 0 ? D : 128)) >> 4);
+        return true;
+      };
+      auto issue_qk = [&](int j) {
         if constexpr (QB == 0) {
-          const uint64_t dk = make_desc(sbase + SM::offK + st * SM::kK + sub * BN * D, D);
 #pragma unroll
           for (int kk = 0; kk < D / 32; ++kk)
             mma_f8_ss(tS + (j & 1) * S_STRIDE, dq + (uint64_t)(kk * 2), dk + (uint64_t)(kk * 2), id_qk, kk > 0 ? 1u : 0u);
@@ -930,26 +953,34 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           // BF16: K steps of 16 channels, four per 64-channel panel
           const uint32_t id_qk_bf16 = make_idesc_bf16(BN);
 #pragma unroll
-          for (int kk = 0; kk < D / 16; ++kk) {
-            const uint64_t da = make_desc(sbase + SM::offQ + t * SM::kQ + (kk >> 2) * (kTileM * 128), 128) + (uint64_t)((kk & 3) * 2);
-            const uint64_t db = make_desc(sbase + SM::offK + st * SM::kK + (kk >> 2) * (kChunk * 128) + sub * BN * 128, 128) +
-                                (uint64_t)((kk & 3) * 2);
-            mma_bf16_ss(tS + (j & 1) * S_STRIDE, da, db, id_qk_bf16, kk > 0 ? 1u : 0u);
-          }
+          for (int kk = 0; kk < D / 16; ++kk)
+            mma_bf16_ss(tS + (j & 1) * S_STRIDE, dq + (uint64_t)((((kk >> 2) * (kTileM * 128)) >> 4) + (kk & 3) * 2),
+                        dk + (uint64_t)((((kk >> 2) * (kChunk * 128)) >> 4) + (kk & 3) * 2), id_qk_bf16, kk > 0 ? 1u : 0u);
         }
         tc_commit(BAR_SFULL(t, j & 1));
-        if (sub == NSUB - 1 || j == nblk - 1) tc_commit(BAR_KFREE(st));
-        return true;
+      };
+      auto retire_qk = [&](int j) {
+        if (qk.sub == NSUB - 1 || j == nblk - 1) tc_commit(BAR_KFREE(qk.st));
+        advance(qk);
       };
       unsigned long long n_elided = 0;
-      auto issue_pv = [&](int j) -> bool {
-        const int c = j / NSUB, sub = j % NSUB, st = c % kFastStages;
+      auto ready_pv = [&]() -> bool {
         // (the stage's V is awaited even when no P.V reads it: a stage is handed back only once its load has landed)
-        if (sub == 0 && !mbar_wait(BAR_VFULL(st), (c / kFastStages) & 1, abort_flag, p.status, 33)) return false;
+        if (pv.sub == 0 && !mbar_wait(BAR_VFULL(pv.st), pv.par, abort_flag, p.status, 33)) return false;
         if constexpr (VALPHA) {
-          if (sub == 0 && !mbar_wait(BAR_SIDEFULL(st), (c / kFastStages) & 1, abort_flag, p.status, 37)) return false;
+          if (pv.sub == 0 && !mbar_wait(BAR_SIDEFULL(pv.st), pv.par, abort_flag, p.status, 37)) return false;
         }
-        tc_fence_after();
+        const int key0 = pv.sub * BN;
+        if constexpr (PK == 0) {
+          dv = dv0 + (uint64_t)((pv.st * SM::kV) >> 4) + (uint64_t)(key0 >> 4);
+        } else {
+          // keys key0 ... of the stage: panel key0 / 64, (key0 % 64) keys = 2 bytes each into its rows
+          dv = dv0 + (uint64_t)((pv.st * SM::kV + (key0 >> 6) * (D * 128)) >> 4) + (uint64_t)(((key0 & 63) * 2) >> 4);
+        }
+        if constexpr (VALPHA) da = da0 + (uint64_t)(((pv.st * 2 + (key0 >> sl_shift)) * SM::kAext) >> 4);
+        return true;
+      };
+      auto issue_pv = [&](int j) {
         bool elide = false;
         if constexpr (TV) {
           // every row of the tile skipped this block: there is no P. (Never the first block: a row's running max
@@ -960,43 +991,50 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         if (elide) {
           // the commits below still fire: they track the operations issued so far
         } else if constexpr (PK == 0) {
-          const uint64_t dv = make_desc(sbase + SM::offV + st * SM::kV, kChunk);
 #pragma unroll
           for (int kk = 0; kk < BN / 32; ++kk)
-            mma_f8_ts(tO, tS + (j & 1) * S_STRIDE + kk * 8, dv + (uint64_t)((sub * BN + kk * 32) >> 4), id_pv,
-                      (j > 0 || kk > 0) ? 1u : 0u);
+            mma_f8_ts(tO, tS + (j & 1) * S_STRIDE + kk * 8, dv + (uint64_t)(kk * 2), id_pv, (j > 0 || kk > 0) ? 1u : 0u);
         } else {
-          // keys sub * BN ... of the stage: panel (sub * BN) / 64, (sub * BN) % 64 keys = 2 bytes each into its rows
-          const int key0 = sub * BN;
-          const uint64_t dv = make_desc(sbase + SM::offV + st * SM::kV + (key0 >> 6) * (D * 128), 128) +
-                              (uint64_t)(((key0 & 63) * 2) >> 4);
 #pragma unroll
           for (int kk = 0; kk < BN / 16; ++kk)
             mma_bf16_ts(tO, tS + (j & 1) * S_STRIDE + kk * 8, dv + (uint64_t)(kk * 2), id_pv_bf16,
                         (j > 0 || kk > 0) ? 1u : 0u);
-          if constexpr (VALPHA) {
-            // one more K step: the row-sum pieces (TMEM columns 32..39 of the block's buffer) against alpha' pieces
-            const int sl = key0 / min(p.v_smooth_block, kChunk);
-            mma_bf16_ts(tO, tS + (j & 1) * S_STRIDE + 32, make_desc(sbase + SM::offAext + (st * 2 + sl) * SM::kAext, 32),
-                        id_pv_bf16, 1u);
-          }
+          // one more K step: the row-sum pieces (TMEM columns 32..39 of the block's buffer) against alpha' pieces
+          if constexpr (VALPHA) mma_bf16_ts(tO, tS + (j & 1) * S_STRIDE + 32, da, id_pv_bf16, 1u);
         }
+      };
+      // (a commit covers everything this thread has issued so far: the stage hand-backs below may follow the next
+      // Q.K^T, they only fire a little later)
+      auto retire_pv = [&](int j) {
         if (j == nblk - 2) tc_commit(BAR_PENULT(t));
         if (j == nblk - 1) tc_commit(BAR_ODONE(t));
-        if (sub == NSUB - 1 || j == nblk - 1) {
-          tc_commit(BAR_VFREE(st));
-          if constexpr (VALPHA) tc_commit(BAR_SIDEFREE(st));
+        if (pv.sub == NSUB - 1 || j == nblk - 1) {
+          tc_commit(BAR_VFREE(pv.st));
+          if constexpr (VALPHA) tc_commit(BAR_SIDEFREE(pv.st));
         }
-        return true;
+        advance(pv);
       };
-      if (ok) ok = issue_qk(0);
-      if (ok && nblk > 1) ok = issue_qk(1);
+      for (int j = 0; j < 2 && j < nblk && ok; ++j) {
+        ok = ready_qk();
+        if (ok) {
+          tc_fence_after();
+          issue_qk(j);
+          retire_qk(j);
+        }
+      }
       for (int it = 0; it < nblk && ok; ++it) {
         // P.V of this block once its P is in TMEM (and the rows that raised their max are rescaled), then
         // Q.K^T of block it + 2 into the S buffer that P has just been read from
-        ok = mbar_wait(BAR_PRDY(t, it & 1), (it >> 1) & 1, abort_flag, p.status, 35);
-        if (ok) ok = issue_pv(it);
-        if (ok && it + 2 < nblk) ok = issue_qk(it + 2);
+        const bool more_qk = it + 2 < nblk;
+        ok = ready_pv();
+        if (ok && more_qk) ok = ready_qk();
+        if (ok) ok = mbar_wait(BAR_PRDY(t, it & 1), (it >> 1) & 1, abort_flag, p.status, 35);
+        if (!ok) break;
+        tc_fence_after();
+        issue_pv(it);
+        if (more_qk) issue_qk(it + 2);                 // the softmax warps wait for this one: nothing else comes first
+        retire_pv(it);
+        if (more_qk) retire_qk(it + 2);
       }
       if constexpr (TV) {
         if (p.elided != nullptr && n_elided != 0) atomicAdd(p.elided, n_elided);
