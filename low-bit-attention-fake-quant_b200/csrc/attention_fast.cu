@@ -172,7 +172,7 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       mbar_init(BAR_KFREE(s), 2);
       mbar_init(BAR_VFREE(s), 2);
       mbar_init(BAR_SIDEFULL(s), 1);
-      mbar_init(BAR_SIDEFREE(s), (CORR ? kFastSoftmaxWarps : 0) + (VALPHA ? 2 : 0) + ((CORR || VALPHA) ? 0 : 1));
+      mbar_init(BAR_SIDEFREE(s), CORR ? kFastSoftmaxWarps : 1);      // the bias rows' readers; the alpha' tiles go with V
     }
     misc[1] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -885,7 +885,8 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           tma_load_3d(sbase + SM::offV + st * SM::kV + D * 128, &tm_v, c * kChunk + 64, 0, bh, BAR_VFULL(st));
         }
         if constexpr (CORR || VALPHA) {
-          if (c >= kFastStages && !mbar_wait(BAR_SIDEFREE(st), ((c / kFastStages) - 1) & 1, abort_flag, p.status, 23)) break;
+          // (the alpha' tiles are read by the same MMAs as V^T: the wait for the V stage above covers them)
+          if (CORR && c >= kFastStages && !mbar_wait(BAR_SIDEFREE(st), ((c / kFastStages) - 1) & 1, abort_flag, p.status, 23)) break;
           const int vsb_c = min(p.v_smooth_block, kChunk);          // keys per V-smoothing tile within a stage
           const int ntile = VALPHA ? kChunk / vsb_c : 0;
           mbar_expect_tx(BAR_SIDEFULL(st), (CORR ? 2 * kChunk * 4 : 0) + ntile * SM::kAext);
@@ -1010,7 +1011,6 @@ attn_fast_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         if (j == nblk - 1) tc_commit(BAR_ODONE(t));
         if (pv.sub == NSUB - 1 || j == nblk - 1) {
           tc_commit(BAR_VFREE(pv.st));
-          if constexpr (VALPHA) tc_commit(BAR_SIDEFREE(pv.st));
         }
         advance(pv);
       };
