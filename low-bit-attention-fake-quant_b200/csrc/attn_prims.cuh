@@ -63,6 +63,16 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
       : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
   return ok != 0;
 }
+// Non-blocking test of a phase
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
 // One probe that may park the thread for up to `ns` nanoseconds while the phase is pending (the hardware
 // wakes it as soon as the phase completes), so that a waiting warp does not compete for issue slots.
 __device__ __forceinline__ bool mbar_try_parked(uint32_t bar, uint32_t parity, uint32_t ns) {
